@@ -1,0 +1,125 @@
+// CPU build of the per-edge / per-atom arithmetic headers used by the CUDA
+// kernels, exposed with a C ABI so pytest can check them against the oracle
+// with ctypes.  Test infrastructure only: nothing in the product links this.
+#include <cstring>
+#include "../tace_b200/csrc/tace_math.cuh"
+#include "../tace_b200/csrc/tp_gen.cuh"
+
+using namespace tace;
+
+template <typename T>
+static void build_G(const short* gs, const unsigned char* gy, const double* gc, int ng, const T* Y, T* G) {
+  for (int i = 0; i < ng; ++i) {
+    T s = 0;
+    for (int k = gs[i]; k < gs[i + 1]; ++k) s += T(gc[k]) * Y[gy[k]];
+    G[i] = s;
+  }
+}
+
+#define TP_CASE(TAG)                                                                            \
+  if (mode == 0) {                                                                              \
+    double xx[TP_##TAG::NX], ww[TP_##TAG::NP], aa[TP_##TAG::NM], G[TP_##TAG::NG];               \
+    memcpy(xx, x, sizeof xx); memcpy(ww, w, sizeof ww); memset(aa, 0, sizeof aa);               \
+    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
+    tp_fwd_##TAG<double>(xx, G, ww, aa); memcpy(out0, aa, sizeof aa);                           \
+  } else if (mode == 1) {                                                                       \
+    double gg[TP_##TAG::NM], ww[TP_##TAG::NP], dx[TP_##TAG::NX], G[TP_##TAG::NG];               \
+    memcpy(gg, g, sizeof gg); memcpy(ww, w, sizeof ww); memset(dx, 0, sizeof dx);               \
+    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
+    tp_bwdx_##TAG<double>(gg, G, ww, dx); memcpy(out0, dx, sizeof dx);                          \
+  } else {                                                                                      \
+    double xx[TP_##TAG::NX], gg[TP_##TAG::NM], ww[TP_##TAG::NP], dw[TP_##TAG::NP];              \
+    double dY[TP_##TAG::D], G[TP_##TAG::NG];                                                    \
+    memcpy(xx, x, sizeof xx); memcpy(gg, g, sizeof gg); memcpy(ww, w, sizeof ww);               \
+    memset(dY, 0, sizeof dY);                                                                   \
+    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
+    tp_bwdw_##TAG<double>(xx, gg, G, ww, dw, dY);                                               \
+    memcpy(out0, dw, sizeof dw); memcpy(out1, dY, sizeof dY);                                   \
+  }                                                                                             \
+  return 0;
+
+extern "C" {
+
+// mode 0: forward (out0 = message components); 1: d/dx (out0); 2: d/dw (out0) and d/dY (out1)
+int h_tp(int L, int scalar_src, int mode, const double* x, const double* Y, const double* w, const double* g,
+         double* out0, double* out1) {
+  if (L == 1 && scalar_src) { TP_CASE(L1_S) }
+  if (L == 1 && !scalar_src) { TP_CASE(L1_F) }
+  if (L == 2 && scalar_src) { TP_CASE(L2_S) }
+  if (L == 2 && !scalar_src) { TP_CASE(L2_F) }
+  if (L == 3 && scalar_src) { TP_CASE(L3_S) }
+  if (L == 3 && !scalar_src) { TP_CASE(L3_F) }
+  return -1;
+}
+
+int h_tp_dims(int L, int scalar_src, int* dims) {
+#define DIMS(TAG) { dims[0] = TP_##TAG::NP; dims[1] = TP_##TAG::NX; dims[2] = TP_##TAG::NM; dims[3] = TP_##TAG::D; return 0; }
+  if (L == 1 && scalar_src) DIMS(L1_S)
+  if (L == 1 && !scalar_src) DIMS(L1_F)
+  if (L == 2 && scalar_src) DIMS(L2_S)
+  if (L == 2 && !scalar_src) DIMS(L2_F)
+  if (L == 3 && scalar_src) DIMS(L3_S)
+  if (L == 3 && !scalar_src) DIMS(L3_F)
+  return -1;
+}
+
+#define PB_CASE(TAG)                                                                 \
+  {                                                                                  \
+    double aa[PB_##TAG::D], bb[PB_##TAG::NB], da[PB_##TAG::D];                       \
+    memcpy(aa, a, sizeof aa);                                                        \
+    if (mode == 0) { pb_fwd_##TAG<double>(aa, bb); memcpy(out, bb, sizeof bb); }     \
+    else { memcpy(bb, db, sizeof bb); memset(da, 0, sizeof da);                      \
+           pb_bwd_##TAG<double>(aa, bb, da); memcpy(out, da, sizeof da); }           \
+    return PB_##TAG::NB;                                                             \
+  }
+
+// mode 0: b = A x A (out = b); mode 1: da from db.  Returns the number of b components.
+int h_pb(int L, int last, int mode, const double* a, const double* db, double* out) {
+  if (L == 1 && !last) PB_CASE(L1_A)
+  if (L == 1 && last) PB_CASE(L1_T)
+  if (L == 2 && !last) PB_CASE(L2_A)
+  if (L == 2 && last) PB_CASE(L2_T)
+  if (L == 3 && !last) PB_CASE(L3_A)
+  if (L == 3 && last) PB_CASE(L3_T)
+  return -1;
+}
+
+void h_sh(int L, const double* n, double* Y) {
+  if (L == 1) { double y[4]; sh_eval<double, 1>(n[0], n[1], n[2], y); memcpy(Y, y, sizeof y); }
+  if (L == 2) { double y[9]; sh_eval<double, 2>(n[0], n[1], n[2], y); memcpy(Y, y, sizeof y); }
+  if (L == 3) { double y[16]; sh_eval<double, 3>(n[0], n[1], n[2], y); memcpy(Y, y, sizeof y); }
+}
+
+void h_sh_grad(int L, const double* n, const double* dY, double* dn) {
+  double g[3];
+  if (L == 1) { double y[4]; memcpy(y, dY, sizeof y); sh_grad<double, 1>(n[0], n[1], n[2], y, g); }
+  if (L == 2) { double y[9]; memcpy(y, dY, sizeof y); sh_grad<double, 2>(n[0], n[1], n[2], y, g); }
+  if (L == 3) { double y[16]; memcpy(y, dY, sizeof y); sh_grad<double, 3>(n[0], n[1], n[2], y, g); }
+  memcpy(dn, g, sizeof g);
+}
+
+void h_radial(double d, double rc, int p, double* b, double* db) {
+  double bb[kNumBessel], dd[kNumBessel];
+  RadialParams<double> rp;
+  for (int n = 0; n < kNumBessel; ++n) rp.w[n] = (n + 1) * 3.14159265358979323846 / rc;
+  rp.pref = std::sqrt(2.0 / rc); rp.rc = rc; rp.p = p;
+  radial_eval<double>(d, rp, bb, dd);
+  memcpy(b, bb, sizeof bb); memcpy(db, dd, sizeof dd);
+}
+
+void h_mlp(const double* b, const double* A0, const double* A1, const double* A2, const double* A1t,
+           const double* A2t, const double* dh3, double* h3, double* db) {
+  double bb[kNumBessel], hh[kHidden], dh[kHidden], dbb[kNumBessel];
+  memcpy(bb, b, sizeof bb); memcpy(dh, dh3, sizeof dh);
+  mlp_hidden_fwd<double>(bb, A0, A1, A2, hh);
+  mlp_hidden_bwd<double>(bb, A0, A1, A2, A1t, A2t, dh, dbb);
+  memcpy(h3, hh, sizeof hh); memcpy(db, dbb, sizeof dbb);
+}
+
+void h_edge_grad(const double* v, double dd, const double* dn, double* g) {
+  double vv[3] = {v[0], v[1], v[2]}, dnn[3] = {dn[0], dn[1], dn[2]}, gg[3];
+  const double d0 = std::sqrt(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+  edge_vector_grad<double>(vv, d0, d0 + 1e-9, dd, dnn, gg);
+  memcpy(g, gg, sizeof gg);
+}
+}

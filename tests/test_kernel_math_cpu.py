@@ -1,0 +1,168 @@
+"""The arithmetic headers the CUDA kernels are built from, compiled for the CPU and checked
+against the oracle (values) and autograd (hand-written derivatives)."""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import o3
+from oracle import model as om
+
+DP = ctypes.POINTER(ctypes.c_double)
+
+
+def ptr(a):
+    return a.ctypes.data_as(DP)
+
+
+def paths_and_layout(L, in1, outs):
+    paths = [(l1, l2, l3) for l3 in outs for l1 in in1 for l2 in range(L + 1)
+             if abs(l1 - l2) <= l3 <= l1 + l2 and (l1 + l2 + l3) % 2 == 0]
+    k = {l: sum(1 for p in paths if p[2] == l) for l in outs}
+    base, acc = {}, 0
+    for l in outs:
+        base[l] = acc
+        acc += (2 * l + 1) * k[l]
+    cnt = {l: 0 for l in outs}
+    idx = []
+    for (_, _, l3) in paths:
+        idx.append([base[l3] + m3 * k[l3] + cnt[l3] for m3 in range(2 * l3 + 1)])
+        cnt[l3] += 1
+    return paths, idx, acc
+
+
+def oracle_tp(L, scalar_src, x, Y, w):
+    in1 = [0] if scalar_src else list(range(L + 1))
+    irr1 = o3.Irreps([(1, l) for l in in1])
+    irr2 = o3.Irreps.spherical_harmonics(L)
+    paths, out = om.generate_paths(o3.Irreps([(1, l) for l in range(L + 1)]), irr1, irr2, "uvu")
+    tp = om.TensorProduct(irr1, irr2, out, paths)
+    return tp(x[None], Y[None], w[None])[0], out
+
+
+@pytest.mark.parametrize("L", [1, 2, 3])
+@pytest.mark.parametrize("scalar_src", [True, False])
+def test_interaction_tp_matches_oracle(cpu_harness, L, scalar_src):
+    torch.manual_seed(L * 2 + scalar_src)
+    dims = (ctypes.c_int * 4)()
+    assert cpu_harness.h_tp_dims(L, int(scalar_src), dims) == 0
+    NP, NX, NM, D = list(dims)
+    in1 = [0] if scalar_src else list(range(L + 1))
+    paths, idx, nm = paths_and_layout(L, in1, list(range(L + 1)))
+    assert nm == NM and len(paths) == NP
+    x = torch.randn(NX, dtype=torch.float64, requires_grad=True)
+    Y = torch.randn(D, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(NP, dtype=torch.float64, requires_grad=True)
+    ref, out_irreps = oracle_tp(L, scalar_src, x, Y, w)
+    # oracle output: per path p a [1, 2l3+1] block, in path order
+    perm = [i for blk in idx for i in blk]
+    out = np.zeros(NM)
+    z = np.zeros(max(NM, D))
+    cpu_harness.h_tp(L, int(scalar_src), 0, ptr(x.detach().numpy()), ptr(Y.detach().numpy()), ptr(w.detach().numpy()),
+                     ptr(z), ptr(out), ptr(z))
+    np.testing.assert_allclose(out[perm], ref.detach().numpy(), rtol=0, atol=1e-13)
+    # backward against autograd
+    g_ref = torch.randn(NM, dtype=torch.float64)  # gradient wrt oracle-ordered output
+    dx_ref, dY_ref, dw_ref = torch.autograd.grad(ref, [x, Y, w], g_ref)
+    g_mine = np.zeros(NM)
+    g_mine[perm] = g_ref.numpy()
+    dx = np.zeros(NX)
+    cpu_harness.h_tp(L, int(scalar_src), 1, ptr(z), ptr(Y.detach().numpy()), ptr(w.detach().numpy()), ptr(g_mine),
+                     ptr(dx), ptr(z))
+    np.testing.assert_allclose(dx, dx_ref.numpy(), rtol=0, atol=1e-12)
+    dw, dY = np.zeros(NP), np.zeros(D)
+    cpu_harness.h_tp(L, int(scalar_src), 2, ptr(x.detach().numpy()), ptr(Y.detach().numpy()), ptr(w.detach().numpy()),
+                     ptr(g_mine), ptr(dw), ptr(dY))
+    np.testing.assert_allclose(dw, dw_ref.numpy(), rtol=0, atol=1e-12)
+    np.testing.assert_allclose(dY, dY_ref.numpy(), rtol=0, atol=1e-12)
+
+
+@pytest.mark.parametrize("L", [1, 2, 3])
+@pytest.mark.parametrize("last", [False, True])
+def test_product_basis_matches_oracle(cpu_harness, L, last):
+    torch.manual_seed(10 + L)
+    D = (L + 1) ** 2
+    outs = [0] if last else list(range(L + 1))
+    irr = o3.Irreps([(1, l) for l in range(L + 1)])
+    paths, out = om.generate_paths(o3.Irreps([(1, l) for l in outs]), irr, irr, "uuu", identical_inputs=True)
+    tp = om.TensorProduct(irr, irr, out, paths)
+    a = torch.randn(D, dtype=torch.float64, requires_grad=True)
+    ref = tp(a[None], a[None])[0]
+    _, idx, nb = paths_and_layout(L, list(range(L + 1)), outs)
+    perm = [i for blk in idx for i in blk]
+    b = np.zeros(nb)
+    assert cpu_harness.h_pb(L, int(last), 0, ptr(a.detach().numpy()), ptr(b), ptr(b)) == nb
+    np.testing.assert_allclose(b[perm], ref.detach().numpy(), rtol=0, atol=1e-13)
+    g_ref = torch.randn(nb, dtype=torch.float64)
+    (da_ref,) = torch.autograd.grad(ref, [a], g_ref)
+    g_mine = np.zeros(nb)
+    g_mine[perm] = g_ref.numpy()
+    da = np.zeros(D)
+    cpu_harness.h_pb(L, int(last), 1, ptr(a.detach().numpy()), ptr(g_mine), ptr(da))
+    np.testing.assert_allclose(da, da_ref.numpy(), rtol=0, atol=1e-12)
+
+
+@pytest.mark.parametrize("L", [1, 2, 3])
+def test_spherical_harmonics_and_gradient(cpu_harness, L):
+    torch.manual_seed(L)
+    D = (L + 1) ** 2
+    n = torch.randn(3, dtype=torch.float64) * 0.7
+    n.requires_grad_(True)
+    ref = o3.spherical_harmonics(L, n[None], "component")[0]
+    Y = np.zeros(D)
+    cpu_harness.h_sh(L, ptr(n.detach().numpy()), ptr(Y))
+    np.testing.assert_allclose(Y, ref.detach().numpy(), rtol=0, atol=1e-13)
+    dY = torch.randn(D, dtype=torch.float64)
+    (dn_ref,) = torch.autograd.grad(ref, [n], dY)
+    dn = np.zeros(3)
+    cpu_harness.h_sh_grad(L, ptr(n.detach().numpy()), ptr(dY.numpy()), ptr(dn))
+    np.testing.assert_allclose(dn, dn_ref.numpy(), rtol=0, atol=1e-12)
+
+
+def test_radial_basis_and_gradient(cpu_harness):
+    torch.set_default_dtype(torch.float64)
+    try:
+        rb = om.RadialBasis(5.0, 8, 5)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    for d0 in [0.8, 2.553, 4.2, 4.999, 5.0, 5.3]:
+        d = torch.tensor([[d0]], dtype=torch.float64, requires_grad=True)
+        ref = rb(d)[0]
+        jac = torch.stack([torch.autograd.grad(ref[i], d, retain_graph=True)[0][0, 0] for i in range(8)])
+        b, db = np.zeros(8), np.zeros(8)
+        cpu_harness.h_radial.argtypes = [ctypes.c_double, ctypes.c_double, ctypes.c_int, DP, DP]
+        cpu_harness.h_radial(d0, 5.0, 5, ptr(b), ptr(db))
+        np.testing.assert_allclose(b, ref.detach().numpy(), rtol=0, atol=1e-13)
+        np.testing.assert_allclose(db, jac.numpy(), rtol=0, atol=1e-12)
+
+
+def test_radial_mlp_hidden_layers(cpu_harness):
+    torch.manual_seed(3)
+    mlp = om.MLP([8, 64, 64, 64, 11]).double()
+    lins = [m for m in mlp.mlp if isinstance(m, om.MlpLinear)]
+    A = [(l.weight * l.alpha).detach().numpy().copy() for l in lins[:3]]
+    At = [np.ascontiguousarray(a.T) for a in A]
+    b = torch.randn(1, 8, dtype=torch.float64, requires_grad=True)
+    h3_ref = torch.nn.functional.silu(mlp.mlp[4](mlp.mlp[3](mlp.mlp[2](mlp.mlp[1](mlp.mlp[0](b))))))
+    dh3 = torch.randn(1, 64, dtype=torch.float64)
+    (db_ref,) = torch.autograd.grad(h3_ref, [b], dh3)
+    h3, db = np.zeros(64), np.zeros(8)
+    cpu_harness.h_mlp(ptr(b.detach().numpy()), ptr(A[0]), ptr(A[1]), ptr(A[2]), ptr(At[1]), ptr(At[2]),
+                      ptr(dh3.numpy()), ptr(h3), ptr(db))
+    np.testing.assert_allclose(h3, h3_ref.detach().numpy()[0], rtol=0, atol=1e-13)
+    np.testing.assert_allclose(db, db_ref.numpy()[0], rtol=0, atol=1e-12)
+
+
+def test_edge_vector_gradient(cpu_harness):
+    torch.manual_seed(5)
+    v = torch.randn(3, dtype=torch.float64, requires_grad=True)
+    d = (v**2).sum().sqrt() + 1e-9
+    n = v / d
+    dd, dn = torch.randn((), dtype=torch.float64), torch.randn(3, dtype=torch.float64)
+    (g_ref,) = torch.autograd.grad(d * dd + (n * dn).sum(), [v])
+    g = np.zeros(3)
+    cpu_harness.h_edge_grad.argtypes = [DP, ctypes.c_double, DP, DP]
+    cpu_harness.h_edge_grad(ptr(v.detach().numpy()), float(dd), ptr(dn.numpy()), ptr(g))
+    np.testing.assert_allclose(g, g_ref.numpy(), rtol=0, atol=1e-12)
