@@ -1,0 +1,145 @@
+/*
+ * C ABI of libtace_b200.so: TACE energy / conservative force / virial evaluation and the
+ * cell-list neighbour list as hand-written CUDA kernels for sm_100a.
+ *
+ * The reference (xvzemin/tace) is pure Python: there is no foreign-function interface to
+ * mirror, so each entry point cites the Python interface it stands behind (paths relative
+ * to the reference project root).  Conventions:
+ *   - plain pointers and sizes only; every array argument is DEVICE memory owned by the
+ *     caller unless a comment says "host"; the library never frees caller memory;
+ *   - all work is enqueued on the given stream, nothing synchronises except where stated;
+ *   - every function returns an int status (0 = ok, negative = error, see
+ *     tace_status_string); no C++ exception crosses the boundary, nothing traps or aborts;
+ *   - a TaceModel is not re-entrant (one call at a time); distinct models are independent;
+ *   - there is no CPU fallback: without a CUDA device tace_create fails.
+ */
+#ifndef TACE_B200_H
+#define TACE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct TaceModel TaceModel;
+typedef void* tace_stream_t; /* a cudaStream_t */
+
+enum {
+  TACE_OK = 0,
+  TACE_ERR_INVALID_ARGUMENT = -1,
+  TACE_ERR_UNSUPPORTED_CONFIG = -2,
+  TACE_ERR_CAPACITY = -3,
+  TACE_ERR_CUDA = -4,
+  TACE_ERR_NO_DEVICE = -5,
+  TACE_ERR_UNKNOWN_WEIGHT = -6,
+  TACE_ERR_WEIGHTS_MISSING = -7
+};
+
+enum { TACE_F32 = 0, TACE_F64 = 1 };
+
+/* Hyper-parameters of the model body.  Stands behind the constructor
+ * tace.models.e3nnTACE(**cfg) (tace/models/_e3nn/tace.py:29-62) after
+ * check_model_config (tace/models/_e3nn/default.py:231-316), for the options this path
+ * supports: cgtp interaction + cgtp product basis, natural parity, Lmax == lmax. */
+typedef struct {
+  int dtype;          /* TACE_F32 or TACE_F64 */
+  int L;              /* Lmax == lmax, 1..3 */
+  int num_layers;     /* >= 1 */
+  int num_channel;    /* multiple of 32, <= 256 */
+  int num_elements;   /* length of the sorted atomic-number list */
+  int correlation;    /* product-basis correlation order: 1 or 2 */
+  int num_bessel;     /* must be 8 */
+  int mlp_hidden;     /* must be 64 (three hidden layers) */
+  int envelope_p;     /* polynomial cutoff exponent (default 5) */
+  int readout_hidden; /* width of the energy read-out hidden layer (default 16, <= 64) */
+  double cutoff;
+  double avg_num_neighbors;
+} TaceConfig;
+
+/* One batch of structures on the device.  Stands behind the `data` dictionary consumed by
+ * TensorModel.forward (tace/models/adapter.py:32-41, 278-384).  Reals are in the model
+ * dtype.  In graph mode `positions`, `lattice`, `edge_shifts` are given and edge vectors are
+ * r[target] - r[source] + shift @ lattice[graph]; in edge-vector mode (the LAMMPS ML-IAP
+ * path, tace/interface/lammps/mliap.py:117-136) `edge_vector` is given instead, atoms
+ * [n_local, n_atoms) are ghosts that only act as message sources, and forces are returned
+ * per edge. */
+typedef struct {
+  int64_t n_atoms;           /* local + ghost atoms */
+  int64_t n_local;           /* atoms that receive messages and own an energy */
+  int64_t n_edges;
+  int32_t n_graphs;
+  const void* positions;     /* [n_atoms,3] or NULL */
+  const void* lattice;       /* [n_graphs,3,3] row vectors, or NULL */
+  const int32_t* species;    /* [n_atoms] index into the model's element list */
+  const int32_t* graph_ptr;  /* [n_graphs+1] first atom of each graph (atoms sorted by graph) */
+  const int64_t* edge_index; /* [2,n_edges]: row 0 = source, row 1 = target (any order) */
+  const void* edge_shifts;   /* [n_edges,3] or NULL */
+  const void* edge_vector;   /* [n_edges,3] or NULL */
+} TaceBatch;
+
+/* Outputs, any of which may be NULL to skip it.  Stands behind the dictionary returned by
+ * TensorModel.forward (tace/models/adapter.py:162-174, tace/models/_e3nn/tace.py:764-786):
+ * forces = -dE/dr, virials = -dE/d(strain), stress = -virials/|det lattice|,
+ * edge_forces = +dE/d(edge_vector). */
+typedef struct {
+  void* energy;      /* [n_graphs] */
+  void* node_energy; /* [n_local] */
+  void* forces;      /* [n_atoms,3] */
+  void* virials;     /* [n_graphs,3,3] */
+  void* stress;      /* [n_graphs,3,3] */
+  void* edge_forces; /* [n_edges,3], in the caller's edge order */
+} TaceOutputs;
+
+const char* tace_status_string(int status);
+
+/* tace.models.e3nnTACE(**cfg): validates the configuration, selects the current CUDA device
+ * (must be compute capability 10.x) and allocates the weight arena. */
+int tace_create(const TaceConfig* cfg, TaceModel** out);
+void tace_destroy(TaceModel* model);
+
+/* Weight arena.  Stands behind load_state_dict / the `.pt` checkpoint contract
+ * (tace/lightning/lit_model.py:587-609,664-677): the host side repacks the reference's
+ * parameters (normalisation constants folded in) into the named arrays listed here and
+ * uploads each one (HOST pointer, model dtype).  tace_forward refuses to run until every
+ * array has been set. */
+int tace_weight_count(const TaceModel* model);
+int tace_weight_info(const TaceModel* model, int index, const char** name, int64_t* numel);
+int tace_set_weight(TaceModel* model, const char* name, const void* host_data, int64_t numel);
+
+/* Bytes of device scratch tace_forward needs for a batch of this size. */
+int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_local, int64_t n_edges,
+                         int32_t n_graphs, size_t* bytes);
+
+/* TensorModel.forward(data) (tace/models/adapter.py:32-41): energy, then the hand-written
+ * backward pass for forces / virials / stress / edge forces (replaces the autograd call at
+ * tace/models/adapter.py:95-104).  `workspace` is device memory of at least
+ * tace_workspace_bytes bytes, 256-byte aligned. */
+int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace,
+                 size_t workspace_bytes, tace_stream_t stream);
+
+/* Debug taps used by the parity tests: copies a named intermediate of the last tace_forward
+ * call ("M0", "A0", "h1", ...) into `dst` (device, model dtype, at most `numel` elements).
+ * Returns the number of elements copied or a negative status. */
+int64_t tace_debug_read(TaceModel* model, const char* name, void* dst, int64_t numel, tace_stream_t stream);
+
+/* Cell-list neighbour list for a batch of periodic structures.  Stands behind
+ * get_neighborhood (tace/dataset/neighbour_list.py:195-298, matscipy "ijS" semantics): full
+ * list, D = r_j - r_i + S @ cell, strict |D| < cutoff evaluated in fp64, self pairs kept
+ * unless S = 0, no shifts along non-periodic axes.  Edges come out grouped by target atom.
+ * Two calls: tace_nl_count fills `counts[n_atoms]` (neighbours per target atom) and the
+ * total; the caller sizes the outputs; tace_nl_fill writes edge_index [2,n_edges]
+ * (row 0 = source, row 1 = target) and integer shifts [n_edges,3].
+ * positions/lattice are fp64, pbc is [n_graphs,3] bytes. `row_ptr` is int64 [n_atoms+1]
+ * (exclusive prefix sum of counts, computed by the caller). */
+int tace_nl_count(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
+                  int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, tace_stream_t stream);
+int tace_nl_fill(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
+                 int32_t n_graphs, int64_t n_atoms, double cutoff, const int64_t* row_ptr, int64_t n_edges,
+                 int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TACE_B200_H */

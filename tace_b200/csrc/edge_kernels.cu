@@ -1,0 +1,190 @@
+// Per-edge kernels: geometry, angular and radial features, hidden layers of the radial MLP
+// (forward), and the chain rule back to the edge vector (backward); force and virial sums.
+//
+// One thread per edge.  The radial-MLP weights (67 KB in fp32 per layer) are read straight
+// from global memory: every thread of a warp reads the same address, so each load is one
+// L1-resident broadcast.
+#include "kernels.h"
+
+namespace tace {
+
+template <typename T>
+__device__ __forceinline__ void edge_geometry(const EdgeArgs<T>& a, long long e, T (&v)[3], T& d0, T& d) {
+  const int eo = a.e_orig[e];
+  if (a.edge_vector) {
+    v[0] = a.edge_vector[3LL * eo + 0];
+    v[1] = a.edge_vector[3LL * eo + 1];
+    v[2] = a.edge_vector[3LL * eo + 2];
+  } else {
+    const long long s = a.e_src[e], t = a.e_dst[e];
+    const T* lat = a.lattice + 9LL * a.atom_graph[s];
+    const T s0 = a.shifts[3LL * eo + 0], s1 = a.shifts[3LL * eo + 1], s2 = a.shifts[3LL * eo + 2];
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      v[k] = (a.positions[3 * t + k] - a.positions[3 * s + k]) + (s0 * lat[k] + s1 * lat[3 + k] + s2 * lat[6 + k]);
+  }
+  d0 = sqrt(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+  d = d0 + T(1e-9);  // tace/models/adapter.py:347
+}
+
+template <typename T, int L>
+__global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
+  constexpr int D = (L + 1) * (L + 1);
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  T v[3], d0, d;
+  edge_geometry(a, e, v, d0, d);
+  a.vec[3 * e + 0] = v[0]; a.vec[3 * e + 1] = v[1]; a.vec[3 * e + 2] = v[2];
+  const T inv = T(1) / d;
+  T Y[D];
+  sh_eval<T, L>(v[0] * inv, v[1] * inv, v[2] * inv, Y);
+#pragma unroll
+  for (int k = 0; k < D; ++k) a.Y[e * D + k] = Y[k];
+  T b[kNumBessel];
+  radial_eval<T>(d, a.rp, b, nullptr);
+  for (int t = 0; t < a.n_layers; ++t) {
+    T h3[kHidden];
+    mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3);
+    T* out = a.H3[t] + e * kHidden;
+    for (int j = 0; j < kHidden; ++j) out[j] = h3[j];
+  }
+}
+
+template <typename T, int L>
+__global__ void __launch_bounds__(128) edge_bwd_kernel(const EdgeArgs<T> a) {
+  constexpr int D = (L + 1) * (L + 1);
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  T v[3], d0, d;
+  edge_geometry(a, e, v, d0, d);
+  T b[kNumBessel], dbdd[kNumBessel];
+  radial_eval<T>(d, a.rp, b, dbdd);
+  T dd = T(0);
+  for (int t = 0; t < a.n_layers; ++t) {
+    T dh3[kHidden], db[kNumBessel];
+    const T* in = a.dH3[t] + e * kHidden;
+    for (int j = 0; j < kHidden; ++j) dh3[j] = in[j];
+    mlp_hidden_bwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
+    for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
+  }
+  const T inv = T(1) / d;
+  T dY[D], dn[3], g[3];
+#pragma unroll
+  for (int k = 0; k < D; ++k) dY[k] = a.dY[e * D + k];
+  sh_grad<T, L>(v[0] * inv, v[1] * inv, v[2] * inv, dY, dn);
+  edge_vector_grad<T>(v, d0, d, dd, dn, g);
+  a.g[3 * e + 0] = g[0]; a.g[3 * e + 1] = g[1]; a.g[3 * e + 2] = g[2];
+  if (a.edge_forces) {
+    const long long eo = a.e_orig[e];
+    a.edge_forces[3 * eo + 0] = g[0]; a.edge_forces[3 * eo + 1] = g[1]; a.edge_forces[3 * eo + 2] = g[2];
+  }
+}
+
+template <typename T>
+cudaError_t launch_edge_fwd(const EdgeArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((a.E + 127) / 128);
+  if (a.L == 1) edge_fwd_kernel<T, 1><<<grid, 128, 0, s>>>(a);
+  else if (a.L == 2) edge_fwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
+  else if (a.L == 3) edge_fwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_edge_bwd(const EdgeArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((a.E + 127) / 128);
+  if (a.L == 1) edge_bwd_kernel<T, 1><<<grid, 128, 0, s>>>(a);
+  else if (a.L == 2) edge_bwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
+  else if (a.L == 3) edge_bwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---- forces and virials ------------------------------------------------------------------------
+template <typename T>
+__global__ void forces_kernel(const ForceArgs<T> a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.n_atoms) return;
+  T f[3] = {T(0), T(0), T(0)};
+  T w[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) w[k] = T(0);
+  if (i < a.n_local) {
+    for (int e = a.rowptr_dst[i]; e < a.rowptr_dst[i + 1]; ++e) {
+      const T g0 = a.g[3LL * e], g1 = a.g[3LL * e + 1], g2 = a.g[3LL * e + 2];
+      f[0] -= g0; f[1] -= g1; f[2] -= g2;
+      if (a.atom_virial) {
+        const T v0 = a.vec[3LL * e], v1 = a.vec[3LL * e + 1], v2 = a.vec[3LL * e + 2];
+        w[0] += v0 * g0; w[1] += v0 * g1; w[2] += v0 * g2;
+        w[3] += v1 * g0; w[4] += v1 * g1; w[5] += v1 * g2;
+        w[6] += v2 * g0; w[7] += v2 * g1; w[8] += v2 * g2;
+      }
+    }
+    if (a.atom_virial)
+      for (int k = 0; k < 9; ++k) a.atom_virial[9LL * i + k] = w[k];
+  }
+  if (a.forces) {
+    for (int k = a.rowptr_src[i]; k < a.rowptr_src[i + 1]; ++k) {
+      const long long e = a.perm_src[k];
+      f[0] += a.g[3 * e]; f[1] += a.g[3 * e + 1]; f[2] += a.g[3 * e + 2];
+    }
+    a.forces[3LL * i] = f[0]; a.forces[3LL * i + 1] = f[1]; a.forces[3LL * i + 2] = f[2];
+  }
+}
+template <typename T>
+cudaError_t launch_forces(const ForceArgs<T>& a, cudaStream_t s) {
+  if (a.n_atoms <= 0) return cudaSuccess;
+  forces_kernel<T><<<(a.n_atoms + 127) / 128, 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void graph_virial_kernel(const T* __restrict__ atom_virial, const int* __restrict__ graph_ptr,
+                                    const T* __restrict__ lattice, T* virials, T* stress) {
+  __shared__ T red[9][128];
+  const int g = blockIdx.x;
+  T w[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) w[k] = T(0);
+  for (int i = graph_ptr[g] + threadIdx.x; i < graph_ptr[g + 1]; i += blockDim.x)
+#pragma unroll
+    for (int k = 0; k < 9; ++k) w[k] += atom_virial[9LL * i + k];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) red[k][threadIdx.x] = w[k];
+  __syncthreads();
+  for (int off = 64; off > 0; off >>= 1) {
+    if (threadIdx.x < off)
+#pragma unroll
+      for (int k = 0; k < 9; ++k) red[k][threadIdx.x] += red[k][threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x < 9) {
+    const int r = threadIdx.x / 3, c = threadIdx.x % 3;
+    const T sym = T(0.5) * (red[3 * r + c][0] + red[3 * c + r][0]);  // dE/d(strain)
+    if (virials) virials[9LL * g + threadIdx.x] = -sym;
+    if (stress) {
+      const T* m = lattice + 9LL * g;
+      const T det = m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
+      const T st = sym / fabs(det);
+      stress[9LL * g + threadIdx.x] = (fabs(st) < T(1e10)) ? st : T(0);  // tace/models/adapter.py:114-115
+    }
+  }
+}
+template <typename T>
+cudaError_t launch_graph_virial(const T* atom_virial, const int* graph_ptr, const T* lattice, T* virials, T* stress,
+                                int n_graphs, cudaStream_t s) {
+  if (n_graphs <= 0) return cudaSuccess;
+  graph_virial_kernel<T><<<n_graphs, 128, 0, s>>>(atom_virial, graph_ptr, lattice, virials, stress);
+  return cudaGetLastError();
+}
+
+#define INST(T)                                                                                      \
+  template cudaError_t launch_edge_fwd<T>(const EdgeArgs<T>&, cudaStream_t);                         \
+  template cudaError_t launch_edge_bwd<T>(const EdgeArgs<T>&, cudaStream_t);                         \
+  template cudaError_t launch_forces<T>(const ForceArgs<T>&, cudaStream_t);                          \
+  template cudaError_t launch_graph_virial<T>(const T*, const int*, const T*, T*, T*, int, cudaStream_t);
+INST(float)
+INST(double)
+
+}  // namespace tace

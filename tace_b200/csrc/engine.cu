@@ -1,0 +1,647 @@
+// Host-side engine behind the C ABI (include/tace_b200.h): model plan, weight arena,
+// workspace layout and the forward / hand-written backward schedule of one
+// energy + forces + virial evaluation.
+//
+// Schedule of one call (reference: TensorModel.forward, tace/models/adapter.py:32-41, over
+// Representation.forward, tace/models/_e3nn/representation.py:302-429):
+//   graph prep -> edge features + radial MLP hidden layers -> per layer:
+//   [linear_up, last radial layer (GEMM), tensor-product message passing, linear_down,
+//    gate, linear, product basis, per-species coefficient linears, linear (+ skip)]
+//   -> read-out -> the same chain in reverse with transposed weights -> edge-vector gradients
+//   -> forces / virials / stress.
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/tace_b200.h"
+#include "gemm.cuh"
+#include "kernels.h"
+#include "tp_gen.cuh"
+
+namespace tace {
+
+namespace {
+
+struct TPMeta { int NP, NX, NM; const int* k; const int* base; };
+struct PBMeta { int NP, NB; const int* k; const int* base; };
+
+bool tp_meta(int L, bool scalar, TPMeta& m) {
+#define TPM(TAG) { m = {TP_##TAG::NP, TP_##TAG::NX, TP_##TAG::NM, tp_##TAG##_k, tp_##TAG##_base}; return true; }
+  if (L == 1 && scalar) TPM(L1_S)
+  if (L == 1) TPM(L1_F)
+  if (L == 2 && scalar) TPM(L2_S)
+  if (L == 2) TPM(L2_F)
+  if (L == 3 && scalar) TPM(L3_S)
+  if (L == 3) TPM(L3_F)
+#undef TPM
+  return false;
+}
+bool pb_meta(int L, bool last, PBMeta& m) {
+#define PBM(TAG) { m = {PB_##TAG::NP, PB_##TAG::NB, pb_##TAG##_k, pb_##TAG##_base}; return true; }
+  if (L == 1 && last) PBM(L1_T)
+  if (L == 1) PBM(L1_A)
+  if (L == 2 && last) PBM(L2_T)
+  if (L == 2) PBM(L2_A)
+  if (L == 3 && last) PBM(L3_T)
+  if (L == 3) PBM(L3_A)
+#undef PBM
+  return false;
+}
+
+struct WeightEntry {
+  std::string name;
+  long long numel;
+  long long offset;  // elements into the arena
+  bool set;
+};
+
+struct LayerPlan {
+  bool scalar_src, last, has_res;
+  TPMeta tp;
+  PBMeta pb;
+  int Din;                  // components per atom of the layer input (1 or D)
+  int Dout;                 // components per atom of the layer output (D or 1)
+  std::vector<int> in_ls;   // ranks present in the input
+  std::vector<int> out_ls;  // ranks present in the output
+};
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+// Bump allocator over the caller's workspace; in "measure" mode it only counts.
+struct Arena {
+  unsigned char* base = nullptr;
+  size_t used = 0;
+  template <typename U>
+  U* take(size_t count) {
+    U* p = base ? reinterpret_cast<U*>(base + used) : nullptr;
+    used += align256(sizeof(U) * (count ? count : 1));
+    return p;
+  }
+};
+
+}  // namespace
+
+struct ModelBase {
+  TaceConfig cfg;
+  virtual ~ModelBase() {}
+  virtual int weight_count() const = 0;
+  virtual int weight_info(int i, const char** name, int64_t* numel) const = 0;
+  virtual int set_weight(const char* name, const void* host, int64_t numel) = 0;
+  virtual int workspace_bytes(int64_t n_atoms, int64_t n_local, int64_t n_edges, int32_t n_graphs, size_t* bytes) = 0;
+  virtual int forward(const TaceBatch* b, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) = 0;
+  virtual int64_t debug_read(const char* name, void* dst, int64_t numel, cudaStream_t s) = 0;
+};
+
+template <typename T>
+struct Model : ModelBase {
+  int L, D, C, NL_, n_el, H;
+  std::vector<LayerPlan> layers;
+  std::vector<WeightEntry> weights;
+  T* arena = nullptr;
+  long long arena_numel = 0;
+  struct DebugBuf { std::string name; const void* ptr; long long numel; };
+  std::vector<DebugBuf> debug;
+  T host_bessel[kNumBessel + 1];  // host copies of the radial frequencies and prefactor
+
+  ~Model() override {
+    if (arena) cudaFree(arena);
+  }
+
+  void add_weight(const std::string& name, long long numel) {
+    weights.push_back({name, numel, arena_numel, false});
+    arena_numel += (numel + 63) / 64 * 64;
+  }
+  const T* w(const std::string& name) const {
+    for (const auto& e : weights)
+      if (e.name == name) return arena + e.offset;
+    return nullptr;
+  }
+
+  int init(const TaceConfig& c) {
+    cfg = c;
+    L = c.L; D = (L + 1) * (L + 1); C = c.num_channel; NL_ = c.num_layers; n_el = c.num_elements; H = c.readout_hidden;
+    layers.resize(NL_);
+    for (int t = 0; t < NL_; ++t) {
+      LayerPlan& p = layers[t];
+      p.scalar_src = (t == 0);
+      p.last = (t == NL_ - 1);
+      p.has_res = (t > 0);
+      if (!tp_meta(L, p.scalar_src, p.tp) || !pb_meta(L, p.last, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      p.Din = p.scalar_src ? 1 : D;
+      p.Dout = p.last ? 1 : D;
+      p.in_ls.clear(); p.out_ls.clear();
+      for (int l = 0; l <= (p.scalar_src ? 0 : L); ++l) p.in_ls.push_back(l);
+      for (int l = 0; l <= (p.last ? 0 : L); ++l) p.out_ls.push_back(l);
+    }
+    add_weight("emb", (long long)n_el * C);
+    add_weight("bessel", kNumBessel);
+    add_weight("bessel_pref", 1);
+    for (int t = 0; t < NL_; ++t) {
+      const LayerPlan& p = layers[t];
+      const std::string pre = "t" + std::to_string(t) + ".";
+      for (int l : p.in_ls) { add_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
+      add_weight(pre + "up.b", C);
+      add_weight(pre + "A0", kNumBessel * kHidden);
+      add_weight(pre + "A1", kHidden * kHidden);
+      add_weight(pre + "A2", kHidden * kHidden);
+      add_weight(pre + "A1t", kHidden * kHidden);
+      add_weight(pre + "A2t", kHidden * kHidden);
+      add_weight(pre + "W3", (long long)kHidden * p.tp.NP * C);
+      add_weight(pre + "W3t", (long long)kHidden * p.tp.NP * C);
+      for (int l = 0; l <= L; ++l) {
+        const long long outl = (l == 0) ? (long long)(L + 2) * C : C;
+        add_weight(pre + "down.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
+        add_weight(pre + "downT.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
+        add_weight(pre + "nl.l" + std::to_string(l), (long long)C * C);
+        add_weight(pre + "nlT.l" + std::to_string(l), (long long)C * C);
+      }
+      add_weight(pre + "down.b", (long long)(L + 2) * C);
+      add_weight(pre + "nl.b", C);
+      for (size_t i = 0; i < p.out_ls.size(); ++i) {
+        const int l = p.out_ls[i];
+        const std::string ls = std::to_string(l);
+        add_weight(pre + "c0.l" + ls, (long long)n_el * C * C);
+        add_weight(pre + "c0T.l" + ls, (long long)n_el * C * C);
+        if (cfg.correlation >= 2) {
+          add_weight(pre + "c1.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
+          add_weight(pre + "c1T.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
+        }
+        add_weight(pre + "lin.l" + ls, (long long)C * C);
+        add_weight(pre + "linT.l" + ls, (long long)C * C);
+        if (p.has_res) {
+          add_weight(pre + "res.l" + ls, (long long)n_el * C * C);
+          add_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
+        }
+      }
+      add_weight(pre + "c.b", (long long)n_el * C);
+      add_weight(pre + "lin.b", C);
+      if (p.has_res) add_weight(pre + "res.b", (long long)n_el * C);
+    }
+    add_weight("ro.W1", (long long)C * H);
+    add_weight("ro.W2", H);
+    add_weight("scale", n_el);
+    add_weight("e0", n_el);
+    if (cudaMalloc(&arena, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
+    if (cudaMemset(arena, 0, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
+    return TACE_OK;
+  }
+
+  int weight_count() const override { return (int)weights.size(); }
+  int weight_info(int i, const char** name, int64_t* numel) const override {
+    if (i < 0 || i >= (int)weights.size()) return TACE_ERR_INVALID_ARGUMENT;
+    if (name) *name = weights[i].name.c_str();
+    if (numel) *numel = weights[i].numel;
+    return TACE_OK;
+  }
+  int set_weight(const char* name, const void* host, int64_t numel) override {
+    if (!name || !host) return TACE_ERR_INVALID_ARGUMENT;
+    for (auto& e : weights) {
+      if (e.name == name) {
+        if (numel != e.numel) return TACE_ERR_INVALID_ARGUMENT;
+        if (cudaMemcpy(arena + e.offset, host, sizeof(T) * (size_t)numel, cudaMemcpyHostToDevice) != cudaSuccess)
+          return TACE_ERR_CUDA;
+        if (e.name == "bessel") memcpy(host_bessel, host, sizeof(T) * kNumBessel);
+        if (e.name == "bessel_pref") memcpy(host_bessel + kNumBessel, host, sizeof(T));
+        e.set = true;
+        return TACE_OK;
+      }
+    }
+    return TACE_ERR_UNKNOWN_WEIGHT;
+  }
+
+  // ---- workspace ---------------------------------------------------------------------------
+  struct LayerBufs {
+    T *h_in, *x, *W, *H3, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
+    T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
+  };
+  struct Bufs {
+    int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr;
+    void* prep_temp; size_t prep_temp_bytes;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial;
+    std::vector<LayerBufs> lay;
+  };
+
+  size_t layout(Arena& ar, Bufs& b, long long N, long long NL, long long E, int B) {
+    b.e_src = ar.take<int>(E); b.e_dst = ar.take<int>(E); b.e_orig = ar.take<int>(E); b.perm_src = ar.take<int>(E);
+    b.rowptr_dst = ar.take<int>(NL + 1); b.rowptr_src = ar.take<int>(N + 1); b.atom_graph = ar.take<int>(N);
+    b.species_perm = ar.take<int>(NL); b.species_ptr = ar.take<int>(n_el + 1); b.tile_ptr = ar.take<int>(4 * (n_el + 1));
+    b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
+    b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
+    b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
+    b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
+    b.lay.resize(NL_);
+    T* prev_h = ar.take<T>((size_t)N * C);   // h_0: species embedding, scalar channels
+    T* prev_gh = nullptr;
+    for (int t = 0; t < NL_; ++t) {
+      const LayerPlan& p = layers[t];
+      LayerBufs& lb = b.lay[t];
+      lb.h_in = prev_h;
+      lb.gh_in = prev_gh;
+      lb.x = ar.take<T>((size_t)N * p.tp.NX * C);
+      lb.gx = p.scalar_src ? nullptr : ar.take<T>((size_t)N * p.tp.NX * C);
+      lb.H3 = ar.take<T>((size_t)E * kHidden);
+      lb.W = ar.take<T>((size_t)E * p.tp.NP * C);
+      lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
+      lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
+      lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
+      lb.a = ar.take<T>((size_t)NL * D * C);
+      lb.ga = ar.take<T>((size_t)NL * D * C);
+      lb.A = ar.take<T>((size_t)NL * D * C);
+      lb.gA = ar.take<T>((size_t)NL * D * C);
+      lb.B2 = ar.take<T>((size_t)NL * p.pb.NB * C);
+      lb.out = ar.take<T>((size_t)NL * p.Dout * C);
+      lb.gout = ar.take<T>((size_t)NL * p.Dout * C);
+      lb.h_out = ar.take<T>((size_t)N * p.Dout * C);
+      lb.gh_out = ar.take<T>((size_t)N * p.Dout * C);
+      prev_h = lb.h_out;
+      prev_gh = lb.gh_out;
+    }
+    return ar.used;
+  }
+
+  int workspace_bytes(int64_t n_atoms, int64_t n_local, int64_t n_edges, int32_t n_graphs, size_t* bytes) override {
+    if (!bytes || n_atoms < 0 || n_local < 0 || n_local > n_atoms || n_edges < 0 || n_graphs < 0) return TACE_ERR_INVALID_ARGUMENT;
+    if (n_edges >= (1LL << 31) - 64 || n_atoms >= (1LL << 31) - 64) return TACE_ERR_CAPACITY;
+    Arena ar; Bufs b;
+    *bytes = layout(ar, b, n_atoms, n_local, n_edges, n_graphs) + 256;
+    return TACE_OK;
+  }
+
+  // ---- GEMM helpers ----------------------------------------------------------------------------
+  static void add_problem(GemmBatch<T>& gb, const T* A, long long a_s1, long long a_s2, int q, int K, const T* Bm, int N,
+                          T* Cm, long long c_s1, long long c_s2, const T* bias, int accumulate, long long b_gs = 0,
+                          long long bias_gs = 0, const int* tile_ptr = nullptr) {
+    GemmProblem<T>& p = gb.p[gb.n_problems++];
+    p.A = A; p.B = Bm; p.C = Cm; p.bias = bias; p.q = q; p.N = N; p.K = K;
+    p.a_s1 = a_s1; p.a_s2 = a_s2; p.c_s1 = c_s1; p.c_s2 = c_s2;
+    p.b_group_stride = b_gs; p.bias_group_stride = bias_gs; p.accumulate = accumulate; p.tile_ptr = tile_ptr;
+  }
+  static GemmBatch<T> plain_batch(long long n_atoms) {
+    GemmBatch<T> gb;
+    memset(&gb, 0, sizeof(gb));
+    gb.n_groups = 1; gb.n_atoms = (int)n_atoms;
+    return gb;
+  }
+  GemmBatch<T> species_batch(const Bufs& b) const {
+    GemmBatch<T> gb;
+    memset(&gb, 0, sizeof(gb));
+    gb.n_groups = n_el; gb.group_ptr = b.species_ptr; gb.atom_map = b.species_perm;
+    return gb;
+  }
+  const int* tiles(const Bufs& b, int l) const { return b.tile_ptr + l * (n_el + 1); }
+
+#define CK(expr)                                                                                 \
+  do {                                                                                           \
+    cudaError_t err__ = (expr);                                                                  \
+    if (err__ != cudaSuccess) {                                                                  \
+      fprintf(stderr, "tace_b200: CUDA error %s at %s:%d\n", cudaGetErrorString(err__), __FILE__, __LINE__); \
+      return TACE_ERR_CUDA;                                                                      \
+    }                                                                                            \
+  } while (0)
+
+  int forward(const TaceBatch* bt, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) override {
+    if (!bt || !o || !ws) return TACE_ERR_INVALID_ARGUMENT;
+    for (const auto& e : weights)
+      if (!e.set) return TACE_ERR_WEIGHTS_MISSING;
+    const long long N = bt->n_atoms, NL = bt->n_local, E = bt->n_edges;
+    const int B = bt->n_graphs;
+    if (N < 0 || NL < 0 || NL > N || E < 0 || B <= 0 || !bt->species || !bt->graph_ptr || (E > 0 && !bt->edge_index))
+      return TACE_ERR_INVALID_ARGUMENT;
+    const bool vec_mode = bt->edge_vector != nullptr;
+    if (!vec_mode && E > 0 && (!bt->positions || !bt->lattice || !bt->edge_shifts)) return TACE_ERR_INVALID_ARGUMENT;
+    if (NL != N && NL_ > 1) return TACE_ERR_UNSUPPORTED_CONFIG;  // ghost atoms need a feature exchange between layers
+    if ((reinterpret_cast<uintptr_t>(ws) & 255) != 0) return TACE_ERR_INVALID_ARGUMENT;
+    Arena ar; ar.base = static_cast<unsigned char*>(ws);
+    Bufs b;
+    if (layout(ar, b, N, NL, E, B) > ws_bytes) return TACE_ERR_CAPACITY;
+    debug.clear();
+    const bool need_grad = o->forces || o->virials || o->stress || o->edge_forces;
+
+    // ---- graph preparation
+    GraphPrepArgs gp;
+    gp.E = E; gp.n_atoms = (int)N; gp.n_local = (int)NL; gp.n_graphs = B; gp.n_elements = n_el;
+    gp.edge_index = bt->edge_index; gp.species = bt->species; gp.graph_ptr = bt->graph_ptr;
+    gp.e_src = b.e_src; gp.e_dst = b.e_dst; gp.e_orig = b.e_orig; gp.rowptr_dst = b.rowptr_dst;
+    gp.perm_src = b.perm_src; gp.rowptr_src = b.rowptr_src; gp.atom_graph = b.atom_graph;
+    gp.species_perm = b.species_perm; gp.species_ptr = b.species_ptr; gp.tile_ptr = b.tile_ptr;
+    gp.temp = b.prep_temp; gp.temp_bytes = b.prep_temp_bytes;
+    CK(launch_graph_prep(gp, s));
+
+    // ---- edge features
+    EdgeArgs<T> ea;
+    memset(&ea, 0, sizeof(ea));
+    ea.L = L; ea.n_layers = NL_; ea.E = E;
+    ea.e_src = b.e_src; ea.e_dst = b.e_dst; ea.e_orig = b.e_orig;
+    ea.positions = static_cast<const T*>(bt->positions); ea.lattice = static_cast<const T*>(bt->lattice);
+    ea.atom_graph = b.atom_graph; ea.shifts = static_cast<const T*>(bt->edge_shifts);
+    ea.edge_vector = static_cast<const T*>(bt->edge_vector);
+    {
+      // the radial parameters travel by value inside the kernel arguments
+      for (int k = 0; k < kNumBessel; ++k) ea.rp.w[k] = host_bessel[k];
+      ea.rp.pref = host_bessel[kNumBessel];
+      ea.rp.rc = T(cfg.cutoff); ea.rp.p = cfg.envelope_p;
+    }
+    for (int t = 0; t < NL_; ++t) {
+      const std::string pre = "t" + std::to_string(t) + ".";
+      ea.mlp[t] = {w(pre + "A0"), w(pre + "A1"), w(pre + "A2"), w(pre + "A1t"), w(pre + "A2t")};
+      ea.H3[t] = b.lay[t].H3;
+      ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
+    }
+    ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
+    CK(launch_edge_fwd(ea, s));
+    debug.push_back({"Y", b.Y, (long long)D * E});
+    debug.push_back({"vec", b.vec, 3 * E});
+
+    // ---- layers, forward
+    CK(launch_species_gather(w("emb"), bt->species, b.lay[0].h_in, (int)N, C, s));
+    for (int t = 0; t < NL_; ++t) {
+      const LayerPlan& p = layers[t];
+      LayerBufs& lb = b.lay[t];
+      const std::string pre = "t" + std::to_string(t) + ".";
+      const std::string ts = std::to_string(t);
+      {  // linear_up on every atom (ghosts included: they are message sources)
+        GemmBatch<T> gb = plain_batch(N);
+        for (int l : p.in_ls)
+          add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "up.l" + std::to_string(l)), C,
+                      lb.x + (long long)l * l * C, (long long)p.tp.NX * C, C, l == 0 ? w(pre + "up.b") : nullptr, 0);
+        CK(launch_gemm(gb, N, s));
+      }
+      {  // last radial-MLP layer: per-edge path weights
+        GemmBatch<T> gb = plain_batch(E);
+        add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), p.tp.NP * C, lb.W, (long long)p.tp.NP * C, 0, nullptr, 0);
+        CK(launch_gemm(gb, E, s));
+      }
+      TPArgs<T> ta;
+      memset(&ta, 0, sizeof(ta));
+      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
+      ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W; ta.x = lb.x; ta.M = lb.M;
+      CK(launch_tp_fwd(ta, s));
+      debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
+      debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
+      {  // linear_down (1/avg_num_neighbors folded into the weights)
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l = 0; l <= L; ++l) {
+          const int K = p.tp.k[l] * C;
+          const int Nout = (l == 0) ? (L + 2) * C : C;
+          T* dst = (l == 0) ? lb.Gt : lb.Gt + (long long)(L + 1 + l * l) * C;
+          add_problem(gb, lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, K, 2 * l + 1, K,
+                      w(pre + "down.l" + std::to_string(l)), Nout, dst, (long long)(L + 1 + D) * C, C,
+                      l == 0 ? w(pre + "down.b") : nullptr, 0);
+        }
+        CK(launch_gemm(gb, NL, s));
+      }
+      CK(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, s));
+      {
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l = 0; l <= L; ++l)
+          add_problem(gb, lb.a + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nl.l" + std::to_string(l)), C,
+                      lb.A + (long long)l * l * C, (long long)D * C, C, l == 0 ? w(pre + "nl.b") : nullptr, 0);
+        CK(launch_gemm(gb, NL, s));
+      }
+      debug.push_back({"A" + ts, lb.A, NL * D * C});
+      if (cfg.correlation >= 2) CK(launch_pb_fwd(lb.A, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
+      {  // per-species coefficients
+        GemmBatch<T> gb = species_batch(b);
+        for (int l : p.out_ls)
+          add_problem(gb, lb.A + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "c0.l" + std::to_string(l)), C,
+                      lb.out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "c.b") : nullptr, 0,
+                      (long long)C * C, C, tiles(b, l));
+        CK(launch_gemm(gb, NL, s));
+        if (cfg.correlation >= 2) {
+          GemmBatch<T> g2 = species_batch(b);
+          for (size_t i = 0; i < p.out_ls.size(); ++i) {
+            const int l = p.out_ls[i];
+            const int K = p.pb.k[i] * C;
+            add_problem(g2, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, 2 * l + 1, K,
+                        w(pre + "c1.l" + std::to_string(l)), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 1,
+                        (long long)K * C, 0, tiles(b, l));
+          }
+          CK(launch_gemm(g2, NL, s));
+        }
+      }
+      {
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l : p.out_ls)
+          add_problem(gb, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "lin.l" + std::to_string(l)),
+                      C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "lin.b") : nullptr, 0);
+        CK(launch_gemm(gb, NL, s));
+      }
+      if (p.has_res) {  // per-species skip connection from the layer input
+        GemmBatch<T> gb = species_batch(b);
+        for (int l : p.out_ls)
+          add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "res.l" + std::to_string(l)),
+                      C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "res.b") : nullptr, 1,
+                      (long long)C * C, C, tiles(b, l));
+        CK(launch_gemm(gb, NL, s));
+      }
+      debug.push_back({"h" + std::to_string(t + 1), lb.h_out, NL * p.Dout * C});
+    }
+
+    // ---- read-out
+    LayerBufs& top = b.lay[NL_ - 1];
+    ReadoutArgs<T> ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.h = top.h_out; ra.hs = (long long)layers[NL_ - 1].Dout * C; ra.W1 = w("ro.W1"); ra.W2 = w("ro.W2");
+    ra.scale = w("scale"); ra.e0 = w("e0"); ra.species = bt->species; ra.atom_graph = b.atom_graph;
+    ra.graph_ptr = bt->graph_ptr; ra.rowptr_dst = b.rowptr_dst; ra.node_energy = static_cast<T*>(o->node_energy);
+    ra.e_scaled = b.e_scaled; ra.gh = need_grad ? top.gh_out : nullptr; ra.n = (int)NL; ra.C = C; ra.H = H;
+    CK(launch_readout(ra, s));
+    if (o->energy) CK(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, static_cast<T*>(o->energy), B, s));
+    if (!need_grad) return TACE_OK;
+
+    // ---- layers, backward
+    for (int t = NL_ - 1; t >= 0; --t) {
+      const LayerPlan& p = layers[t];
+      LayerBufs& lb = b.lay[t];
+      const std::string pre = "t" + std::to_string(t) + ".";
+      {  // through the final linear
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l : p.out_ls)
+          add_problem(gb, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "linT.l" + std::to_string(l)),
+                      C, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 0);
+        CK(launch_gemm(gb, NL, s));
+      }
+      if ((int)p.out_ls.size() != L + 1) CK(launch_fill_zero(lb.gA, NL * D * C, s));
+      {  // through the per-species coefficients
+        GemmBatch<T> gb = species_batch(b);
+        for (int l : p.out_ls)
+          add_problem(gb, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "c0T.l" + std::to_string(l)),
+                      C, lb.gA + (long long)l * l * C, (long long)D * C, C, nullptr, 0, (long long)C * C, 0, tiles(b, l));
+        CK(launch_gemm(gb, NL, s));
+        if (cfg.correlation >= 2) {
+          GemmBatch<T> g2 = species_batch(b);
+          for (size_t i = 0; i < p.out_ls.size(); ++i) {
+            const int l = p.out_ls[i];
+            const int K = p.pb.k[i] * C;
+            add_problem(g2, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C,
+                        w(pre + "c1T.l" + std::to_string(l)), K, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K,
+                        nullptr, 0, (long long)K * C, 0, tiles(b, l));
+          }
+          CK(launch_gemm(g2, NL, s));
+          CK(launch_pb_bwd(lb.A, lb.B2, lb.gA, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
+        }
+      }
+      {
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l = 0; l <= L; ++l)
+          add_problem(gb, lb.gA + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nlT.l" + std::to_string(l)), C,
+                      lb.ga + (long long)l * l * C, (long long)D * C, C, nullptr, 0);
+        CK(launch_gemm(gb, NL, s));
+      }
+      CK(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, s));
+      {  // through linear_down; the gradient of the messages overwrites the messages
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l = 0; l <= L; ++l) {
+          const int Nk = p.tp.k[l] * C;
+          const int Kin = (l == 0) ? (L + 2) * C : C;
+          const T* src = (l == 0) ? lb.gGt : lb.gGt + (long long)(L + 1 + l * l) * C;
+          add_problem(gb, src, (long long)(L + 1 + D) * C, C, 2 * l + 1, Kin, w(pre + "downT.l" + std::to_string(l)), Nk,
+                      lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, Nk, nullptr, 0);
+        }
+        CK(launch_gemm(gb, NL, s));
+      }
+      TPArgs<T> ta;
+      memset(&ta, 0, sizeof(ta));
+      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W;
+      ta.x = lb.x; ta.gM = lb.M;
+      if (!p.scalar_src) {  // gradient with respect to the source features (needs W before it is overwritten)
+        ta.n_seg = (int)N; ta.rowptr = b.rowptr_src; ta.perm = b.perm_src; ta.dx = lb.gx;
+        CK(launch_tp_bwd_src(ta, s));
+      }
+      ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.perm = nullptr; ta.dW = lb.W; ta.dY = b.dY;
+      ta.accumulate_dY = (t != NL_ - 1);
+      CK(launch_tp_bwd_edge(ta, s));
+      {  // back through the last radial-MLP layer
+        GemmBatch<T> gb = plain_batch(E);
+        add_problem(gb, lb.W, (long long)p.tp.NP * C, 0, 1, p.tp.NP * C, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
+        CK(launch_gemm(gb, E, s));
+      }
+      if (!p.scalar_src) {
+        GemmBatch<T> gb = plain_batch(NL);
+        for (int l : p.in_ls)
+          add_problem(gb, lb.gx + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C, w(pre + "upT.l" + std::to_string(l)),
+                      C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 0);
+        CK(launch_gemm(gb, NL, s));
+        if (p.has_res) {
+          GemmBatch<T> g2 = species_batch(b);
+          for (int l : p.out_ls)
+            add_problem(g2, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C,
+                        w(pre + "resT.l" + std::to_string(l)), C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 1,
+                        (long long)C * C, 0, tiles(b, l));
+          CK(launch_gemm(g2, NL, s));
+        }
+      }
+    }
+
+    // ---- back to the edge vectors, then forces and virials
+    CK(launch_edge_bwd(ea, s));
+    debug.push_back({"g", b.g, 3 * E});
+    const bool want_virial = (o->virials || o->stress) && !vec_mode;
+    ForceArgs<T> fa;
+    memset(&fa, 0, sizeof(fa));
+    fa.n_atoms = (int)N; fa.n_local = (int)NL; fa.rowptr_dst = b.rowptr_dst; fa.rowptr_src = b.rowptr_src;
+    fa.perm_src = b.perm_src; fa.g = b.g; fa.vec = b.vec; fa.forces = static_cast<T*>(o->forces);
+    fa.atom_virial = want_virial ? b.atom_virial : nullptr;
+    if (fa.forces || fa.atom_virial) CK(launch_forces(fa, s));
+    if (want_virial)
+      CK(launch_graph_virial(b.atom_virial, bt->graph_ptr, static_cast<const T*>(bt->lattice), static_cast<T*>(o->virials),
+                             static_cast<T*>(o->stress), B, s));
+    return TACE_OK;
+  }
+
+  int64_t debug_read(const char* name, void* dst, int64_t numel, cudaStream_t s) override {
+    for (const auto& d : debug) {
+      if (d.name == name) {
+        const long long n = d.numel < numel ? d.numel : numel;
+        if (cudaMemcpyAsync(dst, d.ptr, sizeof(T) * (size_t)n, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return TACE_ERR_CUDA;
+        return n;
+      }
+    }
+    return TACE_ERR_INVALID_ARGUMENT;
+  }
+};
+
+}  // namespace tace
+
+using tace::ModelBase;
+
+struct TaceModel {
+  ModelBase* impl;
+};
+
+extern "C" {
+
+const char* tace_status_string(int status) {
+  switch (status) {
+    case TACE_OK: return "ok";
+    case TACE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case TACE_ERR_UNSUPPORTED_CONFIG: return "unsupported model configuration";
+    case TACE_ERR_CAPACITY: return "capacity exceeded (workspace too small or index range)";
+    case TACE_ERR_CUDA: return "CUDA error";
+    case TACE_ERR_NO_DEVICE: return "no sm_100 CUDA device";
+    case TACE_ERR_UNKNOWN_WEIGHT: return "unknown weight name";
+    case TACE_ERR_WEIGHTS_MISSING: return "weights not fully set";
+    default: return "unknown status";
+  }
+}
+
+int tace_create(const TaceConfig* cfg, TaceModel** out) {
+  if (!cfg || !out) return TACE_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (cfg->L < 1 || cfg->L > 3 || cfg->num_layers < 1 || cfg->num_layers > tace::kMaxLayers || cfg->num_channel < 32 ||
+      cfg->num_channel > 256 || (cfg->num_channel & 31) || cfg->num_elements < 1 || cfg->correlation < 1 ||
+      cfg->correlation > 2 || cfg->num_bessel != tace::kNumBessel || cfg->mlp_hidden != tace::kHidden ||
+      cfg->readout_hidden < 1 || cfg->readout_hidden > 64 || cfg->envelope_p < 2 || !(cfg->cutoff > 0.0) ||
+      !(cfg->avg_num_neighbors > 0.0) || (cfg->dtype != TACE_F32 && cfg->dtype != TACE_F64))
+    return TACE_ERR_UNSUPPORTED_CONFIG;
+  int dev = 0;
+  cudaDeviceProp prop;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return TACE_ERR_NO_DEVICE;
+  if (prop.major != 10) return TACE_ERR_NO_DEVICE;
+  ModelBase* impl = nullptr;
+  int st;
+  if (cfg->dtype == TACE_F32) {
+    auto* m = new (std::nothrow) tace::Model<float>();
+    if (!m) return TACE_ERR_CUDA;
+    st = m->init(*cfg); impl = m;
+  } else {
+    auto* m = new (std::nothrow) tace::Model<double>();
+    if (!m) return TACE_ERR_CUDA;
+    st = m->init(*cfg); impl = m;
+  }
+  if (st != TACE_OK) { delete impl; return st; }
+  *out = new TaceModel{impl};
+  return TACE_OK;
+}
+
+void tace_destroy(TaceModel* model) {
+  if (!model) return;
+  delete model->impl;
+  delete model;
+}
+
+int tace_weight_count(const TaceModel* model) { return model ? model->impl->weight_count() : TACE_ERR_INVALID_ARGUMENT; }
+int tace_weight_info(const TaceModel* model, int index, const char** name, int64_t* numel) {
+  return model ? model->impl->weight_info(index, name, numel) : TACE_ERR_INVALID_ARGUMENT;
+}
+int tace_set_weight(TaceModel* model, const char* name, const void* host_data, int64_t numel) {
+  return model ? model->impl->set_weight(name, host_data, numel) : TACE_ERR_INVALID_ARGUMENT;
+}
+int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_local, int64_t n_edges, int32_t n_graphs,
+                         size_t* bytes) {
+  return model ? const_cast<TaceModel*>(model)->impl->workspace_bytes(n_atoms, n_local, n_edges, n_graphs, bytes)
+               : TACE_ERR_INVALID_ARGUMENT;
+}
+int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace, size_t workspace_bytes,
+                 tace_stream_t stream) {
+  if (!model) return TACE_ERR_INVALID_ARGUMENT;
+  return model->impl->forward(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+int64_t tace_debug_read(TaceModel* model, const char* name, void* dst, int64_t numel, tace_stream_t stream) {
+  if (!model || !name || !dst) return TACE_ERR_INVALID_ARGUMENT;
+  return model->impl->debug_read(name, dst, numel, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

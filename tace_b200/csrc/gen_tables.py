@@ -160,7 +160,7 @@ def gen_interaction(L, scalar_src, out):
 
     # forward: acc[idx(p,m3)] += w[p] * sum_m1 x[m1] G[m1][m3]
     o("template <typename T>")
-    o(f"TACE_HD inline void tp_fwd_{tag}(const T (&x)[{nx}], const T* __restrict__ G, const T (&w)[{P}], T (&acc)[{lay.nm}]) {{")
+    o(f"TACE_HD TACE_INLINE void tp_fwd_{tag}(const T (&x)[{nx}], const T* __restrict__ G, const T (&w)[{P}], T (&acc)[{lay.nm}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         for m3 in range(2 * l3 + 1):
             terms = [f"x[{xoff[l1] + m1}] * G[{gterm(p, m1, m3)}]" for m1 in range(2 * l1 + 1)
@@ -171,7 +171,7 @@ def gen_interaction(L, scalar_src, out):
 
     # backward wrt x (source features): dx[m1] += w[p] * sum_m3 G[m1][m3] g[idx(p,m3)]
     o("template <typename T>")
-    o(f"TACE_HD inline void tp_bwdx_{tag}(const T (&g)[{lay.nm}], const T* __restrict__ G, const T (&w)[{P}], T (&dx)[{nx}]) {{")
+    o(f"TACE_HD TACE_INLINE void tp_bwdx_{tag}(const T (&g)[{lay.nm}], const T* __restrict__ G, const T (&w)[{P}], T (&dx)[{nx}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         for m1 in range(2 * l1 + 1):
             terms = [f"G[{gterm(p, m1, m3)}] * g[{lay.idx(p, m3)}]" for m3 in range(2 * l3 + 1)
@@ -182,7 +182,7 @@ def gen_interaction(L, scalar_src, out):
 
     # backward wrt per-edge weights and angular features
     o("template <typename T>")
-    o(f"TACE_HD inline void tp_bwdw_{tag}(const T (&x)[{nx}], const T (&g)[{lay.nm}], const T* __restrict__ G, "
+    o(f"TACE_HD TACE_INLINE void tp_bwdw_{tag}(const T (&x)[{nx}], const T (&g)[{lay.nm}], const T* __restrict__ G, "
       f"const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         n3 = 2 * l3 + 1
@@ -200,6 +200,17 @@ def gen_interaction(L, scalar_src, out):
                 o(f"    dY[{l2 * l2 + m2}] += w[{p}] * ({' + '.join(terms)});")
         o("  }")
     o("}")
+    o(f"struct TPX_{tag} : TP_{tag} {{")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd(const T (&x)[{nx}], const T* __restrict__ G, const T (&w)[{P}], "
+      f"T (&acc)[{lay.nm}]) {{ tp_fwd_{tag}<T>(x, G, w, acc); }}")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwdx(const T (&g)[{lay.nm}], const T* __restrict__ G, const T (&w)[{P}], "
+      f"T (&dx)[{nx}]) {{ tp_bwdx_{tag}<T>(g, G, w, dx); }}")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwdw(const T (&x)[{nx}], const T (&g)[{lay.nm}], const T* __restrict__ G, "
+      f"const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}]) {{ tp_bwdw_{tag}<T>(x, g, G, w, dw, dY); }}")
+    o(f"  static TACE_D TACE_INLINE const short* gstart() {{ return tp_{tag}_gstart; }}")
+    o(f"  static TACE_D TACE_INLINE const unsigned char* gy() {{ return tp_{tag}_gy; }}")
+    o(f"  static TACE_D TACE_INLINE const double* gc() {{ return tp_{tag}_gc; }}")
+    o("};")
     return dict(tag=tag, P=P, nm=lay.nm, ng=ng, nnz=nnz_total)
 
 
@@ -220,7 +231,7 @@ def gen_product(L, last, out):
     o(f"static const int pb_{tag}_k[{len(outs)}] = {{{', '.join(str(lay.k[l]) for l in outs)}}};")
     o(f"static const int pb_{tag}_base[{len(outs)}] = {{{', '.join(str(lay.base[l]) for l in outs)}}};")
     o("template <typename T>")
-    o(f"TACE_HD inline void pb_fwd_{tag}(const T (&a)[{D}], T (&b)[{lay.nm}]) {{")
+    o(f"TACE_HD TACE_INLINE void pb_fwd_{tag}(const T (&a)[{D}], T (&b)[{lay.nm}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         K = w3j(l1, l2, l3) * math.sqrt(2 * l3 + 1)
         for m3 in range(2 * l3 + 1):
@@ -229,7 +240,7 @@ def gen_product(L, last, out):
             o(f"  b[{lay.idx(p, m3)}] = {' + '.join(terms) if terms else 'T(0)'};")
     o("}")
     o("template <typename T>")
-    o(f"TACE_HD inline void pb_bwd_{tag}(const T (&a)[{D}], const T (&db)[{lay.nm}], T (&da)[{D}]) {{")
+    o(f"TACE_HD TACE_INLINE void pb_bwd_{tag}(const T (&a)[{D}], const T (&db)[{lay.nm}], T (&da)[{D}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         K = w3j(l1, l2, l3) * math.sqrt(2 * l3 + 1)
         for m1 in range(2 * l1 + 1):
@@ -243,6 +254,11 @@ def gen_product(L, last, out):
             if terms:
                 o(f"  da[{l2 * l2 + m2}] += {' + '.join(terms)};")
     o("}")
+    o(f"struct PBX_{tag} : PB_{tag} {{")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd(const T (&a)[{D}], T (&b)[{lay.nm}]) {{ pb_fwd_{tag}<T>(a, b); }}")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd(const T (&a)[{D}], const T (&db)[{lay.nm}], T (&da)[{D}]) "
+      f"{{ pb_bwd_{tag}<T>(a, db, da); }}")
+    o("};")
     return dict(tag=tag, P=P, nb=lay.nm, nnz=nnz)
 
 

@@ -1,0 +1,120 @@
+// Graph preparation: from the caller's edge_index (any order) to target-sorted and
+// source-sorted CSR views, the atom -> graph map, and the species-sorted atom permutation used
+// by the per-species linear layers.  Stable radix sorts (CUB) keep every ordering
+// deterministic, which makes the segmented sums downstream bit-reproducible.
+#include <cub/cub.cuh>
+#include "kernels.h"
+
+namespace tace {
+
+namespace {
+
+__global__ void iota_and_key_kernel(const int64_t* __restrict__ key_src, int* keys, int* vals, long long n) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  keys[i] = (int)key_src[i];
+  vals[i] = (int)i;
+}
+__global__ void iota_and_key32_kernel(const int* __restrict__ key_src, int* keys, int* vals, long long n) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  keys[i] = key_src[i];
+  vals[i] = (int)i;
+}
+__global__ void gather_src_kernel(const int64_t* __restrict__ src_row, const int* __restrict__ e_orig, int* e_src, long long n) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  e_src[i] = (int)src_row[e_orig[i]];
+}
+// rowptr[i] = number of sorted keys < i, i = 0..n_rows
+__global__ void lower_bound_kernel(const int* __restrict__ sorted_keys, long long n_keys, int* rowptr, int n_rows) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > n_rows) return;
+  long long lo = 0, hi = n_keys;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if (sorted_keys[mid] < i) lo = mid + 1; else hi = mid;
+  }
+  rowptr[i] = (int)lo;
+}
+__global__ void atom_graph_kernel(const int* __restrict__ graph_ptr, int n_graphs, int* atom_graph, int n_atoms) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_atoms) return;
+  int lo = 0, hi = n_graphs;  // largest g with graph_ptr[g] <= i
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (graph_ptr[mid] <= i) lo = mid; else hi = mid;
+  }
+  atom_graph[i] = lo;
+}
+__global__ void tile_ptr_kernel(const int* __restrict__ species_ptr, int n_el, int* tile_ptr) {
+  const int qi = threadIdx.x;  // q = 2*qi + 1
+  if (qi >= 4) return;
+  const int q = 2 * qi + 1;
+  int* tp = tile_ptr + qi * (n_el + 1);
+  int acc = 0;
+  for (int g = 0; g < n_el; ++g) {
+    tp[g] = acc;
+    acc += ((species_ptr[g + 1] - species_ptr[g]) * q + 63) / 64;
+  }
+  tp[n_el] = acc;
+}
+
+inline size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
+
+size_t cub_sort_bytes(long long n) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr, (int*)nullptr,
+                                  (int)n);
+  return bytes;
+}
+
+}  // namespace
+
+size_t graph_prep_temp_bytes(long long E, int n_atoms) {
+  const long long n = E > n_atoms ? E : n_atoms;
+  return 3 * align_up(sizeof(int) * (size_t)n) + align_up(cub_sort_bytes(n)) + 256;
+}
+
+cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
+  const long long n = a.E > a.n_atoms ? a.E : a.n_atoms;
+  unsigned char* p = static_cast<unsigned char*>(a.temp);
+  int* keys_in = reinterpret_cast<int*>(p); p += align_up(sizeof(int) * (size_t)n);
+  int* vals_in = reinterpret_cast<int*>(p); p += align_up(sizeof(int) * (size_t)n);
+  int* keys_out = reinterpret_cast<int*>(p); p += align_up(sizeof(int) * (size_t)n);
+  void* cub_temp = p;
+  size_t cub_bytes = cub_sort_bytes(n);
+  if ((size_t)(p - static_cast<unsigned char*>(a.temp)) + cub_bytes > a.temp_bytes) return cudaErrorInvalidValue;
+  int bits = 1;
+  while ((1LL << bits) < (long long)a.n_atoms + 1 && bits < 31) ++bits;
+  cudaError_t err;
+
+  atom_graph_kernel<<<(a.n_atoms + 255) / 256, 256, 0, s>>>(a.graph_ptr, a.n_graphs, a.atom_graph, a.n_atoms);
+
+  if (a.E > 0) {
+    const unsigned eb = (unsigned)((a.E + 255) / 256);
+    // target-sorted view
+    iota_and_key_kernel<<<eb, 256, 0, s>>>(a.edge_index + a.E, keys_in, vals_in, a.E);
+    err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, a.e_dst, vals_in, a.e_orig, (int)a.E, 0, bits, s);
+    if (err != cudaSuccess) return err;
+    gather_src_kernel<<<eb, 256, 0, s>>>(a.edge_index, a.e_orig, a.e_src, a.E);
+    // source-sorted view over the target-sorted numbering
+    iota_and_key32_kernel<<<eb, 256, 0, s>>>(a.e_src, keys_in, vals_in, a.E);
+    err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.perm_src, (int)a.E, 0, bits, s);
+    if (err != cudaSuccess) return err;
+  }
+  lower_bound_kernel<<<(a.n_local + 256) / 256, 256, 0, s>>>(a.e_dst, a.E, a.rowptr_dst, a.n_local);
+  lower_bound_kernel<<<(a.n_atoms + 256) / 256, 256, 0, s>>>(keys_out, a.E, a.rowptr_src, a.n_atoms);
+
+  // species-sorted permutation of the local atoms
+  int sbits = 1;
+  while ((1 << sbits) < a.n_elements + 1 && sbits < 31) ++sbits;
+  iota_and_key32_kernel<<<(a.n_local + 255) / 256, 256, 0, s>>>(a.species, keys_in, vals_in, a.n_local);
+  err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.species_perm, a.n_local, 0, sbits, s);
+  if (err != cudaSuccess) return err;
+  lower_bound_kernel<<<(a.n_elements + 256) / 256, 256, 0, s>>>(keys_out, a.n_local, a.species_ptr, a.n_elements);
+  tile_ptr_kernel<<<1, 32, 0, s>>>(a.species_ptr, a.n_elements, a.tile_ptr);
+  return cudaGetLastError();
+}
+
+}  // namespace tace

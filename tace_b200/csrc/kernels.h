@@ -1,0 +1,134 @@
+// Internal launcher interface between the engine (engine.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "tace_math.cuh"
+
+namespace tace {
+
+// ---- interaction tensor product (tp_kernels.cu) ---------------------------------------------
+// Message passing m_i = sum_{e: target(e) = i} sum_p w[e,p,c] (x[source(e)] (x) Y[e])_p, its
+// transpose with respect to the source features, and the gradients with respect to the
+// per-edge weights and angular features.  Follows O3ScatterTensorProduct.forward
+// (tace/models/_e3nn/fused.py:259-271); edges are grouped by target (forward, edge gradients)
+// or by source (source gradients) so every sum is a segmented reduction without atomics.
+template <typename T>
+struct TPArgs {
+  int L, scalar_src, C;
+  int n_seg;          // number of targets (or sources) = thread blocks
+  const int* rowptr;  // [n_seg+1] CSR over the segment's edges
+  const int* perm;    // source pass: CSR slot -> edge id (target-sorted numbering); else nullptr
+  const int* e_src;   // [E] source atom of each edge (target-sorted numbering)
+  const int* e_dst;   // [E] target atom
+  const T* Y;         // [E][D] angular features
+  const T* W;         // [E][NP*C] per-edge path weights
+  const T* x;         // [N][NX][C] source features
+  T* M;               // forward output [n_seg][NM][C]
+  const T* gM;        // [n_targets][NM][C] gradient of the messages
+  T* dW;              // edge pass output [E][NP*C] (may alias W)
+  T* dY;              // edge pass output [E][D]
+  int accumulate_dY;  // add into dY instead of overwriting
+  T* dx;              // source pass output [n_seg][NX][C]
+};
+template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_tp_bwd_edge(const TPArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_tp_bwd_src(const TPArgs<T>& a, cudaStream_t s);
+
+// ---- per-atom element-wise kernels (node_kernels.cu) -----------------------------------------
+// x0[n][c] = table[species[n]][c]
+template <typename T> cudaError_t launch_species_gather(const T* table, const int* species, T* out, int n, int C, cudaStream_t s);
+// gate (tace/models/_e3nn/nonlinear.py:125-135): Gt = [(L+1)C gates | D*C gated] per atom.
+template <typename T> cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, cudaStream_t s);
+template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, cudaStream_t s);
+// product basis A (x) A (tace/models/_e3nn/prod.py:242-256, fused.py:90-95)
+template <typename T> cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int last, int C, cudaStream_t s);
+template <typename T> cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int last, int C, cudaStream_t s);
+// read-out C -> H -> 1 with scaled SiLU, per-species scale, isolated-atom masking, atomic energies
+// (tace/models/_e3nn/readout.py:72-84, tace/models/blocks.py:250-273,332-379, _e3nn/tace.py:361-417).
+template <typename T>
+struct ReadoutArgs {
+  const T* h;        // [n][hs] scalar channels at offset 0, stride hs
+  long long hs;
+  const T* W1;       // [C][H]
+  const T* W2;       // [H]
+  const T* scale;    // [n_el]
+  const T* e0;       // [n_el]
+  const int* species;
+  const int* atom_graph;  // [n] graph of each atom
+  const int* graph_ptr;   // [B+1]
+  const int* rowptr_dst;  // [n+1] to count a graph's edges
+  T* node_energy;    // [n] or nullptr (E0 + scaled read-out)
+  T* e_scaled;       // [n] scaled read-out without E0 (summed per graph together with E0)
+  T* gh;             // [n][C] d(sum E)/dh, or nullptr
+  int n, C, H;
+};
+template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);
+// energy[g] = sum_{i in g} (e0[species_i] + e_scaled[i])
+template <typename T> cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr,
+                                                     T* energy, int n_graphs, cudaStream_t s);
+template <typename T> cudaError_t launch_fill_zero(T* p, long long n, cudaStream_t s);
+template <typename T> cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s);
+
+// ---- per-edge kernels (edge_kernels.cu) -------------------------------------------------------
+template <typename T>
+struct MlpWeights {
+  const T* A0; const T* A1; const T* A2; const T* A1t; const T* A2t;
+};
+constexpr int kMaxLayers = 4;
+template <typename T>
+struct EdgeArgs {
+  int L, n_layers;
+  long long E;
+  const int* e_src; const int* e_dst; const int* e_orig;  // target-sorted edges; e_orig = caller's edge id
+  const T* positions;    // [N][3] or nullptr
+  const T* lattice;      // [B][3][3]
+  const int* atom_graph; // [N]
+  const T* shifts;       // [E][3] caller order, or nullptr
+  const T* edge_vector;  // [E][3] caller order, or nullptr
+  RadialParams<T> rp;
+  MlpWeights<T> mlp[kMaxLayers];
+  T* vec;                // [E][3] edge vectors (target-sorted order)
+  T* Y;                  // [E][D]
+  T* H3[kMaxLayers];     // [E][64] last hidden activation of each layer's radial MLP
+  // backward
+  const T* dH3[kMaxLayers];
+  const T* dY;           // [E][D]
+  T* g;                  // [E][3] dE/d(edge vector), target-sorted order
+  T* edge_forces;        // [E][3] caller order, or nullptr
+};
+template <typename T> cudaError_t launch_edge_fwd(const EdgeArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_edge_bwd(const EdgeArgs<T>& a, cudaStream_t s);
+
+// forces[i] = -(sum_{e: target = i} g_e - sum_{e: source = i} g_e); per-atom virial rows
+// w[i] = sum_{e: target = i} v_e (x) g_e (tace/models/adapter.py:106-116, utils.py:50-79).
+template <typename T>
+struct ForceArgs {
+  int n_atoms, n_local;
+  const int* rowptr_dst; const int* rowptr_src; const int* perm_src;
+  const T* g; const T* vec;
+  T* forces;       // [n_atoms][3] or nullptr
+  T* atom_virial;  // [n_local][9] or nullptr
+};
+template <typename T> cudaError_t launch_forces(const ForceArgs<T>& a, cudaStream_t s);
+// virials[g] = -sym(sum_i w[i]); stress = -virials / |det lattice| with |stress| >= 1e10 zeroed
+template <typename T> cudaError_t launch_graph_virial(const T* atom_virial, const int* graph_ptr, const T* lattice, T* virials,
+                                                     T* stress, int n_graphs, cudaStream_t s);
+
+// ---- graph preparation (graph_kernels.cu) ------------------------------------------------------
+struct GraphPrepArgs {
+  long long E; int n_atoms, n_local, n_graphs, n_elements;
+  const int64_t* edge_index;  // [2][E]
+  const int* species; const int* graph_ptr;
+  // outputs
+  int* e_src; int* e_dst; int* e_orig;  // target-sorted
+  int* rowptr_dst;            // [n_local+1]
+  int* perm_src; int* rowptr_src;       // [E], [n_atoms+1]
+  int* atom_graph;            // [n_atoms]
+  int* species_perm; int* species_ptr;  // [n_local], [n_elements+1]
+  int* tile_ptr;              // [4][n_elements+1] for q = 1,3,5,7
+  void* temp; size_t temp_bytes;
+};
+size_t graph_prep_temp_bytes(long long E, int n_atoms);
+cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s);
+
+}  // namespace tace

@@ -1,0 +1,242 @@
+// Per-atom element-wise kernels: species gather, gate, product basis, read-out, graph sums.
+// Feature layout everywhere: [atom][component (l, m)][channel], channel fastest, so a warp
+// always touches 32 consecutive channels of one component.
+#include "kernels.h"
+#include "tp_gen.cuh"
+
+namespace tace {
+
+constexpr double kSigmoidCst = 1.8467055342154763;  // tace/models/mlp.py:43
+constexpr double kSiluCst = 1.6791767923989418;     // tace/models/mlp.py:34
+
+template <typename T>
+__global__ void fill_zero_kernel(T* p, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) p[i] = T(0);
+}
+template <typename T>
+cudaError_t launch_fill_zero(T* p, long long n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const int blocks = (int)(((n + 255) / 256 < 148LL * 16) ? (n + 255) / 256 : 148LL * 16);
+  fill_zero_kernel<T><<<blocks, 256, 0, s>>>(p, n);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void add_inplace_kernel(T* dst, const T* src, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
+}
+template <typename T>
+cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const int blocks = (int)(((n + 255) / 256 < 148LL * 16) ? (n + 255) / 256 : 148LL * 16);
+  add_inplace_kernel<T><<<blocks, 256, 0, s>>>(dst, src, n);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void species_gather_kernel(const T* __restrict__ table, const int* __restrict__ species, T* out, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  out[idx] = table[(long long)species[i] * C + c];
+}
+template <typename T>
+cudaError_t launch_species_gather(const T* table, const int* species, T* out, int n, int C, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const long long tot = (long long)n * C;
+  species_gather_kernel<T><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>(table, species, out, n, C);
+  return cudaGetLastError();
+}
+
+// ---- gate --------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int n, int L, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  const int D = (L + 1) * (L + 1);
+  const T* row = Gt + (long long)i * (L + 1 + D) * C;
+  T* out = a + (long long)i * D * C;
+  for (int l = 0; l <= L; ++l) {
+    const T gate = T(kSigmoidCst) * sigmoid_(row[l * C + c]);
+    for (int m = 0; m < 2 * l + 1; ++m) {
+      const int k = l * l + m;
+      out[k * C + c] = row[(L + 1 + k) * C + c] * gate;
+    }
+  }
+}
+template <typename T>
+__global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ ga, T* __restrict__ gGt, int n, int L, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  const int D = (L + 1) * (L + 1);
+  const T* row = Gt + (long long)i * (L + 1 + D) * C;
+  const T* g = ga + (long long)i * D * C;
+  T* out = gGt + (long long)i * (L + 1 + D) * C;
+  for (int l = 0; l <= L; ++l) {
+    const T sg = sigmoid_(row[l * C + c]);
+    const T gate = T(kSigmoidCst) * sg;
+    T acc = T(0);
+    for (int m = 0; m < 2 * l + 1; ++m) {
+      const int k = l * l + m;
+      const T gk = g[k * C + c];
+      acc += gk * row[(L + 1 + k) * C + c];
+      out[(L + 1 + k) * C + c] = gk * gate;
+    }
+    out[l * C + c] = acc * T(kSigmoidCst) * sg * (T(1) - sg);
+  }
+}
+template <typename T>
+cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  gate_fwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, a, n, L, C);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  gate_bwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, ga, gGt, n, L, C);
+  return cudaGetLastError();
+}
+
+// ---- product basis -----------------------------------------------------------------------------
+template <typename T, typename PB>
+__global__ void __launch_bounds__(128) pb_fwd_kernel(const T* __restrict__ A, T* __restrict__ B2, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  T a[PB::D], b[PB::NB];
+  const T* Ai = A + (long long)i * PB::D * C;
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) a[k] = Ai[k * C + c];
+  PB::template fwd<T>(a, b);
+  T* Bi = B2 + (long long)i * PB::NB * C;
+#pragma unroll
+  for (int k = 0; k < PB::NB; ++k) Bi[k * C + c] = b[k];
+}
+// gA += d(B2)/dA^T gB2
+template <typename T, typename PB>
+__global__ void __launch_bounds__(128) pb_bwd_kernel(const T* __restrict__ A, const T* __restrict__ gB2, T* __restrict__ gA, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  T a[PB::D], db[PB::NB], da[PB::D];
+  const T* Ai = A + (long long)i * PB::D * C;
+  const T* Gi = gB2 + (long long)i * PB::NB * C;
+  T* gAi = gA + (long long)i * PB::D * C;
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) { a[k] = Ai[k * C + c]; da[k] = gAi[k * C + c]; }
+#pragma unroll
+  for (int k = 0; k < PB::NB; ++k) db[k] = Gi[k * C + c];
+  PB::template bwd<T>(a, db, da);
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) gAi[k * C + c] = da[k];
+}
+
+#define TACE_PB_DISPATCH(KERNEL, ...)                                                      \
+  if (n <= 0) return cudaSuccess;                                                          \
+  const unsigned grid = (unsigned)(((long long)n * C + 127) / 128);                        \
+  if (L == 1 && !last) KERNEL<T, PBX_L1_A><<<grid, 128, 0, s>>>(__VA_ARGS__);               \
+  else if (L == 1) KERNEL<T, PBX_L1_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
+  else if (L == 2 && !last) KERNEL<T, PBX_L2_A><<<grid, 128, 0, s>>>(__VA_ARGS__);          \
+  else if (L == 2) KERNEL<T, PBX_L2_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
+  else if (L == 3 && !last) KERNEL<T, PBX_L3_A><<<grid, 128, 0, s>>>(__VA_ARGS__);          \
+  else if (L == 3) KERNEL<T, PBX_L3_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
+  else return cudaErrorInvalidValue;                                                       \
+  return cudaGetLastError();
+
+template <typename T>
+cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int last, int C, cudaStream_t s) {
+  TACE_PB_DISPATCH(pb_fwd_kernel, A, B2, n, C)
+}
+template <typename T>
+cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int last, int C, cudaStream_t s) {
+  TACE_PB_DISPATCH(pb_bwd_kernel, A, gB2, gA, n, C)
+}
+
+// ---- read-out ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void readout_kernel(const ReadoutArgs<T> a) {
+  extern __shared__ unsigned char smem_raw[];
+  T* W1s = reinterpret_cast<T*>(smem_raw);  // [C][H]
+  for (int k = threadIdx.x; k < a.C * a.H; k += blockDim.x) W1s[k] = a.W1[k];
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.n) return;
+  const T* h = a.h + (long long)i * a.hs;
+  T r[64];
+  for (int j = 0; j < a.H; ++j) r[j] = T(0);
+  for (int c = 0; c < a.C; ++c) {
+    const T hc = h[c];
+    for (int j = 0; j < a.H; ++j) r[j] += hc * W1s[c * a.H + j];
+  }
+  T e = T(0);
+  for (int j = 0; j < a.H; ++j) {
+    e += T(kSiluCst) * silu_(r[j]) * a.W2[j];
+    r[j] = T(kSiluCst) * silu_grad_(r[j]) * a.W2[j];  // d e / d r_j
+  }
+  const int z = a.species[i];
+  const int g = a.atom_graph[i];
+  const int n_nodes = a.graph_ptr[g + 1] - a.graph_ptr[g];
+  const int n_edges = a.rowptr_dst[a.graph_ptr[g + 1]] - a.rowptr_dst[a.graph_ptr[g]];
+  const T sc = (n_nodes == 1 && n_edges == 0) ? T(0) : a.scale[z];
+  const T es = e * sc;
+  a.e_scaled[i] = es;
+  if (a.node_energy) a.node_energy[i] = a.e0[z] + es;
+  if (a.gh) {
+    T* gh = a.gh + (long long)i * a.C;
+    for (int c = 0; c < a.C; ++c) {
+      T v = T(0);
+      for (int j = 0; j < a.H; ++j) v += r[j] * W1s[c * a.H + j];
+      gh[c] = v * sc;
+    }
+  }
+}
+template <typename T>
+cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
+  if (a.n <= 0) return cudaSuccess;
+  if (a.H > 64) return cudaErrorInvalidValue;
+  const size_t smem = sizeof(T) * a.C * a.H;
+  readout_kernel<T><<<(a.n + 63) / 64, 64, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void graph_energy_kernel(const T* __restrict__ e_scaled, const T* __restrict__ e0, const int* __restrict__ species,
+                                    const int* __restrict__ graph_ptr, T* energy) {
+  __shared__ T red[256];
+  const int g = blockIdx.x;
+  T acc = T(0);
+  for (int i = graph_ptr[g] + threadIdx.x; i < graph_ptr[g + 1]; i += blockDim.x) acc += e0[species[i]] + e_scaled[i];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) energy[g] = red[0];
+}
+template <typename T>
+cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr, T* energy,
+                                int n_graphs, cudaStream_t s) {
+  if (n_graphs <= 0) return cudaSuccess;
+  graph_energy_kernel<T><<<n_graphs, 256, 0, s>>>(e_scaled, e0, species, graph_ptr, energy);
+  return cudaGetLastError();
+}
+
+#define INST(T)                                                                                               \
+  template cudaError_t launch_fill_zero<T>(T*, long long, cudaStream_t);                                      \
+  template cudaError_t launch_add_inplace<T>(T*, const T*, long long, cudaStream_t);                          \
+  template cudaError_t launch_species_gather<T>(const T*, const int*, T*, int, int, cudaStream_t);            \
+  template cudaError_t launch_gate_fwd<T>(const T*, T*, int, int, int, cudaStream_t);                         \
+  template cudaError_t launch_gate_bwd<T>(const T*, const T*, T*, int, int, int, cudaStream_t);               \
+  template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
+  template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
+  template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \
+  template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, T*, int, cudaStream_t);
+INST(float)
+INST(double)
+template cudaError_t launch_fill_zero<int>(int*, long long, cudaStream_t);
+
+}  // namespace tace

@@ -8,12 +8,14 @@
 #include <cstdint>
 
 #if defined(__CUDACC__)
-#define TACE_HD __host__ __device__ __forceinline__
-#define TACE_D __device__ __forceinline__
+#define TACE_HD __host__ __device__
+#define TACE_D __device__
+#define TACE_INLINE __forceinline__
 #define TACE_CONST static __device__ const
 #else
 #define TACE_HD
 #define TACE_D
+#define TACE_INLINE inline
 #define TACE_CONST static const
 #ifndef __restrict__
 #define __restrict__
@@ -23,16 +25,16 @@
 namespace tace {
 
 template <typename T>
-TACE_HD inline T sigmoid_(T x) { return T(1) / (T(1) + exp(-x)); }
+TACE_HD TACE_INLINE T sigmoid_(T x) { return T(1) / (T(1) + exp(-x)); }
 template <>
-TACE_HD inline float sigmoid_<float>(float x) { return 1.0f / (1.0f + expf(-x)); }
+TACE_HD TACE_INLINE float sigmoid_<float>(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 template <typename T>
-TACE_HD inline T silu_(T x) { return x * sigmoid_(x); }
+TACE_HD TACE_INLINE T silu_(T x) { return x * sigmoid_(x); }
 
 // d/dx [x * sigmoid(x)] = s * (1 + x * (1 - s))
 template <typename T>
-TACE_HD inline T silu_grad_(T x) {
+TACE_HD TACE_INLINE T silu_grad_(T x) {
   const T s = sigmoid_(x);
   return s * (T(1) + x * (T(1) - s));
 }

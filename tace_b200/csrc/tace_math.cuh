@@ -21,7 +21,7 @@ constexpr int kHidden = 64;
 
 // ---- spherical harmonics, component normalisation ---------------------------
 template <typename T, int L>
-TACE_HD inline void sh_eval(const T x, const T y, const T z, T (&Y)[(L + 1) * (L + 1)]) {
+TACE_HD TACE_INLINE void sh_eval(const T x, const T y, const T z, T (&Y)[(L + 1) * (L + 1)]) {
   Y[0] = T(1);
   if (L >= 1) {
     const T c1 = T(1.7320508075688772);
@@ -55,7 +55,7 @@ TACE_HD inline void sh_eval(const T x, const T y, const T z, T (&Y)[(L + 1) * (L
 
 // dn[a] = sum_i dY[i] * dY_i/dn_a  (dY[0] does not contribute)
 template <typename T, int L>
-TACE_HD inline void sh_grad(const T x, const T y, const T z, const T (&dY)[(L + 1) * (L + 1)], T (&dn)[3]) {
+TACE_HD TACE_INLINE void sh_grad(const T x, const T y, const T z, const T (&dY)[(L + 1) * (L + 1)], T (&dn)[3]) {
   T gx = T(0), gy = T(0), gz = T(0);
   if (L >= 1) {
     const T c1 = T(1.7320508075688772);
@@ -85,13 +85,13 @@ TACE_HD inline void sh_grad(const T x, const T y, const T z, const T (&dY)[(L + 
 }
 
 // ---- radial basis -------------------------------------------------------------
-template <typename T> TACE_HD inline T sin_(T x) { return sin(x); }
-template <> TACE_HD inline float sin_<float>(float x) { return sinf(x); }
-template <typename T> TACE_HD inline T cos_(T x) { return cos(x); }
-template <> TACE_HD inline float cos_<float>(float x) { return cosf(x); }
+template <typename T> TACE_HD TACE_INLINE T sin_(T x) { return sin(x); }
+template <> TACE_HD TACE_INLINE float sin_<float>(float x) { return sinf(x); }
+template <typename T> TACE_HD TACE_INLINE T cos_(T x) { return cos(x); }
+template <> TACE_HD TACE_INLINE float cos_<float>(float x) { return cosf(x); }
 
 template <typename T>
-TACE_HD inline T ipow_(T x, int p) {
+TACE_HD TACE_INLINE T ipow_(T x, int p) {
   T r = T(1);
   for (int i = 0; i < p; ++i) r *= x;
   return r;
@@ -109,7 +109,7 @@ struct RadialParams {
 
 // b[n] = pref sin(w_n d) / d * u(d/rc), n = 0..7; if db != nullptr also d b[n] / d d.
 template <typename T>
-TACE_HD inline void radial_eval(const T d, const RadialParams<T>& rp, T (&b)[kNumBessel], T* db) {
+TACE_HD TACE_INLINE void radial_eval(const T d, const RadialParams<T>& rp, T (&b)[kNumBessel], T* db) {
   const T rc = rp.rc;
   const int p = rp.p;
   const T xr = d / rc;
@@ -135,7 +135,7 @@ TACE_HD inline void radial_eval(const T d, const RadialParams<T>& rp, T (&b)[kNu
 // Weights are stored [in][out] with the 1/sqrt(fan_in) and sqrt(2) gains folded in.
 // z3 (pre-activation of the third layer) -> h3 = silu(z3) feeds the last-layer GEMM.
 template <typename T>
-TACE_HD inline void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
+TACE_HD TACE_INLINE void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
                                    const T* __restrict__ A2, T (&h3)[kHidden]) {
   T h1[kHidden], h2[kHidden];
 #pragma unroll
@@ -164,7 +164,7 @@ TACE_HD inline void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict
 // Given dE/dh3, returns dE/db by recomputing the hidden activations.
 // A1t / A2t are the transposed ([out][in]) copies of A1 / A2; A0 is used as stored.
 template <typename T>
-TACE_HD inline void mlp_hidden_bwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
+TACE_HD TACE_INLINE void mlp_hidden_bwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
                                    const T* __restrict__ A2, const T* __restrict__ A1t, const T* __restrict__ A2t,
                                    const T (&dh3)[kHidden], T (&db)[kNumBessel]) {
   T z1[kHidden], h1[kHidden], z2[kHidden], h2[kHidden], t[kHidden];
@@ -205,7 +205,7 @@ TACE_HD inline void mlp_hidden_bwd(const T (&b)[kNumBessel], const T* __restrict
 // Given dE/dd (through the radial basis) and dE/dn (through the angular basis):
 //   dE/dv = dd * v/|v| + dn/d - v (v.dn) / (d^2 |v|).
 template <typename T>
-TACE_HD inline void edge_vector_grad(const T (&v)[3], const T d0, const T d, const T dd, const T (&dn)[3], T (&g)[3]) {
+TACE_HD TACE_INLINE void edge_vector_grad(const T (&v)[3], const T d0, const T d, const T dd, const T (&dn)[3], T (&g)[3]) {
   const T vdn = v[0] * dn[0] + v[1] * dn[1] + v[2] * dn[2];
   const T a = dd / d0 - vdn / (d * d * d0);
   const T inv_d = T(1) / d;

@@ -1,0 +1,420 @@
+"""Drop-in mirror of ``tace.models`` for the energy / force / stress path.
+
+``e3nnTACE`` (alias ``cartTACE``) keeps the reference constructor signature
+(``tace/models/_e3nn/tace.py:29-62``) and parameter names, so a reference ``.pt`` checkpoint's
+``state_dict`` loads unchanged; ``TensorModel`` keeps the reference wrapper contract
+(``tace/models/adapter.py:23-41``): ``forward(data) -> dict`` with ``energy``, ``node_energy``,
+``forces``, ``virials``, ``stress``, ``edge_forces``.  All arithmetic happens in
+``libtace_b200.so`` (hand-written CUDA, forward and backward); PyTorch only owns the device
+buffers and the stream.  There is no autograd and no CPU fallback, and ``forward`` never
+mutates ``data``.
+"""
+
+from __future__ import annotations
+
+import copy
+import ctypes
+import math
+from typing import Any, Dict, List, Optional, Union
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .pack import ModelPlan, pack_weights
+
+# Options of the reference constructor that this path implements; anything else raises.
+_DEFAULTS: Dict[str, Any] = {
+    "mmax": 2, "Lmax": 2, "lmax": 3, "mag_Lmax": 1, "parity": False, "num_channel": 64, "num_layers": 2,
+    "target_property": ["energy", "forces"], "embedding_property": [],
+    "fidelity": {"name": "PBE", "atomic_energy": None},
+    "node_embedding": {"type": "linear"}, "edge_embedding": {"type": "identity"}, "edge_update": {"type": "identity"},
+    "radial_basis": {"bias": False, "r_min": 0.0, "radial_basis": "j0", "num_radial_basis": 8, "distance_transform": None,
+                     "cutoff_fn": "c2poly", "polynomial_cutoff": 5, "trainable": False, "apply_cutoff": True,
+                     "hidden": [64, 64, 64], "use_dydynamic_cutoff": False},
+    "atomic_basis": {"type": "cgtp", "l1l2": None, "scatter_norm": "avg_num_neighbors", "nonlinear": "sigmoid_gate",
+                     "gate_m0": True, "scalar_act": None, "tensor_act": None, "node_wise_hidden": None},
+    "resnet": {"type": "BB", "linear_type": "aware", "use_first_resnet": False},
+    "layer_norm": {"pre_norm_type": None, "final_norm_type": None, "use_first_pre_norm": False},
+    "product_basis": {"type": "cgtp", "l1l2": None, "correlation": 2, "return_components": None, "num_expert": None,
+                      "num_channel_per_expert": None, "use_shared_expert": False, "nonlinear": None, "agnostic": False},
+    "readout_emlp": {"bias": False, "hidden": [16], "use_alllayer": False, "use_uie": False},
+    "scale_shift": {"enable": True, "scale_type": "rms_forces", "shift_type": None, "scale_trainable": False,
+                    "shift_trainable": False, "all_atoms": False},
+    "short_range": {"zbl": {"enable": False}},
+    "long_range": {"les": {"enable": False}},
+    "dropout": {"use_first_dropout": False, "stochastic_depth": 0.0},
+}
+
+_SUPPORTED_TARGETS = {"energy", "forces", "stress", "virials", "edge_forces"}
+
+
+def _merge(default: Dict, user: Dict) -> Dict:
+    """tace/models/_e3nn/default.py:180-212 (recursive_update)."""
+    out = {}
+    for k, dv in default.items():
+        if k not in user:
+            out[k] = copy.deepcopy(dv)
+        elif isinstance(dv, dict) and isinstance(user[k], dict):
+            out[k] = _merge(dv, user[k])
+        else:
+            out[k] = copy.deepcopy(user[k])
+    for k, v in user.items():
+        if k not in out:
+            out[k] = copy.deepcopy(v)
+    return out
+
+
+def _require(cond: bool, what: str) -> None:
+    if not cond:
+        raise NotImplementedError(f"tace_b200 implements the cgtp energy/force path only: {what}")
+
+
+def check_model_config(cfg: Dict) -> Dict:
+    """The part of tace/models/_e3nn/default.py:231-316 this path needs, plus refusal of
+    every option that is not implemented (never silently ignored)."""
+    cfg = _merge(_DEFAULTS, {k: v for k, v in cfg.items() if v is not None or k == "max_neighbors"})
+    if cfg.get("max_neighbors") is not None:
+        raise ValueError("TACE does not truncate neighbor lists. Set `max_neighbors: null` in the model configuration.")
+    stats = cfg.get("statistics")
+    if not isinstance(stats, (list, tuple)) or not stats:
+        raise ValueError("statistics must be a non-empty list of dicts")
+    _require(len(stats) == 1, "one fidelity (multi-head read-outs are not built)")
+    cfg["atomic_numbers"] = sorted({int(z) for s in stats for z in s["atomic_numbers"]})
+    cfg["avg_num_neighbors"] = sum(float(s["avg_num_neighbors"]) for s in stats) / len(stats)
+    cfg["atomic_energies"] = [s["atomic_energy"] for s in stats]
+    _require(cfg["Lmax"] == cfg["lmax"], "Lmax == lmax")
+    _require(1 <= cfg["Lmax"] <= 3, "1 <= Lmax <= 3")
+    _require(not cfg["parity"], "parity=False")
+    _require(cfg["num_channel"] % 32 == 0 and 32 <= cfg["num_channel"] <= 256, "num_channel a multiple of 32, <= 256")
+    _require(1 <= cfg["num_layers"] <= 4, "1..4 layers")
+    _require(set(cfg["target_property"]) <= _SUPPORTED_TARGETS and "energy" in cfg["target_property"],
+             f"target_property within {sorted(_SUPPORTED_TARGETS)} including energy")
+    _require(not cfg["embedding_property"], "no universal embeddings")
+    for section, key, allowed in [
+        ("node_embedding", "type", {"linear"}), ("edge_embedding", "type", {"identity"}), ("edge_update", "type", {"identity"}),
+        ("radial_basis", "radial_basis", {"j0", "bessel"}), ("radial_basis", "cutoff_fn", {"c2poly", "polynomial"}),
+        ("radial_basis", "distance_transform", {None}), ("radial_basis", "apply_cutoff", {True}),
+        ("radial_basis", "bias", {False}), ("radial_basis", "use_dydynamic_cutoff", {False}),
+        ("radial_basis", "num_radial_basis", {8}),
+        ("atomic_basis", "scatter_norm", {"avg_num_neighbors"}), ("atomic_basis", "gate_m0", {True}),
+        ("atomic_basis", "l1l2", {None}), ("atomic_basis", "scalar_act", {None, "sigmoid"}),
+        ("atomic_basis", "tensor_act", {None, "sigmoid"}), ("atomic_basis", "node_wise_hidden", {None}),
+        ("resnet", "type", {"BB"}), ("resnet", "linear_type", {"aware"}), ("resnet", "use_first_resnet", {False}),
+        ("layer_norm", "pre_norm_type", {None}), ("layer_norm", "final_norm_type", {None}),
+        ("product_basis", "l1l2", {None}), ("product_basis", "return_components", {None}),
+        ("product_basis", "num_expert", {None, 1}), ("product_basis", "nonlinear", {None}),
+        ("product_basis", "agnostic", {False}), ("product_basis", "use_shared_expert", {False}),
+        ("readout_emlp", "bias", {False}), ("readout_emlp", "use_alllayer", {False}), ("readout_emlp", "use_uie", {False}),
+        ("scale_shift", "enable", {True}), ("scale_shift", "all_atoms", {False}), ("scale_shift", "shift_type", {None}),
+    ]:
+        _require(cfg[section][key] in allowed, f"{section}.{key} in {allowed}, got {cfg[section][key]!r}")
+    _require(list(cfg["radial_basis"]["hidden"]) == [64, 64, 64], "radial_basis.hidden == [64, 64, 64]")
+    _require(len(cfg["readout_emlp"]["hidden"]) == 1 and cfg["readout_emlp"]["hidden"][0] <= 64, "one read-out hidden layer <= 64")
+    _require(not cfg["short_range"]["zbl"]["enable"], "no ZBL")
+    _require(not cfg["long_range"]["les"]["enable"], "no LES")
+    _require(cfg["dropout"]["stochastic_depth"] == 0.0, "no stochastic depth")
+
+    def to_list(x):
+        return [x] * cfg["num_layers"] if not isinstance(x, list) else x
+
+    for section, key in [("atomic_basis", "type"), ("product_basis", "type"), ("atomic_basis", "nonlinear"),
+                         ("product_basis", "correlation")]:
+        cfg[section][key] = to_list(cfg[section][key])
+    _require(all(t == "cgtp" for t in cfg["atomic_basis"]["type"]), "atomic_basis.type == cgtp")
+    _require(all(t in ("cgtp", "spatial", "coupled") for t in cfg["product_basis"]["type"]), "product_basis.type == cgtp")
+    _require(all(n == "sigmoid_gate" for n in cfg["atomic_basis"]["nonlinear"]), "atomic_basis.nonlinear == sigmoid_gate")
+    corr = cfg["product_basis"]["correlation"]
+    _require(len(set(corr)) == 1 and corr[0] in (1, 2), "product_basis.correlation in {1, 2}, equal on all layers")
+    return cfg
+
+
+def _set_nested(root: torch.nn.Module, dotted: str, tensor: torch.Tensor, buffer: bool) -> None:
+    parts = dotted.split(".")
+    mod = root
+    for p in parts[:-1]:
+        if p not in mod._modules:
+            mod.add_module(p, torch.nn.Module())
+        mod = mod._modules[p]
+    if buffer:
+        mod.register_buffer(parts[-1], tensor)
+    else:
+        mod.register_parameter(parts[-1], torch.nn.Parameter(tensor, requires_grad=False))
+
+
+class e3nnTACE(torch.nn.Module):
+    """Parameter container with the reference constructor and state_dict layout.
+
+    Weights are drawn like the reference's initialisers (unit normal for the equivariant
+    linears, U(-sqrt3, sqrt3) for the radial MLP, zero biases; ``tace/models/linear.py:260-261,
+    331-337, 428-431``) from the global torch generator."""
+
+    def __init__(self, Lmax: int = None, lmax: int = None, num_layers: int = None, num_channel: int = None,
+                 cutoff: float = None, statistics: List[Dict] = None, target_property: List[str] = None,
+                 max_neighbors: Union[int, None] = None, fidelity: Dict = None, node_embedding: Dict = None,
+                 edge_embedding: Dict = None, edge_update: Dict = None, radial_basis: Dict = None, atomic_basis: Dict = None,
+                 product_basis: Dict = None, readout_emlp: Dict = None, scale_shift: Dict = None, short_range: Dict = None,
+                 long_range: Dict = None, universal_embedding: Dict = None, special: Dict = {}, resnet: Dict = {},
+                 layer_norm: Dict = {}, normalizer: Dict = {}, parity: bool = False, mmax: int = 2, mag_Lmax: int = 1,
+                 dropout: Dict = {}, embedding_property=[], atomic_numbers=None, **kwargs):
+        cfg = {k: v for k, v in locals().items() if k not in ("self", "kwargs", "__class__") and not k.startswith("_")}
+        cfg.update(kwargs)
+        self.model_config = copy.deepcopy(cfg)
+        if universal_embedding:
+            _require(not any(v.get("enable") for v in universal_embedding.values()), "no universal embeddings")
+        cfg.pop("universal_embedding", None)
+        for k in ("special", "resnet", "layer_norm", "normalizer", "dropout"):
+            if not cfg.get(k):
+                cfg.pop(k, None)
+        if cutoff is None:
+            raise ValueError("cutoff is required")
+        cfg = check_model_config(cfg)
+        super().__init__()
+        self.cfg = cfg
+        self.fidelity = [cfg["fidelity"]] if isinstance(cfg["fidelity"], dict) else cfg["fidelity"]
+        self.num_fidelities = 1
+        self.max_neighbors = None
+        self.target_property = list(cfg["target_property"])
+        self.num_layers = cfg["num_layers"]
+        self.statistics = cfg["statistics"]
+        self.embedding_property = []
+        self.num_elements = len(cfg["atomic_numbers"])
+        self.num_channel = cfg["num_channel"]
+        dt = torch.get_default_dtype()
+        rc = float(cfg["cutoff"])
+        nb = cfg["radial_basis"]["num_radial_basis"]
+        self.plan = ModelPlan(cfg["Lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
+                              cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64)
+        self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
+        self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
+        for name, shape in self.plan.parameter_shapes().items():
+            if name.endswith(".bias"):
+                value = torch.zeros(shape, dtype=dt)
+            elif ".edge_info.mlp." in name:
+                value = torch.empty(shape, dtype=dt).uniform_(-math.sqrt(3.0), math.sqrt(3.0))
+            else:
+                value = torch.randn(shape, dtype=dt)
+            _set_nested(self, name, value, buffer=False)
+        rb = "representation.radial_basis."
+        _set_nested(self, "representation.atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64), True)
+        _set_nested(self, rb + "radial_fn.bessel_weights", math.pi / rc * torch.linspace(1.0, nb, nb, dtype=dt), True)
+        _set_nested(self, rb + "radial_fn.cutoff", torch.tensor(rc, dtype=dt), True)
+        _set_nested(self, rb + "radial_fn.prefactor", torch.tensor(math.sqrt(2.0 / rc), dtype=dt), True)
+        _set_nested(self, rb + "cutoff_fn.p", torch.tensor(cfg["radial_basis"]["polynomial_cutoff"], dtype=torch.int), True)
+        _set_nested(self, rb + "cutoff_fn.cutoff", torch.tensor(rc, dtype=dt), True)
+        zs = cfg["atomic_numbers"]
+        ae = [{int(k): float(v) for k, v in d.items()} for d in cfg["atomic_energies"]]
+        _set_nested(self, "atomic_energy_layer.atomic_energy",
+                    torch.tensor([[d.get(int(z), 0.0) for z in zs] for d in ae], dtype=dt), True)
+        sk = cfg["scale_shift"]["scale_type"]
+        scale = [[float({int(k): float(v) for k, v in (s[sk] if sk else {}).items()}.get(int(z), 1.0)) for z in zs]
+                 for s in cfg["statistics"]]
+        _set_nested(self, "scale_shift.scale", torch.tensor(scale, dtype=dt), True)
+        _set_nested(self, "scale_shift.shift", torch.zeros(len(scale), len(zs), dtype=dt), True)
+        _set_nested(self, "scale_shift.atomic_numbers", torch.tensor(zs, dtype=torch.int64), True)
+
+    def forward(self, data, graph=None):
+        raise RuntimeError("call the TensorModel wrapper; the model body runs inside libtace_b200.so")
+
+
+cartTACE = e3nnTACE  # the reference exports the same architecture under both names (tace/models/__init__.py:4-7)
+
+
+class _Flags:
+    pass
+
+
+class TensorModel(torch.nn.Module):
+    """``TensorModel(readout_fn)`` with the reference's ``forward(data)`` contract."""
+
+    def __init__(self, readout_fn: e3nnTACE):
+        super().__init__()
+        self.readout_fn = readout_fn
+        self.num_fidelities = 1
+        self.lmp = False
+        self.fidelity_idx = 0
+        self._handle = None
+        self._handle_key = None
+        self._workspace = None
+        self._set_target_property()
+
+    # ---- reference getters (tace/models/adapter.py:386-452) ----------------------------------
+    def get_fidelity_idx(self) -> int:
+        return int(self.fidelity_idx)
+
+    def reset_fidelity_idx(self, fidelity_idx: Union[int, None] = 0) -> None:
+        if fidelity_idx not in (None, 0):
+            raise NotImplementedError("single-fidelity models only")
+
+    def get_embedding_property(self) -> List[str]:
+        return []
+
+    def get_target_property(self) -> List[str]:
+        return list(set(self.readout_fn.target_property))
+
+    def reset_target_property(self, target_property: List[str]) -> None:
+        assert isinstance(target_property, list)
+        _require(set(target_property) <= _SUPPORTED_TARGETS, f"targets within {sorted(_SUPPORTED_TARGETS)}")
+        self.readout_fn.target_property = target_property
+        self._set_target_property()
+
+    def _set_target_property(self) -> None:
+        self.flags = _Flags()
+        for k in _SUPPORTED_TARGETS:
+            setattr(self.flags, f"compute_{k}", k in self.get_target_property())
+
+    def _set_lammps_mliap(self, enable: bool = False) -> None:
+        self.lmp = enable
+
+    def get_model_dtype(self) -> torch.dtype:
+        return self.readout_fn.cutoff.dtype
+
+    def get_max_neighbors(self):
+        return None
+
+    def get_cutoff(self) -> float:
+        return float(self.readout_fn.cutoff.item())
+
+    def get_atomic_numbers(self) -> List[int]:
+        return [int(z) for z in self.readout_fn.atomic_numbers.cpu().tolist()]
+
+    # ---- native model handle ----------------------------------------------------------------------
+    def _native(self, device: torch.device):
+        rf = self.readout_fn
+        dtype = self.get_model_dtype()
+        key = (device.index, dtype, sum(int(p._version) for p in rf.state_dict().values()))
+        if self._handle is not None and key == self._handle_key:
+            return self._handle
+        self.release()
+        lib = _lib.load()
+        plan = rf.plan
+        cfg = _lib.TaceConfig(
+            dtype=_lib.TACE_F64 if dtype == torch.float64 else _lib.TACE_F32, L=plan.L, num_layers=plan.num_layers,
+            num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
+            mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
+            cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]))
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")
+            packed = pack_weights(plan, rf.state_dict(), float(rf.cfg["avg_num_neighbors"]))
+            npdt = np.float64 if dtype == torch.float64 else np.float32
+            name, numel = ctypes.c_char_p(), ctypes.c_int64()
+            for i in range(lib.tace_weight_count(handle)):
+                _lib.check(lib.tace_weight_info(handle, i, ctypes.byref(name), ctypes.byref(numel)), "tace_weight_info")
+                arr = np.ascontiguousarray(packed[name.value.decode()], dtype=npdt).reshape(-1)
+                if arr.size != numel.value:
+                    raise _lib.TaceError(f"weight {name.value.decode()}: packed {arr.size} elements, library expects {numel.value}")
+                _lib.check(lib.tace_set_weight(handle, name.value, arr.ctypes.data_as(ctypes.c_void_p), arr.size), "tace_set_weight")
+        self._handle, self._handle_key = handle, key
+        return handle
+
+    def release(self) -> None:
+        if self._handle is not None:
+            _lib.load().tace_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+    def __getstate__(self):
+        state = self.__dict__.copy()
+        state["_handle"], state["_handle_key"], state["_workspace"] = None, None, None
+        return state
+
+    def _get_workspace(self, nbytes: int, device: torch.device) -> torch.Tensor:
+        ws = self._workspace
+        if ws is None or ws.numel() < nbytes or ws.device != device:
+            self._workspace = None
+            ws = torch.empty(int(nbytes * 1.1) + 4096, dtype=torch.uint8, device=device)
+            self._workspace = ws
+        return ws
+
+    # ---- forward -------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, data: Dict[str, torch.Tensor]) -> Dict[str, Optional[torch.Tensor]]:
+        lib = _lib.load()
+        dtype = self.get_model_dtype()
+        node_attrs = data["node_attrs"]
+        device = node_attrs.device
+        if device.type != "cuda":
+            raise _lib.TaceError("tace_b200 runs on CUDA devices only (no CPU path)")
+        handle = self._native(device)
+        flags = self.flags
+        species = data["species"] if "species" in data else node_attrs.argmax(dim=-1)
+        species = species.to(torch.int32).contiguous()
+        edge_index = data["edge_index"].to(torch.int64).contiguous()
+        E = int(edge_index.shape[1])
+        keep = [species, edge_index]
+
+        def real(x):
+            x = x.detach().to(dtype).contiguous()
+            keep.append(x)
+            return x
+
+        batch = _lib.TaceBatch()
+        if self.lmp:
+            nlocal, nghost = int(data["natoms"][0]), int(data["natoms"][1])
+            n_atoms, n_local, n_graphs = nlocal + nghost, nlocal, 1
+            graph_ptr = torch.tensor([0, nlocal], dtype=torch.int32, device=device)
+            batch.edge_vector = real(data["edge_vector"]).data_ptr()
+        else:
+            n_atoms = n_local = int(node_attrs.shape[0])
+            graph_ptr = data["ptr"].to(torch.int32).contiguous()
+            n_graphs = int(graph_ptr.numel() - 1)
+            batch.positions = real(data["positions"]).data_ptr()
+            batch.lattice = real(data["lattice"]).reshape(-1, 3, 3).data_ptr()
+            batch.edge_shifts = real(data["edge_shifts"]).data_ptr()
+        keep.append(graph_ptr)
+        batch.n_atoms, batch.n_local, batch.n_edges, batch.n_graphs = n_atoms, n_local, E, n_graphs
+        batch.species, batch.graph_ptr, batch.edge_index = species.data_ptr(), graph_ptr.data_ptr(), edge_index.data_ptr()
+
+        out = _lib.TaceOutputs()
+        res: Dict[str, Optional[torch.Tensor]] = {k: None for k in
+                                                   ("energy", "node_energy", "forces", "virials", "stress", "edge_forces")}
+        res["energy"] = torch.empty(n_graphs, dtype=dtype, device=device)
+        res["node_energy"] = torch.empty(n_local, dtype=dtype, device=device)
+        out.energy, out.node_energy = res["energy"].data_ptr(), res["node_energy"].data_ptr()
+        if flags.compute_forces and not self.lmp:
+            res["forces"] = torch.empty(n_atoms, 3, dtype=dtype, device=device)
+            out.forces = res["forces"].data_ptr()
+        if (flags.compute_stress or flags.compute_virials) and not self.lmp:
+            res["virials"] = torch.empty(n_graphs, 3, 3, dtype=dtype, device=device)
+            res["stress"] = torch.empty(n_graphs, 3, 3, dtype=dtype, device=device)
+            out.virials, out.stress = res["virials"].data_ptr(), res["stress"].data_ptr()
+        if flags.compute_edge_forces or self.lmp:
+            res["edge_forces"] = torch.empty(E, 3, dtype=dtype, device=device)
+            out.edge_forces = res["edge_forces"].data_ptr()
+
+        with torch.cuda.device(device):
+            nbytes = ctypes.c_size_t()
+            _lib.check(lib.tace_workspace_bytes(handle, n_atoms, n_local, E, n_graphs, ctypes.byref(nbytes)), "tace_workspace_bytes")
+            ws = self._get_workspace(nbytes.value, device)
+            ws_ptr = (ws.data_ptr() + 255) & ~255
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _lib.check(lib.tace_forward(handle, ctypes.byref(batch), ctypes.byref(out), ws_ptr,
+                                        ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
+        return res
+
+    def debug_read(self, name: str, numel: int) -> torch.Tensor:
+        """Copy a named intermediate of the last forward call (parity tests)."""
+        lib = _lib.load()
+        device = self._workspace.device
+        buf = torch.empty(numel, dtype=self.get_model_dtype(), device=device)
+        n = lib.tace_debug_read(self._handle, name.encode(), buf.data_ptr(), numel, torch.cuda.current_stream(device).cuda_stream)
+        if n < 0:
+            raise _lib.TaceError(f"tace_debug_read({name}): status {n}")
+        return buf[:n]
+
+
+def create_model(model_config: Dict, statistics=None, target_property=None, **_) -> TensorModel:
+    """``TensorModel(e3nnTACE(**model_config))`` as tace/lightning/torch_model.py:54-114 builds it."""
+    cfg = dict(model_config)
+    cfg.pop("_target_", None)
+    if statistics is not None:
+        cfg["statistics"] = statistics
+    if target_property is not None:
+        cfg["target_property"] = target_property
+    return TensorModel(e3nnTACE(**cfg))

@@ -1,0 +1,154 @@
+"""Model plan (path bookkeeping) and repacking of reference-named parameters into the
+arrays ``libtace_b200.so`` consumes.
+
+Parameter names, flat-weight order and normalisation constants follow the reference
+(paths relative to its project root):
+
+* flat linear weights = concatenation, in (input block, output block) order, of
+  ``[mul_in, mul_out]`` matrices, each used with the factor 1/sqrt(fan_in)
+  (``tace/models/linear.py:282-374`` over e3nn ``o3.Linear``);
+* tensor-product paths are enumerated output-rank major, then first input, then second
+  (``tace/models/_e3nn/paths.py:30-71``); the radial MLP emits one weight per (path, channel),
+  path major (``tace/models/_e3nn/inter.py:92-99,180``);
+* radial MLP layers carry 1/sqrt(fan_in) and, after the first, a sqrt(2) gain
+  (``tace/models/mlp.py:155-170``);
+* messages are divided by ``avg_num_neighbors`` after ``linear_down``
+  (``tace/models/_e3nn/base.py:240-249``), folded into that layer's weights here.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List
+
+import numpy as np
+
+
+def tp_paths(in1_ls, in2_ls, out_ls):
+    return [(l1, l2, l3) for l3 in out_ls for l1 in in1_ls for l2 in in2_ls
+            if abs(l1 - l2) <= l3 <= l1 + l2 and (l1 + l2 + l3) % 2 == 0]
+
+
+class LayerPlan:
+    def __init__(self, t: int, num_layers: int, L: int):
+        self.t = t
+        self.scalar_src = t == 0
+        self.last = t == num_layers - 1
+        self.has_res = t > 0
+        all_ls = list(range(L + 1))
+        self.in_ls = [0] if self.scalar_src else all_ls
+        self.out_ls = [0] if self.last else all_ls
+        self.tp_paths = tp_paths(self.in_ls, all_ls, all_ls)
+        self.k = [sum(1 for p in self.tp_paths if p[2] == l) for l in all_ls]
+        self.pb_paths = tp_paths(all_ls, all_ls, self.out_ls)
+        self.kp = [sum(1 for p in self.pb_paths if p[2] == l) for l in self.out_ls]
+
+
+class ModelPlan:
+    def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
+                 readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64):
+        self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
+        self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
+        self.layers = [LayerPlan(t, num_layers, L) for t in range(num_layers)]
+
+    def parameter_shapes(self) -> Dict[str, tuple]:
+        """Reference parameter names (without the ``readout_fn.`` prefix) and shapes."""
+        C, n_el, L = self.C, self.n_el, self.L
+        out = {"representation.node_embedding.elem_emb1.weight": (n_el * C,)}
+        for lp in self.layers:
+            pre = f"representation.interactions.{lp.t}."
+            out[pre + "linear_up.weight"] = (len(lp.in_ls) * C * C,)
+            out[pre + "linear_up.bias"] = (C,)
+            dims = [self.num_bessel] + [self.mlp_hidden] * 3 + [len(lp.tp_paths) * C]
+            for i, (a, b) in enumerate(zip(dims, dims[1:])):
+                out[pre + f"edge_info.mlp.{2 * i}.weight"] = (a, b)
+            out[pre + "linear_down.weight"] = (sum(lp.k[l] * C * ((L + 2) * C if l == 0 else C) for l in range(L + 1)),)
+            out[pre + "linear_down.bias"] = ((L + 2) * C,)
+            out[pre + "linear_nonlinearity.weight"] = ((L + 1) * C * C,)
+            out[pre + "linear_nonlinearity.bias"] = (C,)
+            if lp.has_res:
+                out[pre + "resnetBB.weight"] = (n_el, len(lp.out_ls) * C * C)
+                out[pre + "resnetBB.bias"] = (n_el, C)
+            pp = f"representation.products.{lp.t}."
+            out[pp + "coefs.0.weight"] = (n_el, len(lp.out_ls) * C * C)
+            out[pp + "coefs.0.bias"] = (n_el, C)
+            if self.correlation >= 2:
+                out[pp + "coefs.1.weight"] = (n_el, sum(kp * C * C for kp in lp.kp))
+                out[pp + "coefs.1.bias"] = (n_el, C)
+            out[pp + "linear.weight"] = (len(lp.out_ls) * C * C,)
+            out[pp + "linear.bias"] = (C,)
+        out["energy_readouts.0.linear2.0.weight"] = (C * self.H,)
+        out["energy_readouts.0.linear2.1.weight"] = (self.H,)
+        return out
+
+
+def _np(t) -> np.ndarray:
+    return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
+
+
+def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: float, prefix: str = "") -> Dict[str, np.ndarray]:
+    """fp64 arrays keyed by the names ``tace_weight_info`` reports."""
+    C, n_el, L = plan.C, plan.n_el, plan.L
+    g = lambda k: _np(sd[prefix + k])
+    out: Dict[str, np.ndarray] = {}
+    out["emb"] = g("representation.node_embedding.elem_emb1.weight").reshape(n_el, C) / math.sqrt(n_el)
+    out["bessel"] = g("representation.radial_basis.radial_fn.bessel_weights").reshape(-1)
+    out["bessel_pref"] = g("representation.radial_basis.radial_fn.prefactor").reshape(1)
+
+    def split(flat: np.ndarray, shapes: List[tuple]) -> List[np.ndarray]:
+        res, off = [], 0
+        for shp in shapes:
+            n = int(np.prod(shp))
+            res.append(flat[..., off:off + n].reshape(flat.shape[:-1] + shp))
+            off += n
+        assert off == flat.shape[-1], (off, flat.shape)
+        return res
+
+    def put(name: str, mat: np.ndarray, transposed_name: str = None):
+        out[name] = np.ascontiguousarray(mat)
+        if transposed_name:
+            out[transposed_name] = np.ascontiguousarray(np.swapaxes(mat, -1, -2))
+
+    for lp in plan.layers:
+        t = lp.t
+        pre = f"representation.interactions.{t}."
+        pp = f"representation.products.{t}."
+        tp = f"t{t}."
+        for l, m in zip(lp.in_ls, split(g(pre + "linear_up.weight"), [(C, C)] * len(lp.in_ls))):
+            put(tp + f"up.l{l}", m / math.sqrt(C), tp + f"upT.l{l}")
+        out[tp + "up.b"] = g(pre + "linear_up.bias")
+        nb, hd = plan.num_bessel, plan.mlp_hidden
+        out[tp + "A0"] = g(pre + "edge_info.mlp.0.weight") / math.sqrt(nb)
+        put(tp + "A1", g(pre + "edge_info.mlp.2.weight") * math.sqrt(2.0 / hd), tp + "A1t")
+        put(tp + "A2", g(pre + "edge_info.mlp.4.weight") * math.sqrt(2.0 / hd), tp + "A2t")
+        put(tp + "W3", g(pre + "edge_info.mlp.6.weight") * math.sqrt(2.0 / hd), tp + "W3t")
+        down_shapes = [(lp.k[l] * C, (L + 2) * C if l == 0 else C) for l in range(L + 1)]
+        for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
+            put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
+        out[tp + "down.b"] = g(pre + "linear_down.bias") / avg_num_neighbors
+        for l, m in enumerate(split(g(pre + "linear_nonlinearity.weight"), [(C, C)] * (L + 1))):
+            put(tp + f"nl.l{l}", m / math.sqrt(C), tp + f"nlT.l{l}")
+        out[tp + "nl.b"] = g(pre + "linear_nonlinearity.bias")
+        for l, m in zip(lp.out_ls, split(g(pp + "coefs.0.weight"), [(C, C)] * len(lp.out_ls))):
+            put(tp + f"c0.l{l}", m / math.sqrt(C), tp + f"c0T.l{l}")
+        bias = g(pp + "coefs.0.bias").copy()
+        if plan.correlation >= 2:
+            for l, kp, m in zip(lp.out_ls, lp.kp, split(g(pp + "coefs.1.weight"), [(kp * C, C) for kp in lp.kp])):
+                put(tp + f"c1.l{l}", m / math.sqrt(kp * C), tp + f"c1T.l{l}")
+            bias = bias + g(pp + "coefs.1.bias")
+        out[tp + "c.b"] = bias
+        for l, m in zip(lp.out_ls, split(g(pp + "linear.weight"), [(C, C)] * len(lp.out_ls))):
+            put(tp + f"lin.l{l}", m / math.sqrt(C), tp + f"linT.l{l}")
+        out[tp + "lin.b"] = g(pp + "linear.bias")
+        if lp.has_res:
+            for l, m in zip(lp.out_ls, split(g(pre + "resnetBB.weight"), [(C, C)] * len(lp.out_ls))):
+                put(tp + f"res.l{l}", m / math.sqrt(C), tp + f"resT.l{l}")
+            out[tp + "res.b"] = g(pre + "resnetBB.bias")
+    out["ro.W1"] = g("energy_readouts.0.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
+    out["ro.W2"] = g("energy_readouts.0.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
+    out["scale"] = g("scale_shift.scale")[0]
+    out["e0"] = g("atomic_energy_layer.atomic_energy")[0]
+    shift = g("scale_shift.shift")
+    if np.any(shift != 0.0):
+        raise NotImplementedError("a non-zero energy shift (scale_shift.shift_type) is not supported")
+    return out

@@ -1,0 +1,74 @@
+"""Shared helpers of the parity tests: build matching CUDA / oracle models and inputs."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import tace_b200
+from tace_b200 import synth
+
+
+def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
+                targets=("energy", "forces", "stress")):
+    """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
+    from oracle.model import build_oracle
+
+    cfg = synth.model_config(L, C, cutoff, elements, avg, num_layers=num_layers, correlation=correlation,
+                             target_property=targets)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        torch.manual_seed(seed)
+        model = tace_b200.TensorModel(tace_b200.e3nnTACE(**cfg))
+        # non-zero biases and species-dependent scale / E0 so every term is exercised
+        g = torch.Generator().manual_seed(seed + 1)
+        sd = model.state_dict()
+        for k, v in sd.items():
+            if k.endswith(".bias"):
+                v.copy_(0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
+        sd["readout_fn.scale_shift.scale"].copy_(0.5 + torch.rand(sd["readout_fn.scale_shift.scale"].shape, generator=g, dtype=dtype))
+        sd["readout_fn.atomic_energy_layer.atomic_energy"].copy_(
+            torch.randn(sd["readout_fn.atomic_energy_layer.atomic_energy"].shape, generator=g, dtype=dtype))
+    finally:
+        torch.set_default_dtype(prev)
+    oracle = build_oracle(cfg, model.state_dict(), dtype)
+    return model, oracle, cfg
+
+
+def oracle_batch(structures, elements, cutoff, dtype):
+    """Input dictionary for the oracle with the brute-force neighbour list (CPU tensors)."""
+    from oracle.neighbour_list import neighbour_list
+
+    b = synth.collate(structures)
+    eis, ess = [], []
+    for s, off in zip(structures, b["ptr"][:-1]):
+        ei, es = neighbour_list(s["positions"], s["cell"], s["pbc"], cutoff)
+        eis.append(ei + off)
+        ess.append(es)
+    zs = sorted(elements)
+    idx = np.array([zs.index(int(z)) for z in b["atomic_numbers"]])
+    return {
+        "positions": torch.tensor(b["positions"], dtype=dtype),
+        "lattice": torch.tensor(b["lattice"], dtype=dtype),
+        "node_attrs": torch.nn.functional.one_hot(torch.tensor(idx), len(zs)).to(dtype),
+        "edge_index": torch.tensor(np.concatenate(eis, axis=1), dtype=torch.int64),
+        "edge_shifts": torch.tensor(np.concatenate(ess, axis=0), dtype=dtype),
+        "batch": torch.tensor(b["batch"]),
+        "ptr": torch.tensor(b["ptr"]),
+    }
+
+
+def to_device(data, device):
+    return {k: v.to(device) for k, v in data.items()}
+
+
+def feats_to_oracle_layout(x: torch.Tensor, ls, C: int) -> torch.Tensor:
+    """[n][component][channel] (rank blocks in `ls`) -> e3nn mul_ir [n][sum_l C*(2l+1)]."""
+    n = x.shape[0]
+    x = x.reshape(n, -1, C)
+    out, off = [], 0
+    for l in ls:
+        blk = x[:, off:off + 2 * l + 1, :]  # [n, m, c]
+        out.append(blk.permute(0, 2, 1).reshape(n, -1))
+        off += 2 * l + 1
+    return torch.cat(out, dim=1)
