@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the TACE energy + force + stress path on B200.
+
+One "step" = one evaluation of energy, conservative forces and stress for the whole batch of the
+workload (BASELINE config 2: 64 random periodic crystals, fp32, L = 3, 128 channels, 89 elements).
+With N GPUs every rank evaluates its own batch of 64 crystals (weak scaling, no collective on the
+data path).  `value` is timed with the batch and its neighbour list resident in HBM; `e2e` goes
+through the public API from pinned host buffers (upload, GPU neighbour list, evaluation,
+download of energy / forces / stress).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload NAME]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np
+import torch
+
+METRIC = "atom-steps/s (E+F)"
+UNIT = "atom-steps/s"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def build_model(wl: dict, dtype):
+    import tace_b200
+    from tace_b200 import synth
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"])
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        torch.manual_seed(0)
+        model = tace_b200.TensorModel(tace_b200.e3nnTACE(**cfg))
+    finally:
+        torch.set_default_dtype(prev)
+    return model, cfg
+
+
+def algorithmic_bytes(phase: str, dims: dict):
+    """Bytes the phase's kernel must move if every per-edge tensor is recomputed on chip: one gather of
+    the source features per edge, one pass over the per-atom messages (or their gradient), the edge list."""
+    s, E, N, C = dims["s"], dims["E"], dims["N"], dims["C"]
+    layer = int(phase[1]) if phase.startswith("t") and phase[1].isdigit() else 0
+    NX = 1 if layer == 0 else dims["D"]
+    NM = dims["NM"][layer]
+    if ".tp" in phase:
+        return s * (E * NX * C + N * NM * C) + 4 * E
+    return None
+
+
+def gemm_flops(phase: str, dims: dict):
+    layer = int(phase[1])
+    return 2.0 * dims["E"] * 64 * dims["NP"][layer] * dims["C"]
+
+
+def cpu_sample(structures, wl, dtype, state_dict, budget_s: float, evals: int):
+    """Times the CPU oracle (PyTorch, autograd forces, all host threads) on as many crystals of the
+    workload as fit the time budget.  Returns (atom-steps/s, description, cores)."""
+    from helpers import oracle_batch
+    from oracle.model import build_oracle
+    from tace_b200 import synth
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"])
+    oracle = build_oracle(cfg, state_dict, dtype)
+    order = sorted(range(len(structures)), key=lambda i: len(structures[i]["positions"]))
+    probe = [structures[order[0]]]
+    data = oracle_batch(probe, wl["elements"], wl["cutoff"], dtype)
+    t0 = time.perf_counter(); oracle(data); t1 = time.perf_counter()
+    per_edge = (t1 - t0) / max(1, data["edge_index"].shape[1])
+    # choose crystals (smallest first) so that `evals` evaluations fit the budget
+    chosen, edges = [], 0
+    for i in order:
+        est = len(structures[i]["positions"]) * wl["avg_num_neighbors"]
+        if chosen and (edges + est) * per_edge * evals > budget_s:
+            break
+        chosen.append(structures[i]); edges += est
+    data = oracle_batch(chosen, wl["elements"], wl["cutoff"], dtype)
+    n_atoms = data["positions"].shape[0]
+    return oracle, data, n_atoms, len(chosen), cores
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the CPU restatement of the reference path (the reference itself needs e3nn /
+    matscipy / ase, which cannot be installed offline), all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    from tace_b200 import synth
+    wl = synth.WORKLOADS[args.workload]
+    dtype = torch.float64 if wl["dtype"] == "float64" else torch.float32
+    structures = synth.workload_structures(args.workload)
+    model, cfg = build_model(wl, dtype)
+    oracle, data, n_atoms, n_struct, cores = cpu_sample(structures, wl, dtype, model.state_dict(), 90.0, args.steps + args.warmup)
+    for _ in range(args.warmup):
+        oracle(data)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle(data)
+    dt = time.perf_counter() - t0
+    value = n_atoms * args.steps / dt
+    sample = f"{n_struct} smallest crystals of the batch ({n_atoms} atoms, {data['edge_index'].shape[1]} edges) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
+        "config": {"workload": args.workload, "L": wl["L"], "channels": wl["channels"], "cutoff": wl["cutoff"],
+                   "elements": len(wl["elements"]), "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="crystals64_fp32")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: tace_b200 has no CPU path")
+    rank, world, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+
+    from tace_b200 import synth
+    from tace_b200.graph import build_batch, z_to_index
+    wl = synth.WORKLOADS[args.workload]
+    dtype = torch.float64 if wl["dtype"] == "float64" else torch.float32
+    if args.workload == "crystals64_fp32":
+        structures = synth.random_crystals(64, seed=1 + rank)  # every rank its own batch (weak scaling)
+    else:
+        structures = synth.workload_structures(args.workload)
+    model, cfg = build_model(wl, dtype)
+    host = synth.collate(structures)
+    host["species"] = z_to_index(host["atomic_numbers"], wl["elements"])
+    pinned = {k: torch.as_tensor(v).pin_memory() for k, v in host.items()}
+    n_atoms = int(host["positions"].shape[0])
+
+    data = build_batch(pinned, wl["elements"], wl["cutoff"], dtype, device)
+    n_edges = int(data["edge_index"].shape[1])
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
+
+    for _ in range(args.warmup):
+        out = model(data)
+    torch.cuda.synchronize()
+    launches0 = model.launch_count()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier(world)
+    for k in range(args.steps):
+        flush.fill_(k & 0xFF)  # evict L2 between timed steps (outside the per-step event pair)
+        starts[k].record()
+        out = model(data)
+        stops[k].record()
+    barrier(world)
+    step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    total_ms = max_over_ranks(sum(step_ms), world, device)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = model.launch_count() - launches0
+    total_atoms = sum_over_ranks(float(n_atoms), world, device)
+    value = total_atoms * args.steps / (total_ms * 1e-3)
+
+    # per-phase device times (separate, untimed passes with event recording switched on)
+    model.enable_profile(True)
+    phases = {}
+    reps = 3
+    for _ in range(reps):
+        flush.fill_(1)
+        model(data)
+        for name, ms in model.read_profile().items():
+            phases[name] = phases.get(name, 0.0) + ms / reps
+    model.enable_profile(False)
+
+    # end to end through the public API: pinned host buffers -> upload -> neighbour list -> evaluation -> download
+    def e2e_step():
+        d = build_batch(pinned, wl["elements"], wl["cutoff"], dtype, device)
+        o = model(d)
+        return o["energy"].cpu(), o["forces"].cpu(), o["stress"].cpu()
+
+    for _ in range(args.warmup):
+        res = e2e_step()
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        res = e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
+    barrier(world)
+    h2d = sum(int(pinned[k].numel() * pinned[k].element_size()) for k in ("positions", "lattice", "pbc", "ptr", "species", "batch"))
+    d2h = sum(int(t.numel() * t.element_size()) for t in res)
+    e2e_value = total_atoms * args.steps / e2e_s
+
+    if rank != 0:
+        return
+
+    pk = peaks()
+    plan = model.readout_fn.plan
+    L, C = plan.L, plan.C
+    dims = {"s": 4 if dtype == torch.float32 else 8, "E": n_edges, "N": n_atoms, "C": C, "D": (L + 1) ** 2,
+            "NM": [sum((2 * l + 1) * lp.k[l] for l in range(L + 1)) for lp in plan.layers],
+            "NP": [len(lp.tp_paths) for lp in plan.layers]}
+    kernel_phases = {k: v for k, v in phases.items() if k not in ("end",)}
+    top = max(kernel_phases, key=kernel_phases.get)
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as fh:
+            traffic = json.load(fh).get(f"{args.workload}:{top}")
+    ab = algorithmic_bytes(top, dims)
+    if ab is not None:
+        achieved = ab / (phases[top] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": ab, "ms_per_launch": phases[top]}
+    else:
+        fl = gemm_flops(top, dims)
+        achieved = fl / (phases[top] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16_tflops"], "traffic": traffic, "peak_source": pk["source"],
+                    "flops_per_launch": fl, "ms_per_launch": phases[top]}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        oracle, cdata, c_atoms, c_struct, cores = cpu_sample(structures, wl, dtype, model.state_dict(), 20.0, 3)
+        oracle(cdata)
+        t0 = time.perf_counter()
+        for _ in range(2):
+            oracle(cdata)
+        dt = (time.perf_counter() - t0) / 2
+        cpu = {"value": c_atoms / dt, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{c_struct} smallest crystals of the batch ({c_atoms} atoms, {cdata['edge_index'].shape[1]} edges), "
+                         f"2 timed evaluations of the PyTorch CPU restatement with autograd forces"}
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
+        "config": {"workload": args.workload, "L": L, "channels": C, "cutoff": wl["cutoff"], "elements": len(wl["elements"]),
+                   "atoms_per_gpu": n_atoms, "edges_per_gpu": n_edges, "graphs_per_gpu": len(structures),
+                   "parallelism": f"dp{world} (independent batches, no data-path collective)",
+                   "l2": "flushed between timed steps (256 MiB write outside the per-step CUDA-event pair)"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
+    }))
+
+
+if __name__ == "__main__":
+    main()

@@ -119,6 +119,16 @@ int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_loca
 int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace,
                  size_t workspace_bytes, tace_stream_t stream);
 
+/* Instrumentation (no counterpart in the reference, which has no tracing on this path):
+ * tace_launch_count returns the number of this library's kernels enqueued by tace_forward so far
+ * (CUB radix-sort launches are not counted).  With profiling enabled, tace_forward records a
+ * CUDA event on its stream at every phase boundary; tace_profile_read synchronises on the events
+ * of phase `index` of the last call and returns its name and device time in milliseconds. */
+int64_t tace_launch_count(const TaceModel* model);
+int tace_profile_enable(TaceModel* model, int enable);
+int tace_profile_count(const TaceModel* model);
+int tace_profile_read(TaceModel* model, int index, const char** name, float* ms);
+
 /* Debug taps used by the parity tests: copies a named intermediate of the last tace_forward
  * call ("M0", "A0", "h1", ...) into `dst` (device, model dtype, at most `numel` elements).
  * Returns the number of elements copied or a negative status. */

@@ -92,6 +92,37 @@ struct ModelBase {
   virtual int workspace_bytes(int64_t n_atoms, int64_t n_local, int64_t n_edges, int32_t n_graphs, size_t* bytes) = 0;
   virtual int forward(const TaceBatch* b, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) = 0;
   virtual int64_t debug_read(const char* name, void* dst, int64_t numel, cudaStream_t s) = 0;
+
+  // kernel-launch counter and optional per-phase CUDA-event timing
+  long long launches = 0;
+  bool profile = false;
+  std::vector<std::string> phase_names;
+  std::vector<cudaEvent_t> phase_events;
+  size_t phase_used = 0;
+  void phase(const char* name, cudaStream_t s) {
+    if (!profile) return;
+    if (phase_used == phase_events.size()) {
+      cudaEvent_t e;
+      if (cudaEventCreate(&e) != cudaSuccess) return;
+      phase_events.push_back(e);
+      phase_names.push_back("");
+    }
+    phase_names[phase_used] = name;
+    cudaEventRecord(phase_events[phase_used], s);
+    ++phase_used;
+  }
+  int phase_count() const { return phase_used > 0 ? (int)phase_used - 1 : 0; }
+  int phase_read(int i, const char** name, float* ms) {
+    if (i < 0 || i >= phase_count()) return TACE_ERR_INVALID_ARGUMENT;
+    if (cudaEventSynchronize(phase_events[i + 1]) != cudaSuccess) return TACE_ERR_CUDA;
+    if (cudaEventElapsedTime(ms, phase_events[i], phase_events[i + 1]) != cudaSuccess) return TACE_ERR_CUDA;
+    *name = phase_names[i].c_str();
+    return TACE_OK;
+  }
+  void release_events() {
+    for (auto e : phase_events) cudaEventDestroy(e);
+    phase_events.clear();
+  }
 };
 
 template <typename T>
@@ -107,6 +138,7 @@ struct Model : ModelBase {
 
   ~Model() override {
     if (arena) cudaFree(arena);
+    release_events();
   }
 
   void add_weight(const std::string& name, long long numel) {
@@ -301,6 +333,9 @@ struct Model : ModelBase {
     }                                                                                            \
   } while (0)
 
+#define CKL(expr) do { CK(expr); ++launches; } while (0)
+#define PH(name) phase(name, s)
+
   int forward(const TaceBatch* bt, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) override {
     if (!bt || !o || !ws) return TACE_ERR_INVALID_ARGUMENT;
     for (const auto& e : weights)
@@ -319,6 +354,8 @@ struct Model : ModelBase {
     debug.clear();
     const bool need_grad = o->forces || o->virials || o->stress || o->edge_forces;
 
+    phase_used = 0;
+    PH("graph_prep");
     // ---- graph preparation
     GraphPrepArgs gp;
     gp.E = E; gp.n_atoms = (int)N; gp.n_local = (int)NL; gp.n_graphs = B; gp.n_elements = n_el;
@@ -327,7 +364,9 @@ struct Model : ModelBase {
     gp.perm_src = b.perm_src; gp.rowptr_src = b.rowptr_src; gp.atom_graph = b.atom_graph;
     gp.species_perm = b.species_perm; gp.species_ptr = b.species_ptr; gp.tile_ptr = b.tile_ptr;
     gp.temp = b.prep_temp; gp.temp_bytes = b.prep_temp_bytes;
-    CK(launch_graph_prep(gp, s));
+    CKL(launch_graph_prep(gp, s));
+    launches += 8;  // launch_graph_prep runs nine kernels of its own besides the radix sorts
+    PH("edge_fwd");
 
     // ---- edge features
     EdgeArgs<T> ea;
@@ -350,36 +389,41 @@ struct Model : ModelBase {
       ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
     }
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
-    CK(launch_edge_fwd(ea, s));
+    CKL(launch_edge_fwd(ea, s));
     debug.push_back({"Y", b.Y, (long long)D * E});
     debug.push_back({"vec", b.vec, 3 * E});
 
     // ---- layers, forward
-    CK(launch_species_gather(w("emb"), bt->species, b.lay[0].h_in, (int)N, C, s));
+    PH("embed");
+    CKL(launch_species_gather(w("emb"), bt->species, b.lay[0].h_in, (int)N, C, s));
     for (int t = 0; t < NL_; ++t) {
       const LayerPlan& p = layers[t];
       LayerBufs& lb = b.lay[t];
       const std::string pre = "t" + std::to_string(t) + ".";
       const std::string ts = std::to_string(t);
+      PH(("t" + ts + ".fwd.linear_up").c_str());
       {  // linear_up on every atom (ghosts included: they are message sources)
         GemmBatch<T> gb = plain_batch(N);
         for (int l : p.in_ls)
           add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "up.l" + std::to_string(l)), C,
                       lb.x + (long long)l * l * C, (long long)p.tp.NX * C, C, l == 0 ? w(pre + "up.b") : nullptr, 0);
-        CK(launch_gemm(gb, N, s));
+        CKL(launch_gemm(gb, N, s));
       }
+      PH(("t" + ts + ".fwd.radial_gemm").c_str());
       {  // last radial-MLP layer: per-edge path weights
         GemmBatch<T> gb = plain_batch(E);
         add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), p.tp.NP * C, lb.W, (long long)p.tp.NP * C, 0, nullptr, 0);
-        CK(launch_gemm(gb, E, s));
+        CKL(launch_gemm(gb, E, s));
       }
+      PH(("t" + ts + ".fwd.tp").c_str());
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
       ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W; ta.x = lb.x; ta.M = lb.M;
-      CK(launch_tp_fwd(ta, s));
+      CKL(launch_tp_fwd(ta, s));
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
+      PH(("t" + ts + ".fwd.node").c_str());
       {  // linear_down (1/avg_num_neighbors folded into the weights)
         GemmBatch<T> gb = plain_batch(NL);
         for (int l = 0; l <= L; ++l) {
@@ -390,25 +434,25 @@ struct Model : ModelBase {
                       w(pre + "down.l" + std::to_string(l)), Nout, dst, (long long)(L + 1 + D) * C, C,
                       l == 0 ? w(pre + "down.b") : nullptr, 0);
         }
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
-      CK(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, s));
+      CKL(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, s));
       {
         GemmBatch<T> gb = plain_batch(NL);
         for (int l = 0; l <= L; ++l)
           add_problem(gb, lb.a + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nl.l" + std::to_string(l)), C,
                       lb.A + (long long)l * l * C, (long long)D * C, C, l == 0 ? w(pre + "nl.b") : nullptr, 0);
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
       debug.push_back({"A" + ts, lb.A, NL * D * C});
-      if (cfg.correlation >= 2) CK(launch_pb_fwd(lb.A, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
+      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.A, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
       {  // per-species coefficients
         GemmBatch<T> gb = species_batch(b);
         for (int l : p.out_ls)
           add_problem(gb, lb.A + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "c0.l" + std::to_string(l)), C,
                       lb.out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "c.b") : nullptr, 0,
                       (long long)C * C, C, tiles(b, l));
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
         if (cfg.correlation >= 2) {
           GemmBatch<T> g2 = species_batch(b);
           for (size_t i = 0; i < p.out_ls.size(); ++i) {
@@ -418,7 +462,7 @@ struct Model : ModelBase {
                         w(pre + "c1.l" + std::to_string(l)), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 1,
                         (long long)K * C, 0, tiles(b, l));
           }
-          CK(launch_gemm(g2, NL, s));
+          CKL(launch_gemm(g2, NL, s));
         }
       }
       {
@@ -426,7 +470,7 @@ struct Model : ModelBase {
         for (int l : p.out_ls)
           add_problem(gb, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "lin.l" + std::to_string(l)),
                       C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "lin.b") : nullptr, 0);
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
       if (p.has_res) {  // per-species skip connection from the layer input
         GemmBatch<T> gb = species_batch(b);
@@ -434,12 +478,13 @@ struct Model : ModelBase {
           add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "res.l" + std::to_string(l)),
                       C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "res.b") : nullptr, 1,
                       (long long)C * C, C, tiles(b, l));
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
       debug.push_back({"h" + std::to_string(t + 1), lb.h_out, NL * p.Dout * C});
     }
 
     // ---- read-out
+    PH("readout");
     LayerBufs& top = b.lay[NL_ - 1];
     ReadoutArgs<T> ra;
     memset(&ra, 0, sizeof(ra));
@@ -447,29 +492,31 @@ struct Model : ModelBase {
     ra.scale = w("scale"); ra.e0 = w("e0"); ra.species = bt->species; ra.atom_graph = b.atom_graph;
     ra.graph_ptr = bt->graph_ptr; ra.rowptr_dst = b.rowptr_dst; ra.node_energy = static_cast<T*>(o->node_energy);
     ra.e_scaled = b.e_scaled; ra.gh = need_grad ? top.gh_out : nullptr; ra.n = (int)NL; ra.C = C; ra.H = H;
-    CK(launch_readout(ra, s));
-    if (o->energy) CK(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, static_cast<T*>(o->energy), B, s));
-    if (!need_grad) return TACE_OK;
+    CKL(launch_readout(ra, s));
+    if (o->energy) CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, static_cast<T*>(o->energy), B, s));
+    if (!need_grad) { PH("end"); return TACE_OK; }
 
     // ---- layers, backward
     for (int t = NL_ - 1; t >= 0; --t) {
       const LayerPlan& p = layers[t];
       LayerBufs& lb = b.lay[t];
       const std::string pre = "t" + std::to_string(t) + ".";
+      const std::string ts = std::to_string(t);
+      PH(("t" + ts + ".bwd.node").c_str());
       {  // through the final linear
         GemmBatch<T> gb = plain_batch(NL);
         for (int l : p.out_ls)
           add_problem(gb, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "linT.l" + std::to_string(l)),
                       C, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 0);
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
-      if ((int)p.out_ls.size() != L + 1) CK(launch_fill_zero(lb.gA, NL * D * C, s));
+      if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gA, NL * D * C, s));
       {  // through the per-species coefficients
         GemmBatch<T> gb = species_batch(b);
         for (int l : p.out_ls)
           add_problem(gb, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "c0T.l" + std::to_string(l)),
                       C, lb.gA + (long long)l * l * C, (long long)D * C, C, nullptr, 0, (long long)C * C, 0, tiles(b, l));
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
         if (cfg.correlation >= 2) {
           GemmBatch<T> g2 = species_batch(b);
           for (size_t i = 0; i < p.out_ls.size(); ++i) {
@@ -479,8 +526,8 @@ struct Model : ModelBase {
                         w(pre + "c1T.l" + std::to_string(l)), K, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K,
                         nullptr, 0, (long long)K * C, 0, tiles(b, l));
           }
-          CK(launch_gemm(g2, NL, s));
-          CK(launch_pb_bwd(lb.A, lb.B2, lb.gA, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
+          CKL(launch_gemm(g2, NL, s));
+          CKL(launch_pb_bwd(lb.A, lb.B2, lb.gA, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
         }
       }
       {
@@ -488,9 +535,9 @@ struct Model : ModelBase {
         for (int l = 0; l <= L; ++l)
           add_problem(gb, lb.gA + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nlT.l" + std::to_string(l)), C,
                       lb.ga + (long long)l * l * C, (long long)D * C, C, nullptr, 0);
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
-      CK(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, s));
+      CKL(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, s));
       {  // through linear_down; the gradient of the messages overwrites the messages
         GemmBatch<T> gb = plain_batch(NL);
         for (int l = 0; l <= L; ++l) {
@@ -500,54 +547,61 @@ struct Model : ModelBase {
           add_problem(gb, src, (long long)(L + 1 + D) * C, C, 2 * l + 1, Kin, w(pre + "downT.l" + std::to_string(l)), Nk,
                       lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, Nk, nullptr, 0);
         }
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
       }
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W;
       ta.x = lb.x; ta.gM = lb.M;
       if (!p.scalar_src) {  // gradient with respect to the source features (needs W before it is overwritten)
+        PH(("t" + ts + ".bwd.tp_src").c_str());
         ta.n_seg = (int)N; ta.rowptr = b.rowptr_src; ta.perm = b.perm_src; ta.dx = lb.gx;
-        CK(launch_tp_bwd_src(ta, s));
+        CKL(launch_tp_bwd_src(ta, s));
       }
+      PH(("t" + ts + ".bwd.tp_edge").c_str());
       ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.perm = nullptr; ta.dW = lb.W; ta.dY = b.dY;
       ta.accumulate_dY = (t != NL_ - 1);
-      CK(launch_tp_bwd_edge(ta, s));
+      CKL(launch_tp_bwd_edge(ta, s));
+      PH(("t" + ts + ".bwd.radial_gemm").c_str());
       {  // back through the last radial-MLP layer
         GemmBatch<T> gb = plain_batch(E);
         add_problem(gb, lb.W, (long long)p.tp.NP * C, 0, 1, p.tp.NP * C, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
-        CK(launch_gemm(gb, E, s));
+        CKL(launch_gemm(gb, E, s));
       }
       if (!p.scalar_src) {
+        PH(("t" + ts + ".bwd.linear_up").c_str());
         GemmBatch<T> gb = plain_batch(NL);
         for (int l : p.in_ls)
           add_problem(gb, lb.gx + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C, w(pre + "upT.l" + std::to_string(l)),
                       C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 0);
-        CK(launch_gemm(gb, NL, s));
+        CKL(launch_gemm(gb, NL, s));
         if (p.has_res) {
           GemmBatch<T> g2 = species_batch(b);
           for (int l : p.out_ls)
             add_problem(g2, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C,
                         w(pre + "resT.l" + std::to_string(l)), C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 1,
                         (long long)C * C, 0, tiles(b, l));
-          CK(launch_gemm(g2, NL, s));
+          CKL(launch_gemm(g2, NL, s));
         }
       }
     }
 
     // ---- back to the edge vectors, then forces and virials
-    CK(launch_edge_bwd(ea, s));
+    PH("edge_bwd");
+    CKL(launch_edge_bwd(ea, s));
     debug.push_back({"g", b.g, 3 * E});
+    PH("forces");
     const bool want_virial = (o->virials || o->stress) && !vec_mode;
     ForceArgs<T> fa;
     memset(&fa, 0, sizeof(fa));
     fa.n_atoms = (int)N; fa.n_local = (int)NL; fa.rowptr_dst = b.rowptr_dst; fa.rowptr_src = b.rowptr_src;
     fa.perm_src = b.perm_src; fa.g = b.g; fa.vec = b.vec; fa.forces = static_cast<T*>(o->forces);
     fa.atom_virial = want_virial ? b.atom_virial : nullptr;
-    if (fa.forces || fa.atom_virial) CK(launch_forces(fa, s));
+    if (fa.forces || fa.atom_virial) CKL(launch_forces(fa, s));
     if (want_virial)
-      CK(launch_graph_virial(b.atom_virial, bt->graph_ptr, static_cast<const T*>(bt->lattice), static_cast<T*>(o->virials),
+      CKL(launch_graph_virial(b.atom_virial, bt->graph_ptr, static_cast<const T*>(bt->lattice), static_cast<T*>(o->virials),
                              static_cast<T*>(o->stress), B, s));
+    PH("end");
     return TACE_OK;
   }
 
@@ -638,6 +692,18 @@ int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* ou
                  tace_stream_t stream) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   return model->impl->forward(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+int64_t tace_launch_count(const TaceModel* model) { return model ? model->impl->launches : TACE_ERR_INVALID_ARGUMENT; }
+int tace_profile_enable(TaceModel* model, int enable) {
+  if (!model) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->profile = enable != 0;
+  model->impl->phase_used = 0;
+  return TACE_OK;
+}
+int tace_profile_count(const TaceModel* model) { return model ? model->impl->phase_count() : TACE_ERR_INVALID_ARGUMENT; }
+int tace_profile_read(TaceModel* model, int index, const char** name, float* ms) {
+  if (!model || !name || !ms) return TACE_ERR_INVALID_ARGUMENT;
+  return model->impl->phase_read(index, name, ms);
 }
 int64_t tace_debug_read(TaceModel* model, const char* name, void* dst, int64_t numel, tace_stream_t stream) {
   if (!model || !name || !dst) return TACE_ERR_INVALID_ARGUMENT;

@@ -25,24 +25,36 @@ def z_to_index(atomic_numbers: Sequence[int], model_numbers: Sequence[int]) -> n
 
 def build_batch(batch: Dict[str, np.ndarray], model_numbers: Sequence[int], cutoff: float, dtype: torch.dtype,
                 device: torch.device) -> Dict[str, torch.Tensor]:
-    """``batch`` as returned by ``tace_b200.synth.collate`` (host arrays).  Uploads the structure,
-    builds the neighbour list on ``device`` and returns the model input dictionary."""
+    """``batch`` as returned by ``tace_b200.synth.collate``: host numpy arrays or (pinned) CPU
+    tensors; an optional ``species`` entry (index into the model's element list) replaces the
+    lookup from ``atomic_numbers``.  Uploads the structure, builds the neighbour list on ``device``
+    and returns the model input dictionary."""
     n_el = len(model_numbers)
-    pos64 = torch.as_tensor(batch["positions"], dtype=torch.float64).to(device)
-    cells = np.stack([complete_cell(c, batch["positions"][a:b], p, cutoff)
-                      for c, p, a, b in zip(batch["lattice"], batch["pbc"], batch["ptr"][:-1], batch["ptr"][1:])])
-    lat64 = torch.as_tensor(cells, dtype=torch.float64).to(device)
-    ptr = torch.as_tensor(batch["ptr"], dtype=torch.int64).to(device)
-    pbc = torch.as_tensor(np.asarray(batch["pbc"], dtype=np.uint8)).to(device)
+    pbc_host = np.asarray(batch["pbc"], dtype=np.uint8)
+    lattice_host = batch["lattice"]
+    if pbc_host.all():
+        cells = lattice_host  # fully periodic: the cell is used as given
+    else:
+        pos_np, lat_np, ptr_np = (np.asarray(batch[k]) for k in ("positions", "lattice", "ptr"))
+        cells = np.stack([complete_cell(c, pos_np[a:b], p, cutoff)
+                          for c, p, a, b in zip(lat_np, pbc_host, ptr_np[:-1], ptr_np[1:])])
+    up = lambda x, dt: torch.as_tensor(x, dtype=dt).to(device, non_blocking=True)
+    pos64 = up(batch["positions"], torch.float64)
+    lat64 = up(cells, torch.float64)
+    ptr = up(batch["ptr"], torch.int64)
+    pbc = up(pbc_host, torch.uint8)
     edge_index, shifts = neighbor_list_batch(pos64, lat64, pbc, ptr.to(torch.int32), cutoff)
-    species = torch.as_tensor(z_to_index(batch["atomic_numbers"], model_numbers)).to(device)
+    if "species" in batch:
+        species = up(batch["species"], torch.int64)
+    else:
+        species = up(z_to_index(np.asarray(batch["atomic_numbers"]), model_numbers), torch.int64)
     return {
         "positions": pos64.to(dtype),
-        "lattice": torch.as_tensor(batch["lattice"], dtype=torch.float64).to(device).to(dtype),
+        "lattice": up(lattice_host, torch.float64).to(dtype),
         "node_attrs": torch.nn.functional.one_hot(species, n_el).to(dtype),
         "species": species.to(torch.int32),
         "edge_index": edge_index,
         "edge_shifts": shifts.to(dtype),
-        "batch": torch.as_tensor(batch["batch"], dtype=torch.int64).to(device),
+        "batch": up(batch["batch"], torch.int64),
         "ptr": ptr,
     }

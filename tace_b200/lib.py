@@ -18,6 +18,7 @@ TACE_F32, TACE_F64 = 0, 1
 EXPORTS = [
     "tace_status_string", "tace_create", "tace_destroy", "tace_weight_count", "tace_weight_info", "tace_set_weight",
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill",
+    "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read",
 ]
 
 
@@ -77,6 +78,11 @@ def load() -> ctypes.CDLL:
     lib.tace_forward.argtypes = [c_void_p, POINTER(TaceBatch), POINTER(TaceOutputs), c_void_p, c_size_t, c_void_p]
     lib.tace_debug_read.argtypes = [c_void_p, c_char_p, c_void_p, c_int64, c_void_p]
     lib.tace_debug_read.restype = c_int64
+    lib.tace_launch_count.argtypes = [c_void_p]
+    lib.tace_launch_count.restype = c_int64
+    lib.tace_profile_enable.argtypes = [c_void_p, c_int]
+    lib.tace_profile_count.argtypes = [c_void_p]
+    lib.tace_profile_read.argtypes = [c_void_p, c_int, POINTER(c_char_p), POINTER(ctypes.c_float)]
     lib.tace_nl_count.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_void_p]
     lib.tace_nl_fill.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_int64,
                                  c_void_p, c_void_p, c_void_p]

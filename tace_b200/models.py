@@ -398,6 +398,26 @@ class TensorModel(torch.nn.Module):
                                         ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
         return res
 
+    def launch_count(self) -> int:
+        """Kernels of libtace_b200.so enqueued by this model's forward calls so far."""
+        return int(_lib.load().tace_launch_count(self._handle)) if self._handle is not None else 0
+
+    def enable_profile(self, enable: bool = True) -> None:
+        """Record a CUDA event at every phase boundary of forward (see ``read_profile``)."""
+        if self._handle is None:
+            raise _lib.TaceError("run one forward call before enabling the profile")
+        _lib.check(_lib.load().tace_profile_enable(self._handle, int(enable)), "tace_profile_enable")
+
+    def read_profile(self) -> Dict[str, float]:
+        """Phase name -> device milliseconds of the last forward call (synchronises)."""
+        lib = _lib.load()
+        out: Dict[str, float] = {}
+        name, ms = ctypes.c_char_p(), ctypes.c_float()
+        for i in range(lib.tace_profile_count(self._handle)):
+            _lib.check(lib.tace_profile_read(self._handle, i, ctypes.byref(name), ctypes.byref(ms)), "tace_profile_read")
+            out[name.value.decode()] = out.get(name.value.decode(), 0.0) + float(ms.value)
+        return out
+
     def debug_read(self, name: str, numel: int) -> torch.Tensor:
         """Copy a named intermediate of the last forward call (parity tests)."""
         lib = _lib.load()

@@ -162,6 +162,9 @@ WORKLOADS = {
     "cu256_fp64": dict(L=2, channels=64, cutoff=5.0, elements=[29], avg_num_neighbors=42.75, dtype="float64"),
     "crystals64_fp32": dict(L=3, channels=128, cutoff=6.0, elements=list(range(1, 90)), avg_num_neighbors=63.3,
                             dtype="float32"),
+    # a quarter of the batch above, used for profiler captures
+    "crystals16_fp32": dict(L=3, channels=128, cutoff=6.0, elements=list(range(1, 90)), avg_num_neighbors=63.3,
+                            dtype="float32"),
     "water32400_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32"),
     "cual1m_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
 }
@@ -172,6 +175,8 @@ def workload_structures(name: str) -> List[Structure]:
         return [fcc_supercell(4, 3.61, 0.05, seed=0)]
     if name == "crystals64_fp32":
         return random_crystals(64, seed=1)
+    if name == "crystals16_fp32":
+        return random_crystals(16, seed=1)
     if name == "water32400_fp32":
         return [water_box()]
     if name == "cual1m_fp32":
