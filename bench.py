@@ -314,7 +314,8 @@ def main():
     dims = {"s": 4 if dtype == torch.float32 else 8, "E": n_edges, "N": n_atoms, "C": C, "D": (L + 1) ** 2,
             "NM": [sum((2 * l + 1) * lp.k[l] for l in range(L + 1)) for lp in plan.layers],
             "NP": [len(lp.tp_paths) for lp in plan.layers]}
-    kernel_phases = {k: v for k, v in phases.items() if k not in ("end",)}
+    # the dominant kernel: tensor-product passes and the radial-MLP GEMMs are single-kernel phases
+    kernel_phases = {k: v for k, v in phases.items() if ".tp" in k or "radial_gemm" in k}
     top = max(kernel_phases, key=kernel_phases.get)
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
