@@ -129,6 +129,20 @@ int tace_profile_enable(TaceModel* model, int enable);
 int tace_profile_count(const TaceModel* model);
 int tace_profile_read(TaceModel* model, int index, const char** name, float* ms);
 
+/* Dense fp32 GEMM on the tcgen05 tensor cores with 3xTF32 operand splitting:
+ * C[M,N] = A[M,K] @ B[N,K]^T, A row-major with leading dimension lda, B given K-major as its TF32 high
+ * part B_hi and residual B_lo = B - B_hi, C row-major with leading dimension ldc.  K must be a multiple
+ * of 32, N of 64, lda and ldc of 4, all pointers 16-byte aligned.  Stands behind the reference's
+ * mlpLinear (torch.mm, tace/models/linear.py:267-276); tace_forward uses it for the last radial-MLP
+ * layer of fp32 models.  `error_flag` is a device int that must be zero on entry; it receives a
+ * non-zero code if a bounded wait inside the kernel expired (results are then undefined). */
+int tace_tc_gemm_f32(const float* A, int64_t lda, const float* B_hi, const float* B_lo, float* C, int64_t ldc, int32_t M,
+                     int32_t N, int32_t K, int32_t* error_flag, tace_stream_t stream);
+
+/* Reads (and clears) the model's device-side error word: 0 = none; non-zero = a bounded wait in a
+ * kernel launched by tace_forward expired.  Synchronises the device. */
+int tace_device_error(TaceModel* model, int32_t* code);
+
 /* Debug taps used by the parity tests: copies a named intermediate of the last tace_forward
  * call ("M0", "A0", "h1", ...) into `dst` (device, model dtype, at most `numel` elements).
  * Returns the number of elements copied or a negative status. */

@@ -95,6 +95,7 @@ struct ModelBase {
 
   // kernel-launch counter and optional per-phase CUDA-event timing
   long long launches = 0;
+  int* dev_error = nullptr;  // device word written by kernels whose bounded waits expire
   bool profile = false;
   std::vector<std::string> phase_names;
   std::vector<cudaEvent_t> phase_events;
@@ -138,8 +139,10 @@ struct Model : ModelBase {
 
   ~Model() override {
     if (arena) cudaFree(arena);
+    if (dev_error) cudaFree(dev_error);
     release_events();
   }
+  static constexpr bool kTensorCore = sizeof(T) == 4;  // fp32 models run the radial GEMMs on tcgen05
 
   void add_weight(const std::string& name, long long numel) {
     weights.push_back({name, numel, arena_numel, false});
@@ -182,6 +185,12 @@ struct Model : ModelBase {
       add_weight(pre + "A2t", kHidden * kHidden);
       add_weight(pre + "W3", (long long)kHidden * p.tp.NP * C);
       add_weight(pre + "W3t", (long long)kHidden * p.tp.NP * C);
+      if (kTensorCore) {  // TF32 high parts and residuals of both orientations
+        add_weight(pre + "W3_hi", (long long)kHidden * p.tp.NP * C);
+        add_weight(pre + "W3_lo", (long long)kHidden * p.tp.NP * C);
+        add_weight(pre + "W3t_hi", (long long)kHidden * p.tp.NP * C);
+        add_weight(pre + "W3t_lo", (long long)kHidden * p.tp.NP * C);
+      }
       for (int l = 0; l <= L; ++l) {
         const long long outl = (l == 0) ? (long long)(L + 2) * C : C;
         add_weight(pre + "down.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
@@ -217,6 +226,8 @@ struct Model : ModelBase {
     add_weight("e0", n_el);
     if (cudaMalloc(&arena, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
     if (cudaMemset(arena, 0, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
+    if (cudaMalloc(&dev_error, sizeof(int)) != cudaSuccess || cudaMemset(dev_error, 0, sizeof(int)) != cudaSuccess)
+      return TACE_ERR_CUDA;
     return TACE_OK;
   }
 
@@ -410,7 +421,11 @@ struct Model : ModelBase {
         CKL(launch_gemm(gb, N, s));
       }
       PH(("t" + ts + ".fwd.radial_gemm").c_str());
-      {  // last radial-MLP layer: per-edge path weights
+      if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // last radial-MLP layer on tcgen05: W[e, :] = H3[e, :] @ W3
+        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.H3), kHidden, reinterpret_cast<const float*>(w(pre + "W3t_hi")),
+                           reinterpret_cast<const float*>(w(pre + "W3t_lo")), reinterpret_cast<float*>(lb.W),
+                           (long long)p.tp.NP * C, (int)E, p.tp.NP * C, kHidden, dev_error, s));
+      } else {
         GemmBatch<T> gb = plain_batch(E);
         add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), p.tp.NP * C, lb.W, (long long)p.tp.NP * C, 0, nullptr, 0);
         CKL(launch_gemm(gb, E, s));
@@ -563,7 +578,11 @@ struct Model : ModelBase {
       ta.accumulate_dY = (t != NL_ - 1);
       CKL(launch_tp_bwd_edge(ta, s));
       PH(("t" + ts + ".bwd.radial_gemm").c_str());
-      {  // back through the last radial-MLP layer
+      if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // back through the last radial-MLP layer: dH3[e, :] = dW[e, :] @ W3^T
+        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.W), (long long)p.tp.NP * C,
+                           reinterpret_cast<const float*>(w(pre + "W3_hi")), reinterpret_cast<const float*>(w(pre + "W3_lo")),
+                           reinterpret_cast<float*>(lb.H3), kHidden, (int)E, kHidden, p.tp.NP * C, dev_error, s));
+      } else {
         GemmBatch<T> gb = plain_batch(E);
         add_problem(gb, lb.W, (long long)p.tp.NP * C, 0, 1, p.tp.NP * C, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
         CKL(launch_gemm(gb, E, s));
@@ -692,6 +711,14 @@ int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* ou
                  tace_stream_t stream) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   return model->impl->forward(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+int tace_device_error(TaceModel* model, int32_t* code) {
+  if (!model || !code) return TACE_ERR_INVALID_ARGUMENT;
+  int v = 0;
+  if (cudaMemcpy(&v, model->impl->dev_error, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return TACE_ERR_CUDA;
+  if (v != 0 && cudaMemset(model->impl->dev_error, 0, sizeof(int)) != cudaSuccess) return TACE_ERR_CUDA;
+  *code = v;
+  return TACE_OK;
 }
 int64_t tace_launch_count(const TaceModel* model) { return model ? model->impl->launches : TACE_ERR_INVALID_ARGUMENT; }
 int tace_profile_enable(TaceModel* model, int enable) {

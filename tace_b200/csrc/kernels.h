@@ -132,3 +132,11 @@ size_t graph_prep_temp_bytes(long long E, int n_atoms);
 cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s);
 
 }  // namespace tace
+
+namespace tace {
+// FP32-accurate GEMM on tcgen05 tensor cores (tc_gemm.cu): C[M,N] = A[M,K] @ B[N,K]^T with B given
+// as its TF32 high part and residual.  `error_flag` (device int) receives a non-zero code if a
+// bounded wait inside the kernel expired.
+cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
+                           int N, int K, int* error_flag, cudaStream_t s);
+}  // namespace tace

@@ -1,0 +1,329 @@
+// FP32-accurate dense GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), used for
+// the last layer of the radial MLP and its transpose (the reference's mlpLinear torch.mm,
+// tace/models/linear.py:267-276, which produces the per-edge tensor-product weights
+// [edges, paths*channels]).
+//
+//   C[M, N] = A[M, K] @ B[N, K]^T        (both operands K-major, C row-major, all fp32)
+//
+// Plain TF32 (10-bit mantissa) is too coarse for the 1e-5 eV/atom parity target, so every
+// operand is split into a TF32-exact high part and a residual, x = hi + lo, and the product is
+// accumulated as hi*hi + hi*lo + lo*hi in the FP32 TMEM accumulator (the dropped lo*lo term is
+// ~2^-22 relative).  The weight operand B is split once on the host; the activation operand A
+// is split in shared memory right after its TMA load, element-wise and in place, which keeps
+// the 128-byte-swizzled layout the TMA engine wrote.
+//
+// One CTA = 128 threads walks its share of 128 x BN output tiles.  Per 32-wide K step a 3-stage
+// ring holds {A, A_lo, B_hi, B_lo}; thread 0 issues the TMA loads and the tcgen05.mma
+// instructions, all four warps split A and run the epilogue (tcgen05.ld of their 32 TMEM lanes,
+// 128-bit stores).  Every mbarrier wait is bounded: on expiry the CTA records an error code in
+// global memory, stops waiting, drains and frees its TMEM, and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/tace_b200.h"
+#include "kernels.h"
+
+namespace tace {
+
+namespace {
+
+constexpr int kBM = 128;      // rows per tile = TMEM lanes
+constexpr int kBK = 32;       // fp32 elements per K step = one 128-byte swizzle row
+constexpr int kStages = 3;
+constexpr int kTileABytes = kBM * kBK * 4;  // 16 KB
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred P1;\n mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n selp.b32 %0, 1, 0, P1;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is hit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
+  if (*abort_flag) return false;
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// K-major operand tile with 128-byte rows and 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for this layout)
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+struct TcParams {
+  int M, N, K;
+  float* C;
+  long long ldc;
+  int* error;
+};
+
+template <int BN>
+struct TcSmem {
+  static constexpr int kTileBBytes = BN * kBK * 4;
+  static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
+  static constexpr int kBarrierBytes = 128;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                         const __grid_constant__ CUtensorMap tmBhi,
+                                                         const __grid_constant__ CUtensorMap tmBlo, const TcParams p) {
+  using S = TcSmem<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte-swizzled tiles need 1024-byte alignment
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + kStages * S::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * kStages);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kStages * S::kStageBytes + 8 * (2 * kStages + 1));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kStages * S::kStageBytes + 8 * (2 * kStages + 1) + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = p.N / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int num_k = p.K / kBK;
+  const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int total = my_tiles * num_k;
+  // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+  auto stage_a = [&](int s) { return base + s * S::kStageBytes; };
+  auto stage_alo = [&](int s) { return base + s * S::kStageBytes + kTileABytes; };
+  auto stage_bhi = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes; };
+  auto stage_blo = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes + S::kTileBBytes; };
+
+  int issued = 0;
+  auto issue = [&](int j) {  // thread 0: TMA loads of flat step j into its ring slot
+    const int s = j % kStages, ph = (j / kStages) & 1;
+    mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.error, 1);
+    if (*abort_flag) return;
+    const int tile = blockIdx.x + (j / num_k) * gridDim.x, ks = j % num_k;
+    const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+    mbar_expect_tx(full_bar(s), kTileABytes + 2 * S::kTileBBytes);
+    tma_load_2d(stage_a(s), &tmA, full_bar(s), ks * kBK, m0);
+    tma_load_2d(stage_bhi(s), &tmBhi, full_bar(s), ks * kBK, n0);
+    tma_load_2d(stage_blo(s), &tmBlo, full_bar(s), ks * kBK, n0);
+  };
+  if (tid == 0)
+    for (; issued < kStages - 1 && issued < total; ++issued) issue(issued);
+
+  uint32_t acc_phase = 0;
+  int consumed = 0;
+  for (int i = 0; i < total; ++i) {
+    const int s = i % kStages, ph = (i / kStages) & 1;
+    const int ks = i % num_k;
+    mbar_wait(full_bar(s), ph, abort_flag, p.error, 2);
+    // split A into TF32-exact high part (in place) and residual
+    {
+      float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
+      float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
+#pragma unroll
+      for (int j = 0; j < kTileABytes / 16 / 128; ++j) {
+        const int idx = tid + j * 128;
+        const float4 v = a[idx];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        a[idx] = h;
+        alo[idx] = l;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) break;  // uniform: every writer of the flag precedes this barrier or the next one
+    consumed = i + 1;
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int k8 = 0; k8 < kBK / 8; ++k8) {
+        const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
+        const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
+        umma_tf32(tmem_base, da, db, idesc, (ks > 0 || k8 > 0) ? 1u : 0u);
+        umma_tf32(tmem_base, da, dbl, idesc, 1u);
+        umma_tf32(tmem_base, dal, db, idesc, 1u);
+      }
+      umma_commit(empty_bar(s));              // ring slot reusable once these MMAs have read it
+      if (ks == num_k - 1) umma_commit(acc_bar);  // accumulator of this tile complete
+      if (issued < total) { issue(issued); ++issued; }
+    }
+    if (ks == num_k - 1) {
+      mbar_wait(acc_bar, acc_phase, abort_flag, p.error, 3);
+      acc_phase ^= 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int tile = blockIdx.x + (i / num_k) * gridDim.x;
+      const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+      const int row = m0 + warp * 32 + lane;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.M && !*abort_flag) {
+          float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0 + c * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                 __uint_as_float(r[4 * q + 3]));
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncthreads();  // TMEM may be overwritten by the next tile's first MMA
+      if (*abort_flag) break;
+    }
+  }
+  // Drain: loads that were issued but never consumed must land before the CTA exits.
+  __syncthreads();
+  if (tid == 0) {
+    for (int j = consumed; j < issued; ++j) {
+      const int s = j % kStages, ph = (j / kStages) & 1;
+      for (uint32_t it = 0; it < kSpinLimit; ++it)
+        if (mbar_try_wait(full_bar(s), ph)) break;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D fp32 tensor [rows][cols] with `ld` elements between rows; box = [box_rows][32 columns], 128-byte swizzle.
+bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+cudaError_t launch_tc(const CUtensorMap& a, const CUtensorMap& bh, const CUtensorMap& bl, const TcParams& p, int sms, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * (p.N / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  tc_gemm_kernel<BN><<<grid, 128, TcSmem<BN>::kTotal, s>>>(a, bh, bl, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
+                           int N, int K, int* error_flag, cudaStream_t s) {
+  if (M <= 0) return cudaSuccess;
+  if (K % kBK != 0 || N % 64 != 0 || (lda % 4) != 0 || (ldc % 4) != 0 || !error_flag) return cudaErrorInvalidValue;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return cudaErrorInvalidValue;
+  }
+  const int bn = (N % 128 == 0) ? 128 : 64;
+  CUtensorMap ma, mbh, mbl;
+  if (!make_map(&ma, A, M, K, lda, kBM) || !make_map(&mbh, Bhi, N, K, K, bn) || !make_map(&mbl, Blo, N, K, K, bn))
+    return cudaErrorInvalidValue;
+  TcParams p{M, N, K, C, ldc, error_flag};
+  return bn == 128 ? launch_tc<128>(ma, mbh, mbl, p, sms, s) : launch_tc<64>(ma, mbh, mbl, p, sms, s);
+}
+
+}  // namespace tace
+
+extern "C" int tace_tc_gemm_f32(const float* A, int64_t lda, const float* B_hi, const float* B_lo, float* C, int64_t ldc,
+                                int32_t M, int32_t N, int32_t K, int32_t* error_flag, tace_stream_t stream) {
+  if (!A || !B_hi || !B_lo || !C) return TACE_ERR_INVALID_ARGUMENT;
+  cudaError_t e = tace::launch_tc_gemm(A, lda, B_hi, B_lo, C, ldc, M, N, K, error_flag, static_cast<cudaStream_t>(stream));
+  if (e == cudaErrorInvalidValue) return TACE_ERR_INVALID_ARGUMENT;
+  return e == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}

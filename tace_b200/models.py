@@ -398,6 +398,14 @@ class TensorModel(torch.nn.Module):
                                         ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
         return res
 
+    def device_error(self) -> int:
+        """Non-zero if a bounded wait inside a kernel expired since the last check (synchronises)."""
+        if self._handle is None:
+            return 0
+        code = ctypes.c_int32()
+        _lib.check(_lib.load().tace_device_error(self._handle, ctypes.byref(code)), "tace_device_error")
+        return int(code.value)
+
     def launch_count(self) -> int:
         """Kernels of libtace_b200.so enqueued by this model's forward calls so far."""
         return int(_lib.load().tace_launch_count(self._handle)) if self._handle is not None else 0

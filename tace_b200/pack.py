@@ -82,6 +82,13 @@ class ModelPlan:
         return out
 
 
+def split_tf32(w: np.ndarray):
+    """fp32 value = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits zero)."""
+    w32 = np.ascontiguousarray(w, dtype=np.float32)
+    hi = (w32.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    return hi, w32 - hi
+
+
 def _np(t) -> np.ndarray:
     return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
 
@@ -122,6 +129,9 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         put(tp + "A1", g(pre + "edge_info.mlp.2.weight") * math.sqrt(2.0 / hd), tp + "A1t")
         put(tp + "A2", g(pre + "edge_info.mlp.4.weight") * math.sqrt(2.0 / hd), tp + "A2t")
         put(tp + "W3", g(pre + "edge_info.mlp.6.weight") * math.sqrt(2.0 / hd), tp + "W3t")
+        for name in ("W3", "W3t"):  # TF32 high part / residual for the tensor-core GEMM of fp32 models
+            hi, lo = split_tf32(out[tp + name])
+            out[tp + name + "_hi"], out[tp + name + "_lo"] = hi, lo
         down_shapes = [(lp.k[l] * C, (L + 2) * C if l == 0 else C) for l in range(L + 1)]
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
             put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
