@@ -15,7 +15,10 @@
 // One CTA = 128 threads walks its share of 128 x BN output tiles.  Per 32-wide K step a 3-stage
 // ring holds {A, A_lo, B_hi, B_lo}; thread 0 issues the TMA loads and the tcgen05.mma
 // instructions, all four warps split A and run the epilogue (tcgen05.ld of their 32 TMEM lanes,
-// 128-bit stores).  Every mbarrier wait is bounded: on expiry the CTA records an error code in
+// 128-bit stores).  The tensor core adds into its accumulator with truncation, an error that
+// grows linearly with the number of accumulated instructions; long K loops are therefore cut
+// into chunks of kChunk steps whose partial sums are drained from TMEM and added in FP32
+// registers with round-to-nearest.  Every mbarrier wait is bounded: on expiry the CTA records an error code in
 // global memory, stops waiting, drains and frees its TMEM, and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -31,6 +34,7 @@ namespace {
 constexpr int kBM = 128;      // rows per tile = TMEM lanes
 constexpr int kBK = 32;       // fp32 elements per K step = one 128-byte swizzle row
 constexpr int kStages = 3;
+constexpr int kChunk = 8;     // K steps accumulated inside TMEM before draining into FP32 registers
 constexpr int kTileABytes = kBM * kBK * 4;  // 16 KB
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -176,9 +180,12 @@ __global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__
 
   uint32_t acc_phase = 0;
   int consumed = 0;
+  float accr[BN];  // this thread's output row (row = 32 * warp + lane of the tile)
   for (int i = 0; i < total; ++i) {
     const int s = i % kStages, ph = (i / kStages) & 1;
     const int ks = i % num_k;
+    const bool chunk_begin = (ks % kChunk) == 0;
+    const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == num_k - 1;
     mbar_wait(full_bar(s), ph, abort_flag, p.error, 2);
     // split A into TF32-exact high part (in place) and residual
     {
@@ -208,36 +215,39 @@ __global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__
       for (int k8 = 0; k8 < kBK / 8; ++k8) {
         const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
         const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
-        umma_tf32(tmem_base, da, db, idesc, (ks > 0 || k8 > 0) ? 1u : 0u);
+        umma_tf32(tmem_base, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
         umma_tf32(tmem_base, da, dbl, idesc, 1u);
         umma_tf32(tmem_base, dal, db, idesc, 1u);
       }
-      umma_commit(empty_bar(s));              // ring slot reusable once these MMAs have read it
-      if (ks == num_k - 1) umma_commit(acc_bar);  // accumulator of this tile complete
+      umma_commit(empty_bar(s));           // ring slot reusable once these MMAs have read it
+      if (chunk_end) umma_commit(acc_bar);  // partial sum of this chunk complete
       if (issued < total) { issue(issued); ++issued; }
     }
-    if (ks == num_k - 1) {
+    if (chunk_end) {
       mbar_wait(acc_bar, acc_phase, abort_flag, p.error, 3);
       acc_phase ^= 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int tile = blockIdx.x + (i / num_k) * gridDim.x;
-      const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-      const int row = m0 + warp * 32 + lane;
+      const bool first_chunk = ks < kChunk;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 32, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < p.M && !*abort_flag) {
-          float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0 + c * 32);
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
-                                 __uint_as_float(r[4 * q + 3]));
+        for (int q = 0; q < 32; ++q) accr[c * 32 + q] = first_chunk ? __uint_as_float(r[q]) : accr[c * 32 + q] + __uint_as_float(r[q]);
+      }
+      if (ks == num_k - 1) {
+        const int tile = blockIdx.x + (i / num_k) * gridDim.x;
+        const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+        const int row = m0 + warp * 32 + lane;
+        if (row < p.M && !*abort_flag) {
+          float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0);
+#pragma unroll
+          for (int q = 0; q < BN / 4; ++q) dst[q] = make_float4(accr[4 * q], accr[4 * q + 1], accr[4 * q + 2], accr[4 * q + 3]);
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();  // TMEM may be overwritten by the next tile's first MMA
+      __syncthreads();  // TMEM may be overwritten by the next chunk's first MMA
       if (*abort_flag) break;
     }
   }
