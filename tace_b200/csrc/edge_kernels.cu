@@ -5,6 +5,7 @@
 // from global memory: every thread of a warp reads the same address, so each load is one
 // L1-resident broadcast.
 #include "kernels.h"
+#include "tp_gen.cuh"
 
 namespace tace {
 
@@ -27,6 +28,11 @@ __device__ __forceinline__ void edge_geometry(const EdgeArgs<T>& a, long long e,
   d = d0 + T(1e-9);  // tace/models/adapter.py:347
 }
 
+template <int L> struct TPOf;
+template <> struct TPOf<1> { using S = TPX_L1_S; using F = TPX_L1_F; };
+template <> struct TPOf<2> { using S = TPX_L2_S; using F = TPX_L2_F; };
+template <> struct TPOf<3> { using S = TPX_L3_S; using F = TPX_L3_F; };
+
 template <typename T, int L>
 __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   constexpr int D = (L + 1) * (L + 1);
@@ -40,6 +46,9 @@ __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   sh_eval<T, L>(v[0] * inv, v[1] * inv, v[2] * inv, Y);
 #pragma unroll
   for (int k = 0; k < D; ++k) a.Y[e * D + k] = Y[k];
+  // channel-independent coupling rows G = K . Y consumed by the tensor-product kernels
+  TPOf<L>::S::template build_G<T>(Y, a.G_scalar + e * TPOf<L>::S::NG);
+  if (a.G_full) TPOf<L>::F::template build_G<T>(Y, a.G_full + e * TPOf<L>::F::NG);
   T b[kNumBessel];
   radial_eval<T>(d, a.rp, b, nullptr);
   for (int t = 0; t < a.n_layers; ++t) {

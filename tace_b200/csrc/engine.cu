@@ -24,11 +24,11 @@ namespace tace {
 
 namespace {
 
-struct TPMeta { int NP, NX, NM; const int* k; const int* base; };
+struct TPMeta { int NP, NX, NM, NG; const int* k; const int* base; };
 struct PBMeta { int NP, NB; const int* k; const int* base; };
 
 bool tp_meta(int L, bool scalar, TPMeta& m) {
-#define TPM(TAG) { m = {TP_##TAG::NP, TP_##TAG::NX, TP_##TAG::NM, tp_##TAG##_k, tp_##TAG##_base}; return true; }
+#define TPM(TAG) { m = {TPX_##TAG::NP, TPX_##TAG::NX, TPX_##TAG::NM, TPX_##TAG::NG, tp_##TAG##_k, tp_##TAG##_base}; return true; }
   if (L == 1 && scalar) TPM(L1_S)
   if (L == 1) TPM(L1_F)
   if (L == 2 && scalar) TPM(L2_S)
@@ -262,7 +262,7 @@ struct Model : ModelBase {
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr;
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *G_scalar, *G_full, *dxe;
     std::vector<LayerBufs> lay;
   };
 
@@ -274,6 +274,9 @@ struct Model : ModelBase {
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
+    b.G_scalar = ar.take<T>((size_t)E * layers[0].tp.NG);
+    b.G_full = NL_ > 1 ? ar.take<T>((size_t)E * layers[1].tp.NG) : nullptr;
+    b.dxe = NL_ > 1 ? ar.take<T>((size_t)E * D * C) : nullptr;  // per-edge gradient rows of the source features
     b.lay.resize(NL_);
     T* prev_h = ar.take<T>((size_t)N * C);   // h_0: species embedding, scalar channels
     T* prev_gh = nullptr;
@@ -399,6 +402,7 @@ struct Model : ModelBase {
       ea.H3[t] = b.lay[t].H3;
       ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
     }
+    ea.G_scalar = b.G_scalar; ea.G_full = b.G_full;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
     debug.push_back({"Y", b.Y, (long long)D * E});
@@ -434,7 +438,7 @@ struct Model : ModelBase {
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
-      ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W; ta.x = lb.x; ta.M = lb.M;
+      ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full; ta.W = lb.W; ta.x = lb.x; ta.M = lb.M;
       CKL(launch_tp_fwd(ta, s));
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
@@ -564,19 +568,19 @@ struct Model : ModelBase {
         }
         CKL(launch_gemm(gb, NL, s));
       }
+      // edge pass: gradients of the per-edge weights (in place over W), of the angular features and,
+      // per edge, of the source features
+      PH(("t" + ts + ".bwd.tp").c_str());
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
-      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.e_dst = b.e_dst; ta.Y = b.Y; ta.W = lb.W;
-      ta.x = lb.x; ta.gM = lb.M;
-      if (!p.scalar_src) {  // gradient with respect to the source features (needs W before it is overwritten)
-        PH(("t" + ts + ".bwd.tp_src").c_str());
-        ta.n_seg = (int)N; ta.rowptr = b.rowptr_src; ta.perm = b.perm_src; ta.dx = lb.gx;
-        CKL(launch_tp_bwd_src(ta, s));
+      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full;
+      ta.W = lb.W; ta.x = lb.x; ta.gM = lb.M; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.dW = lb.W; ta.dY = b.dY;
+      ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
+      CKL(launch_tp_bwd(ta, s));
+      if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
+        PH(("t" + ts + ".bwd.src_sum").c_str());
+        CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, p.tp.NX * C, s));
       }
-      PH(("t" + ts + ".bwd.tp_edge").c_str());
-      ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.perm = nullptr; ta.dW = lb.W; ta.dY = b.dY;
-      ta.accumulate_dY = (t != NL_ - 1);
-      CKL(launch_tp_bwd_edge(ta, s));
       PH(("t" + ts + ".bwd.radial_gemm").c_str());
       if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // back through the last radial-MLP layer: dH3[e, :] = dW[e, :] @ W3^T
         CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.W), (long long)p.tp.NP * C,

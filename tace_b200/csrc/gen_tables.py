@@ -112,6 +112,16 @@ def lit(v):
 
 # ----------------------------------------------------------- interaction TP code
 def gen_interaction(L, scalar_src, out):
+    """Emits, for one (L, source kind):
+
+    * ``build_G``: the channel-independent coupling of one edge, G[i] = sum_m2 K^p[m1,m2,m3] Y[l2,m2]
+      for every structurally non-zero (p, m1, m3), ordered output-group major, then (p, m3, m1), each
+      group padded to a multiple of four entries so the kernels read it with 128-bit loads;
+    * ``fwd<g>``: message components of output group g (ranks are split into at most two groups to
+      halve the accumulator registers per thread);
+    * ``bwd``: gradients with respect to the per-edge weights, the angular features and the source
+      features of one (edge, channel).
+    """
     tag = f"L{L}_{'S' if scalar_src else 'F'}"
     in1 = [0] if scalar_src else list(range(L + 1))
     sh = list(range(L + 1))
@@ -121,97 +131,118 @@ def gen_interaction(L, scalar_src, out):
     xoff = {l: (0 if scalar_src else l * l) for l in in1}
     nx = 1 if scalar_src else (L + 1) ** 2
     D = (L + 1) ** 2
-    # G holds, per edge, only the structurally non-zero entries of
-    # G^p[m1][m3] = sum_m2 K^p[m1,m2,m3] * Y[l2^2 + m2]; gi[(p, m1, m3)] is the compact index.
-    gi, g_start, g_y, g_c = {}, [0], [], []
-    nnz_total = 0
-    for p, (l1, l2, l3) in enumerate(paths):
-        K = w3j(l1, l2, l3) * math.sqrt(2 * l3 + 1)
-        nnz_total += int(np.count_nonzero(K))
-        for m1 in range(2 * l1 + 1):
-            for m3 in range(2 * l3 + 1):
-                m2s = [m2 for m2 in range(2 * l2 + 1) if K[m1, m2, m3] != 0.0]
-                if not m2s:
-                    continue
-                gi[(p, m1, m3)] = len(g_start) - 1
-                for m2 in m2s:
-                    g_y.append(l2 * l2 + m2)
-                    g_c.append(K[m1, m2, m3])
-                g_start.append(len(g_y))
-    ng = len(g_start) - 1
     P = len(paths)
+    Ks = [w3j(*p) * math.sqrt(2 * p[2] + 1) for p in paths]
+    nnz_l3 = {l: sum(int(np.count_nonzero(K)) for K, p in zip(Ks, paths) if p[2] == l) for l in outs}
+    # output-rank groups: one group for small cases, otherwise split at the rank that balances the work
+    if scalar_src or L < 2:
+        groups = [outs]
+    else:
+        best = min(range(1, L + 1), key=lambda c: abs(sum(nnz_l3[l] for l in outs[:c]) - sum(nnz_l3[l] for l in outs[c:])))
+        groups = [outs[:best], outs[best:]]
+    gi, terms = {}, []          # compact index of (p, m1, m3); per entry the list of (y index, coefficient)
+    grp_goff, grp_gcnt, grp_p0, grp_np, grp_m0, grp_nm = [], [], [], [], [], []
+    for ls in groups:
+        while len(terms) % 4:
+            terms.append([])     # padding entry (stays zero)
+        grp_goff.append(len(terms))
+        ps = [p for p, pt in enumerate(paths) if pt[2] in ls]
+        grp_p0.append(ps[0]); grp_np.append(len(ps))
+        grp_m0.append(lay.base[ls[0]]); grp_nm.append(sum((2 * l + 1) * lay.k[l] for l in ls))
+        for p in ps:
+            l1, l2, l3 = paths[p]
+            K = Ks[p]
+            for m3 in range(2 * l3 + 1):
+                for m1 in range(2 * l1 + 1):
+                    t = [(l2 * l2 + m2, K[m1, m2, m3]) for m2 in range(2 * l2 + 1) if K[m1, m2, m3] != 0.0]
+                    if t:
+                        gi[(p, m1, m3)] = len(terms)
+                        terms.append(t)
+        grp_gcnt.append(len(terms) - grp_goff[-1])
+    while len(terms) % 4:
+        terms.append([])
+    ng = len(terms)
+    nnz_total = sum(int(np.count_nonzero(K)) for K in Ks)
+    ngrp = len(groups)
 
     o = out.append
-    o(f"// ---- interaction tensor product, L={L}, {'scalar' if scalar_src else 'full'} source: "
-      f"{P} paths, {lay.nm} message components, {ng} non-zero G entries, {nnz_total} coupling non-zeros")
-    o(f"struct TP_{tag} {{")
-    o(f"  static constexpr int L = {L}, NP = {P}, NX = {nx}, NM = {lay.nm}, NG = {ng}, D = {D}, NNZ = {len(g_y)};")
-    o("};")
-    o(f"static const int tp_{tag}_path_l3[{P}] = {{{', '.join(str(p[2]) for p in paths)}}};")
+    o(f"// ---- interaction tensor product, L={L}, {'scalar' if scalar_src else 'full'} source: {P} paths, "
+      f"{lay.nm} message components, {len(gi)} non-zero G entries (padded to {ng}), {nnz_total} coupling non-zeros, "
+      f"output groups {groups}")
     o(f"static const int tp_{tag}_k[{L + 1}] = {{{', '.join(str(lay.k[l]) for l in outs)}}};")
     o(f"static const int tp_{tag}_base[{L + 1}] = {{{', '.join(str(lay.base[l]) for l in outs)}}};")
-    o(f"static const int tp_{tag}_plocal[{P}] = {{{', '.join(str(v) for v in lay.plocal)}}};")
-    o(f"TACE_CONST short tp_{tag}_gstart[{ng + 1}] = {{{', '.join(str(v) for v in g_start)}}};")
-    o(f"TACE_CONST unsigned char tp_{tag}_gy[{len(g_y)}] = {{{', '.join(str(v) for v in g_y)}}};")
-    o(f"TACE_CONST double tp_{tag}_gc[{len(g_c)}] = {{{', '.join(repr(float(v)) for v in g_c)}}};")
+    o(f"struct TPX_{tag} {{")
+    o(f"  static constexpr int L = {L}, NP = {P}, NX = {nx}, NM = {lay.nm}, NG = {ng}, D = {D}, NGRP = {ngrp};")
+    for name, arr in [("GOFF", grp_goff), ("GCNT", [((c + 3) // 4) * 4 for c in grp_gcnt]), ("P0", grp_p0), ("NPG", grp_np),
+                      ("M0", grp_m0), ("NMG", grp_nm)]:
+        o(f"  static constexpr int {name}0 = {arr[0]}, {name}1 = {arr[-1]};")
+    # build_G
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void build_G(const T (&Y)[{D}], T* __restrict__ G) {{")
+    for i, t in enumerate(terms):
+        expr = " + ".join(f"{lit(float(c))} * Y[{y}]" for y, c in t) if t else "T(0)"
+        o(f"    G[{i}] = {expr};")
+    o("  }")
 
-    def gterm(p, m1, m3):
-        return gi.get((p, m1, m3))
+    def load_G(lo, hi, loaded):
+        """Emit 4-wide loads covering entries [lo, hi); returns the lines."""
+        lines = []
+        for j in range(lo // 4, (hi + 3) // 4):
+            if j not in loaded:
+                loaded.add(j)
+                lines.append(f"    T G_{4 * j}, G_{4 * j + 1}, G_{4 * j + 2}, G_{4 * j + 3}; "
+                             f"ld4(G + {4 * j}, G_{4 * j}, G_{4 * j + 1}, G_{4 * j + 2}, G_{4 * j + 3});")
+        return lines
 
-    # forward: acc[idx(p,m3)] += w[p] * sum_m1 x[m1] G[m1][m3]
-    o("template <typename T>")
-    o(f"TACE_HD TACE_INLINE void tp_fwd_{tag}(const T (&x)[{nx}], const T* __restrict__ G, const T (&w)[{P}], T (&acc)[{lay.nm}]) {{")
-    for p, (l1, l2, l3) in enumerate(paths):
-        for m3 in range(2 * l3 + 1):
-            terms = [f"x[{xoff[l1] + m1}] * G[{gterm(p, m1, m3)}]" for m1 in range(2 * l1 + 1)
-                     if gterm(p, m1, m3) is not None]
-            if terms:
-                o(f"  acc[{lay.idx(p, m3)}] += w[{p}] * ({' + '.join(terms)});")
-    o("}")
-
-    # backward wrt x (source features): dx[m1] += w[p] * sum_m3 G[m1][m3] g[idx(p,m3)]
-    o("template <typename T>")
-    o(f"TACE_HD TACE_INLINE void tp_bwdx_{tag}(const T (&g)[{lay.nm}], const T* __restrict__ G, const T (&w)[{P}], T (&dx)[{nx}]) {{")
-    for p, (l1, l2, l3) in enumerate(paths):
-        for m1 in range(2 * l1 + 1):
-            terms = [f"G[{gterm(p, m1, m3)}] * g[{lay.idx(p, m3)}]" for m3 in range(2 * l3 + 1)
-                     if gterm(p, m1, m3) is not None]
-            if terms:
-                o(f"  dx[{xoff[l1] + m1}] += w[{p}] * ({' + '.join(terms)});")
-    o("}")
-
-    # backward wrt per-edge weights and angular features
-    o("template <typename T>")
-    o(f"TACE_HD TACE_INLINE void tp_bwdw_{tag}(const T (&x)[{nx}], const T (&g)[{lay.nm}], const T* __restrict__ G, "
-      f"const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}]) {{")
-    for p, (l1, l2, l3) in enumerate(paths):
-        n3 = 2 * l3 + 1
-        K = w3j(l1, l2, l3) * math.sqrt(2 * l3 + 1)
-        o("  {")
-        pairs = [(m1, m3) for m1 in range(2 * l1 + 1) for m3 in range(n3) if gterm(p, m1, m3) is not None]
-        for m1, m3 in pairs:
-            o(f"    const T q{m1}_{m3} = x[{xoff[l1] + m1}] * g[{lay.idx(p, m3)}];")
-        terms = [f"G[{gterm(p, m1, m3)}] * q{m1}_{m3}" for m1, m3 in pairs]
-        o(f"    dw[{p}] = {' + '.join(terms)};")
-        for m2 in range(2 * l2 + 1):
-            terms = [f"{lit(float(K[m1, m2, m3]))} * q{m1}_{m3}"
-                     for m1, m3 in pairs if K[m1, m2, m3] != 0.0]
-            if terms:
-                o(f"    dY[{l2 * l2 + m2}] += w[{p}] * ({' + '.join(terms)});")
+    # forward per group: acc[local idx] += w[p_local] * sum_m1 x[m1] G[m1][m3]; G points at the edge's full row
+    for g, ls in enumerate(groups):
+        ps = [p for p, pt in enumerate(paths) if pt[2] in ls]
+        o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd{g}(const T (&x)[{nx}], const T* __restrict__ G, "
+          f"const T (&w)[{grp_np[g]}], T (&acc)[{grp_nm[g]}]) {{")
+        loaded = set()
+        for p in ps:
+            l1, l2, l3 = paths[p]
+            ids = [gi[(p, m1, m3)] for m3 in range(2 * l3 + 1) for m1 in range(2 * l1 + 1) if (p, m1, m3) in gi]
+            for line in load_G(min(ids), max(ids) + 1, loaded):
+                o(line)
+            for m3 in range(2 * l3 + 1):
+                ts = [f"x[{xoff[l1] + m1}] * G_{gi[(p, m1, m3)]}" for m1 in range(2 * l1 + 1) if (p, m1, m3) in gi]
+                if ts:
+                    o(f"    acc[{lay.idx(p, m3) - grp_m0[g]}] += w[{p - grp_p0[g]}] * ({' + '.join(ts)});")
         o("  }")
-    o("}")
-    o(f"struct TPX_{tag} : TP_{tag} {{")
-    o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd(const T (&x)[{nx}], const T* __restrict__ G, const T (&w)[{P}], "
-      f"T (&acc)[{lay.nm}]) {{ tp_fwd_{tag}<T>(x, G, w, acc); }}")
-    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwdx(const T (&g)[{lay.nm}], const T* __restrict__ G, const T (&w)[{P}], "
-      f"T (&dx)[{nx}]) {{ tp_bwdx_{tag}<T>(g, G, w, dx); }}")
-    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwdw(const T (&x)[{nx}], const T (&g)[{lay.nm}], const T* __restrict__ G, "
-      f"const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}]) {{ tp_bwdw_{tag}<T>(x, g, G, w, dw, dY); }}")
-    o(f"  static TACE_D TACE_INLINE const short* gstart() {{ return tp_{tag}_gstart; }}")
-    o(f"  static TACE_D TACE_INLINE const unsigned char* gy() {{ return tp_{tag}_gy; }}")
-    o(f"  static TACE_D TACE_INLINE const double* gc() {{ return tp_{tag}_gc; }}")
+
+    if ngrp == 1:  # single group: fwd1 is never launched, but must exist for the kernel template
+        o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd1(const T (&x)[{nx}], const T* __restrict__ G, "
+          f"const T (&w)[{grp_np[0]}], T (&acc)[{grp_nm[0]}]) {{ fwd0<T>(x, G, w, acc); }}")
+
+    # backward of one (edge, channel): g is read from gs[k * gstride] (the target's message gradient, channel c)
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd(const T (&x)[{nx}], const T* __restrict__ gs, int gstride, "
+      f"const T* __restrict__ G, const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}], T (&dx)[{nx}]) {{")
+    for p, (l1, l2, l3) in enumerate(paths):
+        K = Ks[p]
+        n3 = 2 * l3 + 1
+        pairs = [(m1, m3) for m3 in range(n3) for m1 in range(2 * l1 + 1) if (p, m1, m3) in gi]
+        ids = [gi[(p, m1, m3)] for m1, m3 in pairs]
+        o("  {")
+        for line in load_G(min(ids), max(ids) + 1, set()):
+            o(line)
+        for m3 in range(n3):
+            o(f"    const T g{m3} = gs[{lay.idx(p, m3)} * gstride];")
+        for m1, m3 in pairs:
+            o(f"    const T q{m1}_{m3} = x[{xoff[l1] + m1}] * g{m3};")
+        o(f"    dw[{p}] = {' + '.join(f'G_{gi[(p, m1, m3)]} * q{m1}_{m3}' for m1, m3 in pairs)};")
+        for m2 in range(2 * l2 + 1):
+            ts = [f"{lit(float(K[m1, m2, m3]))} * q{m1}_{m3}" for m1, m3 in pairs if K[m1, m2, m3] != 0.0]
+            if ts:
+                o(f"    dY[{l2 * l2 + m2}] += w[{p}] * ({' + '.join(ts)});")
+        if not scalar_src:
+            for m1 in range(2 * l1 + 1):
+                ts = [f"G_{gi[(p, m1, m3)]} * g{m3}" for m3 in range(n3) if (p, m1, m3) in gi]
+                if ts:
+                    o(f"    dx[{xoff[l1] + m1}] += w[{p}] * ({' + '.join(ts)});")
+        o("  }")
+    o("  }")
     o("};")
-    return dict(tag=tag, P=P, nm=lay.nm, ng=ng, nnz=nnz_total)
+    return dict(tag=tag, P=P, nm=lay.nm, ng=ng, nnz=nnz_total, groups=groups, gcnt=grp_gcnt, nmg=grp_nm)
 
 
 # ------------------------------------------------------------- product basis code

@@ -15,24 +15,24 @@ namespace tace {
 template <typename T>
 struct TPArgs {
   int L, scalar_src, C;
-  int n_seg;          // number of targets (or sources) = thread blocks
-  const int* rowptr;  // [n_seg+1] CSR over the segment's edges
-  const int* perm;    // source pass: CSR slot -> edge id (target-sorted numbering); else nullptr
-  const int* e_src;   // [E] source atom of each edge (target-sorted numbering)
-  const int* e_dst;   // [E] target atom
-  const T* Y;         // [E][D] angular features
+  int n_seg;          // number of target atoms = thread blocks (per output group)
+  const int* rowptr;  // [n_seg+1] CSR over the edges of each target (edges are target-sorted)
+  const int* e_src;   // [E] source atom of each edge
+  const T* G;         // [E][NG] channel-independent coupling of each edge (TPX::build_G)
   const T* W;         // [E][NP*C] per-edge path weights
   const T* x;         // [N][NX][C] source features
   T* M;               // forward output [n_seg][NM][C]
-  const T* gM;        // [n_targets][NM][C] gradient of the messages
-  T* dW;              // edge pass output [E][NP*C] (may alias W)
-  T* dY;              // edge pass output [E][D]
+  const T* gM;        // [n_seg][NM][C] gradient of the messages
+  T* dW;              // backward output [E][NP*C] (may alias W)
+  T* dY;              // backward output [E][D]
   int accumulate_dY;  // add into dY instead of overwriting
-  T* dx;              // source pass output [n_seg][NX][C]
+  T* dxe;             // backward output [E][NX][C]: per-edge gradient of the source features (full source only)
 };
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
-template <typename T> cudaError_t launch_tp_bwd_edge(const TPArgs<T>& a, cudaStream_t s);
-template <typename T> cudaError_t launch_tp_bwd_src(const TPArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_tp_bwd(const TPArgs<T>& a, cudaStream_t s);
+// gx[b] = sum of dxe over the edges whose source is b (edges listed by perm within rowptr_src segments)
+template <typename T> cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx,
+                                                          int n_atoms, int row_len, cudaStream_t s);
 
 // ---- per-atom element-wise kernels (node_kernels.cu) -----------------------------------------
 // x0[n][c] = table[species[n]][c]
@@ -89,6 +89,8 @@ struct EdgeArgs {
   MlpWeights<T> mlp[kMaxLayers];
   T* vec;                // [E][3] edge vectors (target-sorted order)
   T* Y;                  // [E][D]
+  T* G_scalar;           // [E][NG] coupling rows for the scalar-source layer (TPX_L*_S::build_G)
+  T* G_full;             // [E][NG] coupling rows for the full-source layers, or nullptr
   T* H3[kMaxLayers];     // [E][64] last hidden activation of each layer's radial MLP
   // backward
   const T* dH3[kMaxLayers];

@@ -24,6 +24,21 @@
 
 namespace tace {
 
+// Four consecutive table entries; under nvcc one (fp32) or two (fp64) 16-byte loads, p 16-byte aligned.
+#if defined(__CUDACC__)
+TACE_HD TACE_INLINE void ld4(const float* p, float& a, float& b, float& c, float& d) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  a = v.x; b = v.y; c = v.z; d = v.w;
+}
+TACE_HD TACE_INLINE void ld4(const double* p, double& a, double& b, double& c, double& d) {
+  const double2 u = *reinterpret_cast<const double2*>(p), v = *reinterpret_cast<const double2*>(p + 2);
+  a = u.x; b = u.y; c = v.x; d = v.y;
+}
+#else
+template <typename T>
+inline void ld4(const T* p, T& a, T& b, T& c, T& d) { a = p[0]; b = p[1]; c = p[2]; d = p[3]; }
+#endif
+
 template <typename T>
 TACE_HD TACE_INLINE T sigmoid_(T x) { return T(1) / (T(1) + exp(-x)); }
 template <>

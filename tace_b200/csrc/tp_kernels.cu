@@ -1,12 +1,17 @@
-// Interaction tensor-product kernels: forward message passing and its two backward passes.
+// Interaction tensor-product kernels: forward message passing and its backward pass.
 //
-// One thread block per target atom (forward, edge-gradient pass) or per source atom
-// (source-gradient pass), one thread per channel.  The block walks the atom's edge segment
-// in batches of kEdgeBatch edges: the channel-independent coupling G_e = K . Y_e of each edge
-// is built cooperatively in shared memory, then every thread contracts its own channel with
-// fully unrolled generated code (tp_gen.cuh), keeping the per-atom sums in registers.
-// The edge lists are sorted, so the sums are segmented reductions: no atomics, and results
-// are bit-reproducible from run to run.
+// One thread block per target atom, one thread per channel.  The channel-independent coupling
+// G_e = K . Y_e of every edge is computed once per evaluation (edge_kernels.cu) and stored as a
+// row of NG values; a block copies the rows of a batch of its edges into shared memory with
+// 128-bit loads, then every thread contracts its own channel with fully unrolled generated
+// code (tp_gen.cuh) that reads G four entries at a time.
+//
+// Forward: the output ranks are split into (at most) two groups, one block per (target, group),
+// which halves the accumulator registers and doubles the resident warps.
+// Backward: one pass per target produces, for every edge, the gradient of the per-edge weights
+// (in place over W), of the angular features (reduced over channels with warp shuffles) and of
+// the source features (one row per edge, summed per source atom by launch_segment_sum_rows).
+// Edge lists are sorted, so every sum is a segmented reduction: no atomics, bit-reproducible.
 #include "kernels.h"
 #include "tp_gen.cuh"
 
@@ -14,97 +19,92 @@ namespace tace {
 
 constexpr int kEdgeBatch = 8;
 
-template <typename T, typename TP>
-__device__ __forceinline__ void build_G_batch(const T* __restrict__ Y, const int* edge_ids, int nb, T* Gs) {
-  // Gs[e][gi] = sum_k gc[k] * Y[edge e][gy[k]]
-  const short* gs = TP::gstart();
-  const unsigned char* gy = TP::gy();
-  const double* gc = TP::gc();
-  for (int idx = threadIdx.x; idx < nb * TP::NG; idx += blockDim.x) {
-    const int e = idx / TP::NG, gi = idx - e * TP::NG;
-    const T* Ye = Y + (long long)edge_ids[e] * TP::D;
-    T s = T(0);
-    for (int k = gs[gi]; k < gs[gi + 1]; ++k) s += T(gc[k]) * Ye[gy[k]];
-    Gs[e * TP::NG + gi] = s;
+// copy `count` (multiple of 4) entries starting at `offset` of the G rows of edges [e0, e0 + nb)
+template <typename T, int NG>
+__device__ __forceinline__ void stage_G(const T* __restrict__ G, int e0, int nb, int offset, int count, T* Gs) {
+  constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
+  const int per_edge = count / V;
+  for (int idx = threadIdx.x; idx < nb * per_edge; idx += blockDim.x) {
+    const int e = idx / per_edge, v = idx - e * per_edge;
+    const int4 val = *reinterpret_cast<const int4*>(G + (long long)(e0 + e) * NG + offset + v * V);
+    *reinterpret_cast<int4*>(Gs + e * NG + offset + v * V) = val;
   }
 }
 
-template <typename T, typename TP>
+template <typename T, typename TP, int GRP>
 __global__ void __launch_bounds__(256) tp_fwd_kernel(const TPArgs<T> a) {
+  constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
+  constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
+  constexpr int GOFF = GRP == 0 ? TP::GOFF0 : TP::GOFF1, GCNT = GRP == 0 ? TP::GCNT0 : TP::GCNT1;
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
-  __shared__ T Gs[kEdgeBatch * TP::NG];
-  __shared__ int eid[kEdgeBatch];
+  __shared__ __align__(16) T Gs[kEdgeBatch * TP::NG];
   __shared__ int esrc[kEdgeBatch];
-  T acc[TP::NM];
+  T acc[NMG];
 #pragma unroll
-  for (int k = 0; k < TP::NM; ++k) acc[k] = T(0);
+  for (int k = 0; k < NMG; ++k) acc[k] = T(0);
   const int beg = a.rowptr[i], end = a.rowptr[i + 1];
   for (int e0 = beg; e0 < end; e0 += kEdgeBatch) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
-    if (threadIdx.x < nb) {
-      eid[threadIdx.x] = e0 + threadIdx.x;
-      esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
-    }
-    __syncthreads();
-    build_G_batch<T, TP>(a.Y, eid, nb, Gs);
+    if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
+    stage_G<T, TP::NG>(a.G, e0, nb, GOFF, GCNT, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
       const long long s = esrc[e];
-      T xv[TP::NX], wv[TP::NP];
+      T xv[TP::NX], wv[NPG];
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) xv[k] = a.x[(s * TP::NX + k) * C + c];
-      const T* We = a.W + (long long)(e0 + e) * TP::NP * C;
+      const T* We = a.W + ((long long)(e0 + e) * TP::NP + P0) * C;
 #pragma unroll
-      for (int p = 0; p < TP::NP; ++p) wv[p] = We[p * C + c];
-      TP::template fwd<T>(xv, Gs + e * TP::NG, wv, acc);
+      for (int p = 0; p < NPG; ++p) wv[p] = We[p * C + c];
+      if constexpr (GRP == 0) TP::template fwd0<T>(xv, Gs + e * TP::NG, wv, acc);
+      else TP::template fwd1<T>(xv, Gs + e * TP::NG, wv, acc);
     }
   }
-  T* Mi = a.M + (long long)i * TP::NM * C;
+  T* Mi = a.M + ((long long)i * TP::NM + M0) * C;
 #pragma unroll
-  for (int k = 0; k < TP::NM; ++k) Mi[k * C + c] = acc[k];
+  for (int k = 0; k < NMG; ++k) Mi[k * C + c] = acc[k];
 }
 
-// Edge-gradient pass: dW[e,p,c] and dY[e,:] for every edge of target atom i.
+// Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
 template <typename T, typename TP>
-__global__ void __launch_bounds__(256) tp_bwd_edge_kernel(const TPArgs<T> a) {
+__global__ void __launch_bounds__(256) tp_bwd_kernel(const TPArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ T Gs[kEdgeBatch * TP::NG];
-  __shared__ T red[kEdgeBatch * 8 * TP::D];  // [edge][warp][D], up to 8 warps
-  __shared__ int eid[kEdgeBatch];
+  T* gMs = reinterpret_cast<T*>(smem_raw);          // [NM][C]
+  T* Gs = gMs + TP::NM * C;                          // [kEdgeBatch][NG]
+  T* red = Gs + kEdgeBatch * TP::NG;                 // [kEdgeBatch][8 warps][D]
   __shared__ int esrc[kEdgeBatch];
-  T gv[TP::NM];
   const T* gMi = a.gM + (long long)i * TP::NM * C;
-#pragma unroll
-  for (int k = 0; k < TP::NM; ++k) gv[k] = gMi[k * C + c];
+  for (int k = 0; k < TP::NM; ++k) gMs[k * C + c] = gMi[k * C + c];  // each thread later reads only its own column
   const int beg = a.rowptr[i], end = a.rowptr[i + 1];
   for (int e0 = beg; e0 < end; e0 += kEdgeBatch) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
-    if (threadIdx.x < nb) {
-      eid[threadIdx.x] = e0 + threadIdx.x;
-      esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
-    }
-    __syncthreads();
-    build_G_batch<T, TP>(a.Y, eid, nb, Gs);
+    if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
+    stage_G<T, TP::NG>(a.G, e0, nb, 0, TP::NG, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
       const long long s = esrc[e];
-      T xv[TP::NX], wv[TP::NP], dw[TP::NP], dYp[TP::D];
+      T xv[TP::NX], wv[TP::NP], dw[TP::NP], dYp[TP::D], dx[TP::NX];
 #pragma unroll
-      for (int k = 0; k < TP::NX; ++k) xv[k] = a.x[(s * TP::NX + k) * C + c];
+      for (int k = 0; k < TP::NX; ++k) { xv[k] = a.x[(s * TP::NX + k) * C + c]; dx[k] = T(0); }
       const long long wbase = (long long)(e0 + e) * TP::NP * C;
 #pragma unroll
       for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
 #pragma unroll
       for (int k = 0; k < TP::D; ++k) dYp[k] = T(0);
-      TP::template bwdw<T>(xv, gv, Gs + e * TP::NG, wv, dw, dYp);
+      TP::template bwd<T>(xv, gMs + c, C, Gs + e * TP::NG, wv, dw, dYp, dx);
 #pragma unroll
       for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
-      // reduce dY over the channels of this warp
+      if (a.dxe) {
+        T* out = a.dxe + (long long)(e0 + e) * TP::NX * C;
 #pragma unroll
-      for (int k = 0; k < TP::D; ++k) {
+        for (int k = 0; k < TP::NX; ++k) out[k * C + c] = dx[k];
+      }
+#pragma unroll
+      for (int k = 0; k < TP::D; ++k) {  // reduce dY over the channels of this warp
         T v = dYp[k];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
@@ -122,67 +122,63 @@ __global__ void __launch_bounds__(256) tp_bwd_edge_kernel(const TPArgs<T> a) {
   }
 }
 
-// Source-gradient pass: dx[b] = sum over edges whose source is b.
-template <typename T, typename TP>
-__global__ void __launch_bounds__(256) tp_bwd_src_kernel(const TPArgs<T> a) {
-  const int b = blockIdx.x, c = threadIdx.x, C = a.C;
-  __shared__ T Gs[kEdgeBatch * TP::NG];
-  __shared__ int eid[kEdgeBatch];
-  __shared__ int edst[kEdgeBatch];
-  T dx[TP::NX];
-#pragma unroll
-  for (int k = 0; k < TP::NX; ++k) dx[k] = T(0);
-  const int beg = a.rowptr[b], end = a.rowptr[b + 1];
-  for (int k0 = beg; k0 < end; k0 += kEdgeBatch) {
-    const int nb = min(kEdgeBatch, end - k0);
-    __syncthreads();
-    if (threadIdx.x < nb) {
-      const int e = a.perm[k0 + threadIdx.x];
-      eid[threadIdx.x] = e;
-      edst[threadIdx.x] = a.e_dst[e];
-    }
-    __syncthreads();
-    build_G_batch<T, TP>(a.Y, eid, nb, Gs);
-    __syncthreads();
-    for (int e = 0; e < nb; ++e) {
-      const long long d = edst[e];
-      T gv[TP::NM], wv[TP::NP];
-      const T* gMd = a.gM + d * TP::NM * C;
-#pragma unroll
-      for (int k = 0; k < TP::NM; ++k) gv[k] = gMd[k * C + c];
-      const T* We = a.W + (long long)eid[e] * TP::NP * C;
-#pragma unroll
-      for (int p = 0; p < TP::NP; ++p) wv[p] = We[p * C + c];
-      TP::template bwdx<T>(gv, Gs + e * TP::NG, wv, dx);
-    }
+template <typename T>
+__global__ void segment_sum_rows_kernel(const T* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
+                                        T* __restrict__ gx, int row_len) {
+  const int b = blockIdx.x;
+  const int beg = rowptr[b], end = rowptr[b + 1];
+  for (int k = threadIdx.x; k < row_len; k += blockDim.x) {
+    T acc = T(0);
+    for (int j = beg; j < end; ++j) acc += dxe[(long long)perm[j] * row_len + k];
+    gx[(long long)b * row_len + k] = acc;
   }
-  T* out = a.dx + (long long)b * TP::NX * C;
-#pragma unroll
-  for (int k = 0; k < TP::NX; ++k) out[k * C + c] = dx[k];
+}
+template <typename T>
+cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx, int n_atoms, int row_len,
+                                    cudaStream_t s) {
+  if (n_atoms <= 0) return cudaSuccess;
+  segment_sum_rows_kernel<T><<<n_atoms, 256, 0, s>>>(dxe, rowptr_src, perm_src, gx, row_len);
+  return cudaGetLastError();
 }
 
-#define TACE_TP_DISPATCH(KERNEL)                                                         \
-  if (a.n_seg <= 0) return cudaSuccess;                                                  \
-  if (a.C > 256 || (a.C & 31)) return cudaErrorInvalidValue;                             \
-  const dim3 grid(a.n_seg), block(a.C);                                                  \
-  if (a.L == 1 && a.scalar_src) KERNEL<T, TPX_L1_S><<<grid, block, 0, s>>>(a);           \
-  else if (a.L == 1) KERNEL<T, TPX_L1_F><<<grid, block, 0, s>>>(a);                      \
-  else if (a.L == 2 && a.scalar_src) KERNEL<T, TPX_L2_S><<<grid, block, 0, s>>>(a);      \
-  else if (a.L == 2) KERNEL<T, TPX_L2_F><<<grid, block, 0, s>>>(a);                      \
-  else if (a.L == 3 && a.scalar_src) KERNEL<T, TPX_L3_S><<<grid, block, 0, s>>>(a);      \
-  else if (a.L == 3) KERNEL<T, TPX_L3_F><<<grid, block, 0, s>>>(a);                      \
-  else return cudaErrorInvalidValue;                                                     \
+template <typename T, typename TP>
+cudaError_t launch_fwd_t(const TPArgs<T>& a, cudaStream_t s) {
+  tp_fwd_kernel<T, TP, 0><<<a.n_seg, a.C, 0, s>>>(a);
+  if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1><<<a.n_seg, a.C, 0, s>>>(a);
   return cudaGetLastError();
+}
+template <typename T, typename TP>
+cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
+  const size_t smem = sizeof(T) * ((size_t)TP::NM * a.C + kEdgeBatch * TP::NG + kEdgeBatch * 8 * TP::D);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  tp_bwd_kernel<T, TP><<<a.n_seg, a.C, smem, s>>>(a);
+  return cudaGetLastError();
+}
 
-template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(tp_fwd_kernel) }
-template <typename T> cudaError_t launch_tp_bwd_edge(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(tp_bwd_edge_kernel) }
-template <typename T> cudaError_t launch_tp_bwd_src(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(tp_bwd_src_kernel) }
+#define TACE_TP_DISPATCH(FN)                                              \
+  if (a.n_seg <= 0) return cudaSuccess;                                   \
+  if (a.C > 256 || (a.C & 31)) return cudaErrorInvalidValue;              \
+  if (a.L == 1 && a.scalar_src) return FN<T, TPX_L1_S>(a, s);             \
+  if (a.L == 1) return FN<T, TPX_L1_F>(a, s);                             \
+  if (a.L == 2 && a.scalar_src) return FN<T, TPX_L2_S>(a, s);             \
+  if (a.L == 2) return FN<T, TPX_L2_F>(a, s);                             \
+  if (a.L == 3 && a.scalar_src) return FN<T, TPX_L3_S>(a, s);             \
+  if (a.L == 3) return FN<T, TPX_L3_F>(a, s);                             \
+  return cudaErrorInvalidValue;
+
+template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(launch_fwd_t) }
+template <typename T> cudaError_t launch_tp_bwd(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(launch_bwd_t) }
 
 template cudaError_t launch_tp_fwd<float>(const TPArgs<float>&, cudaStream_t);
 template cudaError_t launch_tp_fwd<double>(const TPArgs<double>&, cudaStream_t);
-template cudaError_t launch_tp_bwd_edge<float>(const TPArgs<float>&, cudaStream_t);
-template cudaError_t launch_tp_bwd_edge<double>(const TPArgs<double>&, cudaStream_t);
-template cudaError_t launch_tp_bwd_src<float>(const TPArgs<float>&, cudaStream_t);
-template cudaError_t launch_tp_bwd_src<double>(const TPArgs<double>&, cudaStream_t);
+template cudaError_t launch_tp_bwd<float>(const TPArgs<float>&, cudaStream_t);
+template cudaError_t launch_tp_bwd<double>(const TPArgs<double>&, cudaStream_t);
+template cudaError_t launch_segment_sum_rows<float>(const float*, const int*, const int*, float*, int, int, cudaStream_t);
+template cudaError_t launch_segment_sum_rows<double>(const double*, const int*, const int*, double*, int, int, cudaStream_t);
 
 }  // namespace tace

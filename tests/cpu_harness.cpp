@@ -7,53 +7,47 @@
 
 using namespace tace;
 
-template <typename T>
-static void build_G(const short* gs, const unsigned char* gy, const double* gc, int ng, const T* Y, T* G) {
-  for (int i = 0; i < ng; ++i) {
-    T s = 0;
-    for (int k = gs[i]; k < gs[i + 1]; ++k) s += T(gc[k]) * Y[gy[k]];
-    G[i] = s;
+#define TP_CASE(TAG)                                                                              \
+  {                                                                                               \
+    using TP = TPX_##TAG;                                                                         \
+    double YY[TP::D], xx[TP::NX], ww[TP::NP];                                                     \
+    alignas(16) double G[TP::NG];                                                                 \
+    memcpy(YY, Y, sizeof YY); memcpy(xx, x, sizeof xx); memcpy(ww, w, sizeof ww);                 \
+    TP::build_G<double>(YY, G);                                                                   \
+    if (mode == 0) {                                                                              \
+      double a0[TP::NMG0], w0[TP::NPG0];                                                          \
+      memset(a0, 0, sizeof a0); memcpy(w0, ww + TP::P00, sizeof w0);                              \
+      TP::fwd0<double>(xx, G, w0, a0); memcpy(out0 + TP::M00, a0, sizeof a0);                     \
+      if (TP::NGRP > 1) {                                                                         \
+        double a1[TP::NMG1], w1[TP::NPG1];                                                        \
+        memset(a1, 0, sizeof a1); memcpy(w1, ww + TP::P01, sizeof w1);                            \
+        TP::fwd1<double>(xx, G, w1, a1); memcpy(out0 + TP::M01, a1, sizeof a1);                   \
+      }                                                                                           \
+    } else {                                                                                      \
+      double dw[TP::NP], dY[TP::D], dx[TP::NX];                                                   \
+      memset(dY, 0, sizeof dY); memset(dx, 0, sizeof dx);                                         \
+      TP::bwd<double>(xx, g, 1, G, ww, dw, dY, dx);                                               \
+      memcpy(out0, dw, sizeof dw); memcpy(out1, dY, sizeof dY); memcpy(out2, dx, sizeof dx);      \
+    }                                                                                             \
+    return 0;                                                                                     \
   }
-}
-
-#define TP_CASE(TAG)                                                                            \
-  if (mode == 0) {                                                                              \
-    double xx[TP_##TAG::NX], ww[TP_##TAG::NP], aa[TP_##TAG::NM], G[TP_##TAG::NG];               \
-    memcpy(xx, x, sizeof xx); memcpy(ww, w, sizeof ww); memset(aa, 0, sizeof aa);               \
-    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
-    tp_fwd_##TAG<double>(xx, G, ww, aa); memcpy(out0, aa, sizeof aa);                           \
-  } else if (mode == 1) {                                                                       \
-    double gg[TP_##TAG::NM], ww[TP_##TAG::NP], dx[TP_##TAG::NX], G[TP_##TAG::NG];               \
-    memcpy(gg, g, sizeof gg); memcpy(ww, w, sizeof ww); memset(dx, 0, sizeof dx);               \
-    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
-    tp_bwdx_##TAG<double>(gg, G, ww, dx); memcpy(out0, dx, sizeof dx);                          \
-  } else {                                                                                      \
-    double xx[TP_##TAG::NX], gg[TP_##TAG::NM], ww[TP_##TAG::NP], dw[TP_##TAG::NP];              \
-    double dY[TP_##TAG::D], G[TP_##TAG::NG];                                                    \
-    memcpy(xx, x, sizeof xx); memcpy(gg, g, sizeof gg); memcpy(ww, w, sizeof ww);               \
-    memset(dY, 0, sizeof dY);                                                                   \
-    build_G(tp_##TAG##_gstart, tp_##TAG##_gy, tp_##TAG##_gc, TP_##TAG::NG, Y, G);               \
-    tp_bwdw_##TAG<double>(xx, gg, G, ww, dw, dY);                                               \
-    memcpy(out0, dw, sizeof dw); memcpy(out1, dY, sizeof dY);                                   \
-  }                                                                                             \
-  return 0;
 
 extern "C" {
 
-// mode 0: forward (out0 = message components); 1: d/dx (out0); 2: d/dw (out0) and d/dY (out1)
+// mode 0: forward (out0 = message components); mode 1: out0 = d/dw, out1 = d/dY, out2 = d/dx
 int h_tp(int L, int scalar_src, int mode, const double* x, const double* Y, const double* w, const double* g,
-         double* out0, double* out1) {
-  if (L == 1 && scalar_src) { TP_CASE(L1_S) }
-  if (L == 1 && !scalar_src) { TP_CASE(L1_F) }
-  if (L == 2 && scalar_src) { TP_CASE(L2_S) }
-  if (L == 2 && !scalar_src) { TP_CASE(L2_F) }
-  if (L == 3 && scalar_src) { TP_CASE(L3_S) }
-  if (L == 3 && !scalar_src) { TP_CASE(L3_F) }
+         double* out0, double* out1, double* out2) {
+  if (L == 1 && scalar_src) TP_CASE(L1_S)
+  if (L == 1 && !scalar_src) TP_CASE(L1_F)
+  if (L == 2 && scalar_src) TP_CASE(L2_S)
+  if (L == 2 && !scalar_src) TP_CASE(L2_F)
+  if (L == 3 && scalar_src) TP_CASE(L3_S)
+  if (L == 3 && !scalar_src) TP_CASE(L3_F)
   return -1;
 }
 
 int h_tp_dims(int L, int scalar_src, int* dims) {
-#define DIMS(TAG) { dims[0] = TP_##TAG::NP; dims[1] = TP_##TAG::NX; dims[2] = TP_##TAG::NM; dims[3] = TP_##TAG::D; return 0; }
+#define DIMS(TAG) { dims[0] = TPX_##TAG::NP; dims[1] = TPX_##TAG::NX; dims[2] = TPX_##TAG::NM; dims[3] = TPX_##TAG::D; return 0; }
   if (L == 1 && scalar_src) DIMS(L1_S)
   if (L == 1 && !scalar_src) DIMS(L1_F)
   if (L == 2 && scalar_src) DIMS(L2_S)

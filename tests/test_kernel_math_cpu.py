@@ -59,24 +59,21 @@ def test_interaction_tp_matches_oracle(cpu_harness, L, scalar_src):
     # oracle output: per path p a [1, 2l3+1] block, in path order
     perm = [i for blk in idx for i in blk]
     out = np.zeros(NM)
-    z = np.zeros(max(NM, D))
-    cpu_harness.h_tp(L, int(scalar_src), 0, ptr(x.detach().numpy()), ptr(Y.detach().numpy()), ptr(w.detach().numpy()),
-                     ptr(z), ptr(out), ptr(z))
+    z = np.zeros(max(NM, D, NX))
+    xn, Yn, wn = x.detach().numpy(), Y.detach().numpy(), w.detach().numpy()
+    cpu_harness.h_tp(L, int(scalar_src), 0, ptr(xn), ptr(Yn), ptr(wn), ptr(z), ptr(out), ptr(z), ptr(z))
     np.testing.assert_allclose(out[perm], ref.detach().numpy(), rtol=0, atol=1e-13)
     # backward against autograd
     g_ref = torch.randn(NM, dtype=torch.float64)  # gradient wrt oracle-ordered output
     dx_ref, dY_ref, dw_ref = torch.autograd.grad(ref, [x, Y, w], g_ref)
     g_mine = np.zeros(NM)
     g_mine[perm] = g_ref.numpy()
-    dx = np.zeros(NX)
-    cpu_harness.h_tp(L, int(scalar_src), 1, ptr(z), ptr(Y.detach().numpy()), ptr(w.detach().numpy()), ptr(g_mine),
-                     ptr(dx), ptr(z))
-    np.testing.assert_allclose(dx, dx_ref.numpy(), rtol=0, atol=1e-12)
-    dw, dY = np.zeros(NP), np.zeros(D)
-    cpu_harness.h_tp(L, int(scalar_src), 2, ptr(x.detach().numpy()), ptr(Y.detach().numpy()), ptr(w.detach().numpy()),
-                     ptr(g_mine), ptr(dw), ptr(dY))
+    dw, dY, dx = np.zeros(NP), np.zeros(D), np.zeros(NX)
+    cpu_harness.h_tp(L, int(scalar_src), 1, ptr(xn), ptr(Yn), ptr(wn), ptr(g_mine), ptr(dw), ptr(dY), ptr(dx))
     np.testing.assert_allclose(dw, dw_ref.numpy(), rtol=0, atol=1e-12)
     np.testing.assert_allclose(dY, dY_ref.numpy(), rtol=0, atol=1e-12)
+    if not scalar_src:  # the scalar-source layer never needs the source gradient
+        np.testing.assert_allclose(dx, dx_ref.numpy(), rtol=0, atol=1e-12)
 
 
 @pytest.mark.parametrize("L", [1, 2, 3])
