@@ -119,6 +119,19 @@ int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_loca
 int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace,
                  size_t workspace_bytes, tace_stream_t stream);
 
+/* Ghost-row exchange for edge-vector mode with n_local < n_atoms and more than one layer.  Stands
+ * behind lmp_data.forward_exchange / reverse_exchange as used by GhostExchange
+ * (tace/models/lammps.py:82-129): before every layer after the first, tace_forward synchronises its
+ * stream and calls fn(user, 0, in, out, n_atoms, vec_len): `in` holds the per-atom source features
+ * [n_atoms, vec_len] (model dtype, device memory) with ghost rows zero, and the callback must fill
+ * `out` with the same rows where every ghost row is a copy of its owner's row.  In the backward pass it
+ * calls fn(user, 1, in, out, n_atoms, vec_len) with the gradient rows; the callback must write to `out`
+ * the local rows plus the sum of the rows of their ghosts.  Both buffers belong to the workspace; the
+ * callback must finish its device work (or order it on the stream of tace_forward) before returning.
+ * Return 0 on success. */
+typedef int (*tace_exchange_fn)(void* user, int reverse, const void* in, void* out, int64_t n_rows, int32_t vec_len);
+int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user);
+
 /* Instrumentation (no counterpart in the reference, which has no tracing on this path):
  * tace_launch_count returns the number of this library's kernels enqueued by tace_forward so far
  * (CUB radix-sort launches are not counted).  With profiling enabled, tace_forward records a

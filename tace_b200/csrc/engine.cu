@@ -95,6 +95,8 @@ struct ModelBase {
 
   // kernel-launch counter and optional per-phase CUDA-event timing
   long long launches = 0;
+  tace_exchange_fn exchange_fn = nullptr;  // ghost-row exchange between layers (edge-vector mode)
+  void* exchange_user = nullptr;
   int* dev_error = nullptr;  // device word written by kernels whose bounded waits expire
   bool profile = false;
   std::vector<std::string> phase_names;
@@ -256,7 +258,7 @@ struct Model : ModelBase {
 
   // ---- workspace ---------------------------------------------------------------------------
   struct LayerBufs {
-    T *h_in, *x, *W, *H3, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
+    T *h_in, *x, *xx, *gxx, *W, *H3, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
   };
   struct Bufs {
@@ -287,6 +289,9 @@ struct Model : ModelBase {
       lb.gh_in = prev_gh;
       lb.x = ar.take<T>((size_t)N * p.tp.NX * C);
       lb.gx = p.scalar_src ? nullptr : ar.take<T>((size_t)N * p.tp.NX * C);
+      const bool ghosts = (N != NL) && !p.scalar_src;  // exchanged copies of x and of its gradient
+      lb.xx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
+      lb.gxx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.H3 = ar.take<T>((size_t)E * kHidden);
       lb.W = ar.take<T>((size_t)E * p.tp.NP * C);
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
@@ -360,7 +365,8 @@ struct Model : ModelBase {
       return TACE_ERR_INVALID_ARGUMENT;
     const bool vec_mode = bt->edge_vector != nullptr;
     if (!vec_mode && E > 0 && (!bt->positions || !bt->lattice || !bt->edge_shifts)) return TACE_ERR_INVALID_ARGUMENT;
-    if (NL != N && NL_ > 1) return TACE_ERR_UNSUPPORTED_CONFIG;  // ghost atoms need a feature exchange between layers
+    // ghost atoms need a feature exchange between layers (tace_set_exchange)
+    if (NL != N && NL_ > 1 && (!exchange_fn || !vec_mode)) return TACE_ERR_UNSUPPORTED_CONFIG;
     if ((reinterpret_cast<uintptr_t>(ws) & 255) != 0) return TACE_ERR_INVALID_ARGUMENT;
     Arena ar; ar.base = static_cast<unsigned char*>(ws);
     Bufs b;
@@ -417,12 +423,22 @@ struct Model : ModelBase {
       const std::string pre = "t" + std::to_string(t) + ".";
       const std::string ts = std::to_string(t);
       PH(("t" + ts + ".fwd.linear_up").c_str());
-      {  // linear_up on every atom (ghosts included: they are message sources)
-        GemmBatch<T> gb = plain_batch(N);
+      const long long n_up = p.scalar_src ? N : NL;  // layer 0 embeds every atom; later layers own only local rows
+      {  // linear_up
+        GemmBatch<T> gb = plain_batch(n_up);
         for (int l : p.in_ls)
           add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "up.l" + std::to_string(l)), C,
                       lb.x + (long long)l * l * C, (long long)p.tp.NX * C, C, l == 0 ? w(pre + "up.b") : nullptr, 0);
-        CKL(launch_gemm(gb, N, s));
+        CKL(launch_gemm(gb, n_up, s));
+      }
+      const T* x_src = lb.x;
+      if (lb.xx) {
+        // Ghost rows of x are copies of rows owned elsewhere: zero them, let the caller's exchange fill
+        // them (lmp_data.forward_exchange in the reference, tace/models/lammps.py:82-129).
+        CKL(launch_fill_zero(lb.x + NL * p.tp.NX * C, (N - NL) * p.tp.NX * C, s));
+        if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+        if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
+        x_src = lb.xx;
       }
       PH(("t" + ts + ".fwd.radial_gemm").c_str());
       if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // last radial-MLP layer on tcgen05: W[e, :] = H3[e, :] @ W3
@@ -438,7 +454,7 @@ struct Model : ModelBase {
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
-      ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full; ta.W = lb.W; ta.x = lb.x; ta.M = lb.M;
+      ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full; ta.W = lb.W; ta.x = x_src; ta.M = lb.M;
       CKL(launch_tp_fwd(ta, s));
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
@@ -574,12 +590,16 @@ struct Model : ModelBase {
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full;
-      ta.W = lb.W; ta.x = lb.x; ta.gM = lb.M; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.dW = lb.W; ta.dY = b.dY;
+      ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.dW = lb.W; ta.dY = b.dY;
       ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
       CKL(launch_tp_bwd(ta, s));
       if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
         PH(("t" + ts + ".bwd.src_sum").c_str());
         CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, p.tp.NX * C, s));
+        if (lb.gxx) {  // gradients that landed on ghost rows go back to their owners (reverse_exchange)
+          if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+          if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
+        }
       }
       PH(("t" + ts + ".bwd.radial_gemm").c_str());
       if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // back through the last radial-MLP layer: dH3[e, :] = dW[e, :] @ W3^T
@@ -595,7 +615,7 @@ struct Model : ModelBase {
         PH(("t" + ts + ".bwd.linear_up").c_str());
         GemmBatch<T> gb = plain_batch(NL);
         for (int l : p.in_ls)
-          add_problem(gb, lb.gx + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C, w(pre + "upT.l" + std::to_string(l)),
+          add_problem(gb, (lb.gxx ? lb.gxx : lb.gx) + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C, w(pre + "upT.l" + std::to_string(l)),
                       C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 0);
         CKL(launch_gemm(gb, NL, s));
         if (p.has_res) {
@@ -715,6 +735,12 @@ int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* ou
                  tace_stream_t stream) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   return model->impl->forward(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user) {
+  if (!model) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->exchange_fn = fn;
+  model->impl->exchange_user = user;
+  return TACE_OK;
 }
 int tace_device_error(TaceModel* model, int32_t* code) {
   if (!model || !code) return TACE_ERR_INVALID_ARGUMENT;

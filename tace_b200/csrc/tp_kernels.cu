@@ -32,7 +32,7 @@ __device__ __forceinline__ void stage_G(const T* __restrict__ G, int e0, int nb,
 }
 
 template <typename T, typename TP, int GRP>
-__global__ void __launch_bounds__(256) tp_fwd_kernel(const TPArgs<T> a) {
+__global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
   constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
   constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
   constexpr int GOFF = GRP == 0 ? TP::GOFF0 : TP::GOFF1, GCNT = GRP == 0 ? TP::GCNT0 : TP::GCNT1;
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256) tp_fwd_kernel(const TPArgs<T> a) {
 
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
 template <typename T, typename TP>
-__global__ void __launch_bounds__(256) tp_bwd_kernel(const TPArgs<T> a) {
+__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -388,6 +388,10 @@ class TensorModel(torch.nn.Module):
             res["edge_forces"] = torch.empty(E, 3, dtype=dtype, device=device)
             out.edge_forces = res["edge_forces"].data_ptr()
 
+        exchange_cb = None
+        if self.lmp and n_atoms != n_local and self.readout_fn.num_layers > 1:
+            exchange_cb = self._make_exchange(data["lmp_data"], dtype, device)
+            _lib.check(lib.tace_set_exchange(handle, exchange_cb, None), "tace_set_exchange")
         with torch.cuda.device(device):
             nbytes = ctypes.c_size_t()
             _lib.check(lib.tace_workspace_bytes(handle, n_atoms, n_local, E, n_graphs, ctypes.byref(nbytes)), "tace_workspace_bytes")
@@ -396,7 +400,34 @@ class TensorModel(torch.nn.Module):
             stream = torch.cuda.current_stream(device).cuda_stream
             _lib.check(lib.tace_forward(handle, ctypes.byref(batch), ctypes.byref(out), ws_ptr,
                                         ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
+        if exchange_cb is not None:
+            _lib.check(lib.tace_set_exchange(handle, _lib.EXCHANGE_FN(0), None), "tace_set_exchange")
         return res
+
+    def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device):
+        """ctypes callback handing the workspace rows to ``lmp_data.forward_exchange`` /
+        ``reverse_exchange`` as torch views (tace/models/lammps.py:82-102)."""
+        itemsize = torch.empty((), dtype=dtype).element_size()
+
+        def view(ptr: int, rows: int, cols: int) -> torch.Tensor:
+            ws = self._workspace
+            off = ptr - ws.data_ptr()
+            return ws[off:off + rows * cols * itemsize].view(dtype).view(rows, cols)
+
+        def callback(_user, reverse, in_ptr, out_ptr, n_rows, vec_len):
+            try:
+                src, dst = view(in_ptr, n_rows, vec_len), view(out_ptr, n_rows, vec_len)
+                if reverse:
+                    lmp_data.reverse_exchange(src, dst, vec_len)
+                else:
+                    lmp_data.forward_exchange(src, dst, vec_len)
+                torch.cuda.synchronize(device)
+                return 0
+            except Exception as exc:  # an exception must not cross the C boundary
+                self._exchange_error = exc
+                return 1
+
+        return _lib.EXCHANGE_FN(callback)
 
     def device_error(self) -> int:
         """Non-zero if a bounded wait inside a kernel expired since the last check (synchronises)."""

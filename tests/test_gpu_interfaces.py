@@ -1,0 +1,123 @@
+"""ASE calculator and LAMMPS ML-IAP entry points, driven with stand-in `atoms` / `data` objects."""
+import numpy as np
+import pytest
+import torch
+
+from tace_b200 import synth
+from tace_b200.interface import TACEAseCalc, TACELammpsCalc
+from tace_b200.interface.ase_calculator import export_tace
+from helpers import make_models, oracle_batch, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+class FakeAtoms:
+    def __init__(self, s):
+        self.s = s
+        self.info = {}
+
+    def get_positions(self): return self.s["positions"]
+    def get_atomic_numbers(self): return self.s["atomic_numbers"]
+    def get_cell(self): return self.s["cell"]
+    def get_pbc(self): return np.array(self.s["pbc"])
+    def __len__(self): return len(self.s["positions"])
+
+
+def test_ase_calculator_matches_oracle_and_pt_roundtrip(tmp_path):
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=0, species=(13, 29), fractions=(0.5, 0.5))
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64)
+    path = str(tmp_path / "model.pt")
+    export_tace(model, path)
+    calc = TACEAseCalc(path, device="cuda:0")
+    calc.calculate(FakeAtoms(s))
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64))
+    assert abs(calc.results["energy"] - ref["energy"].item()) < 1e-8 * len(s["positions"])
+    assert calc.results["free_energy"] == calc.results["energy"]
+    assert np.abs(calc.results["forces"] - ref["forces"].numpy()).max() < 1e-7
+    assert calc.results["stress"].shape == (3, 3)
+    assert np.abs(calc.results["stress"] - ref["stress"][0].numpy()).max() < 1e-7
+    assert set(calc.implemented_properties) >= {"energy", "free_energy", "forces", "stress"}
+
+
+class FakeLammpsData:
+    """Single-rank stand-in for the Kokkos ML-IAP data object: local atoms plus periodic ghost copies."""
+
+    def __init__(self, s, cutoff, elements, device):
+        from oracle.neighbour_list import neighbour_list
+        ei, es = neighbour_list(s["positions"], s["cell"], s["pbc"], cutoff)
+        n = len(s["positions"])
+        ghost_of = {}          # (owner, shift) -> ghost index
+        owners = []
+        pair_i, pair_j, rij = [], [], []
+        for (src, dst), sh in zip(ei.T, es):
+            # edge source -> target with vector r_dst - r_src + sh @ cell; LAMMPS pair (i = target, j = source or its ghost)
+            key = (int(src), tuple(int(v) for v in -sh))
+            if key[1] == (0, 0, 0):
+                j = int(src)
+            else:
+                if key not in ghost_of:
+                    ghost_of[key] = n + len(owners)
+                    owners.append(int(src))
+                j = ghost_of[key]
+            pair_i.append(int(dst)); pair_j.append(j)
+            rij.append(s["positions"][dst] - s["positions"][src] + sh @ s["cell"])
+        zs = sorted(elements)
+        species = [zs.index(int(z)) for z in s["atomic_numbers"]]
+        self.nlocal, self.ntotal, self.npairs = n, n + len(owners), len(pair_i)
+        self.owner = torch.tensor(owners, dtype=torch.int64, device=device)
+        self.elems = torch.tensor(species + [species[o] for o in owners], dtype=torch.int32, device=device)
+        self.rij = torch.tensor(np.array(rij), dtype=torch.float64, device=device)
+        self.pair_i = torch.tensor(pair_i, dtype=torch.int32, device=device)
+        self.pair_j = torch.tensor(pair_j, dtype=torch.int32, device=device)
+        self.eatoms = torch.zeros(n, dtype=torch.float64, device=device)
+        self.energy = None
+        self.pair_forces = None
+        self.exchanges = 0
+
+    def forward_exchange(self, src, dst, vec_len):
+        dst.copy_(src)
+        dst[self.nlocal:] = src[self.owner]
+        self.exchanges += 1
+
+    def reverse_exchange(self, src, dst, vec_len):
+        dst.copy_(src)
+        dst[: self.nlocal].index_add_(0, self.owner, src[self.nlocal:])
+        self.exchanges += 1
+
+    def update_pair_forces(self, f):
+        self.pair_forces = f.clone()
+
+
+@pytest.mark.parametrize("num_layers", [1, 2, 3])
+def test_lammps_mliap_with_ghost_exchange_matches_graph_mode(num_layers):
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=4, species=(13, 29), fractions=(0.5, 0.5))
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, num_layers=num_layers)
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64), compute_stress=False)
+    dev = torch.device("cuda:0")
+    data = FakeLammpsData(s, 4.0, [13, 29], dev)
+    assert data.ntotal > data.nlocal
+    calc = TACELammpsCalc(model)
+    assert calc.element_types == ["Al", "Cu"] and abs(calc.rcutfac - 2.0) < 1e-12
+    calc.compute_forces(data)
+    n = data.nlocal
+    assert abs(data.energy - ref["energy"].item()) < 1e-8 * n
+    assert (data.eatoms.cpu() - ref["node_energy"]).abs().max().item() < 1e-8
+    # forces as LAMMPS assembles them from pair forces (newton on): f_i -= f_ij, f_j += f_ij, ghosts folded back
+    f = torch.zeros(data.ntotal, 3, dtype=torch.float64, device=dev)
+    f.index_add_(0, data.pair_i.long(), -data.pair_forces)
+    f.index_add_(0, data.pair_j.long(), data.pair_forces)
+    f[:n].index_add_(0, data.owner, f[n:])
+    assert (f[:n].cpu() - ref["forces"]).abs().max().item() < 1e-7
+    assert data.exchanges == 2 * (num_layers - 1)
+
+
+def test_lammps_requires_kokkos_exchange():
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=4)
+    model, _, _ = make_models(2, 32, [29], 4.0, 20.0, torch.float64)
+    data = FakeLammpsData(s, 4.0, [29], torch.device("cuda:0"))
+    calc = TACELammpsCalc(model)
+
+    class NoExchange:
+        nlocal, ntotal, npairs, elems = data.nlocal, data.ntotal, data.npairs, data.elems
+    with pytest.raises(RuntimeError, match="KOKKOS"):
+        calc.compute_forces(NoExchange())
