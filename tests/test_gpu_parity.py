@@ -99,3 +99,54 @@ def test_edge_vector_mode_matches_graph_mode():
     out = model(to_device(data, torch.device("cuda:0")))
     assert (out["edge_forces"].cpu() - ref["edge_forces"]).abs().max().item() < 1e-7
     assert (out["forces"].cpu() - ref["forces"]).abs().max().item() < 1e-7
+
+
+def test_golden_model_case():
+    """The committed golden vectors (tests/golden/case_fcc32_L2_C32.npz), fp64 and fp32."""
+    import tace_b200
+    from golden_util import load_case
+    blob, sd, cfg, s = load_case()
+    for dtype in (torch.float64, torch.float32):
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(dtype)
+        try:
+            model = tace_b200.TensorModel(tace_b200.e3nnTACE(**cfg))
+        finally:
+            torch.set_default_dtype(prev)
+        own = model.state_dict()
+        model.load_state_dict({k: sd[k].to(own[k].dtype) for k in own})
+        data = to_device(oracle_batch([s], [29], float(blob["cutoff"]), dtype), torch.device("cuda:0"))
+        out = model(data)
+        etol, ftol = TOL[dtype]
+        n = len(s["positions"])
+        assert abs(out["energy"].item() - blob["energy"].item()) / n <= etol * max(1.0, abs(blob["energy"].item()) / n)
+        assert np.abs(out["forces"].cpu().numpy() - blob["forces"]).max() <= ftol
+        assert np.abs(out["stress"].cpu().numpy() - blob["stress"]).max() <= ftol
+
+
+def test_full_size_properties_config2():
+    """BASELINE config 2 at full size (64 crystals, L=3, 128 channels, 89 elements, fp32): properties that need
+    no oracle - net force per crystal ~ 0, run-to-run bit reproducibility, energy unchanged by a rigid shift
+    and by relabelling atoms inside the batch order of the edge list."""
+    from tace_b200.graph import build_batch
+    wl = synth.WORKLOADS["crystals64_fp32"]
+    structs = synth.workload_structures("crystals64_fp32")
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"])
+    import tace_b200
+    torch.manual_seed(0)
+    model = tace_b200.TensorModel(tace_b200.e3nnTACE(**cfg))
+    dev = torch.device("cuda:0")
+    data = build_batch(synth.collate(structs), wl["elements"], wl["cutoff"], torch.float32, dev)
+    a = model(data)
+    b = model(data)
+    assert model.device_error() == 0
+    assert torch.equal(a["energy"], b["energy"]) and torch.equal(a["forces"], b["forces"])
+    fscale = a["forces"].abs().max().item()
+    net = torch.zeros(len(structs), 3, device=dev).index_add_(0, data["batch"], a["forces"])
+    assert net.abs().max().item() <= 2e-4 * max(1.0, fscale)
+    perm = torch.randperm(data["edge_index"].shape[1], device=dev)
+    shuffled = dict(data, edge_index=data["edge_index"][:, perm].contiguous(), edge_shifts=data["edge_shifts"][perm].contiguous())
+    c = model(shuffled)
+    n_per = (data["ptr"][1:] - data["ptr"][:-1]).float()
+    assert ((c["energy"] - a["energy"]).abs() / n_per).max().item() <= 1e-5 * max(1.0, (a["energy"].abs() / n_per).max().item())
+    assert (c["forces"] - a["forces"]).abs().max().item() <= 1e-4 * max(1.0, fscale)
