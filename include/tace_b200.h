@@ -176,6 +176,34 @@ int tace_nl_fill(const double* positions, const double* lattice, const uint8_t* 
                  int32_t n_graphs, int64_t n_atoms, double cutoff, const int64_t* row_ptr, int64_t n_edges,
                  int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream);
 
+/* Neighbour list in one call that allocates nothing.  No counterpart in the reference.
+ *
+ * For hosts that must not allocate device memory while they run: an MD engine that has handed all of
+ * the GPU's memory to its own pool (LAMMPS/Kokkos style) so a cudaMalloc inside a plugin can fail or
+ * fragment it, or a latency-sensitive loop that cannot afford the device-wide synchronisation a
+ * cudaMalloc/cudaFree pair implies.  tace_nl_count / tace_nl_fill take their temporary buffers from the
+ * stream-ordered allocator and need a host round trip for the edge count; this variant keeps its
+ * temporaries (bins, sort keys, cell starts, sort workspace) in a fixed 2 MiB device array built into
+ * the library (every GPU that loads the library holds those 2 MiB until the process exits), computes
+ * the row pointers on the device and fills the caller's edge arrays directly.  It calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *
+ * Limits: n_atoms <= 16384 and n_graphs <= 1024, otherwise TACE_ERR_CAPACITY and nothing is launched.
+ * Outputs (device memory of the caller): row_ptr int64 [n_atoms+1] (exclusive prefix sum of the
+ * neighbour counts; row_ptr[n_atoms] is the number of edges found), edge_index int64 [2, max_edges]
+ * (row stride max_edges; row 0 = source, row 1 = target), edge_shifts int32 [max_edges, 3].  Edges
+ * beyond max_edges are not written: compare row_ptr[n_atoms] with max_edges after the stream has
+ * finished.  Edge order and content are identical to tace_nl_count + tace_nl_fill.
+ *
+ * The first call on a device looks up the device address of the built-in array (with that device
+ * current); make that first call before any stream capture.  All calls share the one array, so two
+ * calls that overlap on the GPU (different streams, or different host threads) race; calls on one
+ * stream are safe back to back, and every call overwrites all scratch it later reads, so nothing needs
+ * clearing between calls. */
+int tace_nl_build_noalloc(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
+                          int32_t n_graphs, int64_t n_atoms, double cutoff, int64_t max_edges, int64_t* row_ptr,
+                          int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

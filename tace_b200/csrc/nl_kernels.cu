@@ -249,10 +249,106 @@ int nl_run(bool fill, const double* pos, const double* lattice, const uint8_t* p
   return err == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }
 
+// ---- neighbour list without any allocation -------------------------------------------------------
+// Scratch for tace_nl_build_noalloc lives in this file-scope device array (2 MiB per GPU that loads
+// the library, held until the process exits).  In host code the name `nl_static_scratch` is only a
+// handle for the runtime, not a device address: the address is looked up once per device with
+// cudaGetSymbolAddress and that pointer is what the kernels receive.
+constexpr int kNoAllocMaxAtoms = 16384;
+constexpr int kNoAllocMaxGraphs = 1024;
+constexpr size_t kNoAllocScratchBytes = size_t(2) << 20;
+static __device__ __align__(256) unsigned char nl_static_scratch[kNoAllocScratchBytes];
+
+// row_ptr[0] = 0, row_ptr[i + 1] = counts[0] + ... + counts[i]; one block, any n
+__global__ void nl_scan_counts_kernel(const int* __restrict__ counts, int n, int64_t* row_ptr) {
+  __shared__ long long part[1024];
+  __shared__ long long carry;
+  if (threadIdx.x == 0) { carry = 0; row_ptr[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    part[threadIdx.x] = i < n ? counts[i] : 0;
+    __syncthreads();
+    for (int off = 1; off < (int)blockDim.x; off <<= 1) {  // inclusive Hillis-Steele scan of this chunk
+      const long long add = (int)threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+      __syncthreads();
+      part[threadIdx.x] += add;
+      __syncthreads();
+    }
+    if (i < n) row_ptr[i + 1] = carry + part[threadIdx.x];
+    __syncthreads();
+    if (threadIdx.x == 0) carry += part[blockDim.x - 1];
+    __syncthreads();
+  }
+}
+
+int nl_build_noalloc(const double* pos, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr, int32_t n_graphs,
+                     int64_t n_atoms64, double cutoff, int64_t max_edges, int64_t* row_ptr, int64_t* edge_index, int32_t* shifts,
+                     cudaStream_t s) {
+  if (!pos || !lattice || !pbc || !graph_ptr || !row_ptr || n_graphs <= 0 || n_atoms64 < 0 || max_edges < 0 || !(cutoff > 0.0) ||
+      (max_edges > 0 && (!edge_index || !shifts)))
+    return TACE_ERR_INVALID_ARGUMENT;
+  if (n_atoms64 > kNoAllocMaxAtoms || n_graphs > kNoAllocMaxGraphs) return TACE_ERR_CAPACITY;
+  const int n_atoms = (int)n_atoms64;
+  // one-time, per-device lookup of the scratch array's device address (with that device current)
+  constexpr int kMaxDevices = 64;
+  static unsigned char* scratch_of_device[kMaxDevices] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TACE_ERR_NO_DEVICE;
+  if (!scratch_of_device[dev]) {
+    unsigned char* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, nl_static_scratch) != cudaSuccess || !ptr) return TACE_ERR_CUDA;
+    scratch_of_device[dev] = ptr;
+  }
+  unsigned char* p = scratch_of_device[dev];
+  unsigned char* const end = p + kNoAllocScratchBytes;
+  auto al = [](size_t x) { return (x + 255) & ~size_t(255); };
+  const int max_cells = 2 * n_atoms + n_graphs + 1;
+  GraphBins* bins = reinterpret_cast<GraphBins*>(p); p += al(sizeof(GraphBins) * n_graphs);
+  int* total = reinterpret_cast<int*>(p); p += al(sizeof(int));
+  int* keys = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(n_atoms + 1));
+  int* vals = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(n_atoms + 1));
+  int* keys_sorted = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(n_atoms + 1));
+  int* atoms_sorted = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(n_atoms + 1));
+  int* img = reinterpret_cast<int*>(p); p += al(sizeof(int) * 3 * (size_t)(n_atoms + 1));
+  int* cell_start = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(max_cells + 1));
+  int* counts = reinterpret_cast<int*>(p); p += al(sizeof(int) * (size_t)(n_atoms + 1));
+  size_t cub_bytes = 0;
+  if (n_atoms > 0)
+    cub::DeviceRadixSort::SortPairs(nullptr, cub_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr, (int*)nullptr, n_atoms);
+  void* cub_temp = p;
+  if (p + cub_bytes > end) return TACE_ERR_CAPACITY;
+
+  if (n_atoms == 0) {
+    nl_scan_counts_kernel<<<1, 32, 0, s>>>(counts, 0, row_ptr);
+    return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+  }
+  nl_setup_kernel<<<n_graphs, 128, 0, s>>>(pos, lattice, pbc, graph_ptr, cutoff, bins);
+  nl_offsets_kernel<<<1, 1, 0, s>>>(bins, n_graphs, total);
+  const int ab = (n_atoms + 127) / 128;
+  nl_bin_kernel<<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, keys, vals, img);
+  if (cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys, keys_sorted, vals, atoms_sorted, n_atoms, 0, 32, s) != cudaSuccess)
+    return TACE_ERR_CUDA;
+  nl_cell_start_kernel<<<(max_cells + 128) / 128, 128, 0, s>>>(keys_sorted, n_atoms, cell_start, max_cells);
+  nl_search_kernel<false><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+                                             counts, nullptr, 0, nullptr, nullptr);
+  nl_scan_counts_kernel<<<1, 1024, 0, s>>>(counts, n_atoms, row_ptr);
+  nl_search_kernel<true><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+                                            nullptr, row_ptr, max_edges, edge_index, shifts);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
 }  // namespace
 }  // namespace tace
 
 extern "C" {
+
+int tace_nl_build_noalloc(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
+                          int32_t n_graphs, int64_t n_atoms, double cutoff, int64_t max_edges, int64_t* row_ptr,
+                          int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream) {
+  return tace::nl_build_noalloc(positions, lattice, pbc, graph_ptr, n_graphs, n_atoms, cutoff, max_edges, row_ptr, edge_index,
+                                edge_shifts, static_cast<cudaStream_t>(stream));
+}
 
 int tace_nl_count(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
                   int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, tace_stream_t stream) {

@@ -19,7 +19,7 @@ EXPORTS = [
     "tace_status_string", "tace_create", "tace_destroy", "tace_weight_count", "tace_weight_info", "tace_set_weight",
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill",
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
-    "tace_device_error", "tace_set_exchange",
+    "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc",
 ]
 
 
@@ -89,6 +89,8 @@ def load() -> ctypes.CDLL:
     lib.tace_tc_gemm_f32.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32,
                                      c_void_p, c_void_p]
     lib.tace_device_error.argtypes = [c_void_p, POINTER(c_int32)]
+    lib.tace_nl_build_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_int64, c_void_p,
+                                          c_void_p, c_void_p, c_void_p]
     lib.tace_set_exchange.argtypes = [c_void_p, EXCHANGE_FN, c_void_p]
     lib.tace_nl_count.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_void_p]
     lib.tace_nl_fill.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_int64,
