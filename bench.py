@@ -305,6 +305,9 @@ def main():
     d2h = sum(int(t.numel() * t.element_size()) for t in res)
     e2e_value = total_atoms * args.steps / e2e_s
 
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
     if rank != 0:
         return
 

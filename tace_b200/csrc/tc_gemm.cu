@@ -12,10 +12,11 @@
 // is split in shared memory right after its TMA load, element-wise and in place, which keeps
 // the 128-byte-swizzled layout the TMA engine wrote.
 //
-// One CTA = 128 threads walks its share of 128 x BN output tiles.  Per 32-wide K step a 3-stage
-// ring holds {A, A_lo, B_hi, B_lo}; thread 0 issues the TMA loads and the tcgen05.mma
-// instructions, all four warps split A and run the epilogue (tcgen05.ld of their 32 TMEM lanes,
-// 128-bit stores).  The tensor core adds into its accumulator with truncation, an error that
+// One persistent CTA per SM walks its share of 128 x BN output tiles with specialised warps: a TMA
+// producer fills a 3- or 4-stage ring of {A, A_lo, B_hi, B_lo} per 32-wide K step, four warps split A,
+// one thread issues the tcgen05.mma instructions into one of two TMEM accumulators, and four
+// epilogue warps drain the other accumulator (tcgen05.ld of their 32 lanes, 128-bit stores), so
+// loads, splitting, tensor-core work and stores overlap.  The tensor core adds into its accumulator with truncation, an error that
 // grows linearly with the number of accumulated instructions; long K loops are therefore cut
 // into chunks of kChunk steps whose partial sums are drained from TMEM and added in FP32
 // registers with round-to-nearest.  Every mbarrier wait is bounded: on expiry the CTA records an error code in
@@ -33,7 +34,6 @@ namespace {
 
 constexpr int kBM = 128;      // rows per tile = TMEM lanes
 constexpr int kBK = 32;       // fp32 elements per K step = one 128-byte swizzle row
-constexpr int kStages = 3;
 constexpr int kChunk = 8;     // K steps accumulated inside TMEM before draining into FP32 registers
 constexpr int kTileABytes = kBM * kBK * 4;  // 16 KB
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -110,39 +110,56 @@ struct TcParams {
   int* error;
 };
 
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = operand
+// splitters, warps 6-9 = epilogue (each owns the 32 TMEM lanes 32 * (warp % 4) .. + 31).
+constexpr int kThreads = 320;
+constexpr int kSplitWarp0 = 2, kEpiWarp0 = 6;
+
 template <int BN>
 struct TcSmem {
+  static constexpr int kStages = BN == 128 ? 3 : 4;
   static constexpr int kTileBBytes = BN * kBK * 4;
   static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
-  static constexpr int kBarrierBytes = 128;
+  static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN>
-__global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                         const __grid_constant__ CUtensorMap tmBhi,
-                                                         const __grid_constant__ CUtensorMap tmBlo, const TcParams p) {
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// ONE_CHUNK: the whole K loop fits one TMEM accumulation chunk, so the epilogue stores straight from
+// the drained registers and needs no running sums.
+template <int BN, bool ONE_CHUNK>
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                              const __grid_constant__ CUtensorMap tmBhi,
+                                                              const __grid_constant__ CUtensorMap tmBlo, const TcParams p) {
   using S = TcSmem<BN>;
+  constexpr int kStages = S::kStages;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte-swizzled tiles need 1024-byte alignment
   unsigned char* base_ptr = smem_raw + (base - raw);
   const uint32_t bars = base + kStages * S::kStageBytes;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * kStages);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kStages * S::kStageBytes + 8 * (2 * kStages + 1));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kStages * S::kStageBytes + 8 * (2 * kStages + 1) + 8);
+  // barriers: raw[s] TMA landed | ready[s] operands split | empty[s] MMAs done reading | acc_full[a] | acc_empty[a]
+  auto raw_bar = [&](int s) { return bars + 8u * s; };
+  auto ready_bar = [&](int s) { return bars + 8u * (kStages + s); };
+  auto empty_bar = [&](int s) { return bars + 8u * (2 * kStages + s); };
+  auto acc_full = [&](int a) { return bars + 8u * (3 * kStages + a); };
+  auto acc_empty = [&](int a) { return bars + 8u * (3 * kStages + 2 + a); };
+  unsigned char* misc = base_ptr + kStages * S::kStageBytes + 8 * (3 * kStages + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(acc_bar, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), 128); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(BN));
+  if (warp == 1) {  // two accumulators of BN fp32 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -153,47 +170,76 @@ __global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__
   const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = p.N / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int num_k = p.K / kBK;
+  const int chunks_per_tile = (num_k + kChunk - 1) / kChunk;
   const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  const int total = my_tiles * num_k;
+  const int total = my_tiles * num_k;  // flat K steps of this CTA
   // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-
   auto stage_a = [&](int s) { return base + s * S::kStageBytes; };
   auto stage_alo = [&](int s) { return base + s * S::kStageBytes + kTileABytes; };
   auto stage_bhi = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes; };
   auto stage_blo = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes + S::kTileBBytes; };
 
-  int issued = 0;
-  auto issue = [&](int j) {  // thread 0: TMA loads of flat step j into its ring slot
-    const int s = j % kStages, ph = (j / kStages) & 1;
-    mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.error, 1);
-    if (*abort_flag) return;
-    const int tile = blockIdx.x + (j / num_k) * gridDim.x, ks = j % num_k;
-    const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-    mbar_expect_tx(full_bar(s), kTileABytes + 2 * S::kTileBBytes);
-    tma_load_2d(stage_a(s), &tmA, full_bar(s), ks * kBK, m0);
-    tma_load_2d(stage_bhi(s), &tmBhi, full_bar(s), ks * kBK, n0);
-    tma_load_2d(stage_blo(s), &tmBlo, full_bar(s), ks * kBK, n0);
-  };
-  if (tid == 0)
-    for (; issued < kStages - 1 && issued < total; ++issued) issue(issued);
-
-  uint32_t acc_phase = 0;
-  int consumed = 0;
-  float accr[BN];  // this thread's output row (row = 32 * warp + lane of the tile)
-  for (int i = 0; i < total; ++i) {
-    const int s = i % kStages, ph = (i / kStages) & 1;
-    const int ks = i % num_k;
-    const bool chunk_begin = (ks % kChunk) == 0;
-    const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == num_k - 1;
-    mbar_wait(full_bar(s), ph, abort_flag, p.error, 2);
-    // split A into TF32-exact high part (in place) and residual
-    {
+  if (warp == 0) {
+    // ---- TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int j = 0; j < total; ++j) {
+        const int s = j % kStages, ph = (j / kStages) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.error, 1)) break;
+        const int tile = blockIdx.x + (j / num_k) * gridDim.x, ks = j % num_k;
+        const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+        mbar_expect_tx(raw_bar(s), kTileABytes + 2 * S::kTileBBytes);
+        tma_load_2d(stage_a(s), &tmA, raw_bar(s), ks * kBK, m0);
+        tma_load_2d(stage_bhi(s), &tmBhi, raw_bar(s), ks * kBK, n0);
+        tma_load_2d(stage_blo(s), &tmBlo, raw_bar(s), ks * kBK, n0);
+        issued = j + 1;
+      }
+      if (*abort_flag) {  // loads already issued must land before the CTA exits
+        for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
+          const int s = j % kStages, ph = (j / kStages) & 1;
+          for (uint32_t it = 0; it < kSpinLimit; ++it)
+            if (mbar_try_wait(raw_bar(s), ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      for (int i = 0; i < total; ++i) {
+        const int s = i % kStages, ph = (i / kStages) & 1;
+        const int ks = i % num_k;
+        const int chunk = (i / num_k) * chunks_per_tile + ks / kChunk;  // flat chunk index of this CTA
+        const int a = chunk & 1;
+        const bool chunk_begin = (ks % kChunk) == 0;
+        const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == num_k - 1;
+        if (chunk_begin && !mbar_wait(acc_empty(a), ((chunk >> 1) & 1) ^ 1, abort_flag, p.error, 4)) break;
+        if (!mbar_wait(ready_bar(s), ph, abort_flag, p.error, 2)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d = tmem_base + a * BN;
+#pragma unroll
+        for (int k8 = 0; k8 < kBK / 8; ++k8) {
+          const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
+          const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
+          umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
+          umma_tf32(d, da, dbl, idesc, 1u);
+          umma_tf32(d, dal, db, idesc, 1u);
+        }
+        umma_commit(empty_bar(s));             // ring slot reusable once these MMAs have read it
+        if (chunk_end) umma_commit(acc_full(a));  // partial sum of this chunk complete
+      }
+    }
+  } else if (warp < kEpiWarp0) {
+    // ---- operand splitters: A = hi + lo with hi exact in TF32, element-wise and in place
+    const int t = tid - kSplitWarp0 * 32;
+    for (int i = 0; i < total; ++i) {
+      const int s = i % kStages, ph = (i / kStages) & 1;
+      if (!mbar_wait(raw_bar(s), ph, abort_flag, p.error, 3)) break;
       float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
       float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
 #pragma unroll
       for (int j = 0; j < kTileABytes / 16 / 128; ++j) {
-        const int idx = tid + j * 128;
+        const int idx = t + j * 128;
         const float4 v = a[idx];
         float4 h, l;
         h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
@@ -203,66 +249,53 @@ __global__ void __launch_bounds__(128, 1) tc_gemm_kernel(const __grid_constant__
         a[idx] = h;
         alo[idx] = l;
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+      mbar_arrive(ready_bar(s));
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (*abort_flag) break;  // uniform: every writer of the flag precedes this barrier or the next one
-    consumed = i + 1;
-    if (tid == 0) {
+  } else {
+    // ---- epilogue: drain each chunk's partial sum from TMEM, add in FP32 registers, store at tile end
+    const int ew = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31; warps 6-9 cover all four quarters
+    float accr[ONE_CHUNK ? 1 : BN];
+    const int n_chunks = my_tiles * chunks_per_tile;
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+      const int a = chunk & 1;
+      const int tile_i = chunk / chunks_per_tile, cin = chunk % chunks_per_tile;
+      const int tile = blockIdx.x + tile_i * gridDim.x;
+      const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+      const int row = m0 + ew * 32 + lane;
+      float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0);
+      if (!mbar_wait(acc_full(a), (chunk >> 1) & 1, abort_flag, p.error, 5)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int k8 = 0; k8 < kBK / 8; ++k8) {
-        const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
-        const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
-        umma_tf32(tmem_base, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
-        umma_tf32(tmem_base, da, dbl, idesc, 1u);
-        umma_tf32(tmem_base, dal, db, idesc, 1u);
-      }
-      umma_commit(empty_bar(s));           // ring slot reusable once these MMAs have read it
-      if (chunk_end) umma_commit(acc_bar);  // partial sum of this chunk complete
-      if (issued < total) { issue(issued); ++issued; }
-    }
-    if (chunk_end) {
-      mbar_wait(acc_bar, acc_phase, abort_flag, p.error, 3);
-      acc_phase ^= 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool first_chunk = ks < kChunk;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(ew * 32) << 16) + a * BN + c * 32, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if constexpr (ONE_CHUNK) {
+          if (row < p.M) {
 #pragma unroll
-        for (int q = 0; q < 32; ++q) accr[c * 32 + q] = first_chunk ? __uint_as_float(r[q]) : accr[c * 32 + q] + __uint_as_float(r[q]);
+            for (int q = 0; q < 8; ++q)
+              dst[c * 8 + q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                           __uint_as_float(r[4 * q + 3]));
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) accr[c * 32 + q] = cin == 0 ? __uint_as_float(r[q]) : accr[c * 32 + q] + __uint_as_float(r[q]);
+        }
       }
-      if (ks == num_k - 1) {
-        const int tile = blockIdx.x + (i / num_k) * gridDim.x;
-        const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-        const int row = m0 + warp * 32 + lane;
-        if (row < p.M && !*abort_flag) {
-          float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(acc_empty(a));  // the issuer may overwrite this accumulator
+      if constexpr (!ONE_CHUNK) {
+        if (cin == chunks_per_tile - 1 && row < p.M) {
 #pragma unroll
           for (int q = 0; q < BN / 4; ++q) dst[q] = make_float4(accr[4 * q], accr[4 * q + 1], accr[4 * q + 2], accr[4 * q + 3]);
         }
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();  // TMEM may be overwritten by the next chunk's first MMA
-      if (*abort_flag) break;
-    }
-  }
-  // Drain: loads that were issued but never consumed must land before the CTA exits.
-  __syncthreads();
-  if (tid == 0) {
-    for (int j = consumed; j < issued; ++j) {
-      const int s = j % kStages, ph = (j / kStages) & 1;
-      for (uint32_t it = 0; it < kSpinLimit; ++it)
-        if (mbar_try_wait(full_bar(s), ph)) break;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN));
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -294,17 +327,17 @@ bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
+template <int BN, bool ONE_CHUNK>
 cudaError_t launch_tc(const CUtensorMap& a, const CUtensorMap& bh, const CUtensorMap& bl, const TcParams& p, int sms, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, ONE_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int tiles = ((p.M + kBM - 1) / kBM) * (p.N / BN);
   const int grid = tiles < sms ? tiles : sms;
-  tc_gemm_kernel<BN><<<grid, 128, TcSmem<BN>::kTotal, s>>>(a, bh, bl, p);
+  tc_gemm_kernel<BN, ONE_CHUNK><<<grid, kThreads, TcSmem<BN>::kTotal, s>>>(a, bh, bl, p);
   return cudaGetLastError();
 }
 
@@ -325,7 +358,9 @@ cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, cons
   if (!make_map(&ma, A, M, K, lda, kBM) || !make_map(&mbh, Bhi, N, K, K, bn) || !make_map(&mbl, Blo, N, K, K, bn))
     return cudaErrorInvalidValue;
   TcParams p{M, N, K, C, ldc, error_flag};
-  return bn == 128 ? launch_tc<128>(ma, mbh, mbl, p, sms, s) : launch_tc<64>(ma, mbh, mbl, p, sms, s);
+  const bool one = K / kBK <= kChunk;
+  if (bn == 128) return one ? launch_tc<128, true>(ma, mbh, mbl, p, sms, s) : launch_tc<128, false>(ma, mbh, mbl, p, sms, s);
+  return one ? launch_tc<64, true>(ma, mbh, mbl, p, sms, s) : launch_tc<64, false>(ma, mbh, mbl, p, sms, s);
 }
 
 }  // namespace tace
