@@ -150,6 +150,11 @@ struct Model : ModelBase {
     weights.push_back({name, numel, arena_numel, false});
     arena_numel += (numel + 63) / 64 * 64;
   }
+  // a channel-mixing matrix used by the tensor-core path also needs its TF32 high part and residual
+  void add_linear_weight(const std::string& name, long long numel) {
+    add_weight(name, numel);
+    if (kTensorCore) { add_weight(name + "_hi", numel); add_weight(name + "_lo", numel); }
+  }
   const T* w(const std::string& name) const {
     for (const auto& e : weights)
       if (e.name == name) return arena + e.offset;
@@ -178,7 +183,7 @@ struct Model : ModelBase {
     for (int t = 0; t < NL_; ++t) {
       const LayerPlan& p = layers[t];
       const std::string pre = "t" + std::to_string(t) + ".";
-      for (int l : p.in_ls) { add_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
+      for (int l : p.in_ls) { add_linear_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_linear_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
       add_weight(pre + "up.b", C);
       add_weight(pre + "A0", kNumBessel * kHidden);
       add_weight(pre + "A1", kHidden * kHidden);
@@ -195,10 +200,10 @@ struct Model : ModelBase {
       }
       for (int l = 0; l <= L; ++l) {
         const long long outl = (l == 0) ? (long long)(L + 2) * C : C;
-        add_weight(pre + "down.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
-        add_weight(pre + "downT.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
-        add_weight(pre + "nl.l" + std::to_string(l), (long long)C * C);
-        add_weight(pre + "nlT.l" + std::to_string(l), (long long)C * C);
+        add_linear_weight(pre + "down.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
+        add_linear_weight(pre + "downT.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
+        add_linear_weight(pre + "nl.l" + std::to_string(l), (long long)C * C);
+        add_linear_weight(pre + "nlT.l" + std::to_string(l), (long long)C * C);
       }
       add_weight(pre + "down.b", (long long)(L + 2) * C);
       add_weight(pre + "nl.b", C);
@@ -211,8 +216,8 @@ struct Model : ModelBase {
           add_weight(pre + "c1.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
           add_weight(pre + "c1T.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
         }
-        add_weight(pre + "lin.l" + ls, (long long)C * C);
-        add_weight(pre + "linT.l" + ls, (long long)C * C);
+        add_linear_weight(pre + "lin.l" + ls, (long long)C * C);
+        add_linear_weight(pre + "linT.l" + ls, (long long)C * C);
         if (p.has_res) {
           add_weight(pre + "res.l" + ls, (long long)n_el * C * C);
           add_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
@@ -343,6 +348,33 @@ struct Model : ModelBase {
   }
   const int* tiles(const Bufs& b, int l) const { return b.tile_ptr + l * (n_el + 1); }
 
+  // One per-rank linear of a launch: rows (atom, m) of A times the [K][N] matrix `wname`;
+  // `wname_t` names the same matrix transposed ([N][K]), which is what the tensor-core path reads.
+  struct LinSpec {
+    const T* A; long long a_s1, a_s2; int q, K;
+    std::string wname, wname_t; int N;
+    T* Cm; long long c_s1, c_s2; const T* bias;
+  };
+  // Plain (not per-species) linears: tcgen05 for fp32 models when every shape fits, CUDA cores otherwise.
+  cudaError_t run_linear(const std::vector<LinSpec>& specs, long long n_atoms, cudaStream_t s) {
+    bool tc = kTensorCore && !specs.empty() && specs.size() <= 4;
+    for (const auto& sp : specs) tc = tc && tc_linear_supported(sp.N, sp.K);
+    if (tc) {
+      TcLinearProblem probs[4];
+      for (size_t i = 0; i < specs.size(); ++i) {
+        const LinSpec& sp = specs[i];
+        probs[i] = {reinterpret_cast<const float*>(sp.A), sp.a_s1, sp.a_s2, sp.q, n_atoms, sp.K, sp.N,
+                    reinterpret_cast<const float*>(w(sp.wname_t + "_hi")), reinterpret_cast<const float*>(w(sp.wname_t + "_lo")),
+                    reinterpret_cast<float*>(sp.Cm), sp.c_s1, sp.c_s2, reinterpret_cast<const float*>(sp.bias)};
+      }
+      return launch_tc_linear(probs, (int)specs.size(), dev_error, s);
+    }
+    GemmBatch<T> gb = plain_batch(n_atoms);
+    for (const auto& sp : specs)
+      add_problem(gb, sp.A, sp.a_s1, sp.a_s2, sp.q, sp.K, w(sp.wname), sp.N, sp.Cm, sp.c_s1, sp.c_s2, sp.bias, 0);
+    return launch_gemm(gb, n_atoms, s);
+  }
+
 #define CK(expr)                                                                                 \
   do {                                                                                           \
     cudaError_t err__ = (expr);                                                                  \
@@ -425,11 +457,12 @@ struct Model : ModelBase {
       PH(("t" + ts + ".fwd.linear_up").c_str());
       const long long n_up = p.scalar_src ? N : NL;  // layer 0 embeds every atom; later layers own only local rows
       {  // linear_up
-        GemmBatch<T> gb = plain_batch(n_up);
+        std::vector<LinSpec> sp;
         for (int l : p.in_ls)
-          add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "up.l" + std::to_string(l)), C,
-                      lb.x + (long long)l * l * C, (long long)p.tp.NX * C, C, l == 0 ? w(pre + "up.b") : nullptr, 0);
-        CKL(launch_gemm(gb, n_up, s));
+          sp.push_back({lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, pre + "up.l" + std::to_string(l),
+                        pre + "upT.l" + std::to_string(l), C, lb.x + (long long)l * l * C, (long long)p.tp.NX * C, C,
+                        l == 0 ? w(pre + "up.b") : nullptr});
+        CKL(run_linear(sp, n_up, s));
       }
       const T* x_src = lb.x;
       if (lb.xx) {
@@ -460,24 +493,25 @@ struct Model : ModelBase {
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
       PH(("t" + ts + ".fwd.node").c_str());
       {  // linear_down (1/avg_num_neighbors folded into the weights)
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l) {
           const int K = p.tp.k[l] * C;
           const int Nout = (l == 0) ? (L + 2) * C : C;
           T* dst = (l == 0) ? lb.Gt : lb.Gt + (long long)(L + 1 + l * l) * C;
-          add_problem(gb, lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, K, 2 * l + 1, K,
-                      w(pre + "down.l" + std::to_string(l)), Nout, dst, (long long)(L + 1 + D) * C, C,
-                      l == 0 ? w(pre + "down.b") : nullptr, 0);
+          sp.push_back({lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, K, 2 * l + 1, K, pre + "down.l" + std::to_string(l),
+                        pre + "downT.l" + std::to_string(l), Nout, dst, (long long)(L + 1 + D) * C, C,
+                        l == 0 ? w(pre + "down.b") : nullptr});
         }
-        CKL(launch_gemm(gb, NL, s));
+        CKL(run_linear(sp, NL, s));
       }
       CKL(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, s));
       {
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l)
-          add_problem(gb, lb.a + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nl.l" + std::to_string(l)), C,
-                      lb.A + (long long)l * l * C, (long long)D * C, C, l == 0 ? w(pre + "nl.b") : nullptr, 0);
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.a + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, pre + "nl.l" + std::to_string(l),
+                        pre + "nlT.l" + std::to_string(l), C, lb.A + (long long)l * l * C, (long long)D * C, C,
+                        l == 0 ? w(pre + "nl.b") : nullptr});
+        CKL(run_linear(sp, NL, s));
       }
       debug.push_back({"A" + ts, lb.A, NL * D * C});
       if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.A, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
@@ -501,11 +535,12 @@ struct Model : ModelBase {
         }
       }
       {
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l : p.out_ls)
-          add_problem(gb, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "lin.l" + std::to_string(l)),
-                      C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "lin.b") : nullptr, 0);
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "lin.l" + std::to_string(l),
+                        pre + "linT.l" + std::to_string(l), C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C,
+                        l == 0 ? w(pre + "lin.b") : nullptr});
+        CKL(run_linear(sp, NL, s));
       }
       if (p.has_res) {  // per-species skip connection from the layer input
         GemmBatch<T> gb = species_batch(b);
@@ -539,11 +574,11 @@ struct Model : ModelBase {
       const std::string ts = std::to_string(t);
       PH(("t" + ts + ".bwd.node").c_str());
       {  // through the final linear
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l : p.out_ls)
-          add_problem(gb, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "linT.l" + std::to_string(l)),
-                      C, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 0);
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "linT.l" + std::to_string(l),
+                        pre + "lin.l" + std::to_string(l), C, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, nullptr});
+        CKL(run_linear(sp, NL, s));
       }
       if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gA, NL * D * C, s));
       {  // through the per-species coefficients
@@ -566,23 +601,23 @@ struct Model : ModelBase {
         }
       }
       {
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l)
-          add_problem(gb, lb.gA + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "nlT.l" + std::to_string(l)), C,
-                      lb.ga + (long long)l * l * C, (long long)D * C, C, nullptr, 0);
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.gA + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, pre + "nlT.l" + std::to_string(l),
+                        pre + "nl.l" + std::to_string(l), C, lb.ga + (long long)l * l * C, (long long)D * C, C, nullptr});
+        CKL(run_linear(sp, NL, s));
       }
       CKL(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, s));
       {  // through linear_down; the gradient of the messages overwrites the messages
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l) {
           const int Nk = p.tp.k[l] * C;
           const int Kin = (l == 0) ? (L + 2) * C : C;
           const T* src = (l == 0) ? lb.gGt : lb.gGt + (long long)(L + 1 + l * l) * C;
-          add_problem(gb, src, (long long)(L + 1 + D) * C, C, 2 * l + 1, Kin, w(pre + "downT.l" + std::to_string(l)), Nk,
-                      lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, Nk, nullptr, 0);
+          sp.push_back({src, (long long)(L + 1 + D) * C, C, 2 * l + 1, Kin, pre + "downT.l" + std::to_string(l),
+                        pre + "down.l" + std::to_string(l), Nk, lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, Nk, nullptr});
         }
-        CKL(launch_gemm(gb, NL, s));
+        CKL(run_linear(sp, NL, s));
       }
       // edge pass: gradients of the per-edge weights (in place over W), of the angular features and,
       // per edge, of the source features
@@ -613,11 +648,12 @@ struct Model : ModelBase {
       }
       if (!p.scalar_src) {
         PH(("t" + ts + ".bwd.linear_up").c_str());
-        GemmBatch<T> gb = plain_batch(NL);
+        std::vector<LinSpec> sp;
         for (int l : p.in_ls)
-          add_problem(gb, (lb.gxx ? lb.gxx : lb.gx) + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C, w(pre + "upT.l" + std::to_string(l)),
-                      C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 0);
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({(lb.gxx ? lb.gxx : lb.gx) + (long long)l * l * C, (long long)p.tp.NX * C, C, 2 * l + 1, C,
+                        pre + "upT.l" + std::to_string(l), pre + "up.l" + std::to_string(l), C, lb.gh_in + (long long)l * l * C,
+                        (long long)p.Din * C, C, nullptr});
+        CKL(run_linear(sp, NL, s));
         if (p.has_res) {
           GemmBatch<T> g2 = species_batch(b);
           for (int l : p.out_ls)

@@ -139,6 +139,19 @@ namespace tace {
 // FP32-accurate GEMM on tcgen05 tensor cores (tc_gemm.cu): C[M,N] = A[M,K] @ B[N,K]^T with B given
 // as its TF32 high part and residual.  `error_flag` (device int) receives a non-zero code if a
 // bounded wait inside the kernel expired.
+// Batched form for the per-rank linears: up to four problems per launch, rows = (atom, component) pairs
+// addressed as base + atom * atom_stride + component * comp_stride (elements), K and N contiguous.
+struct TcLinearProblem {
+  const float* A; long long a_atom_stride, a_comp_stride;
+  int q;                 // components per atom (2l+1), <= 128
+  long long n_atoms;
+  int K, N;
+  const float* Bhi; const float* Blo;  // [N][K]
+  float* C; long long c_s1, c_s2;
+  const float* bias;     // [N] or nullptr
+};
+bool tc_linear_supported(int N, int K);
+cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s);
 cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
                            int N, int K, int* error_flag, cudaStream_t s);
 }  // namespace tace

@@ -24,6 +24,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cstring>
 
 #include "../../include/tace_b200.h"
 #include "kernels.h"
@@ -103,17 +104,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-struct TcParams {
-  int M, N, K;
+// One linear problem of a launch: C[(atom, m), :] = A[(atom, m), 0:K] @ B[0:N, 0:K]^T (+ bias).
+// Rows are (atom, component) pairs; the 3-D tensor map of A is {K, q, atoms} with box {32, q, R},
+// R = 128 / q atoms per tile, so a tile's rows land in shared memory in (atom, m) order.
+struct TcProblem {
+  CUtensorMap tmA, tmBhi, tmBlo;
   float* C;
-  long long ldc;
+  const float* bias;     // [N] or nullptr
+  long long c_s1, c_s2;  // atom stride / component stride of C rows (elements)
+  int q, R, n_atoms, N, K;
+};
+constexpr int kTcMaxProblems = 4;
+struct TcBatch {
+  TcProblem p[kTcMaxProblems];
+  int n_problems;
+  int tile_start[kTcMaxProblems + 1];  // prefix sum of the problems' tile counts
   int* error;
 };
 
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = operand
-// splitters, warps 6-9 = epilogue (each owns the 32 TMEM lanes 32 * (warp % 4) .. + 31).
-constexpr int kThreads = 320;
-constexpr int kSplitWarp0 = 2, kEpiWarp0 = 6;
+// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = operand
+// splitters, warps 4-7 = epilogue (warp w owns the TMEM lanes 32 * (w % 4) .. + 31).
+constexpr int kThreads = 256;
+constexpr int kSplitThreads = 64;
 
 template <int BN>
 struct TcSmem {
@@ -127,13 +139,34 @@ struct TcSmem {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 
-// ONE_CHUNK: the whole K loop fits one TMEM accumulation chunk, so the epilogue stores straight from
-// the drained registers and needs no running sums.
+struct TileInfo {
+  int prob, atom0, n0, num_k;
+};
+template <int BN>
+__device__ __forceinline__ TileInfo decode_tile(const TcBatch& b, int tile) {
+  int pi = 0;
+  while (pi + 1 < b.n_problems && tile >= b.tile_start[pi + 1]) ++pi;
+  const int local = tile - b.tile_start[pi];
+  const int tiles_n = b.p[pi].N / BN;
+  TileInfo t;
+  t.prob = pi;
+  t.atom0 = (local / tiles_n) * b.p[pi].R;
+  t.n0 = (local % tiles_n) * BN;
+  t.num_k = b.p[pi].K / kBK;
+  return t;
+}
+
+// ONE_CHUNK: every K loop of the launch fits one TMEM accumulation chunk, so the epilogue stores
+// straight from the drained registers and needs no running sums.
 template <int BN, bool ONE_CHUNK>
-__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                              const __grid_constant__ CUtensorMap tmBhi,
-                                                              const __grid_constant__ CUtensorMap tmBlo, const TcParams p) {
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_constant__ TcBatch batch) {
   using S = TcSmem<BN>;
   constexpr int kStages = S::kStages;
   extern __shared__ unsigned char smem_raw[];
@@ -153,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), 128); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), kSplitThreads); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -167,12 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (p.M + kBM - 1) / kBM, tiles_n = p.N / BN;
-  const int n_tiles = tiles_m * tiles_n;
-  const int num_k = p.K / kBK;
-  const int chunks_per_tile = (num_k + kChunk - 1) / kChunk;
-  const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  const int total = my_tiles * num_k;  // flat K steps of this CTA
+  const int n_tiles = batch.tile_start[batch.n_problems];
   // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   auto stage_a = [&](int s) { return base + s * S::kStageBytes; };
@@ -183,20 +211,23 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   if (warp == 0) {
     // ---- TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int j = 0; j < total; ++j) {
-        const int s = j % kStages, ph = (j / kStages) & 1;
-        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.error, 1)) break;
-        const int tile = blockIdx.x + (j / num_k) * gridDim.x, ks = j % num_k;
-        const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-        mbar_expect_tx(raw_bar(s), kTileABytes + 2 * S::kTileBBytes);
-        tma_load_2d(stage_a(s), &tmA, raw_bar(s), ks * kBK, m0);
-        tma_load_2d(stage_bhi(s), &tmBhi, raw_bar(s), ks * kBK, n0);
-        tma_load_2d(stage_blo(s), &tmBlo, raw_bar(s), ks * kBK, n0);
-        issued = j + 1;
+      int step = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = decode_tile<BN>(batch, tile);
+        const TcProblem& P = batch.p[t.prob];
+        const uint32_t a_bytes = (uint32_t)P.R * P.q * kBK * 4;
+        for (int ks = 0; ks < t.num_k; ++ks, ++step) {
+          const int s = step % kStages, ph = (step / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, batch.error, 1)) { ok = false; break; }
+          mbar_expect_tx(raw_bar(s), a_bytes + 2 * S::kTileBBytes);
+          tma_load_3d(stage_a(s), &P.tmA, raw_bar(s), ks * kBK, 0, t.atom0);
+          tma_load_2d(stage_bhi(s), &P.tmBhi, raw_bar(s), ks * kBK, t.n0);
+          tma_load_2d(stage_blo(s), &P.tmBlo, raw_bar(s), ks * kBK, t.n0);
+        }
       }
       if (*abort_flag) {  // loads already issued must land before the CTA exits
-        for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
+        for (int j = step > kStages ? step - kStages : 0; j < step; ++j) {
           const int s = j % kStages, ph = (j / kStages) & 1;
           for (uint32_t it = 0; it < kSpinLimit; ++it)
             if (mbar_try_wait(raw_bar(s), ph)) break;
@@ -206,89 +237,116 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      for (int i = 0; i < total; ++i) {
-        const int s = i % kStages, ph = (i / kStages) & 1;
-        const int ks = i % num_k;
-        const int chunk = (i / num_k) * chunks_per_tile + ks / kChunk;  // flat chunk index of this CTA
-        const int a = chunk & 1;
-        const bool chunk_begin = (ks % kChunk) == 0;
-        const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == num_k - 1;
-        if (chunk_begin && !mbar_wait(acc_empty(a), ((chunk >> 1) & 1) ^ 1, abort_flag, p.error, 4)) break;
-        if (!mbar_wait(ready_bar(s), ph, abort_flag, p.error, 2)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d = tmem_base + a * BN;
+      int step = 0, chunk = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = decode_tile<BN>(batch, tile);
+        for (int ks = 0; ks < t.num_k; ++ks, ++step) {
+          const int s = step % kStages, ph = (step / kStages) & 1;
+          const int a = chunk & 1;
+          const bool chunk_begin = (ks % kChunk) == 0;
+          const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == t.num_k - 1;
+          if (chunk_begin && !mbar_wait(acc_empty(a), ((chunk >> 1) & 1) ^ 1, abort_flag, batch.error, 4)) { ok = false; break; }
+          if (!mbar_wait(ready_bar(s), ph, abort_flag, batch.error, 2)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t d = tmem_base + a * BN;
 #pragma unroll
-        for (int k8 = 0; k8 < kBK / 8; ++k8) {
-          const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
-          const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
-          umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
-          umma_tf32(d, da, dbl, idesc, 1u);
-          umma_tf32(d, dal, db, idesc, 1u);
+          for (int k8 = 0; k8 < kBK / 8; ++k8) {
+            const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
+            const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
+            umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
+            umma_tf32(d, da, dbl, idesc, 1u);
+            umma_tf32(d, dal, db, idesc, 1u);
+          }
+          umma_commit(empty_bar(s));  // ring slot reusable once these MMAs have read it
+          if (chunk_end) { umma_commit(acc_full(a)); ++chunk; }  // partial sum of this chunk complete
         }
-        umma_commit(empty_bar(s));             // ring slot reusable once these MMAs have read it
-        if (chunk_end) umma_commit(acc_full(a));  // partial sum of this chunk complete
       }
     }
-  } else if (warp < kEpiWarp0) {
+  } else if (warp < 4) {
     // ---- operand splitters: A = hi + lo with hi exact in TF32, element-wise and in place
-    const int t = tid - kSplitWarp0 * 32;
-    for (int i = 0; i < total; ++i) {
-      const int s = i % kStages, ph = (i / kStages) & 1;
-      if (!mbar_wait(raw_bar(s), ph, abort_flag, p.error, 3)) break;
-      float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
-      float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
+    const int t64 = tid - 64;
+    int step = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = decode_tile<BN>(batch, tile);
+      for (int ks = 0; ks < t.num_k; ++ks, ++step) {
+        const int s = step % kStages, ph = (step / kStages) & 1;
+        if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3)) { ok = false; break; }
+        float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
+        float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
 #pragma unroll
-      for (int j = 0; j < kTileABytes / 16 / 128; ++j) {
-        const int idx = t + j * 128;
-        const float4 v = a[idx];
-        float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
-        a[idx] = h;
-        alo[idx] = l;
+        for (int j = 0; j < kTileABytes / 16 / kSplitThreads; ++j) {
+          const int idx = t64 + j * kSplitThreads;
+          const float4 v = a[idx];
+          float4 h, l;
+          h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+          h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+          h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+          h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+          a[idx] = h;
+          alo[idx] = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+        mbar_arrive(ready_bar(s));
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-      mbar_arrive(ready_bar(s));
     }
   } else {
     // ---- epilogue: drain each chunk's partial sum from TMEM, add in FP32 registers, store at tile end
-    const int ew = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31; warps 6-9 cover all four quarters
+    const int ew = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     float accr[ONE_CHUNK ? 1 : BN];
-    const int n_chunks = my_tiles * chunks_per_tile;
-    for (int chunk = 0; chunk < n_chunks; ++chunk) {
-      const int a = chunk & 1;
-      const int tile_i = chunk / chunks_per_tile, cin = chunk % chunks_per_tile;
-      const int tile = blockIdx.x + tile_i * gridDim.x;
-      const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-      const int row = m0 + ew * 32 + lane;
-      float4* dst = reinterpret_cast<float4*>(p.C + (long long)row * p.ldc + n0);
-      if (!mbar_wait(acc_full(a), (chunk >> 1) & 1, abort_flag, p.error, 5)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    int chunk = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = decode_tile<BN>(batch, tile);
+      const TcProblem& P = batch.p[t.prob];
+      const int r = ew * 32 + lane;
+      const int al = r / P.q, m = r - al * P.q;
+      const bool valid = r < P.R * P.q && t.atom0 + al < P.n_atoms;
+      float* dst = P.C + (long long)(t.atom0 + al) * P.c_s1 + (long long)m * P.c_s2 + t.n0;
+      const float* bias = P.bias ? P.bias + t.n0 : nullptr;
+      const int n_chunks = (t.num_k + kChunk - 1) / kChunk;
+      for (int cin = 0; cin < n_chunks; ++cin, ++chunk) {
+        const int a = chunk & 1;
+        if (!mbar_wait(acc_full(a), (chunk >> 1) & 1, abort_flag, batch.error, 5)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(ew * 32) << 16) + a * BN + c * 32, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if constexpr (ONE_CHUNK) {
-          if (row < p.M) {
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t rr[32];
+          tmem_ld32(tmem_base + ((uint32_t)(ew * 32) << 16) + a * BN + c * 32, rr);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if constexpr (ONE_CHUNK) {
+            if (valid) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              dst[c * 8 + q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
-                                           __uint_as_float(r[4 * q + 3]));
+              for (int q4 = 0; q4 < 8; ++q4) {
+                float4 v = make_float4(__uint_as_float(rr[4 * q4]), __uint_as_float(rr[4 * q4 + 1]),
+                                       __uint_as_float(rr[4 * q4 + 2]), __uint_as_float(rr[4 * q4 + 3]));
+                if (bias) {
+                  const float4 bv = *reinterpret_cast<const float4*>(bias + c * 32 + 4 * q4);
+                  v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                }
+                *reinterpret_cast<float4*>(dst + c * 32 + 4 * q4) = v;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) accr[c * 32 + q] = cin == 0 ? __uint_as_float(rr[q]) : accr[c * 32 + q] + __uint_as_float(rr[q]);
           }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 32; ++q) accr[c * 32 + q] = cin == 0 ? __uint_as_float(r[q]) : accr[c * 32 + q] + __uint_as_float(r[q]);
         }
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(acc_empty(a));  // the issuer may overwrite this accumulator
-      if constexpr (!ONE_CHUNK) {
-        if (cin == chunks_per_tile - 1 && row < p.M) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(acc_empty(a));  // the issuer may overwrite this accumulator
+        if constexpr (!ONE_CHUNK) {
+          if (cin == n_chunks - 1 && valid) {
 #pragma unroll
-          for (int q = 0; q < BN / 4; ++q) dst[q] = make_float4(accr[4 * q], accr[4 * q + 1], accr[4 * q + 2], accr[4 * q + 3]);
+            for (int q4 = 0; q4 < BN / 4; ++q4) {
+              float4 v = make_float4(accr[4 * q4], accr[4 * q4 + 1], accr[4 * q4 + 2], accr[4 * q4 + 3]);
+              if (bias) {
+                const float4 bv = *reinterpret_cast<const float4*>(bias + 4 * q4);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              *reinterpret_cast<float4*>(dst + 4 * q4) = v;
+            }
+          }
         }
       }
     }
@@ -315,7 +373,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D fp32 tensor [rows][cols] with `ld` elements between rows; box = [box_rows][32 columns], 128-byte swizzle.
-bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows) {
+bool make_map_2d(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -326,41 +384,89 @@ bool make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// 3-D fp32 tensor [atoms][q][K]; box = [R atoms][q][32], 128-byte swizzle.
+bool make_map_3d(CUtensorMap* map, const float* ptr, long long atoms, int q, long long K, long long atom_stride,
+                 long long comp_stride, int R) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)q, (cuuint64_t)atoms};
+  const cuuint64_t strides[2] = {(cuuint64_t)(q == 1 ? atom_stride : comp_stride) * sizeof(float),
+                                 (cuuint64_t)atom_stride * sizeof(float)};
+  const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)q, (cuuint32_t)R};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 template <int BN, bool ONE_CHUNK>
-cudaError_t launch_tc(const CUtensorMap& a, const CUtensorMap& bh, const CUtensorMap& bl, const TcParams& p, int sms, cudaStream_t s) {
+cudaError_t launch_tc(const TcBatch& b, int sms, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, ONE_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const int tiles = ((p.M + kBM - 1) / kBM) * (p.N / BN);
+  const int tiles = b.tile_start[b.n_problems];
   const int grid = tiles < sms ? tiles : sms;
-  tc_gemm_kernel<BN, ONE_CHUNK><<<grid, kThreads, TcSmem<BN>::kTotal, s>>>(a, bh, bl, p);
+  tc_gemm_kernel<BN, ONE_CHUNK><<<grid, kThreads, TcSmem<BN>::kTotal, s>>>(b);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
-                           int N, int K, int* error_flag, cudaStream_t s) {
-  if (M <= 0) return cudaSuccess;
-  if (K % kBK != 0 || N % 64 != 0 || (lda % 4) != 0 || (ldc % 4) != 0 || !error_flag) return cudaErrorInvalidValue;
+bool tc_linear_supported(int N, int K) { return N % 64 == 0 && K % kBK == 0; }
+
+cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s) {
+  if (n_problems <= 0) return cudaSuccess;
+  if (n_problems > kTcMaxProblems || !error_flag) return cudaErrorInvalidValue;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return cudaErrorInvalidValue;
   }
-  const int bn = (N % 128 == 0) ? 128 : 64;
-  CUtensorMap ma, mbh, mbl;
-  if (!make_map(&ma, A, M, K, lda, kBM) || !make_map(&mbh, Bhi, N, K, K, bn) || !make_map(&mbl, Blo, N, K, K, bn))
-    return cudaErrorInvalidValue;
-  TcParams p{M, N, K, C, ldc, error_flag};
-  const bool one = K / kBK <= kChunk;
-  if (bn == 128) return one ? launch_tc<128, true>(ma, mbh, mbl, p, sms, s) : launch_tc<128, false>(ma, mbh, mbl, p, sms, s);
-  return one ? launch_tc<64, true>(ma, mbh, mbl, p, sms, s) : launch_tc<64, false>(ma, mbh, mbl, p, sms, s);
+  bool all128 = true, one = true;
+  for (int i = 0; i < n_problems; ++i) {
+    const TcLinearProblem& h = probs[i];
+    if (!tc_linear_supported(h.N, h.K) || h.q < 1 || h.q > 128 || (h.a_atom_stride & 3) || (h.a_comp_stride & 3) || (h.c_s1 & 3) ||
+        (h.c_s2 & 3))
+      return cudaErrorInvalidValue;
+    all128 = all128 && (h.N % 128 == 0);
+    one = one && (h.K / kBK <= kChunk);
+  }
+  const int bn = all128 ? 128 : 64;
+  TcBatch b;
+  memset(&b, 0, sizeof(b));
+  b.n_problems = 0;
+  b.error = error_flag;
+  int tiles = 0;
+  for (int i = 0; i < n_problems; ++i) {
+    const TcLinearProblem& h = probs[i];
+    if (h.n_atoms <= 0) continue;
+    TcProblem& P = b.p[b.n_problems];
+    P.q = h.q; P.R = kBM / h.q; P.n_atoms = (int)h.n_atoms; P.N = h.N; P.K = h.K;
+    P.C = h.C; P.bias = h.bias; P.c_s1 = h.c_s1; P.c_s2 = h.c_s2;
+    if (!make_map_3d(&P.tmA, h.A, h.n_atoms, h.q, h.K, h.a_atom_stride, h.a_comp_stride, P.R) ||
+        !make_map_2d(&P.tmBhi, h.Bhi, h.N, h.K, h.K, bn) || !make_map_2d(&P.tmBlo, h.Blo, h.N, h.K, h.K, bn))
+      return cudaErrorInvalidValue;
+    b.tile_start[b.n_problems] = tiles;
+    tiles += (int)((h.n_atoms + P.R - 1) / P.R) * (h.N / bn);
+    ++b.n_problems;
+  }
+  for (int i = b.n_problems; i <= kTcMaxProblems; ++i) b.tile_start[i] = tiles;
+  if (tiles == 0) return cudaSuccess;
+  if (bn == 128) return one ? launch_tc<128, true>(b, sms, s) : launch_tc<128, false>(b, sms, s);
+  return one ? launch_tc<64, true>(b, sms, s) : launch_tc<64, false>(b, sms, s);
+}
+
+cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
+                           int N, int K, int* error_flag, cudaStream_t s) {
+  if (M <= 0) return cudaSuccess;
+  TcLinearProblem h;
+  h.A = A; h.a_atom_stride = lda; h.a_comp_stride = lda; h.q = 1; h.n_atoms = M; h.K = K;
+  h.Bhi = Bhi; h.Blo = Blo; h.N = N; h.C = C; h.c_s1 = ldc; h.c_s2 = 0; h.bias = nullptr;
+  return launch_tc_linear(&h, 1, error_flag, s);
 }
 
 }  // namespace tace

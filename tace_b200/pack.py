@@ -154,6 +154,11 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
             for l, m in zip(lp.out_ls, split(g(pre + "resnetBB.weight"), [(C, C)] * len(lp.out_ls))):
                 put(tp + f"res.l{l}", m / math.sqrt(C), tp + f"resT.l{l}")
             out[tp + "res.b"] = g(pre + "resnetBB.bias")
+    # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
+    for name in list(out):
+        stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
+        if stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT") and name.split(".")[-1].startswith("l"):
+            out[name + "_hi"], out[name + "_lo"] = split_tf32(out[name])
     out["ro.W1"] = g("energy_readouts.0.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
     out["ro.W2"] = g("energy_readouts.0.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
     out["scale"] = g("scale_shift.scale")[0]

@@ -150,3 +150,10 @@ def test_full_size_properties_config2():
     n_per = (data["ptr"][1:] - data["ptr"][:-1]).float()
     assert ((c["energy"] - a["energy"]).abs() / n_per).max().item() <= 1e-5 * max(1.0, (a["energy"].abs() / n_per).max().item())
     assert (c["forces"] - a["forces"]).abs().max().item() <= 1e-4 * max(1.0, fscale)
+
+
+@pytest.mark.parametrize("L,C", [(2, 64), (3, 128)])
+def test_fp32_tensor_core_channel_widths(L, C):
+    """Channel counts for which fp32 models run the radial GEMMs and the per-rank linears on tcgen05."""
+    structs = synth.random_crystals(2, seed=9, nmin=6, nmax=12, zmax=2)
+    model_out, ref = run_case(structs, L, C, [1, 2], 4.5, torch.float32)
