@@ -49,14 +49,43 @@ __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   // channel-independent coupling rows G = K . Y consumed by the tensor-product kernels
   TPOf<L>::S::template build_G<T>(Y, a.G_scalar + e * TPOf<L>::S::NG);
   if (a.G_full) TPOf<L>::F::template build_G<T>(Y, a.G_full + e * TPOf<L>::F::NG);
+  a.dlen[e] = d;
+}
+
+// Radial basis and hidden layers of every layer's radial MLP (independent of L, so compiled once per dtype).
+template <typename T>
+__global__ void __launch_bounds__(128) edge_mlp_fwd_kernel(const EdgeArgs<T> a) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
   T b[kNumBessel];
-  radial_eval<T>(d, a.rp, b, nullptr);
+  radial_eval<T>(a.dlen[e], a.rp, b, nullptr);
   for (int t = 0; t < a.n_layers; ++t) {
     T h3[kHidden];
-    mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3);
+    mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3, a.Z[t] + e * 3 * kHidden);
     T* out = a.H3[t] + e * kHidden;
+#pragma unroll
     for (int j = 0; j < kHidden; ++j) out[j] = h3[j];
   }
+}
+
+// dE/dd through every layer's radial MLP and the radial basis.
+template <typename T>
+__global__ void __launch_bounds__(128) edge_mlp_bwd_kernel(const EdgeArgs<T> a) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  T b[kNumBessel], dbdd[kNumBessel];
+  radial_eval<T>(a.dlen[e], a.rp, b, dbdd);
+  T dd = T(0);
+  for (int t = 0; t < a.n_layers; ++t) {
+    T dh3[kHidden], db[kNumBessel];
+    const T* in = a.dH3[t] + e * kHidden;
+#pragma unroll
+    for (int j4 = 0; j4 < kHidden / 4; ++j4) ld4(in + 4 * j4, dh3[4 * j4], dh3[4 * j4 + 1], dh3[4 * j4 + 2], dh3[4 * j4 + 3]);
+    mlp_hidden_bwd<T>(a.Z[t] + e * 3 * kHidden, a.mlp[t].A0, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
+#pragma unroll
+    for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
+  }
+  a.ddlen[e] = dd;
 }
 
 template <typename T, int L>
@@ -66,16 +95,7 @@ __global__ void __launch_bounds__(128) edge_bwd_kernel(const EdgeArgs<T> a) {
   if (e >= a.E) return;
   T v[3], d0, d;
   edge_geometry(a, e, v, d0, d);
-  T b[kNumBessel], dbdd[kNumBessel];
-  radial_eval<T>(d, a.rp, b, dbdd);
-  T dd = T(0);
-  for (int t = 0; t < a.n_layers; ++t) {
-    T dh3[kHidden], db[kNumBessel];
-    const T* in = a.dH3[t] + e * kHidden;
-    for (int j = 0; j < kHidden; ++j) dh3[j] = in[j];
-    mlp_hidden_bwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
-    for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
-  }
+  const T dd = a.ddlen[e];
   const T inv = T(1) / d;
   T dY[D], dn[3], g[3];
 #pragma unroll
@@ -97,12 +117,14 @@ cudaError_t launch_edge_fwd(const EdgeArgs<T>& a, cudaStream_t s) {
   else if (a.L == 2) edge_fwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
   else if (a.L == 3) edge_fwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);
   else return cudaErrorInvalidValue;
+  edge_mlp_fwd_kernel<T><<<grid, 128, 0, s>>>(a);
   return cudaGetLastError();
 }
 template <typename T>
 cudaError_t launch_edge_bwd(const EdgeArgs<T>& a, cudaStream_t s) {
   if (a.E <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)((a.E + 127) / 128);
+  edge_mlp_bwd_kernel<T><<<grid, 128, 0, s>>>(a);
   if (a.L == 1) edge_bwd_kernel<T, 1><<<grid, 128, 0, s>>>(a);
   else if (a.L == 2) edge_bwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
   else if (a.L == 3) edge_bwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);

@@ -263,13 +263,13 @@ struct Model : ModelBase {
 
   // ---- workspace ---------------------------------------------------------------------------
   struct LayerBufs {
-    T *h_in, *x, *xx, *gxx, *W, *H3, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
+    T *h_in, *x, *xx, *gxx, *W, *H3, *Zmlp, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr;
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *G_scalar, *G_full, *dxe;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *G_scalar, *G_full, *dxe, *dlen, *ddlen;
     std::vector<LayerBufs> lay;
   };
 
@@ -281,6 +281,7 @@ struct Model : ModelBase {
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
+    b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
     b.G_scalar = ar.take<T>((size_t)E * layers[0].tp.NG);
     b.G_full = NL_ > 1 ? ar.take<T>((size_t)E * layers[1].tp.NG) : nullptr;
     b.dxe = NL_ > 1 ? ar.take<T>((size_t)E * D * C) : nullptr;  // per-edge gradient rows of the source features
@@ -298,6 +299,7 @@ struct Model : ModelBase {
       lb.xx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.gxx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.H3 = ar.take<T>((size_t)E * kHidden);
+      lb.Zmlp = ar.take<T>((size_t)E * 3 * kHidden);
       lb.W = ar.take<T>((size_t)E * p.tp.NP * C);
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
@@ -438,11 +440,13 @@ struct Model : ModelBase {
       const std::string pre = "t" + std::to_string(t) + ".";
       ea.mlp[t] = {w(pre + "A0"), w(pre + "A1"), w(pre + "A2"), w(pre + "A1t"), w(pre + "A2t")};
       ea.H3[t] = b.lay[t].H3;
+      ea.Z[t] = b.lay[t].Zmlp;
       ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
     }
-    ea.G_scalar = b.G_scalar; ea.G_full = b.G_full;
+    ea.G_scalar = b.G_scalar; ea.G_full = b.G_full; ea.dlen = b.dlen; ea.ddlen = b.ddlen;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
+    ++launches;  // geometry kernel + radial-MLP kernel
     debug.push_back({"Y", b.Y, (long long)D * E});
     debug.push_back({"vec", b.vec, 3 * E});
 
@@ -668,6 +672,7 @@ struct Model : ModelBase {
     // ---- back to the edge vectors, then forces and virials
     PH("edge_bwd");
     CKL(launch_edge_bwd(ea, s));
+    ++launches;
     debug.push_back({"g", b.g, 3 * E});
     PH("forces");
     const bool want_virial = (o->virials || o->stress) && !vec_mode;

@@ -87,11 +87,14 @@ struct EdgeArgs {
   const T* edge_vector;  // [E][3] caller order, or nullptr
   RadialParams<T> rp;
   MlpWeights<T> mlp[kMaxLayers];
+  T* dlen;               // [E] edge length |v| + 1e-9
+  T* ddlen;              // [E] dE/d(edge length) through the radial branch (backward)
   T* vec;                // [E][3] edge vectors (target-sorted order)
   T* Y;                  // [E][D]
   T* G_scalar;           // [E][NG] coupling rows for the scalar-source layer (TPX_L*_S::build_G)
   T* G_full;             // [E][NG] coupling rows for the full-source layers, or nullptr
   T* H3[kMaxLayers];     // [E][64] last hidden activation of each layer's radial MLP
+  T* Z[kMaxLayers];      // [E][192] pre-activations of the three hidden layers, kept for the backward pass
   // backward
   const T* dH3[kMaxLayers];
   const T* dY;           // [E][D]

@@ -132,70 +132,66 @@ TACE_HD TACE_INLINE void radial_eval(const T d, const RadialParams<T>& rp, T (&b
 }
 
 // ---- radial MLP hidden layers ---------------------------------------------------
-// Weights are stored [in][out] with the 1/sqrt(fan_in) and sqrt(2) gains folded in.
-// z3 (pre-activation of the third layer) -> h3 = silu(z3) feeds the last-layer GEMM.
-template <typename T>
-TACE_HD TACE_INLINE void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
-                                   const T* __restrict__ A2, T (&h3)[kHidden]) {
-  T h1[kHidden], h2[kHidden];
+// Weights are stored [in][out] with the 1/sqrt(fan_in) and sqrt(2) gains folded in.  Everything is
+// kept in registers: y = x @ A is evaluated as a sum of outer-product rows, so the 64 outputs are
+// statically indexed accumulators and each weight row is read with 16-byte loads (every thread of a
+// warp reads the same address, i.e. one broadcast transaction per load).
+template <typename T, int K>
+TACE_HD TACE_INLINE void matvec64(const T (&x)[K], const T* __restrict__ A, T (&y)[kHidden]) {
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) {
-    T s = T(0);
+  for (int j = 0; j < kHidden; ++j) y[j] = T(0);
+#pragma unroll 1
+  for (int k = 0; k < K; ++k) {  // rolled: x sits in local memory (one read per 64 FMAs), y in registers
+    const T xk = x[k];
 #pragma unroll
-    for (int k = 0; k < kNumBessel; ++k) s += b[k] * A0[k * kHidden + j];
-    h1[j] = silu_(s);
-  }
-#pragma unroll 4
-  for (int j = 0; j < kHidden; ++j) {
-    T s = T(0);
-#pragma unroll
-    for (int k = 0; k < kHidden; ++k) s += h1[k] * A1[k * kHidden + j];
-    h2[j] = silu_(s);
-  }
-#pragma unroll 4
-  for (int j = 0; j < kHidden; ++j) {
-    T s = T(0);
-#pragma unroll
-    for (int k = 0; k < kHidden; ++k) s += h2[k] * A2[k * kHidden + j];
-    h3[j] = silu_(s);
+    for (int j4 = 0; j4 < kHidden / 4; ++j4) {
+      T a0, a1, a2, a3;
+      ld4(A + k * kHidden + 4 * j4, a0, a1, a2, a3);
+      y[4 * j4] += xk * a0; y[4 * j4 + 1] += xk * a1; y[4 * j4 + 2] += xk * a2; y[4 * j4 + 3] += xk * a3;
+    }
   }
 }
 
-// Given dE/dh3, returns dE/db by recomputing the hidden activations.
+// Forward: h3 = silu(z3) feeds the last-layer GEMM; the pre-activations z1 | z2 | z3 are written to
+// `zsave` (192 values, 16-byte aligned) for the backward pass when it is not null.
+template <typename T>
+TACE_HD TACE_INLINE void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
+                                   const T* __restrict__ A2, T (&h3)[kHidden], T* __restrict__ zsave) {
+  T z[kHidden], h[kHidden];
+  matvec64<T, kNumBessel>(b, A0, z);
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[j] = z[j]; h[j] = silu_(z[j]); }
+  matvec64<T, kHidden>(h, A1, z);
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[kHidden + j] = z[j]; h[j] = silu_(z[j]); }
+  matvec64<T, kHidden>(h, A2, z);
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[2 * kHidden + j] = z[j]; h3[j] = silu_(z[j]); }
+}
+
+// Backward: given dE/dh3 and the saved pre-activations, returns dE/db.
 // A1t / A2t are the transposed ([out][in]) copies of A1 / A2; A0 is used as stored.
 template <typename T>
-TACE_HD TACE_INLINE void mlp_hidden_bwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
-                                   const T* __restrict__ A2, const T* __restrict__ A1t, const T* __restrict__ A2t,
-                                   const T (&dh3)[kHidden], T (&db)[kNumBessel]) {
-  T z1[kHidden], h1[kHidden], z2[kHidden], h2[kHidden], t[kHidden];
-  for (int j = 0; j < kHidden; ++j) {
-    T s = T(0);
-    for (int k = 0; k < kNumBessel; ++k) s += b[k] * A0[k * kHidden + j];
-    z1[j] = s; h1[j] = silu_(s);
-  }
-  for (int j = 0; j < kHidden; ++j) {
-    T s = T(0);
-    for (int k = 0; k < kHidden; ++k) s += h1[k] * A1[k * kHidden + j];
-    z2[j] = s; h2[j] = silu_(s);
-  }
-  for (int j = 0; j < kHidden; ++j) {  // t = dE/dz3
-    T s = T(0);
-    for (int k = 0; k < kHidden; ++k) s += h2[k] * A2[k * kHidden + j];
-    t[j] = dh3[j] * silu_grad_(s);
-  }
-  for (int k = 0; k < kHidden; ++k) {  // h2 <- dE/dz2
-    T s = T(0);
-    for (int j = 0; j < kHidden; ++j) s += t[j] * A2t[j * kHidden + k];
-    h2[k] = s * silu_grad_(z2[k]);
-  }
-  for (int k = 0; k < kHidden; ++k) {  // h1 <- dE/dz1
-    T s = T(0);
-    for (int j = 0; j < kHidden; ++j) s += h2[j] * A1t[j * kHidden + k];
-    h1[k] = s * silu_grad_(z1[k]);
-  }
+TACE_HD TACE_INLINE void mlp_hidden_bwd(const T* __restrict__ zsave, const T* __restrict__ A0, const T* __restrict__ A1t,
+                                   const T* __restrict__ A2t, const T (&dh3)[kHidden], T (&db)[kNumBessel]) {
+  T dz[kHidden], dh[kHidden];
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh3[j] * silu_grad_(zsave[2 * kHidden + j]);
+  matvec64<T, kHidden>(dz, A2t, dh);
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[kHidden + j]);
+  matvec64<T, kHidden>(dz, A1t, dh);
+#pragma unroll
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[j]);
+#pragma unroll
   for (int k = 0; k < kNumBessel; ++k) {
     T s = T(0);
-    for (int j = 0; j < kHidden; ++j) s += h1[j] * A0[k * kHidden + j];
+#pragma unroll
+    for (int j4 = 0; j4 < kHidden / 4; ++j4) {
+      T a0, a1, a2, a3;
+      ld4(A0 + k * kHidden + 4 * j4, a0, a1, a2, a3);
+      s += dz[4 * j4] * a0 + dz[4 * j4 + 1] * a1 + dz[4 * j4 + 2] * a2 + dz[4 * j4 + 3] * a3;
+    }
     db[k] = s;
   }
 }

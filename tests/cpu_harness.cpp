@@ -104,9 +104,11 @@ void h_radial(double d, double rc, int p, double* b, double* db) {
 void h_mlp(const double* b, const double* A0, const double* A1, const double* A2, const double* A1t,
            const double* A2t, const double* dh3, double* h3, double* db) {
   double bb[kNumBessel], hh[kHidden], dh[kHidden], dbb[kNumBessel];
+  alignas(16) double zs[3 * kHidden];
   memcpy(bb, b, sizeof bb); memcpy(dh, dh3, sizeof dh);
-  mlp_hidden_fwd<double>(bb, A0, A1, A2, hh);
-  mlp_hidden_bwd<double>(bb, A0, A1, A2, A1t, A2t, dh, dbb);
+  (void)A1; (void)A2;
+  mlp_hidden_fwd<double>(bb, A0, A1, A2, hh, zs);
+  mlp_hidden_bwd<double>(zs, A0, A1t, A2t, dh, dbb);
   memcpy(h3, hh, sizeof hh); memcpy(db, dbb, sizeof dbb);
 }
 
