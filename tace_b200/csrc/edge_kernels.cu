@@ -5,7 +5,6 @@
 // from global memory: every thread of a warp reads the same address, so each load is one
 // L1-resident broadcast.
 #include "kernels.h"
-#include "tp_gen.cuh"
 
 namespace tace {
 
@@ -28,11 +27,6 @@ __device__ __forceinline__ void edge_geometry(const EdgeArgs<T>& a, long long e,
   d = d0 + T(1e-9);  // tace/models/adapter.py:347
 }
 
-template <int L> struct TPOf;
-template <> struct TPOf<1> { using S = TPX_L1_S; using F = TPX_L1_F; };
-template <> struct TPOf<2> { using S = TPX_L2_S; using F = TPX_L2_F; };
-template <> struct TPOf<3> { using S = TPX_L3_S; using F = TPX_L3_F; };
-
 template <typename T, int L>
 __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   constexpr int D = (L + 1) * (L + 1);
@@ -46,25 +40,36 @@ __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   sh_eval<T, L>(v[0] * inv, v[1] * inv, v[2] * inv, Y);
 #pragma unroll
   for (int k = 0; k < D; ++k) a.Y[e * D + k] = Y[k];
-  // channel-independent coupling rows G = K . Y consumed by the tensor-product kernels
-  TPOf<L>::S::template build_G<T>(Y, a.G_scalar + e * TPOf<L>::S::NG);
-  if (a.G_full) TPOf<L>::F::template build_G<T>(Y, a.G_full + e * TPOf<L>::F::NG);
   a.dlen[e] = d;
 }
 
 // Radial basis and hidden layers of every layer's radial MLP (independent of L, so compiled once per dtype).
 template <typename T>
 __global__ void __launch_bounds__(128) edge_mlp_fwd_kernel(const EdgeArgs<T> a) {
-  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (e >= a.E) return;
+  // Per-thread rows would be written 16 bytes at a time to 32 different lines per warp; instead the
+  // pre-activations go out component-major (consecutive edges contiguous) and the [edge][64] activation
+  // rows the GEMM needs are transposed through shared memory and written as one contiguous block.
+  __shared__ T tile[64][kHidden + 1];
+  const long long e0 = blockIdx.x * (long long)blockDim.x;
+  const long long e = e0 + threadIdx.x;
+  const bool live = e < a.E;
   T b[kNumBessel];
-  radial_eval<T>(a.dlen[e], a.rp, b, nullptr);
+  if (live) radial_eval<T>(a.dlen[e], a.rp, b, nullptr);
   for (int t = 0; t < a.n_layers; ++t) {
     T h3[kHidden];
-    mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3, a.Z[t] + e * 3 * kHidden);
-    T* out = a.H3[t] + e * kHidden;
+    if (live) mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3, a.Z[t] + e, a.E);
+    for (int half = 0; half < 2; ++half) {  // 64 rows at a time through the shared tile
+      if (live && (threadIdx.x >> 6) == half) {
 #pragma unroll
-    for (int j = 0; j < kHidden; ++j) out[j] = h3[j];
+        for (int j = 0; j < kHidden; ++j) tile[threadIdx.x & 63][j] = h3[j];
+      }
+      __syncthreads();
+      const long long r0 = e0 + 64 * half;
+      const long long n_live = a.E - r0 < 64 ? a.E - r0 : 64;
+      T* out = a.H3[t] + r0 * kHidden;
+      for (long long idx = threadIdx.x; idx < n_live * kHidden; idx += blockDim.x) out[idx] = tile[idx / kHidden][idx % kHidden];
+      __syncthreads();
+    }
   }
 }
 
@@ -81,7 +86,7 @@ __global__ void __launch_bounds__(128) edge_mlp_bwd_kernel(const EdgeArgs<T> a) 
     const T* in = a.dH3[t] + e * kHidden;
 #pragma unroll
     for (int j4 = 0; j4 < kHidden / 4; ++j4) ld4(in + 4 * j4, dh3[4 * j4], dh3[4 * j4 + 1], dh3[4 * j4 + 2], dh3[4 * j4 + 3]);
-    mlp_hidden_bwd<T>(a.Z[t] + e * 3 * kHidden, a.mlp[t].A0, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
+    mlp_hidden_bwd<T>(a.Z[t] + e, a.E, a.mlp[t].A0, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
 #pragma unroll
     for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
   }

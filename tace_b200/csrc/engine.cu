@@ -269,7 +269,7 @@ struct Model : ModelBase {
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr;
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *G_scalar, *G_full, *dxe, *dlen, *ddlen;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen;
     std::vector<LayerBufs> lay;
   };
 
@@ -282,8 +282,6 @@ struct Model : ModelBase {
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
-    b.G_scalar = ar.take<T>((size_t)E * layers[0].tp.NG);
-    b.G_full = NL_ > 1 ? ar.take<T>((size_t)E * layers[1].tp.NG) : nullptr;
     b.dxe = NL_ > 1 ? ar.take<T>((size_t)E * D * C) : nullptr;  // per-edge gradient rows of the source features
     b.lay.resize(NL_);
     T* prev_h = ar.take<T>((size_t)N * C);   // h_0: species embedding, scalar channels
@@ -443,7 +441,7 @@ struct Model : ModelBase {
       ea.Z[t] = b.lay[t].Zmlp;
       ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
     }
-    ea.G_scalar = b.G_scalar; ea.G_full = b.G_full; ea.dlen = b.dlen; ea.ddlen = b.ddlen;
+    ea.dlen = b.dlen; ea.ddlen = b.ddlen;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
     ++launches;  // geometry kernel + radial-MLP kernel
@@ -491,7 +489,7 @@ struct Model : ModelBase {
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
       ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
-      ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full; ta.W = lb.W; ta.x = x_src; ta.M = lb.M;
+      ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M;
       CKL(launch_tp_fwd(ta, s));
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
@@ -628,7 +626,7 @@ struct Model : ModelBase {
       PH(("t" + ts + ".bwd.tp").c_str());
       TPArgs<T> ta;
       memset(&ta, 0, sizeof(ta));
-      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.G = p.scalar_src ? b.G_scalar : b.G_full;
+      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
       ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.dW = lb.W; ta.dY = b.dY;
       ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
       CKL(launch_tp_bwd(ta, s));

@@ -176,11 +176,26 @@ def gen_interaction(L, scalar_src, out):
     for name, arr in [("GOFF", grp_goff), ("GCNT", [((c + 3) // 4) * 4 for c in grp_gcnt]), ("P0", grp_p0), ("NPG", grp_np),
                       ("M0", grp_m0), ("NMG", grp_nm)]:
         o(f"  static constexpr int {name}0 = {arr[0]}, {name}1 = {arr[-1]};")
-    # build_G
+    # build_G in parts: each output group's entries are cut into two halves so that four threads (two per
+    # group) can build one edge's row cooperatively inside the tensor-product kernels
+    part_bounds = []
+    for g in range(ngrp):
+        lo, hi = grp_goff[g], grp_goff[g] + ((grp_gcnt[g] + 3) // 4) * 4
+        mid = lo + (((hi - lo) // 2 + 3) // 4) * 4
+        part_bounds += [(lo, mid), (mid, hi)]
+    o(f"  static constexpr int NPART = {len(part_bounds)};")
+    o(f"  template <int PART, typename T> static TACE_HD TACE_INLINE void build_G_part(const T* __restrict__ Y, T* __restrict__ G) {{")
+    for pi, (lo, hi) in enumerate(part_bounds):
+        o(f"    if constexpr (PART == {pi}) {{")
+        for i in range(lo, hi):
+            t = terms[i]
+            expr = " + ".join(f"{lit(float(c))} * Y[{y}]" for y, c in t) if t else "T(0)"
+            o(f"      G[{i}] = {expr};")
+        o("    }")
+    o("  }")
     o(f"  template <typename T> static TACE_HD TACE_INLINE void build_G(const T (&Y)[{D}], T* __restrict__ G) {{")
-    for i, t in enumerate(terms):
-        expr = " + ".join(f"{lit(float(c))} * Y[{y}]" for y, c in t) if t else "T(0)"
-        o(f"    G[{i}] = {expr};")
+    for pi in range(len(part_bounds)):
+        o(f"    build_G_part<{pi}, T>(Y, G);")
     o("  }")
 
     def load_G(lo, hi, loaded):

@@ -18,7 +18,7 @@ struct TPArgs {
   int n_seg;          // number of target atoms = thread blocks (per output group)
   const int* rowptr;  // [n_seg+1] CSR over the edges of each target (edges are target-sorted)
   const int* e_src;   // [E] source atom of each edge
-  const T* G;         // [E][NG] channel-independent coupling of each edge (TPX::build_G)
+  const T* Y;         // [E][D] spherical harmonics of each edge
   const T* W;         // [E][NP*C] per-edge path weights
   const T* x;         // [N][NX][C] source features
   T* M;               // forward output [n_seg][NM][C]
@@ -91,10 +91,8 @@ struct EdgeArgs {
   T* ddlen;              // [E] dE/d(edge length) through the radial branch (backward)
   T* vec;                // [E][3] edge vectors (target-sorted order)
   T* Y;                  // [E][D]
-  T* G_scalar;           // [E][NG] coupling rows for the scalar-source layer (TPX_L*_S::build_G)
-  T* G_full;             // [E][NG] coupling rows for the full-source layers, or nullptr
   T* H3[kMaxLayers];     // [E][64] last hidden activation of each layer's radial MLP
-  T* Z[kMaxLayers];      // [E][192] pre-activations of the three hidden layers, kept for the backward pass
+  T* Z[kMaxLayers];      // [192][E] pre-activations of the three hidden layers (component-major), kept for the backward pass
   // backward
   const T* dH3[kMaxLayers];
   const T* dY;           // [E][D]

@@ -152,37 +152,37 @@ TACE_HD TACE_INLINE void matvec64(const T (&x)[K], const T* __restrict__ A, T (&
   }
 }
 
-// Forward: h3 = silu(z3) feeds the last-layer GEMM; the pre-activations z1 | z2 | z3 are written to
-// `zsave` (192 values, 16-byte aligned) for the backward pass when it is not null.
+// Forward: h3 = silu(z3) feeds the last-layer GEMM; the pre-activations z1 | z2 | z3 (192 values) are
+// written for the backward pass to zsave[k * zstride], k = 0..191.
 template <typename T>
 TACE_HD TACE_INLINE void mlp_hidden_fwd(const T (&b)[kNumBessel], const T* __restrict__ A0, const T* __restrict__ A1,
-                                   const T* __restrict__ A2, T (&h3)[kHidden], T* __restrict__ zsave) {
+                                   const T* __restrict__ A2, T (&h3)[kHidden], T* __restrict__ zsave, long long zstride) {
   T z[kHidden], h[kHidden];
   matvec64<T, kNumBessel>(b, A0, z);
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[j] = z[j]; h[j] = silu_(z[j]); }
+  for (int j = 0; j < kHidden; ++j) { zsave[j * zstride] = z[j]; h[j] = silu_(z[j]); }
   matvec64<T, kHidden>(h, A1, z);
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[kHidden + j] = z[j]; h[j] = silu_(z[j]); }
+  for (int j = 0; j < kHidden; ++j) { zsave[(kHidden + j) * zstride] = z[j]; h[j] = silu_(z[j]); }
   matvec64<T, kHidden>(h, A2, z);
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) { if (zsave) zsave[2 * kHidden + j] = z[j]; h3[j] = silu_(z[j]); }
+  for (int j = 0; j < kHidden; ++j) { zsave[(2 * kHidden + j) * zstride] = z[j]; h3[j] = silu_(z[j]); }
 }
 
 // Backward: given dE/dh3 and the saved pre-activations, returns dE/db.
 // A1t / A2t are the transposed ([out][in]) copies of A1 / A2; A0 is used as stored.
 template <typename T>
-TACE_HD TACE_INLINE void mlp_hidden_bwd(const T* __restrict__ zsave, const T* __restrict__ A0, const T* __restrict__ A1t,
+TACE_HD TACE_INLINE void mlp_hidden_bwd(const T* __restrict__ zsave, long long zstride, const T* __restrict__ A0, const T* __restrict__ A1t,
                                    const T* __restrict__ A2t, const T (&dh3)[kHidden], T (&db)[kNumBessel]) {
   T dz[kHidden], dh[kHidden];
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) dz[j] = dh3[j] * silu_grad_(zsave[2 * kHidden + j]);
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh3[j] * silu_grad_(zsave[(2 * kHidden + j) * zstride]);
   matvec64<T, kHidden>(dz, A2t, dh);
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[kHidden + j]);
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[(kHidden + j) * zstride]);
   matvec64<T, kHidden>(dz, A1t, dh);
 #pragma unroll
-  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[j]);
+  for (int j = 0; j < kHidden; ++j) dz[j] = dh[j] * silu_grad_(zsave[j * zstride]);
 #pragma unroll
   for (int k = 0; k < kNumBessel; ++k) {
     T s = T(0);

@@ -1,9 +1,8 @@
 // Interaction tensor-product kernels: forward message passing and its backward pass.
 //
 // One thread block per target atom, one thread per channel.  The channel-independent coupling
-// G_e = K . Y_e of every edge is computed once per evaluation (edge_kernels.cu) and stored as a
-// row of NG values; a block copies the rows of a batch of its edges into shared memory with
-// 128-bit loads, then every thread contracts its own channel with fully unrolled generated
+// G_e = K . Y_e of a batch of the block's edges is built in shared memory from the edges' spherical
+// harmonics by a few threads running generated straight-line code; then every thread contracts its own channel with fully unrolled generated
 // code (tp_gen.cuh) that reads G four entries at a time.
 //
 // Forward: the output ranks are split into (at most) two groups, one block per (target, group),
@@ -19,15 +18,20 @@ namespace tace {
 
 constexpr int kEdgeBatch = 8;
 
-// copy `count` (multiple of 4) entries starting at `offset` of the G rows of edges [e0, e0 + nb)
-template <typename T, int NG>
-__device__ __forceinline__ void stage_G(const T* __restrict__ G, int e0, int nb, int offset, int count, T* Gs) {
-  constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
-  const int per_edge = count / V;
-  for (int idx = threadIdx.x; idx < nb * per_edge; idx += blockDim.x) {
-    const int e = idx / per_edge, v = idx - e * per_edge;
-    const int4 val = *reinterpret_cast<const int4*>(G + (long long)(e0 + e) * NG + offset + v * V);
-    *reinterpret_cast<int4*>(Gs + e * NG + offset + v * V) = val;
+// Build the coupling rows G_e = K . Y_e of edges [e0, e0 + nb) in shared memory: the generated row
+// builder comes in TP::NPART parts (two per output group); parts [part0, part0 + nparts) are built, one
+// thread per (edge, part).
+template <typename T, typename TP>
+__device__ __forceinline__ void build_G_rows(const T* __restrict__ Y, int e0, int nb, int part0, int nparts, T* Gs) {
+  const int t = threadIdx.x;
+  if (t < nb * nparts) {
+    const int e = t / nparts, part = part0 + (t - e * nparts);
+    const T* Ye = Y + (long long)(e0 + e) * TP::D;
+    T* Ge = Gs + e * TP::NG;
+    if (part == 0) TP::template build_G_part<0, T>(Ye, Ge);
+    else if (part == 1) TP::template build_G_part<1, T>(Ye, Ge);
+    else if (part == 2) TP::template build_G_part<(TP::NPART > 2 ? 2 : 0), T>(Ye, Ge);
+    else TP::template build_G_part<(TP::NPART > 3 ? 3 : 0), T>(Ye, Ge);
   }
 }
 
@@ -35,7 +39,6 @@ template <typename T, typename TP, int GRP>
 __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
   constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
   constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
-  constexpr int GOFF = GRP == 0 ? TP::GOFF0 : TP::GOFF1, GCNT = GRP == 0 ? TP::GCNT0 : TP::GCNT1;
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   __shared__ __align__(16) T Gs[kEdgeBatch * TP::NG];
   __shared__ int esrc[kEdgeBatch];
@@ -47,7 +50,7 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
     if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
-    stage_G<T, TP::NG>(a.G, e0, nb, GOFF, GCNT, Gs);
+    build_G_rows<T, TP>(a.Y, e0, nb, 2 * GRP, 2, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
       const long long s = esrc[e];
@@ -83,7 +86,7 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
     if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
-    stage_G<T, TP::NG>(a.G, e0, nb, 0, TP::NG, Gs);
+    build_G_rows<T, TP>(a.Y, e0, nb, 0, TP::NPART, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
       const long long s = esrc[e];

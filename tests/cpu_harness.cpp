@@ -107,8 +107,8 @@ void h_mlp(const double* b, const double* A0, const double* A1, const double* A2
   alignas(16) double zs[3 * kHidden];
   memcpy(bb, b, sizeof bb); memcpy(dh, dh3, sizeof dh);
   (void)A1; (void)A2;
-  mlp_hidden_fwd<double>(bb, A0, A1, A2, hh, zs);
-  mlp_hidden_bwd<double>(zs, A0, A1t, A2t, dh, dbb);
+  mlp_hidden_fwd<double>(bb, A0, A1, A2, hh, zs, 1);
+  mlp_hidden_bwd<double>(zs, 1, A0, A1t, A2t, dh, dbb);
   memcpy(h3, hh, sizeof hh); memcpy(db, dbb, sizeof dbb);
 }
 
