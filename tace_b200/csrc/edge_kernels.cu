@@ -43,12 +43,11 @@ __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
   a.dlen[e] = d;
 }
 
-// Radial basis and hidden layers of every layer's radial MLP (independent of L, so compiled once per dtype).
+// First layer of every radial MLP (8 -> 64, no activation yet): z1 = b(d) @ A0.  One thread per edge; the
+// [edge][64] rows are transposed through shared memory so the block writes one contiguous chunk
+// instead of 32 scattered 16-byte pieces per warp store.  The 64 -> 64 layers run as GEMMs.
 template <typename T>
-__global__ void __launch_bounds__(128) edge_mlp_fwd_kernel(const EdgeArgs<T> a) {
-  // Per-thread rows would be written 16 bytes at a time to 32 different lines per warp; instead the
-  // pre-activations go out component-major (consecutive edges contiguous) and the [edge][64] activation
-  // rows the GEMM needs are transposed through shared memory and written as one contiguous block.
+__global__ void __launch_bounds__(128) edge_mlp_in_kernel(const EdgeArgs<T> a) {
   __shared__ T tile[64][kHidden + 1];
   const long long e0 = blockIdx.x * (long long)blockDim.x;
   const long long e = e0 + threadIdx.x;
@@ -56,41 +55,100 @@ __global__ void __launch_bounds__(128) edge_mlp_fwd_kernel(const EdgeArgs<T> a) 
   T b[kNumBessel];
   if (live) radial_eval<T>(a.dlen[e], a.rp, b, nullptr);
   for (int t = 0; t < a.n_layers; ++t) {
-    T h3[kHidden];
-    if (live) mlp_hidden_fwd<T>(b, a.mlp[t].A0, a.mlp[t].A1, a.mlp[t].A2, h3, a.Z[t] + e, a.E);
+    T z[kHidden];
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < kHidden; ++j) z[j] = T(0);
+#pragma unroll
+      for (int k = 0; k < kNumBessel; ++k)
+#pragma unroll
+        for (int j4 = 0; j4 < kHidden / 4; ++j4) {
+          T a0, a1, a2, a3;
+          ld4(a.mlp[t].A0 + k * kHidden + 4 * j4, a0, a1, a2, a3);
+          z[4 * j4] += b[k] * a0; z[4 * j4 + 1] += b[k] * a1; z[4 * j4 + 2] += b[k] * a2; z[4 * j4 + 3] += b[k] * a3;
+        }
+    }
     for (int half = 0; half < 2; ++half) {  // 64 rows at a time through the shared tile
       if (live && (threadIdx.x >> 6) == half) {
 #pragma unroll
-        for (int j = 0; j < kHidden; ++j) tile[threadIdx.x & 63][j] = h3[j];
+        for (int j = 0; j < kHidden; ++j) tile[threadIdx.x & 63][j] = z[j];
       }
       __syncthreads();
       const long long r0 = e0 + 64 * half;
       const long long n_live = a.E - r0 < 64 ? a.E - r0 : 64;
-      T* out = a.H3[t] + r0 * kHidden;
+      T* out = a.Z1[t] + r0 * kHidden;
       for (long long idx = threadIdx.x; idx < n_live * kHidden; idx += blockDim.x) out[idx] = tile[idx / kHidden][idx % kHidden];
       __syncthreads();
     }
   }
 }
 
-// dE/dd through every layer's radial MLP and the radial basis.
+// dE/dd: back through the first MLP layer and the radial basis.  dH1 = dE/d(silu(z1)).
 template <typename T>
-__global__ void __launch_bounds__(128) edge_mlp_bwd_kernel(const EdgeArgs<T> a) {
+__global__ void __launch_bounds__(128) edge_mlp_out_kernel(const EdgeArgs<T> a) {
   const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (e >= a.E) return;
   T b[kNumBessel], dbdd[kNumBessel];
   radial_eval<T>(a.dlen[e], a.rp, b, dbdd);
   T dd = T(0);
   for (int t = 0; t < a.n_layers; ++t) {
-    T dh3[kHidden], db[kNumBessel];
-    const T* in = a.dH3[t] + e * kHidden;
+    const T* g = a.dH1[t] + e * kHidden;
+    const T* z = a.Z1[t] + e * kHidden;
+    T db[kNumBessel];
 #pragma unroll
-    for (int j4 = 0; j4 < kHidden / 4; ++j4) ld4(in + 4 * j4, dh3[4 * j4], dh3[4 * j4 + 1], dh3[4 * j4 + 2], dh3[4 * j4 + 3]);
-    mlp_hidden_bwd<T>(a.Z[t] + e, a.E, a.mlp[t].A0, a.mlp[t].A1t, a.mlp[t].A2t, dh3, db);
+    for (int k = 0; k < kNumBessel; ++k) db[k] = T(0);
+#pragma unroll
+    for (int j4 = 0; j4 < kHidden / 4; ++j4) {
+      T g0, g1, g2, g3, z0, z1, z2, z3;
+      ld4(g + 4 * j4, g0, g1, g2, g3);
+      ld4(z + 4 * j4, z0, z1, z2, z3);
+      const T d0 = g0 * silu_grad_(z0), d1 = g1 * silu_grad_(z1), d2 = g2 * silu_grad_(z2), d3 = g3 * silu_grad_(z3);
+#pragma unroll
+      for (int k = 0; k < kNumBessel; ++k) {
+        T a0, a1, a2, a3;
+        ld4(a.mlp[t].A0 + k * kHidden + 4 * j4, a0, a1, a2, a3);
+        db[k] += d0 * a0 + d1 * a1 + d2 * a2 + d3 * a3;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
   }
   a.ddlen[e] = dd;
+}
+
+template <typename T>
+__global__ void silu_kernel(const T* __restrict__ in, T* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) out[i] = silu_(in[i]);
+}
+template <typename T>
+__global__ void silu_grad_mul_kernel(T* __restrict__ g, const T* __restrict__ z, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) g[i] *= silu_grad_(z[i]);
+}
+template <typename T>
+cudaError_t launch_silu(const T* in, T* out, long long n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const long long blocks = (n + 255) / 256;
+  silu_kernel<T><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(in, out, n);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_silu_grad_mul(T* g, const T* z, long long n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const long long blocks = (n + 255) / 256;
+  silu_grad_mul_kernel<T><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(g, z, n);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_edge_mlp_in(const EdgeArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  edge_mlp_in_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_edge_mlp_out(const EdgeArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  edge_mlp_out_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a);
+  return cudaGetLastError();
 }
 
 template <typename T, int L>
@@ -122,14 +180,12 @@ cudaError_t launch_edge_fwd(const EdgeArgs<T>& a, cudaStream_t s) {
   else if (a.L == 2) edge_fwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
   else if (a.L == 3) edge_fwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);
   else return cudaErrorInvalidValue;
-  edge_mlp_fwd_kernel<T><<<grid, 128, 0, s>>>(a);
   return cudaGetLastError();
 }
 template <typename T>
 cudaError_t launch_edge_bwd(const EdgeArgs<T>& a, cudaStream_t s) {
   if (a.E <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)((a.E + 127) / 128);
-  edge_mlp_bwd_kernel<T><<<grid, 128, 0, s>>>(a);
   if (a.L == 1) edge_bwd_kernel<T, 1><<<grid, 128, 0, s>>>(a);
   else if (a.L == 2) edge_bwd_kernel<T, 2><<<grid, 128, 0, s>>>(a);
   else if (a.L == 3) edge_bwd_kernel<T, 3><<<grid, 128, 0, s>>>(a);
@@ -218,6 +274,10 @@ cudaError_t launch_graph_virial(const T* atom_virial, const int* graph_ptr, cons
 #define INST(T)                                                                                      \
   template cudaError_t launch_edge_fwd<T>(const EdgeArgs<T>&, cudaStream_t);                         \
   template cudaError_t launch_edge_bwd<T>(const EdgeArgs<T>&, cudaStream_t);                         \
+  template cudaError_t launch_edge_mlp_in<T>(const EdgeArgs<T>&, cudaStream_t);                      \
+  template cudaError_t launch_edge_mlp_out<T>(const EdgeArgs<T>&, cudaStream_t);                     \
+  template cudaError_t launch_silu<T>(const T*, T*, long long, cudaStream_t);                        \
+  template cudaError_t launch_silu_grad_mul<T>(T*, const T*, long long, cudaStream_t);               \
   template cudaError_t launch_forces<T>(const ForceArgs<T>&, cudaStream_t);                          \
   template cudaError_t launch_graph_virial<T>(const T*, const int*, const T*, T*, T*, int, cudaStream_t);
 INST(float)

@@ -186,10 +186,10 @@ struct Model : ModelBase {
       for (int l : p.in_ls) { add_linear_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_linear_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
       add_weight(pre + "up.b", C);
       add_weight(pre + "A0", kNumBessel * kHidden);
-      add_weight(pre + "A1", kHidden * kHidden);
-      add_weight(pre + "A2", kHidden * kHidden);
-      add_weight(pre + "A1t", kHidden * kHidden);
-      add_weight(pre + "A2t", kHidden * kHidden);
+      add_linear_weight(pre + "A1", kHidden * kHidden);
+      add_linear_weight(pre + "A2", kHidden * kHidden);
+      add_linear_weight(pre + "A1t", kHidden * kHidden);
+      add_linear_weight(pre + "A2t", kHidden * kHidden);
       add_weight(pre + "W3", (long long)kHidden * p.tp.NP * C);
       add_weight(pre + "W3t", (long long)kHidden * p.tp.NP * C);
       if (kTensorCore) {  // TF32 high parts and residuals of both orientations
@@ -263,7 +263,7 @@ struct Model : ModelBase {
 
   // ---- workspace ---------------------------------------------------------------------------
   struct LayerBufs {
-    T *h_in, *x, *xx, *gxx, *W, *H3, *Zmlp, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
+    T *h_in, *x, *xx, *gxx, *W, *H3, *Z1, *Z2, *Z3, *Hact, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
   };
   struct Bufs {
@@ -297,7 +297,8 @@ struct Model : ModelBase {
       lb.xx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.gxx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.H3 = ar.take<T>((size_t)E * kHidden);
-      lb.Zmlp = ar.take<T>((size_t)E * 3 * kHidden);
+      lb.Z1 = ar.take<T>((size_t)E * kHidden); lb.Z2 = ar.take<T>((size_t)E * kHidden);
+      lb.Z3 = ar.take<T>((size_t)E * kHidden); lb.Hact = ar.take<T>((size_t)E * kHidden);
       lb.W = ar.take<T>((size_t)E * p.tp.NP * C);
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
@@ -437,14 +438,34 @@ struct Model : ModelBase {
     for (int t = 0; t < NL_; ++t) {
       const std::string pre = "t" + std::to_string(t) + ".";
       ea.mlp[t] = {w(pre + "A0"), w(pre + "A1"), w(pre + "A2"), w(pre + "A1t"), w(pre + "A2t")};
-      ea.H3[t] = b.lay[t].H3;
-      ea.Z[t] = b.lay[t].Zmlp;
-      ea.dH3[t] = b.lay[t].H3;  // the gradient overwrites the activation in the backward pass
+      ea.Z1[t] = b.lay[t].Z1;
+      ea.dH1[t] = b.lay[t].Z3;  // the backward pass reuses the third pre-activation buffer for dE/dh1
     }
     ea.dlen = b.dlen; ea.ddlen = b.ddlen;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
-    ++launches;  // geometry kernel + radial-MLP kernel
+    // radial MLP hidden layers 8 -> 64 -> 64 -> 64 (tace/models/mlp.py:136-191): the first layer per edge, the
+    // two 64 x 64 layers as GEMMs over all edges (all interaction layers in one launch), SiLU in between
+    PH("radial_mlp_fwd");
+    CKL(launch_edge_mlp_in(ea, s));
+    {
+      const long long n64 = E * kHidden;
+      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z1, b.lay[t].Hact, n64, s));
+      std::vector<LinSpec> sp;
+      for (int t = 0; t < NL_; ++t) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1", pre + "A1t", kHidden, b.lay[t].Z2, kHidden, 0, nullptr});
+      }
+      CKL(run_linear(sp, E, s));
+      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z2, b.lay[t].Hact, n64, s));
+      sp.clear();
+      for (int t = 0; t < NL_; ++t) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A2", pre + "A2t", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
+      }
+      CKL(run_linear(sp, E, s));
+      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z3, b.lay[t].H3, n64, s));
+    }
     debug.push_back({"Y", b.Y, (long long)D * E});
     debug.push_back({"vec", b.vec, 3 * E});
 
@@ -668,9 +689,27 @@ struct Model : ModelBase {
     }
 
     // ---- back to the edge vectors, then forces and virials
+    PH("radial_mlp_bwd");
+    {  // lay[t].H3 now holds dE/dh3 of each layer's radial MLP
+      const long long n64 = E * kHidden;
+      for (int t = 0; t < NL_; ++t) CKL(launch_silu_grad_mul(b.lay[t].H3, b.lay[t].Z3, n64, s));
+      std::vector<LinSpec> sp;
+      for (int t = 0; t < NL_; ++t) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        sp.push_back({b.lay[t].H3, kHidden, 0, 1, kHidden, pre + "A2t", pre + "A2", kHidden, b.lay[t].Hact, kHidden, 0, nullptr});
+      }
+      CKL(run_linear(sp, E, s));
+      for (int t = 0; t < NL_; ++t) CKL(launch_silu_grad_mul(b.lay[t].Hact, b.lay[t].Z2, n64, s));
+      sp.clear();
+      for (int t = 0; t < NL_; ++t) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1t", pre + "A1", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
+      }
+      CKL(run_linear(sp, E, s));
+      CKL(launch_edge_mlp_out(ea, s));
+    }
     PH("edge_bwd");
     CKL(launch_edge_bwd(ea, s));
-    ++launches;
     debug.push_back({"g", b.g, 3 * E});
     PH("forces");
     const bool want_virial = (o->virials || o->stress) && !vec_mode;

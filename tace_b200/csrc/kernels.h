@@ -91,16 +91,20 @@ struct EdgeArgs {
   T* ddlen;              // [E] dE/d(edge length) through the radial branch (backward)
   T* vec;                // [E][3] edge vectors (target-sorted order)
   T* Y;                  // [E][D]
-  T* H3[kMaxLayers];     // [E][64] last hidden activation of each layer's radial MLP
-  T* Z[kMaxLayers];      // [192][E] pre-activations of the three hidden layers (component-major), kept for the backward pass
+  T* Z1[kMaxLayers];     // [E][64] pre-activation of the first hidden layer of each layer's radial MLP
+  const T* dH1[kMaxLayers];  // [E][64] gradient of the first hidden activation (backward)
   // backward
-  const T* dH3[kMaxLayers];
   const T* dY;           // [E][D]
   T* g;                  // [E][3] dE/d(edge vector), target-sorted order
   T* edge_forces;        // [E][3] caller order, or nullptr
 };
 template <typename T> cudaError_t launch_edge_fwd(const EdgeArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_edge_bwd(const EdgeArgs<T>& a, cudaStream_t s);
+// radial MLP: first layer (8 -> 64) forward / backward per edge; the 64 -> 64 layers are GEMMs
+template <typename T> cudaError_t launch_edge_mlp_in(const EdgeArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_edge_mlp_out(const EdgeArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_silu(const T* in, T* out, long long n, cudaStream_t s);           // out = silu(in)
+template <typename T> cudaError_t launch_silu_grad_mul(T* g, const T* z, long long n, cudaStream_t s);     // g *= silu'(z)
 
 // forces[i] = -(sum_{e: target = i} g_e - sum_{e: source = i} g_e); per-atom virial rows
 // w[i] = sum_{e: target = i} v_e (x) g_e (tace/models/adapter.py:106-116, utils.py:50-79).

@@ -140,8 +140,8 @@ template <typename T, int K>
 TACE_HD TACE_INLINE void matvec64(const T (&x)[K], const T* __restrict__ A, T (&y)[kHidden]) {
 #pragma unroll
   for (int j = 0; j < kHidden; ++j) y[j] = T(0);
-#pragma unroll 1
-  for (int k = 0; k < K; ++k) {  // rolled: x sits in local memory (one read per 64 FMAs), y in registers
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {  // partly unrolled so the weight loads of the next rows overlap the FMAs; y stays in registers
     const T xk = x[k];
 #pragma unroll
     for (int j4 = 0; j4 < kHidden / 4; ++j4) {
