@@ -210,17 +210,17 @@ struct Model : ModelBase {
       for (size_t i = 0; i < p.out_ls.size(); ++i) {
         const int l = p.out_ls[i];
         const std::string ls = std::to_string(l);
-        add_weight(pre + "c0.l" + ls, (long long)n_el * C * C);
-        add_weight(pre + "c0T.l" + ls, (long long)n_el * C * C);
+        add_linear_weight(pre + "c0.l" + ls, (long long)n_el * C * C);
+        add_linear_weight(pre + "c0T.l" + ls, (long long)n_el * C * C);
         if (cfg.correlation >= 2) {
-          add_weight(pre + "c1.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
-          add_weight(pre + "c1T.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
+          add_linear_weight(pre + "c1.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
+          add_linear_weight(pre + "c1T.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
         }
         add_linear_weight(pre + "lin.l" + ls, (long long)C * C);
         add_linear_weight(pre + "linT.l" + ls, (long long)C * C);
         if (p.has_res) {
-          add_weight(pre + "res.l" + ls, (long long)n_el * C * C);
-          add_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
+          add_linear_weight(pre + "res.l" + ls, (long long)n_el * C * C);
+          add_linear_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
         }
       }
       add_weight(pre + "c.b", (long long)n_el * C);
@@ -265,9 +265,10 @@ struct Model : ModelBase {
   struct LayerBufs {
     T *h_in, *x, *xx, *gxx, *W, *H3, *Z1, *Z2, *Z3, *Hact, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
+    T *As, *gAs, *gout_s, *hs;  // species-sorted copies used by the per-species linears
   };
   struct Bufs {
-    int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr;
+    int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
     void* prep_temp; size_t prep_temp_bytes;
     T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen;
     std::vector<LayerBufs> lay;
@@ -277,6 +278,7 @@ struct Model : ModelBase {
     b.e_src = ar.take<int>(E); b.e_dst = ar.take<int>(E); b.e_orig = ar.take<int>(E); b.perm_src = ar.take<int>(E);
     b.rowptr_dst = ar.take<int>(NL + 1); b.rowptr_src = ar.take<int>(N + 1); b.atom_graph = ar.take<int>(N);
     b.species_perm = ar.take<int>(NL); b.species_ptr = ar.take<int>(n_el + 1); b.tile_ptr = ar.take<int>(4 * (n_el + 1));
+    b.tc_tile_ptr = ar.take<int>(4 * (n_el + 1));
     b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
@@ -308,6 +310,10 @@ struct Model : ModelBase {
       lb.A = ar.take<T>((size_t)NL * D * C);
       lb.gA = ar.take<T>((size_t)NL * D * C);
       lb.B2 = ar.take<T>((size_t)NL * p.pb.NB * C);
+      lb.As = ar.take<T>((size_t)NL * D * C);
+      lb.gAs = ar.take<T>((size_t)NL * D * C);
+      lb.gout_s = ar.take<T>((size_t)NL * p.Dout * C);
+      lb.hs = p.has_res ? ar.take<T>((size_t)NL * p.Din * C) : nullptr;
       lb.out = ar.take<T>((size_t)NL * p.Dout * C);
       lb.gout = ar.take<T>((size_t)NL * p.Dout * C);
       lb.h_out = ar.take<T>((size_t)N * p.Dout * C);
@@ -341,12 +347,6 @@ struct Model : ModelBase {
     gb.n_groups = 1; gb.n_atoms = (int)n_atoms;
     return gb;
   }
-  GemmBatch<T> species_batch(const Bufs& b) const {
-    GemmBatch<T> gb;
-    memset(&gb, 0, sizeof(gb));
-    gb.n_groups = n_el; gb.group_ptr = b.species_ptr; gb.atom_map = b.species_perm;
-    return gb;
-  }
   const int* tiles(const Bufs& b, int l) const { return b.tile_ptr + l * (n_el + 1); }
 
   // One per-rank linear of a launch: rows (atom, m) of A times the [K][N] matrix `wname`;
@@ -373,6 +373,46 @@ struct Model : ModelBase {
     GemmBatch<T> gb = plain_batch(n_atoms);
     for (const auto& sp : specs)
       add_problem(gb, sp.A, sp.a_s1, sp.a_s2, sp.q, sp.K, w(sp.wname), sp.N, sp.Cm, sp.c_s1, sp.c_s2, sp.bias, 0);
+    return launch_gemm(gb, n_atoms, s);
+  }
+
+  // Per-species linears (the reference's e3nnElementLinear, tace/models/linear.py:377-481).  A holds rows of the
+  // species-sorted atoms, so species g owns the contiguous rows [species_ptr[g], species_ptr[g+1]) and uses the g-th
+  // matrix of `wname` ([n_el][K][N]); `mapped` sends row a of the result to atom species_perm[a].
+  struct SpeciesSpec {
+    const T* A; long long a_s1, a_s2; int q, K;
+    std::string wname, wname_t; int N;
+    T* Cm; long long c_s1, c_s2; const T* bias; bool mapped; int accumulate;
+  };
+  cudaError_t run_species_linear(const std::vector<SpeciesSpec>& specs, const Bufs& b, long long n_atoms, cudaStream_t s) {
+    if (specs.empty()) return cudaSuccess;
+    bool tc = kTensorCore && specs.size() <= 4;
+    for (const auto& sp : specs) tc = tc && tc_linear_supported(sp.N, sp.K) && sp.mapped == specs[0].mapped;
+    if (tc) {
+      TcLinearProblem probs[4];
+      for (size_t i = 0; i < specs.size(); ++i) {
+        const SpeciesSpec& sp = specs[i];
+        TcLinearProblem& h = probs[i];
+        memset(&h, 0, sizeof(h));
+        h.A = reinterpret_cast<const float*>(sp.A); h.a_atom_stride = sp.a_s1; h.a_comp_stride = sp.a_s2; h.q = sp.q;
+        h.n_atoms = n_atoms; h.K = sp.K; h.N = sp.N;
+        h.Bhi = reinterpret_cast<const float*>(w(sp.wname_t + "_hi")); h.Blo = reinterpret_cast<const float*>(w(sp.wname_t + "_lo"));
+        h.C = reinterpret_cast<float*>(sp.Cm); h.c_s1 = sp.c_s1; h.c_s2 = sp.c_s2; h.bias = reinterpret_cast<const float*>(sp.bias);
+        h.n_groups = n_el; h.group_ptr = b.species_ptr; h.tile_ptr = b.tc_tile_ptr + (sp.q / 2) * (n_el + 1);
+        h.atom_map = sp.mapped ? b.species_perm : nullptr;
+        h.b_group_stride = (long long)sp.K * sp.N; h.bias_group_stride = sp.N; h.accumulate = sp.accumulate;
+      }
+      return launch_tc_linear(probs, (int)specs.size(), dev_error, s);
+    }
+    GemmBatch<T> gb;
+    memset(&gb, 0, sizeof(gb));
+    gb.n_groups = n_el; gb.group_ptr = b.species_ptr; gb.atom_map = nullptr;
+    gb.c_atom_map = specs[0].mapped ? b.species_perm : nullptr;
+    for (const auto& sp : specs) {
+      if (sp.mapped != specs[0].mapped) return cudaErrorInvalidValue;
+      add_problem(gb, sp.A, sp.a_s1, sp.a_s2, sp.q, sp.K, w(sp.wname), sp.N, sp.Cm, sp.c_s1, sp.c_s2, sp.bias, sp.accumulate,
+                  (long long)sp.K * sp.N, sp.N, tiles(b, sp.q / 2));
+    }
     return launch_gemm(gb, n_atoms, s);
   }
 
@@ -415,7 +455,7 @@ struct Model : ModelBase {
     gp.edge_index = bt->edge_index; gp.species = bt->species; gp.graph_ptr = bt->graph_ptr;
     gp.e_src = b.e_src; gp.e_dst = b.e_dst; gp.e_orig = b.e_orig; gp.rowptr_dst = b.rowptr_dst;
     gp.perm_src = b.perm_src; gp.rowptr_src = b.rowptr_src; gp.atom_graph = b.atom_graph;
-    gp.species_perm = b.species_perm; gp.species_ptr = b.species_ptr; gp.tile_ptr = b.tile_ptr;
+    gp.species_perm = b.species_perm; gp.species_ptr = b.species_ptr; gp.tile_ptr = b.tile_ptr; gp.tc_tile_ptr = b.tc_tile_ptr;
     gp.temp = b.prep_temp; gp.temp_bytes = b.prep_temp_bytes;
     CKL(launch_graph_prep(gp, s));
     launches += 8;  // launch_graph_prep runs nine kernels of its own besides the radix sorts
@@ -537,24 +577,25 @@ struct Model : ModelBase {
         CKL(run_linear(sp, NL, s));
       }
       debug.push_back({"A" + ts, lb.A, NL * D * C});
-      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.A, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
-      {  // per-species coefficients
-        GemmBatch<T> gb = species_batch(b);
+      // per-species part in species-sorted space: gather A, product basis, coefficient linears scatter into `out`
+      CKL(launch_gather_rows(lb.A, b.species_perm, lb.As, NL, D * C, s));
+      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
+      {
+        std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
-          add_problem(gb, lb.A + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, w(pre + "c0.l" + std::to_string(l)), C,
-                      lb.out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "c.b") : nullptr, 0,
-                      (long long)C * C, C, tiles(b, l));
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.As + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, pre + "c0.l" + std::to_string(l),
+                        pre + "c0T.l" + std::to_string(l), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C,
+                        l == 0 ? w(pre + "c.b") : nullptr, true, 0});
+        CKL(run_species_linear(sp, b, NL, s));
         if (cfg.correlation >= 2) {
-          GemmBatch<T> g2 = species_batch(b);
+          sp.clear();
           for (size_t i = 0; i < p.out_ls.size(); ++i) {
             const int l = p.out_ls[i];
             const int K = p.pb.k[i] * C;
-            add_problem(g2, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, 2 * l + 1, K,
-                        w(pre + "c1.l" + std::to_string(l)), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, 1,
-                        (long long)K * C, 0, tiles(b, l));
+            sp.push_back({lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, 2 * l + 1, K, pre + "c1.l" + std::to_string(l),
+                          pre + "c1T.l" + std::to_string(l), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, true, 1});
           }
-          CKL(launch_gemm(g2, NL, s));
+          CKL(run_species_linear(sp, b, NL, s));
         }
       }
       {
@@ -566,12 +607,13 @@ struct Model : ModelBase {
         CKL(run_linear(sp, NL, s));
       }
       if (p.has_res) {  // per-species skip connection from the layer input
-        GemmBatch<T> gb = species_batch(b);
+        CKL(launch_gather_rows(lb.h_in, b.species_perm, lb.hs, NL, p.Din * C, s));
+        std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
-          add_problem(gb, lb.h_in + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, w(pre + "res.l" + std::to_string(l)),
-                      C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C, l == 0 ? w(pre + "res.b") : nullptr, 1,
-                      (long long)C * C, C, tiles(b, l));
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.hs + (long long)l * l * C, (long long)p.Din * C, C, 2 * l + 1, C, pre + "res.l" + std::to_string(l),
+                        pre + "resT.l" + std::to_string(l), C, lb.h_out + (long long)l * l * C, (long long)p.Dout * C, C,
+                        l == 0 ? w(pre + "res.b") : nullptr, true, 1});
+        CKL(run_species_linear(sp, b, NL, s));
       }
       debug.push_back({"h" + std::to_string(t + 1), lb.h_out, NL * p.Dout * C});
     }
@@ -603,26 +645,29 @@ struct Model : ModelBase {
                         pre + "lin.l" + std::to_string(l), C, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, nullptr});
         CKL(run_linear(sp, NL, s));
       }
-      if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gA, NL * D * C, s));
-      {  // through the per-species coefficients
-        GemmBatch<T> gb = species_batch(b);
+      // through the per-species coefficients and the product basis, in species-sorted space
+      CKL(launch_gather_rows(lb.gout, b.species_perm, lb.gout_s, NL, p.Dout * C, s));
+      if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gAs, NL * D * C, s));
+      {
+        std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
-          add_problem(gb, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, w(pre + "c0T.l" + std::to_string(l)),
-                      C, lb.gA + (long long)l * l * C, (long long)D * C, C, nullptr, 0, (long long)C * C, 0, tiles(b, l));
-        CKL(launch_gemm(gb, NL, s));
+          sp.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "c0T.l" + std::to_string(l),
+                        pre + "c0.l" + std::to_string(l), C, lb.gAs + (long long)l * l * C, (long long)D * C, C, nullptr, false, 0});
+        CKL(run_species_linear(sp, b, NL, s));
         if (cfg.correlation >= 2) {
-          GemmBatch<T> g2 = species_batch(b);
+          sp.clear();
           for (size_t i = 0; i < p.out_ls.size(); ++i) {
             const int l = p.out_ls[i];
             const int K = p.pb.k[i] * C;
-            add_problem(g2, lb.gout + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C,
-                        w(pre + "c1T.l" + std::to_string(l)), K, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K,
-                        nullptr, 0, (long long)K * C, 0, tiles(b, l));
+            sp.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "c1T.l" + std::to_string(l),
+                          pre + "c1.l" + std::to_string(l), K, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, nullptr,
+                          false, 0});
           }
-          CKL(launch_gemm(g2, NL, s));
-          CKL(launch_pb_bwd(lb.A, lb.B2, lb.gA, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
+          CKL(run_species_linear(sp, b, NL, s));
+          CKL(launch_pb_bwd(lb.As, lb.B2, lb.gAs, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
         }
       }
+      CKL(launch_scatter_rows(lb.gAs, b.species_perm, lb.gA, NL, D * C, s));
       {
         std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l)
@@ -678,12 +723,12 @@ struct Model : ModelBase {
                         (long long)p.Din * C, C, nullptr});
         CKL(run_linear(sp, NL, s));
         if (p.has_res) {
-          GemmBatch<T> g2 = species_batch(b);
+          CKL(launch_gather_rows(lb.gh_out, b.species_perm, lb.gout_s, NL, p.Dout * C, s));
+          std::vector<SpeciesSpec> sp2;
           for (int l : p.out_ls)
-            add_problem(g2, lb.gh_out + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C,
-                        w(pre + "resT.l" + std::to_string(l)), C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, 1,
-                        (long long)C * C, 0, tiles(b, l));
-          CKL(launch_gemm(g2, NL, s));
+            sp2.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "resT.l" + std::to_string(l),
+                           pre + "res.l" + std::to_string(l), C, lb.gh_in + (long long)l * l * C, (long long)p.Din * C, C, nullptr, true, 1});
+          CKL(run_species_linear(sp2, b, NL, s));
         }
       }
     }

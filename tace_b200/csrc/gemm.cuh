@@ -40,7 +40,8 @@ struct GemmBatch {
   int n_problems;
   int n_groups;          // 1 unless per-species
   const int* group_ptr;  // [n_groups+1] atom ranges in `atom_map` order, or nullptr (=> all atoms)
-  const int* atom_map;   // sorted position -> atom index, or nullptr (identity)
+  const int* atom_map;   // row position -> atom index of A, or nullptr (identity)
+  const int* c_atom_map; // row position -> atom index of C, or nullptr (identity)
   int n_atoms;           // used when group_ptr == nullptr
 };
 
@@ -82,9 +83,10 @@ __global__ void __launch_bounds__(256) gemm_kernel(const GemmBatch<T> batch) {
     if (r < M) {
       const int pos = a_begin + r / q;
       const int m = r % q;
-      const long long atom = batch.atom_map ? batch.atom_map[pos] : pos;
-      ao = atom * P.a_s1 + m * P.a_s2;
-      co = atom * P.c_s1 + m * P.c_s2;
+      const long long a_atom = batch.atom_map ? batch.atom_map[pos] : pos;
+      const long long c_atom = batch.c_atom_map ? batch.c_atom_map[pos] : pos;
+      ao = a_atom * P.a_s1 + m * P.a_s2;
+      co = c_atom * P.c_s1 + m * P.c_s2;
     }
     a_off[tid] = ao;
     c_off[tid] = co;

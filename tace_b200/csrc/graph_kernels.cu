@@ -47,15 +47,19 @@ __global__ void atom_graph_kernel(const int* __restrict__ graph_ptr, int n_graph
   }
   atom_graph[i] = lo;
 }
-__global__ void tile_ptr_kernel(const int* __restrict__ species_ptr, int n_el, int* tile_ptr) {
-  const int qi = threadIdx.x;  // q = 2*qi + 1
-  if (qi >= 4) return;
+// tile_ptr: 64-row tiles of the CUDA-core GEMM; tc_tile_ptr: (128 / q)-atom tiles of the tensor-core GEMM
+__global__ void tile_ptr_kernel(const int* __restrict__ species_ptr, int n_el, int* tile_ptr, int* tc_tile_ptr) {
+  const int qi = threadIdx.x & 3;  // q = 2*qi + 1
+  const bool tc = threadIdx.x >= 4;
+  if (threadIdx.x >= 8) return;
   const int q = 2 * qi + 1;
-  int* tp = tile_ptr + qi * (n_el + 1);
+  int* tp = (tc ? tc_tile_ptr : tile_ptr) + qi * (n_el + 1);
+  const int R = 128 / q;
   int acc = 0;
   for (int g = 0; g < n_el; ++g) {
     tp[g] = acc;
-    acc += ((species_ptr[g + 1] - species_ptr[g]) * q + 63) / 64;
+    const int cnt = species_ptr[g + 1] - species_ptr[g];
+    acc += tc ? (cnt + R - 1) / R : (cnt * q + 63) / 64;
   }
   tp[n_el] = acc;
 }
@@ -113,7 +117,7 @@ cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
   err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.species_perm, a.n_local, 0, sbits, s);
   if (err != cudaSuccess) return err;
   lower_bound_kernel<<<(a.n_elements + 256) / 256, 256, 0, s>>>(keys_out, a.n_local, a.species_ptr, a.n_elements);
-  tile_ptr_kernel<<<1, 32, 0, s>>>(a.species_ptr, a.n_elements, a.tile_ptr);
+  tile_ptr_kernel<<<1, 32, 0, s>>>(a.species_ptr, a.n_elements, a.tile_ptr, a.tc_tile_ptr);
   return cudaGetLastError();
 }
 

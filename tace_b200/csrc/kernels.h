@@ -67,6 +67,9 @@ template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaSt
 template <typename T> cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr,
                                                      T* energy, int n_graphs, cudaStream_t s);
 template <typename T> cudaError_t launch_fill_zero(T* p, long long n, cudaStream_t s);
+// dst[i] = src[perm[i]] (gather) / dst[perm[i]] = src[i] (scatter), rows of row_len elements
+template <typename T> cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);
+template <typename T> cudaError_t launch_scatter_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);
 template <typename T> cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s);
 
 // ---- per-edge kernels (edge_kernels.cu) -------------------------------------------------------
@@ -132,7 +135,8 @@ struct GraphPrepArgs {
   int* perm_src; int* rowptr_src;       // [E], [n_atoms+1]
   int* atom_graph;            // [n_atoms]
   int* species_perm; int* species_ptr;  // [n_local], [n_elements+1]
-  int* tile_ptr;              // [4][n_elements+1] for q = 1,3,5,7
+  int* tile_ptr;              // [4][n_elements+1] for q = 1,3,5,7: 64-row tiles per species
+  int* tc_tile_ptr;           // [4][n_elements+1]: (128 / q)-atom tiles per species
   void* temp; size_t temp_bytes;
 };
 size_t graph_prep_temp_bytes(long long E, int n_atoms);
@@ -154,6 +158,13 @@ struct TcLinearProblem {
   const float* Bhi; const float* Blo;  // [N][K]
   float* C; long long c_s1, c_s2;
   const float* bias;     // [N] or nullptr
+  // per-species form: atoms of A are sorted by species; group g owns atoms [group_ptr[g], group_ptr[g+1]) and tiles
+  // [tile_ptr[g], tile_ptr[g+1]) of 128 / q atoms (device arrays); weights / bias of group g sit b_group_stride /
+  // bias_group_stride elements apart; rows of C go to atom_map[sorted atom] (nullptr: same order as A)
+  int n_groups;          // 0: a single group (plain linear)
+  const int* group_ptr; const int* tile_ptr; const int* atom_map;
+  long long b_group_stride, bias_group_stride;
+  int accumulate;        // C += instead of C =
 };
 bool tc_linear_supported(int N, int K);
 cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s);

@@ -33,6 +33,30 @@ cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s
   return cudaGetLastError();
 }
 
+template <typename T, bool SCATTER>
+__global__ void permute_rows_kernel(const T* __restrict__ src, const int* __restrict__ perm, T* __restrict__ dst, long long n, int row_len) {
+  const long long total = n * row_len;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long i = idx / row_len, k = idx - i * row_len;
+    const long long j = perm[i];
+    if (SCATTER) dst[j * row_len + k] = src[idx]; else dst[idx] = src[j * row_len + k];
+  }
+}
+template <typename T>
+cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const long long blocks = (n * row_len + 255) / 256;
+  permute_rows_kernel<T, false><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(src, perm, dst, n, row_len);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_scatter_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const long long blocks = (n * row_len + 255) / 256;
+  permute_rows_kernel<T, true><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(src, perm, dst, n, row_len);
+  return cudaGetLastError();
+}
+
 template <typename T>
 __global__ void species_gather_kernel(const T* __restrict__ table, const int* __restrict__ species, T* out, int n, int C) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -228,6 +252,8 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
 #define INST(T)                                                                                               \
   template cudaError_t launch_fill_zero<T>(T*, long long, cudaStream_t);                                      \
   template cudaError_t launch_add_inplace<T>(T*, const T*, long long, cudaStream_t);                          \
+  template cudaError_t launch_gather_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);         \
+  template cudaError_t launch_scatter_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);        \
   template cudaError_t launch_species_gather<T>(const T*, const int*, T*, int, int, cudaStream_t);            \
   template cudaError_t launch_gate_fwd<T>(const T*, T*, int, int, int, cudaStream_t);                         \
   template cudaError_t launch_gate_bwd<T>(const T*, const T*, T*, int, int, int, cudaStream_t);               \

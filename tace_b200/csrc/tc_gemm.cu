@@ -67,12 +67,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   atomicCAS(error, 0, code);
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
 // K-major operand tile with 128-byte rows and 128-byte swizzle: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -108,11 +102,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // Rows are (atom, component) pairs; the 3-D tensor map of A is {K, q, atoms} with box {32, q, R},
 // R = 128 / q atoms per tile, so a tile's rows land in shared memory in (atom, m) order.
 struct TcProblem {
-  CUtensorMap tmA, tmBhi, tmBlo;
+  CUtensorMap tmA, tmBhi, tmBlo;  // B maps are 3-D {K, N, groups}
   float* C;
-  const float* bias;     // [N] or nullptr
+  const float* bias;     // [N] (per group) or nullptr
   long long c_s1, c_s2;  // atom stride / component stride of C rows (elements)
+  long long bias_group_stride;
   int q, R, n_atoms, N, K;
+  // per-species problems: atoms are sorted by species, group g owns atoms [group_ptr[g], group_ptr[g+1]) and
+  // R-atom tiles [tile_ptr[g], tile_ptr[g+1]); both arrays live in device memory.  n_groups == 0: one group.
+  int n_groups;
+  const int* group_ptr;
+  const int* tile_ptr;
+  const int* atom_map;   // row of C for sorted atom a is atom_map[a]; nullptr: identity
+  int accumulate;        // C += instead of C =
 };
 constexpr int kTcMaxProblems = 4;
 struct TcBatch {
@@ -147,19 +149,36 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 
 struct TileInfo {
-  int prob, atom0, n0, num_k;
+  int prob, atom0, atom_end, group, n0, num_k;
 };
+// tile_start: prefix sums of the problems' tile counts (in shared memory: grouped problems only know
+// their tile count on the device)
 template <int BN>
-__device__ __forceinline__ TileInfo decode_tile(const TcBatch& b, int tile) {
+__device__ __forceinline__ TileInfo decode_tile(const TcBatch& b, const int* tile_start, int tile) {
   int pi = 0;
-  while (pi + 1 < b.n_problems && tile >= b.tile_start[pi + 1]) ++pi;
-  const int local = tile - b.tile_start[pi];
-  const int tiles_n = b.p[pi].N / BN;
+  while (pi + 1 < b.n_problems && tile >= tile_start[pi + 1]) ++pi;
+  const TcProblem& P = b.p[pi];
+  const int local = tile - tile_start[pi];
+  const int tiles_n = P.N / BN;
+  const int mt = local / tiles_n;
   TileInfo t;
   t.prob = pi;
-  t.atom0 = (local / tiles_n) * b.p[pi].R;
-  t.n0 = (local % tiles_n) * BN;
-  t.num_k = b.p[pi].K / kBK;
+  t.n0 = (local - mt * tiles_n) * BN;
+  t.num_k = P.K / kBK;
+  if (P.n_groups > 0) {
+    int lo = 0, hi = P.n_groups;  // largest g with tile_ptr[g] <= mt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (P.tile_ptr[mid] <= mt) lo = mid; else hi = mid;
+    }
+    t.group = lo;
+    t.atom0 = P.group_ptr[lo] + (mt - P.tile_ptr[lo]) * P.R;
+    t.atom_end = P.group_ptr[lo + 1];
+  } else {
+    t.group = 0;
+    t.atom0 = mt * P.R;
+    t.atom_end = P.n_atoms;
+  }
   return t;
 }
 
@@ -183,12 +202,21 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   unsigned char* misc = base_ptr + kStages * S::kStageBytes + 8 * (3 * kStages + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
+  int* tile_start = reinterpret_cast<int*>(misc + 16);  // [n_problems + 1]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), kSplitThreads); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
     *abort_flag = 0;
+    int acc = 0;
+    for (int i = 0; i < batch.n_problems; ++i) {
+      const TcProblem& P = batch.p[i];
+      tile_start[i] = acc;
+      const int tiles_m = P.n_groups > 0 ? P.tile_ptr[P.n_groups] : (P.n_atoms + P.R - 1) / P.R;
+      acc += tiles_m * (P.N / BN);
+    }
+    for (int i = batch.n_problems; i <= kTcMaxProblems; ++i) tile_start[i] = acc;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // two accumulators of BN fp32 columns
@@ -200,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_tiles = batch.tile_start[batch.n_problems];
+  const int n_tiles = tile_start[batch.n_problems];
   // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   auto stage_a = [&](int s) { return base + s * S::kStageBytes; };
@@ -214,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       int step = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const TileInfo t = decode_tile<BN>(batch, tile);
+        const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
         const TcProblem& P = batch.p[t.prob];
         const uint32_t a_bytes = (uint32_t)P.R * P.q * kBK * 4;
         for (int ks = 0; ks < t.num_k; ++ks, ++step) {
@@ -222,8 +250,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, batch.error, 1)) { ok = false; break; }
           mbar_expect_tx(raw_bar(s), a_bytes + 2 * S::kTileBBytes);
           tma_load_3d(stage_a(s), &P.tmA, raw_bar(s), ks * kBK, 0, t.atom0);
-          tma_load_2d(stage_bhi(s), &P.tmBhi, raw_bar(s), ks * kBK, t.n0);
-          tma_load_2d(stage_blo(s), &P.tmBlo, raw_bar(s), ks * kBK, t.n0);
+          tma_load_3d(stage_bhi(s), &P.tmBhi, raw_bar(s), ks * kBK, t.n0, t.group);
+          tma_load_3d(stage_blo(s), &P.tmBlo, raw_bar(s), ks * kBK, t.n0, t.group);
         }
       }
       if (*abort_flag) {  // loads already issued must land before the CTA exits
@@ -240,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       int step = 0, chunk = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const TileInfo t = decode_tile<BN>(batch, tile);
+        const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
         for (int ks = 0; ks < t.num_k; ++ks, ++step) {
           const int s = step % kStages, ph = (step / kStages) & 1;
           const int a = chunk & 1;
@@ -269,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
     int step = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      const TileInfo t = decode_tile<BN>(batch, tile);
+      const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
       for (int ks = 0; ks < t.num_k; ++ks, ++step) {
         const int s = step % kStages, ph = (step / kStages) & 1;
         if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3)) { ok = false; break; }
@@ -298,13 +326,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
     int chunk = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      const TileInfo t = decode_tile<BN>(batch, tile);
+      const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
       const TcProblem& P = batch.p[t.prob];
       const int r = ew * 32 + lane;
       const int al = r / P.q, m = r - al * P.q;
-      const bool valid = r < P.R * P.q && t.atom0 + al < P.n_atoms;
-      float* dst = P.C + (long long)(t.atom0 + al) * P.c_s1 + (long long)m * P.c_s2 + t.n0;
-      const float* bias = P.bias ? P.bias + t.n0 : nullptr;
+      const bool valid = r < P.R * P.q && t.atom0 + al < t.atom_end;
+      long long atom = t.atom0 + al;
+      if (valid && P.atom_map) atom = P.atom_map[atom];
+      float* dst = P.C + atom * P.c_s1 + (long long)m * P.c_s2 + t.n0;
+      const float* bias = P.bias ? P.bias + t.group * P.bias_group_stride + t.n0 : nullptr;
+      const bool accumulate = P.accumulate != 0;
       const int n_chunks = (t.num_k + kChunk - 1) / kChunk;
       for (int cin = 0; cin < n_chunks; ++cin, ++chunk) {
         const int a = chunk & 1;
@@ -325,6 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
                   const float4 bv = *reinterpret_cast<const float4*>(bias + c * 32 + 4 * q4);
                   v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
                 }
+                if (accumulate) {
+                  const float4 ov = *reinterpret_cast<const float4*>(dst + c * 32 + 4 * q4);
+                  v.x += ov.x; v.y += ov.y; v.z += ov.z; v.w += ov.w;
+                }
                 *reinterpret_cast<float4*>(dst + c * 32 + 4 * q4) = v;
               }
             }
@@ -343,6 +378,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
               if (bias) {
                 const float4 bv = *reinterpret_cast<const float4*>(bias + 4 * q4);
                 v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              if (accumulate) {
+                const float4 ov = *reinterpret_cast<const float4*>(dst + 4 * q4);
+                v.x += ov.x; v.y += ov.y; v.z += ov.z; v.w += ov.w;
               }
               *reinterpret_cast<float4*>(dst + 4 * q4) = v;
             }
@@ -372,15 +411,15 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D fp32 tensor [rows][cols] with `ld` elements between rows; box = [box_rows][32 columns], 128-byte swizzle.
-bool make_map_2d(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld, int box_rows) {
+// 3-D fp32 weight tensor [groups][N][K]; box = [1][box_rows][32], 128-byte swizzle.
+bool make_map_b(CUtensorMap* map, const float* ptr, int groups, long long N, long long K, long long group_stride, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)groups};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * sizeof(float), (cuuint64_t)(groups > 1 ? group_stride : N * K) * sizeof(float)};
+  const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -407,7 +446,7 @@ cudaError_t launch_tc(const TcBatch& b, int sms, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const int tiles = b.tile_start[b.n_problems];
+  const int tiles = b.tile_start[b.n_problems];  // upper bound for per-species problems
   const int grid = tiles < sms ? tiles : sms;
   tc_gemm_kernel<BN, ONE_CHUNK><<<grid, kThreads, TcSmem<BN>::kTotal, s>>>(b);
   return cudaGetLastError();
@@ -446,12 +485,17 @@ cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* 
     if (h.n_atoms <= 0) continue;
     TcProblem& P = b.p[b.n_problems];
     P.q = h.q; P.R = kBM / h.q; P.n_atoms = (int)h.n_atoms; P.N = h.N; P.K = h.K;
-    P.C = h.C; P.bias = h.bias; P.c_s1 = h.c_s1; P.c_s2 = h.c_s2;
+    P.C = h.C; P.bias = h.bias; P.c_s1 = h.c_s1; P.c_s2 = h.c_s2; P.bias_group_stride = h.bias_group_stride;
+    P.n_groups = h.n_groups; P.group_ptr = h.group_ptr; P.tile_ptr = h.tile_ptr; P.atom_map = h.atom_map;
+    P.accumulate = h.accumulate;
+    const int groups = h.n_groups > 0 ? h.n_groups : 1;
+    if (h.n_groups > 0 && (!h.group_ptr || !h.tile_ptr)) return cudaErrorInvalidValue;
     if (!make_map_3d(&P.tmA, h.A, h.n_atoms, h.q, h.K, h.a_atom_stride, h.a_comp_stride, P.R) ||
-        !make_map_2d(&P.tmBhi, h.Bhi, h.N, h.K, h.K, bn) || !make_map_2d(&P.tmBlo, h.Blo, h.N, h.K, h.K, bn))
+        !make_map_b(&P.tmBhi, h.Bhi, groups, h.N, h.K, h.b_group_stride, bn) ||
+        !make_map_b(&P.tmBlo, h.Blo, groups, h.N, h.K, h.b_group_stride, bn))
       return cudaErrorInvalidValue;
     b.tile_start[b.n_problems] = tiles;
-    tiles += (int)((h.n_atoms + P.R - 1) / P.R) * (h.N / bn);
+    tiles += (int)((h.n_atoms + P.R - 1) / P.R + h.n_groups) * (h.N / bn);
     ++b.n_problems;
   }
   for (int i = b.n_problems; i <= kTcMaxProblems; ++i) b.tile_start[i] = tiles;
@@ -464,6 +508,7 @@ cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, cons
                            int N, int K, int* error_flag, cudaStream_t s) {
   if (M <= 0) return cudaSuccess;
   TcLinearProblem h;
+  memset(&h, 0, sizeof(h));
   h.A = A; h.a_atom_stride = lda; h.a_comp_stride = lda; h.q = 1; h.n_atoms = M; h.K = K;
   h.Bhi = Bhi; h.Blo = Blo; h.N = N; h.C = C; h.c_s1 = ldc; h.c_s2 = 0; h.bias = nullptr;
   return launch_tc_linear(&h, 1, error_flag, s);

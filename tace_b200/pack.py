@@ -157,7 +157,8 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
     # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
     for name in list(out):
         stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
-        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT") and name.split(".")[-1].startswith("l")) \
+        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "res", "resT")
+                and name.split(".")[-1].startswith("l")) \
                 or stem in ("A1", "A1t", "A2", "A2t"):
             out[name + "_hi"], out[name + "_lo"] = split_tf32(out[name])
     out["ro.W1"] = g("energy_readouts.0.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
