@@ -119,6 +119,17 @@ int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_loca
 int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace,
                  size_t workspace_bytes, tace_stream_t stream);
 
+/* CUDA-graph replay of tace_forward (no reference counterpart; the reference relies on torch.compile /
+ * AOT-Inductor for launch overhead, tace/compile/aot.py).  Enabled by default: the second tace_forward call
+ * with the same n_atoms, n_local, n_edges, n_graphs, requested outputs and workspace is captured into a
+ * CUDA graph; later calls copy the inputs into a staging area at the end of the workspace, launch the graph
+ * on `stream` and copy the results out, so input and output pointers may differ from call to call.  Calls
+ * with an exchange callback, with profiling enabled, or with new sizes run launch by launch.
+ * tace_set_graph_mode(model, 0) switches replay off and frees the captured graphs;
+ * tace_graph_replays returns how many calls were served by a graph launch. */
+int tace_set_graph_mode(TaceModel* model, int enable);
+int64_t tace_graph_replays(const TaceModel* model);
+
 /* Ghost-row exchange for edge-vector mode with n_local < n_atoms and more than one layer.  Stands
  * behind lmp_data.forward_exchange / reverse_exchange as used by GhostExchange
  * (tace/models/lammps.py:82-129): before every layer after the first, tace_forward synchronises its
@@ -203,6 +214,35 @@ int tace_nl_fill(const double* positions, const double* lattice, const uint8_t* 
 int tace_nl_build_noalloc(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
                           int32_t n_graphs, int64_t n_atoms, double cutoff, int64_t max_edges, int64_t* row_ptr,
                           int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream);
+
+/* ---- molecular dynamics on the device (domain-decomposed driver) -------------------------------------
+ * The reference ships no integrator: its MD examples run under LAMMPS (`fix nve`, docs lammps.rst) or
+ * ASE, which call the model once per step through tace/interface/lammps/mliap.py:96-115 or
+ * tace/interface/ase/calculator.py:128-178.  These entry points keep the rest of such a step on the GPU.
+ * All pointers are device pointers; every call is asynchronous on `stream`.
+ *
+ * tace_md_kick_drift: v += kick * F * inv_mass (skipped when forces == NULL), then x += dt * v (skipped
+ *   when positions == NULL).  positions / velocities fp64 [n_atoms,3]; forces [n_atoms,3] in force_dtype
+ *   (TACE_F32 / TACE_F64); inv_mass fp64 [n_atoms].  Units are the caller's (kick carries dt/2 and the
+ *   unit conversion).
+ * tace_md_kinetic_energy: out[0] = sum_i 0.5 * mass_i * |v_i|^2 in a fixed summation order; scratch holds
+ *   at least 1024 doubles.
+ * tace_edge_vectors: out[e] = positions[target_e] - positions[source_e] evaluated in fp64 and rounded to
+ *   `dtype` (edge_index int64 [2,n_edges], row 0 = source); the edge-vector input of tace_forward
+ *   (tace/models/adapter.py:341-352 computes the same difference in the model dtype).
+ * tace_rows_gather: dst[r,:] = src[index[r],:] for r < n_rows (packs a halo message; elem_bytes 4 or 8).
+ * tace_rows_scatter_add: dst[index[r],:] += src[r,:]; the indices of one call must be distinct (unpacks
+ *   gradients returned by a neighbouring domain, tace/models/lammps.py:105-129); float / double rows. */
+int tace_md_kick_drift(double* positions, double* velocities, const void* forces, int32_t force_dtype, const double* inv_mass,
+                       int64_t n_atoms, double kick, double dt, tace_stream_t stream);
+int tace_md_kinetic_energy(const double* velocities, const double* mass, int64_t n_atoms, double* scratch, double* out,
+                           tace_stream_t stream);
+int tace_edge_vectors(const double* positions, const int64_t* edge_index, int64_t n_edges, void* out, int32_t dtype,
+                      tace_stream_t stream);
+int tace_rows_gather(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,
+                     tace_stream_t stream);
+int tace_rows_scatter_add(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,
+                          tace_stream_t stream);
 
 #ifdef __cplusplus
 }

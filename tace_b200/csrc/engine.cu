@@ -126,6 +126,150 @@ struct ModelBase {
     for (auto e : phase_events) cudaEventDestroy(e);
     phase_events.clear();
   }
+
+  // ---- CUDA-graph replay ------------------------------------------------------------------------
+  // A forward pass is several hundred short launches whose arguments depend only on the batch
+  // sizes and the workspace address.  The second call with the same sizes is captured into a CUDA
+  // graph on a private stream; from then on inputs are copied into a staging area at the end of
+  // the workspace, the graph is launched on the caller's stream, and results are copied out, so
+  // the caller's input and output pointers may change freely between calls.
+  struct GraphKey {
+    int64_t n_atoms, n_local, n_edges;
+    int32_t n_graphs, vec_mode;
+    uint32_t out_mask;
+    void* ws;
+    size_t ws_bytes;
+    bool operator==(const GraphKey& o) const {
+      return n_atoms == o.n_atoms && n_local == o.n_local && n_edges == o.n_edges && n_graphs == o.n_graphs &&
+             vec_mode == o.vec_mode && out_mask == o.out_mask && ws == o.ws && ws_bytes == o.ws_bytes;
+    }
+  };
+  struct GraphEntry { GraphKey key; cudaGraphExec_t exec; long long launches; unsigned long long last_use; };
+  static constexpr size_t kMaxGraphs = 4, kMaxSeen = 16;
+  int graph_mode = 1;
+  std::vector<GraphKey> seen, rejected;
+  std::vector<GraphEntry> graphs;
+  cudaStream_t capture_stream = nullptr;
+  unsigned long long graph_clock = 0;
+  long long graph_replays = 0;
+
+  struct Stage {  // byte offsets (from the staging base) of the copies of every input and output
+    size_t positions, lattice, species, graph_ptr, edge_index, edge_shifts, edge_vector;
+    size_t energy, node_energy, forces, virials, stress, edge_forces, total;
+  };
+  Stage stage_layout(int64_t N, int64_t NL, int64_t E, int32_t B) const {
+    const size_t ts = cfg.dtype == TACE_F32 ? 4 : 8;
+    Stage st;
+    size_t off = 0;
+    auto take = [&off](size_t bytes) { const size_t at = off; off += align256(bytes ? bytes : 1); return at; };
+    st.positions = take(ts * 3 * N); st.lattice = take(ts * 9 * B); st.species = take(4 * (size_t)N);
+    st.graph_ptr = take(4 * (size_t)(B + 1)); st.edge_index = take(16 * (size_t)E); st.edge_shifts = take(ts * 3 * E);
+    st.edge_vector = take(ts * 3 * E);
+    st.energy = take(ts * B); st.node_energy = take(ts * NL); st.forces = take(ts * 3 * N); st.virials = take(ts * 9 * B);
+    st.stress = take(ts * 9 * B); st.edge_forces = take(ts * 3 * E);
+    st.total = off;
+    return st;
+  }
+  void release_graphs() {
+    for (auto& g : graphs) cudaGraphExecDestroy(g.exec);
+    graphs.clear(); seen.clear(); rejected.clear();
+    if (capture_stream) { cudaStreamDestroy(capture_stream); capture_stream = nullptr; }
+  }
+
+  int forward_entry(const TaceBatch* bt, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (!bt || !o || !ws) return TACE_ERR_INVALID_ARGUMENT;
+    const int64_t N = bt->n_atoms, NL = bt->n_local, E = bt->n_edges;
+    const int32_t B = bt->n_graphs;
+    if (!graph_mode || profile || exchange_fn || N <= 0 || E <= 0 || B <= 0 || NL < 0 || NL > N)
+      return forward(bt, o, ws, ws_bytes, s);
+    const Stage st = stage_layout(N, NL, E, B);
+    if (ws_bytes < st.total + 256) return forward(bt, o, ws, ws_bytes, s);
+    const size_t body_bytes = (ws_bytes - st.total) & ~size_t(255);
+    unsigned char* sb = static_cast<unsigned char*>(ws) + body_bytes;
+    GraphKey key{N, NL, E, B, bt->edge_vector ? 1 : 0, 0u, ws, ws_bytes};
+    const void* outs[6] = {o->energy, o->node_energy, o->forces, o->virials, o->stress, o->edge_forces};
+    for (int k = 0; k < 6; ++k) if (outs[k]) key.out_mask |= 1u << k;
+    // inputs the pass reads (all must be present for the staged path)
+    if (!bt->species || !bt->graph_ptr || !bt->edge_index) return forward(bt, o, ws, ws_bytes, s);
+    if (!key.vec_mode && (!bt->positions || !bt->lattice || !bt->edge_shifts)) return forward(bt, o, ws, ws_bytes, s);
+
+    GraphEntry* hit = nullptr;
+    for (auto& g : graphs) if (g.key == key) hit = &g;
+    if (!hit) {
+      for (const auto& r : rejected) if (r == key) return forward(bt, o, ws, ws_bytes, s);
+      bool was_seen = false;
+      for (const auto& k : seen) if (k == key) was_seen = true;
+      if (!was_seen) {  // first call with these sizes: run it directly (also configures kernel attributes)
+        if (seen.size() >= kMaxSeen) seen.erase(seen.begin());
+        seen.push_back(key);
+        return forward(bt, o, ws, ws_bytes, s);
+      }
+      // second call: capture a pass that works on the staged copies
+      if (!capture_stream && cudaStreamCreateWithFlags(&capture_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return forward(bt, o, ws, ws_bytes, s);
+      TaceBatch sbt = *bt;
+      TaceOutputs so;
+      const size_t ts = cfg.dtype == TACE_F32 ? 4 : 8;
+      (void)ts;
+      sbt.species = reinterpret_cast<const int32_t*>(sb + st.species);
+      sbt.graph_ptr = reinterpret_cast<const int32_t*>(sb + st.graph_ptr);
+      sbt.edge_index = reinterpret_cast<const int64_t*>(sb + st.edge_index);
+      sbt.positions = key.vec_mode ? nullptr : sb + st.positions;
+      sbt.lattice = key.vec_mode ? nullptr : sb + st.lattice;
+      sbt.edge_shifts = key.vec_mode ? nullptr : sb + st.edge_shifts;
+      sbt.edge_vector = key.vec_mode ? sb + st.edge_vector : nullptr;
+      so.energy = o->energy ? sb + st.energy : nullptr;
+      so.node_energy = o->node_energy ? sb + st.node_energy : nullptr;
+      so.forces = o->forces ? sb + st.forces : nullptr;
+      so.virials = o->virials ? sb + st.virials : nullptr;
+      so.stress = o->stress ? sb + st.stress : nullptr;
+      so.edge_forces = o->edge_forces ? sb + st.edge_forces : nullptr;
+      const long long before = launches;
+      cudaGraph_t graph = nullptr;
+      cudaGraphExec_t exec = nullptr;
+      bool ok = cudaStreamBeginCapture(capture_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      if (ok) {
+        const int status = forward(&sbt, &so, ws, body_bytes, capture_stream);
+        const cudaError_t ce = cudaStreamEndCapture(capture_stream, &graph);
+        ok = status == TACE_OK && ce == cudaSuccess && graph != nullptr;
+      }
+      const long long per_pass = launches - before;
+      launches = before;
+      if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+      if (graph) cudaGraphDestroy(graph);
+      if (!ok) {
+        cudaGetLastError();  // a failed capture leaves a sticky-free error behind; this sizes runs without a graph
+        rejected.push_back(key);
+        return forward(bt, o, ws, ws_bytes, s);
+      }
+      if (graphs.size() >= kMaxGraphs) {
+        size_t oldest = 0;
+        for (size_t k = 1; k < graphs.size(); ++k) if (graphs[k].last_use < graphs[oldest].last_use) oldest = k;
+        cudaGraphExecDestroy(graphs[oldest].exec);
+        graphs.erase(graphs.begin() + oldest);
+      }
+      graphs.push_back({key, exec, per_pass, 0});
+      hit = &graphs.back();
+    }
+    hit->last_use = ++graph_clock;
+    const size_t ts = cfg.dtype == TACE_F32 ? 4 : 8;
+    auto copy = [s](void* dst, const void* src, size_t bytes) {
+      return bytes == 0 || cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s) == cudaSuccess;
+    };
+    bool ok = copy(sb + st.species, bt->species, 4 * (size_t)N) && copy(sb + st.graph_ptr, bt->graph_ptr, 4 * (size_t)(B + 1)) &&
+              copy(sb + st.edge_index, bt->edge_index, 16 * (size_t)E);
+    if (key.vec_mode) ok = ok && copy(sb + st.edge_vector, bt->edge_vector, ts * 3 * E);
+    else ok = ok && copy(sb + st.positions, bt->positions, ts * 3 * N) && copy(sb + st.lattice, bt->lattice, ts * 9 * B) &&
+              copy(sb + st.edge_shifts, bt->edge_shifts, ts * 3 * E);
+    if (!ok || cudaGraphLaunch(hit->exec, s) != cudaSuccess) return TACE_ERR_CUDA;
+    launches += hit->launches;
+    ++graph_replays;
+    ok = (!o->energy || copy(o->energy, sb + st.energy, ts * B)) && (!o->node_energy || copy(o->node_energy, sb + st.node_energy, ts * NL)) &&
+         (!o->forces || copy(o->forces, sb + st.forces, ts * 3 * N)) && (!o->virials || copy(o->virials, sb + st.virials, ts * 9 * B)) &&
+         (!o->stress || copy(o->stress, sb + st.stress, ts * 9 * B)) &&
+         (!o->edge_forces || copy(o->edge_forces, sb + st.edge_forces, ts * 3 * E));
+    return ok ? TACE_OK : TACE_ERR_CUDA;
+  }
 };
 
 template <typename T>
@@ -328,7 +472,7 @@ struct Model : ModelBase {
     if (!bytes || n_atoms < 0 || n_local < 0 || n_local > n_atoms || n_edges < 0 || n_graphs < 0) return TACE_ERR_INVALID_ARGUMENT;
     if (n_edges >= (1LL << 31) - 64 || n_atoms >= (1LL << 31) - 64) return TACE_ERR_CAPACITY;
     Arena ar; Bufs b;
-    *bytes = layout(ar, b, n_atoms, n_local, n_edges, n_graphs) + 256;
+    *bytes = layout(ar, b, n_atoms, n_local, n_edges, n_graphs) + 512 + this->stage_layout(n_atoms, n_local, n_edges, n_graphs).total;
     return TACE_OK;
   }
 
@@ -838,6 +982,7 @@ int tace_create(const TaceConfig* cfg, TaceModel** out) {
 
 void tace_destroy(TaceModel* model) {
   if (!model) return;
+  model->impl->release_graphs();
   delete model->impl;
   delete model;
 }
@@ -857,8 +1002,15 @@ int tace_workspace_bytes(const TaceModel* model, int64_t n_atoms, int64_t n_loca
 int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* out, void* workspace, size_t workspace_bytes,
                  tace_stream_t stream) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
-  return model->impl->forward(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  return model->impl->forward_entry(batch, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
+int tace_set_graph_mode(TaceModel* model, int enable) {
+  if (!model) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->graph_mode = enable != 0;
+  if (!enable) model->impl->release_graphs();
+  return TACE_OK;
+}
+int64_t tace_graph_replays(const TaceModel* model) { return model ? model->impl->graph_replays : TACE_ERR_INVALID_ARGUMENT; }
 int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   model->impl->exchange_fn = fn;

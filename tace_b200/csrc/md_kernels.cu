@@ -1,0 +1,160 @@
+// Molecular-dynamics support kernels for the domain-decomposed driver: velocity-Verlet updates,
+// kinetic energy, edge vectors from fp64 positions, and the row gather / scatter-add used to pack and
+// unpack halo messages.  All are single-pass streaming kernels (HBM-bound); state (positions,
+// velocities) is fp64, forces arrive in the model's dtype.
+//
+// The reference has no integrator of its own: its MD runs go through LAMMPS (`fix nve`) or ASE; these
+// entry points stand in for that host so a whole MD step stays on the device.
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <type_traits>
+
+#include "../../include/tace_b200.h"
+
+namespace tace {
+namespace {
+
+template <typename F>
+__global__ void md_kick_drift_kernel(double* __restrict__ pos, double* __restrict__ vel, const F* __restrict__ forces,
+                                     const double* __restrict__ inv_mass, long long n3, double kick, double dt) {
+  const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (k >= n3) return;
+  double v = vel[k];
+  if (forces) v += kick * (double)forces[k] * inv_mass[k / 3];
+  vel[k] = v;
+  if (pos) pos[k] += dt * v;
+}
+
+__global__ void md_kinetic_partial_kernel(const double* __restrict__ vel, const double* __restrict__ mass, long long n,
+                                          double* __restrict__ partial) {
+  __shared__ double red[256];
+  double acc = 0.0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const double vx = vel[3 * i], vy = vel[3 * i + 1], vz = vel[3 * i + 2];
+    acc += 0.5 * mass[i] * (vx * vx + vy * vy + vz * vz);
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[blockIdx.x] = red[0];
+}
+__global__ void md_kinetic_final_kernel(const double* __restrict__ partial, int n_partial, double* out) {
+  __shared__ double red[256];
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n_partial; i += blockDim.x) acc += partial[i];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = red[0];
+}
+
+template <typename T>
+__global__ void edge_vectors_kernel(const double* __restrict__ pos, const int64_t* __restrict__ edge_index, long long E,
+                                    T* __restrict__ out) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const long long s = edge_index[e], t = edge_index[E + e];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) out[3 * e + k] = (T)(pos[3 * t + k] - pos[3 * s + k]);
+}
+
+// dst[r] = src[idx[r]]  (GATHER)   or   dst[idx[r]] += src[r]  (indices unique within one call)
+template <typename V, bool GATHER>
+__global__ void rows_kernel(const V* __restrict__ src, const int64_t* __restrict__ idx, long long n_rows, int row_len,
+                            V* __restrict__ dst) {
+  const long long total = n_rows * row_len;
+  for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < total; k += (long long)gridDim.x * blockDim.x) {
+    const long long r = k / row_len;
+    const int c = (int)(k - r * row_len);
+    if (GATHER) dst[k] = src[idx[r] * row_len + c];
+    else {
+      V* d = dst + idx[r] * row_len + c;
+      *d = *d + src[k];
+    }
+  }
+}
+
+inline unsigned grid_for(long long total, int block) {
+  long long g = (total + block - 1) / block;
+  const long long cap = 148LL * 16;
+  return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+}  // namespace tace
+
+using namespace tace;
+
+extern "C" int tace_md_kick_drift(double* positions, double* velocities, const void* forces, int32_t force_dtype,
+                                  const double* inv_mass, int64_t n_atoms, double kick, double dt, tace_stream_t stream) {
+  if (!velocities || n_atoms < 0 || (forces && !inv_mass)) return TACE_ERR_INVALID_ARGUMENT;
+  if (force_dtype != TACE_F32 && force_dtype != TACE_F64) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_atoms == 0) return TACE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long n3 = 3 * n_atoms;
+  const unsigned blocks = (unsigned)((n3 + 255) / 256);
+  if (force_dtype == TACE_F32)
+    md_kick_drift_kernel<float><<<blocks, 256, 0, s>>>(positions, velocities, static_cast<const float*>(forces), inv_mass, n3, kick, dt);
+  else
+    md_kick_drift_kernel<double><<<blocks, 256, 0, s>>>(positions, velocities, static_cast<const double*>(forces), inv_mass, n3, kick, dt);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+extern "C" int tace_md_kinetic_energy(const double* velocities, const double* mass, int64_t n_atoms, double* scratch,
+                                      double* out, tace_stream_t stream) {
+  if (!velocities || !mass || !scratch || !out || n_atoms < 0) return TACE_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  long long blocks = (n_atoms + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 1024) blocks = 1024;
+  md_kinetic_partial_kernel<<<(unsigned)blocks, 256, 0, s>>>(velocities, mass, n_atoms, scratch);
+  md_kinetic_final_kernel<<<1, 256, 0, s>>>(scratch, (int)blocks, out);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+extern "C" int tace_edge_vectors(const double* positions, const int64_t* edge_index, int64_t n_edges, void* out, int32_t dtype,
+                                 tace_stream_t stream) {
+  if (n_edges < 0 || (n_edges > 0 && (!positions || !edge_index || !out))) return TACE_ERR_INVALID_ARGUMENT;
+  if (dtype != TACE_F32 && dtype != TACE_F64) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_edges == 0) return TACE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)((n_edges + 255) / 256);
+  if (dtype == TACE_F32) edge_vectors_kernel<float><<<blocks, 256, 0, s>>>(positions, edge_index, n_edges, static_cast<float*>(out));
+  else edge_vectors_kernel<double><<<blocks, 256, 0, s>>>(positions, edge_index, n_edges, static_cast<double*>(out));
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+namespace {
+template <bool GATHER>
+int rows_dispatch(const void* src, const int64_t* idx, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,
+                  tace_stream_t stream) {
+  if (n_rows < 0 || row_len <= 0 || (n_rows > 0 && (!src || !idx || !dst))) return TACE_ERR_INVALID_ARGUMENT;
+  if (elem_bytes != 4 && elem_bytes != 8) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_rows == 0) return TACE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = grid_for(n_rows * (long long)row_len, 256);
+  // a gather moves bit patterns (any 4- or 8-byte type); a scatter-add treats them as float / double
+  using V4 = typename std::conditional<GATHER, uint32_t, float>::type;
+  using V8 = typename std::conditional<GATHER, uint64_t, double>::type;
+  if (elem_bytes == 4)
+    rows_kernel<V4, GATHER><<<blocks, 256, 0, s>>>(static_cast<const V4*>(src), idx, n_rows, row_len, static_cast<V4*>(dst));
+  else
+    rows_kernel<V8, GATHER><<<blocks, 256, 0, s>>>(static_cast<const V8*>(src), idx, n_rows, row_len, static_cast<V8*>(dst));
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+}  // namespace
+
+extern "C" int tace_rows_gather(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes,
+                                void* dst, tace_stream_t stream) {
+  return rows_dispatch<true>(src, index, n_rows, row_len, elem_bytes, dst, stream);
+}
+extern "C" int tace_rows_scatter_add(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes,
+                                     void* dst, tace_stream_t stream) {
+  return rows_dispatch<false>(src, index, n_rows, row_len, elem_bytes, dst, stream);
+}

@@ -19,7 +19,8 @@ EXPORTS = [
     "tace_status_string", "tace_create", "tace_destroy", "tace_weight_count", "tace_weight_info", "tace_set_weight",
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill",
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
-    "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc",
+    "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
+    "tace_edge_vectors", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays",
 ]
 
 
@@ -95,8 +96,25 @@ def load() -> ctypes.CDLL:
     lib.tace_nl_count.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_void_p]
     lib.tace_nl_fill.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_int64,
                                  c_void_p, c_void_p, c_void_p]
+    lib.tace_set_graph_mode.argtypes = [c_void_p, c_int]
+    lib.tace_graph_replays.argtypes = [c_void_p]
+    lib.tace_graph_replays.restype = c_int64
+    lib.tace_md_kick_drift.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_double, c_double, c_void_p]
+    lib.tace_md_kinetic_energy.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+    lib.tace_edge_vectors.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_void_p]
+    lib.tace_rows_gather.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
+    lib.tace_rows_scatter_add.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
     _lib = lib
     return lib
+
+
+def dtype_code(dtype) -> int:
+    import torch
+    if dtype == torch.float32:
+        return TACE_F32
+    if dtype == torch.float64:
+        return TACE_F64
+    raise TaceError(f"unsupported dtype {dtype}")
 
 
 def check(status: int, what: str) -> None:

@@ -1,0 +1,201 @@
+"""Velocity-Verlet molecular dynamics of one periodic system on one or several GPUs.
+
+Every rank owns the atoms of one block of the cell (``tace_b200.domain``), keeps positions and
+velocities in fp64 on its GPU and, per step: half kick + drift, ghost positions from the owning
+ranks, a fresh neighbour list over owned targets, one model evaluation in edge-vector mode (the
+LAMMPS contract of the reference: ghost feature rows refreshed between interaction layers, ghost
+gradients returned to their owners, ``tace/models/lammps.py:82-142``), forces that landed on ghost
+rows returned to their owners, second half kick.  Ownership and ghost lists are rebuilt when an atom
+has moved more than half the skin.
+
+Units: eV, Angstrom, atomic mass units, femtoseconds.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import time
+from typing import Dict, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .domain import Domain
+from .graph import z_to_index
+from .neighbour_list import neighbor_list_batch
+
+# 1 eV / amu in Angstrom^2 / fs^2, and Boltzmann's constant in eV / K
+ACCEL = 9.64853321233e-3
+KB = 8.617333262e-5
+
+# standard atomic weights of the elements the synthetic workloads use (amu)
+_MASSES = {1: 1.008, 6: 12.011, 7: 14.007, 8: 15.999, 13: 26.9815385, 14: 28.085, 22: 47.867, 23: 50.9415, 24: 51.9961,
+           26: 55.845, 27: 58.933194, 28: 58.6934, 29: 63.546}
+
+
+def masses_for(atomic_numbers: Sequence[int]) -> np.ndarray:
+    try:
+        return np.array([_MASSES[int(z)] for z in atomic_numbers], dtype=np.float64)
+    except KeyError as exc:  # pragma: no cover - message only
+        raise ValueError(f"no tabulated mass for Z={exc.args[0]}; pass `masses` explicitly") from None
+
+
+def maxwell_boltzmann(masses: np.ndarray, temperature: float, seed: int) -> np.ndarray:
+    """Velocities (Angstrom / fs) at ``temperature`` with zero total momentum, rescaled to the exact
+    kinetic temperature."""
+    rng = np.random.default_rng(seed)
+    sigma = np.sqrt(KB * temperature * ACCEL / masses)[:, None]
+    v = rng.normal(size=(len(masses), 3)) * sigma
+    v -= (masses[:, None] * v).sum(0) / masses.sum()
+    ke = 0.5 * (masses[:, None] * v * v).sum() / ACCEL
+    t_now = 2.0 * ke / (3.0 * len(masses) * KB)
+    return v * np.sqrt(temperature / t_now) if t_now > 0 else v
+
+
+class DomainMD:
+    """``model``: a ``tace_b200.models.TensorModel``.  ``positions`` [N,3], ``atomic_numbers`` [N],
+    ``velocities`` [N,3] describe the WHOLE system and must be identical on every rank (each rank keeps
+    only its own block).  ``group``: the ``torch.distributed`` process group (``None`` = default group;
+    unused when ``world_size == 1``)."""
+
+    def __init__(self, model, cell: np.ndarray, positions: np.ndarray, atomic_numbers: np.ndarray,
+                 velocities: Optional[np.ndarray] = None, masses: Optional[np.ndarray] = None, dt: float = 1.0,
+                 skin: float = 0.5, rank: int = 0, world_size: int = 1, device: Optional[torch.device] = None,
+                 grid: Optional[Tuple[int, int, int]] = None, group=None):
+        self.model = model
+        self.device = torch.device(device if device is not None else "cuda")
+        self.rank, self.world_size, self.group = rank, world_size, group
+        self.dt = float(dt)
+        self.cutoff = float(model.get_cutoff())
+        self.dtype = model.get_model_dtype()
+        self.lib = _lib.load()
+        model._set_lammps_mliap(True)
+        model.reset_target_property(["energy", "forces"])
+        self.domain = Domain(cell, self.cutoff, skin, rank, world_size, self.device, grid=grid, group=group)
+
+        positions = np.asarray(positions, dtype=np.float64)
+        n = positions.shape[0]
+        z = np.asarray(atomic_numbers)
+        if masses is None:
+            masses = masses_for(z)
+        if velocities is None:
+            velocities = np.zeros((n, 3))
+        species = z_to_index(z, model.get_atomic_numbers())
+        # every rank starts from the same global arrays and keeps its own block: rank r contributes
+        # the r-th slice to the first partition, which then moves every atom to its owner
+        lo, hi = (n * rank) // world_size, (n * (rank + 1)) // world_size
+        dev = self.device
+        state = {
+            "positions": torch.as_tensor(positions[lo:hi], dtype=torch.float64, device=dev),
+            "velocities": torch.as_tensor(np.asarray(velocities, dtype=np.float64)[lo:hi], device=dev),
+            "species": torch.as_tensor(np.asarray(species[lo:hi], dtype=np.int64), device=dev),
+            "mass": torch.as_tensor(np.asarray(masses, dtype=np.float64)[lo:hi], device=dev),
+            "ids": torch.arange(lo, hi, dtype=torch.int64, device=dev),
+        }
+        self.n_global = n
+        self.step_count = 0
+        self.timings: Dict[str, float] = {}
+        self._repartition(state)
+        self.forces = None
+        self.potential_energy = None
+        self._evaluate()
+
+    # -- state -------------------------------------------------------------------------------------
+    def _repartition(self, state: Dict[str, torch.Tensor]) -> None:
+        new = self.domain.partition(state)
+        self.positions = new["positions"].contiguous()
+        self.velocities = new["velocities"].contiguous()
+        self.species = new["species"].contiguous()
+        self.mass = new["mass"].contiguous()
+        self.ids = new["ids"].contiguous()
+        self.inv_mass = (1.0 / self.mass).contiguous()
+        self.local_species = self.domain.local_rows(self.species).to(torch.int32).contiguous()
+        self._ke_scratch = torch.empty(1025, dtype=torch.float64, device=self.device)
+
+    def _state(self) -> Dict[str, torch.Tensor]:
+        return {"positions": self.positions, "velocities": self.velocities, "species": self.species, "mass": self.mass,
+                "ids": self.ids}
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    # -- one force evaluation ------------------------------------------------------------------------
+    def _evaluate(self) -> None:
+        dom = self.domain
+        n, g = dom.n_owned, dom.n_ghost
+        t0 = time.perf_counter()
+        local_pos = dom.local_positions(self.positions)
+        t1 = time.perf_counter()
+        # open (non-periodic) neighbour list over owned + ghost atoms, owned targets only
+        lattice = torch.eye(3, dtype=torch.float64, device=self.device)[None]
+        pbc = torch.zeros(1, 3, dtype=torch.uint8, device=self.device)
+        ptr = torch.tensor([0, n + g], dtype=torch.int32, device=self.device)
+        edge_index, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff, n_targets=n)
+        E = int(edge_index.shape[1])
+        vec = torch.empty(E, 3, dtype=self.dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.tace_edge_vectors(local_pos.data_ptr(), edge_index.data_ptr(), E, vec.data_ptr(),
+                                                  _lib.dtype_code(self.dtype), self._stream()), "tace_edge_vectors")
+        t2 = time.perf_counter()
+        out = self.model({"species": self.local_species, "edge_index": edge_index, "edge_vector": vec, "natoms": (n, g),
+                          "lmp_data": dom.exchange})
+        forces = out["forces"]
+        if g:
+            dom.exchange.reverse_exchange(forces, forces, 3)
+        self.forces = forces[:n].contiguous()
+        self.node_energy = out["node_energy"]
+        self.n_edges = E
+        t3 = time.perf_counter()
+        for k, v in (("halo_positions", t1 - t0), ("neighbour_list", t2 - t1), ("model", t3 - t2)):
+            self.timings[k] = self.timings.get(k, 0.0) + v
+
+    # -- integration ---------------------------------------------------------------------------------
+    def step(self, n_steps: int = 1) -> None:
+        kick = 0.5 * self.dt * ACCEL
+        fcode = _lib.dtype_code(self.dtype)
+        for _ in range(n_steps):
+            n = self.domain.n_owned
+            with torch.cuda.device(self.device):
+                _lib.check(self.lib.tace_md_kick_drift(self.positions.data_ptr(), self.velocities.data_ptr(), self.forces.data_ptr(),
+                                                       fcode, self.inv_mass.data_ptr(), n, kick, self.dt, self._stream()),
+                           "tace_md_kick_drift")
+            if self.domain.needs_partition(self.positions):
+                self._repartition(self._state())
+            self._evaluate()
+            n = self.domain.n_owned
+            with torch.cuda.device(self.device):
+                _lib.check(self.lib.tace_md_kick_drift(None, self.velocities.data_ptr(), self.forces.data_ptr(), fcode,
+                                                       self.inv_mass.data_ptr(), n, kick, 0.0, self._stream()), "tace_md_kick_drift")
+            self.step_count += 1
+
+    # -- observables (collective: every rank must call) ---------------------------------------------
+    def _all_sum(self, x: torch.Tensor) -> float:
+        if self.world_size > 1:
+            import torch.distributed as dist
+
+            x = x.clone()
+            dist.all_reduce(x, group=self.group)
+        return float(x.item())
+
+    def kinetic_energy(self) -> float:
+        out = self._ke_scratch[1024:1025]
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.tace_md_kinetic_energy(self.velocities.data_ptr(), self.mass.data_ptr(), self.domain.n_owned,
+                                                       self._ke_scratch.data_ptr(), out.data_ptr(), self._stream()),
+                       "tace_md_kinetic_energy")
+        return self._all_sum(out.clone().reshape(())) / ACCEL
+
+    def potential(self) -> float:
+        return self._all_sum(self.node_energy.to(torch.float64).sum())
+
+    def temperature(self) -> float:
+        return 2.0 * self.kinetic_energy() / (3.0 * self.n_global * KB)
+
+    def gather(self) -> Dict[str, np.ndarray]:
+        """Whole-system positions, velocities and forces ordered by atom id (collective)."""
+        parts = {"ids": self.ids, "positions": self.positions, "velocities": self.velocities,
+                 "forces": self.forces.to(torch.float64)}
+        full = {k: torch.cat(self.domain._all_gather_rows(v.contiguous())) for k, v in parts.items()}
+        order = torch.argsort(full["ids"])
+        return {k: v[order].cpu().numpy() for k, v in full.items()}

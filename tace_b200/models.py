@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import copy
 import ctypes
+import os
 import math
 from typing import Any, Dict, List, Optional, Union
 
@@ -236,6 +237,7 @@ class TensorModel(torch.nn.Module):
         self._handle = None
         self._handle_key = None
         self._workspace = None
+        self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
         self._set_target_property()
 
     # ---- reference getters (tace/models/adapter.py:386-452) ----------------------------------
@@ -305,8 +307,19 @@ class TensorModel(torch.nn.Module):
                 if arr.size != numel.value:
                     raise _lib.TaceError(f"weight {name.value.decode()}: packed {arr.size} elements, library expects {numel.value}")
                 _lib.check(lib.tace_set_weight(handle, name.value, arr.ctypes.data_as(ctypes.c_void_p), arr.size), "tace_set_weight")
+            _lib.check(lib.tace_set_graph_mode(handle, int(self._graph_mode)), "tace_set_graph_mode")
         self._handle, self._handle_key = handle, key
         return handle
+
+    def set_graph_mode(self, enable: bool = True) -> None:
+        """Replay repeated evaluations of one batch shape as a CUDA graph (default on; the environment
+        variable TACE_B200_GRAPHS=0 turns it off for every model)."""
+        self._graph_mode = bool(enable)
+        if self._handle is not None:
+            _lib.check(_lib.load().tace_set_graph_mode(self._handle, int(self._graph_mode)), "tace_set_graph_mode")
+
+    def graph_replays(self) -> int:
+        return int(_lib.load().tace_graph_replays(self._handle)) if self._handle is not None else 0
 
     def release(self) -> None:
         if self._handle is not None:
@@ -337,8 +350,8 @@ class TensorModel(torch.nn.Module):
     def forward(self, data: Dict[str, torch.Tensor]) -> Dict[str, Optional[torch.Tensor]]:
         lib = _lib.load()
         dtype = self.get_model_dtype()
-        node_attrs = data["node_attrs"]
-        device = node_attrs.device
+        node_attrs = data.get("node_attrs")
+        device = (node_attrs if node_attrs is not None else data["species"]).device
         if device.type != "cuda":
             raise _lib.TaceError("tace_b200 runs on CUDA devices only (no CPU path)")
         handle = self._native(device)
@@ -361,7 +374,7 @@ class TensorModel(torch.nn.Module):
             graph_ptr = torch.tensor([0, nlocal], dtype=torch.int32, device=device)
             batch.edge_vector = real(data["edge_vector"]).data_ptr()
         else:
-            n_atoms = n_local = int(node_attrs.shape[0])
+            n_atoms = n_local = int(species.shape[0])
             graph_ptr = data["ptr"].to(torch.int32).contiguous()
             n_graphs = int(graph_ptr.numel() - 1)
             batch.positions = real(data["positions"]).data_ptr()
@@ -377,7 +390,7 @@ class TensorModel(torch.nn.Module):
         res["energy"] = torch.empty(n_graphs, dtype=dtype, device=device)
         res["node_energy"] = torch.empty(n_local, dtype=dtype, device=device)
         out.energy, out.node_energy = res["energy"].data_ptr(), res["node_energy"].data_ptr()
-        if flags.compute_forces and not self.lmp:
+        if flags.compute_forces:  # edge-vector mode: rows of ghost atoms hold the force parts that belong to their owners
             res["forces"] = torch.empty(n_atoms, 3, dtype=dtype, device=device)
             out.forces = res["forces"].data_ptr()
         if (flags.compute_stress or flags.compute_virials) and not self.lmp:

@@ -43,10 +43,12 @@ def complete_cell(lattice: np.ndarray, positions: np.ndarray, pbc, cutoff: float
 
 
 def neighbor_list_batch(positions: torch.Tensor, lattice: torch.Tensor, pbc: torch.Tensor, graph_ptr: torch.Tensor,
-                        cutoff: float) -> Tuple[torch.Tensor, torch.Tensor]:
+                        cutoff: float, n_targets: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """positions fp64 [N,3], lattice fp64 [B,3,3], pbc uint8 [B,3], graph_ptr int32 [B+1], all on
     one CUDA device.  Returns ``edge_index int64[2,E]`` (row 0 = source, row 1 = target, grouped by
-    target) and ``edge_shifts int32[E,3]`` with edge vector = r[target] - r[source] + shift @ cell."""
+    target) and ``edge_shifts int32[E,3]`` with edge vector = r[target] - r[source] + shift @ cell.
+    ``n_targets``: keep only edges whose target is one of the first ``n_targets`` atoms (the owned
+    atoms of a domain; the rest are ghost copies that only act as sources)."""
     lib = _lib.load()
     dev = positions.device
     if dev.type != "cuda":
@@ -61,6 +63,8 @@ def neighbor_list_batch(positions: torch.Tensor, lattice: torch.Tensor, pbc: tor
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(lib.tace_nl_count(positions.data_ptr(), lattice.data_ptr(), pbc.data_ptr(), graph_ptr.data_ptr(), b, n,
                                      float(cutoff), counts.data_ptr(), stream), "tace_nl_count")
+        if n_targets is not None and n_targets < n:
+            counts[n_targets:] = 0  # rows without edges start at the end of the list and write nothing
         row_ptr = torch.zeros(n + 1, dtype=torch.int64, device=dev)
         torch.cumsum(counts, 0, out=row_ptr[1:])
         n_edges = int(row_ptr[-1].item())

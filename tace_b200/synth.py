@@ -90,7 +90,7 @@ def random_crystals(num: int = 64, seed: int = 1, nmin: int = 8, nmax: int = 64,
     return out
 
 
-def water_box(n_side: int = 22, box: float = 68.6, sigma: float = 0.03, seed: int = 2, n_mol: int = 10800) -> Structure:
+def water_box(n_side: int = 23, box: float = 68.6, sigma: float = 0.03, seed: int = 2, n_mol: int = 10800) -> Structure:
     """Rigid H2O molecules (O-H 0.9572 A, H-O-H 104.52 deg) on a jittered grid with uniform random
     orientations and Gaussian noise.  Defaults give 32,400 atoms at 1.0 g/cm^3."""
     rng = np.random.default_rng(seed)

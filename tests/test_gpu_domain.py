@@ -1,0 +1,179 @@
+"""Domain-decomposed evaluation and MD on the GPU.
+
+One rank (the block is the whole cell, ghosts are periodic images of the rank's own atoms) must give the
+oracle's energy and forces; two ranks on two GPUs (skipped on a single-GPU machine) must give the same
+forces as one; the MD support kernels are checked against torch; NVE dynamics must conserve energy and
+momentum."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import make_models, oracle_batch
+from tace_b200 import lib as _lib
+from tace_b200 import synth
+from tace_b200.md import ACCEL, DomainMD, masses_for, maxwell_boltzmann
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _system(seed=7):
+    return synth.fcc_supercell(3, 3.61, 0.05, seed=seed, species=(13, 29), fractions=(0.3, 0.7))
+
+
+@pytest.mark.parametrize("num_layers", [1, 2])
+def test_single_rank_domain_matches_oracle(num_layers):
+    s = _system()
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, num_layers=num_layers, targets=("energy", "forces"))
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64))
+    md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], skin=0.4, device=DEV)
+    assert md.domain.n_ghost > 0
+    got = md.gather()
+    assert abs(md.potential() - float(ref["energy"][0])) / len(s["positions"]) < 1e-8
+    assert np.abs(got["forces"] - ref["forces"].detach().numpy()).max() < 1e-7
+    assert model.device_error() == 0
+
+
+def test_md_support_kernels_match_torch():
+    lib = _lib.load()
+    g = torch.Generator(device="cpu").manual_seed(0)
+    n = 1000
+    pos = torch.randn(n, 3, generator=g, dtype=torch.float64).to(DEV)
+    vel = torch.randn(n, 3, generator=g, dtype=torch.float64).to(DEV)
+    mass = (torch.rand(n, generator=g, dtype=torch.float64) + 0.5).to(DEV)
+    inv_mass = 1.0 / mass
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    for dtype in (torch.float32, torch.float64):
+        f = torch.randn(n, 3, generator=g, dtype=torch.float64).to(DEV).to(dtype)
+        p2, v2 = pos.clone(), vel.clone()
+        _lib.check(lib.tace_md_kick_drift(p2.data_ptr(), v2.data_ptr(), f.data_ptr(), _lib.dtype_code(dtype), inv_mass.data_ptr(), n,
+                                          0.25, 2.0, stream), "kick_drift")
+        v_ref = vel + 0.25 * f.to(torch.float64) * inv_mass[:, None]
+        assert torch.allclose(v2, v_ref, rtol=0, atol=1e-14)
+        assert torch.allclose(p2, pos + 2.0 * v_ref, rtol=0, atol=1e-13)
+        v3 = vel.clone()
+        _lib.check(lib.tace_md_kick_drift(None, v3.data_ptr(), f.data_ptr(), _lib.dtype_code(dtype), inv_mass.data_ptr(), n, 0.25, 0.0,
+                                          stream), "kick")
+        assert torch.equal(v3, v2)
+    scratch = torch.empty(1024, dtype=torch.float64, device=DEV)
+    out = torch.empty(1, dtype=torch.float64, device=DEV)
+    _lib.check(lib.tace_md_kinetic_energy(vel.data_ptr(), mass.data_ptr(), n, scratch.data_ptr(), out.data_ptr(), stream), "ke")
+    assert abs(out.item() - float((0.5 * mass[:, None] * vel * vel).sum())) < 1e-9
+    # edge vectors
+    E = 5000
+    ei = torch.randint(0, n, (2, E), generator=g).to(DEV)
+    for dtype in (torch.float32, torch.float64):
+        vec = torch.empty(E, 3, dtype=dtype, device=DEV)
+        _lib.check(lib.tace_edge_vectors(pos.data_ptr(), ei.data_ptr(), E, vec.data_ptr(), _lib.dtype_code(dtype), stream), "vec")
+        assert torch.equal(vec, (pos[ei[1]] - pos[ei[0]]).to(dtype))
+    # row gather / scatter-add (distinct indices)
+    for dtype in (torch.float32, torch.float64, torch.int64, torch.int32):
+        src = (torch.randn(n, 7, generator=g, dtype=torch.float64) * 100).to(DEV).to(dtype).contiguous()
+        idx = torch.randperm(n, generator=g)[:300].to(DEV)
+        dst = torch.empty(300, 7, dtype=dtype, device=DEV)
+        _lib.check(lib.tace_rows_gather(src.data_ptr(), idx.data_ptr(), 300, 7, src.element_size(), dst.data_ptr(), stream), "gather")
+        assert torch.equal(dst, src[idx])
+        if dtype.is_floating_point:
+            acc = src.clone()
+            _lib.check(lib.tace_rows_scatter_add(dst.data_ptr(), idx.data_ptr(), 300, 7, src.element_size(), acc.data_ptr(), stream),
+                       "scatter_add")
+            ref = src.clone()
+            ref[idx] += dst
+            assert torch.equal(acc, ref)
+
+
+def test_nve_conserves_energy_and_momentum():
+    s = _system(seed=9)
+    model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+    masses = masses_for(s["atomic_numbers"])
+    vel = maxwell_boltzmann(masses, 300.0, seed=1)
+    md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, dt=1.0, skin=0.3, device=DEV)
+    assert abs(md.temperature() - 300.0) < 1e-6
+    e0 = md.potential() + md.kinetic_energy()
+    scale = abs(md.kinetic_energy())
+    md.step(25)
+    e1 = md.potential() + md.kinetic_energy()
+    # random weights give a rough energy surface; velocity Verlet with dt = 1 fs still keeps the total
+    # energy to a small fraction of the kinetic energy
+    assert abs(e1 - e0) < 2e-3 * scale, (e0, e1, scale)
+    out = md.gather()
+    p = (masses[:, None] * out["velocities"]).sum(0)
+    assert np.abs(p).max() < 1e-9 * np.abs(masses[:, None] * out["velocities"]).sum()
+    assert model.device_error() == 0
+
+
+def test_repartition_keeps_the_trajectory():
+    """Same dynamics with a tiny skin (re-partition nearly every step) and a large one."""
+    s = _system(seed=11)
+    masses = masses_for(s["atomic_numbers"])
+    vel = maxwell_boltzmann(masses, 600.0, seed=2)
+    outs = []
+    for skin in (0.02, 1.0):
+        model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+        md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, dt=1.0, skin=skin, device=DEV)
+        md.step(10)
+        outs.append((md.gather(), md.domain.n_partitions))
+    assert outs[0][1] > outs[1][1] >= 1
+    a, b = outs[0][0], outs[1][0]
+    cell = s["cell"]
+    d = a["positions"] - b["positions"]
+    d -= np.round(d @ np.linalg.inv(cell)) @ cell  # positions are wrapped at every partition
+    assert np.abs(d).max() < 1e-9
+    assert np.abs(a["forces"] - b["forces"]).max() < 1e-8
+
+
+def _two_rank_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        s = _system(seed=13)
+        model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+        masses = masses_for(s["atomic_numbers"])
+        vel = maxwell_boltzmann(masses, 300.0, seed=3)
+        md = DomainMD(model.to(dev), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, skin=0.4, rank=rank,
+                      world_size=world, device=dev)
+        e = md.potential()
+        md.step(3)
+        out = md.gather()
+        ret[rank] = {"energy": e, "forces": out["forces"], "positions": out["positions"], "owned": md.domain.n_owned,
+                     "err": model.device_error()}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_match_one():
+    import torch.multiprocessing as mp
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    s = _system(seed=13)
+    model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+    masses = masses_for(s["atomic_numbers"])
+    vel = maxwell_boltzmann(masses, 300.0, seed=3)
+    md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, skin=0.4, device=DEV)
+    e = md.potential()
+    md.step(3)
+    one = md.gather()
+    for r in range(2):
+        assert ret[r]["err"] == 0 and 0 < ret[r]["owned"] < len(s["positions"])
+        assert abs(ret[r]["energy"] - e) < 1e-8 * len(s["positions"])
+        assert np.abs(ret[r]["forces"] - one["forces"]).max() < 1e-8
+        assert np.abs(ret[r]["positions"] - one["positions"]).max() < 1e-10

@@ -157,3 +157,35 @@ def test_fp32_tensor_core_channel_widths(L, C):
     """Channel counts for which fp32 models run the radial GEMMs and the per-rank linears on tcgen05."""
     structs = synth.random_crystals(2, seed=9, nmin=6, nmax=12, zmax=2)
     model_out, ref = run_case(structs, L, C, [1, 2], 4.5, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_graph_replay_is_bit_identical_and_follows_new_inputs(dtype):
+    """From the third evaluation of one batch shape on, the pass is replayed as a CUDA graph: results must
+    equal the launch-by-launch pass bit for bit, also when the caller's tensors live at new addresses and
+    hold new coordinates."""
+    structs = synth.random_crystals(3, seed=8, nmin=4, nmax=10, zmax=3)
+    model, oracle, cfg = make_models(2, 32, [1, 2, 3], 4.5, 20.0, dtype)
+    dev = torch.device("cuda:0")
+    data = to_device(oracle_batch(structs, [1, 2, 3], 4.5, dtype), dev)
+    first = {k: v.clone() for k, v in model(data).items() if v is not None}
+    assert model.graph_replays() == 0
+    keep = []
+    for _ in range(3):
+        again = {k: v.clone() for k, v in data.items()}  # fresh addresses
+        keep.append(again)
+        out = model(again)
+        for k, v in first.items():
+            assert torch.equal(out[k], v), k
+    assert model.graph_replays() >= 2
+    # same shapes, scaled coordinates: the replay must read the new values
+    scaled = {k: v.clone() for k, v in data.items()}
+    scaled["positions"] = data["positions"] * 1.01
+    scaled["lattice"] = data["lattice"] * 1.01
+    replayed = {k: v.clone() for k, v in model(scaled).items() if v is not None}
+    model.set_graph_mode(False)
+    direct = model(scaled)
+    for k, v in replayed.items():
+        assert torch.equal(direct[k], v), k
+    assert not torch.equal(replayed["energy"], first["energy"])
+    assert model.device_error() == 0
