@@ -128,6 +128,15 @@ int tace_forward(TaceModel* model, const TaceBatch* batch, const TaceOutputs* ou
  * tace_set_graph_mode(model, 0) switches replay off and frees the captured graphs;
  * tace_graph_replays returns how many calls were served by a graph launch. */
 int tace_set_graph_mode(TaceModel* model, int enable);
+
+/* Edge chunking (no reference counterpart: the reference materialises every per-edge tensor, which bounds the
+ * system size by memory, tace/models/_e3nn/inter.py:185-285).  A batch with more than `max_edges` edges
+ * (default 2^21, minimum 1024) is evaluated in chunks of target atoms holding about `max_edges` edges each; per-edge
+ * activations, path weights and source gradients exist for one chunk at a time and are recomputed in the backward
+ * pass.  tace_workspace_bytes reflects the setting, so call it after changing the limit.  A chunk always ends at an
+ * atom boundary; an atom with more than 8192 neighbours makes tace_forward return a capacity error.  Chunked
+ * passes read the chunk table back to the host once (one stream synchronisation per call). */
+int tace_set_chunk_edges(TaceModel* model, int64_t max_edges);
 int64_t tace_graph_replays(const TaceModel* model);
 
 /* Ghost-row exchange for edge-vector mode with n_local < n_atoms and more than one layer.  Stands

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(128) edge_mlp_out_kernel(const EdgeArgs<T> a) 
 #pragma unroll
     for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
   }
-  a.ddlen[e] = dd;
+  a.ddlen[e] = a.accumulate_ddlen ? a.ddlen[e] + dd : dd;
 }
 
 template <typename T>

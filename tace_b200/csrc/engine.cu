@@ -95,6 +95,10 @@ struct ModelBase {
 
   // kernel-launch counter and optional per-phase CUDA-event timing
   long long launches = 0;
+  // Batches with more edges than this are evaluated in chunks of target atoms: the per-edge tensors (radial-MLP
+  // activations, path weights, per-edge source gradients) then exist for one chunk at a time and the backward pass
+  // recomputes them, so memory per edge drops from kilobytes to about two hundred bytes.
+  long long max_chunk_edges = 1LL << 21;
   tace_exchange_fn exchange_fn = nullptr;  // ghost-row exchange between layers (edge-vector mode)
   void* exchange_user = nullptr;
   int* dev_error = nullptr;  // device word written by kernels whose bounded waits expire
@@ -180,7 +184,7 @@ struct ModelBase {
     if (!bt || !o || !ws) return TACE_ERR_INVALID_ARGUMENT;
     const int64_t N = bt->n_atoms, NL = bt->n_local, E = bt->n_edges;
     const int32_t B = bt->n_graphs;
-    if (!graph_mode || profile || exchange_fn || N <= 0 || E <= 0 || B <= 0 || NL < 0 || NL > N)
+    if (!graph_mode || profile || exchange_fn || N <= 0 || E <= 0 || B <= 0 || NL < 0 || NL > N || E > max_chunk_edges)
       return forward(bt, o, ws, ws_bytes, s);
     const Stage st = stage_layout(N, NL, E, B);
     if (ws_bytes < st.total + 256) return forward(bt, o, ws, ws_bytes, s);
@@ -406,6 +410,7 @@ struct Model : ModelBase {
   }
 
   // ---- workspace ---------------------------------------------------------------------------
+  static constexpr long long kChunkSlack = 8192;  // a chunk ends at an atom boundary: room for one atom's edges beyond the target
   struct LayerBufs {
     T *h_in, *x, *xx, *gxx, *W, *H3, *Z1, *Z2, *Z3, *Hact, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
@@ -413,6 +418,8 @@ struct Model : ModelBase {
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
+    int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
+    int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
     T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen;
     std::vector<LayerBufs> lay;
@@ -428,7 +435,21 @@ struct Model : ModelBase {
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
-    b.dxe = NL_ > 1 ? ar.take<T>((size_t)E * D * C) : nullptr;  // per-edge gradient rows of the source features
+    const bool chunked = E > max_chunk_edges;
+    b.n_chunks = chunked ? (int)((E + max_chunk_edges - 1) / max_chunk_edges) : 1;
+    b.chunk_rows = chunked ? max_chunk_edges + kChunkSlack : E;
+    const long long Ec = b.chunk_rows;
+    b.chunk_atom_ptr = ar.take<int>(b.n_chunks + 1); b.chunk_edge_ptr = ar.take<int>(b.n_chunks + 1);
+    b.keys_cs = chunked ? ar.take<int>(E) : nullptr; b.perm_cs = chunked ? ar.take<int>(E) : nullptr;
+    b.dxe = NL_ > 1 ? ar.take<T>((size_t)Ec * D * C) : nullptr;  // per-edge gradient rows of the source features
+    T* shared_edge[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    T* shared_W = nullptr;
+    if (chunked) {  // one set of chunk-sized per-edge buffers serves every layer
+      for (int k = 0; k < 5; ++k) shared_edge[k] = ar.take<T>((size_t)Ec * kHidden);
+      int np_max = 0;
+      for (const auto& p : layers) np_max = p.tp.NP > np_max ? p.tp.NP : np_max;
+      shared_W = ar.take<T>((size_t)Ec * np_max * C);
+    }
     b.lay.resize(NL_);
     T* prev_h = ar.take<T>((size_t)N * C);   // h_0: species embedding, scalar channels
     T* prev_gh = nullptr;
@@ -442,10 +463,12 @@ struct Model : ModelBase {
       const bool ghosts = (N != NL) && !p.scalar_src;  // exchanged copies of x and of its gradient
       lb.xx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.gxx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
-      lb.H3 = ar.take<T>((size_t)E * kHidden);
-      lb.Z1 = ar.take<T>((size_t)E * kHidden); lb.Z2 = ar.take<T>((size_t)E * kHidden);
-      lb.Z3 = ar.take<T>((size_t)E * kHidden); lb.Hact = ar.take<T>((size_t)E * kHidden);
-      lb.W = ar.take<T>((size_t)E * p.tp.NP * C);
+      lb.H3 = chunked ? shared_edge[0] : ar.take<T>((size_t)E * kHidden);
+      lb.Z1 = chunked ? shared_edge[1] : ar.take<T>((size_t)E * kHidden);
+      lb.Z2 = chunked ? shared_edge[2] : ar.take<T>((size_t)E * kHidden);
+      lb.Z3 = chunked ? shared_edge[3] : ar.take<T>((size_t)E * kHidden);
+      lb.Hact = chunked ? shared_edge[4] : ar.take<T>((size_t)E * kHidden);
+      lb.W = chunked ? shared_W : ar.take<T>((size_t)E * p.tp.NP * C);
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
@@ -572,6 +595,88 @@ struct Model : ModelBase {
 #define CKL(expr) do { CK(expr); ++launches; } while (0)
 #define PH(name) phase(name, s)
 
+  // Arguments of the per-edge MLP kernels for layers `ts` over edges [e0, e0 + Ec); row r of every [.][64] buffer is edge e0 + r.
+  EdgeArgs<T> edge_range(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec) const {
+    EdgeArgs<T> r = ea;
+    r.E = Ec; r.n_layers = (int)ts.size(); r.dlen = ea.dlen + e0; r.ddlen = ea.ddlen + e0;
+    for (size_t i = 0; i < ts.size(); ++i) {
+      r.mlp[i] = ea.mlp[ts[i]];
+      r.Z1[i] = b.lay[ts[i]].Z1;
+      r.dH1[i] = b.lay[ts[i]].Z3;  // the backward pass reuses the third pre-activation buffer for dE/dh1
+    }
+    return r;
+  }
+  // radial MLP hidden layers 8 -> 64 -> 64 -> 64 (tace/models/mlp.py:136-191): the first layer per edge, the
+  // two 64 x 64 layers as GEMMs over the edges (all layers of `ts` in one launch), SiLU in between
+  int radial_forward(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec, cudaStream_t s) {
+    if (Ec <= 0) return TACE_OK;
+    const EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
+    CKL(launch_edge_mlp_in(er, s));
+    const long long n64 = Ec * kHidden;
+    for (int t : ts) CKL(launch_silu(b.lay[t].Z1, b.lay[t].Hact, n64, s));
+    std::vector<LinSpec> sp;
+    for (int t : ts) {
+      const std::string pre = "t" + std::to_string(t) + ".";
+      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1", pre + "A1t", kHidden, b.lay[t].Z2, kHidden, 0, nullptr});
+    }
+    CKL(run_linear(sp, Ec, s));
+    for (int t : ts) CKL(launch_silu(b.lay[t].Z2, b.lay[t].Hact, n64, s));
+    sp.clear();
+    for (int t : ts) {
+      const std::string pre = "t" + std::to_string(t) + ".";
+      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A2", pre + "A2t", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
+    }
+    CKL(run_linear(sp, Ec, s));
+    for (int t : ts) CKL(launch_silu(b.lay[t].Z3, b.lay[t].H3, n64, s));
+    return TACE_OK;
+  }
+  // back through the hidden layers: lay[t].H3 holds dE/dh3 on entry; ddlen receives dE/d(edge length)
+  int radial_backward(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec, int accumulate,
+                      cudaStream_t s) {
+    if (Ec <= 0) return TACE_OK;
+    const long long n64 = Ec * kHidden;
+    for (int t : ts) CKL(launch_silu_grad_mul(b.lay[t].H3, b.lay[t].Z3, n64, s));
+    std::vector<LinSpec> sp;
+    for (int t : ts) {
+      const std::string pre = "t" + std::to_string(t) + ".";
+      sp.push_back({b.lay[t].H3, kHidden, 0, 1, kHidden, pre + "A2t", pre + "A2", kHidden, b.lay[t].Hact, kHidden, 0, nullptr});
+    }
+    CKL(run_linear(sp, Ec, s));
+    for (int t : ts) CKL(launch_silu_grad_mul(b.lay[t].Hact, b.lay[t].Z2, n64, s));
+    sp.clear();
+    for (int t : ts) {
+      const std::string pre = "t" + std::to_string(t) + ".";
+      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1t", pre + "A1", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
+    }
+    CKL(run_linear(sp, Ec, s));
+    EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
+    er.accumulate_ddlen = accumulate;
+    CKL(launch_edge_mlp_out(er, s));
+    return TACE_OK;
+  }
+  // last radial-MLP layer for edges [e0, e0 + Ec): W[e, :] = H3[e, :] @ W3 (forward) or dH3[e, :] = dW[e, :] @ W3^T
+  int radial_last(const LayerPlan& p, const LayerBufs& lb, const std::string& pre, long long Ec, bool backward, cudaStream_t s) {
+    if (Ec <= 0) return TACE_OK;
+    const int NW = p.tp.NP * C;
+    if (kTensorCore && NW % 64 == 0) {
+      if (!backward)
+        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.H3), kHidden, reinterpret_cast<const float*>(w(pre + "W3t_hi")),
+                           reinterpret_cast<const float*>(w(pre + "W3t_lo")), reinterpret_cast<float*>(lb.W), (long long)NW, (int)Ec,
+                           NW, kHidden, dev_error, s));
+      else
+        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.W), (long long)NW, reinterpret_cast<const float*>(w(pre + "W3_hi")),
+                           reinterpret_cast<const float*>(w(pre + "W3_lo")), reinterpret_cast<float*>(lb.H3), kHidden, (int)Ec,
+                           kHidden, NW, dev_error, s));
+    } else {
+      GemmBatch<T> gb = plain_batch(Ec);
+      if (!backward) add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), NW, lb.W, (long long)NW, 0, nullptr, 0);
+      else add_problem(gb, lb.W, (long long)NW, 0, 1, NW, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
+      CKL(launch_gemm(gb, Ec, s));
+    }
+    return TACE_OK;
+  }
+#define CKS(expr) do { const int st__ = (expr); if (st__ != TACE_OK) return st__; } while (0)
+
   int forward(const TaceBatch* bt, const TaceOutputs* o, void* ws, size_t ws_bytes, cudaStream_t s) override {
     if (!bt || !o || !ws) return TACE_ERR_INVALID_ARGUMENT;
     for (const auto& e : weights)
@@ -603,6 +708,24 @@ struct Model : ModelBase {
     gp.temp = b.prep_temp; gp.temp_bytes = b.prep_temp_bytes;
     CKL(launch_graph_prep(gp, s));
     launches += 8;  // launch_graph_prep runs nine kernels of its own besides the radix sorts
+    // edge chunks: one chunk (all atoms) unless the batch exceeds max_chunk_edges
+    const bool chunked = E > max_chunk_edges;
+    std::vector<int> chunk_atom{0, (int)NL}, chunk_edge{0, (int)E};
+    if (chunked) {
+      const int nc = b.n_chunks;
+      CKL(launch_chunk_bounds(b.rowptr_dst, (int)NL, max_chunk_edges, nc, b.chunk_atom_ptr, b.chunk_edge_ptr, s));
+      chunk_atom.assign(nc + 1, 0); chunk_edge.assign(nc + 1, 0);
+      CK(cudaMemcpyAsync(chunk_atom.data(), b.chunk_atom_ptr, sizeof(int) * (nc + 1), cudaMemcpyDeviceToHost, s));
+      CK(cudaMemcpyAsync(chunk_edge.data(), b.chunk_edge_ptr, sizeof(int) * (nc + 1), cudaMemcpyDeviceToHost, s));
+      CK(cudaStreamSynchronize(s));
+      for (int c = 0; c < nc; ++c)
+        if (chunk_edge[c + 1] - chunk_edge[c] > b.chunk_rows) return TACE_ERR_CAPACITY;  // an atom with more than kChunkSlack edges
+      if (need_grad && NL_ > 1) {
+        CKL(launch_chunk_src_sort(b.e_src, E, (int)N, b.chunk_edge_ptr, nc, b.keys_cs, b.perm_cs, b.prep_temp, b.prep_temp_bytes, s));
+        ++launches;
+      }
+    }
+    const int n_chunks = (int)chunk_atom.size() - 1;
     PH("edge_fwd");
 
     // ---- edge features
@@ -628,28 +751,10 @@ struct Model : ModelBase {
     ea.dlen = b.dlen; ea.ddlen = b.ddlen;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
-    // radial MLP hidden layers 8 -> 64 -> 64 -> 64 (tace/models/mlp.py:136-191): the first layer per edge, the
-    // two 64 x 64 layers as GEMMs over all edges (all interaction layers in one launch), SiLU in between
+    std::vector<int> all_layers;
+    for (int t = 0; t < NL_; ++t) all_layers.push_back(t);
     PH("radial_mlp_fwd");
-    CKL(launch_edge_mlp_in(ea, s));
-    {
-      const long long n64 = E * kHidden;
-      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z1, b.lay[t].Hact, n64, s));
-      std::vector<LinSpec> sp;
-      for (int t = 0; t < NL_; ++t) {
-        const std::string pre = "t" + std::to_string(t) + ".";
-        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1", pre + "A1t", kHidden, b.lay[t].Z2, kHidden, 0, nullptr});
-      }
-      CKL(run_linear(sp, E, s));
-      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z2, b.lay[t].Hact, n64, s));
-      sp.clear();
-      for (int t = 0; t < NL_; ++t) {
-        const std::string pre = "t" + std::to_string(t) + ".";
-        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A2", pre + "A2t", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
-      }
-      CKL(run_linear(sp, E, s));
-      for (int t = 0; t < NL_; ++t) CKL(launch_silu(b.lay[t].Z3, b.lay[t].H3, n64, s));
-    }
+    if (!chunked) CKS(radial_forward(ea, b, all_layers, 0, E, s));  // all layers at once; chunked passes do it per layer and chunk
     debug.push_back({"Y", b.Y, (long long)D * E});
     debug.push_back({"vec", b.vec, 3 * E});
 
@@ -680,22 +785,22 @@ struct Model : ModelBase {
         if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
         x_src = lb.xx;
       }
-      PH(("t" + ts + ".fwd.radial_gemm").c_str());
-      if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // last radial-MLP layer on tcgen05: W[e, :] = H3[e, :] @ W3
-        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.H3), kHidden, reinterpret_cast<const float*>(w(pre + "W3t_hi")),
-                           reinterpret_cast<const float*>(w(pre + "W3t_lo")), reinterpret_cast<float*>(lb.W),
-                           (long long)p.tp.NP * C, (int)E, p.tp.NP * C, kHidden, dev_error, s));
-      } else {
-        GemmBatch<T> gb = plain_batch(E);
-        add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), p.tp.NP * C, lb.W, (long long)p.tp.NP * C, 0, nullptr, 0);
-        CKL(launch_gemm(gb, E, s));
+      for (int c = 0; c < n_chunks; ++c) {
+        const long long e0 = chunk_edge[c], Ec = chunk_edge[c + 1] - e0;
+        const int a0 = chunk_atom[c], na = chunk_atom[c + 1] - a0;
+        if (chunked) {
+          PH("radial_mlp_fwd");
+          CKS(radial_forward(ea, b, std::vector<int>{t}, e0, Ec, s));
+        }
+        PH(("t" + ts + ".fwd.radial_gemm").c_str());
+        CKS(radial_last(p, lb, pre, Ec, false, s));
+        PH(("t" + ts + ".fwd.tp").c_str());
+        TPArgs<T> ta;
+        memset(&ta, 0, sizeof(ta));
+        ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
+        ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M + (long long)a0 * p.tp.NM * C; ta.e_base = e0;
+        CKL(launch_tp_fwd(ta, s));
       }
-      PH(("t" + ts + ".fwd.tp").c_str());
-      TPArgs<T> ta;
-      memset(&ta, 0, sizeof(ta));
-      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst;
-      ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M;
-      CKL(launch_tp_fwd(ta, s));
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
       debug.push_back({"M" + ts, lb.M, NL * p.tp.NM * C});
       PH(("t" + ts + ".fwd.node").c_str());
@@ -833,30 +938,39 @@ struct Model : ModelBase {
       }
       // edge pass: gradients of the per-edge weights (in place over W), of the angular features and,
       // per edge, of the source features
-      PH(("t" + ts + ".bwd.tp").c_str());
-      TPArgs<T> ta;
-      memset(&ta, 0, sizeof(ta));
-      ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
-      ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M; ta.n_seg = (int)NL; ta.rowptr = b.rowptr_dst; ta.dW = lb.W; ta.dY = b.dY;
-      ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
-      CKL(launch_tp_bwd(ta, s));
-      if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
-        PH(("t" + ts + ".bwd.src_sum").c_str());
-        CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, p.tp.NX * C, s));
-        if (lb.gxx) {  // gradients that landed on ghost rows go back to their owners (reverse_exchange)
-          if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
-          if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
+      if (chunked && !p.scalar_src) CKL(launch_fill_zero(lb.gx, N * p.tp.NX * C, s));  // chunks add their shares
+      for (int c = 0; c < n_chunks; ++c) {
+        const long long e0 = chunk_edge[c], Ec = chunk_edge[c + 1] - e0;
+        const int a0 = chunk_atom[c], na = chunk_atom[c + 1] - a0;
+        if (chunked) {  // the per-edge activations and weights of this chunk were not kept: recompute them
+          PH("radial_mlp_fwd");
+          CKS(radial_forward(ea, b, std::vector<int>{t}, e0, Ec, s));
+          PH(("t" + ts + ".fwd.radial_gemm").c_str());
+          CKS(radial_last(p, lb, pre, Ec, false, s));
+        }
+        PH(("t" + ts + ".bwd.tp").c_str());
+        TPArgs<T> ta;
+        memset(&ta, 0, sizeof(ta));
+        ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
+        ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M + (long long)a0 * p.tp.NM * C; ta.n_seg = na;
+        ta.rowptr = b.rowptr_dst + a0; ta.dW = lb.W; ta.dY = b.dY; ta.e_base = e0;
+        ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
+        CKL(launch_tp_bwd(ta, s));
+        if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
+          PH(("t" + ts + ".bwd.src_sum").c_str());
+          if (chunked) CKL(launch_chunk_src_sum(b.dxe, b.keys_cs, b.perm_cs, e0, e0 + Ec, (long long)c * N, lb.gx, p.tp.NX * C, s));
+          else CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, p.tp.NX * C, s));
+        }
+        PH(("t" + ts + ".bwd.radial_gemm").c_str());
+        CKS(radial_last(p, lb, pre, Ec, true, s));  // back through the last radial-MLP layer: H3 <- dE/dh3
+        if (chunked) {
+          PH("radial_mlp_bwd");
+          CKS(radial_backward(ea, b, std::vector<int>{t}, e0, Ec, t != NL_ - 1, s));
         }
       }
-      PH(("t" + ts + ".bwd.radial_gemm").c_str());
-      if (kTensorCore && (p.tp.NP * C) % 64 == 0) {  // back through the last radial-MLP layer: dH3[e, :] = dW[e, :] @ W3^T
-        CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.W), (long long)p.tp.NP * C,
-                           reinterpret_cast<const float*>(w(pre + "W3_hi")), reinterpret_cast<const float*>(w(pre + "W3_lo")),
-                           reinterpret_cast<float*>(lb.H3), kHidden, (int)E, kHidden, p.tp.NP * C, dev_error, s));
-      } else {
-        GemmBatch<T> gb = plain_batch(E);
-        add_problem(gb, lb.W, (long long)p.tp.NP * C, 0, 1, p.tp.NP * C, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
-        CKL(launch_gemm(gb, E, s));
+      if (lb.gxx) {  // gradients that landed on ghost rows go back to their owners (reverse_exchange)
+        if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+        if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
       }
       if (!p.scalar_src) {
         PH(("t" + ts + ".bwd.linear_up").c_str());
@@ -879,24 +993,7 @@ struct Model : ModelBase {
 
     // ---- back to the edge vectors, then forces and virials
     PH("radial_mlp_bwd");
-    {  // lay[t].H3 now holds dE/dh3 of each layer's radial MLP
-      const long long n64 = E * kHidden;
-      for (int t = 0; t < NL_; ++t) CKL(launch_silu_grad_mul(b.lay[t].H3, b.lay[t].Z3, n64, s));
-      std::vector<LinSpec> sp;
-      for (int t = 0; t < NL_; ++t) {
-        const std::string pre = "t" + std::to_string(t) + ".";
-        sp.push_back({b.lay[t].H3, kHidden, 0, 1, kHidden, pre + "A2t", pre + "A2", kHidden, b.lay[t].Hact, kHidden, 0, nullptr});
-      }
-      CKL(run_linear(sp, E, s));
-      for (int t = 0; t < NL_; ++t) CKL(launch_silu_grad_mul(b.lay[t].Hact, b.lay[t].Z2, n64, s));
-      sp.clear();
-      for (int t = 0; t < NL_; ++t) {
-        const std::string pre = "t" + std::to_string(t) + ".";
-        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1t", pre + "A1", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
-      }
-      CKL(run_linear(sp, E, s));
-      CKL(launch_edge_mlp_out(ea, s));
-    }
+    if (!chunked) CKS(radial_backward(ea, b, all_layers, 0, E, 0, s));  // lay[t].H3 holds dE/dh3 of each layer's radial MLP
     PH("edge_bwd");
     CKL(launch_edge_bwd(ea, s));
     debug.push_back({"g", b.g, 3 * E});
@@ -1008,6 +1105,12 @@ int tace_set_graph_mode(TaceModel* model, int enable) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   model->impl->graph_mode = enable != 0;
   if (!enable) model->impl->release_graphs();
+  return TACE_OK;
+}
+int tace_set_chunk_edges(TaceModel* model, int64_t max_edges) {
+  if (!model || max_edges < 1024) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->max_chunk_edges = max_edges;
+  model->impl->release_graphs();
   return TACE_OK;
 }
 int64_t tace_graph_replays(const TaceModel* model) { return model ? model->impl->graph_replays : TACE_ERR_INVALID_ARGUMENT; }

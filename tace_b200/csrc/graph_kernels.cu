@@ -64,6 +64,30 @@ __global__ void tile_ptr_kernel(const int* __restrict__ species_ptr, int n_el, i
   tp[n_el] = acc;
 }
 
+__global__ void chunk_bounds_kernel(const int* __restrict__ rowptr, int n_local, long long target, int n_chunks, int* atom_ptr,
+                                    int* edge_ptr) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c > n_chunks) return;
+  int a = n_local;
+  if (c < n_chunks) {  // first atom whose edge offset is >= c * target
+    const long long want = c * target;
+    int lo = 0, hi = n_local;
+    while (lo < hi) { const int mid = (lo + hi) >> 1; if (rowptr[mid] < want) lo = mid + 1; else hi = mid; }
+    a = lo;
+  }
+  atom_ptr[c] = a;
+  edge_ptr[c] = rowptr[a];
+}
+__global__ void chunk_key_kernel(const int* __restrict__ e_src, long long E, int n_atoms, const int* __restrict__ edge_ptr,
+                                 int n_chunks, int* keys, int* vals) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int lo = 0, hi = n_chunks;  // largest c with edge_ptr[c] <= e
+  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (edge_ptr[mid] <= e) lo = mid; else hi = mid; }
+  keys[e] = lo * n_atoms + e_src[e];
+  vals[e] = (int)e;
+}
+
 inline size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
 
 size_t cub_sort_bytes(long long n) {
@@ -119,6 +143,28 @@ cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
   lower_bound_kernel<<<(a.n_elements + 256) / 256, 256, 0, s>>>(keys_out, a.n_local, a.species_ptr, a.n_elements);
   tile_ptr_kernel<<<1, 32, 0, s>>>(a.species_ptr, a.n_elements, a.tile_ptr, a.tc_tile_ptr);
   return cudaGetLastError();
+}
+
+cudaError_t launch_chunk_bounds(const int* rowptr_dst, int n_local, long long target_edges, int n_chunks, int* atom_ptr,
+                                int* edge_ptr, cudaStream_t s) {
+  chunk_bounds_kernel<<<(n_chunks + 128) / 128, 128, 0, s>>>(rowptr_dst, n_local, target_edges, n_chunks, atom_ptr, edge_ptr);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_chunk_src_sort(const int* e_src, long long E, int n_atoms, const int* edge_ptr, int n_chunks, int* keys,
+                                  int* perm, void* temp, size_t temp_bytes, cudaStream_t s) {
+  if (E <= 0) return cudaSuccess;
+  if ((long long)n_chunks * n_atoms >= (1LL << 31)) return cudaErrorInvalidValue;
+  unsigned char* p = static_cast<unsigned char*>(temp);
+  int* keys_in = reinterpret_cast<int*>(p); p += align_up(sizeof(int) * (size_t)E);
+  int* vals_in = reinterpret_cast<int*>(p); p += align_up(sizeof(int) * (size_t)E);
+  p += align_up(sizeof(int) * (size_t)E);
+  size_t cub_bytes = cub_sort_bytes(E);
+  if ((size_t)(p - static_cast<unsigned char*>(temp)) + cub_bytes > temp_bytes) return cudaErrorInvalidValue;
+  int bits = 1;
+  while ((1LL << bits) < (long long)n_chunks * n_atoms + 1 && bits < 31) ++bits;
+  chunk_key_kernel<<<(unsigned)((E + 255) / 256), 256, 0, s>>>(e_src, E, n_atoms, edge_ptr, n_chunks, keys_in, vals_in);
+  return cub::DeviceRadixSort::SortPairs(p, cub_bytes, keys_in, keys, vals_in, perm, (int)E, 0, bits, s);
 }
 
 }  // namespace tace

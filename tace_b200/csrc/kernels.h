@@ -27,12 +27,18 @@ struct TPArgs {
   T* dY;              // backward output [E][D]
   int accumulate_dY;  // add into dY instead of overwriting
   T* dxe;             // backward output [E][NX][C]: per-edge gradient of the source features (full source only)
+  long long e_base;   // W, dW and dxe hold the rows of edges [e_base, ...) only (edge-chunked passes); Y, dY, e_src are whole
 };
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_tp_bwd(const TPArgs<T>& a, cudaStream_t s);
 // gx[b] = sum of dxe over the edges whose source is b (edges listed by perm within rowptr_src segments)
 template <typename T> cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx,
                                                           int n_atoms, int row_len, cudaStream_t s);
+// Edge-chunked variant: positions [k0, k1) of the (chunk, source)-sorted edge list belong to one chunk whose dxe rows start
+// at edge k0; every run of equal keys is summed in list order and ADDED to gx[key - key_base] (runs of one chunk have
+// distinct sources, chunks are processed one after another, so the sum order is fixed).
+template <typename T> cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const int* keys, const int* perm, long long k0,
+                                                       long long k1, long long key_base, T* gx, int row_len, cudaStream_t s);
 
 // ---- per-atom element-wise kernels (node_kernels.cu) -----------------------------------------
 // x0[n][c] = table[species[n]][c]
@@ -96,6 +102,7 @@ struct EdgeArgs {
   T* Y;                  // [E][D]
   T* Z1[kMaxLayers];     // [E][64] pre-activation of the first hidden layer of each layer's radial MLP
   const T* dH1[kMaxLayers];  // [E][64] gradient of the first hidden activation (backward)
+  int accumulate_ddlen;  // launch_edge_mlp_out adds into ddlen instead of overwriting (layer-by-layer passes)
   // backward
   const T* dY;           // [E][D]
   T* g;                  // [E][3] dE/d(edge vector), target-sorted order
@@ -141,6 +148,13 @@ struct GraphPrepArgs {
 };
 size_t graph_prep_temp_bytes(long long E, int n_atoms);
 cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s);
+// Edge chunks for systems whose per-edge tensors do not fit: chunk c = target atoms [atom_ptr[c], atom_ptr[c+1]) with
+// atom_ptr[c] = first atom whose edge offset reaches c * target_edges; edge_ptr[c] = rowptr_dst[atom_ptr[c]].
+cudaError_t launch_chunk_bounds(const int* rowptr_dst, int n_local, long long target_edges, int n_chunks, int* atom_ptr,
+                                int* edge_ptr, cudaStream_t s);
+// keys[k], perm[k]: edges sorted by (chunk, source atom); key = chunk * n_atoms + source.  temp as for launch_graph_prep.
+cudaError_t launch_chunk_src_sort(const int* e_src, long long E, int n_atoms, const int* edge_ptr, int n_chunks, int* keys,
+                                  int* perm, void* temp, size_t temp_bytes, cudaStream_t s);
 
 }  // namespace tace
 

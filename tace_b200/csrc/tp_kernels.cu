@@ -57,7 +57,7 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
       T xv[TP::NX], wv[NPG];
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) xv[k] = a.x[(s * TP::NX + k) * C + c];
-      const T* We = a.W + ((long long)(e0 + e) * TP::NP + P0) * C;
+      const T* We = a.W + ((long long)(e0 + e - a.e_base) * TP::NP + P0) * C;
 #pragma unroll
       for (int p = 0; p < NPG; ++p) wv[p] = We[p * C + c];
       if constexpr (GRP == 0) TP::template fwd0<T>(xv, Gs + e * TP::NG, wv, acc);
@@ -93,7 +93,7 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
       T xv[TP::NX], wv[TP::NP], dw[TP::NP], dYp[TP::D], dx[TP::NX];
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) { xv[k] = a.x[(s * TP::NX + k) * C + c]; dx[k] = T(0); }
-      const long long wbase = (long long)(e0 + e) * TP::NP * C;
+      const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C;
 #pragma unroll
       for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
 #pragma unroll
@@ -102,7 +102,7 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
 #pragma unroll
       for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
       if (a.dxe) {
-        T* out = a.dxe + (long long)(e0 + e) * TP::NX * C;
+        T* out = a.dxe + (long long)(e0 + e - a.e_base) * TP::NX * C;
 #pragma unroll
         for (int k = 0; k < TP::NX; ++k) out[k * C + c] = dx[k];
       }
@@ -141,6 +141,29 @@ cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const i
                                     cudaStream_t s) {
   if (n_atoms <= 0) return cudaSuccess;
   segment_sum_rows_kernel<T><<<n_atoms, 256, 0, s>>>(dxe, rowptr_src, perm_src, gx, row_len);
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void chunk_src_sum_kernel(const T* __restrict__ dxe, const int* __restrict__ keys, const int* __restrict__ perm,
+                                     long long k0, long long k1, long long key_base, T* __restrict__ gx, int row_len) {
+  const long long k = k0 + blockIdx.x;
+  const int key = keys[k];
+  if (k > k0 && keys[k - 1] == key) return;  // not the head of a run
+  long long end = k + 1;
+  while (end < k1 && keys[end] == key) ++end;
+  T* dst = gx + ((long long)key - key_base) * row_len;
+  for (int c = threadIdx.x; c < row_len; c += blockDim.x) {
+    T acc = T(0);
+    for (long long j = k; j < end; ++j) acc += dxe[((long long)perm[j] - k0) * row_len + c];
+    dst[c] += acc;
+  }
+}
+template <typename T>
+cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const int* keys, const int* perm, long long k0, long long k1,
+                                 long long key_base, T* gx, int row_len, cudaStream_t s) {
+  if (k1 <= k0) return cudaSuccess;
+  chunk_src_sum_kernel<T><<<(unsigned)(k1 - k0), 128, 0, s>>>(dxe_chunk, keys, perm, k0, k1, key_base, gx, row_len);
   return cudaGetLastError();
 }
 
@@ -183,5 +206,7 @@ template cudaError_t launch_tp_bwd<float>(const TPArgs<float>&, cudaStream_t);
 template cudaError_t launch_tp_bwd<double>(const TPArgs<double>&, cudaStream_t);
 template cudaError_t launch_segment_sum_rows<float>(const float*, const int*, const int*, float*, int, int, cudaStream_t);
 template cudaError_t launch_segment_sum_rows<double>(const double*, const int*, const int*, double*, int, int, cudaStream_t);
+template cudaError_t launch_chunk_src_sum<float>(const float*, const int*, const int*, long long, long long, long long, float*, int, cudaStream_t);
+template cudaError_t launch_chunk_src_sum<double>(const double*, const int*, const int*, long long, long long, long long, double*, int, cudaStream_t);
 
 }  // namespace tace

@@ -21,6 +21,7 @@ EXPORTS = [
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
     "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
     "tace_edge_vectors", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays",
+    "tace_set_chunk_edges",
 ]
 
 
@@ -97,6 +98,7 @@ def load() -> ctypes.CDLL:
     lib.tace_nl_fill.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_int64,
                                  c_void_p, c_void_p, c_void_p]
     lib.tace_set_graph_mode.argtypes = [c_void_p, c_int]
+    lib.tace_set_chunk_edges.argtypes = [c_void_p, c_int64]
     lib.tace_graph_replays.argtypes = [c_void_p]
     lib.tace_graph_replays.restype = c_int64
     lib.tace_md_kick_drift.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_double, c_double, c_void_p]

@@ -238,6 +238,7 @@ class TensorModel(torch.nn.Module):
         self._handle_key = None
         self._workspace = None
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
+        self._chunk_edges = None
         self._set_target_property()
 
     # ---- reference getters (tace/models/adapter.py:386-452) ----------------------------------
@@ -308,6 +309,8 @@ class TensorModel(torch.nn.Module):
                     raise _lib.TaceError(f"weight {name.value.decode()}: packed {arr.size} elements, library expects {numel.value}")
                 _lib.check(lib.tace_set_weight(handle, name.value, arr.ctypes.data_as(ctypes.c_void_p), arr.size), "tace_set_weight")
             _lib.check(lib.tace_set_graph_mode(handle, int(self._graph_mode)), "tace_set_graph_mode")
+            if self._chunk_edges is not None:
+                _lib.check(lib.tace_set_chunk_edges(handle, int(self._chunk_edges)), "tace_set_chunk_edges")
         self._handle, self._handle_key = handle, key
         return handle
 
@@ -317,6 +320,13 @@ class TensorModel(torch.nn.Module):
         self._graph_mode = bool(enable)
         if self._handle is not None:
             _lib.check(_lib.load().tace_set_graph_mode(self._handle, int(self._graph_mode)), "tace_set_graph_mode")
+
+    def set_chunk_edges(self, max_edges: Optional[int]) -> None:
+        """Batches with more edges than this are evaluated chunk by chunk of target atoms with the per-edge tensors
+        recomputed in the backward pass (library default 2**21 edges)."""
+        self._chunk_edges = None if max_edges is None else int(max_edges)
+        if self._handle is not None and max_edges is not None:
+            _lib.check(_lib.load().tace_set_chunk_edges(self._handle, int(max_edges)), "tace_set_chunk_edges")
 
     def graph_replays(self) -> int:
         return int(_lib.load().tace_graph_replays(self._handle)) if self._handle is not None else 0
