@@ -239,6 +239,7 @@ class TensorModel(torch.nn.Module):
         self._workspace = None
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
         self._chunk_edges = None
+        self._auto_chunk = None
         self._set_target_property()
 
     # ---- reference getters (tace/models/adapter.py:386-452) ----------------------------------
@@ -289,6 +290,7 @@ class TensorModel(torch.nn.Module):
         if self._handle is not None and key == self._handle_key:
             return self._handle
         self.release()
+        self._auto_chunk = None
         lib = _lib.load()
         plan = rf.plan
         cfg = _lib.TaceConfig(
@@ -351,7 +353,7 @@ class TensorModel(torch.nn.Module):
         ws = self._workspace
         if ws is None or ws.numel() < nbytes or ws.device != device:
             self._workspace = None
-            ws = torch.empty(int(nbytes * 1.1) + 4096, dtype=torch.uint8, device=device)
+            ws = torch.empty(int(nbytes * (1.1 if nbytes < (8 << 30) else 1.02)) + 4096, dtype=torch.uint8, device=device)
             self._workspace = ws
         return ws
 
@@ -417,7 +419,23 @@ class TensorModel(torch.nn.Module):
             _lib.check(lib.tace_set_exchange(handle, exchange_cb, None), "tace_set_exchange")
         with torch.cuda.device(device):
             nbytes = ctypes.c_size_t()
-            _lib.check(lib.tace_workspace_bytes(handle, n_atoms, n_local, E, n_graphs, ctypes.byref(nbytes)), "tace_workspace_bytes")
+
+            def needed() -> int:
+                _lib.check(lib.tace_workspace_bytes(handle, n_atoms, n_local, E, n_graphs, ctypes.byref(nbytes)), "tace_workspace_bytes")
+                return int(nbytes.value)
+
+            if self._chunk_edges is None:
+                # automatic edge chunking: keep every per-edge tensor resident when the workspace fits in
+                # 80 % of the memory this model may use, otherwise halve the chunk size until it does
+                free, _total = torch.cuda.mem_get_info(device)
+                budget = 0.8 * (free + (self._workspace.numel() if self._workspace is not None else 0))
+                for limit in (max(E, 1 << 21), 1 << 22, 1 << 21, 1 << 20, 1 << 19, 1 << 18):
+                    if limit != self._auto_chunk:
+                        _lib.check(lib.tace_set_chunk_edges(handle, int(limit)), "tace_set_chunk_edges")
+                        self._auto_chunk = limit
+                    if needed() <= budget or limit == 1 << 18:
+                        break
+            needed()
             ws = self._get_workspace(nbytes.value, device)
             ws_ptr = (ws.data_ptr() + 255) & ~255
             stream = torch.cuda.current_stream(device).cuda_stream

@@ -167,7 +167,10 @@ WORKLOADS = {
                             dtype="float32"),
     "water32400_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32"),
     "cual1m_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
+    # one eighth of the system above (the share of one GPU in an 8-GPU run), for development runs
+    "cual131k_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
 }
+MD_WORKLOADS = {"cual1m_fp32": 64, "cual131k_fp32": 32}  # FCC cells per side
 
 
 def workload_structures(name: str) -> List[Structure]:
@@ -179,6 +182,6 @@ def workload_structures(name: str) -> List[Structure]:
         return random_crystals(16, seed=1)
     if name == "water32400_fp32":
         return [water_box()]
-    if name == "cual1m_fp32":
-        return [fcc_supercell(64, 3.65, 0.05, seed=4, species=(13, 29), fractions=(0.1, 0.9))]
+    if name in MD_WORKLOADS:
+        return [fcc_supercell(MD_WORKLOADS[name], 3.65, 0.05, seed=4, species=(13, 29), fractions=(0.1, 0.9))]
     raise KeyError(name)
