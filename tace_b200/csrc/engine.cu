@@ -568,6 +568,7 @@ struct Model : ModelBase {
         h.n_groups = n_el; h.group_ptr = b.species_ptr; h.tile_ptr = b.tc_tile_ptr + (sp.q / 2) * (n_el + 1);
         h.atom_map = sp.mapped ? b.species_perm : nullptr;
         h.b_group_stride = (long long)sp.K * sp.N; h.bias_group_stride = sp.N; h.accumulate = sp.accumulate;
+        h.b_tiled = 1;  // the packed per-species hi / lo parts are K-tile-major (read once per pass, straight from DRAM)
       }
       return launch_tc_linear(probs, (int)specs.size(), dev_error, s);
     }

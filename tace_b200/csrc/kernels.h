@@ -179,6 +179,7 @@ struct TcLinearProblem {
   const int* group_ptr; const int* tile_ptr; const int* atom_map;
   long long b_group_stride, bias_group_stride;
   int accumulate;        // C += instead of C =
+  int b_tiled;           // Bhi / Blo are stored K-tile-major, [groups][K/32][N][32] (b_group_stride must be N*K)
 };
 bool tc_linear_supported(int N, int K);
 cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s);

@@ -115,6 +115,9 @@ struct TcProblem {
   const int* tile_ptr;
   const int* atom_map;   // row of C for sorted atom a is atom_map[a]; nullptr: identity
   int accumulate;        // C += instead of C =
+  int b_tiled;           // B maps are 4-D {32, N, K/32, groups} over K-tile-major weights
+  int c_tma;             // plain row-major result (q = 1, no map, no accumulate): written by TMA stores through tmC
+  CUtensorMap tmC;       // 2-D {N, rows}, box 32 x 32, 128-byte swizzle
 };
 constexpr int kTcMaxProblems = 4;
 struct TcBatch {
@@ -135,7 +138,9 @@ struct TcSmem {
   static constexpr int kTileBBytes = BN * kBK * 4;
   static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  // result staging for TMA stores: per epilogue warp two slabs of 32 rows x 32 columns (128-byte swizzled rows)
+  static constexpr int kStoreBytes = 4 * 2 * 32 * 128;
+  static constexpr int kTotal = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -146,6 +151,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y) : "memory");
 }
 
 struct TileInfo {
@@ -192,14 +209,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte-swizzled tiles need 1024-byte alignment
   unsigned char* base_ptr = smem_raw + (base - raw);
-  const uint32_t bars = base + kStages * S::kStageBytes;
+  const uint32_t store_base = base + kStages * S::kStageBytes;  // 1024-byte aligned: stage sizes are multiples of 1024
+  const uint32_t bars = store_base + S::kStoreBytes;
   // barriers: raw[s] TMA landed | ready[s] operands split | empty[s] MMAs done reading | acc_full[a] | acc_empty[a]
   auto raw_bar = [&](int s) { return bars + 8u * s; };
   auto ready_bar = [&](int s) { return bars + 8u * (kStages + s); };
   auto empty_bar = [&](int s) { return bars + 8u * (2 * kStages + s); };
   auto acc_full = [&](int a) { return bars + 8u * (3 * kStages + a); };
   auto acc_empty = [&](int a) { return bars + 8u * (3 * kStages + 2 + a); };
-  unsigned char* misc = base_ptr + kStages * S::kStageBytes + 8 * (3 * kStages + 4);
+  unsigned char* misc = base_ptr + kStages * S::kStageBytes + S::kStoreBytes + 8 * (3 * kStages + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
   int* tile_start = reinterpret_cast<int*>(misc + 16);  // [n_problems + 1]
@@ -250,8 +268,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, batch.error, 1)) { ok = false; break; }
           mbar_expect_tx(raw_bar(s), a_bytes + 2 * S::kTileBBytes);
           tma_load_3d(stage_a(s), &P.tmA, raw_bar(s), ks * kBK, 0, t.atom0);
-          tma_load_3d(stage_bhi(s), &P.tmBhi, raw_bar(s), ks * kBK, t.n0, t.group);
-          tma_load_3d(stage_blo(s), &P.tmBlo, raw_bar(s), ks * kBK, t.n0, t.group);
+          if (P.b_tiled) {  // weights stored K-tile-major: one contiguous block per (k-step, n-tile)
+            tma_load_4d(stage_bhi(s), &P.tmBhi, raw_bar(s), 0, t.n0, ks, t.group);
+            tma_load_4d(stage_blo(s), &P.tmBlo, raw_bar(s), 0, t.n0, ks, t.group);
+          } else {
+            tma_load_3d(stage_bhi(s), &P.tmBhi, raw_bar(s), ks * kBK, t.n0, t.group);
+            tma_load_3d(stage_blo(s), &P.tmBlo, raw_bar(s), ks * kBK, t.n0, t.group);
+          }
         }
       }
       if (*abort_flag) {  // loads already issued must land before the CTA exits
@@ -323,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
     // ---- epilogue: drain each chunk's partial sum from TMEM, add in FP32 registers, store at tile end
     const int ew = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     float accr[ONE_CHUNK ? 1 : BN];
-    int chunk = 0;
+    int chunk = 0, slab = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
@@ -347,21 +370,55 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           tmem_ld32(tmem_base + ((uint32_t)(ew * 32) << 16) + a * BN + c * 32, rr);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if constexpr (ONE_CHUNK) {
-            if (valid) {
+            if (P.c_tma) {
+              // stage the warp's 32 x 32 slab in shared memory (16-byte chunk j of row r at chunk j ^ (r & 7), the
+              // 128-byte swizzle of the tensor map) and let the TMA unit write whole 128-byte rows; rows past the
+              // end of the tensor are clipped by the hardware
+              const uint32_t buf = store_base + (uint32_t)((ew * 2 + (slab & 1)) * 32 * 128);
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // slab - 2 has left this buffer
+              __syncwarp();
 #pragma unroll
               for (int q4 = 0; q4 < 8; ++q4) {
-                float4 v = make_float4(__uint_as_float(rr[4 * q4]), __uint_as_float(rr[4 * q4 + 1]),
-                                       __uint_as_float(rr[4 * q4 + 2]), __uint_as_float(rr[4 * q4 + 3]));
+                float4 v = make_float4(__uint_as_float(rr[4 * q4]), __uint_as_float(rr[4 * q4 + 1]), __uint_as_float(rr[4 * q4 + 2]),
+                                       __uint_as_float(rr[4 * q4 + 3]));
                 if (bias) {
                   const float4 bv = *reinterpret_cast<const float4*>(bias + c * 32 + 4 * q4);
                   v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
                 }
-                if (accumulate) {
-                  const float4 ov = *reinterpret_cast<const float4*>(dst + c * 32 + 4 * q4);
-                  v.x += ov.x; v.y += ov.y; v.z += ov.z; v.w += ov.w;
-                }
-                *reinterpret_cast<float4*>(dst + c * 32 + 4 * q4) = v;
+                const uint32_t addr = buf + (uint32_t)(lane * 128 + ((q4 ^ (lane & 7)) << 4));
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
               }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> TMA reads
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&P.tmC, buf, t.n0 + c * 32, t.atom0 + ew * 32);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+              ++slab;
+            } else if (valid) {
+              // all loads of a slab before its first store: a load that follows a store to the same 128-byte line
+              // waits for that store to be acknowledged by L2, which would serialise the row
+              float4 v[8];
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                v[q4] = make_float4(__uint_as_float(rr[4 * q4]), __uint_as_float(rr[4 * q4 + 1]), __uint_as_float(rr[4 * q4 + 2]),
+                                    __uint_as_float(rr[4 * q4 + 3]));
+              if (bias) {
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                  const float4 bv = *reinterpret_cast<const float4*>(bias + c * 32 + 4 * q4);
+                  v[q4].x += bv.x; v[q4].y += bv.y; v[q4].z += bv.z; v[q4].w += bv.w;
+                }
+              }
+              if (accumulate) {
+                float4 ov[8];
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) ov[q4] = *reinterpret_cast<const float4*>(dst + c * 32 + 4 * q4);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) { v[q4].x += ov[q4].x; v[q4].y += ov[q4].y; v[q4].z += ov[q4].z; v[q4].w += ov[q4].w; }
+              }
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) *reinterpret_cast<float4*>(dst + c * 32 + 4 * q4) = v[q4];
             }
           } else {
 #pragma unroll
@@ -372,24 +429,29 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
         mbar_arrive(acc_empty(a));  // the issuer may overwrite this accumulator
         if constexpr (!ONE_CHUNK) {
           if (cin == n_chunks - 1 && valid) {
+            if (accumulate) {  // every load of the row before its first store (see above)
 #pragma unroll
-            for (int q4 = 0; q4 < BN / 4; ++q4) {
-              float4 v = make_float4(accr[4 * q4], accr[4 * q4 + 1], accr[4 * q4 + 2], accr[4 * q4 + 3]);
-              if (bias) {
-                const float4 bv = *reinterpret_cast<const float4*>(bias + 4 * q4);
-                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-              }
-              if (accumulate) {
+              for (int q4 = 0; q4 < BN / 4; ++q4) {
                 const float4 ov = *reinterpret_cast<const float4*>(dst + 4 * q4);
-                v.x += ov.x; v.y += ov.y; v.z += ov.z; v.w += ov.w;
+                accr[4 * q4] += ov.x; accr[4 * q4 + 1] += ov.y; accr[4 * q4 + 2] += ov.z; accr[4 * q4 + 3] += ov.w;
               }
-              *reinterpret_cast<float4*>(dst + 4 * q4) = v;
             }
+            if (bias) {
+#pragma unroll
+              for (int q4 = 0; q4 < BN / 4; ++q4) {
+                const float4 bv = *reinterpret_cast<const float4*>(bias + 4 * q4);
+                accr[4 * q4] += bv.x; accr[4 * q4 + 1] += bv.y; accr[4 * q4 + 2] += bv.z; accr[4 * q4 + 3] += bv.w;
+              }
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < BN / 4; ++q4)
+              *reinterpret_cast<float4*>(dst + 4 * q4) = make_float4(accr[4 * q4], accr[4 * q4 + 1], accr[4 * q4 + 2], accr[4 * q4 + 3]);
           }
         }
       }
     }
   }
+  if (warp >= 4 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // TMA stores of this warp are complete
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
@@ -423,6 +485,19 @@ bool make_map_b(CUtensorMap* map, const float* ptr, int groups, long long N, lon
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// The same weights stored K-tile-major, [groups][K/32][N][32]: the 128-byte rows of one (k-step, n-tile) operand block are
+// adjacent in memory, so a block that is read once from DRAM (per-species weights) streams as whole pages.
+bool make_map_b_tiled(CUtensorMap* map, const float* ptr, int groups, long long N, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)kBK, (cuuint64_t)N, (cuuint64_t)(K / kBK), (cuuint64_t)groups};
+  const cuuint64_t strides[3] = {(cuuint64_t)kBK * sizeof(float), (cuuint64_t)N * kBK * sizeof(float), (cuuint64_t)N * K * sizeof(float)};
+  const cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 // 3-D fp32 tensor [atoms][q][K]; box = [R atoms][q][32], 128-byte swizzle.
 bool make_map_3d(CUtensorMap* map, const float* ptr, long long atoms, int q, long long K, long long atom_stride,
                  long long comp_stride, int R) {
@@ -436,6 +511,18 @@ bool make_map_3d(CUtensorMap* map, const float* ptr, long long atoms, int q, lon
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 2-D fp32 result [rows][N] with row stride ldc; box = 32 rows x 32 columns, 128-byte swizzle.
+bool make_map_c(CUtensorMap* map, float* ptr, long long rows, long long N, long long ldc) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldc * sizeof(float)};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, bool ONE_CHUNK>
@@ -490,10 +577,19 @@ cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* 
     P.accumulate = h.accumulate;
     const int groups = h.n_groups > 0 ? h.n_groups : 1;
     if (h.n_groups > 0 && (!h.group_ptr || !h.tile_ptr)) return cudaErrorInvalidValue;
-    if (!make_map_3d(&P.tmA, h.A, h.n_atoms, h.q, h.K, h.a_atom_stride, h.a_comp_stride, P.R) ||
-        !make_map_b(&P.tmBhi, h.Bhi, groups, h.N, h.K, h.b_group_stride, bn) ||
-        !make_map_b(&P.tmBlo, h.Blo, groups, h.N, h.K, h.b_group_stride, bn))
+    P.b_tiled = h.b_tiled;
+    if (h.b_tiled && groups > 1 && h.b_group_stride != (long long)h.N * h.K) return cudaErrorInvalidValue;
+    if (!make_map_3d(&P.tmA, h.A, h.n_atoms, h.q, h.K, h.a_atom_stride, h.a_comp_stride, P.R)) return cudaErrorInvalidValue;
+    if (h.b_tiled ? (!make_map_b_tiled(&P.tmBhi, h.Bhi, groups, h.N, h.K, bn) || !make_map_b_tiled(&P.tmBlo, h.Blo, groups, h.N, h.K, bn))
+                  : (!make_map_b(&P.tmBhi, h.Bhi, groups, h.N, h.K, h.b_group_stride, bn) ||
+                     !make_map_b(&P.tmBlo, h.Blo, groups, h.N, h.K, h.b_group_stride, bn)))
       return cudaErrorInvalidValue;
+    // large plain results (the per-edge weights of the radial MLP) leave through TMA stores
+    P.c_tma = 0;
+    if (one && h.q == 1 && h.n_groups == 0 && !h.atom_map && !h.accumulate && (reinterpret_cast<uintptr_t>(h.C) & 15) == 0) {
+      if (!make_map_c(&P.tmC, h.C, h.n_atoms, h.N, h.c_s1)) return cudaErrorInvalidValue;
+      P.c_tma = 1;
+    }
     b.tile_start[b.n_problems] = tiles;
     tiles += (int)((h.n_atoms + P.R - 1) / P.R + h.n_groups) * (h.N / bn);
     ++b.n_problems;

@@ -89,6 +89,15 @@ def split_tf32(w: np.ndarray):
     return hi, w32 - hi
 
 
+def tile_k_major(w: np.ndarray, tile: int = 32) -> np.ndarray:
+    """[..., N, K] -> [..., K/tile, N, tile] (same number of elements)."""
+    n, k = w.shape[-2], w.shape[-1]
+    if k % tile:
+        raise ValueError("contraction length must be a multiple of the K tile")
+    lead = w.shape[:-2]
+    return np.ascontiguousarray(np.swapaxes(w.reshape(lead + (n, k // tile, tile)), -3, -2))
+
+
 def _np(t) -> np.ndarray:
     return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
 
@@ -160,7 +169,12 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "res", "resT")
                 and name.split(".")[-1].startswith("l")) \
                 or stem in ("A1", "A1t", "A2", "A2t"):
-            out[name + "_hi"], out[name + "_lo"] = split_tf32(out[name])
+            hi, lo = split_tf32(out[name])
+            if stem in ("c0", "c0T", "c1", "c1T", "res", "resT"):
+                # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,
+                # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
+                hi, lo = tile_k_major(hi), tile_k_major(lo)
+            out[name + "_hi"], out[name + "_lo"] = hi, lo
     out["ro.W1"] = g("energy_readouts.0.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
     out["ro.W2"] = g("energy_readouts.0.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
     out["scale"] = g("scale_shift.scale")[0]
