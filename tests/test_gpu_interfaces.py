@@ -121,3 +121,40 @@ def test_lammps_requires_kokkos_exchange():
         nlocal, ntotal, npairs, elems = data.nlocal, data.ntotal, data.npairs, data.elems
     with pytest.raises(RuntimeError, match="KOKKOS"):
         calc.compute_forces(NoExchange())
+
+
+class FakeSimState:
+    """The attributes of a torch_sim SimState that the model interface reads."""
+
+    def __init__(self, structures, device):
+        b = synth.collate(structures)
+        self.positions = torch.as_tensor(b["positions"], device=device)
+        self.row_vector_cell = torch.as_tensor(b["lattice"], device=device)
+        self.pbc = torch.tensor([True, True, True], device=device)
+        self.atomic_numbers = torch.as_tensor(b["atomic_numbers"], device=device)
+        self.system_idx = torch.as_tensor(b["batch"], device=device)
+
+
+def test_torchsim_model_matches_oracle_and_reuses_cached_setup():
+    from tace_b200.interface import TACETorchSimCalc
+
+    structs = synth.random_crystals(3, seed=12, nmin=4, nmax=10, zmax=3)
+    model, oracle, cfg = make_models(2, 32, [1, 2, 3], 4.5, 20.0, torch.float64)
+    ref = oracle(oracle_batch(structs, [1, 2, 3], 4.5, torch.float64))
+    dev = torch.device("cuda:0")
+    calc = TACETorchSimCalc(model, device=dev, dtype=torch.float64)
+    state = FakeSimState(structs, dev)
+    for _ in range(2):  # the second call reuses the cached species / pointers
+        out = calc(state)
+        n_per = torch.tensor([len(s["positions"]) for s in structs], dtype=torch.float64)
+        assert ((out["energy"].cpu() - ref["energy"]).abs() / n_per).max() < 1e-8
+        assert (out["forces"].cpu() - ref["forces"]).abs().max() < 1e-7
+        assert (out["stress"].cpu() - ref["stress"]).abs().max() < 1e-7
+    assert calc.compute_forces and calc.compute_stress and calc.device == dev and calc.dtype == torch.float64
+    with pytest.raises(NotImplementedError):
+        TACETorchSimCalc(model, device=dev, enable_cue=True)
+    # an element outside the model's table is refused
+    state.atomic_numbers = state.atomic_numbers.clone()
+    state.atomic_numbers[0] = 7
+    with pytest.raises(ValueError):
+        calc(state)
