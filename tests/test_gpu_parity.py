@@ -212,3 +212,40 @@ def test_edge_chunked_pass_matches_the_whole_pass(dtype, num_layers):
             assert (out[k] - v).abs().max().item() <= tol * scale, k
     assert model.graph_replays() == 0
     assert model.device_error() == 0
+
+
+def test_forces_and_stress_match_finite_differences_of_the_energy():
+    """Central differences of the CUDA energy itself (fp64): F = -dE/dr, stress = (1/V) dE/d(strain) with the
+    symmetric strain applied to positions and cell (tace/models/utils.py:50-79, adapter.py:106-116)."""
+    s = synth.random_crystals(1, seed=21, nmin=6, nmax=6, zmax=3)[0]
+    model, _, _ = make_models(2, 32, [1, 2, 3], 4.5, 20.0, torch.float64)
+    dev = torch.device("cuda:0")
+
+    def energy_of(struct):
+        return model(to_device(oracle_batch([struct], [1, 2, 3], 4.5, torch.float64), dev))["energy"].item()
+
+    base = model(to_device(oracle_batch([s], [1, 2, 3], 4.5, torch.float64), dev))
+    forces, stress = base["forces"].cpu().numpy(), base["stress"].cpu().numpy()[0]
+    h = 1e-5
+    for i, k in [(0, 0), (3, 1), (5, 2)]:
+        e = []
+        for sign in (+1, -1):
+            p = dict(s)
+            p["positions"] = s["positions"].copy()
+            p["positions"][i, k] += sign * h
+            e.append(energy_of(p))
+        assert abs(-(e[0] - e[1]) / (2 * h) - forces[i, k]) < 1e-6
+    vol = abs(np.linalg.det(s["cell"]))
+    for a, b in [(0, 0), (1, 2), (2, 0)]:
+        e = []
+        for sign in (+1, -1):
+            eps = np.zeros((3, 3))
+            eps[a, b] += 0.5 * sign * h
+            eps[b, a] += 0.5 * sign * h
+            p = dict(s)
+            p["positions"] = s["positions"] @ (np.eye(3) + eps)
+            p["cell"] = s["cell"] @ (np.eye(3) + eps)
+            e.append(energy_of(p))
+        fd = (e[0] - e[1]) / (2 * h) / vol
+        assert abs(fd - stress[a, b]) < 1e-6, (a, b, fd, stress[a, b])
+        assert abs(stress[a, b] - stress[b, a]) < 1e-12
