@@ -45,7 +45,7 @@ enum { TACE_F32 = 0, TACE_F64 = 1 };
  * supports: cgtp interaction + cgtp product basis, natural parity, Lmax == lmax. */
 typedef struct {
   int dtype;          /* TACE_F32 or TACE_F64 */
-  int L;              /* Lmax == lmax, 1..3 */
+  int L;              /* rank of the angular features and the atomic basis (the reference's lmax), 1..3 */
   int num_layers;     /* >= 1 */
   int num_channel;    /* multiple of 32, <= 256 */
   int num_elements;   /* length of the sorted atomic-number list */
@@ -56,6 +56,8 @@ typedef struct {
   int readout_hidden; /* width of the energy read-out hidden layer (default 16, <= 64) */
   double cutoff;
   double avg_num_neighbors;
+  int Lnode;          /* rank of the node features between layers (the reference's Lmax), 1..L; 0 means "same as L".
+                         Lnode < L needs correlation == 2 (tace/models/_e3nn/base.py:113-360) */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -27,25 +27,33 @@ namespace {
 struct TPMeta { int NP, NX, NM, NG; const int* k; const int* base; };
 struct PBMeta { int NP, NB; const int* k; const int* base; };
 
-bool tp_meta(int L, bool scalar, TPMeta& m) {
+// L: rank of the angular features and messages; Lin: rank of the source features (< 0: scalar source)
+bool tp_meta(int L, int Lin, TPMeta& m) {
 #define TPM(TAG) { m = {TPX_##TAG::NP, TPX_##TAG::NX, TPX_##TAG::NM, TPX_##TAG::NG, tp_##TAG##_k, tp_##TAG##_base}; return true; }
-  if (L == 1 && scalar) TPM(L1_S)
-  if (L == 1) TPM(L1_F)
-  if (L == 2 && scalar) TPM(L2_S)
-  if (L == 2) TPM(L2_F)
-  if (L == 3 && scalar) TPM(L3_S)
-  if (L == 3) TPM(L3_F)
+  if (L == 1 && Lin < 0) TPM(L1_S)
+  if (L == 1 && Lin == 1) TPM(L1_F)
+  if (L == 2 && Lin < 0) TPM(L2_S)
+  if (L == 2 && Lin == 1) TPM(L2_N1)
+  if (L == 2 && Lin == 2) TPM(L2_F)
+  if (L == 3 && Lin < 0) TPM(L3_S)
+  if (L == 3 && Lin == 1) TPM(L3_N1)
+  if (L == 3 && Lin == 2) TPM(L3_N2)
+  if (L == 3 && Lin == 3) TPM(L3_F)
 #undef TPM
   return false;
 }
-bool pb_meta(int L, bool last, PBMeta& m) {
+// L: rank of A; Lout: highest output rank (< 0: scalar outputs only)
+bool pb_meta(int L, int Lout, PBMeta& m) {
 #define PBM(TAG) { m = {PB_##TAG::NP, PB_##TAG::NB, pb_##TAG##_k, pb_##TAG##_base}; return true; }
-  if (L == 1 && last) PBM(L1_T)
-  if (L == 1) PBM(L1_A)
-  if (L == 2 && last) PBM(L2_T)
-  if (L == 2) PBM(L2_A)
-  if (L == 3 && last) PBM(L3_T)
-  if (L == 3) PBM(L3_A)
+  if (L == 1 && Lout < 0) PBM(L1_T)
+  if (L == 1 && Lout == 1) PBM(L1_A)
+  if (L == 2 && Lout < 0) PBM(L2_T)
+  if (L == 2 && Lout == 1) PBM(L2_N1)
+  if (L == 2 && Lout == 2) PBM(L2_A)
+  if (L == 3 && Lout < 0) PBM(L3_T)
+  if (L == 3 && Lout == 1) PBM(L3_N1)
+  if (L == 3 && Lout == 2) PBM(L3_N2)
+  if (L == 3 && Lout == 3) PBM(L3_A)
 #undef PBM
   return false;
 }
@@ -278,7 +286,7 @@ struct ModelBase {
 
 template <typename T>
 struct Model : ModelBase {
-  int L, D, C, NL_, n_el, H;
+  int L, Ln, D, C, NL_, n_el, H;
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
   T* arena = nullptr;
@@ -312,18 +320,21 @@ struct Model : ModelBase {
   int init(const TaceConfig& c) {
     cfg = c;
     L = c.L; D = (L + 1) * (L + 1); C = c.num_channel; NL_ = c.num_layers; n_el = c.num_elements; H = c.readout_hidden;
+    Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
+    if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
+    const int Dn = (Ln + 1) * (Ln + 1);
     layers.resize(NL_);
     for (int t = 0; t < NL_; ++t) {
       LayerPlan& p = layers[t];
       p.scalar_src = (t == 0);
       p.last = (t == NL_ - 1);
       p.has_res = (t > 0);
-      if (!tp_meta(L, p.scalar_src, p.tp) || !pb_meta(L, p.last, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
-      p.Din = p.scalar_src ? 1 : D;
-      p.Dout = p.last ? 1 : D;
+      if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !pb_meta(L, p.last ? -1 : Ln, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      p.Din = p.scalar_src ? 1 : Dn;
+      p.Dout = p.last ? 1 : Dn;
       p.in_ls.clear(); p.out_ls.clear();
-      for (int l = 0; l <= (p.scalar_src ? 0 : L); ++l) p.in_ls.push_back(l);
-      for (int l = 0; l <= (p.last ? 0 : L); ++l) p.out_ls.push_back(l);
+      for (int l = 0; l <= (p.scalar_src ? 0 : Ln); ++l) p.in_ls.push_back(l);
+      for (int l = 0; l <= (p.last ? 0 : Ln); ++l) p.out_ls.push_back(l);
     }
     add_weight("emb", (long long)n_el * C);
     add_weight("bessel", kNumBessel);
@@ -798,7 +809,7 @@ struct Model : ModelBase {
         PH(("t" + ts + ".fwd.tp").c_str());
         TPArgs<T> ta;
         memset(&ta, 0, sizeof(ta));
-        ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
+        ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
         ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M + (long long)a0 * p.tp.NM * C; ta.e_base = e0;
         CKL(launch_tp_fwd(ta, s));
       }
@@ -829,7 +840,7 @@ struct Model : ModelBase {
       debug.push_back({"A" + ts, lb.A, NL * D * C});
       // per-species part in species-sorted space: gather A, product basis, coefficient linears scatter into `out`
       CKL(launch_gather_rows(lb.A, b.species_perm, lb.As, NL, D * C, s));
-      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.last ? 1 : 0, C, s));
+      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.last ? -1 : Ln, C, s));
       {
         std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
@@ -914,7 +925,7 @@ struct Model : ModelBase {
                           false, 0});
           }
           CKL(run_species_linear(sp, b, NL, s));
-          CKL(launch_pb_bwd(lb.As, lb.B2, lb.gAs, (int)NL, L, p.last ? 1 : 0, C, s));  // B2 now holds its gradient
+          CKL(launch_pb_bwd(lb.As, lb.B2, lb.gAs, (int)NL, L, p.last ? -1 : Ln, C, s));  // B2 now holds its gradient
         }
       }
       CKL(launch_scatter_rows(lb.gAs, b.species_perm, lb.gA, NL, D * C, s));
@@ -952,7 +963,7 @@ struct Model : ModelBase {
         PH(("t" + ts + ".bwd.tp").c_str());
         TPArgs<T> ta;
         memset(&ta, 0, sizeof(ta));
-        ta.L = L; ta.scalar_src = p.scalar_src; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
+        ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
         ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M + (long long)a0 * p.tp.NM * C; ta.n_seg = na;
         ta.rowptr = b.rowptr_dst + a0; ta.dW = lb.W; ta.dY = b.dY; ta.e_base = e0;
         ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;

@@ -111,8 +111,9 @@ def lit(v):
 
 
 # ----------------------------------------------------------- interaction TP code
-def gen_interaction(L, scalar_src, out):
-    """Emits, for one (L, source kind):
+def gen_interaction(L, Lin, out):
+    """Emits, for edge / message rank L (angular features and messages carry ranks 0..L) and source rank Lin
+    (source features carry ranks 0..Lin; Lin < 0: scalar source, the first layer):
 
     * ``build_G``: the channel-independent coupling of one edge, G[i] = sum_m2 K^p[m1,m2,m3] Y[l2,m2]
       for every structurally non-zero (p, m1, m3), ordered output-group major, then (p, m3, m1), each
@@ -122,14 +123,15 @@ def gen_interaction(L, scalar_src, out):
     * ``bwd``: gradients with respect to the per-edge weights, the angular features and the source
       features of one (edge, channel).
     """
-    tag = f"L{L}_{'S' if scalar_src else 'F'}"
-    in1 = [0] if scalar_src else list(range(L + 1))
+    scalar_src = Lin < 0
+    tag = f"L{L}_" + ("S" if scalar_src else "F" if Lin == L else f"N{Lin}")
+    in1 = [0] if scalar_src else list(range(Lin + 1))
     sh = list(range(L + 1))
     outs = list(range(L + 1))
     paths = tp_paths(L, in1, sh, outs)
     lay = Layout(paths, outs)
     xoff = {l: (0 if scalar_src else l * l) for l in in1}
-    nx = 1 if scalar_src else (L + 1) ** 2
+    nx = 1 if scalar_src else (Lin + 1) ** 2
     D = (L + 1) ** 2
     P = len(paths)
     Ks = [w3j(*p) * math.sqrt(2 * p[2] + 1) for p in paths]
@@ -166,7 +168,7 @@ def gen_interaction(L, scalar_src, out):
     ngrp = len(groups)
 
     o = out.append
-    o(f"// ---- interaction tensor product, L={L}, {'scalar' if scalar_src else 'full'} source: {P} paths, "
+    o(f"// ---- interaction tensor product, L={L}, {'scalar' if scalar_src else f'rank <= {Lin}'} source: {P} paths, "
       f"{lay.nm} message components, {len(gi)} non-zero G entries (padded to {ng}), {nnz_total} coupling non-zeros, "
       f"output groups {groups}")
     o(f"static const int tp_{tag}_k[{L + 1}] = {{{', '.join(str(lay.k[l]) for l in outs)}}};")
@@ -261,17 +263,19 @@ def gen_interaction(L, scalar_src, out):
 
 
 # ------------------------------------------------------------- product basis code
-def gen_product(L, last, out):
-    tag = f"L{L}_{'T' if last else 'A'}"  # T = target (scalar) outputs only, A = all ranks
+def gen_product(L, Lout, out):
+    """Input ranks 0..L, output ranks 0..Lout (Lout < 0: scalar outputs only, the last layer)."""
+    last = Lout < 0
+    tag = f"L{L}_" + ("T" if last else "A" if Lout == L else f"N{Lout}")  # T = target (scalar) outputs, A = all ranks
     ls = list(range(L + 1))
-    outs = [0] if last else ls
+    outs = [0] if last else list(range(Lout + 1))
     paths = tp_paths(L, ls, ls, outs)
     lay = Layout(paths, outs)
     D = (L + 1) ** 2
     P = len(paths)
     o = out.append
     nnz = sum(int(np.count_nonzero(w3j(*p))) for p in paths)
-    o(f"// ---- product basis (A x A), L={L}, {'scalar outputs' if last else 'all ranks'}: {P} paths, "
+    o(f"// ---- product basis (A x A), L={L}, {'scalar outputs' if last else f'output ranks <= {Lout}'}: {P} paths, "
       f"{lay.nm} components, {nnz} coupling non-zeros")
     o(f"struct PB_{tag} {{ static constexpr int L = {L}, NP = {P}, NB = {lay.nm}, D = {D}; }};")
     o(f"static const int pb_{tag}_k[{len(outs)}] = {{{', '.join(str(lay.k[l]) for l in outs)}}};")
@@ -319,10 +323,11 @@ def main():
     ]
     summary = []
     for L in (1, 2, 3):
-        for scalar_src in (True, False):
-            summary.append(gen_interaction(L, scalar_src, out))
-        for last in (False, True):
-            summary.append(gen_product(L, last, out))
+        # source / output rank below the edge rank (the reference default is Lmax = 2, lmax = 3), then equal to it
+        for Lin in [-1] + list(range(1, L + 1)):
+            summary.append(gen_interaction(L, Lin, out))
+        for Lout in [-1] + list(range(1, L + 1)):
+            summary.append(gen_product(L, Lout, out))
     out.append("}  // namespace tace")
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "tp_gen.cuh"), "w") as fh:

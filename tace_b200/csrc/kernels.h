@@ -14,7 +14,8 @@ namespace tace {
 // or by source (source gradients) so every sum is a segmented reduction without atomics.
 template <typename T>
 struct TPArgs {
-  int L, scalar_src, C;
+  int L, scalar_src, C;  // L: rank of Y and of the messages; scalar_src: the source is one scalar block (first layer)
+  int Lin;               // rank of the source features when !scalar_src (1..L)
   int n_seg;          // number of target atoms = thread blocks (per output group)
   const int* rowptr;  // [n_seg+1] CSR over the edges of each target (edges are target-sorted)
   const int* e_src;   // [E] source atom of each edge
@@ -47,8 +48,9 @@ template <typename T> cudaError_t launch_species_gather(const T* table, const in
 template <typename T> cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, cudaStream_t s);
 template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, cudaStream_t s);
 // product basis A (x) A (tace/models/_e3nn/prod.py:242-256, fused.py:90-95)
-template <typename T> cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int last, int C, cudaStream_t s);
-template <typename T> cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int last, int C, cudaStream_t s);
+// L: rank of A; Lout: highest output rank, or < 0 for scalar outputs only (the last layer)
+template <typename T> cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int Lout, int C, cudaStream_t s);
+template <typename T> cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int Lout, int C, cudaStream_t s);
 // read-out C -> H -> 1 with scaled SiLU, per-species scale, isolated-atom masking, atomic energies
 // (tace/models/_e3nn/readout.py:72-84, tace/models/blocks.py:250-273,332-379, _e3nn/tace.py:361-417).
 template <typename T>

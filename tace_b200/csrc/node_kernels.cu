@@ -161,21 +161,24 @@ __global__ void __launch_bounds__(128) pb_bwd_kernel(const T* __restrict__ A, co
 #define TACE_PB_DISPATCH(KERNEL, ...)                                                      \
   if (n <= 0) return cudaSuccess;                                                          \
   const unsigned grid = (unsigned)(((long long)n * C + 127) / 128);                        \
-  if (L == 1 && !last) KERNEL<T, PBX_L1_A><<<grid, 128, 0, s>>>(__VA_ARGS__);               \
-  else if (L == 1) KERNEL<T, PBX_L1_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
-  else if (L == 2 && !last) KERNEL<T, PBX_L2_A><<<grid, 128, 0, s>>>(__VA_ARGS__);          \
-  else if (L == 2) KERNEL<T, PBX_L2_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
-  else if (L == 3 && !last) KERNEL<T, PBX_L3_A><<<grid, 128, 0, s>>>(__VA_ARGS__);          \
-  else if (L == 3) KERNEL<T, PBX_L3_T><<<grid, 128, 0, s>>>(__VA_ARGS__);                   \
+  if (L == 1 && Lout < 0) KERNEL<T, PBX_L1_T><<<grid, 128, 0, s>>>(__VA_ARGS__);            \
+  else if (L == 1 && Lout == 1) KERNEL<T, PBX_L1_A><<<grid, 128, 0, s>>>(__VA_ARGS__);      \
+  else if (L == 2 && Lout < 0) KERNEL<T, PBX_L2_T><<<grid, 128, 0, s>>>(__VA_ARGS__);       \
+  else if (L == 2 && Lout == 1) KERNEL<T, PBX_L2_N1><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else if (L == 2 && Lout == 2) KERNEL<T, PBX_L2_A><<<grid, 128, 0, s>>>(__VA_ARGS__);      \
+  else if (L == 3 && Lout < 0) KERNEL<T, PBX_L3_T><<<grid, 128, 0, s>>>(__VA_ARGS__);       \
+  else if (L == 3 && Lout == 1) KERNEL<T, PBX_L3_N1><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else if (L == 3 && Lout == 2) KERNEL<T, PBX_L3_N2><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else if (L == 3 && Lout == 3) KERNEL<T, PBX_L3_A><<<grid, 128, 0, s>>>(__VA_ARGS__);      \
   else return cudaErrorInvalidValue;                                                       \
   return cudaGetLastError();
 
 template <typename T>
-cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int last, int C, cudaStream_t s) {
+cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int Lout, int C, cudaStream_t s) {
   TACE_PB_DISPATCH(pb_fwd_kernel, A, B2, n, C)
 }
 template <typename T>
-cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int last, int C, cudaStream_t s) {
+cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int Lout, int C, cudaStream_t s) {
   TACE_PB_DISPATCH(pb_bwd_kernel, A, gB2, gA, n, C)
 }
 

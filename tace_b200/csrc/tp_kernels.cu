@@ -190,11 +190,14 @@ cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
   if (a.n_seg <= 0) return cudaSuccess;                                   \
   if (a.C > 256 || (a.C & 31)) return cudaErrorInvalidValue;              \
   if (a.L == 1 && a.scalar_src) return FN<T, TPX_L1_S>(a, s);             \
-  if (a.L == 1) return FN<T, TPX_L1_F>(a, s);                             \
+  if (a.L == 1 && a.Lin == 1) return FN<T, TPX_L1_F>(a, s);               \
   if (a.L == 2 && a.scalar_src) return FN<T, TPX_L2_S>(a, s);             \
-  if (a.L == 2) return FN<T, TPX_L2_F>(a, s);                             \
+  if (a.L == 2 && a.Lin == 1) return FN<T, TPX_L2_N1>(a, s);              \
+  if (a.L == 2 && a.Lin == 2) return FN<T, TPX_L2_F>(a, s);               \
   if (a.L == 3 && a.scalar_src) return FN<T, TPX_L3_S>(a, s);             \
-  if (a.L == 3) return FN<T, TPX_L3_F>(a, s);                             \
+  if (a.L == 3 && a.Lin == 1) return FN<T, TPX_L3_N1>(a, s);              \
+  if (a.L == 3 && a.Lin == 2) return FN<T, TPX_L3_N2>(a, s);              \
+  if (a.L == 3 && a.Lin == 3) return FN<T, TPX_L3_F>(a, s);               \
   return cudaErrorInvalidValue;
 
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s) { TACE_TP_DISPATCH(launch_fwd_t) }

@@ -84,8 +84,7 @@ def check_model_config(cfg: Dict) -> Dict:
     cfg["atomic_numbers"] = sorted({int(z) for s in stats for z in s["atomic_numbers"]})
     cfg["avg_num_neighbors"] = sum(float(s["avg_num_neighbors"]) for s in stats) / len(stats)
     cfg["atomic_energies"] = [s["atomic_energy"] for s in stats]
-    _require(cfg["Lmax"] == cfg["lmax"], "Lmax == lmax")
-    _require(1 <= cfg["Lmax"] <= 3, "1 <= Lmax <= 3")
+    _require(1 <= cfg["Lmax"] <= cfg["lmax"] <= 3, "1 <= Lmax <= lmax <= 3")
     _require(not cfg["parity"], "parity=False")
     _require(cfg["num_channel"] % 32 == 0 and 32 <= cfg["num_channel"] <= 256, "num_channel a multiple of 32, <= 256")
     _require(1 <= cfg["num_layers"] <= 4, "1..4 layers")
@@ -127,6 +126,7 @@ def check_model_config(cfg: Dict) -> Dict:
     _require(all(n == "sigmoid_gate" for n in cfg["atomic_basis"]["nonlinear"]), "atomic_basis.nonlinear == sigmoid_gate")
     corr = cfg["product_basis"]["correlation"]
     _require(len(set(corr)) == 1 and corr[0] in (1, 2), "product_basis.correlation in {1, 2}, equal on all layers")
+    _require(corr[0] == 2 or cfg["Lmax"] == cfg["lmax"], "Lmax == lmax when product_basis.correlation == 1")
     return cfg
 
 
@@ -184,8 +184,9 @@ class e3nnTACE(torch.nn.Module):
         dt = torch.get_default_dtype()
         rc = float(cfg["cutoff"])
         nb = cfg["radial_basis"]["num_radial_basis"]
-        self.plan = ModelPlan(cfg["Lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
-                              cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64)
+        self.plan = ModelPlan(cfg["lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
+                              cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64,
+                              Lnode=cfg["Lmax"])
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         for name, shape in self.plan.parameter_shapes().items():
@@ -297,7 +298,7 @@ class TensorModel(torch.nn.Module):
             dtype=_lib.TACE_F64 if dtype == torch.float64 else _lib.TACE_F32, L=plan.L, num_layers=plan.num_layers,
             num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
-            cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]))
+            cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

@@ -30,14 +30,19 @@ def tp_paths(in1_ls, in2_ls, out_ls):
 
 
 class LayerPlan:
-    def __init__(self, t: int, num_layers: int, L: int):
+    """``L``: rank of the angular features and of the atomic basis A (the reference's ``lmax``); ``Lnode``: rank of
+    the node features between layers (``Lmax``), tace/models/_e3nn/base.py:113-360."""
+
+    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None):
+        Lnode = L if Lnode is None else Lnode
         self.t = t
-        self.scalar_src = t == 0
+        self.scalar_src = t == 0 or Lnode == 0
         self.last = t == num_layers - 1
         self.has_res = t > 0
         all_ls = list(range(L + 1))
-        self.in_ls = [0] if self.scalar_src else all_ls
-        self.out_ls = [0] if self.last else all_ls
+        node_ls = list(range(Lnode + 1))
+        self.in_ls = [0] if t == 0 else node_ls
+        self.out_ls = [0] if self.last else node_ls
         self.tp_paths = tp_paths(self.in_ls, all_ls, all_ls)
         self.k = [sum(1 for p in self.tp_paths if p[2] == l) for l in all_ls]
         self.pb_paths = tp_paths(all_ls, all_ls, self.out_ls)
@@ -46,10 +51,11 @@ class LayerPlan:
 
 class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
-                 readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64):
+                 readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
+        self.Lnode = L if Lnode is None else Lnode
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
-        self.layers = [LayerPlan(t, num_layers, L) for t in range(num_layers)]
+        self.layers = [LayerPlan(t, num_layers, L, self.Lnode) for t in range(num_layers)]
 
     def parameter_shapes(self) -> Dict[str, tuple]:
         """Reference parameter names (without the ``readout_fn.`` prefix) and shapes."""

@@ -146,10 +146,12 @@ def statistics(atomic_numbers: Sequence[int], avg_num_neighbors: float) -> List[
 
 
 def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], avg_num_neighbors: float,
-                 num_layers: int = 2, correlation: int = 2, target_property=("energy", "forces", "stress")) -> Dict:
-    """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product)."""
+                 num_layers: int = 2, correlation: int = 2, target_property=("energy", "forces", "stress"),
+                 Lmax: int = None) -> Dict:
+    """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product).  ``L`` is the edge
+    rank ``lmax``; the node rank ``Lmax`` defaults to it."""
     return {
-        "Lmax": L, "lmax": L, "num_layers": num_layers, "num_channel": channels, "cutoff": float(cutoff),
+        "Lmax": L if Lmax is None else Lmax, "lmax": L, "num_layers": num_layers, "num_channel": channels, "cutoff": float(cutoff),
         "statistics": statistics(elements, avg_num_neighbors),
         "target_property": list(target_property), "max_neighbors": None,
         "product_basis": {"correlation": correlation},

@@ -35,25 +35,32 @@ using namespace tace;
 extern "C" {
 
 // mode 0: forward (out0 = message components); mode 1: out0 = d/dw, out1 = d/dY, out2 = d/dx
-int h_tp(int L, int scalar_src, int mode, const double* x, const double* Y, const double* w, const double* g,
+// Lin: rank of the source features, or < 0 for the scalar source of the first layer
+int h_tp(int L, int Lin, int mode, const double* x, const double* Y, const double* w, const double* g,
          double* out0, double* out1, double* out2) {
-  if (L == 1 && scalar_src) TP_CASE(L1_S)
-  if (L == 1 && !scalar_src) TP_CASE(L1_F)
-  if (L == 2 && scalar_src) TP_CASE(L2_S)
-  if (L == 2 && !scalar_src) TP_CASE(L2_F)
-  if (L == 3 && scalar_src) TP_CASE(L3_S)
-  if (L == 3 && !scalar_src) TP_CASE(L3_F)
+  if (L == 1 && Lin < 0) TP_CASE(L1_S)
+  if (L == 1 && Lin == 1) TP_CASE(L1_F)
+  if (L == 2 && Lin < 0) TP_CASE(L2_S)
+  if (L == 2 && Lin == 1) TP_CASE(L2_N1)
+  if (L == 2 && Lin == 2) TP_CASE(L2_F)
+  if (L == 3 && Lin < 0) TP_CASE(L3_S)
+  if (L == 3 && Lin == 1) TP_CASE(L3_N1)
+  if (L == 3 && Lin == 2) TP_CASE(L3_N2)
+  if (L == 3 && Lin == 3) TP_CASE(L3_F)
   return -1;
 }
 
-int h_tp_dims(int L, int scalar_src, int* dims) {
+int h_tp_dims(int L, int Lin, int* dims) {
 #define DIMS(TAG) { dims[0] = TPX_##TAG::NP; dims[1] = TPX_##TAG::NX; dims[2] = TPX_##TAG::NM; dims[3] = TPX_##TAG::D; return 0; }
-  if (L == 1 && scalar_src) DIMS(L1_S)
-  if (L == 1 && !scalar_src) DIMS(L1_F)
-  if (L == 2 && scalar_src) DIMS(L2_S)
-  if (L == 2 && !scalar_src) DIMS(L2_F)
-  if (L == 3 && scalar_src) DIMS(L3_S)
-  if (L == 3 && !scalar_src) DIMS(L3_F)
+  if (L == 1 && Lin < 0) DIMS(L1_S)
+  if (L == 1 && Lin == 1) DIMS(L1_F)
+  if (L == 2 && Lin < 0) DIMS(L2_S)
+  if (L == 2 && Lin == 1) DIMS(L2_N1)
+  if (L == 2 && Lin == 2) DIMS(L2_F)
+  if (L == 3 && Lin < 0) DIMS(L3_S)
+  if (L == 3 && Lin == 1) DIMS(L3_N1)
+  if (L == 3 && Lin == 2) DIMS(L3_N2)
+  if (L == 3 && Lin == 3) DIMS(L3_F)
   return -1;
 }
 
@@ -68,13 +75,17 @@ int h_tp_dims(int L, int scalar_src, int* dims) {
   }
 
 // mode 0: b = A x A (out = b); mode 1: da from db.  Returns the number of b components.
-int h_pb(int L, int last, int mode, const double* a, const double* db, double* out) {
-  if (L == 1 && !last) PB_CASE(L1_A)
-  if (L == 1 && last) PB_CASE(L1_T)
-  if (L == 2 && !last) PB_CASE(L2_A)
-  if (L == 2 && last) PB_CASE(L2_T)
-  if (L == 3 && !last) PB_CASE(L3_A)
-  if (L == 3 && last) PB_CASE(L3_T)
+// Lout: highest output rank, or < 0 for scalar outputs only.
+int h_pb(int L, int Lout, int mode, const double* a, const double* db, double* out) {
+  if (L == 1 && Lout < 0) PB_CASE(L1_T)
+  if (L == 1 && Lout == 1) PB_CASE(L1_A)
+  if (L == 2 && Lout < 0) PB_CASE(L2_T)
+  if (L == 2 && Lout == 1) PB_CASE(L2_N1)
+  if (L == 2 && Lout == 2) PB_CASE(L2_A)
+  if (L == 3 && Lout < 0) PB_CASE(L3_T)
+  if (L == 3 && Lout == 1) PB_CASE(L3_N1)
+  if (L == 3 && Lout == 2) PB_CASE(L3_N2)
+  if (L == 3 && Lout == 3) PB_CASE(L3_A)
   return -1;
 }
 

@@ -249,3 +249,18 @@ def test_forces_and_stress_match_finite_differences_of_the_energy():
         fd = (e[0] - e[1]) / (2 * h) / vol
         assert abs(fd - stress[a, b]) < 1e-6, (a, b, fd, stress[a, b])
         assert abs(stress[a, b] - stress[b, a]) < 1e-12
+
+
+@pytest.mark.parametrize("Lmax,lmax,num_layers,dtype", [(2, 3, 2, torch.float64), (1, 3, 3, torch.float64), (1, 2, 2, torch.float64),
+                                                         (2, 3, 2, torch.float32)])
+def test_node_rank_below_edge_rank(Lmax, lmax, num_layers, dtype):
+    """Lmax < lmax (the reference's default is Lmax = 2, lmax = 3): node features between layers stop at Lmax while
+    the angular features and the atomic basis go to lmax."""
+    structs = synth.random_crystals(2, seed=31, nmin=4, nmax=9, zmax=3)
+    run_case(structs, lmax, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, num_layers=num_layers)
+
+
+def test_reference_default_model_shape():
+    """`e3nnTACE` with the reference defaults (Lmax 2, lmax 3, 64 channels, 2 layers, correlation 2)."""
+    structs = synth.random_crystals(2, seed=32, nmin=4, nmax=8, zmax=2)
+    run_case(structs, 3, 64, [1, 2], 5.0, torch.float32, Lmax=2)

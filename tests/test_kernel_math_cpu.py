@@ -33,8 +33,8 @@ def paths_and_layout(L, in1, outs):
     return paths, idx, acc
 
 
-def oracle_tp(L, scalar_src, x, Y, w):
-    in1 = [0] if scalar_src else list(range(L + 1))
+def oracle_tp(L, Lin, x, Y, w):
+    in1 = [0] if Lin < 0 else list(range(Lin + 1))
     irr1 = o3.Irreps([(1, l) for l in in1])
     irr2 = o3.Irreps.spherical_harmonics(L)
     paths, out = om.generate_paths(o3.Irreps([(1, l) for l in range(L + 1)]), irr1, irr2, "uvu")
@@ -42,26 +42,29 @@ def oracle_tp(L, scalar_src, x, Y, w):
     return tp(x[None], Y[None], w[None])[0], out
 
 
-@pytest.mark.parametrize("L", [1, 2, 3])
-@pytest.mark.parametrize("scalar_src", [True, False])
-def test_interaction_tp_matches_oracle(cpu_harness, L, scalar_src):
-    torch.manual_seed(L * 2 + scalar_src)
+RANK_PAIRS = [(L, Lx) for L in (1, 2, 3) for Lx in [-1] + list(range(1, L + 1))]  # (edge rank, source / output rank)
+
+
+@pytest.mark.parametrize("L,Lin", RANK_PAIRS)
+def test_interaction_tp_matches_oracle(cpu_harness, L, Lin):
+    torch.manual_seed(L * 5 + Lin)
+    scalar_src = Lin < 0
     dims = (ctypes.c_int * 4)()
-    assert cpu_harness.h_tp_dims(L, int(scalar_src), dims) == 0
+    assert cpu_harness.h_tp_dims(L, Lin, dims) == 0
     NP, NX, NM, D = list(dims)
-    in1 = [0] if scalar_src else list(range(L + 1))
+    in1 = [0] if scalar_src else list(range(Lin + 1))
     paths, idx, nm = paths_and_layout(L, in1, list(range(L + 1)))
     assert nm == NM and len(paths) == NP
     x = torch.randn(NX, dtype=torch.float64, requires_grad=True)
     Y = torch.randn(D, dtype=torch.float64, requires_grad=True)
     w = torch.randn(NP, dtype=torch.float64, requires_grad=True)
-    ref, out_irreps = oracle_tp(L, scalar_src, x, Y, w)
+    ref, out_irreps = oracle_tp(L, Lin, x, Y, w)
     # oracle output: per path p a [1, 2l3+1] block, in path order
     perm = [i for blk in idx for i in blk]
     out = np.zeros(NM)
     z = np.zeros(max(NM, D, NX))
     xn, Yn, wn = x.detach().numpy(), Y.detach().numpy(), w.detach().numpy()
-    cpu_harness.h_tp(L, int(scalar_src), 0, ptr(xn), ptr(Yn), ptr(wn), ptr(z), ptr(out), ptr(z), ptr(z))
+    cpu_harness.h_tp(L, Lin, 0, ptr(xn), ptr(Yn), ptr(wn), ptr(z), ptr(out), ptr(z), ptr(z))
     np.testing.assert_allclose(out[perm], ref.detach().numpy(), rtol=0, atol=1e-13)
     # backward against autograd
     g_ref = torch.randn(NM, dtype=torch.float64)  # gradient wrt oracle-ordered output
@@ -69,19 +72,18 @@ def test_interaction_tp_matches_oracle(cpu_harness, L, scalar_src):
     g_mine = np.zeros(NM)
     g_mine[perm] = g_ref.numpy()
     dw, dY, dx = np.zeros(NP), np.zeros(D), np.zeros(NX)
-    cpu_harness.h_tp(L, int(scalar_src), 1, ptr(xn), ptr(Yn), ptr(wn), ptr(g_mine), ptr(dw), ptr(dY), ptr(dx))
+    cpu_harness.h_tp(L, Lin, 1, ptr(xn), ptr(Yn), ptr(wn), ptr(g_mine), ptr(dw), ptr(dY), ptr(dx))
     np.testing.assert_allclose(dw, dw_ref.numpy(), rtol=0, atol=1e-12)
     np.testing.assert_allclose(dY, dY_ref.numpy(), rtol=0, atol=1e-12)
     if not scalar_src:  # the scalar-source layer never needs the source gradient
         np.testing.assert_allclose(dx, dx_ref.numpy(), rtol=0, atol=1e-12)
 
 
-@pytest.mark.parametrize("L", [1, 2, 3])
-@pytest.mark.parametrize("last", [False, True])
-def test_product_basis_matches_oracle(cpu_harness, L, last):
+@pytest.mark.parametrize("L,Lout", RANK_PAIRS)
+def test_product_basis_matches_oracle(cpu_harness, L, Lout):
     torch.manual_seed(10 + L)
     D = (L + 1) ** 2
-    outs = [0] if last else list(range(L + 1))
+    outs = [0] if Lout < 0 else list(range(Lout + 1))
     irr = o3.Irreps([(1, l) for l in range(L + 1)])
     paths, out = om.generate_paths(o3.Irreps([(1, l) for l in outs]), irr, irr, "uuu", identical_inputs=True)
     tp = om.TensorProduct(irr, irr, out, paths)
@@ -90,14 +92,14 @@ def test_product_basis_matches_oracle(cpu_harness, L, last):
     _, idx, nb = paths_and_layout(L, list(range(L + 1)), outs)
     perm = [i for blk in idx for i in blk]
     b = np.zeros(nb)
-    assert cpu_harness.h_pb(L, int(last), 0, ptr(a.detach().numpy()), ptr(b), ptr(b)) == nb
+    assert cpu_harness.h_pb(L, Lout, 0, ptr(a.detach().numpy()), ptr(b), ptr(b)) == nb
     np.testing.assert_allclose(b[perm], ref.detach().numpy(), rtol=0, atol=1e-13)
     g_ref = torch.randn(nb, dtype=torch.float64)
     (da_ref,) = torch.autograd.grad(ref, [a], g_ref)
     g_mine = np.zeros(nb)
     g_mine[perm] = g_ref.numpy()
     da = np.zeros(D)
-    cpu_harness.h_pb(L, int(last), 1, ptr(a.detach().numpy()), ptr(g_mine), ptr(da))
+    cpu_harness.h_pb(L, Lout, 1, ptr(a.detach().numpy()), ptr(g_mine), ptr(da))
     np.testing.assert_allclose(da, da_ref.numpy(), rtol=0, atol=1e-12)
 
 
