@@ -58,6 +58,8 @@ typedef struct {
   double avg_num_neighbors;
   int Lnode;          /* rank of the node features between layers (the reference's Lmax), 1..L; 0 means "same as L".
                          Lnode < L needs correlation == 2 (tace/models/_e3nn/base.py:113-360) */
+  int use_alllayer;   /* readout_emlp.use_alllayer: every layer below the last adds a linear read-out of its scalar
+                         channels (tace/models/_e3nn/readout.py:192-221); weights "ro.lin<t>" */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -393,16 +393,24 @@ class Representation(torch.nn.Module):
 
 
 class ScalarReadOut(torch.nn.Module):
-    """tace/models/_e3nn/readout.py:36-84: C -> 16 -> 1 with normalised SiLU, no bias."""
+    """tace/models/_e3nn/readout.py:36-84.  Last layer: C -> 16 -> 1 with normalised SiLU, no bias
+    (``linear2``); earlier layers (only built with ``use_alllayer``): one linear from the scalar block of
+    the layer's features to the energy (``linear1``)."""
 
-    def __init__(self, num_channel, hidden):
+    def __init__(self, num_channel, hidden, irreps_in=None, last=True):
         super().__init__()
-        dims = [num_channel] + list(hidden) + [1]
-        self.linear2 = torch.nn.ModuleList(
-            [Linear(Irreps([(a, 0)]), Irreps([(b, 0)]), bias=False) for a, b in zip(dims, dims[1:])]
-        )
+        self.last = last
+        if last:
+            dims = [num_channel] + list(hidden) + [1]
+            self.linear2 = torch.nn.ModuleList(
+                [Linear(Irreps([(a, 0)]), Irreps([(b, 0)]), bias=False) for a, b in zip(dims, dims[1:])]
+            )
+        else:
+            self.linear1 = torch.nn.ModuleList([Linear(Irreps(irreps_in), Irreps([(1, 0)]), bias=False)])
 
     def forward(self, x):
+        if not self.last:
+            return self.linear1[0](x)
         for lin in self.linear2[:-1]:
             x = SILU_CST * torch.nn.functional.silu(lin(x))
         return self.linear2[-1](x)
@@ -451,7 +459,7 @@ def resolve_config(user_cfg: Dict) -> Dict:
         "Lmax": 2, "lmax": 3, "num_channel": 64, "num_layers": 2,
         "radial_basis": {"num_radial_basis": 8, "polynomial_cutoff": 5, "hidden": [64, 64, 64]},
         "product_basis": {"correlation": 2},
-        "readout_emlp": {"hidden": [16]},
+        "readout_emlp": {"hidden": [16], "use_alllayer": False},
         "scale_shift": {"scale_type": "rms_forces", "shift_type": None},
     }
     for k, v in copy.deepcopy(user_cfg).items():
@@ -479,7 +487,15 @@ class OracleTACE(torch.nn.Module):
         self.register_buffer("cutoff", torch.tensor(float(cfg["cutoff"])))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         self.representation = Representation(cfg)
-        self.energy_readouts = torch.nn.ModuleList([ScalarReadOut(cfg["num_channel"], cfg["readout_emlp"]["hidden"])])
+        # tace/models/_e3nn/readout.py:192-221: one read-out per layer with use_alllayer, else only the last
+        C, hid = cfg["num_channel"], cfg["readout_emlp"]["hidden"]
+        self.use_alllayer = bool(cfg["readout_emlp"].get("use_alllayer", False))
+        if self.use_alllayer:
+            prods = self.representation.products
+            self.energy_readouts = torch.nn.ModuleList(
+                [ScalarReadOut(C, hid, irreps_in=prods[t].irreps_out, last=(t == len(prods) - 1)) for t in range(len(prods))])
+        else:
+            self.energy_readouts = torch.nn.ModuleList([ScalarReadOut(C, hid)])
         self.atomic_energy_layer = AtomicEnergy(cfg["atomic_energies"], cfg["atomic_numbers"])
         sk, hk = cfg["scale_shift"]["scale_type"], cfg["scale_shift"]["shift_type"]
         scale_d, shift_d = [], []
@@ -532,7 +548,10 @@ class OracleTensorModel(torch.nn.Module):
         desc = m.representation(node_attrs, edge_index, edge_vector, edge_length)
         e_base_node = m.atomic_energy_layer(node_attrs)[arange, node_fidelity]
         e_base_graph = scatter_sum(e_base_node, batch, num_graphs)
-        e_node = m.energy_readouts[0](desc[-1])[arange, node_fidelity]
+        if m.use_alllayer:  # tace/models/_e3nn/tace.py:367-386: every layer's read-out, summed before scale / shift
+            e_node = sum(ro(d)[arange, node_fidelity] for ro, d in zip(m.energy_readouts, desc))
+        else:
+            e_node = m.energy_readouts[0](desc[-1])[arange, node_fidelity]
         e_node = m.scale_shift(e_node, node_attrs, ptr, edge_index, batch, node_fidelity)
         e_graph = scatter_sum(e_node, batch, num_graphs)
         energy = e_base_graph + e_graph

@@ -388,6 +388,8 @@ struct Model : ModelBase {
     }
     add_weight("ro.W1", (long long)C * H);
     add_weight("ro.W2", H);
+    if (c.use_alllayer)
+      for (int t = 0; t + 1 < NL_; ++t) add_weight("ro.lin" + std::to_string(t), C);
     add_weight("scale", n_el);
     add_weight("e0", n_el);
     if (cudaMalloc(&arena, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
@@ -432,7 +434,7 @@ struct Model : ModelBase {
     int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor;
     std::vector<LayerBufs> lay;
   };
 
@@ -444,7 +446,7 @@ struct Model : ModelBase {
     b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
-    b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL);
+    b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL);
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
     const bool chunked = E > max_chunk_edges;
     b.n_chunks = chunked ? (int)((E + max_chunk_edges - 1) / max_chunk_edges) : 1;
@@ -888,6 +890,13 @@ struct Model : ModelBase {
     ra.scale = w("scale"); ra.e0 = w("e0"); ra.species = bt->species; ra.atom_graph = b.atom_graph;
     ra.graph_ptr = bt->graph_ptr; ra.rowptr_dst = b.rowptr_dst; ra.node_energy = static_cast<T*>(o->node_energy);
     ra.e_scaled = b.e_scaled; ra.gh = need_grad ? top.gh_out : nullptr; ra.n = (int)NL; ra.C = C; ra.H = H;
+    if (cfg.use_alllayer) {  // linear read-outs of the layers below the last
+      ra.n_extra = NL_ - 1;
+      for (int t = 0; t + 1 < NL_; ++t) {
+        ra.extra_h[t] = b.lay[t].h_out; ra.extra_hs[t] = (long long)layers[t].Dout * C; ra.extra_w[t] = w("ro.lin" + std::to_string(t));
+      }
+      ra.factor = b.ro_factor;
+    }
     CKL(launch_readout(ra, s));
     if (o->energy) CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, static_cast<T*>(o->energy), B, s));
     if (!need_grad) { PH("end"); return TACE_OK; }
@@ -899,6 +908,8 @@ struct Model : ModelBase {
       const std::string pre = "t" + std::to_string(t) + ".";
       const std::string ts = std::to_string(t);
       PH(("t" + ts + ".bwd.node").c_str());
+      if (cfg.use_alllayer && t + 1 < NL_)  // this layer's own linear read-out, on top of what the layer above sent down
+        CKL(launch_readout_linear_bwd(lb.gh_out, (long long)p.Dout * C, b.ro_factor, w("ro.lin" + ts), (int)NL, C, s));
       {  // through the final linear
         std::vector<LinSpec> sp;
         for (int l : p.out_ls)

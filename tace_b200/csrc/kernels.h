@@ -6,6 +6,9 @@
 
 namespace tace {
 
+constexpr int kMaxLayers = 4;
+
+
 // ---- interaction tensor product (tp_kernels.cu) ---------------------------------------------
 // Message passing m_i = sum_{e: target(e) = i} sum_p w[e,p,c] (x[source(e)] (x) Y[e])_p, its
 // transpose with respect to the source features, and the gradients with respect to the
@@ -69,7 +72,13 @@ struct ReadoutArgs {
   T* e_scaled;       // [n] scaled read-out without E0 (summed per graph together with E0)
   T* gh;             // [n][C] d(sum E)/dh, or nullptr
   int n, C, H;
+  // linear read-outs of earlier layers (use_alllayer): e += sum_c extra_h[t][i * extra_hs[t] + c] * extra_w[t][c]
+  int n_extra;
+  const T* extra_h[kMaxLayers]; long long extra_hs[kMaxLayers]; const T* extra_w[kMaxLayers];
+  T* factor;         // [n] d(node energy)/d(read-out sum): the species scale, 0 for isolated atoms; or nullptr
 };
+// gh[i * hs + c] += factor[i] * w[c]: gradient of an earlier layer's linear read-out
+template <typename T> cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, int n, int C, cudaStream_t s);
 template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);
 // energy[g] = sum_{i in g} (e0[species_i] + e_scaled[i])
 template <typename T> cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr,
@@ -85,7 +94,6 @@ template <typename T>
 struct MlpWeights {
   const T* A0; const T* A1; const T* A2; const T* A1t; const T* A2t;
 };
-constexpr int kMaxLayers = 4;
 template <typename T>
 struct EdgeArgs {
   int L, n_layers;

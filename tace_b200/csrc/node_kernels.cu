@@ -203,6 +203,12 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
     e += T(kSiluCst) * silu_(r[j]) * a.W2[j];
     r[j] = T(kSiluCst) * silu_grad_(r[j]) * a.W2[j];  // d e / d r_j
   }
+  for (int t = 0; t < a.n_extra; ++t) {
+    const T* ht = a.extra_h[t] + (long long)i * a.extra_hs[t];
+    T acc = T(0);
+    for (int c = 0; c < a.C; ++c) acc += ht[c] * a.extra_w[t][c];
+    e += acc;
+  }
   const int z = a.species[i];
   const int g = a.atom_graph[i];
   const int n_nodes = a.graph_ptr[g + 1] - a.graph_ptr[g];
@@ -210,6 +216,7 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
   const T sc = (n_nodes == 1 && n_edges == 0) ? T(0) : a.scale[z];
   const T es = e * sc;
   a.e_scaled[i] = es;
+  if (a.factor) a.factor[i] = sc;
   if (a.node_energy) a.node_energy[i] = a.e0[z] + es;
   if (a.gh) {
     T* gh = a.gh + (long long)i * a.C;
@@ -220,6 +227,22 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
     }
   }
 }
+template <typename T>
+__global__ void readout_linear_bwd_kernel(T* __restrict__ gh, long long hs, const T* __restrict__ factor, const T* __restrict__ w,
+                                          long long n, int C) {
+  const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (k >= n * C) return;
+  const long long i = k / C;
+  const int c = (int)(k - i * C);
+  gh[i * hs + c] += factor[i] * w[c];
+}
+template <typename T>
+cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, int n, int C, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  readout_linear_bwd_kernel<T><<<(unsigned)(((long long)n * C + 255) / 256), 256, 0, s>>>(gh, hs, factor, w, n, C);
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
   if (a.n <= 0) return cudaSuccess;
@@ -254,6 +277,7 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
 
 #define INST(T)                                                                                               \
   template cudaError_t launch_fill_zero<T>(T*, long long, cudaStream_t);                                      \
+  template cudaError_t launch_readout_linear_bwd<T>(T*, long long, const T*, const T*, int, int, cudaStream_t); \
   template cudaError_t launch_add_inplace<T>(T*, const T*, long long, cudaStream_t);                          \
   template cudaError_t launch_gather_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);         \
   template cudaError_t launch_scatter_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);        \

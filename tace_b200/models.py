@@ -105,7 +105,7 @@ def check_model_config(cfg: Dict) -> Dict:
         ("product_basis", "l1l2", {None}), ("product_basis", "return_components", {None}),
         ("product_basis", "num_expert", {None, 1}), ("product_basis", "nonlinear", {None}),
         ("product_basis", "agnostic", {False}), ("product_basis", "use_shared_expert", {False}),
-        ("readout_emlp", "bias", {False}), ("readout_emlp", "use_alllayer", {False}), ("readout_emlp", "use_uie", {False}),
+        ("readout_emlp", "bias", {False}), ("readout_emlp", "use_alllayer", {False, True}), ("readout_emlp", "use_uie", {False}),
         ("scale_shift", "enable", {True}), ("scale_shift", "all_atoms", {False}), ("scale_shift", "shift_type", {None}),
     ]:
         _require(cfg[section][key] in allowed, f"{section}.{key} in {allowed}, got {cfg[section][key]!r}")
@@ -186,7 +186,7 @@ class e3nnTACE(torch.nn.Module):
         nb = cfg["radial_basis"]["num_radial_basis"]
         self.plan = ModelPlan(cfg["lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
                               cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64,
-                              Lnode=cfg["Lmax"])
+                              Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"])
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         for name, shape in self.plan.parameter_shapes().items():
@@ -298,7 +298,8 @@ class TensorModel(torch.nn.Module):
             dtype=_lib.TACE_F64 if dtype == torch.float64 else _lib.TACE_F32, L=plan.L, num_layers=plan.num_layers,
             num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
-            cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode)
+            cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
+            use_alllayer=int(plan.use_alllayer))
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

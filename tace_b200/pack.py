@@ -51,9 +51,11 @@ class LayerPlan:
 
 class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
-                 readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None):
+                 readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
+                 use_alllayer: bool = False):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Lnode = L if Lnode is None else Lnode
+        self.use_alllayer = bool(use_alllayer)
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
         self.layers = [LayerPlan(t, num_layers, L, self.Lnode) for t in range(num_layers)]
 
@@ -83,8 +85,14 @@ class ModelPlan:
                 out[pp + "coefs.1.bias"] = (n_el, C)
             out[pp + "linear.weight"] = (len(lp.out_ls) * C * C,)
             out[pp + "linear.bias"] = (C,)
-        out["energy_readouts.0.linear2.0.weight"] = (C * self.H,)
-        out["energy_readouts.0.linear2.1.weight"] = (self.H,)
+        # tace/models/_e3nn/readout.py:192-221: with use_alllayer every layer has a read-out (a single linear on
+        # the scalar block below the last layer), otherwise the list holds only the last layer's MLP
+        ro = self.num_layers - 1 if self.use_alllayer else 0
+        if self.use_alllayer:
+            for t in range(self.num_layers - 1):
+                out[f"energy_readouts.{t}.linear1.0.weight"] = (C,)
+        out[f"energy_readouts.{ro}.linear2.0.weight"] = (C * self.H,)
+        out[f"energy_readouts.{ro}.linear2.1.weight"] = (self.H,)
         return out
 
 
@@ -181,8 +189,12 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
                 # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
                 hi, lo = tile_k_major(hi), tile_k_major(lo)
             out[name + "_hi"], out[name + "_lo"] = hi, lo
-    out["ro.W1"] = g("energy_readouts.0.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
-    out["ro.W2"] = g("energy_readouts.0.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
+    ro = plan.num_layers - 1 if plan.use_alllayer else 0
+    out["ro.W1"] = g(f"energy_readouts.{ro}.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
+    out["ro.W2"] = g(f"energy_readouts.{ro}.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
+    if plan.use_alllayer:
+        for t in range(plan.num_layers - 1):
+            out[f"ro.lin{t}"] = g(f"energy_readouts.{t}.linear1.0.weight").reshape(C) / math.sqrt(C)
     out["scale"] = g("scale_shift.scale")[0]
     out["e0"] = g("atomic_energy_layer.atomic_energy")[0]
     shift = g("scale_shift.shift")

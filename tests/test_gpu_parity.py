@@ -264,3 +264,10 @@ def test_reference_default_model_shape():
     """`e3nnTACE` with the reference defaults (Lmax 2, lmax 3, 64 channels, 2 layers, correlation 2)."""
     structs = synth.random_crystals(2, seed=32, nmin=4, nmax=8, zmax=2)
     run_case(structs, 3, 64, [1, 2], 5.0, torch.float32, Lmax=2)
+
+
+@pytest.mark.parametrize("num_layers,Lmax,dtype", [(2, None, torch.float64), (3, 1, torch.float64), (2, None, torch.float32)])
+def test_read_out_on_every_layer(num_layers, Lmax, dtype):
+    """readout_emlp.use_alllayer: layers below the last add a linear read-out of their scalar channels."""
+    structs = synth.random_crystals(2, seed=41, nmin=4, nmax=9, zmax=3)
+    run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, num_layers=num_layers, Lmax=Lmax, use_alllayer=True)
