@@ -60,6 +60,8 @@ typedef struct {
                          Lnode < L needs correlation == 2 (tace/models/_e3nn/base.py:113-360) */
   int use_alllayer;   /* readout_emlp.use_alllayer: every layer below the last adds a linear read-out of its scalar
                          channels (tace/models/_e3nn/readout.py:192-221); weights "ro.lin<t>" */
+  int gate_m0_off;    /* 0: atomic_basis.gate_m0 = True (every rank, l = 0 included, scaled by a sigmoid gate; the
+                         reference default); 1: gate_m0 = False (scalars through SiLU, ranks >= 1 gated; nonlinear.py:43-70) */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -186,15 +186,47 @@ class Gate(torch.nn.Module):
         self.irreps_gates = Irreps([(m, 0) for m, _ in self.irreps_gated])
         self.irreps_in = (self.irreps_gates.simplify() + self.irreps_gated).sort().simplify()
         self.irreps_out = self.irreps_gated
+        self.m0 = True
 
     def forward(self, x):
         n = x.shape[0]
+        if not self.m0:
+            return self._forward_scalars_ungated(x)
         ng = self.irreps_gates.dim
         gates = SIGMOID_CST * torch.sigmoid(x[:, :ng])
         gated = x[:, ng:]
         outs, goff = [], 0
         for (m, l), sl in zip(self.irreps_gated, self.irreps_gated.slices()):
             g = gates[:, goff : goff + m]
+            goff += m
+            outs.append((gated[:, sl].reshape(n, m, 2 * l + 1) * g.unsqueeze(-1)).reshape(n, -1))
+        return torch.cat(outs, dim=-1)
+
+
+class ScalarActGate(Gate):
+    """tace/models/_e3nn/nonlinear.py:43-70 (gate_m0=False) over e3nn ``Gate``: input = [scalars | one gate scalar
+    block per rank >= 1 | blocks of rank >= 1]; scalars go through 1.6792*silu, rank l >= 1 is scaled channel-wise
+    by 1.8467*sigmoid(gate l); output = [activated scalars | gated blocks]."""
+
+    def __init__(self, irreps: Irreps):
+        super().__init__(irreps)
+        irreps = Irreps(irreps)
+        self.m0 = False
+        self.n_scalar = sum(m for m, l in irreps if l == 0)
+        self.irreps_gated = Irreps([(m, l) for m, l in irreps if l > 0])
+        self.irreps_gates = Irreps([(m, 0) for m, _ in self.irreps_gated])
+        scalars = Irreps([(self.n_scalar, 0)])
+        self.irreps_in = (scalars + self.irreps_gates.simplify() + self.irreps_gated).sort().simplify()
+        self.irreps_out = (scalars + self.irreps_gated).simplify()
+
+    def _forward_scalars_ungated(self, x):
+        n, ns, ng = x.shape[0], self.n_scalar, self.irreps_gates.dim
+        outs = [SILU_CST * torch.nn.functional.silu(x[:, :ns])]
+        gates = SIGMOID_CST * torch.sigmoid(x[:, ns:ns + ng])
+        gated = x[:, ns + ng:]
+        goff = 0
+        for (m, l), sl in zip(self.irreps_gated, self.irreps_gated.slices()):
+            g = gates[:, goff:goff + m]
             goff += m
             outs.append((gated[:, sl].reshape(n, m, 2 * l + 1) * g.unsqueeze(-1)).reshape(n, -1))
         return torch.cat(outs, dim=-1)
@@ -266,7 +298,7 @@ class Interaction(torch.nn.Module):
     tace/models/_e3nn/base.py:113-249."""
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
-                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps):
+                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
         C = num_channel
@@ -282,7 +314,8 @@ class Interaction(torch.nn.Module):
         self.linear_up = Linear(self.irreps_in, self.irreps_in, bias=True)
         paths, tp_irreps_out = generate_paths(self.irreps_out, self.irreps_in, self.irreps_sh, "uvu")
         self.rejector = TensorProduct(self.irreps_in, self.irreps_sh, tp_irreps_out, paths)
-        self.nonlinearity = Gate(Irreps([(C, l) for _, l in self.irreps_out]))
+        gate_cls = Gate if gate_m0 else ScalarActGate
+        self.nonlinearity = gate_cls(Irreps([(C, l) for _, l in self.irreps_out]))
         self.linear_nonlinearity = Linear(self.nonlinearity.irreps_out, self.irreps_out, bias=True)
         self.linear_down = Linear(tp_irreps_out.simplify(), self.nonlinearity.irreps_in, bias=True)
         self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel])
@@ -373,7 +406,7 @@ class Representation(torch.nn.Module):
             self.interactions.append(
                 Interaction(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
                             cfg["product_basis"]["correlation"][layer], C, rb["num_radial_basis"], rb["hidden"],
-                            irreps_in, [(1, 0)])
+                            irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True))
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],

@@ -287,6 +287,7 @@ struct ModelBase {
 template <typename T>
 struct Model : ModelBase {
   int L, Ln, D, C, NL_, n_el, H;
+  int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
   T* arena = nullptr;
@@ -320,6 +321,7 @@ struct Model : ModelBase {
   int init(const TaceConfig& c) {
     cfg = c;
     L = c.L; D = (L + 1) * (L + 1); C = c.num_channel; NL_ = c.num_layers; n_el = c.num_elements; H = c.readout_hidden;
+    m0 = c.gate_m0_off ? 0 : 1;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     const int Dn = (Ln + 1) * (Ln + 1);
@@ -358,13 +360,13 @@ struct Model : ModelBase {
         add_weight(pre + "W3t_lo", (long long)kHidden * p.tp.NP * C);
       }
       for (int l = 0; l <= L; ++l) {
-        const long long outl = (l == 0) ? (long long)(L + 2) * C : C;
+        const long long outl = (l == 0) ? (long long)(L + 1 + m0) * C : C;
         add_linear_weight(pre + "down.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
         add_linear_weight(pre + "downT.l" + std::to_string(l), (long long)p.tp.k[l] * C * outl);
         add_linear_weight(pre + "nl.l" + std::to_string(l), (long long)C * C);
         add_linear_weight(pre + "nlT.l" + std::to_string(l), (long long)C * C);
       }
-      add_weight(pre + "down.b", (long long)(L + 2) * C);
+      add_weight(pre + "down.b", (long long)(L + 1 + m0) * C);
       add_weight(pre + "nl.b", C);
       for (size_t i = 0; i < p.out_ls.size(); ++i) {
         const int l = p.out_ls[i];
@@ -822,15 +824,15 @@ struct Model : ModelBase {
         std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l) {
           const int K = p.tp.k[l] * C;
-          const int Nout = (l == 0) ? (L + 2) * C : C;
-          T* dst = (l == 0) ? lb.Gt : lb.Gt + (long long)(L + 1 + l * l) * C;
+          const int Nout = (l == 0) ? (L + 1 + m0) * C : C;
+          T* dst = (l == 0) ? lb.Gt : lb.Gt + (long long)(L + m0 + l * l) * C;
           sp.push_back({lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, K, 2 * l + 1, K, pre + "down.l" + std::to_string(l),
                         pre + "downT.l" + std::to_string(l), Nout, dst, (long long)(L + 1 + D) * C, C,
                         l == 0 ? w(pre + "down.b") : nullptr});
         }
         CKL(run_linear(sp, NL, s));
       }
-      CKL(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, s));
+      CKL(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, m0, s));
       {
         std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l)
@@ -947,13 +949,13 @@ struct Model : ModelBase {
                         pre + "nl.l" + std::to_string(l), C, lb.ga + (long long)l * l * C, (long long)D * C, C, nullptr});
         CKL(run_linear(sp, NL, s));
       }
-      CKL(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, s));
+      CKL(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, m0, s));
       {  // through linear_down; the gradient of the messages overwrites the messages
         std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l) {
           const int Nk = p.tp.k[l] * C;
-          const int Kin = (l == 0) ? (L + 2) * C : C;
-          const T* src = (l == 0) ? lb.gGt : lb.gGt + (long long)(L + 1 + l * l) * C;
+          const int Kin = (l == 0) ? (L + 1 + m0) * C : C;
+          const T* src = (l == 0) ? lb.gGt : lb.gGt + (long long)(L + m0 + l * l) * C;
           sp.push_back({src, (long long)(L + 1 + D) * C, C, 2 * l + 1, Kin, pre + "downT.l" + std::to_string(l),
                         pre + "down.l" + std::to_string(l), Nk, lb.M + (long long)p.tp.base[l] * C, (long long)p.tp.NM * C, Nk, nullptr});
         }

@@ -48,8 +48,9 @@ template <typename T> cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const
 // x0[n][c] = table[species[n]][c]
 template <typename T> cudaError_t launch_species_gather(const T* table, const int* species, T* out, int n, int C, cudaStream_t s);
 // gate (tace/models/_e3nn/nonlinear.py:125-135): Gt = [(L+1)C gates | D*C gated] per atom.
-template <typename T> cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, cudaStream_t s);
-template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, cudaStream_t s);
+// m0: 1 = every rank (l = 0 included) scaled by a sigmoid gate; 0 = scalars through the normalised SiLU, ranks >= 1 gated
+template <typename T> cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, int m0, cudaStream_t s);
+template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, int m0, cudaStream_t s);
 // product basis A (x) A (tace/models/_e3nn/prod.py:242-256, fused.py:90-95)
 // L: rank of A; Lout: highest output rank, or < 0 for scalar outputs only (the last layer)
 template <typename T> cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int Lout, int C, cudaStream_t s);

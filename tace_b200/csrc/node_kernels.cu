@@ -73,14 +73,29 @@ cudaError_t launch_species_gather(const T* table, const int* species, T* out, in
 }
 
 // ---- gate --------------------------------------------------------------------------------------
+// Row of Gt per atom, (L + 1 + D) * C long.  m0 != 0 (the reference's gate_m0 = True, nonlinear.py:27-42): [L + 1 gate
+// scalars | all D components], every rank scaled by its gate.  m0 == 0 (gate_m0 = False, the e3nn Gate,
+// nonlinear.py:43-70): [scalars | L gate scalars | components of ranks >= 1 | unused]; the scalars go through the
+// normalised SiLU, rank l >= 1 is scaled by gate l.
 template <typename T>
-__global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int n, int L, int C) {
+__global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int n, int L, int C, int m0) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)n * C) return;
   const int i = idx / C, c = idx - (long long)i * C;
   const int D = (L + 1) * (L + 1);
   const T* row = Gt + (long long)i * (L + 1 + D) * C;
   T* out = a + (long long)i * D * C;
+  if (!m0) {
+    out[c] = T(kSiluCst) * silu_(row[c]);
+    for (int l = 1; l <= L; ++l) {
+      const T gate = T(kSigmoidCst) * sigmoid_(row[l * C + c]);
+      for (int m = 0; m < 2 * l + 1; ++m) {
+        const int k = l * l + m;
+        out[k * C + c] = row[(L + k) * C + c] * gate;
+      }
+    }
+    return;
+  }
   for (int l = 0; l <= L; ++l) {
     const T gate = T(kSigmoidCst) * sigmoid_(row[l * C + c]);
     for (int m = 0; m < 2 * l + 1; ++m) {
@@ -90,7 +105,7 @@ __global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int
   }
 }
 template <typename T>
-__global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ ga, T* __restrict__ gGt, int n, int L, int C) {
+__global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ ga, T* __restrict__ gGt, int n, int L, int C, int m0) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)n * C) return;
   const int i = idx / C, c = idx - (long long)i * C;
@@ -98,6 +113,22 @@ __global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ 
   const T* row = Gt + (long long)i * (L + 1 + D) * C;
   const T* g = ga + (long long)i * D * C;
   T* out = gGt + (long long)i * (L + 1 + D) * C;
+  if (!m0) {
+    out[c] = g[c] * T(kSiluCst) * silu_grad_(row[c]);
+    for (int l = 1; l <= L; ++l) {
+      const T sg = sigmoid_(row[l * C + c]);
+      const T gate = T(kSigmoidCst) * sg;
+      T acc = T(0);
+      for (int m = 0; m < 2 * l + 1; ++m) {
+        const int k = l * l + m;
+        const T gk = g[k * C + c];
+        acc += gk * row[(L + k) * C + c];
+        out[(L + k) * C + c] = gk * gate;
+      }
+      out[l * C + c] = acc * T(kSigmoidCst) * sg * (T(1) - sg);
+    }
+    return;
+  }
   for (int l = 0; l <= L; ++l) {
     const T sg = sigmoid_(row[l * C + c]);
     const T gate = T(kSigmoidCst) * sg;
@@ -112,15 +143,15 @@ __global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ 
   }
 }
 template <typename T>
-cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, cudaStream_t s) {
+cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, int m0, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  gate_fwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, a, n, L, C);
+  gate_fwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, a, n, L, C, m0);
   return cudaGetLastError();
 }
 template <typename T>
-cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, cudaStream_t s) {
+cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, int m0, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  gate_bwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, ga, gGt, n, L, C);
+  gate_bwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, ga, gGt, n, L, C, m0);
   return cudaGetLastError();
 }
 
@@ -282,8 +313,8 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_gather_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);         \
   template cudaError_t launch_scatter_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);        \
   template cudaError_t launch_species_gather<T>(const T*, const int*, T*, int, int, cudaStream_t);            \
-  template cudaError_t launch_gate_fwd<T>(const T*, T*, int, int, int, cudaStream_t);                         \
-  template cudaError_t launch_gate_bwd<T>(const T*, const T*, T*, int, int, int, cudaStream_t);               \
+  template cudaError_t launch_gate_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                    \
+  template cudaError_t launch_gate_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);          \
   template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
   template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
   template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \

@@ -97,7 +97,7 @@ def check_model_config(cfg: Dict) -> Dict:
         ("radial_basis", "distance_transform", {None}), ("radial_basis", "apply_cutoff", {True}),
         ("radial_basis", "bias", {False}), ("radial_basis", "use_dydynamic_cutoff", {False}),
         ("radial_basis", "num_radial_basis", {8}),
-        ("atomic_basis", "scatter_norm", {"avg_num_neighbors"}), ("atomic_basis", "gate_m0", {True}),
+        ("atomic_basis", "scatter_norm", {"avg_num_neighbors"}), ("atomic_basis", "gate_m0", {True, False}),
         ("atomic_basis", "l1l2", {None}), ("atomic_basis", "scalar_act", {None, "sigmoid"}),
         ("atomic_basis", "tensor_act", {None, "sigmoid"}), ("atomic_basis", "node_wise_hidden", {None}),
         ("resnet", "type", {"BB"}), ("resnet", "linear_type", {"aware"}), ("resnet", "use_first_resnet", {False}),
@@ -186,7 +186,7 @@ class e3nnTACE(torch.nn.Module):
         nb = cfg["radial_basis"]["num_radial_basis"]
         self.plan = ModelPlan(cfg["lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
                               cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64,
-                              Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"])
+                              Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"], gate_m0=cfg["atomic_basis"]["gate_m0"])
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         for name, shape in self.plan.parameter_shapes().items():
@@ -299,7 +299,7 @@ class TensorModel(torch.nn.Module):
             num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
             cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
-            use_alllayer=int(plan.use_alllayer))
+            use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0))
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

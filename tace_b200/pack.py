@@ -52,10 +52,11 @@ class LayerPlan:
 class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
-                 use_alllayer: bool = False):
+                 use_alllayer: bool = False, gate_m0: bool = True):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Lnode = L if Lnode is None else Lnode
         self.use_alllayer = bool(use_alllayer)
+        self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
         self.layers = [LayerPlan(t, num_layers, L, self.Lnode) for t in range(num_layers)]
 
@@ -70,8 +71,9 @@ class ModelPlan:
             dims = [self.num_bessel] + [self.mlp_hidden] * 3 + [len(lp.tp_paths) * C]
             for i, (a, b) in enumerate(zip(dims, dims[1:])):
                 out[pre + f"edge_info.mlp.{2 * i}.weight"] = (a, b)
-            out[pre + "linear_down.weight"] = (sum(lp.k[l] * C * ((L + 2) * C if l == 0 else C) for l in range(L + 1)),)
-            out[pre + "linear_down.bias"] = ((L + 2) * C,)
+            n0 = (L + 2) * C if self.gate_m0 else (L + 1) * C
+            out[pre + "linear_down.weight"] = (sum(lp.k[l] * C * (n0 if l == 0 else C) for l in range(L + 1)),)
+            out[pre + "linear_down.bias"] = (n0,)
             out[pre + "linear_nonlinearity.weight"] = ((L + 1) * C * C,)
             out[pre + "linear_nonlinearity.bias"] = (C,)
             if lp.has_res:
@@ -155,7 +157,7 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         for name in ("W3", "W3t"):  # TF32 high part / residual for the tensor-core GEMM of fp32 models
             hi, lo = split_tf32(out[tp + name])
             out[tp + name + "_hi"], out[tp + name + "_lo"] = hi, lo
-        down_shapes = [(lp.k[l] * C, (L + 2) * C if l == 0 else C) for l in range(L + 1)]
+        down_shapes = [(lp.k[l] * C, ((L + 2) * C if plan.gate_m0 else (L + 1) * C) if l == 0 else C) for l in range(L + 1)]
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
             put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
         out[tp + "down.b"] = g(pre + "linear_down.bias") / avg_num_neighbors

@@ -147,7 +147,7 @@ def statistics(atomic_numbers: Sequence[int], avg_num_neighbors: float) -> List[
 
 def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], avg_num_neighbors: float,
                  num_layers: int = 2, correlation: int = 2, target_property=("energy", "forces", "stress"),
-                 Lmax: int = None, use_alllayer: bool = False) -> Dict:
+                 Lmax: int = None, use_alllayer: bool = False, gate_m0: bool = True) -> Dict:
     """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product).  ``L`` is the edge
     rank ``lmax``; the node rank ``Lmax`` defaults to it."""
     return {
@@ -156,6 +156,7 @@ def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], 
         "target_property": list(target_property), "max_neighbors": None,
         "product_basis": {"correlation": correlation},
         "readout_emlp": {"use_alllayer": bool(use_alllayer)},
+        "atomic_basis": {"gate_m0": bool(gate_m0)},
     }
 
 

@@ -9,12 +9,12 @@ from tace_b200 import synth
 
 
 def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
-                targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False):
+                targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True):
     """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
     from oracle.model import build_oracle
 
     cfg = synth.model_config(L, C, cutoff, elements, avg, num_layers=num_layers, correlation=correlation,
-                             target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer)
+                             target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:

@@ -271,3 +271,10 @@ def test_read_out_on_every_layer(num_layers, Lmax, dtype):
     """readout_emlp.use_alllayer: layers below the last add a linear read-out of their scalar channels."""
     structs = synth.random_crystals(2, seed=41, nmin=4, nmax=9, zmax=3)
     run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, num_layers=num_layers, Lmax=Lmax, use_alllayer=True)
+
+
+@pytest.mark.parametrize("L,Lmax,dtype", [(2, None, torch.float64), (3, 2, torch.float64), (3, None, torch.float32)])
+def test_scalars_through_silu_instead_of_a_gate(L, Lmax, dtype):
+    """atomic_basis.gate_m0 = False: the e3nn Gate (scalars through SiLU, only ranks >= 1 gated)."""
+    structs = synth.random_crystals(2, seed=43, nmin=4, nmax=9, zmax=3)
+    run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, gate_m0=False)
