@@ -49,7 +49,7 @@ typedef struct {
   int num_layers;     /* >= 1 */
   int num_channel;    /* multiple of 32, <= 256 */
   int num_elements;   /* length of the sorted atomic-number list */
-  int correlation;    /* product-basis correlation order: 1 or 2 */
+  int correlation;    /* product-basis correlation order: 1, 2 or 3 */
   int num_bessel;     /* must be 8 */
   int mlp_hidden;     /* must be 64 (three hidden layers) */
   int envelope_p;     /* polynomial cutoff exponent (default 5) */
@@ -57,7 +57,7 @@ typedef struct {
   double cutoff;
   double avg_num_neighbors;
   int Lnode;          /* rank of the node features between layers (the reference's Lmax), 1..L; 0 means "same as L".
-                         Lnode < L needs correlation == 2 (tace/models/_e3nn/base.py:113-360) */
+                         Lnode < L needs correlation >= 2 (tace/models/_e3nn/base.py:113-360) */
   int use_alllayer;   /* readout_emlp.use_alllayer: every layer below the last adds a linear read-out of its scalar
                          channels (tace/models/_e3nn/readout.py:192-221); weights "ro.lin<t>" */
   int gate_m0_off;    /* 0: atomic_basis.gate_m0 = True (every rank, l = 0 included, scaled by a sigmoid gate; the

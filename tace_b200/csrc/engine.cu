@@ -58,6 +58,22 @@ bool pb_meta(int L, int Lout, PBMeta& m) {
   return false;
 }
 
+// third-order basis (correlation 3): L = rank of A, Lout as above
+bool pb3_meta(int L, int Lout, PBMeta& m) {
+#define PBM(TAG) { m = {PB3_##TAG::NP, PB3_##TAG::NB, pb3_##TAG##_k, pb3_##TAG##_base}; return true; }
+  if (L == 1 && Lout < 0) PBM(L1_T)
+  if (L == 1 && Lout == 1) PBM(L1_A)
+  if (L == 2 && Lout < 0) PBM(L2_T)
+  if (L == 2 && Lout == 1) PBM(L2_N1)
+  if (L == 2 && Lout == 2) PBM(L2_A)
+  if (L == 3 && Lout < 0) PBM(L3_T)
+  if (L == 3 && Lout == 1) PBM(L3_N1)
+  if (L == 3 && Lout == 2) PBM(L3_N2)
+  if (L == 3 && Lout == 3) PBM(L3_A)
+#undef PBM
+  return false;
+}
+
 struct WeightEntry {
   std::string name;
   long long numel;
@@ -68,7 +84,9 @@ struct WeightEntry {
 struct LayerPlan {
   bool scalar_src, last, has_res;
   TPMeta tp;
-  PBMeta pb;
+  PBMeta pb;                // second-order product basis (all ranks <= L when a third order follows)
+  PBMeta pb3;               // third-order product basis (correlation 3)
+  int pb_lout;              // output-rank argument of the second-order kernels
   int Din;                  // components per atom of the layer input (1 or D)
   int Dout;                 // components per atom of the layer output (D or 1)
   std::vector<int> in_ls;   // ranks present in the input
@@ -331,7 +349,11 @@ struct Model : ModelBase {
       p.scalar_src = (t == 0);
       p.last = (t == NL_ - 1);
       p.has_res = (t > 0);
-      if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !pb_meta(L, p.last ? -1 : Ln, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      const int lout = p.last ? -1 : Ln;
+      p.pb_lout = (c.correlation == 3) ? L : lout;  // with a third order the second keeps every rank (prod.py:216-266)
+      p.pb3 = PBMeta{0, 0, nullptr, nullptr};
+      if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !pb_meta(L, p.pb_lout, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      if (c.correlation == 3 && !pb3_meta(L, lout, p.pb3)) return TACE_ERR_UNSUPPORTED_CONFIG;
       p.Din = p.scalar_src ? 1 : Dn;
       p.Dout = p.last ? 1 : Dn;
       p.in_ls.clear(); p.out_ls.clear();
@@ -376,6 +398,10 @@ struct Model : ModelBase {
         if (cfg.correlation >= 2) {
           add_linear_weight(pre + "c1.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
           add_linear_weight(pre + "c1T.l" + ls, (long long)n_el * p.pb.k[i] * C * C);
+        }
+        if (cfg.correlation >= 3) {
+          add_linear_weight(pre + "c2.l" + ls, (long long)n_el * p.pb3.k[i] * C * C);
+          add_linear_weight(pre + "c2T.l" + ls, (long long)n_el * p.pb3.k[i] * C * C);
         }
         add_linear_weight(pre + "lin.l" + ls, (long long)C * C);
         add_linear_weight(pre + "linT.l" + ls, (long long)C * C);
@@ -430,6 +456,7 @@ struct Model : ModelBase {
     T *h_in, *x, *xx, *gxx, *W, *H3, *Z1, *Z2, *Z3, *Hact, *M, *Gt, *gGt, *a, *A, *B2, *out, *h_out;
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
     T *As, *gAs, *gout_s, *hs;  // species-sorted copies used by the per-species linears
+    T *B3, *gB2;                // third-order basis (reused for its gradient) and the gradient of the second-order one
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
@@ -492,6 +519,8 @@ struct Model : ModelBase {
       lb.A = ar.take<T>((size_t)NL * D * C);
       lb.gA = ar.take<T>((size_t)NL * D * C);
       lb.B2 = ar.take<T>((size_t)NL * p.pb.NB * C);
+      lb.B3 = cfg.correlation >= 3 ? ar.take<T>((size_t)NL * p.pb3.NB * C) : nullptr;
+      lb.gB2 = cfg.correlation >= 3 ? ar.take<T>((size_t)NL * p.pb.NB * C) : nullptr;
       lb.As = ar.take<T>((size_t)NL * D * C);
       lb.gAs = ar.take<T>((size_t)NL * D * C);
       lb.gout_s = ar.take<T>((size_t)NL * p.Dout * C);
@@ -844,7 +873,8 @@ struct Model : ModelBase {
       debug.push_back({"A" + ts, lb.A, NL * D * C});
       // per-species part in species-sorted space: gather A, product basis, coefficient linears scatter into `out`
       CKL(launch_gather_rows(lb.A, b.species_perm, lb.As, NL, D * C, s));
-      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.last ? -1 : Ln, C, s));
+      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.pb_lout, C, s));
+      if (cfg.correlation >= 3) CKL(launch_pb3_fwd(lb.As, lb.B2, lb.B3, (int)NL, L, p.last ? -1 : Ln, C, s));
       {
         std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
@@ -859,6 +889,16 @@ struct Model : ModelBase {
             const int K = p.pb.k[i] * C;
             sp.push_back({lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, 2 * l + 1, K, pre + "c1.l" + std::to_string(l),
                           pre + "c1T.l" + std::to_string(l), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, true, 1});
+          }
+          CKL(run_species_linear(sp, b, NL, s));
+        }
+        if (cfg.correlation >= 3) {
+          sp.clear();
+          for (size_t i = 0; i < p.out_ls.size(); ++i) {
+            const int l = p.out_ls[i];
+            const int K = p.pb3.k[i] * C;
+            sp.push_back({lb.B3 + (long long)p.pb3.base[i] * C, (long long)p.pb3.NB * C, K, 2 * l + 1, K, pre + "c2.l" + std::to_string(l),
+                          pre + "c2T.l" + std::to_string(l), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C, nullptr, true, 1});
           }
           CKL(run_species_linear(sp, b, NL, s));
         }
@@ -929,16 +969,34 @@ struct Model : ModelBase {
                         pre + "c0.l" + std::to_string(l), C, lb.gAs + (long long)l * l * C, (long long)D * C, C, nullptr, false, 0});
         CKL(run_species_linear(sp, b, NL, s));
         if (cfg.correlation >= 2) {
+          // gradient of the second-order basis: written over B2 itself, or into gB2 when the third order still needs B2
+          T* g2 = cfg.correlation >= 3 ? lb.gB2 : lb.B2;
+          if (cfg.correlation >= 3) {
+            CKL(launch_fill_zero(lb.gB2, NL * p.pb.NB * C, s));  // ranks above the output ranks only receive third-order terms
+            sp.clear();
+            for (size_t i = 0; i < p.out_ls.size(); ++i) {
+              const int l = p.out_ls[i];
+              const int K = p.pb3.k[i] * C;
+              sp.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "c2T.l" + std::to_string(l),
+                            pre + "c2.l" + std::to_string(l), K, lb.B3 + (long long)p.pb3.base[i] * C, (long long)p.pb3.NB * C, K,
+                            nullptr, false, 0});
+            }
+            CKL(run_species_linear(sp, b, NL, s));  // B3 now holds its gradient
+          }
           sp.clear();
           for (size_t i = 0; i < p.out_ls.size(); ++i) {
             const int l = p.out_ls[i];
             const int K = p.pb.k[i] * C;
             sp.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "c1T.l" + std::to_string(l),
-                          pre + "c1.l" + std::to_string(l), K, lb.B2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, nullptr,
+                          pre + "c1.l" + std::to_string(l), K, g2 + (long long)p.pb.base[i] * C, (long long)p.pb.NB * C, K, nullptr,
                           false, 0});
           }
           CKL(run_species_linear(sp, b, NL, s));
-          CKL(launch_pb_bwd(lb.As, lb.B2, lb.gAs, (int)NL, L, p.last ? -1 : Ln, C, s));  // B2 now holds its gradient
+          if (cfg.correlation >= 3) {
+            CKL(launch_pb3_bwd(lb.As, lb.B2, lb.B3, lb.gB2, lb.gAs, (int)NL, L, p.last ? -1 : Ln, C, s));
+            ++launches;
+          }
+          CKL(launch_pb_bwd(lb.As, g2, lb.gAs, (int)NL, L, p.pb_lout, C, s));
         }
       }
       CKL(launch_scatter_rows(lb.gAs, b.species_perm, lb.gA, NL, D * C, s));
@@ -1078,7 +1136,7 @@ int tace_create(const TaceConfig* cfg, TaceModel** out) {
   *out = nullptr;
   if (cfg->L < 1 || cfg->L > 3 || cfg->num_layers < 1 || cfg->num_layers > tace::kMaxLayers || cfg->num_channel < 32 ||
       cfg->num_channel > 256 || (cfg->num_channel & 31) || cfg->num_elements < 1 || cfg->correlation < 1 ||
-      cfg->correlation > 2 || cfg->num_bessel != tace::kNumBessel || cfg->mlp_hidden != tace::kHidden ||
+      cfg->correlation > 3 || cfg->num_bessel != tace::kNumBessel || cfg->mlp_hidden != tace::kHidden ||
       cfg->readout_hidden < 1 || cfg->readout_hidden > 64 || cfg->envelope_p < 2 || !(cfg->cutoff > 0.0) ||
       !(cfg->avg_num_neighbors > 0.0) || (cfg->dtype != TACE_F32 && cfg->dtype != TACE_F64))
     return TACE_ERR_UNSUPPORTED_CONFIG;

@@ -312,6 +312,71 @@ def gen_product(L, Lout, out):
     return dict(tag=tag, P=P, nb=lay.nm, nnz=nnz)
 
 
+def gen_product3(L, Lout, out):
+    """Third-order product basis B3 = (A x A) x A (correlation 3, tace/models/_e3nn/prod.py:216-266): the first factor
+    is the full second-order basis (every path of ranks <= L keeps its own slot, layout of PB_L{L}_A), the second is A,
+    outputs carry ranks 0..Lout (Lout < 0: scalars only).  B3 (593 components at L = 3) does not fit in registers, so
+    the forward code stores each component through a strided pointer and the backward pass comes as two functions,
+    one per operand, that read the gradient of B3 the same way."""
+    last = Lout < 0
+    tag = f"L{L}_" + ("T" if last else "A" if Lout == L else f"N{Lout}")
+    ls = list(range(L + 1))
+    outs = [0] if last else list(range(Lout + 1))
+    slots = tp_paths(L, ls, ls, ls)                 # second-order paths = slots of the first operand
+    lay2 = Layout(slots, ls)
+    paths = [(s, lb, l3) for l3 in outs for s, (_, _, lsl) in enumerate(slots) for lb in ls
+             if abs(lsl - lb) <= l3 <= lsl + lb and (lsl + lb + l3) % 2 == 0]
+    lay3 = Layout([(slots[s][2], lb, l3) for s, lb, l3 in paths], outs)
+    D = (L + 1) ** 2
+    o = out.append
+    nnz = sum(int(np.count_nonzero(w3j(slots[s][2], lb, l3))) for s, lb, l3 in paths)
+    o(f"// ---- third-order product basis ((A x A) x A), L={L}, {'scalar outputs' if last else f'output ranks <= {Lout}'}: "
+      f"{len(paths)} paths, {lay3.nm} components, {nnz} coupling non-zeros")
+    o(f"struct PB3_{tag} {{ static constexpr int L = {L}, NP = {len(paths)}, NB = {lay3.nm}, NB2 = {lay2.nm}, D = {D}; }};")
+    o(f"static const int pb3_{tag}_k[{len(outs)}] = {{{', '.join(str(lay3.k[l]) for l in outs)}}};")
+    o(f"static const int pb3_{tag}_base[{len(outs)}] = {{{', '.join(str(lay3.base[l]) for l in outs)}}};")
+    Ks = [w3j(slots[s][2], lb, l3) * math.sqrt(2 * l3 + 1) for s, lb, l3 in paths]
+    o(f"struct PB3X_{tag} : PB3_{tag} {{")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd(const T (&a)[{D}], const T (&b2)[{lay2.nm}], T* __restrict__ b3, long long stride) {{")
+    for p, (s, lb, l3) in enumerate(paths):
+        K, l1 = Ks[p], slots[s][2]
+        for m3 in range(2 * l3 + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * b2[{lay2.idx(s, m1)}] * a[{lb * lb + m2}]"
+                     for m1 in range(2 * l1 + 1) for m2 in range(2 * lb + 1) if K[m1, m2, m3] != 0.0]
+            o(f"    b3[{lay3.idx(p, m3)} * stride] = {' + '.join(terms) if terms else 'T(0)'};")
+    o("  }")
+    # gradient with respect to the second-order basis (accumulated into db2)
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd_b2(const T (&a)[{D}], const T* __restrict__ db3, long long stride, T (&db2)[{lay2.nm}]) {{")
+    for p, (s, lb, l3) in enumerate(paths):
+        K, l1 = Ks[p], slots[s][2]
+        o("    {")
+        for m3 in range(2 * l3 + 1):
+            o(f"      const T g{m3} = db3[{lay3.idx(p, m3)} * stride];")
+        for m1 in range(2 * l1 + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * a[{lb * lb + m2}] * g{m3}"
+                     for m2 in range(2 * lb + 1) for m3 in range(2 * l3 + 1) if K[m1, m2, m3] != 0.0]
+            if terms:
+                o(f"      db2[{lay2.idx(s, m1)}] += {' + '.join(terms)};")
+        o("    }")
+    o("  }")
+    # gradient with respect to A as the second operand (accumulated into da)
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd_a(const T (&b2)[{lay2.nm}], const T* __restrict__ db3, long long stride, T (&da)[{D}]) {{")
+    for p, (s, lb, l3) in enumerate(paths):
+        K, l1 = Ks[p], slots[s][2]
+        o("    {")
+        for m3 in range(2 * l3 + 1):
+            o(f"      const T g{m3} = db3[{lay3.idx(p, m3)} * stride];")
+        for m2 in range(2 * lb + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * b2[{lay2.idx(s, m1)}] * g{m3}"
+                     for m1 in range(2 * l1 + 1) for m3 in range(2 * l3 + 1) if K[m1, m2, m3] != 0.0]
+            if terms:
+                o(f"      da[{lb * lb + m2}] += {' + '.join(terms)};")
+        o("    }")
+    o("  }")
+    o("};")
+    return dict(tag="3:" + tag, P=len(paths), nb=lay3.nm, nnz=nnz)
+
+
 def main():
     out = [
         "// GENERATED by tace_b200/csrc/gen_tables.py -- do not edit by hand.",
@@ -328,6 +393,8 @@ def main():
             summary.append(gen_interaction(L, Lin, out))
         for Lout in [-1] + list(range(1, L + 1)):
             summary.append(gen_product(L, Lout, out))
+        for Lout in [-1] + list(range(1, L + 1)):
+            summary.append(gen_product3(L, Lout, out))
     out.append("}  // namespace tace")
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "tp_gen.cuh"), "w") as fh:

@@ -48,6 +48,11 @@ template <typename T> cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const
 // x0[n][c] = table[species[n]][c]
 template <typename T> cudaError_t launch_species_gather(const T* table, const int* species, T* out, int n, int C, cudaStream_t s);
 // gate (tace/models/_e3nn/nonlinear.py:125-135): Gt = [(L+1)C gates | D*C gated] per atom.
+// Third-order product basis (correlation 3): B3 = (A x A) x A with B2 the full second-order basis (ranks <= L).
+// launch_pb3_bwd adds the gradients into gB2 and gA.
+template <typename T> cudaError_t launch_pb3_fwd(const T* A, const T* B2, T* B3, int n, int L, int Lout, int C, cudaStream_t s);
+template <typename T> cudaError_t launch_pb3_bwd(const T* A, const T* B2, const T* gB3, T* gB2, T* gA, int n, int L, int Lout, int C,
+                                                 cudaStream_t s);
 // m0: 1 = every rank (l = 0 included) scaled by a sigmoid gate; 0 = scalars through the normalised SiLU, ranks >= 1 gated
 template <typename T> cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, int m0, cudaStream_t s);
 template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, int m0, cudaStream_t s);

@@ -213,6 +213,81 @@ cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int Lou
   TACE_PB_DISPATCH(pb_bwd_kernel, A, gB2, gA, n, C)
 }
 
+// ---- third-order product basis (correlation 3) ---------------------------------------------------
+// B3 = (A x A) x A per (atom, channel); B2 is the full second-order basis.  B3 is written / read through the
+// channel-strided column of the thread, so only A and B2 live in registers.
+template <typename T, typename PB3>
+__global__ void __launch_bounds__(128) pb3_fwd_kernel(const T* __restrict__ A, const T* __restrict__ B2, T* __restrict__ B3, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  T a[PB3::D], b2[PB3::NB2];
+#pragma unroll
+  for (int k = 0; k < PB3::D; ++k) a[k] = A[((long long)i * PB3::D + k) * C + c];
+#pragma unroll
+  for (int k = 0; k < PB3::NB2; ++k) b2[k] = B2[((long long)i * PB3::NB2 + k) * C + c];
+  PB3::template fwd<T>(a, b2, B3 + (long long)i * PB3::NB * C + c, C);
+}
+// gB2 += d(B3)/dB2^T gB3 (OPERAND 0) or gA += d(B3)/dA^T gB3 (OPERAND 1): two launches keep the register count down
+template <typename T, typename PB3, int OPERAND>
+__global__ void __launch_bounds__(128) pb3_bwd_kernel(const T* __restrict__ A, const T* __restrict__ B2, const T* __restrict__ gB3,
+                                                      T* __restrict__ gB2, T* __restrict__ gA, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  const T* g3 = gB3 + (long long)i * PB3::NB * C + c;
+  if constexpr (OPERAND == 0) {
+    T a[PB3::D], db2[PB3::NB2];
+#pragma unroll
+    for (int k = 0; k < PB3::D; ++k) a[k] = A[((long long)i * PB3::D + k) * C + c];
+    T* out = gB2 + (long long)i * PB3::NB2 * C + c;
+#pragma unroll
+    for (int k = 0; k < PB3::NB2; ++k) db2[k] = out[(long long)k * C];
+    PB3::template bwd_b2<T>(a, g3, C, db2);
+#pragma unroll
+    for (int k = 0; k < PB3::NB2; ++k) out[(long long)k * C] = db2[k];
+  } else {
+    T b2[PB3::NB2], da[PB3::D];
+#pragma unroll
+    for (int k = 0; k < PB3::NB2; ++k) b2[k] = B2[((long long)i * PB3::NB2 + k) * C + c];
+    T* out = gA + (long long)i * PB3::D * C + c;
+#pragma unroll
+    for (int k = 0; k < PB3::D; ++k) da[k] = out[(long long)k * C];
+    PB3::template bwd_a<T>(b2, g3, C, da);
+#pragma unroll
+    for (int k = 0; k < PB3::D; ++k) out[(long long)k * C] = da[k];
+  }
+}
+
+#define TACE_PB3_DISPATCH(LAUNCH)                                        \
+  if (n <= 0) return cudaSuccess;                                        \
+  const unsigned grid = (unsigned)(((long long)n * C + 127) / 128);      \
+  if (L == 1 && Lout < 0) { LAUNCH(PB3X_L1_T) }                          \
+  else if (L == 1 && Lout == 1) { LAUNCH(PB3X_L1_A) }                    \
+  else if (L == 2 && Lout < 0) { LAUNCH(PB3X_L2_T) }                     \
+  else if (L == 2 && Lout == 1) { LAUNCH(PB3X_L2_N1) }                   \
+  else if (L == 2 && Lout == 2) { LAUNCH(PB3X_L2_A) }                    \
+  else if (L == 3 && Lout < 0) { LAUNCH(PB3X_L3_T) }                     \
+  else if (L == 3 && Lout == 1) { LAUNCH(PB3X_L3_N1) }                   \
+  else if (L == 3 && Lout == 2) { LAUNCH(PB3X_L3_N2) }                   \
+  else if (L == 3 && Lout == 3) { LAUNCH(PB3X_L3_A) }                    \
+  else return cudaErrorInvalidValue;                                     \
+  return cudaGetLastError();
+
+template <typename T>
+cudaError_t launch_pb3_fwd(const T* A, const T* B2, T* B3, int n, int L, int Lout, int C, cudaStream_t s) {
+#define PB3_FWD(P) pb3_fwd_kernel<T, P><<<grid, 128, 0, s>>>(A, B2, B3, n, C);
+  TACE_PB3_DISPATCH(PB3_FWD)
+#undef PB3_FWD
+}
+template <typename T>
+cudaError_t launch_pb3_bwd(const T* A, const T* B2, const T* gB3, T* gB2, T* gA, int n, int L, int Lout, int C, cudaStream_t s) {
+#define PB3_BWD(P) pb3_bwd_kernel<T, P, 0><<<grid, 128, 0, s>>>(A, B2, gB3, gB2, gA, n, C); \
+                   pb3_bwd_kernel<T, P, 1><<<grid, 128, 0, s>>>(A, B2, gB3, gB2, gA, n, C);
+  TACE_PB3_DISPATCH(PB3_BWD)
+#undef PB3_BWD
+}
+
 // ---- read-out ------------------------------------------------------------------------------------
 template <typename T>
 __global__ void readout_kernel(const ReadoutArgs<T> a) {
@@ -308,6 +383,8 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
 
 #define INST(T)                                                                                               \
   template cudaError_t launch_fill_zero<T>(T*, long long, cudaStream_t);                                      \
+  template cudaError_t launch_pb3_fwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);           \
+  template cudaError_t launch_pb3_bwd<T>(const T*, const T*, const T*, T*, T*, int, int, int, int, cudaStream_t); \
   template cudaError_t launch_readout_linear_bwd<T>(T*, long long, const T*, const T*, int, int, cudaStream_t); \
   template cudaError_t launch_add_inplace<T>(T*, const T*, long long, cudaStream_t);                          \
   template cudaError_t launch_gather_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);         \

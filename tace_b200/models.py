@@ -125,8 +125,8 @@ def check_model_config(cfg: Dict) -> Dict:
     _require(all(t in ("cgtp", "spatial", "coupled") for t in cfg["product_basis"]["type"]), "product_basis.type == cgtp")
     _require(all(n == "sigmoid_gate" for n in cfg["atomic_basis"]["nonlinear"]), "atomic_basis.nonlinear == sigmoid_gate")
     corr = cfg["product_basis"]["correlation"]
-    _require(len(set(corr)) == 1 and corr[0] in (1, 2), "product_basis.correlation in {1, 2}, equal on all layers")
-    _require(corr[0] == 2 or cfg["Lmax"] == cfg["lmax"], "Lmax == lmax when product_basis.correlation == 1")
+    _require(len(set(corr)) == 1 and corr[0] in (1, 2, 3), "product_basis.correlation in {1, 2, 3}, equal on all layers")
+    _require(corr[0] >= 2 or cfg["Lmax"] == cfg["lmax"], "Lmax == lmax when product_basis.correlation == 1")
     return cfg
 
 

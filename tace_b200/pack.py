@@ -33,7 +33,7 @@ class LayerPlan:
     """``L``: rank of the angular features and of the atomic basis A (the reference's ``lmax``); ``Lnode``: rank of
     the node features between layers (``Lmax``), tace/models/_e3nn/base.py:113-360."""
 
-    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None):
+    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None, correlation: int = 2):
         Lnode = L if Lnode is None else Lnode
         self.t = t
         self.scalar_src = t == 0 or Lnode == 0
@@ -45,8 +45,15 @@ class LayerPlan:
         self.out_ls = [0] if self.last else node_ls
         self.tp_paths = tp_paths(self.in_ls, all_ls, all_ls)
         self.k = [sum(1 for p in self.tp_paths if p[2] == l) for l in all_ls]
-        self.pb_paths = tp_paths(all_ls, all_ls, self.out_ls)
+        # second-order product basis: with a third order behind it every rank <= L keeps its paths (each path is a
+        # slot of the next product), otherwise only the output ranks (tace/models/_e3nn/prod.py:216-266)
+        self.pb_paths = tp_paths(all_ls, all_ls, all_ls if correlation >= 3 else self.out_ls)
         self.kp = [sum(1 for p in self.pb_paths if p[2] == l) for l in self.out_ls]
+        self.pb3_paths = []
+        if correlation >= 3:
+            self.pb3_paths = [(s, lb, l3) for l3 in self.out_ls for s, (_, _, ls_) in enumerate(self.pb_paths) for lb in all_ls
+                              if abs(ls_ - lb) <= l3 <= ls_ + lb and (ls_ + lb + l3) % 2 == 0]
+        self.kp3 = [sum(1 for p in self.pb3_paths if p[2] == l) for l in self.out_ls]
 
 
 class ModelPlan:
@@ -58,7 +65,7 @@ class ModelPlan:
         self.use_alllayer = bool(use_alllayer)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
-        self.layers = [LayerPlan(t, num_layers, L, self.Lnode) for t in range(num_layers)]
+        self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation) for t in range(num_layers)]
 
     def parameter_shapes(self) -> Dict[str, tuple]:
         """Reference parameter names (without the ``readout_fn.`` prefix) and shapes."""
@@ -85,6 +92,9 @@ class ModelPlan:
             if self.correlation >= 2:
                 out[pp + "coefs.1.weight"] = (n_el, sum(kp * C * C for kp in lp.kp))
                 out[pp + "coefs.1.bias"] = (n_el, C)
+            if self.correlation >= 3:
+                out[pp + "coefs.2.weight"] = (n_el, sum(kp * C * C for kp in lp.kp3))
+                out[pp + "coefs.2.bias"] = (n_el, C)
             out[pp + "linear.weight"] = (len(lp.out_ls) * C * C,)
             out[pp + "linear.bias"] = (C,)
         # tace/models/_e3nn/readout.py:192-221: with use_alllayer every layer has a read-out (a single linear on
@@ -171,6 +181,10 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
             for l, kp, m in zip(lp.out_ls, lp.kp, split(g(pp + "coefs.1.weight"), [(kp * C, C) for kp in lp.kp])):
                 put(tp + f"c1.l{l}", m / math.sqrt(kp * C), tp + f"c1T.l{l}")
             bias = bias + g(pp + "coefs.1.bias")
+        if plan.correlation >= 3:
+            for l, kp, m in zip(lp.out_ls, lp.kp3, split(g(pp + "coefs.2.weight"), [(kp * C, C) for kp in lp.kp3])):
+                put(tp + f"c2.l{l}", m / math.sqrt(kp * C), tp + f"c2T.l{l}")
+            bias = bias + g(pp + "coefs.2.bias")
         out[tp + "c.b"] = bias
         for l, m in zip(lp.out_ls, split(g(pp + "linear.weight"), [(C, C)] * len(lp.out_ls))):
             put(tp + f"lin.l{l}", m / math.sqrt(C), tp + f"linT.l{l}")
@@ -182,11 +196,11 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
     # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
     for name in list(out):
         stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
-        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "res", "resT")
+        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT")
                 and name.split(".")[-1].startswith("l")) \
                 or stem in ("A1", "A1t", "A2", "A2t"):
             hi, lo = split_tf32(out[name])
-            if stem in ("c0", "c0T", "c1", "c1T", "res", "resT"):
+            if stem in ("c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT"):
                 # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,
                 # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
                 hi, lo = tile_k_major(hi), tile_k_major(lo)

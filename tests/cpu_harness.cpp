@@ -89,6 +89,36 @@ int h_pb(int L, int Lout, int mode, const double* a, const double* db, double* o
   return -1;
 }
 
+#define PB3_CASE(TAG)                                                                          \
+  {                                                                                            \
+    using P = PB3X_##TAG;                                                                      \
+    double aa[P::D], b2[P::NB2];                                                               \
+    memcpy(aa, a, sizeof aa); memcpy(b2, b2in, sizeof b2);                                     \
+    if (mode == 0) P::fwd<double>(aa, b2, out0, 1);                                            \
+    else {                                                                                     \
+      double db2[P::NB2], da[P::D];                                                            \
+      memset(db2, 0, sizeof db2); memset(da, 0, sizeof da);                                    \
+      P::bwd_b2<double>(aa, db3, 1, db2); P::bwd_a<double>(b2, db3, 1, da);                    \
+      memcpy(out0, db2, sizeof db2); memcpy(out1, da, sizeof da);                              \
+    }                                                                                          \
+    return P::NB;                                                                              \
+  }
+
+// Third-order basis: mode 0: out0 = (b2 x a); mode 1: out0 = d/db2, out1 = d/da from db3.  Returns the number of
+// third-order components.
+int h_pb3(int L, int Lout, int mode, const double* a, const double* b2in, const double* db3, double* out0, double* out1) {
+  if (L == 1 && Lout < 0) PB3_CASE(L1_T)
+  if (L == 1 && Lout == 1) PB3_CASE(L1_A)
+  if (L == 2 && Lout < 0) PB3_CASE(L2_T)
+  if (L == 2 && Lout == 1) PB3_CASE(L2_N1)
+  if (L == 2 && Lout == 2) PB3_CASE(L2_A)
+  if (L == 3 && Lout < 0) PB3_CASE(L3_T)
+  if (L == 3 && Lout == 1) PB3_CASE(L3_N1)
+  if (L == 3 && Lout == 2) PB3_CASE(L3_N2)
+  if (L == 3 && Lout == 3) PB3_CASE(L3_A)
+  return -1;
+}
+
 void h_sh(int L, const double* n, double* Y) {
   if (L == 1) { double y[4]; sh_eval<double, 1>(n[0], n[1], n[2], y); memcpy(Y, y, sizeof y); }
   if (L == 2) { double y[9]; sh_eval<double, 2>(n[0], n[1], n[2], y); memcpy(Y, y, sizeof y); }

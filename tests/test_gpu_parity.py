@@ -278,3 +278,11 @@ def test_scalars_through_silu_instead_of_a_gate(L, Lmax, dtype):
     """atomic_basis.gate_m0 = False: the e3nn Gate (scalars through SiLU, only ranks >= 1 gated)."""
     structs = synth.random_crystals(2, seed=43, nmin=4, nmax=9, zmax=3)
     run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, gate_m0=False)
+
+
+@pytest.mark.parametrize("L,Lmax,num_layers,dtype", [(2, None, 2, torch.float64), (3, 2, 2, torch.float64), (1, None, 3, torch.float64),
+                                                      (3, None, 2, torch.float32)])
+def test_correlation_three(L, Lmax, num_layers, dtype):
+    """product_basis.correlation = 3: B = W1 A + W2 (A x A) + W3 ((A x A) x A)."""
+    structs = synth.random_crystals(2, seed=47, nmin=4, nmax=8, zmax=3)
+    run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, num_layers=num_layers, correlation=3)

@@ -103,6 +103,49 @@ def test_product_basis_matches_oracle(cpu_harness, L, Lout):
     np.testing.assert_allclose(da, da_ref.numpy(), rtol=0, atol=1e-12)
 
 
+@pytest.mark.parametrize("L,Lout", RANK_PAIRS)
+def test_third_order_product_basis_matches_oracle(cpu_harness, L, Lout):
+    """(A x A) x A of correlation 3: values against the oracle's tensor product, both gradients against autograd."""
+    torch.manual_seed(20 + L)
+    D = (L + 1) ** 2
+    ls = list(range(L + 1))
+    outs = [0] if Lout < 0 else list(range(Lout + 1))
+    irr = o3.Irreps([(1, l) for l in ls])
+    paths2, out2 = om.generate_paths(irr, irr, irr, "uuu", identical_inputs=True)       # every rank keeps its slots
+    paths3, out3 = om.generate_paths(o3.Irreps([(1, l) for l in outs]), out2, irr, "uuu")
+    tp3 = om.TensorProduct(out2, irr, out3, paths3)
+    _, idx2, nb2 = paths_and_layout(L, ls, ls)
+    perm2 = [i for blk in idx2 for i in blk]                                            # oracle order -> slot layout
+    # layout of the third-order output: [l3][m3][path], paths in oracle order
+    l3_of = [l for _, l in out3]
+    k = {l: l3_of.count(l) for l in outs}
+    base, acc = {}, 0
+    for l in outs:
+        base[l] = acc
+        acc += (2 * l + 1) * k[l]
+    cnt, perm3 = {l: 0 for l in outs}, []
+    for l in l3_of:
+        perm3 += [base[l] + m * k[l] + cnt[l] for m in range(2 * l + 1)]
+        cnt[l] += 1
+    a = torch.randn(D, dtype=torch.float64, requires_grad=True)
+    b2_oracle = torch.randn(nb2, dtype=torch.float64, requires_grad=True)
+    ref = tp3(b2_oracle[None], a[None])[0]
+    b2_mine = np.zeros(nb2)
+    b2_mine[perm2] = b2_oracle.detach().numpy()
+    b3 = np.zeros(acc)
+    z = np.zeros(max(acc, nb2, D))
+    assert cpu_harness.h_pb3(L, Lout, 0, ptr(a.detach().numpy()), ptr(b2_mine), ptr(z), ptr(b3), ptr(z)) == acc
+    np.testing.assert_allclose(b3[perm3], ref.detach().numpy(), rtol=0, atol=1e-13)
+    g_ref = torch.randn(acc, dtype=torch.float64)
+    db2_ref, da_ref = torch.autograd.grad(ref, [b2_oracle, a], g_ref)
+    g_mine = np.zeros(acc)
+    g_mine[perm3] = g_ref.numpy()
+    db2, da = np.zeros(nb2), np.zeros(D)
+    cpu_harness.h_pb3(L, Lout, 1, ptr(a.detach().numpy()), ptr(b2_mine), ptr(g_mine), ptr(db2), ptr(da))
+    np.testing.assert_allclose(db2[perm2], db2_ref.numpy(), rtol=0, atol=1e-12)
+    np.testing.assert_allclose(da, da_ref.numpy(), rtol=0, atol=1e-12)
+
+
 @pytest.mark.parametrize("L", [1, 2, 3])
 def test_spherical_harmonics_and_gradient(cpu_harness, L):
     torch.manual_seed(L)
