@@ -62,6 +62,12 @@ typedef struct {
                          channels (tace/models/_e3nn/readout.py:192-221); weights "ro.lin<t>" */
   int gate_m0_off;    /* 0: atomic_basis.gate_m0 = True (every rank, l = 0 included, scaled by a sigmoid gate; the
                          reference default); 1: gate_m0 = False (scalars through SiLU, ranks >= 1 gated; nonlinear.py:43-70) */
+  int mlp_layers;     /* hidden layers of the radial MLP (radial_basis.hidden, all 64 wide): 1..3; 0 means 3 */
+  int mlp_bias;       /* radial_basis.bias: every layer of the radial MLP has a bias ("t<i>.b0".."b3") */
+  int env_after_mlp;  /* radial_basis.apply_cutoff = False: the polynomial envelope multiplies the output of the radial MLP
+                         instead of the radial basis (tace/models/radial.py:974-993, _e3nn/inter.py:174-183) */
+  int edge_update_element2; /* edge_update.type = element2: species embeddings of target and source are appended to the
+                         radial features (tace/models/_e3nn/edge.py:190-257); folded into the tables "t<i>.tdst" / "tsrc" */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

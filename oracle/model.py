@@ -149,24 +149,29 @@ class TensorProduct(torch.nn.Module):
 class MlpLinear(torch.nn.Module):
     """tace/models/linear.py:247-279."""
 
-    def __init__(self, in_dim: int, out_dim: int, alpha: float):
+    def __init__(self, in_dim: int, out_dim: int, alpha: float, bias: bool = False):
         super().__init__()
         self.alpha = alpha
         self.weight = torch.nn.Parameter(torch.empty(in_dim, out_dim).uniform_(-math.sqrt(3), math.sqrt(3)))
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(out_dim))
+        else:
+            self.register_parameter("bias", None)
 
     def forward(self, x):
-        return torch.mm(x, self.weight * self.alpha)
+        y = torch.mm(x, self.weight * self.alpha)
+        return y if self.bias is None else y + self.bias
 
 
 class MLP(torch.nn.Module):
-    """tace/models/mlp.py:136-191 (no bias, plain SiLU, gain sqrt(2) after layer 0)."""
+    """tace/models/mlp.py:136-191 (plain SiLU, gain sqrt(2) after layer 0, optional bias on every layer)."""
 
-    def __init__(self, dims: List[int]):
+    def __init__(self, dims: List[int], bias: bool = False):
         super().__init__()
         mods = []
         for layer, (a, b) in enumerate(zip(dims, dims[1:])):
             gain = 1.0 if layer == 0 else math.sqrt(2.0)
-            mods.append(MlpLinear(a, b, gain / math.sqrt(a)))
+            mods.append(MlpLinear(a, b, gain / math.sqrt(a), bias=bias))
             if layer != len(dims) - 2:
                 mods.append(torch.nn.SiLU())
         self.mlp = torch.nn.Sequential(*mods)
@@ -269,16 +274,35 @@ class C2Poly(torch.nn.Module):
 
 
 class RadialBasis(torch.nn.Module):
-    """tace/models/radial.py:877-993, default options (apply_cutoff=True)."""
+    """tace/models/radial.py:877-993: returns (radial features, envelope or None); with apply_cutoff the envelope is
+    already in the features, otherwise the caller multiplies the radial MLP's output by it (:987-993)."""
 
-    def __init__(self, cutoff, num_basis, p):
+    def __init__(self, cutoff, num_basis, p, apply_cutoff=True):
         super().__init__()
         self.cutoff_fn = C2Poly(cutoff, p)
         self.radial_fn = J0Bessel(cutoff, num_basis)
         self.num_basis = num_basis
+        self.apply_cutoff = apply_cutoff
 
     def forward(self, edge_length):
-        return self.radial_fn(edge_length) * self.cutoff_fn(edge_length)
+        env = self.cutoff_fn(edge_length)
+        radial = self.radial_fn(edge_length)
+        return (radial * env, None) if self.apply_cutoff else (radial, env)
+
+
+class Element2EdgeUpdate(torch.nn.Module):
+    """tace/models/_e3nn/edge.py:190-257: radial features followed by the species embeddings of the target and
+    of the source (in that order; ``ElementEdgeUpdate`` has them the other way round)."""
+
+    def __init__(self, num_elements, num_channel):
+        super().__init__()
+        irr_in, irr_out = Irreps([(num_elements, 0)]), Irreps([(num_channel, 0)])
+        self.source_embedding = Linear(irr_in, irr_out, bias=False)
+        self.target_embedding = Linear(irr_in, irr_out, bias=False)
+
+    def forward(self, node_attrs, edge_feats, edge_index):
+        return torch.cat([edge_feats, self.target_embedding(node_attrs[edge_index[1]]),
+                          self.source_embedding(node_attrs[edge_index[0]])], dim=-1)
 
 
 class NodeEmbedding(torch.nn.Module):
@@ -298,7 +322,7 @@ class Interaction(torch.nn.Module):
     tace/models/_e3nn/base.py:113-249."""
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
-                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True):
+                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
         C = num_channel
@@ -318,14 +342,16 @@ class Interaction(torch.nn.Module):
         self.nonlinearity = gate_cls(Irreps([(C, l) for _, l in self.irreps_out]))
         self.linear_nonlinearity = Linear(self.nonlinearity.irreps_out, self.irreps_out, bias=True)
         self.linear_down = Linear(tp_irreps_out.simplify(), self.nonlinearity.irreps_in, bias=True)
-        self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel])
+        self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel], bias=mlp_bias)
         if layer > 0:  # resnet type "BB", linear_type "aware", use_first_resnet False
             self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True, num_elements=num_elements)
 
-    def forward(self, node_feats, node_attrs, edge_feats, edge_attrs, edge_index):
+    def forward(self, node_feats, node_attrs, edge_feats, edge_attrs, edge_index, edge_cutoff=None):
         sc = self.resnetBB(node_feats, node_attrs) if hasattr(self, "resnetBB") else None
         x = self.linear_up(node_feats)
         w = self.edge_info(edge_feats)
+        if edge_cutoff is not None:  # inter.py:174-183
+            w = w * edge_cutoff
         msg = self.rejector(x[edge_index[0]], edge_attrs, w)  # tace/models/_e3nn/fused.py:269-271
         m = scatter_sum(msg, edge_index[1], x.shape[0])
         m = self.linear_down(m)
@@ -397,7 +423,12 @@ class Representation(torch.nn.Module):
         rb = cfg["radial_basis"]
         self.lmax = l
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
-        self.radial_basis = RadialBasis(cfg["cutoff"], rb["num_radial_basis"], rb["polynomial_cutoff"])
+        self.radial_basis = RadialBasis(cfg["cutoff"], rb["num_radial_basis"], rb["polynomial_cutoff"],
+                                        apply_cutoff=rb.get("apply_cutoff", True))
+        self.element2 = cfg.get("edge_update", {}).get("type", "identity") == "element2"
+        if self.element2:
+            self.edge_updates = torch.nn.ModuleList([Element2EdgeUpdate(n_el, C) for _ in range(cfg["num_layers"])])
+        edge_dim = rb["num_radial_basis"] + (2 * C if self.element2 else 0)
         self.node_embedding = NodeEmbedding(n_el, C)
         self.interactions = torch.nn.ModuleList()
         self.products = torch.nn.ModuleList()
@@ -405,8 +436,9 @@ class Representation(torch.nn.Module):
             irreps_in = self.node_embedding.irreps_out if layer == 0 else self.products[layer - 1].irreps_out
             self.interactions.append(
                 Interaction(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
-                            cfg["product_basis"]["correlation"][layer], C, rb["num_radial_basis"], rb["hidden"],
-                            irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True))
+                            cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
+                            irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True),
+                            mlp_bias=rb.get("bias", False))
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],
@@ -414,12 +446,13 @@ class Representation(torch.nn.Module):
             )
 
     def forward(self, node_attrs, edge_index, edge_vector, edge_length):
-        edge_feats = self.radial_basis(edge_length)  # identity edge embedding / update
+        edge_feats, edge_cutoff = self.radial_basis(edge_length)  # identity edge embedding
         edge_attrs = o3.spherical_harmonics(self.lmax, edge_vector / edge_length, "component")
         h = self.node_embedding(node_attrs)
         descriptors = []
         for inter, prod in zip(self.interactions, self.products):
-            h, sc = inter(h, node_attrs, edge_feats, edge_attrs, edge_index)
+            ef = self.edge_updates[len(descriptors)](node_attrs, edge_feats, edge_index) if self.element2 else edge_feats
+            h, sc = inter(h, node_attrs, ef, edge_attrs, edge_index, edge_cutoff)
             h = prod(h, node_attrs, sc)
             descriptors.append(h)
         return descriptors
@@ -490,7 +523,9 @@ def resolve_config(user_cfg: Dict) -> Dict:
     """The subset of tace/models/_e3nn/default.py:10-177,231-316 this path uses."""
     cfg = {
         "Lmax": 2, "lmax": 3, "num_channel": 64, "num_layers": 2,
-        "radial_basis": {"num_radial_basis": 8, "polynomial_cutoff": 5, "hidden": [64, 64, 64]},
+        "radial_basis": {"num_radial_basis": 8, "polynomial_cutoff": 5, "hidden": [64, 64, 64], "bias": False,
+                         "apply_cutoff": True},
+        "edge_update": {"type": "identity"},
         "product_basis": {"correlation": 2},
         "readout_emlp": {"hidden": [16], "use_alllayer": False},
         "scale_shift": {"scale_type": "rms_forces", "shift_type": None},

@@ -41,6 +41,11 @@ __global__ void __launch_bounds__(128) edge_fwd_kernel(const EdgeArgs<T> a) {
 #pragma unroll
   for (int k = 0; k < D; ++k) a.Y[e * D + k] = Y[k];
   a.dlen[e] = d;
+  if (a.env) {
+    T u, du;
+    envelope_eval<T>(d, a.rp, u, du);
+    a.env[e] = u;
+  }
 }
 
 // First layer of every radial MLP (8 -> 64, no activation yet): z1 = b(d) @ A0.  One thread per edge; the
@@ -58,7 +63,13 @@ __global__ void __launch_bounds__(128) edge_mlp_in_kernel(const EdgeArgs<T> a) {
     T z[kHidden];
     if (live) {
 #pragma unroll
-      for (int j = 0; j < kHidden; ++j) z[j] = T(0);
+      for (int j = 0; j < kHidden; ++j) z[j] = a.mlp[t].b0 ? a.mlp[t].b0[j] : T(0);
+      if (a.mlp[t].tbl_dst) {  // species rows of the element-dependent edge update
+        const T* rd = a.mlp[t].tbl_dst + (long long)a.species[a.e_dst[e]] * kHidden;
+        const T* rs = a.mlp[t].tbl_src + (long long)a.species[a.e_src[e]] * kHidden;
+#pragma unroll
+        for (int j = 0; j < kHidden; ++j) z[j] += rd[j] + rs[j];
+      }
 #pragma unroll
       for (int k = 0; k < kNumBessel; ++k)
 #pragma unroll
@@ -112,6 +123,11 @@ __global__ void __launch_bounds__(128) edge_mlp_out_kernel(const EdgeArgs<T> a) 
     }
 #pragma unroll
     for (int k = 0; k < kNumBessel; ++k) dd += db[k] * dbdd[k];
+  }
+  if (a.denv && a.add_denv) {  // W = envelope * MLP: the envelope's own derivative
+    T u, du;
+    envelope_eval<T>(a.dlen[e], a.rp, u, du);
+    dd += a.denv[e] * du;
   }
   a.ddlen[e] = a.accumulate_ddlen ? a.ddlen[e] + dd : dd;
 }

@@ -305,6 +305,10 @@ struct ModelBase {
 template <typename T>
 struct Model : ModelBase {
   int L, Ln, D, C, NL_, n_el, H;
+  int nh = 3;                 // hidden layers of the radial MLP (radial_basis.hidden)
+  bool mlp_bias = false;      // radial_basis.bias
+  bool env_after = false;     // radial_basis.apply_cutoff = False: envelope multiplies the MLP output
+  bool element2 = false;      // edge_update.type = element2
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -340,6 +344,9 @@ struct Model : ModelBase {
     cfg = c;
     L = c.L; D = (L + 1) * (L + 1); C = c.num_channel; NL_ = c.num_layers; n_el = c.num_elements; H = c.readout_hidden;
     m0 = c.gate_m0_off ? 0 : 1;
+    nh = (c.mlp_layers > 0) ? c.mlp_layers : 3;  // hidden layers of the radial MLP
+    if (nh < 1 || nh > 3) return TACE_ERR_UNSUPPORTED_CONFIG;
+    mlp_bias = c.mlp_bias != 0; env_after = c.env_after_mlp != 0; element2 = c.edge_update_element2 != 0;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     const int Dn = (Ln + 1) * (Ln + 1);
@@ -369,10 +376,15 @@ struct Model : ModelBase {
       for (int l : p.in_ls) { add_linear_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_linear_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
       add_weight(pre + "up.b", C);
       add_weight(pre + "A0", kNumBessel * kHidden);
-      add_linear_weight(pre + "A1", kHidden * kHidden);
-      add_linear_weight(pre + "A2", kHidden * kHidden);
-      add_linear_weight(pre + "A1t", kHidden * kHidden);
-      add_linear_weight(pre + "A2t", kHidden * kHidden);
+      if (nh >= 2) { add_linear_weight(pre + "A1", kHidden * kHidden); add_linear_weight(pre + "A1t", kHidden * kHidden); }
+      if (nh >= 3) { add_linear_weight(pre + "A2", kHidden * kHidden); add_linear_weight(pre + "A2t", kHidden * kHidden); }
+      if (mlp_bias) {
+        add_weight(pre + "b0", kHidden);
+        if (nh >= 2) add_weight(pre + "b1", kHidden);
+        if (nh >= 3) add_weight(pre + "b2", kHidden);
+        add_weight(pre + "b3", (long long)p.tp.NP * C);
+      }
+      if (element2) { add_weight(pre + "tdst", (long long)n_el * kHidden); add_weight(pre + "tsrc", (long long)n_el * kHidden); }
       add_weight(pre + "W3", (long long)kHidden * p.tp.NP * C);
       add_weight(pre + "W3t", (long long)kHidden * p.tp.NP * C);
       if (kTensorCore) {  // TF32 high parts and residuals of both orientations
@@ -463,7 +475,7 @@ struct Model : ModelBase {
     int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor, *env, *denv;
     std::vector<LayerBufs> lay;
   };
 
@@ -477,6 +489,7 @@ struct Model : ModelBase {
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL);
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
+    b.env = env_after ? ar.take<T>(E) : nullptr; b.denv = env_after ? ar.take<T>(E) : nullptr;
     const bool chunked = E > max_chunk_edges;
     b.n_chunks = chunked ? (int)((E + max_chunk_edges - 1) / max_chunk_edges) : 1;
     b.chunk_rows = chunked ? max_chunk_edges + kChunkSlack : E;
@@ -644,13 +657,18 @@ struct Model : ModelBase {
   EdgeArgs<T> edge_range(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec) const {
     EdgeArgs<T> r = ea;
     r.E = Ec; r.n_layers = (int)ts.size(); r.dlen = ea.dlen + e0; r.ddlen = ea.ddlen + e0;
+    r.e_src = ea.e_src + e0; r.e_dst = ea.e_dst + e0;
+    if (ea.env) r.env = ea.env + e0;
+    if (ea.denv) r.denv = ea.denv + e0;
     for (size_t i = 0; i < ts.size(); ++i) {
       r.mlp[i] = ea.mlp[ts[i]];
       r.Z1[i] = b.lay[ts[i]].Z1;
-      r.dH1[i] = b.lay[ts[i]].Z3;  // the backward pass reuses the third pre-activation buffer for dE/dh1
+      r.dH1[i] = dh1_buffer(b.lay[ts[i]]);
     }
     return r;
   }
+  // where the backward pass leaves dE/d(first hidden activation): it ping-pongs through the activation buffers
+  T* dh1_buffer(const LayerBufs& lb) const { return nh == 3 ? lb.Z3 : nh == 2 ? lb.Hact : lb.H3; }
   // radial MLP hidden layers 8 -> 64 -> 64 -> 64 (tace/models/mlp.py:136-191): the first layer per edge, the
   // two 64 x 64 layers as GEMMs over the edges (all layers of `ts` in one launch), SiLU in between
   int radial_forward(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec, cudaStream_t s) {
@@ -658,21 +676,23 @@ struct Model : ModelBase {
     const EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
     CKL(launch_edge_mlp_in(er, s));
     const long long n64 = Ec * kHidden;
-    for (int t : ts) CKL(launch_silu(b.lay[t].Z1, b.lay[t].Hact, n64, s));
-    std::vector<LinSpec> sp;
-    for (int t : ts) {
-      const std::string pre = "t" + std::to_string(t) + ".";
-      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1", pre + "A1t", kHidden, b.lay[t].Z2, kHidden, 0, nullptr});
+    for (int j = 0; j < nh; ++j) {  // hidden layer j: activation, then (unless it is the last) the next 64 x 64 layer
+      const bool last_hidden = (j == nh - 1);
+      for (int t : ts) {
+        const LayerBufs& lb = b.lay[t];
+        const T* z = j == 0 ? lb.Z1 : j == 1 ? lb.Z2 : lb.Z3;
+        CKL(launch_silu(z, last_hidden ? lb.H3 : lb.Hact, n64, s));
+      }
+      if (last_hidden) break;
+      std::vector<LinSpec> sp;
+      for (int t : ts) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        const std::string an = j == 0 ? "A1" : "A2";
+        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + an, pre + an + "t", kHidden, j == 0 ? b.lay[t].Z2 : b.lay[t].Z3, kHidden,
+                      0, mlp_bias ? w(pre + (j == 0 ? "b1" : "b2")) : nullptr});
+      }
+      CKL(run_linear(sp, Ec, s));
     }
-    CKL(run_linear(sp, Ec, s));
-    for (int t : ts) CKL(launch_silu(b.lay[t].Z2, b.lay[t].Hact, n64, s));
-    sp.clear();
-    for (int t : ts) {
-      const std::string pre = "t" + std::to_string(t) + ".";
-      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A2", pre + "A2t", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
-    }
-    CKL(run_linear(sp, Ec, s));
-    for (int t : ts) CKL(launch_silu(b.lay[t].Z3, b.lay[t].H3, n64, s));
     return TACE_OK;
   }
   // back through the hidden layers: lay[t].H3 holds dE/dh3 on entry; ddlen receives dE/d(edge length)
@@ -680,22 +700,29 @@ struct Model : ModelBase {
                       cudaStream_t s) {
     if (Ec <= 0) return TACE_OK;
     const long long n64 = Ec * kHidden;
-    for (int t : ts) CKL(launch_silu_grad_mul(b.lay[t].H3, b.lay[t].Z3, n64, s));
-    std::vector<LinSpec> sp;
-    for (int t : ts) {
-      const std::string pre = "t" + std::to_string(t) + ".";
-      sp.push_back({b.lay[t].H3, kHidden, 0, 1, kHidden, pre + "A2t", pre + "A2", kHidden, b.lay[t].Hact, kHidden, 0, nullptr});
+    // gradient buffer chain: H3 -> Hact -> Z3 (three hidden layers), H3 -> Hact (two), H3 (one); the first layer's
+    // activation derivative is applied by launch_edge_mlp_out
+    for (int j = nh - 1; j >= 1; --j) {
+      for (int t : ts) {
+        const LayerBufs& lb = b.lay[t];
+        T* g = (j == nh - 1) ? lb.H3 : lb.Hact;
+        CKL(launch_silu_grad_mul(g, j == 1 ? lb.Z2 : lb.Z3, n64, s));
+      }
+      std::vector<LinSpec> sp;
+      for (int t : ts) {
+        const std::string pre = "t" + std::to_string(t) + ".";
+        const std::string an = j == 1 ? "A1" : "A2";
+        const LayerBufs& lb = b.lay[t];
+        const T* g = (j == nh - 1) ? lb.H3 : lb.Hact;
+        T* dst = (j == nh - 1) ? lb.Hact : lb.Z3;
+        sp.push_back({g, kHidden, 0, 1, kHidden, pre + an + "t", pre + an, kHidden, dst, kHidden, 0, nullptr});
+      }
+      CKL(run_linear(sp, Ec, s));
     }
-    CKL(run_linear(sp, Ec, s));
-    for (int t : ts) CKL(launch_silu_grad_mul(b.lay[t].Hact, b.lay[t].Z2, n64, s));
-    sp.clear();
-    for (int t : ts) {
-      const std::string pre = "t" + std::to_string(t) + ".";
-      sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + "A1t", pre + "A1", kHidden, b.lay[t].Z3, kHidden, 0, nullptr});
-    }
-    CKL(run_linear(sp, Ec, s));
     EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
     er.accumulate_ddlen = accumulate;
+    // the envelope term enters once: with the whole batch in one call, or with the last layer processed (layer 0)
+    er.add_denv = (ts.size() > 1 || NL_ == 1 || ts[0] == 0) ? 1 : 0;
     CKL(launch_edge_mlp_out(er, s));
     return TACE_OK;
   }
@@ -707,14 +734,15 @@ struct Model : ModelBase {
       if (!backward)
         CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.H3), kHidden, reinterpret_cast<const float*>(w(pre + "W3t_hi")),
                            reinterpret_cast<const float*>(w(pre + "W3t_lo")), reinterpret_cast<float*>(lb.W), (long long)NW, (int)Ec,
-                           NW, kHidden, dev_error, s));
+                           NW, kHidden, dev_error, s, mlp_bias ? reinterpret_cast<const float*>(w(pre + "b3")) : nullptr));
       else
         CKL(launch_tc_gemm(reinterpret_cast<const float*>(lb.W), (long long)NW, reinterpret_cast<const float*>(w(pre + "W3_hi")),
                            reinterpret_cast<const float*>(w(pre + "W3_lo")), reinterpret_cast<float*>(lb.H3), kHidden, (int)Ec,
                            kHidden, NW, dev_error, s));
     } else {
       GemmBatch<T> gb = plain_batch(Ec);
-      if (!backward) add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), NW, lb.W, (long long)NW, 0, nullptr, 0);
+      if (!backward) add_problem(gb, lb.H3, kHidden, 0, 1, kHidden, w(pre + "W3"), NW, lb.W, (long long)NW, 0,
+                                 mlp_bias ? w(pre + "b3") : nullptr, 0);
       else add_problem(gb, lb.W, (long long)NW, 0, 1, NW, w(pre + "W3t"), kHidden, lb.H3, kHidden, 0, nullptr, 0);
       CKL(launch_gemm(gb, Ec, s));
     }
@@ -789,10 +817,16 @@ struct Model : ModelBase {
     }
     for (int t = 0; t < NL_; ++t) {
       const std::string pre = "t" + std::to_string(t) + ".";
-      ea.mlp[t] = {w(pre + "A0"), w(pre + "A1"), w(pre + "A2"), w(pre + "A1t"), w(pre + "A2t")};
+      memset(&ea.mlp[t], 0, sizeof(ea.mlp[t]));
+      ea.mlp[t].A0 = w(pre + "A0");
+      if (mlp_bias) ea.mlp[t].b0 = w(pre + "b0");
+      if (element2) { ea.mlp[t].tbl_dst = w(pre + "tdst"); ea.mlp[t].tbl_src = w(pre + "tsrc"); }
       ea.Z1[t] = b.lay[t].Z1;
-      ea.dH1[t] = b.lay[t].Z3;  // the backward pass reuses the third pre-activation buffer for dE/dh1
+      ea.dH1[t] = dh1_buffer(b.lay[t]);
     }
+    ea.rp.env_after_mlp = env_after ? 1 : 0;
+    ea.species = bt->species;
+    ea.env = b.env; ea.denv = b.denv; ea.add_denv = 1;
     ea.dlen = b.dlen; ea.ddlen = b.ddlen;
     ea.vec = b.vec; ea.Y = b.Y; ea.dY = b.dY; ea.g = b.g; ea.edge_forces = static_cast<T*>(o->edge_forces);
     CKL(launch_edge_fwd(ea, s));
@@ -844,6 +878,7 @@ struct Model : ModelBase {
         memset(&ta, 0, sizeof(ta));
         ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
         ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M + (long long)a0 * p.tp.NM * C; ta.e_base = e0;
+        ta.env = b.env;
         CKL(launch_tp_fwd(ta, s));
       }
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
@@ -1038,6 +1073,7 @@ struct Model : ModelBase {
         ta.W = lb.W; ta.x = lb.xx ? lb.xx : lb.x; ta.gM = lb.M + (long long)a0 * p.tp.NM * C; ta.n_seg = na;
         ta.rowptr = b.rowptr_dst + a0; ta.dW = lb.W; ta.dY = b.dY; ta.e_base = e0;
         ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
+        ta.env = b.env; ta.denv = b.denv; ta.accumulate_denv = (t != NL_ - 1);
         CKL(launch_tp_bwd(ta, s));
         if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
           PH(("t" + ts + ".bwd.src_sum").c_str());

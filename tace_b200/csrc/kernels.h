@@ -31,6 +31,11 @@ struct TPArgs {
   T* dY;              // backward output [E][D]
   int accumulate_dY;  // add into dY instead of overwriting
   T* dxe;             // backward output [E][NX][C]: per-edge gradient of the source features (full source only)
+  // radial_basis.apply_cutoff = False: the path weights are env[e] * W[e, :]; the backward pass stores env[e] * dW and
+  // the per-edge sum of dW * W (gradient with respect to the envelope) in denv
+  const T* env;       // [E] or nullptr
+  T* denv;            // [E] or nullptr
+  int accumulate_denv;
   long long e_base;   // W, dW and dxe hold the rows of edges [e_base, ...) only (edge-chunked passes); Y, dY, e_src are whole
 };
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
@@ -99,6 +104,10 @@ template <typename T> cudaError_t launch_add_inplace(T* dst, const T* src, long 
 template <typename T>
 struct MlpWeights {
   const T* A0; const T* A1; const T* A2; const T* A1t; const T* A2t;
+  const T* b0;       // [64] bias of the first layer, or nullptr
+  // edge_update "element2" (tace/models/_e3nn/edge.py:237-257): the species embeddings of both ends are concatenated to
+  // the radial features, i.e. they add a species-dependent row to the first pre-activation: tables [n_el][64] or nullptr
+  const T* tbl_dst; const T* tbl_src;
 };
 template <typename T>
 struct EdgeArgs {
@@ -119,6 +128,10 @@ struct EdgeArgs {
   T* Z1[kMaxLayers];     // [E][64] pre-activation of the first hidden layer of each layer's radial MLP
   const T* dH1[kMaxLayers];  // [E][64] gradient of the first hidden activation (backward)
   int accumulate_ddlen;  // launch_edge_mlp_out adds into ddlen instead of overwriting (layer-by-layer passes)
+  const int* species;    // [N] (element-dependent edge update), or nullptr
+  T* env;                // [E] envelope values, written by launch_edge_fwd when the cutoff is applied after the MLP
+  const T* denv;         // [E] dE/d(envelope) from the tensor-product backward passes (same case), or nullptr
+  int add_denv;          // this launch_edge_mlp_out call adds the envelope term to ddlen
   // backward
   const T* dY;           // [E][D]
   T* g;                  // [E][3] dE/d(edge vector), target-sorted order
@@ -200,5 +213,5 @@ struct TcLinearProblem {
 bool tc_linear_supported(int N, int K);
 cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s);
 cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
-                           int N, int K, int* error_flag, cudaStream_t s);
+                           int N, int K, int* error_flag, cudaStream_t s, const float* bias = nullptr);
 }  // namespace tace

@@ -105,15 +105,16 @@ struct RadialParams {
   T pref;
   T rc;
   int p;  // envelope exponent
+  int env_after_mlp;  // radial_basis.apply_cutoff = False: the basis carries no envelope, the MLP output is multiplied by it
 };
 
-// b[n] = pref sin(w_n d) / d * u(d/rc), n = 0..7; if db != nullptr also d b[n] / d d.
+// polynomial envelope u(d / rc) and du/dd (tace/models/radial.py:437-472)
 template <typename T>
-TACE_HD TACE_INLINE void radial_eval(const T d, const RadialParams<T>& rp, T (&b)[kNumBessel], T* db) {
+TACE_HD TACE_INLINE void envelope_eval(const T d, const RadialParams<T>& rp, T& u, T& du) {
   const T rc = rp.rc;
   const int p = rp.p;
   const T xr = d / rc;
-  T u = T(0), du = T(0);
+  u = T(0); du = T(0);
   if (d < rc) {
     const T pp = T(p);
     const T xp = ipow_(xr, p - 1);  // x^(p-1)
@@ -121,6 +122,13 @@ TACE_HD TACE_INLINE void radial_eval(const T d, const RadialParams<T>& rp, T (&b
         pp * (pp + T(1)) / T(2) * xp * xr * xr * xr;
     du = -(pp * (pp + T(1)) * (pp + T(2)) / T(2)) * xp * (T(1) - xr) * (T(1) - xr) / rc;
   }
+}
+
+// b[n] = pref sin(w_n d) / d * u(d/rc), n = 0..7 (u = 1 with env_after_mlp); if db != nullptr also d b[n] / d d.
+template <typename T>
+TACE_HD TACE_INLINE void radial_eval(const T d, const RadialParams<T>& rp, T (&b)[kNumBessel], T* db) {
+  T u = T(1), du = T(0);
+  if (!rp.env_after_mlp) envelope_eval<T>(d, rp, u, du);
   const T inv_d = T(1) / d;
   for (int n = 0; n < kNumBessel; ++n) {
     const T wn = rp.w[n];

@@ -601,12 +601,12 @@ cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* 
 }
 
 cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,
-                           int N, int K, int* error_flag, cudaStream_t s) {
+                           int N, int K, int* error_flag, cudaStream_t s, const float* bias) {
   if (M <= 0) return cudaSuccess;
   TcLinearProblem h;
   memset(&h, 0, sizeof(h));
   h.A = A; h.a_atom_stride = lda; h.a_comp_stride = lda; h.q = 1; h.n_atoms = M; h.K = K;
-  h.Bhi = Bhi; h.Blo = Blo; h.N = N; h.C = C; h.c_s1 = ldc; h.c_s2 = 0; h.bias = nullptr;
+  h.Bhi = Bhi; h.Blo = Blo; h.N = N; h.C = C; h.c_s1 = ldc; h.c_s2 = 0; h.bias = bias;
   return launch_tc_linear(&h, 1, error_flag, s);
 }
 
@@ -615,7 +615,7 @@ cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, cons
 extern "C" int tace_tc_gemm_f32(const float* A, int64_t lda, const float* B_hi, const float* B_lo, float* C, int64_t ldc,
                                 int32_t M, int32_t N, int32_t K, int32_t* error_flag, tace_stream_t stream) {
   if (!A || !B_hi || !B_lo || !C) return TACE_ERR_INVALID_ARGUMENT;
-  cudaError_t e = tace::launch_tc_gemm(A, lda, B_hi, B_lo, C, ldc, M, N, K, error_flag, static_cast<cudaStream_t>(stream));
+  cudaError_t e = tace::launch_tc_gemm(A, lda, B_hi, B_lo, C, ldc, M, N, K, error_flag, static_cast<cudaStream_t>(stream), nullptr);
   if (e == cudaErrorInvalidValue) return TACE_ERR_INVALID_ARGUMENT;
   return e == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }

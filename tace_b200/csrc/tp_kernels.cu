@@ -35,7 +35,9 @@ __device__ __forceinline__ void build_G_rows(const T* __restrict__ Y, int e0, in
   }
 }
 
-template <typename T, typename TP, int GRP>
+// ENV: the path weights are multiplied by the per-edge envelope (radial_basis.apply_cutoff = False); a separate
+// instantiation so the default kernels carry none of its registers.
+template <typename T, typename TP, int GRP, bool ENV>
 __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
   constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
   constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
@@ -60,6 +62,11 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
       const T* We = a.W + ((long long)(e0 + e - a.e_base) * TP::NP + P0) * C;
 #pragma unroll
       for (int p = 0; p < NPG; ++p) wv[p] = We[p * C + c];
+      if constexpr (ENV) {
+        const T u = a.env[e0 + e];
+#pragma unroll
+        for (int p = 0; p < NPG; ++p) wv[p] *= u;
+      }
       if constexpr (GRP == 0) TP::template fwd0<T>(xv, Gs + e * TP::NG, wv, acc);
       else TP::template fwd1<T>(xv, Gs + e * TP::NG, wv, acc);
     }
@@ -70,14 +77,15 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
 }
 
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
-template <typename T, typename TP>
-__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
+template <typename T, typename TP, bool ENV>
+__global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   T* gMs = reinterpret_cast<T*>(smem_raw);          // [NM][C]
   T* Gs = gMs + TP::NM * C;                          // [kEdgeBatch][NG]
   T* red = Gs + kEdgeBatch * TP::NG;                 // [kEdgeBatch][8 warps][D]
+  __shared__ T red_u[kEdgeBatch * 8];                // envelope-gradient partial sums
   __shared__ int esrc[kEdgeBatch];
   const T* gMi = a.gM + (long long)i * TP::NM * C;
   for (int k = 0; k < TP::NM; ++k) gMs[k * C + c] = gMi[k * C + c];  // each thread later reads only its own column
@@ -98,7 +106,19 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
       for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
 #pragma unroll
       for (int k = 0; k < TP::D; ++k) dYp[k] = T(0);
+      T u = T(1);
+      if constexpr (ENV) {
+        u = a.env[e0 + e];
+#pragma unroll
+        for (int p = 0; p < TP::NP; ++p) wv[p] *= u;
+      }
       TP::template bwd<T>(xv, gMs + c, C, Gs + e * TP::NG, wv, dw, dYp, dx);
+      T du_part = T(0);  // sum_p dw * (unscaled weight) = sum_p dw * wv / u
+      if constexpr (ENV) {
+#pragma unroll
+        for (int p = 0; p < TP::NP; ++p) { du_part += dw[p] * wv[p]; dw[p] *= u; }
+        du_part = u > T(0) ? du_part / u : T(0);
+      }
 #pragma unroll
       for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
       if (a.dxe) {
@@ -113,6 +133,12 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         if (lane == 0) red[(e * 8 + warp) * TP::D + k] = v;
       }
+      if constexpr (ENV) {  // the same reduction for the envelope gradient
+        T v = du_part;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) red_u[e * 8 + warp] = v;
+      }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nb * TP::D; idx += blockDim.x) {
@@ -121,6 +147,12 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
       for (int w = 0; w < nwarp; ++w) v += red[(e * 8 + w) * TP::D + k];
       T* dst = a.dY + (long long)(e0 + e) * TP::D + k;
       *dst = a.accumulate_dY ? (*dst + v) : v;
+    }
+    if (ENV && (int)threadIdx.x < nb) {
+      T v = T(0);
+      for (int w = 0; w < nwarp; ++w) v += red_u[threadIdx.x * 8 + w];
+      T* dst = a.denv + (e0 + threadIdx.x);
+      *dst = a.accumulate_denv ? (*dst + v) : v;
     }
   }
 }
@@ -169,20 +201,28 @@ cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const int* keys, const int*
 
 template <typename T, typename TP>
 cudaError_t launch_fwd_t(const TPArgs<T>& a, cudaStream_t s) {
-  tp_fwd_kernel<T, TP, 0><<<a.n_seg, a.C, 0, s>>>(a);
-  if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1><<<a.n_seg, a.C, 0, s>>>(a);
+  if (a.env) {
+    tp_fwd_kernel<T, TP, 0, true><<<a.n_seg, a.C, 0, s>>>(a);
+    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, true><<<a.n_seg, a.C, 0, s>>>(a);
+  } else {
+    tp_fwd_kernel<T, TP, 0, false><<<a.n_seg, a.C, 0, s>>>(a);
+    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, false><<<a.n_seg, a.C, 0, s>>>(a);
+  }
   return cudaGetLastError();
 }
 template <typename T, typename TP>
 cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
   const size_t smem = sizeof(T) * ((size_t)TP::NM * a.C + kEdgeBatch * TP::NG + kEdgeBatch * 8 * TP::D);
+  if (a.env && !a.denv) return cudaErrorInvalidValue;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  tp_bwd_kernel<T, TP><<<a.n_seg, a.C, smem, s>>>(a);
+  if (a.env) tp_bwd_kernel<T, TP, true><<<a.n_seg, a.C, smem, s>>>(a);
+  else tp_bwd_kernel<T, TP, false><<<a.n_seg, a.C, smem, s>>>(a);
   return cudaGetLastError();
 }
 

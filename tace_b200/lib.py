@@ -30,7 +30,8 @@ class TaceConfig(ctypes.Structure):
         ("dtype", c_int), ("L", c_int), ("num_layers", c_int), ("num_channel", c_int), ("num_elements", c_int),
         ("correlation", c_int), ("num_bessel", c_int), ("mlp_hidden", c_int), ("envelope_p", c_int),
         ("readout_hidden", c_int), ("cutoff", c_double), ("avg_num_neighbors", c_double), ("Lnode", c_int),
-        ("use_alllayer", c_int), ("gate_m0_off", c_int),
+        ("use_alllayer", c_int), ("gate_m0_off", c_int), ("mlp_layers", c_int), ("mlp_bias", c_int), ("env_after_mlp", c_int),
+        ("edge_update_element2", c_int),
     ]
 
 

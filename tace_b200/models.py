@@ -92,10 +92,10 @@ def check_model_config(cfg: Dict) -> Dict:
              f"target_property within {sorted(_SUPPORTED_TARGETS)} including energy")
     _require(not cfg["embedding_property"], "no universal embeddings")
     for section, key, allowed in [
-        ("node_embedding", "type", {"linear"}), ("edge_embedding", "type", {"identity"}), ("edge_update", "type", {"identity"}),
+        ("node_embedding", "type", {"linear"}), ("edge_embedding", "type", {"identity"}), ("edge_update", "type", {"identity", "element2"}),
         ("radial_basis", "radial_basis", {"j0", "bessel"}), ("radial_basis", "cutoff_fn", {"c2poly", "polynomial"}),
-        ("radial_basis", "distance_transform", {None}), ("radial_basis", "apply_cutoff", {True}),
-        ("radial_basis", "bias", {False}), ("radial_basis", "use_dydynamic_cutoff", {False}),
+        ("radial_basis", "distance_transform", {None}), ("radial_basis", "apply_cutoff", {True, False}),
+        ("radial_basis", "bias", {False, True}), ("radial_basis", "use_dydynamic_cutoff", {False}),
         ("radial_basis", "num_radial_basis", {8}),
         ("atomic_basis", "scatter_norm", {"avg_num_neighbors"}), ("atomic_basis", "gate_m0", {True, False}),
         ("atomic_basis", "l1l2", {None}), ("atomic_basis", "scalar_act", {None, "sigmoid"}),
@@ -109,7 +109,8 @@ def check_model_config(cfg: Dict) -> Dict:
         ("scale_shift", "enable", {True}), ("scale_shift", "all_atoms", {False}), ("scale_shift", "shift_type", {None}),
     ]:
         _require(cfg[section][key] in allowed, f"{section}.{key} in {allowed}, got {cfg[section][key]!r}")
-    _require(list(cfg["radial_basis"]["hidden"]) == [64, 64, 64], "radial_basis.hidden == [64, 64, 64]")
+    hidden = list(cfg["radial_basis"]["hidden"])
+    _require(1 <= len(hidden) <= 3 and all(h == 64 for h in hidden), "radial_basis.hidden: one to three layers of width 64")
     _require(len(cfg["readout_emlp"]["hidden"]) == 1 and cfg["readout_emlp"]["hidden"][0] <= 64, "one read-out hidden layer <= 64")
     _require(not cfg["short_range"]["zbl"]["enable"], "no ZBL")
     _require(not cfg["long_range"]["les"]["enable"], "no LES")
@@ -186,12 +187,17 @@ class e3nnTACE(torch.nn.Module):
         nb = cfg["radial_basis"]["num_radial_basis"]
         self.plan = ModelPlan(cfg["lmax"], cfg["num_layers"], cfg["num_channel"], self.num_elements,
                               cfg["product_basis"]["correlation"][0], cfg["readout_emlp"]["hidden"][0], nb, 64,
-                              Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"], gate_m0=cfg["atomic_basis"]["gate_m0"])
+                              Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"], gate_m0=cfg["atomic_basis"]["gate_m0"],
+                              mlp_layers=len(cfg["radial_basis"]["hidden"]), mlp_bias=cfg["radial_basis"]["bias"],
+                              apply_cutoff=cfg["radial_basis"]["apply_cutoff"],
+                              element2=cfg["edge_update"]["type"] == "element2")
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         for name, shape in self.plan.parameter_shapes().items():
             if name.endswith(".bias"):
                 value = torch.zeros(shape, dtype=dt)
+            elif ".edge_updates." in name:  # tace/models/_e3nn/edge.py:216-221
+                value = torch.empty(shape, dtype=dt).uniform_(-0.001, 0.001)
             elif ".edge_info.mlp." in name:
                 value = torch.empty(shape, dtype=dt).uniform_(-math.sqrt(3.0), math.sqrt(3.0))
             else:
@@ -299,7 +305,8 @@ class TensorModel(torch.nn.Module):
             num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
             cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
-            use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0))
+            use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,
+            mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2))
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

@@ -59,11 +59,14 @@ class LayerPlan:
 class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
-                 use_alllayer: bool = False, gate_m0: bool = True):
+                 use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
+                 apply_cutoff: bool = True, element2: bool = False):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Lnode = L if Lnode is None else Lnode
         self.use_alllayer = bool(use_alllayer)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
+        # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
+        self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
         self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation) for t in range(num_layers)]
 
@@ -75,9 +78,15 @@ class ModelPlan:
             pre = f"representation.interactions.{lp.t}."
             out[pre + "linear_up.weight"] = (len(lp.in_ls) * C * C,)
             out[pre + "linear_up.bias"] = (C,)
-            dims = [self.num_bessel] + [self.mlp_hidden] * 3 + [len(lp.tp_paths) * C]
+            edge_dim = self.num_bessel + (2 * C if self.element2 else 0)
+            dims = [edge_dim] + [self.mlp_hidden] * self.mlp_layers + [len(lp.tp_paths) * C]
             for i, (a, b) in enumerate(zip(dims, dims[1:])):
                 out[pre + f"edge_info.mlp.{2 * i}.weight"] = (a, b)
+                if self.mlp_bias:
+                    out[pre + f"edge_info.mlp.{2 * i}.bias"] = (b,)
+            if self.element2:  # tace/models/_e3nn/edge.py:190-257
+                out[f"representation.edge_updates.{lp.t}.source_embedding.weight"] = (n_el * C,)
+                out[f"representation.edge_updates.{lp.t}.target_embedding.weight"] = (n_el * C,)
             n0 = (L + 2) * C if self.gate_m0 else (L + 1) * C
             out[pre + "linear_down.weight"] = (sum(lp.k[l] * C * (n0 if l == 0 else C) for l in range(L + 1)),)
             out[pre + "linear_down.bias"] = (n0,)
@@ -159,11 +168,26 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         for l, m in zip(lp.in_ls, split(g(pre + "linear_up.weight"), [(C, C)] * len(lp.in_ls))):
             put(tp + f"up.l{l}", m / math.sqrt(C), tp + f"upT.l{l}")
         out[tp + "up.b"] = g(pre + "linear_up.bias")
-        nb, hd = plan.num_bessel, plan.mlp_hidden
-        out[tp + "A0"] = g(pre + "edge_info.mlp.0.weight") / math.sqrt(nb)
-        put(tp + "A1", g(pre + "edge_info.mlp.2.weight") * math.sqrt(2.0 / hd), tp + "A1t")
-        put(tp + "A2", g(pre + "edge_info.mlp.4.weight") * math.sqrt(2.0 / hd), tp + "A2t")
-        put(tp + "W3", g(pre + "edge_info.mlp.6.weight") * math.sqrt(2.0 / hd), tp + "W3t")
+        nb, hd, nh = plan.num_bessel, plan.mlp_hidden, plan.mlp_layers
+        # first layer: fan-in = radial features (+ both species embeddings with the element-dependent edge update, whose
+        # rows become per-species tables added to the first pre-activation: tace/models/_e3nn/edge.py:190-257)
+        w0 = g(pre + "edge_info.mlp.0.weight")
+        out[tp + "A0"] = w0[:nb] / math.sqrt(w0.shape[0])
+        if plan.element2:
+            eu = f"representation.edge_updates.{t}."
+            temb = g(eu + "target_embedding.weight").reshape(n_el, C) / math.sqrt(n_el)
+            semb = g(eu + "source_embedding.weight").reshape(n_el, C) / math.sqrt(n_el)
+            out[tp + "tdst"] = temb @ w0[nb:nb + C] / math.sqrt(w0.shape[0])
+            out[tp + "tsrc"] = semb @ w0[nb + C:nb + 2 * C] / math.sqrt(w0.shape[0])
+        if nh >= 2:
+            put(tp + "A1", g(pre + "edge_info.mlp.2.weight") * math.sqrt(2.0 / hd), tp + "A1t")
+        if nh >= 3:
+            put(tp + "A2", g(pre + "edge_info.mlp.4.weight") * math.sqrt(2.0 / hd), tp + "A2t")
+        put(tp + "W3", g(pre + f"edge_info.mlp.{2 * nh}.weight") * math.sqrt(2.0 / hd), tp + "W3t")
+        if plan.mlp_bias:
+            for j in range(nh):
+                out[tp + f"b{j}"] = g(pre + f"edge_info.mlp.{2 * j}.bias")
+            out[tp + "b3"] = g(pre + f"edge_info.mlp.{2 * nh}.bias")
         for name in ("W3", "W3t"):  # TF32 high part / residual for the tensor-core GEMM of fp32 models
             hi, lo = split_tf32(out[tp + name])
             out[tp + name + "_hi"], out[tp + name + "_lo"] = hi, lo

@@ -133,9 +133,21 @@ void h_sh_grad(int L, const double* n, const double* dY, double* dn) {
   memcpy(dn, g, sizeof g);
 }
 
+// env_after_mlp != 0: b / db without the envelope, which is returned separately in env[0], env[1] (value, derivative)
+void h_radial2(double d, double rc, int p, int env_after_mlp, double* b, double* db, double* env) {
+  double bb[kNumBessel], dd[kNumBessel];
+  RadialParams<double> rp;
+  for (int n = 0; n < kNumBessel; ++n) rp.w[n] = (n + 1) * 3.14159265358979323846 / rc;
+  rp.pref = std::sqrt(2.0 / rc); rp.rc = rc; rp.p = p; rp.env_after_mlp = env_after_mlp;
+  radial_eval<double>(d, rp, bb, dd);
+  memcpy(b, bb, sizeof bb); memcpy(db, dd, sizeof dd);
+  envelope_eval<double>(d, rp, env[0], env[1]);
+}
+
 void h_radial(double d, double rc, int p, double* b, double* db) {
   double bb[kNumBessel], dd[kNumBessel];
   RadialParams<double> rp;
+  rp.env_after_mlp = 0;
   for (int n = 0; n < kNumBessel; ++n) rp.w[n] = (n + 1) * 3.14159265358979323846 / rc;
   rp.pref = std::sqrt(2.0 / rc); rp.rc = rc; rp.p = p;
   radial_eval<double>(d, rp, bb, dd);

@@ -9,12 +9,12 @@ from tace_b200 import synth
 
 
 def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
-                targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True):
+                targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True, radial=None, edge_update="identity"):
     """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
     from oracle.model import build_oracle
 
     cfg = synth.model_config(L, C, cutoff, elements, avg, num_layers=num_layers, correlation=correlation,
-                             target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0)
+                             target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0, radial=radial, edge_update=edge_update)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
@@ -26,6 +26,8 @@ def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correl
         for k, v in sd.items():
             if k.endswith(".bias"):
                 v.copy_(0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
+            if ".edge_updates." in k:  # initialised at 1e-3 in the reference: make the term visible
+                v.copy_(torch.randn(v.shape, generator=g, dtype=v.dtype))
         sd["readout_fn.scale_shift.scale"].copy_(0.5 + torch.rand(sd["readout_fn.scale_shift.scale"].shape, generator=g, dtype=dtype))
         sd["readout_fn.atomic_energy_layer.atomic_energy"].copy_(
             torch.randn(sd["readout_fn.atomic_energy_layer.atomic_energy"].shape, generator=g, dtype=dtype))

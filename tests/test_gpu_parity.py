@@ -286,3 +286,36 @@ def test_correlation_three(L, Lmax, num_layers, dtype):
     """product_basis.correlation = 3: B = W1 A + W2 (A x A) + W3 ((A x A) x A)."""
     structs = synth.random_crystals(2, seed=47, nmin=4, nmax=8, zmax=3)
     run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, num_layers=num_layers, correlation=3)
+
+
+RADIAL_CASES = [
+    ({"hidden": [64, 64]}, "identity"),
+    ({"hidden": [64]}, "identity"),
+    ({"bias": True}, "identity"),
+    ({"apply_cutoff": False}, "identity"),
+    ({"apply_cutoff": False, "bias": True, "hidden": [64, 64]}, "element2"),   # the radial section of example/train/tace.yaml
+    ({}, "element2"),
+]
+
+
+@pytest.mark.parametrize("radial,edge_update", RADIAL_CASES)
+def test_radial_mlp_options_and_element_dependent_edge_update(radial, edge_update):
+    structs = synth.random_crystals(2, seed=53, nmin=4, nmax=9, zmax=3)
+    run_case(structs, 2, 32, [1, 2, 3], 4.5, torch.float64, radial=radial, edge_update=edge_update)
+
+
+def test_example_yaml_like_model_fp32_chunked_and_whole():
+    """Lmax 2 / lmax 3, three layers, envelope after a biased two-layer radial MLP, element2 edge update, e3nn gate:
+    the model section of the reference's example/train/tace.yaml except for its 48 channels."""
+    structs = synth.random_crystals(2, seed=54, nmin=5, nmax=9, zmax=3)
+    kw = dict(Lmax=2, num_layers=3, gate_m0=False, radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},
+              edge_update="element2")
+    out, ref = run_case(structs, 3, 64, [1, 2, 3], 4.5, torch.float32, **kw)
+    model, oracle, cfg = make_models(3, 64, [1, 2, 3], 4.5, 20.0, torch.float64, **kw)
+    dev = torch.device("cuda:0")
+    data = to_device(oracle_batch(structs, [1, 2, 3], 4.5, torch.float64), dev)
+    whole = {k: v.clone() for k, v in model(data).items() if v is not None}
+    model.set_chunk_edges(1024)
+    chunked = model(data)
+    for k, v in whole.items():
+        assert (chunked[k] - v).abs().max().item() <= 1e-10 * max(1.0, v.abs().max().item()), k

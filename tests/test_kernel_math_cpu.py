@@ -146,6 +146,26 @@ def test_third_order_product_basis_matches_oracle(cpu_harness, L, Lout):
     np.testing.assert_allclose(da, da_ref.numpy(), rtol=0, atol=1e-12)
 
 
+def test_radial_basis_without_envelope_and_the_envelope_itself(cpu_harness):
+    """radial_basis.apply_cutoff = False: plain Bessel features plus the envelope (value, derivative) on its own."""
+    torch.set_default_dtype(torch.float64)
+    try:
+        rb = om.RadialBasis(5.0, 8, 5, apply_cutoff=False)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    cpu_harness.h_radial2.argtypes = [ctypes.c_double, ctypes.c_double, ctypes.c_int, ctypes.c_int, DP, DP, DP]
+    for d0 in [0.8, 2.553, 4.2, 4.999, 5.3]:
+        d = torch.tensor([[d0]], dtype=torch.float64, requires_grad=True)
+        feats, env = rb(d)
+        jac = torch.stack([torch.autograd.grad(feats[0, i], d, retain_graph=True)[0][0, 0] for i in range(8)])
+        (denv,) = torch.autograd.grad(env[0, 0], d, allow_unused=True)
+        b, db, e = np.zeros(8), np.zeros(8), np.zeros(2)
+        cpu_harness.h_radial2(d0, 5.0, 5, 1, ptr(b), ptr(db), ptr(e))
+        np.testing.assert_allclose(b, feats[0].detach().numpy(), rtol=0, atol=1e-13)
+        np.testing.assert_allclose(db, jac.numpy(), rtol=0, atol=1e-12)
+        assert abs(e[0] - env.item()) < 1e-14 and abs(e[1] - (0.0 if denv is None else denv.item())) < 1e-12
+
+
 @pytest.mark.parametrize("L", [1, 2, 3])
 def test_spherical_harmonics_and_gradient(cpu_harness, L):
     torch.manual_seed(L)
@@ -171,7 +191,7 @@ def test_radial_basis_and_gradient(cpu_harness):
         torch.set_default_dtype(torch.float32)
     for d0 in [0.8, 2.553, 4.2, 4.999, 5.0, 5.3]:
         d = torch.tensor([[d0]], dtype=torch.float64, requires_grad=True)
-        ref = rb(d)[0]
+        ref = rb(d)[0][0]
         jac = torch.stack([torch.autograd.grad(ref[i], d, retain_graph=True)[0][0, 0] for i in range(8)])
         b, db = np.zeros(8), np.zeros(8)
         cpu_harness.h_radial.argtypes = [ctypes.c_double, ctypes.c_double, ctypes.c_int, DP, DP]
