@@ -86,7 +86,7 @@ def check_model_config(cfg: Dict) -> Dict:
     cfg["atomic_energies"] = [s["atomic_energy"] for s in stats]
     _require(1 <= cfg["Lmax"] <= cfg["lmax"] <= 3, "1 <= Lmax <= lmax <= 3")
     _require(not cfg["parity"], "parity=False")
-    _require(cfg["num_channel"] % 32 == 0 and 32 <= cfg["num_channel"] <= 256, "num_channel a multiple of 32, <= 256")
+    _require(1 <= cfg["num_channel"] <= 256, "1 <= num_channel <= 256 (counts that are not multiples of 32 run zero-padded)")
     _require(1 <= cfg["num_layers"] <= 4, "1..4 layers")
     _require(set(cfg["target_property"]) <= _SUPPORTED_TARGETS and "energy" in cfg["target_property"],
              f"target_property within {sorted(_SUPPORTED_TARGETS)} including energy")
@@ -302,7 +302,7 @@ class TensorModel(torch.nn.Module):
         plan = rf.plan
         cfg = _lib.TaceConfig(
             dtype=_lib.TACE_F64 if dtype == torch.float64 else _lib.TACE_F32, L=plan.L, num_layers=plan.num_layers,
-            num_channel=plan.C, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
+            num_channel=plan.Cp, num_elements=plan.n_el, correlation=plan.correlation, num_bessel=plan.num_bessel,
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
             cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
             use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,

@@ -62,6 +62,7 @@ class ModelPlan:
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
                  apply_cutoff: bool = True, element2: bool = False):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
+        self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
         self.use_alllayer = bool(use_alllayer)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
@@ -133,6 +134,47 @@ def tile_k_major(w: np.ndarray, tile: int = 32) -> np.ndarray:
     return np.ascontiguousarray(np.swapaxes(w.reshape(lead + (n, k // tile, tile)), -3, -2))
 
 
+def _pad_axis(arr: np.ndarray, axis: int, C: int, Cp: int) -> np.ndarray:
+    """An axis made of blocks of C channels -> the same blocks of Cp channels, zero-filled."""
+    axis = axis % arr.ndim
+    n = arr.shape[axis]
+    assert n % C == 0, (arr.shape, axis, C)
+    shp = arr.shape[:axis] + (n // C, C) + arr.shape[axis + 1:]
+    a = arr.reshape(shp)
+    width = [(0, 0)] * a.ndim
+    width[axis + 1] = (0, Cp - C)
+    a = np.pad(a, width)
+    return a.reshape(arr.shape[:axis] + ((n // C) * Cp,) + arr.shape[axis + 1:])
+
+
+def pad_channels(out: Dict[str, np.ndarray], C: int, Cp: int) -> None:
+    """The kernels work on channel counts that are multiples of 32.  Other counts (the reference's example uses 48)
+    run with the channel dimension zero-padded: padded channels stay exactly zero through every layer (zero weights
+    and biases in, zero out; SiLU, gates and products of zeros are zero) and the fan-in factors were taken from the
+    true channel count before this step."""
+    if Cp == C:
+        return
+    both = {"up", "upT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT", "down", "downT"}
+    last_only = {"W3", "b", "b3"}
+    for name in list(out):
+        parts = name.split(".")
+        arr = out[name]
+        if name == "emb":
+            out[name] = _pad_axis(arr, -1, C, Cp)
+        elif name == "ro.W1":
+            out[name] = _pad_axis(arr, 0, C, Cp)
+        elif name.startswith("ro.lin"):
+            out[name] = _pad_axis(arr, -1, C, Cp)
+        elif len(parts) >= 2 and parts[0].startswith("t") and parts[0][1:].isdigit():
+            stem = parts[1]
+            if stem in both and len(parts) == 3 and parts[2].startswith("l"):
+                out[name] = _pad_axis(_pad_axis(arr, -2, C, Cp), -1, C, Cp)
+            elif stem == "W3t":
+                out[name] = _pad_axis(arr, -2, C, Cp)
+            elif stem == "W3" or stem == "b3" or (len(parts) == 3 and parts[2] == "b" and stem in ("up", "nl", "lin", "down", "c", "res")):
+                out[name] = _pad_axis(arr, -1, C, Cp)
+
+
 def _np(t) -> np.ndarray:
     return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
 
@@ -188,9 +230,6 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
             for j in range(nh):
                 out[tp + f"b{j}"] = g(pre + f"edge_info.mlp.{2 * j}.bias")
             out[tp + "b3"] = g(pre + f"edge_info.mlp.{2 * nh}.bias")
-        for name in ("W3", "W3t"):  # TF32 high part / residual for the tensor-core GEMM of fp32 models
-            hi, lo = split_tf32(out[tp + name])
-            out[tp + name + "_hi"], out[tp + name + "_lo"] = hi, lo
         down_shapes = [(lp.k[l] * C, ((L + 2) * C if plan.gate_m0 else (L + 1) * C) if l == 0 else C) for l in range(L + 1)]
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
             put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
@@ -217,24 +256,25 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
             for l, m in zip(lp.out_ls, split(g(pre + "resnetBB.weight"), [(C, C)] * len(lp.out_ls))):
                 put(tp + f"res.l{l}", m / math.sqrt(C), tp + f"resT.l{l}")
             out[tp + "res.b"] = g(pre + "resnetBB.bias")
-    # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
-    for name in list(out):
-        stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
-        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT")
-                and name.split(".")[-1].startswith("l")) \
-                or stem in ("A1", "A1t", "A2", "A2t"):
-            hi, lo = split_tf32(out[name])
-            if stem in ("c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT"):
-                # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,
-                # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
-                hi, lo = tile_k_major(hi), tile_k_major(lo)
-            out[name + "_hi"], out[name + "_lo"] = hi, lo
     ro = plan.num_layers - 1 if plan.use_alllayer else 0
     out["ro.W1"] = g(f"energy_readouts.{ro}.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
     out["ro.W2"] = g(f"energy_readouts.{ro}.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
     if plan.use_alllayer:
         for t in range(plan.num_layers - 1):
             out[f"ro.lin{t}"] = g(f"energy_readouts.{t}.linear1.0.weight").reshape(C) / math.sqrt(C)
+    pad_channels(out, C, plan.Cp)
+    # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
+    for name in list(out):
+        stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
+        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT")
+                and name.split(".")[-1].startswith("l")) \
+                or stem in ("A1", "A1t", "A2", "A2t", "W3", "W3t"):
+            hi, lo = split_tf32(out[name])
+            if stem in ("c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT"):
+                # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,
+                # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
+                hi, lo = tile_k_major(hi), tile_k_major(lo)
+            out[name + "_hi"], out[name + "_lo"] = hi, lo
     out["scale"] = g("scale_shift.scale")[0]
     out["e0"] = g("atomic_energy_layer.atomic_energy")[0]
     shift = g("scale_shift.shift")

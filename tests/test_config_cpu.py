@@ -1,0 +1,60 @@
+"""Constructor / configuration checks that need no GPU: which reference options are accepted, which are refused."""
+import pytest
+import torch
+
+from tace_b200 import synth
+from tace_b200.models import check_model_config, create_model
+
+# the `model.config` section of the reference's example training file (example/train/tace.yaml), values only
+EXAMPLE_MODEL_SECTION = {
+    "cutoff": 6.0, "max_neighbors": None, "target_property": ["energy", "forces", "stress"], "embedding_property": [],
+    "node_embedding": {"type": "linear"}, "edge_embedding": {"type": "identity"}, "edge_update": {"type": "element2"},
+    "mmax": 3, "Lmax": 2, "lmax": 3, "mag_Lmax": 1, "num_layers": 3, "num_channel": 48, "parity": False,
+    "radial_basis": {"radial_basis": "j0", "num_radial_basis": 8, "distance_transform": None, "cutoff_fn": "c2poly",
+                     "polynomial_cutoff": 5, "order": 0, "trainable": False, "apply_cutoff": False, "hidden": [64, 64],
+                     "bias": True, "use_dydynamic_cutoff": False},
+    "resnet": {"type": "BB", "linear_type": "aware", "use_first_resnet": False},
+    "layer_norm": {"pre_norm_type": None, "final_norm_type": None, "use_first_pre_norm": False},
+    "atomic_basis": {"type": "cgtp", "l1l2": None, "scatter_norm": "avg_num_neighbors", "nonlinear": "sigmoid_gate",
+                     "gate_m0": False, "scalar_act": None, "tensor_act": None},
+    "product_basis": {"type": "cgtp", "l1l2": None, "correlation": 2, "return_components": None, "num_expert": None,
+                      "nonlinear": None, "use_shared_expert": False, "agnostic": False},
+    "readout_emlp": {"bias": False, "hidden": [16], "use_alllayer": False, "use_uie": False},
+    "scale_shift": {"enable": True, "scale_type": "rms_forces", "shift_type": None, "all_atoms": False},
+}
+
+
+def test_example_training_configuration_is_accepted_and_builds():
+    cfg = dict(EXAMPLE_MODEL_SECTION, statistics=synth.statistics([1, 6, 8], 30.0))
+    torch.manual_seed(0)
+    model = create_model(cfg)
+    rf = model.readout_fn
+    assert rf.plan.C == 48 and rf.plan.Cp == 64 and rf.plan.L == 3 and rf.plan.Lnode == 2
+    assert rf.plan.mlp_layers == 2 and rf.plan.mlp_bias and not rf.plan.apply_cutoff and rf.plan.element2 and not rf.plan.gate_m0
+    sd = model.state_dict()
+    assert sd["readout_fn.representation.interactions.0.edge_info.mlp.0.weight"].shape == (8 + 2 * 48, 64)
+    assert sd["readout_fn.representation.edge_updates.2.target_embedding.weight"].shape == (3 * 48,)
+    assert "readout_fn.representation.interactions.0.edge_info.mlp.4.bias" in sd
+    assert "readout_fn.representation.interactions.0.edge_info.mlp.6.weight" not in sd
+
+
+@pytest.mark.parametrize("override,needle", [
+    ({"Lmax": 3, "lmax": 2}, "Lmax"),
+    ({"parity": True}, "parity"),
+    ({"product_basis": {"correlation": 4}}, "correlation"),
+    ({"radial_basis": {"hidden": [32, 32]}}, "hidden"),
+    ({"radial_basis": {"cutoff_fn": "cosine"}}, "cutoff_fn"),
+    ({"atomic_basis": {"type": "uv_so2"}}, "atomic_basis.type"),
+    ({"short_range": {"zbl": {"enable": True}}}, "ZBL"),
+    ({"num_channel": 300}, "num_channel"),
+])
+def test_unsupported_options_are_refused_loudly(override, needle):
+    cfg = synth.model_config(2, 32, 4.0, [29], 20.0)
+    for k, v in override.items():
+        if isinstance(v, dict) and isinstance(cfg.get(k), dict):
+            cfg[k] = {**cfg[k], **v}
+        else:
+            cfg[k] = v
+    with pytest.raises(NotImplementedError) as err:
+        check_model_config({k: v for k, v in cfg.items()})
+    assert needle in str(err.value)

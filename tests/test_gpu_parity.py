@@ -319,3 +319,11 @@ def test_example_yaml_like_model_fp32_chunked_and_whole():
     chunked = model(data)
     for k, v in whole.items():
         assert (chunked[k] - v).abs().max().item() <= 1e-10 * max(1.0, v.abs().max().item()), k
+
+
+@pytest.mark.parametrize("C,dtype", [(48, torch.float64), (48, torch.float32), (16, torch.float64)])
+def test_channel_counts_that_are_not_multiples_of_32(C, dtype):
+    """The reference's example configuration has 48 channels: such counts run zero-padded to the next multiple of 32."""
+    structs = synth.random_crystals(2, seed=59, nmin=4, nmax=9, zmax=3)
+    run_case(structs, 3, C, [1, 2, 3], 4.5, dtype, Lmax=2, gate_m0=False, edge_update="element2",
+             radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]}, num_layers=3 if dtype == torch.float64 else 2)
