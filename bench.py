@@ -2,7 +2,7 @@
 """Benchmark of the TACE energy + force + stress path on B200.
 
 One "step" = one evaluation of energy, conservative forces and stress for the whole batch of the
-workload (BASELINE config 2: 64 random periodic crystals, fp32, L = 3, 128 channels, 89 elements).
+workload (the headline configuration: 64 random periodic crystals, fp32, L = 3, 128 channels, 89 elements).
 With N GPUs every rank evaluates its own batch of 64 crystals (weak scaling, no collective on the
 data path).  `value` is timed with the batch and its neighbour list resident in HBM; `e2e` goes
 through the public API from pinned host buffers (upload, GPU neighbour list, evaluation,
@@ -224,7 +224,7 @@ def run_reference(args, rank, world):
 
 
 def run_md(args, wl, dtype, rank, world, device):
-    """Molecular-dynamics workloads (BASELINE config 5): ONE periodic Cu/Al system, velocity Verlet, dt = 1 fs,
+    """Molecular-dynamics workloads: ONE periodic Cu/Al system, velocity Verlet, dt = 1 fs,
     Maxwell-Boltzmann start at 300 K.  A step = half kick + drift, ghost positions, neighbour list, energy and
     forces with halo exchanges between layers, ghost forces returned, half kick.  With N GPUs the box is cut
     into N blocks (strong scaling: the system is the same at every N)."""

@@ -88,7 +88,12 @@ __global__ void __launch_bounds__(128) edge_mlp_in_kernel(const EdgeArgs<T> a) {
       const long long r0 = e0 + 64 * half;
       const long long n_live = a.E - r0 < 64 ? a.E - r0 : 64;
       T* out = a.Z1[t] + r0 * kHidden;
-      for (long long idx = threadIdx.x; idx < n_live * kHidden; idx += blockDim.x) out[idx] = tile[idx / kHidden][idx % kHidden];
+      T* act = a.H1[t] + r0 * kHidden;
+      for (long long idx = threadIdx.x; idx < n_live * kHidden; idx += blockDim.x) {
+        const T z1 = tile[idx / kHidden][idx % kHidden];
+        out[idx] = z1;
+        act[idx] = silu_(z1);
+      }
       __syncthreads();
     }
   }

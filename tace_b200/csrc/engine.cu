@@ -663,6 +663,7 @@ struct Model : ModelBase {
     for (size_t i = 0; i < ts.size(); ++i) {
       r.mlp[i] = ea.mlp[ts[i]];
       r.Z1[i] = b.lay[ts[i]].Z1;
+      r.H1[i] = nh == 1 ? b.lay[ts[i]].H3 : b.lay[ts[i]].Hact;  // activation of the first hidden layer
       r.dH1[i] = dh1_buffer(b.lay[ts[i]]);
     }
     return r;
@@ -679,6 +680,7 @@ struct Model : ModelBase {
     for (int j = 0; j < nh; ++j) {  // hidden layer j: activation, then (unless it is the last) the next 64 x 64 layer
       const bool last_hidden = (j == nh - 1);
       for (int t : ts) {
+        if (j == 0) break;  // launch_edge_mlp_in already wrote silu(Z1)
         const LayerBufs& lb = b.lay[t];
         const T* z = j == 0 ? lb.Z1 : j == 1 ? lb.Z2 : lb.Z3;
         CKL(launch_silu(z, last_hidden ? lb.H3 : lb.Hact, n64, s));

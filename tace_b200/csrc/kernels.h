@@ -126,6 +126,7 @@ struct EdgeArgs {
   T* vec;                // [E][3] edge vectors (target-sorted order)
   T* Y;                  // [E][D]
   T* Z1[kMaxLayers];     // [E][64] pre-activation of the first hidden layer of each layer's radial MLP
+  T* H1[kMaxLayers];     // [E][64] its activation silu(Z1), written by launch_edge_mlp_in as well
   const T* dH1[kMaxLayers];  // [E][64] gradient of the first hidden activation (backward)
   int accumulate_ddlen;  // launch_edge_mlp_out adds into ddlen instead of overwriting (layer-by-layer passes)
   const int* species;    // [N] (element-dependent edge update), or nullptr

@@ -144,14 +144,19 @@ __global__ void nl_cell_start_kernel(const int* __restrict__ sorted_keys, int n_
 __device__ __forceinline__ int floordiv(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
 
 // FILL = false: counts[i] = number of sources of target i; FILL = true: write them at row_ptr[i].
+// One warp per target atom: every lane takes one neighbouring bin (bins are visited in the fixed order d0, d1, d2 of
+// the offsets), counts the sources of its bin that lie inside the cutoff, an exclusive scan over the lanes turns the
+// counts into output positions, and the lane tests its bin again to write.  The output order (by bin, then by sorted
+// source position) does not depend on the lane assignment, so it is deterministic.
 template <bool FILL>
-__global__ void nl_search_kernel(const double* __restrict__ pos, const GraphBins* __restrict__ bins,
+__global__ void __launch_bounds__(128) nl_search_kernel(const double* __restrict__ pos, const GraphBins* __restrict__ bins,
                                  const int* __restrict__ graph_ptr, int n_graphs, int n_atoms, double cutoff,
                                  const int* __restrict__ keys_of_atom, const int* __restrict__ sorted_atoms,
                                  const int* __restrict__ cell_start, const int* __restrict__ img, int* counts,
                                  const int64_t* __restrict__ row_ptr, int64_t n_edges, int64_t* edge_index, int32_t* shifts) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_atoms) return;
+  const int i = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (i >= n_atoms) return;  // whole warps leave together
   int lo = 0, hi = n_graphs;
   while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (graph_ptr[mid] <= i) lo = mid; else hi = mid; }
   const GraphBins& gb = bins[lo];
@@ -160,47 +165,66 @@ __global__ void nl_search_kernel(const double* __restrict__ pos, const GraphBins
   const int key = keys_of_atom[i] - gb.bin_offset;
   const int b2 = key % gb.nb[2], b1 = (key / gb.nb[2]) % gb.nb[1], b0 = key / (gb.nb[2] * gb.nb[1]);
   const int fi0 = img[3LL * i], fi1 = img[3LL * i + 1], fi2 = img[3LL * i + 2];
+  const int w1 = 2 * gb.r[1] + 1, w2 = 2 * gb.r[2] + 1;
+  const int n_cells = (2 * gb.r[0] + 1) * w1 * w2;
   int64_t out = FILL ? row_ptr[i] : 0;
   int count = 0;
-  for (int d0 = -gb.r[0]; d0 <= gb.r[0]; ++d0) {
-    int c0 = b0 + d0, s0 = 0;
-    if (gb.pbc[0]) { s0 = floordiv(c0, gb.nb[0]); c0 -= s0 * gb.nb[0]; } else if (c0 < 0 || c0 >= gb.nb[0]) continue;
-    for (int d1 = -gb.r[1]; d1 <= gb.r[1]; ++d1) {
-      int c1 = b1 + d1, s1 = 0;
-      if (gb.pbc[1]) { s1 = floordiv(c1, gb.nb[1]); c1 -= s1 * gb.nb[1]; } else if (c1 < 0 || c1 >= gb.nb[1]) continue;
-      for (int d2 = -gb.r[2]; d2 <= gb.r[2]; ++d2) {
-        int c2i = b2 + d2, s2 = 0;
-        if (gb.pbc[2]) { s2 = floordiv(c2i, gb.nb[2]); c2i -= s2 * gb.nb[2]; } else if (c2i < 0 || c2i >= gb.nb[2]) continue;
+  for (int cb = 0; cb < n_cells; cb += 32) {
+    const int c = cb + lane;
+    int k_beg = 0, k_end = 0, s0 = 0, s1 = 0, s2 = 0;
+    if (c < n_cells) {
+      const int d0 = c / (w1 * w2) - gb.r[0], d1 = (c / w2) % w1 - gb.r[1], d2 = c % w2 - gb.r[2];
+      int c0 = b0 + d0, c1 = b1 + d1, c2i = b2 + d2;
+      bool inside = true;
+      if (gb.pbc[0]) { s0 = floordiv(c0, gb.nb[0]); c0 -= s0 * gb.nb[0]; } else if (c0 < 0 || c0 >= gb.nb[0]) inside = false;
+      if (gb.pbc[1]) { s1 = floordiv(c1, gb.nb[1]); c1 -= s1 * gb.nb[1]; } else if (c1 < 0 || c1 >= gb.nb[1]) inside = false;
+      if (gb.pbc[2]) { s2 = floordiv(c2i, gb.nb[2]); c2i -= s2 * gb.nb[2]; } else if (c2i < 0 || c2i >= gb.nb[2]) inside = false;
+      if (inside) {
         const int cell = gb.bin_offset + (c0 * gb.nb[1] + c1) * gb.nb[2] + c2i;
-        for (int k = cell_start[cell]; k < cell_start[cell + 1]; ++k) {
-          const int j = sorted_atoms[k];
-          // wrapped image (s0,s1,s2) of source j seen from target i:  r_j - r_i + S' @ cell with
-          // S' = s - fl_j + fl_i;  the edge (source j -> target i) carries shift S = -S'.
-          const int S0 = -(s0 - img[3LL * j] + fi0), S1 = -(s1 - img[3LL * j + 1] + fi1), S2 = -(s2 - img[3LL * j + 2] + fi2);
-          if (j == i && S0 == 0 && S1 == 0 && S2 == 0) continue;
-          const double t0 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[0]), __dmul_rn((double)S1, gb.cell[3])), __dmul_rn((double)S2, gb.cell[6]));
-          const double t1 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[1]), __dmul_rn((double)S1, gb.cell[4])), __dmul_rn((double)S2, gb.cell[7]));
-          const double t2 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[2]), __dmul_rn((double)S1, gb.cell[5])), __dmul_rn((double)S2, gb.cell[8]));
-          const double dx = __dadd_rn(__dadd_rn(xi, -pos[3LL * j]), t0);
-          const double dy = __dadd_rn(__dadd_rn(yi, -pos[3LL * j + 1]), t1);
-          const double dz = __dadd_rn(__dadd_rn(zi, -pos[3LL * j + 2]), t2);
-          const double dsq = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
-          if (dsq < c2) {
-            if (FILL) {
-              if (out < n_edges) {
-                edge_index[out] = j;
-                edge_index[n_edges + out] = i;
-                shifts[3 * out] = S0; shifts[3 * out + 1] = S1; shifts[3 * out + 2] = S2;
-              }
-              ++out;
-            }
-            ++count;
+        k_beg = cell_start[cell]; k_end = cell_start[cell + 1];
+      }
+    }
+    // wrapped image (s0,s1,s2) of source j seen from target i:  r_j - r_i + S' @ cell with S' = s - fl_j + fl_i;
+    // the edge (source j -> target i) carries shift S = -S'.
+    auto test = [&](int k, int& j, int& S0, int& S1, int& S2) -> bool {
+      j = sorted_atoms[k];
+      S0 = -(s0 - img[3LL * j] + fi0); S1 = -(s1 - img[3LL * j + 1] + fi1); S2 = -(s2 - img[3LL * j + 2] + fi2);
+      if (j == i && S0 == 0 && S1 == 0 && S2 == 0) return false;
+      const double t0 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[0]), __dmul_rn((double)S1, gb.cell[3])), __dmul_rn((double)S2, gb.cell[6]));
+      const double t1 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[1]), __dmul_rn((double)S1, gb.cell[4])), __dmul_rn((double)S2, gb.cell[7]));
+      const double t2 = __dadd_rn(__dadd_rn(__dmul_rn((double)S0, gb.cell[2]), __dmul_rn((double)S1, gb.cell[5])), __dmul_rn((double)S2, gb.cell[8]));
+      const double dx = __dadd_rn(__dadd_rn(xi, -pos[3LL * j]), t0);
+      const double dy = __dadd_rn(__dadd_rn(yi, -pos[3LL * j + 1]), t1);
+      const double dz = __dadd_rn(__dadd_rn(zi, -pos[3LL * j + 2]), t2);
+      const double dsq = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+      return dsq < c2;
+    };
+    int n = 0, j, S0, S1, S2;
+    for (int k = k_beg; k < k_end; ++k) n += test(k, j, S0, S1, S2) ? 1 : 0;
+    int incl = n;  // inclusive scan over the lanes
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (FILL && n > 0) {
+      int64_t at = out + (incl - n);
+      for (int k = k_beg; k < k_end; ++k) {
+        if (test(k, j, S0, S1, S2)) {
+          if (at < n_edges) {
+            edge_index[at] = j;
+            edge_index[n_edges + at] = i;
+            shifts[3 * at] = S0; shifts[3 * at + 1] = S1; shifts[3 * at + 2] = S2;
           }
+          ++at;
         }
       }
     }
+    out += total;
+    count += total;
   }
-  if (!FILL) counts[i] = count;
+  if (!FILL && lane == 0) counts[i] = count;
 }
 
 int nl_run(bool fill, const double* pos, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr, int32_t n_graphs,
@@ -233,15 +257,16 @@ int nl_run(bool fill, const double* pos, const double* lattice, const uint8_t* p
   nl_setup_kernel<<<n_graphs, 128, 0, s>>>(pos, lattice, pbc, graph_ptr, cutoff, bins);
   nl_offsets_kernel<<<1, 1, 0, s>>>(bins, n_graphs, total);
   const int ab = (n_atoms + 127) / 128;
+  const unsigned wb = (unsigned)((n_atoms + 3) / 4);  // search kernels: one warp per atom, four warps per block
   nl_bin_kernel<<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, keys, vals, img);
   cudaError_t err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys, keys_sorted, vals, atoms_sorted, n_atoms, 0, 32, s);
   if (err == cudaSuccess) {
     nl_cell_start_kernel<<<(max_cells + 128) / 128, 128, 0, s>>>(keys_sorted, n_atoms, cell_start, max_cells);
     if (fill)
-      nl_search_kernel<true><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+      nl_search_kernel<true><<<wb, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
                                                 nullptr, row_ptr, n_edges, edge_index, shifts);
     else
-      nl_search_kernel<false><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+      nl_search_kernel<false><<<wb, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
                                                  counts, nullptr, 0, nullptr, nullptr);
     err = cudaGetLastError();
   }
@@ -326,14 +351,15 @@ int nl_build_noalloc(const double* pos, const double* lattice, const uint8_t* pb
   nl_setup_kernel<<<n_graphs, 128, 0, s>>>(pos, lattice, pbc, graph_ptr, cutoff, bins);
   nl_offsets_kernel<<<1, 1, 0, s>>>(bins, n_graphs, total);
   const int ab = (n_atoms + 127) / 128;
+  const unsigned wb = (unsigned)((n_atoms + 3) / 4);  // search kernels: one warp per atom, four warps per block
   nl_bin_kernel<<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, keys, vals, img);
   if (cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys, keys_sorted, vals, atoms_sorted, n_atoms, 0, 32, s) != cudaSuccess)
     return TACE_ERR_CUDA;
   nl_cell_start_kernel<<<(max_cells + 128) / 128, 128, 0, s>>>(keys_sorted, n_atoms, cell_start, max_cells);
-  nl_search_kernel<false><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+  nl_search_kernel<false><<<wb, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
                                              counts, nullptr, 0, nullptr, nullptr);
   nl_scan_counts_kernel<<<1, 1024, 0, s>>>(counts, n_atoms, row_ptr);
-  nl_search_kernel<true><<<ab, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
+  nl_search_kernel<true><<<wb, 128, 0, s>>>(pos, bins, graph_ptr, n_graphs, n_atoms, cutoff, keys, atoms_sorted, cell_start, img,
                                             nullptr, row_ptr, max_edges, edge_index, shifts);
   return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }

@@ -52,7 +52,7 @@ def test_triclinic_multi_element_batch(dtype):
 
 
 def test_config1_cu256_fp64():
-    """BASELINE config 1: FCC Cu 4x4x4, L=2, 64 channels, r_cut 5.0, fp64."""
+    """The fp64 reference-runnable configuration: FCC Cu 4x4x4, L=2, 64 channels, r_cut 5.0, fp64."""
     s = synth.workload_structures("cu256_fp64")[0]
     run_case([s], 2, 64, [29], 5.0, torch.float64)
 
@@ -125,7 +125,7 @@ def test_golden_model_case():
 
 
 def test_full_size_properties_config2():
-    """BASELINE config 2 at full size (64 crystals, L=3, 128 channels, 89 elements, fp32): properties that need
+    """The headline configuration at full size (64 crystals, L=3, 128 channels, 89 elements, fp32): properties that need
     no oracle - net force per crystal ~ 0, run-to-run bit reproducibility, energy unchanged by a rigid shift
     and by relabelling atoms inside the batch order of the edge list."""
     from tace_b200.graph import build_batch
