@@ -67,7 +67,17 @@ typedef struct {
   int env_after_mlp;  /* radial_basis.apply_cutoff = False: the polynomial envelope multiplies the output of the radial MLP
                          instead of the radial basis (tace/models/radial.py:974-993, _e3nn/inter.py:174-183) */
   int edge_update_element2; /* edge_update.type = element2: species embeddings of target and source are appended to the
-                         radial features (tace/models/_e3nn/edge.py:190-257); folded into the tables "t<i>.tdst" / "tsrc" */
+                         radial features (tace/models/_e3nn/edge.py:190-257); folded into the tables "t<i>.tdst" / "tsrc".
+                         As in the reference, edge features wider than the radial basis also put a LayerNorm before every
+                         hidden activation of the radial MLP (tace/models/_e3nn/base.py:183-185, tace/models/mlp.py:172-176):
+                         affine weights "t<i>.ln<j>g" / "t<i>.ln<j>b", [64] each */
+  int num_fidelities; /* entries of `statistics` (multi-head read-out, tace/models/_e3nn/readout.py:18-33,72-84): the
+                         read-out weights, species scales and isolated-atom energies carry a leading fidelity axis and
+                         TaceBatch.fidelity picks the head per graph; 0 means 1 */
+  int zbl;            /* short_range.zbl.enable (tace/models/radial.py:788-874, _e3nn/tace.py:387-408): 0 off; 1 pair
+                         repulsion added to the read-out before the species scale (scale_shift.scale_zbl = True);
+                         2 added after it.  Tables "zbl.z", "zbl.rcov" [num_elements] (atomic number, covalent radius)
+                         and "zbl.par" = {0.529 * a_prefactor, a_exp}; the envelope power is envelope_p */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by
@@ -89,6 +99,8 @@ typedef struct {
   const int64_t* edge_index; /* [2,n_edges]: row 0 = source, row 1 = target (any order) */
   const void* edge_shifts;   /* [n_edges,3] or NULL */
   const void* edge_vector;   /* [n_edges,3] or NULL */
+  const int32_t* fidelity;   /* [n_graphs] head of each graph (data["fidelity_idx"], tace/models/adapter.py:280-284),
+                                or NULL for head 0 */
 } TaceBatch;
 
 /* Outputs, any of which may be NULL to skip it.  Stands behind the dictionary returned by

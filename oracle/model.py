@@ -164,15 +164,18 @@ class MlpLinear(torch.nn.Module):
 
 
 class MLP(torch.nn.Module):
-    """tace/models/mlp.py:136-191 (plain SiLU, gain sqrt(2) after layer 0, optional bias on every layer)."""
+    """tace/models/mlp.py:136-191 (plain SiLU, gain sqrt(2) after layer 0, optional bias on every layer, optional
+    LayerNorm between every hidden linear and its activation)."""
 
-    def __init__(self, dims: List[int], bias: bool = False):
+    def __init__(self, dims: List[int], bias: bool = False, layer_norm: bool = False):
         super().__init__()
         mods = []
         for layer, (a, b) in enumerate(zip(dims, dims[1:])):
             gain = 1.0 if layer == 0 else math.sqrt(2.0)
             mods.append(MlpLinear(a, b, gain / math.sqrt(a), bias=bias))
             if layer != len(dims) - 2:
+                if layer_norm:
+                    mods.append(torch.nn.LayerNorm(b))
                 mods.append(torch.nn.SiLU())
         self.mlp = torch.nn.Sequential(*mods)
 
@@ -290,6 +293,37 @@ class RadialBasis(torch.nn.Module):
         return (radial * env, None) if self.apply_cutoff else (radial, env)
 
 
+class ZBLBasis(torch.nn.Module):
+    """tace/models/radial.py:788-874: screened nuclear repulsion (ZBL universal screening function) per pair, cut by the
+    polynomial envelope at the sum of the two covalent radii; half of every directed edge's energy goes to its target.
+    ``covalent_radii`` is a table indexed by atomic number (the reference reads ``ase.data.covalent_radii``)."""
+
+    def __init__(self, covalent_radii, p: int = 5):
+        super().__init__()
+        self.register_buffer("c", torch.tensor([0.1818, 0.5099, 0.2802, 0.02817]))
+        self.register_buffer("p", torch.tensor(p, dtype=torch.int))
+        self.register_buffer("covalent_radii", torch.as_tensor(covalent_radii, dtype=torch.get_default_dtype()))
+        self.register_buffer("a_exp", torch.tensor(0.300))
+        self.register_buffer("a_prefactor", torch.tensor(0.4543))
+
+    def forward(self, x, node_attrs, edge_index, atomic_numbers):
+        source, target = edge_index[0], edge_index[1]
+        z = atomic_numbers[torch.argmax(node_attrs, dim=1)].unsqueeze(-1)
+        zu, zv = z[source], z[target]
+        a = self.a_prefactor * 0.529 / (torch.pow(zu, self.a_exp) + torch.pow(zv, self.a_exp))
+        ra = x / a
+        phi = (self.c[0] * torch.exp(-3.2 * ra) + self.c[1] * torch.exp(-0.9423 * ra)
+               + self.c[2] * torch.exp(-0.4028 * ra) + self.c[3] * torch.exp(-0.2016 * ra))
+        v = (14.3996 * zu * zv) / x * phi
+        r_max = self.covalent_radii[zu] + self.covalent_radii[zv]
+        p = self.p.to(torch.int)
+        xr = x / r_max  # tace/models/radial.py:458-469 with a per-edge cutoff
+        env = (1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * torch.pow(xr, p) + p * (p + 2.0) * torch.pow(xr, p + 1)
+               - (p * (p + 1.0) / 2) * torch.pow(xr, p + 2)) * (x < r_max)
+        v = 0.5 * v * env
+        return scatter_sum(v, target, node_attrs.size(0)).squeeze(-1)
+
+
 class Element2EdgeUpdate(torch.nn.Module):
     """tace/models/_e3nn/edge.py:190-257: radial features followed by the species embeddings of the target and
     of the source (in that order; ``ElementEdgeUpdate`` has them the other way round)."""
@@ -322,7 +356,7 @@ class Interaction(torch.nn.Module):
     tace/models/_e3nn/base.py:113-249."""
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
-                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False):
+                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False, mlp_layer_norm=False):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
         C = num_channel
@@ -342,7 +376,10 @@ class Interaction(torch.nn.Module):
         self.nonlinearity = gate_cls(Irreps([(C, l) for _, l in self.irreps_out]))
         self.linear_nonlinearity = Linear(self.nonlinearity.irreps_out, self.irreps_out, bias=True)
         self.linear_down = Linear(tp_irreps_out.simplify(), self.nonlinearity.irreps_in, bias=True)
-        self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel], bias=mlp_bias)
+        # tace/models/_e3nn/base.py:183-185: edge features wider than the radial basis (an element-dependent edge
+        # update) switch LayerNorm on inside the radial MLP
+        self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel], bias=mlp_bias,
+                             layer_norm=mlp_layer_norm)
         if layer > 0:  # resnet type "BB", linear_type "aware", use_first_resnet False
             self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True, num_elements=num_elements)
 
@@ -438,7 +475,7 @@ class Representation(torch.nn.Module):
                 Interaction(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
                             cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
                             irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True),
-                            mlp_bias=rb.get("bias", False))
+                            mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2)
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],
@@ -463,22 +500,27 @@ class ScalarReadOut(torch.nn.Module):
     (``linear2``); earlier layers (only built with ``use_alllayer``): one linear from the scalar block of
     the layer's features to the energy (``linear1``)."""
 
-    def __init__(self, num_channel, hidden, irreps_in=None, last=True):
+    def __init__(self, num_channel, hidden, irreps_in=None, last=True, num_fidelities=1):
         super().__init__()
         self.last = last
-        if last:
-            dims = [num_channel] + list(hidden) + [1]
+        self.num_fidelities = nf = num_fidelities
+        if last:  # hidden widths and the output are multiplied by the number of fidelities (base.py:386-396)
+            dims = [num_channel] + [h * nf for h in hidden] + [nf]
             self.linear2 = torch.nn.ModuleList(
                 [Linear(Irreps([(a, 0)]), Irreps([(b, 0)]), bias=False) for a, b in zip(dims, dims[1:])]
             )
         else:
-            self.linear1 = torch.nn.ModuleList([Linear(Irreps(irreps_in), Irreps([(1, 0)]), bias=False)])
+            self.linear1 = torch.nn.ModuleList([Linear(Irreps(irreps_in), Irreps([(nf, 0)]), bias=False)])
 
-    def forward(self, x):
+    def forward(self, x, node_fidelity=None):
         if not self.last:
             return self.linear1[0](x)
         for lin in self.linear2[:-1]:
             x = SILU_CST * torch.nn.functional.silu(lin(x))
+            if self.num_fidelities > 1:  # readout.py:18-33 (mh_mask): only the hidden block of the atom's fidelity survives
+                mask = torch.zeros(x.shape[0], self.num_fidelities, x.shape[1] // self.num_fidelities, dtype=x.dtype)
+                mask[torch.arange(x.shape[0]), node_fidelity, :] = 1
+                x = x * mask.reshape(x.shape[0], -1)
         return self.linear2[-1](x)
 
 
@@ -528,7 +570,8 @@ def resolve_config(user_cfg: Dict) -> Dict:
         "edge_update": {"type": "identity"},
         "product_basis": {"correlation": 2},
         "readout_emlp": {"hidden": [16], "use_alllayer": False},
-        "scale_shift": {"scale_type": "rms_forces", "shift_type": None},
+        "scale_shift": {"scale_type": "rms_forces", "shift_type": None, "scale_zbl": True},
+        "short_range": {"zbl": {"enable": False}},
     }
     for k, v in copy.deepcopy(user_cfg).items():
         if isinstance(v, dict) and isinstance(cfg.get(k), dict):
@@ -558,12 +601,21 @@ class OracleTACE(torch.nn.Module):
         # tace/models/_e3nn/readout.py:192-221: one read-out per layer with use_alllayer, else only the last
         C, hid = cfg["num_channel"], cfg["readout_emlp"]["hidden"]
         self.use_alllayer = bool(cfg["readout_emlp"].get("use_alllayer", False))
+        nf = len(cfg["statistics"])  # one statistics entry per fidelity (tace/models/_e3nn/tace.py:75-76)
         if self.use_alllayer:
             prods = self.representation.products
             self.energy_readouts = torch.nn.ModuleList(
-                [ScalarReadOut(C, hid, irreps_in=prods[t].irreps_out, last=(t == len(prods) - 1)) for t in range(len(prods))])
+                [ScalarReadOut(C, hid, irreps_in=prods[t].irreps_out, last=(t == len(prods) - 1), num_fidelities=nf)
+                 for t in range(len(prods))])
         else:
-            self.energy_readouts = torch.nn.ModuleList([ScalarReadOut(C, hid)])
+            self.energy_readouts = torch.nn.ModuleList([ScalarReadOut(C, hid, num_fidelities=nf)])
+        zbl = cfg["short_range"]["zbl"]
+        if zbl.get("enable"):  # tace/models/_e3nn/tace.py:222-228
+            radii = torch.zeros(max(119, max(cfg["atomic_numbers"]) + 1))  # ase.data.covalent_radii has 119 entries
+            for z, r in zbl["covalent_radii"].items():
+                radii[int(z)] = float(r)
+            self.zbl = ZBLBasis(radii, cfg["radial_basis"]["polynomial_cutoff"])
+        self.scale_zbl = bool(cfg["scale_shift"].get("scale_zbl", True))
         self.atomic_energy_layer = AtomicEnergy(cfg["atomic_energies"], cfg["atomic_numbers"])
         sk, hk = cfg["scale_shift"]["scale_type"], cfg["scale_shift"]["shift_type"]
         scale_d, shift_d = [], []
@@ -588,7 +640,8 @@ class OracleTensorModel(torch.nn.Module):
         batch, ptr, edge_index = data["batch"], data["ptr"], data["edge_index"]
         num_graphs = ptr.numel() - 1
         n = node_attrs.shape[0]
-        node_fidelity = torch.zeros_like(batch)
+        # tace/models/adapter.py:280-284: the graph's fidelity for each of its atoms
+        node_fidelity = data["fidelity_idx"][batch] if "fidelity_idx" in data else torch.zeros_like(batch)
         arange = torch.arange(n)
         lmp = "edge_vector" in data and "positions" not in data
         inputs = []
@@ -617,10 +670,16 @@ class OracleTensorModel(torch.nn.Module):
         e_base_node = m.atomic_energy_layer(node_attrs)[arange, node_fidelity]
         e_base_graph = scatter_sum(e_base_node, batch, num_graphs)
         if m.use_alllayer:  # tace/models/_e3nn/tace.py:367-386: every layer's read-out, summed before scale / shift
-            e_node = sum(ro(d)[arange, node_fidelity] for ro, d in zip(m.energy_readouts, desc))
+            e_node = sum(ro(d, node_fidelity)[arange, node_fidelity] for ro, d in zip(m.energy_readouts, desc))
         else:
-            e_node = m.energy_readouts[0](desc[-1])[arange, node_fidelity]
+            e_node = m.energy_readouts[0](desc[-1], node_fidelity)[arange, node_fidelity]
+        if hasattr(m, "zbl"):  # tace/models/_e3nn/tace.py:387-408: before the scale when scale_zbl, after it otherwise
+            e_zbl = m.zbl(edge_length, node_attrs, edge_index, m.atomic_numbers)
+            if m.scale_zbl:
+                e_node = e_node + e_zbl
         e_node = m.scale_shift(e_node, node_attrs, ptr, edge_index, batch, node_fidelity)
+        if hasattr(m, "zbl") and not m.scale_zbl:
+            e_node = e_node + e_zbl
         e_graph = scatter_sum(e_node, batch, num_graphs)
         energy = e_base_graph + e_graph
         out = {"energy": energy.detach(), "node_energy": (e_base_node + e_node).detach(),

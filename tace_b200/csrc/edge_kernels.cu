@@ -118,7 +118,9 @@ __global__ void __launch_bounds__(128) edge_mlp_out_kernel(const EdgeArgs<T> a) 
       T g0, g1, g2, g3, z0, z1, z2, z3;
       ld4(g + 4 * j4, g0, g1, g2, g3);
       ld4(z + 4 * j4, z0, z1, z2, z3);
-      const T d0 = g0 * silu_grad_(z0), d1 = g1 * silu_grad_(z1), d2 = g2 * silu_grad_(z2), d3 = g3 * silu_grad_(z3);
+      // dH1 already holds dE/dz1 when the layer has a LayerNorm (ln_silu_bwd ran over it)
+      const T d0 = a.dz1_given ? g0 : g0 * silu_grad_(z0), d1 = a.dz1_given ? g1 : g1 * silu_grad_(z1),
+              d2 = a.dz1_given ? g2 : g2 * silu_grad_(z2), d3 = a.dz1_given ? g3 : g3 * silu_grad_(z3);
 #pragma unroll
       for (int k = 0; k < kNumBessel; ++k) {
         T a0, a1, a2, a3;
@@ -144,6 +146,118 @@ __global__ void silu_kernel(const T* __restrict__ in, T* __restrict__ out, long 
 template <typename T>
 __global__ void silu_grad_mul_kernel(T* __restrict__ g, const T* __restrict__ z, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) g[i] *= silu_grad_(z[i]);
+}
+// LayerNorm over the 64 features of a row (torch.nn.LayerNorm: biased variance, eps 1e-5, affine) followed by SiLU, as the
+// reference's radial MLP has it between a hidden linear and its activation when the edge features carry species
+// embeddings (tace/models/mlp.py:172-176, tace/models/_e3nn/base.py:183-185).  One warp per row, two features per lane.
+constexpr double kLnEps = 1e-5;
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) ln_silu_fwd_kernel(const T* __restrict__ z, const T* __restrict__ gamma,
+                                                          const T* __restrict__ beta, T* __restrict__ h, long long rows) {
+  const int lane = threadIdx.x & 31;
+  const long long r = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const T z0 = z[r * kHidden + lane], z1 = z[r * kHidden + 32 + lane];
+  const T mean = warp_sum(z0 + z1) * T(1.0 / kHidden);
+  const T c0 = z0 - mean, c1 = z1 - mean;
+  const T rstd = T(1) / sqrt(warp_sum(c0 * c0 + c1 * c1) * T(1.0 / kHidden) + T(kLnEps));
+  h[r * kHidden + lane] = silu_(c0 * rstd * gamma[lane] + beta[lane]);
+  h[r * kHidden + 32 + lane] = silu_(c1 * rstd * gamma[32 + lane] + beta[32 + lane]);
+}
+// g <- dE/dz given g = dE/d(silu(LN(z))); the row statistics are recomputed from z
+template <typename T>
+__global__ void __launch_bounds__(256) ln_silu_bwd_kernel(T* __restrict__ g, const T* __restrict__ z, const T* __restrict__ gamma,
+                                                          const T* __restrict__ beta, long long rows) {
+  const int lane = threadIdx.x & 31;
+  const long long r = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const T z0 = z[r * kHidden + lane], z1 = z[r * kHidden + 32 + lane];
+  const T mean = warp_sum(z0 + z1) * T(1.0 / kHidden);
+  const T c0 = z0 - mean, c1 = z1 - mean;
+  const T rstd = T(1) / sqrt(warp_sum(c0 * c0 + c1 * c1) * T(1.0 / kHidden) + T(kLnEps));
+  const T n0 = c0 * rstd, n1 = c1 * rstd;  // normalised features
+  const T d0 = g[r * kHidden + lane] * silu_grad_(n0 * gamma[lane] + beta[lane]) * gamma[lane];
+  const T d1 = g[r * kHidden + 32 + lane] * silu_grad_(n1 * gamma[32 + lane] + beta[32 + lane]) * gamma[32 + lane];
+  const T m1 = warp_sum(d0 + d1) * T(1.0 / kHidden);
+  const T m2 = warp_sum(d0 * n0 + d1 * n1) * T(1.0 / kHidden);
+  g[r * kHidden + lane] = rstd * (d0 - m1 - n0 * m2);
+  g[r * kHidden + 32 + lane] = rstd * (d1 - m1 - n1 * m2);
+}
+template <typename T>
+cudaError_t launch_ln_silu_fwd(const T* z, const T* gamma, const T* beta, T* h, long long rows, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  ln_silu_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(z, gamma, beta, h, rows);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_ln_silu_bwd(T* g, const T* z, const T* gamma, const T* beta, long long rows, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  ln_silu_bwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, z, gamma, beta, rows);
+  return cudaGetLastError();
+}
+// ---- ZBL pair repulsion (tace/models/radial.py:788-874) ------------------------------------------
+// energy of one directed edge (half of the pair energy) and its derivative with respect to the edge length
+template <typename T>
+__device__ __forceinline__ void zbl_pair(const ZblArgs<T>& a, int su, int sv, T d, T& v, T& dv) {
+  const T zu = a.z[su], zv = a.z[sv];
+  const T inv_a = (pow(zu, a.par[1]) + pow(zv, a.par[1])) / a.par[0];
+  const T x = d * inv_a;
+  const T c[4] = {T(0.1818), T(0.5099), T(0.2802), T(0.02817)};
+  const T k[4] = {T(3.2), T(0.9423), T(0.4028), T(0.2016)};
+  T phi = T(0), dphi = T(0);  // screening function and d phi / d d
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const T t = c[q] * exp(-k[q] * x);
+    phi += t; dphi -= k[q] * inv_a * t;
+  }
+  RadialParams<T> rp;
+  rp.rc = a.rcov[su] + a.rcov[sv]; rp.p = a.p;
+  T u, du;
+  envelope_eval<T>(d, rp, u, du);
+  const T pref = T(0.5 * 14.3996) * zu * zv;
+  const T coul = pref / d;
+  v = coul * phi * u;
+  dv = coul * ((dphi - phi / d) * u + phi * du);
+}
+template <typename T>
+__global__ void zbl_fwd_kernel(const ZblArgs<T> a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.n) return;
+  const int sv = a.species[i];
+  T acc = T(0);
+  for (int e = a.rowptr_dst[i]; e < a.rowptr_dst[i + 1]; ++e) {
+    T v, dv;
+    zbl_pair(a, a.species[a.e_src[e]], sv, a.dlen[e], v, dv);
+    acc += v;
+  }
+  a.node[i] = acc;
+}
+template <typename T>
+__global__ void zbl_bwd_kernel(const ZblArgs<T> a) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  const int i = a.e_dst[e];
+  T v, dv;
+  zbl_pair(a, a.species[a.e_src[e]], a.species[i], a.dlen[e], v, dv);
+  a.ddlen[e] += (a.factor ? a.factor[i] : T(1)) * dv;
+}
+template <typename T>
+cudaError_t launch_zbl_fwd(const ZblArgs<T>& a, cudaStream_t s) {
+  if (a.n <= 0) return cudaSuccess;
+  zbl_fwd_kernel<T><<<(a.n + 127) / 128, 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_zbl_bwd(const ZblArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  zbl_bwd_kernel<T><<<(unsigned)((a.E + 255) / 256), 256, 0, s>>>(a);
+  return cudaGetLastError();
 }
 template <typename T>
 cudaError_t launch_silu(const T* in, T* out, long long n, cudaStream_t s) {
@@ -298,6 +412,10 @@ cudaError_t launch_graph_virial(const T* atom_virial, const int* graph_ptr, cons
   template cudaError_t launch_edge_mlp_in<T>(const EdgeArgs<T>&, cudaStream_t);                      \
   template cudaError_t launch_edge_mlp_out<T>(const EdgeArgs<T>&, cudaStream_t);                     \
   template cudaError_t launch_silu<T>(const T*, T*, long long, cudaStream_t);                        \
+  template cudaError_t launch_zbl_fwd<T>(const ZblArgs<T>&, cudaStream_t);                           \
+  template cudaError_t launch_zbl_bwd<T>(const ZblArgs<T>&, cudaStream_t);                           \
+  template cudaError_t launch_ln_silu_fwd<T>(const T*, const T*, const T*, T*, long long, cudaStream_t); \
+  template cudaError_t launch_ln_silu_bwd<T>(T*, const T*, const T*, const T*, long long, cudaStream_t); \
   template cudaError_t launch_silu_grad_mul<T>(T*, const T*, long long, cudaStream_t);               \
   template cudaError_t launch_forces<T>(const ForceArgs<T>&, cudaStream_t);                          \
   template cudaError_t launch_graph_virial<T>(const T*, const int*, const T*, T*, T*, int, cudaStream_t);

@@ -165,7 +165,7 @@ struct ModelBase {
   // the caller's input and output pointers may change freely between calls.
   struct GraphKey {
     int64_t n_atoms, n_local, n_edges;
-    int32_t n_graphs, vec_mode;
+    int32_t n_graphs, vec_mode;  // vec_mode bit 0: edge-vector input; bit 1: a fidelity array is given
     uint32_t out_mask;
     void* ws;
     size_t ws_bytes;
@@ -184,7 +184,7 @@ struct ModelBase {
   long long graph_replays = 0;
 
   struct Stage {  // byte offsets (from the staging base) of the copies of every input and output
-    size_t positions, lattice, species, graph_ptr, edge_index, edge_shifts, edge_vector;
+    size_t positions, lattice, species, graph_ptr, edge_index, edge_shifts, edge_vector, fidelity;
     size_t energy, node_energy, forces, virials, stress, edge_forces, total;
   };
   Stage stage_layout(int64_t N, int64_t NL, int64_t E, int32_t B) const {
@@ -194,7 +194,7 @@ struct ModelBase {
     auto take = [&off](size_t bytes) { const size_t at = off; off += align256(bytes ? bytes : 1); return at; };
     st.positions = take(ts * 3 * N); st.lattice = take(ts * 9 * B); st.species = take(4 * (size_t)N);
     st.graph_ptr = take(4 * (size_t)(B + 1)); st.edge_index = take(16 * (size_t)E); st.edge_shifts = take(ts * 3 * E);
-    st.edge_vector = take(ts * 3 * E);
+    st.edge_vector = take(ts * 3 * E); st.fidelity = take(4 * (size_t)B);
     st.energy = take(ts * B); st.node_energy = take(ts * NL); st.forces = take(ts * 3 * N); st.virials = take(ts * 9 * B);
     st.stress = take(ts * 9 * B); st.edge_forces = take(ts * 3 * E);
     st.total = off;
@@ -216,12 +216,13 @@ struct ModelBase {
     if (ws_bytes < st.total + 256) return forward(bt, o, ws, ws_bytes, s);
     const size_t body_bytes = (ws_bytes - st.total) & ~size_t(255);
     unsigned char* sb = static_cast<unsigned char*>(ws) + body_bytes;
-    GraphKey key{N, NL, E, B, bt->edge_vector ? 1 : 0, 0u, ws, ws_bytes};
+    GraphKey key{N, NL, E, B, (bt->edge_vector ? 1 : 0) | (bt->fidelity ? 2 : 0), 0u, ws, ws_bytes};
+    const bool vec_in = bt->edge_vector != nullptr;
     const void* outs[6] = {o->energy, o->node_energy, o->forces, o->virials, o->stress, o->edge_forces};
     for (int k = 0; k < 6; ++k) if (outs[k]) key.out_mask |= 1u << k;
     // inputs the pass reads (all must be present for the staged path)
     if (!bt->species || !bt->graph_ptr || !bt->edge_index) return forward(bt, o, ws, ws_bytes, s);
-    if (!key.vec_mode && (!bt->positions || !bt->lattice || !bt->edge_shifts)) return forward(bt, o, ws, ws_bytes, s);
+    if (!vec_in && (!bt->positions || !bt->lattice || !bt->edge_shifts)) return forward(bt, o, ws, ws_bytes, s);
 
     GraphEntry* hit = nullptr;
     for (auto& g : graphs) if (g.key == key) hit = &g;
@@ -244,10 +245,11 @@ struct ModelBase {
       sbt.species = reinterpret_cast<const int32_t*>(sb + st.species);
       sbt.graph_ptr = reinterpret_cast<const int32_t*>(sb + st.graph_ptr);
       sbt.edge_index = reinterpret_cast<const int64_t*>(sb + st.edge_index);
-      sbt.positions = key.vec_mode ? nullptr : sb + st.positions;
-      sbt.lattice = key.vec_mode ? nullptr : sb + st.lattice;
-      sbt.edge_shifts = key.vec_mode ? nullptr : sb + st.edge_shifts;
-      sbt.edge_vector = key.vec_mode ? sb + st.edge_vector : nullptr;
+      sbt.positions = vec_in ? nullptr : sb + st.positions;
+      sbt.lattice = vec_in ? nullptr : sb + st.lattice;
+      sbt.edge_shifts = vec_in ? nullptr : sb + st.edge_shifts;
+      sbt.edge_vector = vec_in ? sb + st.edge_vector : nullptr;
+      sbt.fidelity = bt->fidelity ? reinterpret_cast<const int32_t*>(sb + st.fidelity) : nullptr;
       so.energy = o->energy ? sb + st.energy : nullptr;
       so.node_energy = o->node_energy ? sb + st.node_energy : nullptr;
       so.forces = o->forces ? sb + st.forces : nullptr;
@@ -288,7 +290,8 @@ struct ModelBase {
     };
     bool ok = copy(sb + st.species, bt->species, 4 * (size_t)N) && copy(sb + st.graph_ptr, bt->graph_ptr, 4 * (size_t)(B + 1)) &&
               copy(sb + st.edge_index, bt->edge_index, 16 * (size_t)E);
-    if (key.vec_mode) ok = ok && copy(sb + st.edge_vector, bt->edge_vector, ts * 3 * E);
+    if (bt->fidelity) ok = ok && copy(sb + st.fidelity, bt->fidelity, 4 * (size_t)B);
+    if (vec_in) ok = ok && copy(sb + st.edge_vector, bt->edge_vector, ts * 3 * E);
     else ok = ok && copy(sb + st.positions, bt->positions, ts * 3 * N) && copy(sb + st.lattice, bt->lattice, ts * 9 * B) &&
               copy(sb + st.edge_shifts, bt->edge_shifts, ts * 3 * E);
     if (!ok || cudaGraphLaunch(hit->exec, s) != cudaSuccess) return TACE_ERR_CUDA;
@@ -309,6 +312,8 @@ struct Model : ModelBase {
   bool mlp_bias = false;      // radial_basis.bias
   bool env_after = false;     // radial_basis.apply_cutoff = False: envelope multiplies the MLP output
   bool element2 = false;      // edge_update.type = element2
+  int n_fid = 1;              // read-out heads (entries of `statistics`)
+  int zbl = 0;                // 0 off, 1 ZBL repulsion inside the species scale, 2 outside it
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -347,6 +352,9 @@ struct Model : ModelBase {
     nh = (c.mlp_layers > 0) ? c.mlp_layers : 3;  // hidden layers of the radial MLP
     if (nh < 1 || nh > 3) return TACE_ERR_UNSUPPORTED_CONFIG;
     mlp_bias = c.mlp_bias != 0; env_after = c.env_after_mlp != 0; element2 = c.edge_update_element2 != 0;
+    n_fid = c.num_fidelities > 0 ? c.num_fidelities : 1;
+    zbl = c.zbl;
+    if (zbl < 0 || zbl > 2) return TACE_ERR_UNSUPPORTED_CONFIG;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     const int Dn = (Ln + 1) * (Ln + 1);
@@ -384,7 +392,14 @@ struct Model : ModelBase {
         if (nh >= 3) add_weight(pre + "b2", kHidden);
         add_weight(pre + "b3", (long long)p.tp.NP * C);
       }
-      if (element2) { add_weight(pre + "tdst", (long long)n_el * kHidden); add_weight(pre + "tsrc", (long long)n_el * kHidden); }
+      if (element2) {
+        add_weight(pre + "tdst", (long long)n_el * kHidden); add_weight(pre + "tsrc", (long long)n_el * kHidden);
+        // edge features wider than the radial basis put a LayerNorm before every hidden activation of the radial MLP
+        // (tace/models/_e3nn/base.py:183-185, tace/models/mlp.py:172-176): affine weights per hidden layer
+        for (int j = 0; j < nh; ++j) {
+          add_weight(pre + "ln" + std::to_string(j) + "g", kHidden); add_weight(pre + "ln" + std::to_string(j) + "b", kHidden);
+        }
+      }
       add_weight(pre + "W3", (long long)kHidden * p.tp.NP * C);
       add_weight(pre + "W3t", (long long)kHidden * p.tp.NP * C);
       if (kTensorCore) {  // TF32 high parts and residuals of both orientations
@@ -426,12 +441,13 @@ struct Model : ModelBase {
       add_weight(pre + "lin.b", C);
       if (p.has_res) add_weight(pre + "res.b", (long long)n_el * C);
     }
-    add_weight("ro.W1", (long long)C * H);
-    add_weight("ro.W2", H);
+    add_weight("ro.W1", (long long)n_fid * C * H);
+    add_weight("ro.W2", (long long)n_fid * H);
     if (c.use_alllayer)
-      for (int t = 0; t + 1 < NL_; ++t) add_weight("ro.lin" + std::to_string(t), C);
-    add_weight("scale", n_el);
-    add_weight("e0", n_el);
+      for (int t = 0; t + 1 < NL_; ++t) add_weight("ro.lin" + std::to_string(t), (long long)n_fid * C);
+    add_weight("scale", (long long)n_fid * n_el);
+    add_weight("e0", (long long)n_fid * n_el);
+    if (zbl) { add_weight("zbl.z", n_el); add_weight("zbl.rcov", n_el); add_weight("zbl.par", 2); }
     if (cudaMalloc(&arena, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
     if (cudaMemset(arena, 0, sizeof(T) * (size_t)arena_numel) != cudaSuccess) return TACE_ERR_CUDA;
     if (cudaMalloc(&dev_error, sizeof(int)) != cudaSuccess || cudaMemset(dev_error, 0, sizeof(int)) != cudaSuccess)
@@ -475,7 +491,7 @@ struct Model : ModelBase {
     int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
-    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor, *env, *denv;
+    T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor, *env, *denv, *zbl_node;
     std::vector<LayerBufs> lay;
   };
 
@@ -487,7 +503,7 @@ struct Model : ModelBase {
     b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
-    b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL);
+    b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL); b.zbl_node = zbl ? ar.take<T>(NL) : nullptr;
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
     b.env = env_after ? ar.take<T>(E) : nullptr; b.denv = env_after ? ar.take<T>(E) : nullptr;
     const bool chunked = E > max_chunk_edges;
@@ -677,20 +693,28 @@ struct Model : ModelBase {
     const EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
     CKL(launch_edge_mlp_in(er, s));
     const long long n64 = Ec * kHidden;
+    const bool ln = element2;  // LayerNorm before every hidden activation
     for (int j = 0; j < nh; ++j) {  // hidden layer j: activation, then (unless it is the last) the next 64 x 64 layer
       const bool last_hidden = (j == nh - 1);
       for (int t : ts) {
-        if (j == 0) break;  // launch_edge_mlp_in already wrote silu(Z1)
+        if (!ln && j == 0) break;  // launch_edge_mlp_in wrote silu(Z1) already
         const LayerBufs& lb = b.lay[t];
         const T* z = j == 0 ? lb.Z1 : j == 1 ? lb.Z2 : lb.Z3;
-        CKL(launch_silu(z, last_hidden ? lb.H3 : lb.Hact, n64, s));
+        T* h = last_hidden ? lb.H3 : lb.Hact;
+        if (ln) {
+          const std::string pre = "t" + std::to_string(t) + ".ln" + std::to_string(j);
+          CKL(launch_ln_silu_fwd(z, w(pre + "g"), w(pre + "b"), h, Ec, s));
+        } else {
+          CKL(launch_silu(z, h, n64, s));
+        }
       }
       if (last_hidden) break;
       std::vector<LinSpec> sp;
       for (int t : ts) {
         const std::string pre = "t" + std::to_string(t) + ".";
         const std::string an = j == 0 ? "A1" : "A2";
-        sp.push_back({b.lay[t].Hact, kHidden, 0, 1, kHidden, pre + an, pre + an + "t", kHidden, j == 0 ? b.lay[t].Z2 : b.lay[t].Z3, kHidden,
+        const LayerBufs& lb = b.lay[t];
+        sp.push_back({lb.Hact, kHidden, 0, 1, kHidden, pre + an, pre + an + "t", kHidden, j == 0 ? lb.Z2 : lb.Z3, kHidden,
                       0, mlp_bias ? w(pre + (j == 0 ? "b1" : "b2")) : nullptr});
       }
       CKL(run_linear(sp, Ec, s));
@@ -704,11 +728,17 @@ struct Model : ModelBase {
     const long long n64 = Ec * kHidden;
     // gradient buffer chain: H3 -> Hact -> Z3 (three hidden layers), H3 -> Hact (two), H3 (one); the first layer's
     // activation derivative is applied by launch_edge_mlp_out
+    const bool ln = element2;
     for (int j = nh - 1; j >= 1; --j) {
       for (int t : ts) {
         const LayerBufs& lb = b.lay[t];
         T* g = (j == nh - 1) ? lb.H3 : lb.Hact;
-        CKL(launch_silu_grad_mul(g, j == 1 ? lb.Z2 : lb.Z3, n64, s));
+        if (ln) {
+          const std::string pre = "t" + std::to_string(t) + ".ln" + std::to_string(j);
+          CKL(launch_ln_silu_bwd(g, j == 1 ? lb.Z2 : lb.Z3, w(pre + "g"), w(pre + "b"), Ec, s));
+        } else {
+          CKL(launch_silu_grad_mul(g, j == 1 ? lb.Z2 : lb.Z3, n64, s));
+        }
       }
       std::vector<LinSpec> sp;
       for (int t : ts) {
@@ -722,6 +752,13 @@ struct Model : ModelBase {
       CKL(run_linear(sp, Ec, s));
     }
     EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
+    if (ln) {  // through the first hidden layer's LayerNorm and activation; launch_edge_mlp_out then starts from dE/dz1
+      for (int t : ts) {
+        const std::string pre = "t" + std::to_string(t) + ".ln0";
+        CKL(launch_ln_silu_bwd(dh1_buffer(b.lay[t]), b.lay[t].Z1, w(pre + "g"), w(pre + "b"), Ec, s));
+      }
+      er.dz1_given = 1;
+    }
     er.accumulate_ddlen = accumulate;
     // the envelope term enters once: with the whole batch in one call, or with the last layer processed (layer 0)
     er.add_denv = (ts.size() > 1 || NL_ == 1 || ts[0] == 0) ? 1 : 0;
@@ -969,6 +1006,17 @@ struct Model : ModelBase {
     ra.scale = w("scale"); ra.e0 = w("e0"); ra.species = bt->species; ra.atom_graph = b.atom_graph;
     ra.graph_ptr = bt->graph_ptr; ra.rowptr_dst = b.rowptr_dst; ra.node_energy = static_cast<T*>(o->node_energy);
     ra.e_scaled = b.e_scaled; ra.gh = need_grad ? top.gh_out : nullptr; ra.n = (int)NL; ra.C = C; ra.H = H;
+    ra.fidelity = bt->fidelity; ra.n_el = n_el;
+    ZblArgs<T> za;
+    memset(&za, 0, sizeof(za));
+    if (zbl) {  // pair repulsion per atom, summed over the incoming edges
+      za.rowptr_dst = b.rowptr_dst; za.e_src = b.e_src; za.e_dst = b.e_dst; za.species = bt->species; za.dlen = b.dlen;
+      za.z = w("zbl.z"); za.rcov = w("zbl.rcov"); za.par = w("zbl.par"); za.p = cfg.envelope_p; za.n = (int)NL; za.E = E;
+      za.node = b.zbl_node;
+      CKL(launch_zbl_fwd(za, s));
+      ra.zbl = b.zbl_node; ra.zbl_after = (zbl == 2);
+      ra.factor = b.ro_factor;
+    }
     if (cfg.use_alllayer) {  // linear read-outs of the layers below the last
       ra.n_extra = NL_ - 1;
       for (int t = 0; t + 1 < NL_; ++t) {
@@ -977,7 +1025,8 @@ struct Model : ModelBase {
       ra.factor = b.ro_factor;
     }
     CKL(launch_readout(ra, s));
-    if (o->energy) CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, static_cast<T*>(o->energy), B, s));
+    if (o->energy)
+      CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, bt->fidelity, n_el, static_cast<T*>(o->energy), B, s));
     if (!need_grad) { PH("end"); return TACE_OK; }
 
     // ---- layers, backward
@@ -988,7 +1037,8 @@ struct Model : ModelBase {
       const std::string ts = std::to_string(t);
       PH(("t" + ts + ".bwd.node").c_str());
       if (cfg.use_alllayer && t + 1 < NL_)  // this layer's own linear read-out, on top of what the layer above sent down
-        CKL(launch_readout_linear_bwd(lb.gh_out, (long long)p.Dout * C, b.ro_factor, w("ro.lin" + ts), (int)NL, C, s));
+        CKL(launch_readout_linear_bwd(lb.gh_out, (long long)p.Dout * C, b.ro_factor, w("ro.lin" + ts), b.atom_graph, bt->fidelity,
+                                      (int)NL, C, s));
       {  // through the final linear
         std::vector<LinSpec> sp;
         for (int l : p.out_ls)
@@ -1115,6 +1165,10 @@ struct Model : ModelBase {
     // ---- back to the edge vectors, then forces and virials
     PH("radial_mlp_bwd");
     if (!chunked) CKS(radial_backward(ea, b, all_layers, 0, E, 0, s));  // lay[t].H3 holds dE/dh3 of each layer's radial MLP
+    if (zbl) {  // the repulsion's own dependence on the edge lengths
+      za.ddlen = b.ddlen; za.factor = (zbl == 1) ? b.ro_factor : nullptr;
+      CKL(launch_zbl_bwd(za, s));
+    }
     PH("edge_bwd");
     CKL(launch_edge_bwd(ea, s));
     debug.push_back({"g", b.g, 3 * E});

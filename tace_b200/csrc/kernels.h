@@ -87,13 +87,31 @@ struct ReadoutArgs {
   int n_extra;
   const T* extra_h[kMaxLayers]; long long extra_hs[kMaxLayers]; const T* extra_w[kMaxLayers];
   T* factor;         // [n] d(node energy)/d(read-out sum): the species scale, 0 for isolated atoms; or nullptr
+  // multi-head read-out (tace/models/_e3nn/readout.py:18-33): W1 [n_fid][C][H], W2 [n_fid][H], scale / e0 [n_fid][n_el],
+  // extra_w [n_fid][C]; fidelity[g] is the head of graph g (nullptr: head 0)
+  const int* fidelity; int n_el;
+  // pair repulsion per atom (launch_zbl_fwd) or nullptr; added before the species scale, or after it when zbl_after
+  const T* zbl; int zbl_after;
 };
-// gh[i * hs + c] += factor[i] * w[c]: gradient of an earlier layer's linear read-out
-template <typename T> cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, int n, int C, cudaStream_t s);
+// gh[i * hs + c] += factor[i] * w[f_i * C + c]: gradient of an earlier layer's linear read-out (f_i = head of atom i's graph)
+template <typename T> cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, const int* atom_graph,
+                                                           const int* fidelity, int n, int C, cudaStream_t s);
+// ZBL pair repulsion (tace/models/radial.py:788-874): v_e = 0.5 * 14.3996 Zu Zv / d * phi(d / a) * envelope(d, rcov_u + rcov_v)
+// with a = par[0] / (Zu^par[1] + Zv^par[1]).  Forward: node[i] = sum of v_e over the edges into i (target-sorted CSR);
+// backward: ddlen[e] += factor[target(e)] * dv_e/dd (factor == nullptr: 1).
+template <typename T>
+struct ZblArgs {
+  const int* rowptr_dst; const int* e_src; const int* e_dst; const int* species;
+  const T* dlen; const T* z; const T* rcov; const T* par; int p;
+  int n; long long E;
+  T* node; const T* factor; T* ddlen;
+};
+template <typename T> cudaError_t launch_zbl_fwd(const ZblArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_zbl_bwd(const ZblArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);
 // energy[g] = sum_{i in g} (e0[species_i] + e_scaled[i])
 template <typename T> cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr,
-                                                     T* energy, int n_graphs, cudaStream_t s);
+                                                     const int* fidelity, int n_el, T* energy, int n_graphs, cudaStream_t s);
 template <typename T> cudaError_t launch_fill_zero(T* p, long long n, cudaStream_t s);
 // dst[i] = src[perm[i]] (gather) / dst[perm[i]] = src[i] (scatter), rows of row_len elements
 template <typename T> cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);
@@ -133,6 +151,7 @@ struct EdgeArgs {
   T* env;                // [E] envelope values, written by launch_edge_fwd when the cutoff is applied after the MLP
   const T* denv;         // [E] dE/d(envelope) from the tensor-product backward passes (same case), or nullptr
   int add_denv;          // this launch_edge_mlp_out call adds the envelope term to ddlen
+  int dz1_given;         // dH1 holds dE/d(first pre-activation) already (LayerNorm models): launch_edge_mlp_out applies no silu'
   // backward
   const T* dY;           // [E][D]
   T* g;                  // [E][3] dE/d(edge vector), target-sorted order
@@ -145,6 +164,9 @@ template <typename T> cudaError_t launch_edge_mlp_in(const EdgeArgs<T>& a, cudaS
 template <typename T> cudaError_t launch_edge_mlp_out(const EdgeArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_silu(const T* in, T* out, long long n, cudaStream_t s);           // out = silu(in)
 template <typename T> cudaError_t launch_silu_grad_mul(T* g, const T* z, long long n, cudaStream_t s);     // g *= silu'(z)
+// rows of 64 features: h = silu(LayerNorm(z) * gamma + beta); g <- dE/dz from g = dE/dh (statistics recomputed from z)
+template <typename T> cudaError_t launch_ln_silu_fwd(const T* z, const T* gamma, const T* beta, T* h, long long rows, cudaStream_t s);
+template <typename T> cudaError_t launch_ln_silu_bwd(T* g, const T* z, const T* gamma, const T* beta, long long rows, cudaStream_t s);
 
 // forces[i] = -(sum_{e: target = i} g_e - sum_{e: source = i} g_e); per-atom virial rows
 // w[i] = sum_{e: target = i} v_e (x) g_e (tace/models/adapter.py:106-116, utils.py:50-79).

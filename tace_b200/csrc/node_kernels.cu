@@ -292,35 +292,39 @@ cudaError_t launch_pb3_bwd(const T* A, const T* B2, const T* gB3, T* gB2, T* gA,
 template <typename T>
 __global__ void readout_kernel(const ReadoutArgs<T> a) {
   extern __shared__ unsigned char smem_raw[];
-  T* W1s = reinterpret_cast<T*>(smem_raw);  // [C][H]
+  T* W1s = reinterpret_cast<T*>(smem_raw);  // [C][H]: head 0; other heads are read from global memory
   for (int k = threadIdx.x; k < a.C * a.H; k += blockDim.x) W1s[k] = a.W1[k];
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= a.n) return;
+  const int g = a.atom_graph[i];
+  const int f = a.fidelity ? a.fidelity[g] : 0;
+  const T* W1 = f == 0 ? W1s : a.W1 + (long long)f * a.C * a.H;
+  const T* W2 = a.W2 + f * a.H;
   const T* h = a.h + (long long)i * a.hs;
   T r[64];
   for (int j = 0; j < a.H; ++j) r[j] = T(0);
   for (int c = 0; c < a.C; ++c) {
     const T hc = h[c];
-    for (int j = 0; j < a.H; ++j) r[j] += hc * W1s[c * a.H + j];
+    for (int j = 0; j < a.H; ++j) r[j] += hc * W1[c * a.H + j];
   }
   T e = T(0);
   for (int j = 0; j < a.H; ++j) {
-    e += T(kSiluCst) * silu_(r[j]) * a.W2[j];
-    r[j] = T(kSiluCst) * silu_grad_(r[j]) * a.W2[j];  // d e / d r_j
+    e += T(kSiluCst) * silu_(r[j]) * W2[j];
+    r[j] = T(kSiluCst) * silu_grad_(r[j]) * W2[j];  // d e / d r_j
   }
   for (int t = 0; t < a.n_extra; ++t) {
     const T* ht = a.extra_h[t] + (long long)i * a.extra_hs[t];
     T acc = T(0);
-    for (int c = 0; c < a.C; ++c) acc += ht[c] * a.extra_w[t][c];
+    for (int c = 0; c < a.C; ++c) acc += ht[c] * a.extra_w[t][f * a.C + c];
     e += acc;
   }
-  const int z = a.species[i];
-  const int g = a.atom_graph[i];
+  if (a.zbl && !a.zbl_after) e += a.zbl[i];
+  const int z = f * a.n_el + a.species[i];
   const int n_nodes = a.graph_ptr[g + 1] - a.graph_ptr[g];
   const int n_edges = a.rowptr_dst[a.graph_ptr[g + 1]] - a.rowptr_dst[a.graph_ptr[g]];
   const T sc = (n_nodes == 1 && n_edges == 0) ? T(0) : a.scale[z];
-  const T es = e * sc;
+  const T es = (a.zbl && a.zbl_after) ? e * sc + a.zbl[i] : e * sc;
   a.e_scaled[i] = es;
   if (a.factor) a.factor[i] = sc;
   if (a.node_energy) a.node_energy[i] = a.e0[z] + es;
@@ -328,24 +332,26 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
     T* gh = a.gh + (long long)i * a.C;
     for (int c = 0; c < a.C; ++c) {
       T v = T(0);
-      for (int j = 0; j < a.H; ++j) v += r[j] * W1s[c * a.H + j];
+      for (int j = 0; j < a.H; ++j) v += r[j] * W1[c * a.H + j];
       gh[c] = v * sc;
     }
   }
 }
 template <typename T>
 __global__ void readout_linear_bwd_kernel(T* __restrict__ gh, long long hs, const T* __restrict__ factor, const T* __restrict__ w,
-                                          long long n, int C) {
+                                          const int* __restrict__ atom_graph, const int* __restrict__ fidelity, long long n, int C) {
   const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (k >= n * C) return;
   const long long i = k / C;
   const int c = (int)(k - i * C);
-  gh[i * hs + c] += factor[i] * w[c];
+  const int f = fidelity ? fidelity[atom_graph[i]] : 0;
+  gh[i * hs + c] += factor[i] * w[f * C + c];
 }
 template <typename T>
-cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, int n, int C, cudaStream_t s) {
+cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, const T* w, const int* atom_graph, const int* fidelity,
+                                      int n, int C, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  readout_linear_bwd_kernel<T><<<(unsigned)(((long long)n * C + 255) / 256), 256, 0, s>>>(gh, hs, factor, w, n, C);
+  readout_linear_bwd_kernel<T><<<(unsigned)(((long long)n * C + 255) / 256), 256, 0, s>>>(gh, hs, factor, w, atom_graph, fidelity, n, C);
   return cudaGetLastError();
 }
 
@@ -360,11 +366,12 @@ cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
 
 template <typename T>
 __global__ void graph_energy_kernel(const T* __restrict__ e_scaled, const T* __restrict__ e0, const int* __restrict__ species,
-                                    const int* __restrict__ graph_ptr, T* energy) {
+                                    const int* __restrict__ graph_ptr, const int* __restrict__ fidelity, int n_el, T* energy) {
   __shared__ T red[256];
   const int g = blockIdx.x;
+  const T* e0f = e0 + (fidelity ? fidelity[g] : 0) * n_el;
   T acc = T(0);
-  for (int i = graph_ptr[g] + threadIdx.x; i < graph_ptr[g + 1]; i += blockDim.x) acc += e0[species[i]] + e_scaled[i];
+  for (int i = graph_ptr[g] + threadIdx.x; i < graph_ptr[g + 1]; i += blockDim.x) acc += e0f[species[i]] + e_scaled[i];
   red[threadIdx.x] = acc;
   __syncthreads();
   for (int off = 128; off > 0; off >>= 1) {
@@ -374,10 +381,10 @@ __global__ void graph_energy_kernel(const T* __restrict__ e_scaled, const T* __r
   if (threadIdx.x == 0) energy[g] = red[0];
 }
 template <typename T>
-cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr, T* energy,
-                                int n_graphs, cudaStream_t s) {
+cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr, const int* fidelity,
+                                int n_el, T* energy, int n_graphs, cudaStream_t s) {
   if (n_graphs <= 0) return cudaSuccess;
-  graph_energy_kernel<T><<<n_graphs, 256, 0, s>>>(e_scaled, e0, species, graph_ptr, energy);
+  graph_energy_kernel<T><<<n_graphs, 256, 0, s>>>(e_scaled, e0, species, graph_ptr, fidelity, n_el, energy);
   return cudaGetLastError();
 }
 
@@ -385,7 +392,7 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_fill_zero<T>(T*, long long, cudaStream_t);                                      \
   template cudaError_t launch_pb3_fwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);           \
   template cudaError_t launch_pb3_bwd<T>(const T*, const T*, const T*, T*, T*, int, int, int, int, cudaStream_t); \
-  template cudaError_t launch_readout_linear_bwd<T>(T*, long long, const T*, const T*, int, int, cudaStream_t); \
+  template cudaError_t launch_readout_linear_bwd<T>(T*, long long, const T*, const T*, const int*, const int*, int, int, cudaStream_t); \
   template cudaError_t launch_add_inplace<T>(T*, const T*, long long, cudaStream_t);                          \
   template cudaError_t launch_gather_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);         \
   template cudaError_t launch_scatter_rows<T>(const T*, const int*, T*, long long, int, cudaStream_t);        \
@@ -395,7 +402,7 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
   template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
   template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \
-  template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, T*, int, cudaStream_t);
+  template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, const int*, int, T*, int, cudaStream_t);
 INST(float)
 INST(double)
 template cudaError_t launch_fill_zero<int>(int*, long long, cudaStream_t);

@@ -31,7 +31,7 @@ class TaceConfig(ctypes.Structure):
         ("correlation", c_int), ("num_bessel", c_int), ("mlp_hidden", c_int), ("envelope_p", c_int),
         ("readout_hidden", c_int), ("cutoff", c_double), ("avg_num_neighbors", c_double), ("Lnode", c_int),
         ("use_alllayer", c_int), ("gate_m0_off", c_int), ("mlp_layers", c_int), ("mlp_bias", c_int), ("env_after_mlp", c_int),
-        ("edge_update_element2", c_int),
+        ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int),
     ]
 
 
@@ -39,7 +39,7 @@ class TaceBatch(ctypes.Structure):
     _fields_ = [
         ("n_atoms", c_int64), ("n_local", c_int64), ("n_edges", c_int64), ("n_graphs", c_int32),
         ("positions", c_void_p), ("lattice", c_void_p), ("species", c_void_p), ("graph_ptr", c_void_p),
-        ("edge_index", c_void_p), ("edge_shifts", c_void_p), ("edge_vector", c_void_p),
+        ("edge_index", c_void_p), ("edge_shifts", c_void_p), ("edge_vector", c_void_p), ("fidelity", c_void_p),
     ]
 
 

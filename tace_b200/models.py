@@ -41,8 +41,8 @@ _DEFAULTS: Dict[str, Any] = {
                       "num_channel_per_expert": None, "use_shared_expert": False, "nonlinear": None, "agnostic": False},
     "readout_emlp": {"bias": False, "hidden": [16], "use_alllayer": False, "use_uie": False},
     "scale_shift": {"enable": True, "scale_type": "rms_forces", "shift_type": None, "scale_trainable": False,
-                    "shift_trainable": False, "all_atoms": False},
-    "short_range": {"zbl": {"enable": False}},
+                    "shift_trainable": False, "all_atoms": False, "scale_zbl": True},
+    "short_range": {"zbl": {"enable": False, "trainable": False}},
     "long_range": {"les": {"enable": False}},
     "dropout": {"use_first_dropout": False, "stochastic_depth": 0.0},
 }
@@ -80,7 +80,7 @@ def check_model_config(cfg: Dict) -> Dict:
     stats = cfg.get("statistics")
     if not isinstance(stats, (list, tuple)) or not stats:
         raise ValueError("statistics must be a non-empty list of dicts")
-    _require(len(stats) == 1, "one fidelity (multi-head read-outs are not built)")
+    _require(1 <= len(stats) <= 8, "one to eight fidelities (entries of statistics)")
     cfg["atomic_numbers"] = sorted({int(z) for s in stats for z in s["atomic_numbers"]})
     cfg["avg_num_neighbors"] = sum(float(s["avg_num_neighbors"]) for s in stats) / len(stats)
     cfg["atomic_energies"] = [s["atomic_energy"] for s in stats]
@@ -112,7 +112,8 @@ def check_model_config(cfg: Dict) -> Dict:
     hidden = list(cfg["radial_basis"]["hidden"])
     _require(1 <= len(hidden) <= 3 and all(h == 64 for h in hidden), "radial_basis.hidden: one to three layers of width 64")
     _require(len(cfg["readout_emlp"]["hidden"]) == 1 and cfg["readout_emlp"]["hidden"][0] <= 64, "one read-out hidden layer <= 64")
-    _require(not cfg["short_range"]["zbl"]["enable"], "no ZBL")
+    if cfg["short_range"]["zbl"]["enable"]:
+        cfg["short_range"]["zbl"]["covalent_radii"] = _covalent_radii(cfg)
     _require(not cfg["long_range"]["les"]["enable"], "no LES")
     _require(cfg["dropout"]["stochastic_depth"] == 0.0, "no stochastic depth")
 
@@ -129,6 +130,22 @@ def check_model_config(cfg: Dict) -> Dict:
     _require(len(set(corr)) == 1 and corr[0] in (1, 2, 3), "product_basis.correlation in {1, 2, 3}, equal on all layers")
     _require(corr[0] >= 2 or cfg["Lmax"] == cfg["lmax"], "Lmax == lmax when product_basis.correlation == 1")
     return cfg
+
+
+def _covalent_radii(cfg: Dict) -> Dict[int, float]:
+    """Covalent radius per element for the ZBL envelope.  The reference reads ``ase.data.covalent_radii``
+    (tace/models/radial.py:809-815); this does the same when ase is installed, and otherwise needs the radii of the
+    model's elements in ``short_range.zbl.covalent_radii`` (a {Z: radius in Angstrom} dictionary)."""
+    given = {int(k): float(v) for k, v in (cfg["short_range"]["zbl"].get("covalent_radii") or {}).items()}
+    missing = [z for z in cfg["atomic_numbers"] if z not in given]
+    if missing:
+        try:
+            from ase.data import covalent_radii as table
+        except ImportError:
+            _require(False, f"ZBL needs short_range.zbl.covalent_radii for elements {missing} when ase is not installed")
+        for z in missing:
+            given[z] = float(table[z])
+    return given
 
 
 def _set_nested(root: torch.nn.Module, dotted: str, tensor: torch.Tensor, buffer: bool) -> None:
@@ -174,7 +191,7 @@ class e3nnTACE(torch.nn.Module):
         super().__init__()
         self.cfg = cfg
         self.fidelity = [cfg["fidelity"]] if isinstance(cfg["fidelity"], dict) else cfg["fidelity"]
-        self.num_fidelities = 1
+        self.num_fidelities = len(cfg["statistics"])
         self.max_neighbors = None
         self.target_property = list(cfg["target_property"])
         self.num_layers = cfg["num_layers"]
@@ -190,7 +207,8 @@ class e3nnTACE(torch.nn.Module):
                               Lnode=cfg["Lmax"], use_alllayer=cfg["readout_emlp"]["use_alllayer"], gate_m0=cfg["atomic_basis"]["gate_m0"],
                               mlp_layers=len(cfg["radial_basis"]["hidden"]), mlp_bias=cfg["radial_basis"]["bias"],
                               apply_cutoff=cfg["radial_basis"]["apply_cutoff"],
-                              element2=cfg["edge_update"]["type"] == "element2")
+                              element2=cfg["edge_update"]["type"] == "element2", num_fidelities=self.num_fidelities,
+                              zbl=0 if not cfg["short_range"]["zbl"]["enable"] else (1 if cfg["scale_shift"]["scale_zbl"] else 2))
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
         for name, shape in self.plan.parameter_shapes().items():
@@ -198,6 +216,8 @@ class e3nnTACE(torch.nn.Module):
                 value = torch.zeros(shape, dtype=dt)
             elif ".edge_updates." in name:  # tace/models/_e3nn/edge.py:216-221
                 value = torch.empty(shape, dtype=dt).uniform_(-0.001, 0.001)
+            elif ".edge_info.mlp." in name and len(shape) == 1:  # LayerNorm scale (torch.nn.LayerNorm default)
+                value = torch.ones(shape, dtype=dt)
             elif ".edge_info.mlp." in name:
                 value = torch.empty(shape, dtype=dt).uniform_(-math.sqrt(3.0), math.sqrt(3.0))
             else:
@@ -220,6 +240,16 @@ class e3nnTACE(torch.nn.Module):
         _set_nested(self, "scale_shift.scale", torch.tensor(scale, dtype=dt), True)
         _set_nested(self, "scale_shift.shift", torch.zeros(len(scale), len(zs), dtype=dt), True)
         _set_nested(self, "scale_shift.atomic_numbers", torch.tensor(zs, dtype=torch.int64), True)
+        if cfg["short_range"]["zbl"]["enable"]:  # buffers of the reference's ZBLBasis (tace/models/radial.py:797-819)
+            _require(not cfg["short_range"]["zbl"].get("trainable", False), "short_range.zbl.trainable = False")
+            radii = torch.zeros(max(119, max(zs) + 1), dtype=dt)
+            for z, r in cfg["short_range"]["zbl"]["covalent_radii"].items():
+                radii[int(z)] = float(r)
+            _set_nested(self, "zbl.c", torch.tensor([0.1818, 0.5099, 0.2802, 0.02817], dtype=dt), True)
+            _set_nested(self, "zbl.p", torch.tensor(cfg["radial_basis"]["polynomial_cutoff"], dtype=torch.int), True)
+            _set_nested(self, "zbl.covalent_radii", radii, True)
+            _set_nested(self, "zbl.a_exp", torch.tensor(0.300), True)
+            _set_nested(self, "zbl.a_prefactor", torch.tensor(0.4543), True)
 
     def forward(self, data, graph=None):
         raise RuntimeError("call the TensorModel wrapper; the model body runs inside libtace_b200.so")
@@ -238,7 +268,7 @@ class TensorModel(torch.nn.Module):
     def __init__(self, readout_fn: e3nnTACE):
         super().__init__()
         self.readout_fn = readout_fn
-        self.num_fidelities = 1
+        self.num_fidelities = readout_fn.num_fidelities
         self.lmp = False
         self.fidelity_idx = 0
         self._handle = None
@@ -254,8 +284,11 @@ class TensorModel(torch.nn.Module):
         return int(self.fidelity_idx)
 
     def reset_fidelity_idx(self, fidelity_idx: Union[int, None] = 0) -> None:
-        if fidelity_idx not in (None, 0):
-            raise NotImplementedError("single-fidelity models only")
+        """tace/models/adapter.py:389-391: the head used when ``data`` carries no ``fidelity_idx``."""
+        if fidelity_idx is not None:
+            if not 0 <= int(fidelity_idx) < self.num_fidelities:
+                raise ValueError(f"fidelity_idx {fidelity_idx} outside 0..{self.num_fidelities - 1}")
+            self.fidelity_idx = int(fidelity_idx)
 
     def get_embedding_property(self) -> List[str]:
         return []
@@ -306,7 +339,8 @@ class TensorModel(torch.nn.Module):
             mlp_hidden=plan.mlp_hidden, envelope_p=int(rf.cfg["radial_basis"]["polynomial_cutoff"]), readout_hidden=plan.H,
             cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
             use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,
-            mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2))
+            mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2),
+            num_fidelities=plan.n_fid, zbl=plan.zbl)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")
@@ -404,6 +438,15 @@ class TensorModel(torch.nn.Module):
         keep.append(graph_ptr)
         batch.n_atoms, batch.n_local, batch.n_edges, batch.n_graphs = n_atoms, n_local, E, n_graphs
         batch.species, batch.graph_ptr, batch.edge_index = species.data_ptr(), graph_ptr.data_ptr(), edge_index.data_ptr()
+        if self.num_fidelities > 1:  # tace/models/adapter.py:280-284
+            if "fidelity_idx" in data:
+                fid = data["fidelity_idx"].to(device=device, dtype=torch.int32).contiguous()
+                if fid.numel() != n_graphs or int(fid.min()) < 0 or int(fid.max()) >= self.num_fidelities:
+                    raise ValueError("fidelity_idx must hold one head index in 0..num_fidelities-1 per graph")
+            else:
+                fid = torch.full((n_graphs,), int(self.fidelity_idx), dtype=torch.int32, device=device)
+            keep.append(fid)
+            batch.fidelity = fid.data_ptr()
 
         out = _lib.TaceOutputs()
         res: Dict[str, Optional[torch.Tensor]] = {k: None for k in

@@ -60,16 +60,28 @@ class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
-                 apply_cutoff: bool = True, element2: bool = False):
+                 apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
         self.use_alllayer = bool(use_alllayer)
+        # read-out heads (one per `statistics` entry); ZBL repulsion: 0 off, 1 inside the species scale, 2 outside
+        self.n_fid, self.zbl = int(num_fidelities), int(zbl)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
         self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
         self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation) for t in range(num_layers)]
+
+    @property
+    def mlp_layer_norm(self) -> bool:
+        """Edge features wider than the radial basis (the element-dependent edge update) put a LayerNorm between every
+        hidden linear of the radial MLP and its activation (tace/models/_e3nn/base.py:183-185, tace/models/mlp.py:172-176)."""
+        return self.element2
+
+    def mlp_index(self, i: int) -> int:
+        """Position of the i-th linear inside the radial MLP's ``Sequential`` (linear, [LayerNorm], SiLU, ...)."""
+        return (3 if self.mlp_layer_norm else 2) * i
 
     def parameter_shapes(self) -> Dict[str, tuple]:
         """Reference parameter names (without the ``readout_fn.`` prefix) and shapes."""
@@ -82,9 +94,12 @@ class ModelPlan:
             edge_dim = self.num_bessel + (2 * C if self.element2 else 0)
             dims = [edge_dim] + [self.mlp_hidden] * self.mlp_layers + [len(lp.tp_paths) * C]
             for i, (a, b) in enumerate(zip(dims, dims[1:])):
-                out[pre + f"edge_info.mlp.{2 * i}.weight"] = (a, b)
+                out[pre + f"edge_info.mlp.{self.mlp_index(i)}.weight"] = (a, b)
                 if self.mlp_bias:
-                    out[pre + f"edge_info.mlp.{2 * i}.bias"] = (b,)
+                    out[pre + f"edge_info.mlp.{self.mlp_index(i)}.bias"] = (b,)
+                if self.mlp_layer_norm and i < self.mlp_layers:
+                    out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.weight"] = (b,)
+                    out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.bias"] = (b,)
             if self.element2:  # tace/models/_e3nn/edge.py:190-257
                 out[f"representation.edge_updates.{lp.t}.source_embedding.weight"] = (n_el * C,)
                 out[f"representation.edge_updates.{lp.t}.target_embedding.weight"] = (n_el * C,)
@@ -112,9 +127,10 @@ class ModelPlan:
         ro = self.num_layers - 1 if self.use_alllayer else 0
         if self.use_alllayer:
             for t in range(self.num_layers - 1):
-                out[f"energy_readouts.{t}.linear1.0.weight"] = (C,)
-        out[f"energy_readouts.{ro}.linear2.0.weight"] = (C * self.H,)
-        out[f"energy_readouts.{ro}.linear2.1.weight"] = (self.H,)
+                out[f"energy_readouts.{t}.linear1.0.weight"] = (C * self.n_fid,)
+        # hidden width and output count are multiplied by the number of heads (tace/models/_e3nn/base.py:386-396)
+        out[f"energy_readouts.{ro}.linear2.0.weight"] = (C * self.H * self.n_fid,)
+        out[f"energy_readouts.{ro}.linear2.1.weight"] = (self.H * self.n_fid * self.n_fid,)
         return out
 
 
@@ -162,7 +178,7 @@ def pad_channels(out: Dict[str, np.ndarray], C: int, Cp: int) -> None:
         if name == "emb":
             out[name] = _pad_axis(arr, -1, C, Cp)
         elif name == "ro.W1":
-            out[name] = _pad_axis(arr, 0, C, Cp)
+            out[name] = _pad_axis(arr, -2, C, Cp)
         elif name.startswith("ro.lin"):
             out[name] = _pad_axis(arr, -1, C, Cp)
         elif len(parts) >= 2 and parts[0].startswith("t") and parts[0][1:].isdigit():
@@ -221,15 +237,20 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
             semb = g(eu + "source_embedding.weight").reshape(n_el, C) / math.sqrt(n_el)
             out[tp + "tdst"] = temb @ w0[nb:nb + C] / math.sqrt(w0.shape[0])
             out[tp + "tsrc"] = semb @ w0[nb + C:nb + 2 * C] / math.sqrt(w0.shape[0])
+        mi = plan.mlp_index
         if nh >= 2:
-            put(tp + "A1", g(pre + "edge_info.mlp.2.weight") * math.sqrt(2.0 / hd), tp + "A1t")
+            put(tp + "A1", g(pre + f"edge_info.mlp.{mi(1)}.weight") * math.sqrt(2.0 / hd), tp + "A1t")
         if nh >= 3:
-            put(tp + "A2", g(pre + "edge_info.mlp.4.weight") * math.sqrt(2.0 / hd), tp + "A2t")
-        put(tp + "W3", g(pre + f"edge_info.mlp.{2 * nh}.weight") * math.sqrt(2.0 / hd), tp + "W3t")
+            put(tp + "A2", g(pre + f"edge_info.mlp.{mi(2)}.weight") * math.sqrt(2.0 / hd), tp + "A2t")
+        put(tp + "W3", g(pre + f"edge_info.mlp.{mi(nh)}.weight") * math.sqrt(2.0 / hd), tp + "W3t")
         if plan.mlp_bias:
             for j in range(nh):
-                out[tp + f"b{j}"] = g(pre + f"edge_info.mlp.{2 * j}.bias")
-            out[tp + "b3"] = g(pre + f"edge_info.mlp.{2 * nh}.bias")
+                out[tp + f"b{j}"] = g(pre + f"edge_info.mlp.{mi(j)}.bias")
+            out[tp + "b3"] = g(pre + f"edge_info.mlp.{mi(nh)}.bias")
+        if plan.mlp_layer_norm:
+            for j in range(nh):
+                out[tp + f"ln{j}g"] = g(pre + f"edge_info.mlp.{mi(j) + 1}.weight")
+                out[tp + f"ln{j}b"] = g(pre + f"edge_info.mlp.{mi(j) + 1}.bias")
         down_shapes = [(lp.k[l] * C, ((L + 2) * C if plan.gate_m0 else (L + 1) * C) if l == 0 else C) for l in range(L + 1)]
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
             put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
@@ -257,11 +278,17 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
                 put(tp + f"res.l{l}", m / math.sqrt(C), tp + f"resT.l{l}")
             out[tp + "res.b"] = g(pre + "resnetBB.bias")
     ro = plan.num_layers - 1 if plan.use_alllayer else 0
-    out["ro.W1"] = g(f"energy_readouts.{ro}.linear2.0.weight").reshape(C, plan.H) / math.sqrt(C)
-    out["ro.W2"] = g(f"energy_readouts.{ro}.linear2.1.weight").reshape(plan.H) / math.sqrt(plan.H)
+    # multi-head read-out (tace/models/_e3nn/readout.py:18-33,72-84): the hidden layer is [head][H] wide, the mask keeps
+    # the block of the atom's head and the head's output column is taken, so head f only ever uses W1[:, f, :] and
+    # W2[f, :, f]; the second linear's fan-in is the full hidden width
+    nf, H = plan.n_fid, plan.H
+    w1 = g(f"energy_readouts.{ro}.linear2.0.weight").reshape(C, nf, H) / math.sqrt(C)
+    w2 = g(f"energy_readouts.{ro}.linear2.1.weight").reshape(nf, H, nf) / math.sqrt(H * nf)
+    out["ro.W1"] = np.ascontiguousarray(np.transpose(w1, (1, 0, 2)))
+    out["ro.W2"] = np.stack([w2[f, :, f] for f in range(nf)])
     if plan.use_alllayer:
         for t in range(plan.num_layers - 1):
-            out[f"ro.lin{t}"] = g(f"energy_readouts.{t}.linear1.0.weight").reshape(C) / math.sqrt(C)
+            out[f"ro.lin{t}"] = np.ascontiguousarray(g(f"energy_readouts.{t}.linear1.0.weight").reshape(C, nf).T) / math.sqrt(C)
     pad_channels(out, C, plan.Cp)
     # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
     for name in list(out):
@@ -275,8 +302,13 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
                 # [species][K/32][N][32], so every operand block of the tensor-core GEMM is contiguous
                 hi, lo = tile_k_major(hi), tile_k_major(lo)
             out[name + "_hi"], out[name + "_lo"] = hi, lo
-    out["scale"] = g("scale_shift.scale")[0]
-    out["e0"] = g("atomic_energy_layer.atomic_energy")[0]
+    out["scale"] = g("scale_shift.scale").reshape(nf, n_el)
+    out["e0"] = g("atomic_energy_layer.atomic_energy").reshape(nf, n_el)
+    if plan.zbl:  # tace/models/radial.py:788-874
+        zs = g("atomic_numbers").reshape(-1).astype(np.int64)
+        out["zbl.z"] = zs.astype(np.float64)
+        out["zbl.rcov"] = g("zbl.covalent_radii").reshape(-1)[zs]
+        out["zbl.par"] = np.array([0.529 * float(g("zbl.a_prefactor")), float(g("zbl.a_exp"))])
     shift = g("scale_shift.shift")
     if np.any(shift != 0.0):
         raise NotImplementedError("a non-zero energy shift (scale_shift.shift_type) is not supported")

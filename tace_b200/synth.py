@@ -133,33 +133,35 @@ def collate(structures: Sequence[Structure]) -> Dict[str, np.ndarray]:
     }
 
 
-def statistics(atomic_numbers: Sequence[int], avg_num_neighbors: float) -> List[Dict]:
-    """The statistics list the model constructor consumes (tace/models/_e3nn/default.py:251-280):
-    zero isolated-atom energies, unit force scale."""
+def statistics(atomic_numbers: Sequence[int], avg_num_neighbors: float, num_fidelities: int = 1) -> List[Dict]:
+    """The statistics list the model constructor consumes (tace/models/_e3nn/default.py:251-280), one entry per
+    fidelity: zero isolated-atom energies, unit force scale."""
     zs = sorted(int(z) for z in set(atomic_numbers))
     return [{
         "atomic_numbers": zs,
         "avg_num_neighbors": float(avg_num_neighbors),
         "atomic_energy": {z: 0.0 for z in zs},
         "rms_forces": {z: 1.0 for z in zs},
-    }]
+    } for _ in range(num_fidelities)]
 
 
 def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], avg_num_neighbors: float,
                  num_layers: int = 2, correlation: int = 2, target_property=("energy", "forces", "stress"),
                  Lmax: int = None, use_alllayer: bool = False, gate_m0: bool = True, radial: Dict = None,
-                 edge_update: str = "identity") -> Dict:
+                 edge_update: str = "identity", num_fidelities: int = 1, zbl: Dict = None, scale_zbl: bool = True) -> Dict:
     """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product).  ``L`` is the edge
     rank ``lmax``; the node rank ``Lmax`` defaults to it."""
     return {
         "Lmax": L if Lmax is None else Lmax, "lmax": L, "num_layers": num_layers, "num_channel": channels, "cutoff": float(cutoff),
-        "statistics": statistics(elements, avg_num_neighbors),
+        "statistics": statistics(elements, avg_num_neighbors, num_fidelities),
         "target_property": list(target_property), "max_neighbors": None,
         "product_basis": {"correlation": correlation},
         "readout_emlp": {"use_alllayer": bool(use_alllayer)},
         "atomic_basis": {"gate_m0": bool(gate_m0)},
         "radial_basis": dict(radial or {}),
         "edge_update": {"type": edge_update},
+        "short_range": {"zbl": dict(zbl or {"enable": False})},
+        "scale_shift": {"scale_zbl": bool(scale_zbl)},
     }
 
 

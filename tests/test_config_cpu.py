@@ -34,8 +34,13 @@ def test_example_training_configuration_is_accepted_and_builds():
     sd = model.state_dict()
     assert sd["readout_fn.representation.interactions.0.edge_info.mlp.0.weight"].shape == (8 + 2 * 48, 64)
     assert sd["readout_fn.representation.edge_updates.2.target_embedding.weight"].shape == (3 * 48,)
-    assert "readout_fn.representation.interactions.0.edge_info.mlp.4.bias" in sd
-    assert "readout_fn.representation.interactions.0.edge_info.mlp.6.weight" not in sd
+    # edge features wider than the radial basis: linear, LayerNorm, SiLU, linear, LayerNorm, SiLU, linear
+    assert sd["readout_fn.representation.interactions.0.edge_info.mlp.1.weight"].shape == (64,)
+    assert sd["readout_fn.representation.interactions.0.edge_info.mlp.3.weight"].shape == (64, 64)
+    assert sd["readout_fn.representation.interactions.0.edge_info.mlp.4.bias"].shape == (64,)
+    assert "readout_fn.representation.interactions.0.edge_info.mlp.6.bias" in sd
+    assert "readout_fn.representation.interactions.0.edge_info.mlp.2.weight" not in sd
+    assert "readout_fn.representation.interactions.0.edge_info.mlp.9.weight" not in sd
 
 
 @pytest.mark.parametrize("override,needle", [

@@ -16,9 +16,11 @@ pytestmark = pytest.mark.gpu
 TOL = {torch.float64: (1e-8, 1e-7), torch.float32: (1e-5, 1e-4)}
 
 
-def run_case(structures, L, C, elements, cutoff, dtype, **kw):
+def run_case(structures, L, C, elements, cutoff, dtype, fidelity_idx=None, **kw):
     model, oracle, cfg = make_models(L, C, elements, cutoff, 20.0, dtype, **kw)
     data = oracle_batch(structures, elements, cutoff, dtype)
+    if fidelity_idx is not None:
+        data["fidelity_idx"] = torch.tensor(fidelity_idx, dtype=torch.int64)
     ref = oracle(data)
     out = model(to_device(data, torch.device("cuda:0")))
     torch.cuda.synchronize()
@@ -327,3 +329,47 @@ def test_channel_counts_that_are_not_multiples_of_32(C, dtype):
     structs = synth.random_crystals(2, seed=59, nmin=4, nmax=9, zmax=3)
     run_case(structs, 3, C, [1, 2, 3], 4.5, dtype, Lmax=2, gate_m0=False, edge_update="element2",
              radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]}, num_layers=3 if dtype == torch.float64 else 2)
+
+
+@pytest.mark.parametrize("use_alllayer", [False, True])
+def test_multi_fidelity_read_out(use_alllayer):
+    """Three read-out heads (three `statistics` entries): every graph is evaluated with the head its `fidelity_idx`
+    names; species scales and isolated-atom energies are per head.  Repeated calls (CUDA-graph replay) follow a
+    changed `fidelity_idx`; without the key the head set by reset_fidelity_idx is used."""
+    structs = synth.random_crystals(3, seed=21, nmin=4, nmax=10, zmax=3)
+    dev = torch.device("cuda:0")
+    model, oracle, _ = make_models(2, 32, [1, 2, 3], 4.5, 20.0, torch.float64, num_fidelities=3, use_alllayer=use_alllayer)
+    data = oracle_batch(structs, [1, 2, 3], 4.5, torch.float64)
+    seen = []
+    for fid in ([2, 0, 1], [2, 0, 1], [1, 1, 0], [0, 2, 2]):
+        data["fidelity_idx"] = torch.tensor(fid, dtype=torch.int64)
+        ref = oracle(data)
+        out = model(to_device(data, dev))
+        assert (out["energy"].cpu() - ref["energy"]).abs().max().item() < 1e-8 * 10
+        assert (out["node_energy"].cpu() - ref["node_energy"]).abs().max().item() < 1e-8
+        assert (out["forces"].cpu() - ref["forces"]).abs().max().item() < 1e-7 * max(1.0, ref["forces"].abs().max().item())
+        assert (out["stress"].cpu() - ref["stress"]).abs().max().item() < 1e-6
+        seen.append(ref["energy"])
+    assert model.graph_replays() >= 2
+    assert (seen[0] - seen[2]).abs().max() > 1e-3  # the heads really differ
+    del data["fidelity_idx"]
+    model.reset_fidelity_idx(1)
+    data1 = dict(data, fidelity_idx=torch.tensor([1, 1, 1]))
+    out = model(to_device(data, dev))
+    assert (out["energy"].cpu() - oracle(data1)["energy"]).abs().max().item() < 1e-7
+    with pytest.raises(ValueError):
+        model(to_device(dict(data, fidelity_idx=torch.tensor([0, 3, 1])), dev))
+    assert model.device_error() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("scale_zbl", [True, False])
+def test_zbl_pair_repulsion(dtype, scale_zbl):
+    """short_range.zbl: screened nuclear repulsion inside the sum of the covalent radii, added to the read-out before
+    (scale_zbl) or after the species scale; radii are given in the configuration (no ase here), chosen so that a good
+    share of the pairs sits inside the envelope."""
+    structs = synth.random_crystals(3, seed=23, nmin=4, nmax=10, zmax=3)
+    zbl = {"enable": True, "covalent_radii": {1: 0.9, 2: 1.3, 3: 1.6}}
+    out, ref = run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, zbl=zbl, scale_zbl=scale_zbl)
+    base, _ = run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype)
+    assert (out["energy"] - base["energy"]).abs().max().item() > 1e-2  # the term is really there
