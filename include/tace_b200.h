@@ -78,6 +78,11 @@ typedef struct {
                          repulsion added to the read-out before the species scale (scale_shift.scale_zbl = True);
                          2 added after it.  Tables "zbl.z", "zbl.rcov" [num_elements] (atomic number, covalent radius)
                          and "zbl.par" = {0.529 * a_prefactor, a_exp}; the envelope power is envelope_p */
+  int scatter_norm_density; /* atomic_basis.scatter_norm (tace/models/_e3nn/inter.py:102-110,249-260, base.py:240-249):
+                         0 messages / avg_num_neighbors (folded into the packed linear_down weights); 1 "density": messages
+                         / (beta * sum over incoming edges of tanh(MLP(radial)^2) [* envelope when env_after_mlp] + alpha);
+                         2 "no_cutoff_density": the same without the envelope factor.  Weights "t<i>.dA0" [8][64], "dw1" [64],
+                         "dab" = {alpha, beta} (+ "db0" [64], "db1" [1] with mlp_bias); not with edge_update_element2 */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by
@@ -258,6 +263,10 @@ int tace_nl_build_noalloc(const double* positions, const double* lattice, const 
  *   when positions == NULL).  positions / velocities fp64 [n_atoms,3]; forces [n_atoms,3] in force_dtype
  *   (TACE_F32 / TACE_F64); inv_mass fp64 [n_atoms].  Units are the caller's (kick carries dt/2 and the
  *   unit conversion).
+ * tace_md_langevin: v_i <- c1 v_i + sqrt((1 - c1^2) * kt_scaled * inv_mass_i) * xi with xi standard normal: the exact
+ *   Ornstein-Uhlenbeck update over one step, c1 = exp(-friction * dt); kt_scaled is k_B T in the caller's velocity
+ *   units (mass * velocity^2).  xi is a pure function of (seed, step, ids[i] or i, component): the same trajectory for
+ *   any distribution of the atoms over ranks.  (The reference runs thermostats through ASE or LAMMPS.)
  * tace_md_kinetic_energy: out[0] = sum_i 0.5 * mass_i * |v_i|^2 in a fixed summation order; scratch holds
  *   at least 1024 doubles.
  * tace_edge_vectors: out[e] = positions[target_e] - positions[source_e] evaluated in fp64 and rounded to
@@ -268,6 +277,8 @@ int tace_nl_build_noalloc(const double* positions, const double* lattice, const 
  *   gradients returned by a neighbouring domain, tace/models/lammps.py:105-129); float / double rows. */
 int tace_md_kick_drift(double* positions, double* velocities, const void* forces, int32_t force_dtype, const double* inv_mass,
                        int64_t n_atoms, double kick, double dt, tace_stream_t stream);
+int tace_md_langevin(double* velocities, const double* inv_mass, const int64_t* ids, int64_t n_atoms, double c1,
+                     double kt_scaled, uint64_t seed, uint64_t step, tace_stream_t stream);
 int tace_md_kinetic_energy(const double* velocities, const double* mass, int64_t n_atoms, double* scratch, double* out,
                            tace_stream_t stream);
 int tace_edge_vectors(const double* positions, const int64_t* edge_index, int64_t n_edges, void* out, int32_t dtype,

@@ -356,9 +356,11 @@ class Interaction(torch.nn.Module):
     tace/models/_e3nn/base.py:113-249."""
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
-                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False, mlp_layer_norm=False):
+                 num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False, mlp_layer_norm=False,
+                 scatter_norm="avg_num_neighbors"):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
+        self.scatter_norm = scatter_norm
         C = num_channel
         self.irreps_in = Irreps(irreps_in)
         self.irreps_sh = Irreps.spherical_harmonics(lmax)
@@ -380,6 +382,10 @@ class Interaction(torch.nn.Module):
         # update) switch LayerNorm on inside the radial MLP
         self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel], bias=mlp_bias,
                              layer_norm=mlp_layer_norm)
+        if scatter_norm in ("density", "no_cutoff_density"):  # inter.py:102-110 (the edge density of MACE)
+            self.edge_density = MLP([num_radial_basis, 64, 1], bias=mlp_bias, layer_norm=mlp_layer_norm)
+            self.alpha = torch.nn.Parameter(torch.tensor(float(avg_num_neighbors)))
+            self.beta = torch.nn.Parameter(torch.tensor(0.0))
         if layer > 0:  # resnet type "BB", linear_type "aware", use_first_resnet False
             self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True, num_elements=num_elements)
 
@@ -392,7 +398,16 @@ class Interaction(torch.nn.Module):
         msg = self.rejector(x[edge_index[0]], edge_attrs, w)  # tace/models/_e3nn/fused.py:269-271
         m = scatter_sum(msg, edge_index[1], x.shape[0])
         m = self.linear_down(m)
-        m = m / self.avg_num_neighbors  # base.py:240-249
+        if hasattr(self, "edge_density"):  # inter.py:249-260, base.py:240-249
+            density = torch.tanh(self.edge_density(edge_feats) ** 2)
+            if edge_cutoff is not None and self.scatter_norm == "density":
+                density = density * edge_cutoff
+            density = scatter_sum(density, edge_index[1], x.shape[0])
+            density = density * self.beta + self.alpha
+            density = density.masked_fill(density == 0, 1e-9)
+            m = m / density
+        else:
+            m = m / self.avg_num_neighbors  # base.py:240-249
         m = self.linear_nonlinearity(self.nonlinearity(m))
         return m, sc
 
@@ -475,7 +490,8 @@ class Representation(torch.nn.Module):
                 Interaction(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
                             cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
                             irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True),
-                            mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2)
+                            mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2,
+                            scatter_norm=cfg.get("atomic_basis", {}).get("scatter_norm", "avg_num_neighbors"))
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],

@@ -201,6 +201,63 @@ cudaError_t launch_ln_silu_bwd(T* g, const T* z, const T* gamma, const T* beta, 
   ln_silu_bwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, z, gamma, beta, rows);
   return cudaGetLastError();
 }
+// ---- learned edge density (scatter_norm = density) ----------------------------------------------
+template <typename T>
+__device__ __forceinline__ void density_edge(const DensityArgs<T>& a, T d, T& rho, T& drho) {
+  T b[kNumBessel], db[kNumBessel];
+  radial_eval<T>(d, a.rp, b, db);
+  T y = a.b1 ? a.b1[0] : T(0), dy = T(0);
+  for (int j = 0; j < kHidden; ++j) {
+    T z = a.b0 ? a.b0[j] : T(0), dz = T(0);
+#pragma unroll
+    for (int k = 0; k < kNumBessel; ++k) { z += b[k] * a.A0[k * kHidden + j]; dz += db[k] * a.A0[k * kHidden + j]; }
+    y += silu_(z) * a.w1[j];
+    dy += silu_grad_(z) * dz * a.w1[j];
+  }
+  const T t = tanh(y * y);
+  rho = t;
+  drho = (T(1) - t * t) * T(2) * y * dy;
+  if (a.use_env) {
+    T u, du;
+    envelope_eval<T>(d, a.rp, u, du);
+    drho = drho * u + t * du;
+    rho = t * u;
+  }
+}
+template <typename T>
+__global__ void density_fwd_kernel(const DensityArgs<T> a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.n) return;
+  T acc = T(0);
+  for (int e = a.rowptr_dst[i]; e < a.rowptr_dst[i + 1]; ++e) {
+    T rho, drho;
+    density_edge(a, a.dlen[e], rho, drho);
+    acc += rho;
+  }
+  const T dens = acc * a.ab[1] + a.ab[0];
+  a.inv_density[i] = dens == T(0) ? T(1e9) : T(1) / dens;
+}
+template <typename T>
+__global__ void density_bwd_kernel(const DensityArgs<T> a) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  T rho, drho;
+  density_edge(a, a.dlen[e], rho, drho);
+  a.ddlen[e] += a.gdens[a.e_dst[e]] * a.ab[1] * drho;
+}
+template <typename T>
+cudaError_t launch_density_fwd(const DensityArgs<T>& a, cudaStream_t s) {
+  if (a.n <= 0) return cudaSuccess;
+  density_fwd_kernel<T><<<(a.n + 63) / 64, 64, 0, s>>>(a);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_density_bwd(const DensityArgs<T>& a, cudaStream_t s) {
+  if (a.E <= 0) return cudaSuccess;
+  density_bwd_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
 // ---- ZBL pair repulsion (tace/models/radial.py:788-874) ------------------------------------------
 // energy of one directed edge (half of the pair energy) and its derivative with respect to the edge length
 template <typename T>
@@ -413,6 +470,8 @@ cudaError_t launch_graph_virial(const T* atom_virial, const int* graph_ptr, cons
   template cudaError_t launch_edge_mlp_out<T>(const EdgeArgs<T>&, cudaStream_t);                     \
   template cudaError_t launch_silu<T>(const T*, T*, long long, cudaStream_t);                        \
   template cudaError_t launch_zbl_fwd<T>(const ZblArgs<T>&, cudaStream_t);                           \
+  template cudaError_t launch_density_fwd<T>(const DensityArgs<T>&, cudaStream_t);                   \
+  template cudaError_t launch_density_bwd<T>(const DensityArgs<T>&, cudaStream_t);                   \
   template cudaError_t launch_zbl_bwd<T>(const ZblArgs<T>&, cudaStream_t);                           \
   template cudaError_t launch_ln_silu_fwd<T>(const T*, const T*, const T*, T*, long long, cudaStream_t); \
   template cudaError_t launch_ln_silu_bwd<T>(T*, const T*, const T*, const T*, long long, cudaStream_t); \

@@ -314,6 +314,7 @@ struct Model : ModelBase {
   bool element2 = false;      // edge_update.type = element2
   int n_fid = 1;              // read-out heads (entries of `statistics`)
   int zbl = 0;                // 0 off, 1 ZBL repulsion inside the species scale, 2 outside it
+  int density = 0;            // atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -354,7 +355,8 @@ struct Model : ModelBase {
     mlp_bias = c.mlp_bias != 0; env_after = c.env_after_mlp != 0; element2 = c.edge_update_element2 != 0;
     n_fid = c.num_fidelities > 0 ? c.num_fidelities : 1;
     zbl = c.zbl;
-    if (zbl < 0 || zbl > 2) return TACE_ERR_UNSUPPORTED_CONFIG;
+    density = c.scatter_norm_density;
+    if (zbl < 0 || zbl > 2 || density < 0 || density > 2 || (density && element2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     const int Dn = (Ln + 1) * (Ln + 1);
@@ -391,6 +393,10 @@ struct Model : ModelBase {
         if (nh >= 2) add_weight(pre + "b1", kHidden);
         if (nh >= 3) add_weight(pre + "b2", kHidden);
         add_weight(pre + "b3", (long long)p.tp.NP * C);
+      }
+      if (density) {  // edge-density MLP 8 -> 64 -> 1 and the affine parameters {alpha, beta}
+        add_weight(pre + "dA0", (long long)kNumBessel * kHidden); add_weight(pre + "dw1", kHidden); add_weight(pre + "dab", 2);
+        if (mlp_bias) { add_weight(pre + "db0", kHidden); add_weight(pre + "db1", 1); }
       }
       if (element2) {
         add_weight(pre + "tdst", (long long)n_el * kHidden); add_weight(pre + "tsrc", (long long)n_el * kHidden);
@@ -485,6 +491,7 @@ struct Model : ModelBase {
     T *gh_out, *gout, *gA, *ga, *gx, *gh_in;
     T *As, *gAs, *gout_s, *hs;  // species-sorted copies used by the per-species linears
     T *B3, *gB2;                // third-order basis (reused for its gradient) and the gradient of the second-order one
+    T *inv_density, *gdens;     // learned edge density: 1 / density_i and dE / d density_i
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
@@ -543,6 +550,7 @@ struct Model : ModelBase {
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
+      lb.inv_density = density ? ar.take<T>(NL) : nullptr; lb.gdens = density ? ar.take<T>(NL) : nullptr;
       lb.a = ar.take<T>((size_t)NL * D * C);
       lb.ga = ar.take<T>((size_t)NL * D * C);
       lb.A = ar.take<T>((size_t)NL * D * C);
@@ -683,6 +691,17 @@ struct Model : ModelBase {
       r.dH1[i] = dh1_buffer(b.lay[ts[i]]);
     }
     return r;
+  }
+  DensityArgs<T> density_args(const EdgeArgs<T>& ea, const Bufs& b, const LayerBufs& lb, const std::string& pre, long long NL,
+                              long long E) const {
+    DensityArgs<T> da;
+    memset(&da, 0, sizeof(da));
+    da.rowptr_dst = b.rowptr_dst; da.e_dst = b.e_dst; da.dlen = b.dlen; da.rp = ea.rp;
+    da.A0 = w(pre + "dA0"); da.w1 = w(pre + "dw1"); da.ab = w(pre + "dab");
+    if (mlp_bias) { da.b0 = w(pre + "db0"); da.b1 = w(pre + "db1"); }
+    da.use_env = (env_after && density == 1) ? 1 : 0;
+    da.n = (int)NL; da.E = E; da.inv_density = lb.inv_density;
+    return da;
   }
   // where the backward pass leaves dE/d(first hidden activation): it ping-pongs through the activation buffers
   T* dh1_buffer(const LayerBufs& lb) const { return nh == 3 ? lb.Z3 : nh == 2 ? lb.Hact : lb.H3; }
@@ -935,6 +954,11 @@ struct Model : ModelBase {
         }
         CKL(run_linear(sp, NL, s));
       }
+      if (density) {  // learned normalisation instead of the constant folded into the weights
+        const DensityArgs<T> da = density_args(ea, b, lb, pre, NL, E);
+        CKL(launch_density_fwd(da, s));
+        CKL(launch_scale_rows(lb.Gt, lb.inv_density, NL, (L + m0 + D) * C, (long long)(L + 1 + D) * C, s));
+      }
       CKL(launch_gate_fwd(lb.Gt, lb.a, (int)NL, L, C, m0, s));
       {
         std::vector<LinSpec> sp;
@@ -1095,6 +1119,8 @@ struct Model : ModelBase {
         CKL(run_linear(sp, NL, s));
       }
       CKL(launch_gate_bwd(lb.Gt, lb.ga, lb.gGt, (int)NL, L, C, m0, s));
+      if (density)  // d / d density_i, and the gradient of the unscaled linear_down output
+        CKL(launch_density_node_bwd(lb.gGt, lb.Gt, lb.inv_density, lb.gdens, NL, (L + m0 + D) * C, (long long)(L + 1 + D) * C, s));
       {  // through linear_down; the gradient of the messages overwrites the messages
         std::vector<LinSpec> sp;
         for (int l = 0; l <= L; ++l) {
@@ -1165,6 +1191,13 @@ struct Model : ModelBase {
     // ---- back to the edge vectors, then forces and virials
     PH("radial_mlp_bwd");
     if (!chunked) CKS(radial_backward(ea, b, all_layers, 0, E, 0, s));  // lay[t].H3 holds dE/dh3 of each layer's radial MLP
+    if (density) {  // the densities' dependence on the edge lengths
+      for (int t = 0; t < NL_; ++t) {
+        DensityArgs<T> da = density_args(ea, b, b.lay[t], "t" + std::to_string(t) + ".", NL, E);
+        da.gdens = b.lay[t].gdens; da.ddlen = b.ddlen;
+        CKL(launch_density_bwd(da, s));
+      }
+    }
     if (zbl) {  // the repulsion's own dependence on the edge lengths
       za.ddlen = b.ddlen; za.factor = (zbl == 1) ? b.ro_factor : nullptr;
       CKL(launch_zbl_bwd(za, s));

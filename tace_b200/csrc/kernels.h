@@ -106,6 +106,25 @@ struct ZblArgs {
   int n; long long E;
   T* node; const T* factor; T* ddlen;
 };
+// Learned edge density replacing the constant 1/avg_num_neighbors (atomic_basis.scatter_norm = density,
+// tace/models/_e3nn/inter.py:102-110,249-260): rho_e = tanh(y_e^2) [* envelope], y_e = silu(radial(d_e) A0 + b0) . w1 + b1,
+// density_i = beta * sum_{e -> i} rho_e + alpha (1e-9 where exactly 0), messages / density_i.
+// fwd: inv_density[i]; bwd: ddlen[e] += gdens[target(e)] * beta * d rho_e / d d.  ab = {alpha, beta}.
+template <typename T>
+struct DensityArgs {
+  const int* rowptr_dst; const int* e_dst; const T* dlen; RadialParams<T> rp;
+  const T* A0; const T* b0; const T* w1; const T* b1; const T* ab;
+  int use_env;  // multiply rho_e by the envelope (apply_cutoff = False with scatter_norm = density)
+  int n; long long E;
+  T* inv_density; const T* gdens; T* ddlen;
+};
+template <typename T> cudaError_t launch_density_fwd(const DensityArgs<T>& a, cudaStream_t s);
+template <typename T> cudaError_t launch_density_bwd(const DensityArgs<T>& a, cudaStream_t s);
+// x[i, :width] *= scale[i] (rows `stride` elements apart)
+template <typename T> cudaError_t launch_scale_rows(T* x, const T* scale, long long n, int width, long long stride, cudaStream_t s);
+// gdens[i] = -inv[i] * sum_k gx[i, k] * x[i, k] (0 where the density was replaced by 1e-9), then gx[i, :width] *= inv[i]
+template <typename T> cudaError_t launch_density_node_bwd(T* gx, const T* x, const T* inv, T* gdens, long long n, int width,
+                                                         long long stride, cudaStream_t s);
 template <typename T> cudaError_t launch_zbl_fwd(const ZblArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_zbl_bwd(const ZblArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);

@@ -89,7 +89,43 @@ inline unsigned grid_for(long long total, int block) {
 }  // namespace
 }  // namespace tace
 
+// ---- Langevin thermostat: exact Ornstein-Uhlenbeck update of the velocities ---------------------
+// v <- c1 v + sqrt((1 - c1^2) kT / m) xi, xi standard normal.  The random numbers are a pure function of
+// (seed, step, atom id, component), so a trajectory does not depend on how atoms are spread over ranks.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {  // splitmix64 finaliser
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+__global__ void md_langevin_kernel(double* __restrict__ vel, const double* __restrict__ inv_mass, const long long* __restrict__ ids,
+                                   long long n, double c1, double kt_scaled, unsigned long long seed, unsigned long long step) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long id = ids ? (unsigned long long)ids[i] : (unsigned long long)i;
+  const unsigned long long key = mix64(mix64(seed) ^ mix64(step * 0xD1342543DE82EF95ull + 1) ^ (id * 0x2545F4914F6CDD1Dull));
+  // four uniforms in (0, 1] -> two Box-Muller pairs (three of the four normals are used)
+  double u[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) u[k] = ((double)(mix64(key + k) >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+  const double r0 = sqrt(-2.0 * log(u[0])), r1 = sqrt(-2.0 * log(u[2]));
+  const double two_pi = 6.283185307179586;
+  const double xi[3] = {r0 * cos(two_pi * u[1]), r0 * sin(two_pi * u[1]), r1 * cos(two_pi * u[3])};
+  const double sigma = sqrt((1.0 - c1 * c1) * kt_scaled * inv_mass[i]);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) vel[3 * i + k] = c1 * vel[3 * i + k] + sigma * xi[k];
+}
+
 using namespace tace;
+
+extern "C" int tace_md_langevin(double* velocities, const double* inv_mass, const int64_t* ids, int64_t n_atoms, double c1,
+                                double kt_scaled, uint64_t seed, uint64_t step, tace_stream_t stream) {
+  if (!velocities || !inv_mass || n_atoms < 0 || !(c1 >= 0.0 && c1 <= 1.0) || kt_scaled < 0.0) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_atoms == 0) return TACE_OK;
+  md_langevin_kernel<<<(unsigned)((n_atoms + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      velocities, inv_mass, reinterpret_cast<const long long*>(ids), n_atoms, c1, kt_scaled, seed, step);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
 
 extern "C" int tace_md_kick_drift(double* positions, double* velocities, const void* forces, int32_t force_dtype,
                                   const double* inv_mass, int64_t n_atoms, double kick, double dt, tace_stream_t stream) {

@@ -355,6 +355,48 @@ cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, cons
   return cudaGetLastError();
 }
 
+// ---- rows scaled by the learned edge density ----------------------------------------------------
+template <typename T>
+__global__ void scale_rows_kernel(T* __restrict__ x, const T* __restrict__ scale, long long n, int width, long long stride) {
+  const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (k >= n * width) return;
+  const long long i = k / width;
+  x[i * stride + (k - i * width)] *= scale[i];
+}
+template <typename T>
+cudaError_t launch_scale_rows(T* x, const T* scale, long long n, int width, long long stride, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  scale_rows_kernel<T><<<(unsigned)((n * width + 255) / 256), 256, 0, s>>>(x, scale, n, width, stride);
+  return cudaGetLastError();
+}
+template <typename T>
+__global__ void density_node_bwd_kernel(T* __restrict__ gx, const T* __restrict__ x, const T* __restrict__ inv, T* __restrict__ gdens,
+                                        int width, long long stride) {
+  __shared__ T red[256];
+  const long long i = blockIdx.x;
+  const T iv = inv[i];
+  T acc = T(0);
+  for (int k = threadIdx.x; k < width; k += blockDim.x) {
+    const T g = gx[i * stride + k];
+    acc += g * x[i * stride + k];
+    gx[i * stride + k] = g * iv;
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) gdens[i] = iv == T(1e9) ? T(0) : -iv * red[0];
+}
+template <typename T>
+cudaError_t launch_density_node_bwd(T* gx, const T* x, const T* inv, T* gdens, long long n, int width, long long stride,
+                                    cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  density_node_bwd_kernel<T><<<(unsigned)n, 256, 0, s>>>(gx, x, inv, gdens, width, stride);
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
   if (a.n <= 0) return cudaSuccess;
@@ -402,6 +444,8 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
   template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
   template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \
+  template cudaError_t launch_scale_rows<T>(T*, const T*, long long, int, long long, cudaStream_t);           \
+  template cudaError_t launch_density_node_bwd<T>(T*, const T*, const T*, T*, long long, int, long long, cudaStream_t); \
   template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, const int*, int, T*, int, cudaStream_t);
 INST(float)
 INST(double)

@@ -21,7 +21,7 @@ EXPORTS = [
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
     "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
     "tace_edge_vectors", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays",
-    "tace_set_chunk_edges",
+    "tace_set_chunk_edges", "tace_md_langevin",
 ]
 
 
@@ -31,7 +31,7 @@ class TaceConfig(ctypes.Structure):
         ("correlation", c_int), ("num_bessel", c_int), ("mlp_hidden", c_int), ("envelope_p", c_int),
         ("readout_hidden", c_int), ("cutoff", c_double), ("avg_num_neighbors", c_double), ("Lnode", c_int),
         ("use_alllayer", c_int), ("gate_m0_off", c_int), ("mlp_layers", c_int), ("mlp_bias", c_int), ("env_after_mlp", c_int),
-        ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int),
+        ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int), ("scatter_norm_density", c_int),
     ]
 
 
@@ -104,6 +104,8 @@ def load() -> ctypes.CDLL:
     lib.tace_graph_replays.argtypes = [c_void_p]
     lib.tace_graph_replays.restype = c_int64
     lib.tace_md_kick_drift.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_double, c_double, c_void_p]
+    lib.tace_md_langevin.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_double, c_double, ctypes.c_uint64, ctypes.c_uint64,
+                                     c_void_p]
     lib.tace_md_kinetic_energy.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.tace_edge_vectors.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_void_p]
     lib.tace_rows_gather.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]

@@ -1,4 +1,5 @@
-"""Velocity-Verlet molecular dynamics of one periodic system on one or several GPUs.
+"""Velocity-Verlet molecular dynamics (NVE, or NVT with a Langevin thermostat) of one periodic system on one or
+several GPUs.
 
 Every rank owns the atoms of one block of the cell (``tace_b200.domain``), keeps positions and
 velocities in fp64 on its GPU and, per step: half kick + drift, ghost positions from the owning
@@ -6,7 +7,10 @@ ranks, a fresh neighbour list over owned targets, one model evaluation in edge-v
 LAMMPS contract of the reference: ghost feature rows refreshed between interaction layers, ghost
 gradients returned to their owners, ``tace/models/lammps.py:82-142``), forces that landed on ghost
 rows returned to their owners, second half kick.  Ownership and ghost lists are rebuilt when an atom
-has moved more than half the skin.
+has moved more than half the skin.  With ``friction`` set, every step ends with the exact Ornstein-Uhlenbeck
+velocity update ``v <- c1 v + sqrt((1 - c1^2) kT / m) xi``, ``c1 = exp(-friction dt)``, whose random numbers depend
+only on (seed, step, atom id), so the trajectory is the same for any number of ranks.  ``thermo()`` returns the usual
+thermodynamic output line.
 
 Units: eV, Angstrom, atomic mass units, femtoseconds.
 """
@@ -62,8 +66,13 @@ class DomainMD:
     def __init__(self, model, cell: np.ndarray, positions: np.ndarray, atomic_numbers: np.ndarray,
                  velocities: Optional[np.ndarray] = None, masses: Optional[np.ndarray] = None, dt: float = 1.0,
                  skin: float = 0.5, rank: int = 0, world_size: int = 1, device: Optional[torch.device] = None,
-                 grid: Optional[Tuple[int, int, int]] = None, group=None):
+                 grid: Optional[Tuple[int, int, int]] = None, group=None, temperature: Optional[float] = None,
+                 friction: float = 0.0, seed: int = 0):
+        """``friction`` (1/fs) > 0 with ``temperature`` (K) switches the Langevin thermostat on."""
         self.model = model
+        if friction < 0.0 or (friction > 0.0 and (temperature is None or temperature < 0.0)):
+            raise ValueError("the Langevin thermostat needs friction >= 0 and a target temperature >= 0")
+        self.friction, self.target_temperature, self.seed = float(friction), temperature, int(seed)
         self.device = torch.device(device if device is not None else "cuda")
         self.rank, self.world_size, self.group = rank, world_size, group
         self.dt = float(dt)
@@ -151,7 +160,8 @@ class DomainMD:
             self.timings[k] = self.timings.get(k, 0.0) + v
 
     # -- integration ---------------------------------------------------------------------------------
-    def step(self, n_steps: int = 1) -> None:
+    def step(self, n_steps: int = 1, log_every: int = 0, log=None) -> None:
+        """Advance ``n_steps``; every ``log_every`` steps ``log(self.thermo())`` is called (collective)."""
         kick = 0.5 * self.dt * ACCEL
         fcode = _lib.dtype_code(self.dtype)
         for _ in range(n_steps):
@@ -167,7 +177,13 @@ class DomainMD:
             with torch.cuda.device(self.device):
                 _lib.check(self.lib.tace_md_kick_drift(None, self.velocities.data_ptr(), self.forces.data_ptr(), fcode,
                                                        self.inv_mass.data_ptr(), n, kick, 0.0, self._stream()), "tace_md_kick_drift")
+                if self.friction > 0.0:
+                    _lib.check(self.lib.tace_md_langevin(self.velocities.data_ptr(), self.inv_mass.data_ptr(), self.ids.data_ptr(), n,
+                                                         float(np.exp(-self.friction * self.dt)), KB * self.target_temperature * ACCEL,
+                                                         self.seed, self.step_count, self._stream()), "tace_md_langevin")
             self.step_count += 1
+            if log is not None and log_every > 0 and self.step_count % log_every == 0:
+                log(self.thermo())
 
     # -- observables (collective: every rank must call) ---------------------------------------------
     def _all_sum(self, x: torch.Tensor) -> float:
@@ -191,6 +207,12 @@ class DomainMD:
 
     def temperature(self) -> float:
         return 2.0 * self.kinetic_energy() / (3.0 * self.n_global * KB)
+
+    def thermo(self) -> Dict[str, float]:
+        """Step, time (fs), potential / kinetic / total energy (eV) and temperature (K) of the whole system (collective)."""
+        ke, pe = self.kinetic_energy(), self.potential()
+        return {"step": self.step_count, "time": self.step_count * self.dt, "potential": pe, "kinetic": ke, "total": pe + ke,
+                "temperature": 2.0 * ke / (3.0 * self.n_global * KB)}
 
     def gather(self) -> Dict[str, np.ndarray]:
         """Whole-system positions, velocities and forces ordered by atom id (collective)."""

@@ -97,7 +97,7 @@ def check_model_config(cfg: Dict) -> Dict:
         ("radial_basis", "distance_transform", {None}), ("radial_basis", "apply_cutoff", {True, False}),
         ("radial_basis", "bias", {False, True}), ("radial_basis", "use_dydynamic_cutoff", {False}),
         ("radial_basis", "num_radial_basis", {8}),
-        ("atomic_basis", "scatter_norm", {"avg_num_neighbors"}), ("atomic_basis", "gate_m0", {True, False}),
+        ("atomic_basis", "scatter_norm", {"avg_num_neighbors", "density", "no_cutoff_density"}), ("atomic_basis", "gate_m0", {True, False}),
         ("atomic_basis", "l1l2", {None}), ("atomic_basis", "scalar_act", {None, "sigmoid"}),
         ("atomic_basis", "tensor_act", {None, "sigmoid"}), ("atomic_basis", "node_wise_hidden", {None}),
         ("resnet", "type", {"BB"}), ("resnet", "linear_type", {"aware"}), ("resnet", "use_first_resnet", {False}),
@@ -112,6 +112,8 @@ def check_model_config(cfg: Dict) -> Dict:
     hidden = list(cfg["radial_basis"]["hidden"])
     _require(1 <= len(hidden) <= 3 and all(h == 64 for h in hidden), "radial_basis.hidden: one to three layers of width 64")
     _require(len(cfg["readout_emlp"]["hidden"]) == 1 and cfg["readout_emlp"]["hidden"][0] <= 64, "one read-out hidden layer <= 64")
+    _require(cfg["atomic_basis"]["scatter_norm"] == "avg_num_neighbors" or cfg["edge_update"]["type"] == "identity",
+             "a learned edge density (atomic_basis.scatter_norm) only with edge_update.type = identity")
     if cfg["short_range"]["zbl"]["enable"]:
         cfg["short_range"]["zbl"]["covalent_radii"] = _covalent_radii(cfg)
     _require(not cfg["long_range"]["les"]["enable"], "no LES")
@@ -208,6 +210,7 @@ class e3nnTACE(torch.nn.Module):
                               mlp_layers=len(cfg["radial_basis"]["hidden"]), mlp_bias=cfg["radial_basis"]["bias"],
                               apply_cutoff=cfg["radial_basis"]["apply_cutoff"],
                               element2=cfg["edge_update"]["type"] == "element2", num_fidelities=self.num_fidelities,
+                              density={"avg_num_neighbors": 0, "density": 1, "no_cutoff_density": 2}[cfg["atomic_basis"]["scatter_norm"]],
                               zbl=0 if not cfg["short_range"]["zbl"]["enable"] else (1 if cfg["scale_shift"]["scale_zbl"] else 2))
         self.register_buffer("cutoff", torch.tensor(rc, dtype=dt))
         self.register_buffer("atomic_numbers", torch.tensor(cfg["atomic_numbers"], dtype=torch.int64))
@@ -216,6 +219,12 @@ class e3nnTACE(torch.nn.Module):
                 value = torch.zeros(shape, dtype=dt)
             elif ".edge_updates." in name:  # tace/models/_e3nn/edge.py:216-221
                 value = torch.empty(shape, dtype=dt).uniform_(-0.001, 0.001)
+            elif name.endswith(".alpha"):  # tace/models/_e3nn/inter.py:109-110
+                value = torch.tensor(float(cfg["avg_num_neighbors"]), dtype=dt)
+            elif name.endswith(".beta"):
+                value = torch.zeros((), dtype=dt)
+            elif ".edge_density.mlp." in name:
+                value = torch.empty(shape, dtype=dt).uniform_(-math.sqrt(3.0), math.sqrt(3.0))
             elif ".edge_info.mlp." in name and len(shape) == 1:  # LayerNorm scale (torch.nn.LayerNorm default)
                 value = torch.ones(shape, dtype=dt)
             elif ".edge_info.mlp." in name:
@@ -340,7 +349,7 @@ class TensorModel(torch.nn.Module):
             cutoff=self.get_cutoff(), avg_num_neighbors=float(rf.cfg["avg_num_neighbors"]), Lnode=plan.Lnode,
             use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,
             mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2),
-            num_fidelities=plan.n_fid, zbl=plan.zbl)
+            num_fidelities=plan.n_fid, zbl=plan.zbl, scatter_norm_density=plan.density)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

@@ -60,13 +60,16 @@ class ModelPlan:
     def __init__(self, L: int, num_layers: int, num_channel: int, num_elements: int, correlation: int,
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
-                 apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0):
+                 apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0,
+                 density: int = 0):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
         self.use_alllayer = bool(use_alllayer)
         # read-out heads (one per `statistics` entry); ZBL repulsion: 0 off, 1 inside the species scale, 2 outside
         self.n_fid, self.zbl = int(num_fidelities), int(zbl)
+        # atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density (learned edge density)
+        self.density = int(density)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
         self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
@@ -100,6 +103,14 @@ class ModelPlan:
                 if self.mlp_layer_norm and i < self.mlp_layers:
                     out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.weight"] = (b,)
                     out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.bias"] = (b,)
+            if self.density:  # tace/models/_e3nn/inter.py:102-110
+                out[pre + "edge_density.mlp.0.weight"] = (self.num_bessel, self.mlp_hidden)
+                out[pre + "edge_density.mlp.2.weight"] = (self.mlp_hidden, 1)
+                if self.mlp_bias:
+                    out[pre + "edge_density.mlp.0.bias"] = (self.mlp_hidden,)
+                    out[pre + "edge_density.mlp.2.bias"] = (1,)
+                out[pre + "alpha"] = ()
+                out[pre + "beta"] = ()
             if self.element2:  # tace/models/_e3nn/edge.py:190-257
                 out[f"representation.edge_updates.{lp.t}.source_embedding.weight"] = (n_el * C,)
                 out[f"representation.edge_updates.{lp.t}.target_embedding.weight"] = (n_el * C,)
@@ -252,9 +263,18 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
                 out[tp + f"ln{j}g"] = g(pre + f"edge_info.mlp.{mi(j) + 1}.weight")
                 out[tp + f"ln{j}b"] = g(pre + f"edge_info.mlp.{mi(j) + 1}.bias")
         down_shapes = [(lp.k[l] * C, ((L + 2) * C if plan.gate_m0 else (L + 1) * C) if l == 0 else C) for l in range(L + 1)]
+        # the constant message normalisation is folded into linear_down; a learned density divides at run time instead
+        norm = 1.0 if plan.density else avg_num_neighbors
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
-            put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / avg_num_neighbors, tp + f"downT.l{l}")
-        out[tp + "down.b"] = g(pre + "linear_down.bias") / avg_num_neighbors
+            put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / norm, tp + f"downT.l{l}")
+        out[tp + "down.b"] = g(pre + "linear_down.bias") / norm
+        if plan.density:  # MLP 8 -> 64 -> 1 with the MLP gains (1 / sqrt(fan_in), sqrt(2) after the first layer)
+            out[tp + "dA0"] = g(pre + "edge_density.mlp.0.weight") / math.sqrt(nb)
+            out[tp + "dw1"] = g(pre + "edge_density.mlp.2.weight").reshape(hd) * math.sqrt(2.0 / hd)
+            out[tp + "dab"] = np.array([float(g(pre + "alpha")), float(g(pre + "beta"))])
+            if plan.mlp_bias:
+                out[tp + "db0"] = g(pre + "edge_density.mlp.0.bias")
+                out[tp + "db1"] = g(pre + "edge_density.mlp.2.bias")
         for l, m in enumerate(split(g(pre + "linear_nonlinearity.weight"), [(C, C)] * (L + 1))):
             put(tp + f"nl.l{l}", m / math.sqrt(C), tp + f"nlT.l{l}")
         out[tp + "nl.b"] = g(pre + "linear_nonlinearity.bias")

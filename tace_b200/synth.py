@@ -148,7 +148,8 @@ def statistics(atomic_numbers: Sequence[int], avg_num_neighbors: float, num_fide
 def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], avg_num_neighbors: float,
                  num_layers: int = 2, correlation: int = 2, target_property=("energy", "forces", "stress"),
                  Lmax: int = None, use_alllayer: bool = False, gate_m0: bool = True, radial: Dict = None,
-                 edge_update: str = "identity", num_fidelities: int = 1, zbl: Dict = None, scale_zbl: bool = True) -> Dict:
+                 edge_update: str = "identity", num_fidelities: int = 1, zbl: Dict = None, scale_zbl: bool = True,
+                 scatter_norm: str = "avg_num_neighbors") -> Dict:
     """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product).  ``L`` is the edge
     rank ``lmax``; the node rank ``Lmax`` defaults to it."""
     return {
@@ -157,7 +158,7 @@ def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], 
         "target_property": list(target_property), "max_neighbors": None,
         "product_basis": {"correlation": correlation},
         "readout_emlp": {"use_alllayer": bool(use_alllayer)},
-        "atomic_basis": {"gate_m0": bool(gate_m0)},
+        "atomic_basis": {"gate_m0": bool(gate_m0), "scatter_norm": scatter_norm},
         "radial_basis": dict(radial or {}),
         "edge_update": {"type": edge_update},
         "short_range": {"zbl": dict(zbl or {"enable": False})},

@@ -10,13 +10,13 @@ from tace_b200 import synth
 
 def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
                 targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True, radial=None, edge_update="identity",
-                num_fidelities=1, zbl=None, scale_zbl=True):
+                num_fidelities=1, zbl=None, scale_zbl=True, scatter_norm="avg_num_neighbors"):
     """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
     from oracle.model import build_oracle
 
     cfg = synth.model_config(L, C, cutoff, elements, avg, num_layers=num_layers, correlation=correlation,
                              target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0, radial=radial, edge_update=edge_update,
-                             num_fidelities=num_fidelities, zbl=zbl, scale_zbl=scale_zbl)
+                             num_fidelities=num_fidelities, zbl=zbl, scale_zbl=scale_zbl, scatter_norm=scatter_norm)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
@@ -30,6 +30,10 @@ def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correl
                 v.copy_(0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
             if ".edge_info.mlp." in k and k.endswith(".weight") and v.dim() == 1:  # LayerNorm scale: away from 1
                 v.copy_(1.0 + 0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
+            if k.endswith(".beta"):  # zero in the reference's initialisation: switch the learned density on
+                v.copy_(torch.tensor(0.8, dtype=v.dtype))
+            if k.endswith(".alpha"):
+                v.copy_(torch.tensor(3.0 + torch.rand((), generator=g).item(), dtype=v.dtype))
             if ".edge_updates." in k:  # initialised at 1e-3 in the reference: make the term visible
                 v.copy_(torch.randn(v.shape, generator=g, dtype=v.dtype))
         sd["readout_fn.scale_shift.scale"].copy_(0.5 + torch.rand(sd["readout_fn.scale_shift.scale"].shape, generator=g, dtype=dtype))

@@ -177,3 +177,48 @@ def test_two_ranks_match_one():
         assert abs(ret[r]["energy"] - e) < 1e-8 * len(s["positions"])
         assert np.abs(ret[r]["forces"] - one["forces"]).max() < 1e-8
         assert np.abs(ret[r]["positions"] - one["positions"]).max() < 1e-10
+
+
+def test_langevin_kernel_statistics_and_determinism():
+    lib = _lib.load()
+    n = 200000
+    g = torch.Generator().manual_seed(0)
+    mass = (torch.rand(n, generator=g, dtype=torch.float64) * 50 + 1).to(DEV)
+    inv_mass = 1.0 / mass
+    ids = torch.randperm(n, generator=g).to(DEV)
+    kt = 0.7
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    v = torch.ones(n, 3, dtype=torch.float64, device=DEV)
+    # c1 = 0: the old velocities are forgotten, every component is N(0, kT / m)
+    _lib.check(lib.tace_md_langevin(v.data_ptr(), inv_mass.data_ptr(), ids.data_ptr(), n, 0.0, kt, 7, 3, stream), "langevin")
+    z = v * torch.sqrt(mass / kt)[:, None]
+    assert abs(z.mean().item()) < 0.01 and abs(z.var().item() - 1.0) < 0.01
+    assert abs((z ** 4).mean().item() - 3.0) < 0.1  # Gaussian fourth moment
+    assert abs((z[:, 0] * z[:, 1]).mean().item()) < 0.01 and abs((z[:, 1] * z[:, 2]).mean().item()) < 0.01
+    # the noise of an atom depends on its id, not on its row: a permuted call gives the permuted result
+    perm = torch.randperm(n, generator=g).to(DEV)
+    v2 = torch.ones(n, 3, dtype=torch.float64, device=DEV)
+    inv_mass_p, ids_p = inv_mass[perm].contiguous(), ids[perm].contiguous()
+    _lib.check(lib.tace_md_langevin(v2.data_ptr(), inv_mass_p.data_ptr(), ids_p.data_ptr(), n, 0.0, kt, 7, 3, stream), "langevin")
+    assert torch.equal(v2, v[perm])
+    v3 = torch.ones(n, 3, dtype=torch.float64, device=DEV)
+    _lib.check(lib.tace_md_langevin(v3.data_ptr(), inv_mass.data_ptr(), ids.data_ptr(), n, 0.0, kt, 7, 4, stream), "langevin")
+    assert not torch.equal(v3, v)  # another step, other numbers
+    # c1 = 1: no friction, nothing changes
+    v4 = v.clone()
+    _lib.check(lib.tace_md_langevin(v4.data_ptr(), inv_mass.data_ptr(), ids.data_ptr(), n, 1.0, kt, 7, 5, stream), "langevin")
+    assert torch.equal(v4, v)
+
+
+def test_langevin_dynamics_reaches_the_target_temperature():
+    s = synth.fcc_supercell(4, 3.61, 0.02, seed=15, species=(13, 29), fractions=(0.3, 0.7))
+    model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+    md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], dt=1.0, skin=0.3, device=DEV,
+                  temperature=300.0, friction=0.05, seed=5)
+    lines = []
+    md.step(150, log_every=10, log=lines.append)
+    assert len(lines) == 15 and lines[-1]["step"] == 150 and abs(lines[-1]["total"] - lines[-1]["potential"] - lines[-1]["kinetic"]) < 1e-9
+    temps = [ln["temperature"] for ln in lines[-8:]]
+    # 256 atoms: the instantaneous temperature fluctuates by about 5 %; the mean of the last samples is near the target
+    assert 240.0 < sum(temps) / len(temps) < 360.0, temps
+    assert model.device_error() == 0

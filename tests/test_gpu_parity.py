@@ -373,3 +373,14 @@ def test_zbl_pair_repulsion(dtype, scale_zbl):
     out, ref = run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, zbl=zbl, scale_zbl=scale_zbl)
     base, _ = run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype)
     assert (out["energy"] - base["energy"]).abs().max().item() > 1e-2  # the term is really there
+
+
+@pytest.mark.parametrize("scatter_norm,radial", [
+    ("density", {}), ("density", {"apply_cutoff": False, "bias": True}), ("no_cutoff_density", {"apply_cutoff": False}),
+])
+def test_learned_edge_density_normalisation(scatter_norm, radial):
+    """atomic_basis.scatter_norm = density / no_cutoff_density: messages divided by alpha + beta * sum over the incoming
+    edges of tanh(MLP(radial)^2), with the envelope factor where the reference applies it."""
+    structs = synth.random_crystals(3, seed=27, nmin=4, nmax=10, zmax=3)
+    for dtype in (torch.float64, torch.float32):
+        run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, scatter_norm=scatter_norm, radial=radial)
