@@ -284,7 +284,8 @@ class TensorModel(torch.nn.Module):
         self._handle_key = None
         self._workspace = None
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
-        self._chunk_edges = None
+        # TACE_B200_CHUNK_EDGES=<n>: fixed edge-chunk size for every model instead of the automatic choice
+        self._chunk_edges = int(os.environ["TACE_B200_CHUNK_EDGES"]) if os.environ.get("TACE_B200_CHUNK_EDGES") else None
         self._auto_chunk = None
         self._set_target_property()
 
