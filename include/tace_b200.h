@@ -83,6 +83,10 @@ typedef struct {
                          / (beta * sum over incoming edges of tanh(MLP(radial)^2) [* envelope when env_after_mlp] + alpha);
                          2 "no_cutoff_density": the same without the envelope factor.  Weights "t<i>.dA0" [8][64], "dw1" [64],
                          "dab" = {alpha, beta} (+ "db0" [64], "db1" [1] with mlp_bias); not with edge_update_element2 */
+  int resnet_identity; /* resnet.linear_type = identity (tace/models/_e3nn/residual.py:145-250): the skip connection of layers
+                         above the first copies the ranks the layer output keeps instead of a per-species linear; no
+                         "t<i>.res.*" weights.  (linear_type = agnostic needs no flag: the host repeats the one matrix for
+                         every species, as it does for product_basis.agnostic) */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -351,13 +351,40 @@ class NodeEmbedding(torch.nn.Module):
         return self.elem_emb1(node_attrs)
 
 
+class SkipIdentity(torch.nn.Module):
+    """tace/models/_e3nn/residual.py:170-250: the skip connection without weights.  Equal irreps pass through; a smaller
+    output keeps the first input block of every irrep it has (ProjectDown); a larger one is zero-filled (ProjectUp)."""
+
+    def __init__(self, irreps_in: Irreps, irreps_out: Irreps):
+        super().__init__()
+        self.irreps_in, self.irreps_out = Irreps(irreps_in), Irreps(irreps_out)
+        small, big = (self.irreps_out, self.irreps_in) if self.irreps_out.dim <= self.irreps_in.dim else (self.irreps_in, self.irreps_out)
+        big_slices, used, idx = big.slices(), set(), []
+        for mul_ir in small:
+            for k, (target, sl) in enumerate(zip(big, big_slices)):
+                if k not in used and tuple(mul_ir) == tuple(target):
+                    idx.append(torch.arange(sl.start, sl.stop))
+                    used.add(k)
+                    break
+            else:
+                raise ValueError(f"{small} is not a sub-representation of {big}")
+        self.register_buffer("idx", torch.cat(idx), persistent=False)
+
+    def forward(self, x, attrs=None):
+        if self.irreps_in.dim >= self.irreps_out.dim:
+            return x[:, self.idx]
+        out = x.new_zeros(x.shape[0], self.irreps_out.dim)
+        out[:, self.idx] = x
+        return out
+
+
 class Interaction(torch.nn.Module):
     """tace/models/_e3nn/inter.py:28-285 (O3CgtpInteraction), irreps from
     tace/models/_e3nn/base.py:113-249."""
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
                  num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False, mlp_layer_norm=False,
-                 scatter_norm="avg_num_neighbors"):
+                 scatter_norm="avg_num_neighbors", resnet_linear_type="aware"):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
         self.scatter_norm = scatter_norm
@@ -386,8 +413,12 @@ class Interaction(torch.nn.Module):
             self.edge_density = MLP([num_radial_basis, 64, 1], bias=mlp_bias, layer_norm=mlp_layer_norm)
             self.alpha = torch.nn.Parameter(torch.tensor(float(avg_num_neighbors)))
             self.beta = torch.nn.Parameter(torch.tensor(0.0))
-        if layer > 0:  # resnet type "BB", linear_type "aware", use_first_resnet False
-            self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True, num_elements=num_elements)
+        if layer > 0:  # resnet type "BB", use_first_resnet False; tace/models/_e3nn/residual.py:145-168
+            if resnet_linear_type == "identity":
+                self.resnetBB = SkipIdentity(self.irreps_in, self.irreps_sc)
+            else:
+                self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True,
+                                       num_elements=num_elements if resnet_linear_type == "aware" else None)
 
     def forward(self, node_feats, node_attrs, edge_feats, edge_attrs, edge_index, edge_cutoff=None):
         sc = self.resnetBB(node_feats, node_attrs) if hasattr(self, "resnetBB") else None
@@ -417,10 +448,12 @@ class Product(torch.nn.Module):
     irreps from tace/models/_e3nn/base.py:252-360."""
 
     def __init__(self, layer, num_layers, num_elements, Lmax, lmax, num_channel, correlation, irreps_in,
-                 target_irreps):
+                 target_irreps, agnostic=False):
         super().__init__()
         C = num_channel
         self.correlation = correlation
+        if agnostic:  # prod.py:49-50: one coefficient linear for every species
+            num_elements = None
         last = layer == num_layers - 1
         self.irreps_in = Irreps(irreps_in)
         hidden = Irreps([(C, l) for _, l in self.irreps_in])
@@ -491,11 +524,13 @@ class Representation(torch.nn.Module):
                             cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
                             irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True),
                             mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2,
-                            scatter_norm=cfg.get("atomic_basis", {}).get("scatter_norm", "avg_num_neighbors"))
+                            scatter_norm=cfg.get("atomic_basis", {}).get("scatter_norm", "avg_num_neighbors"),
+                            resnet_linear_type=cfg.get("resnet", {}).get("linear_type", "aware"))
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],
-                        self.interactions[layer].irreps_out, [(1, 0)])
+                        self.interactions[layer].irreps_out, [(1, 0)],
+                        agnostic=cfg["product_basis"].get("agnostic", False))
             )
 
     def forward(self, node_attrs, edge_index, edge_vector, edge_length):

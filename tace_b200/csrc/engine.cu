@@ -315,6 +315,7 @@ struct Model : ModelBase {
   int n_fid = 1;              // read-out heads (entries of `statistics`)
   int zbl = 0;                // 0 off, 1 ZBL repulsion inside the species scale, 2 outside it
   int density = 0;            // atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density
+  bool res_identity = false;  // resnet.linear_type = identity: the skip connection copies the matching ranks, no weights
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -356,6 +357,7 @@ struct Model : ModelBase {
     n_fid = c.num_fidelities > 0 ? c.num_fidelities : 1;
     zbl = c.zbl;
     density = c.scatter_norm_density;
+    res_identity = c.resnet_identity != 0;
     if (zbl < 0 || zbl > 2 || density < 0 || density > 2 || (density && element2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
@@ -438,14 +440,14 @@ struct Model : ModelBase {
         }
         add_linear_weight(pre + "lin.l" + ls, (long long)C * C);
         add_linear_weight(pre + "linT.l" + ls, (long long)C * C);
-        if (p.has_res) {
+        if (p.has_res && !res_identity) {
           add_linear_weight(pre + "res.l" + ls, (long long)n_el * C * C);
           add_linear_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
         }
       }
       add_weight(pre + "c.b", (long long)n_el * C);
       add_weight(pre + "lin.b", C);
-      if (p.has_res) add_weight(pre + "res.b", (long long)n_el * C);
+      if (p.has_res && !res_identity) add_weight(pre + "res.b", (long long)n_el * C);
     }
     add_weight("ro.W1", (long long)n_fid * C * H);
     add_weight("ro.W2", (long long)n_fid * H);
@@ -1009,7 +1011,9 @@ struct Model : ModelBase {
                         l == 0 ? w(pre + "lin.b") : nullptr});
         CKL(run_linear(sp, NL, s));
       }
-      if (p.has_res) {  // per-species skip connection from the layer input
+      if (p.has_res && res_identity) {  // tace/models/_e3nn/residual.py:216-250: the ranks the output keeps, copied over
+        CKL(launch_add_rows(lb.h_out, (long long)p.Dout * C, lb.h_in, (long long)p.Din * C, NL, p.Dout * C, s));
+      } else if (p.has_res) {  // per-species skip connection from the layer input
         CKL(launch_gather_rows(lb.h_in, b.species_perm, lb.hs, NL, p.Din * C, s));
         std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
@@ -1177,7 +1181,9 @@ struct Model : ModelBase {
                         pre + "upT.l" + std::to_string(l), pre + "up.l" + std::to_string(l), C, lb.gh_in + (long long)l * l * C,
                         (long long)p.Din * C, C, nullptr});
         CKL(run_linear(sp, NL, s));
-        if (p.has_res) {
+        if (p.has_res && res_identity) {
+          CKL(launch_add_rows(lb.gh_in, (long long)p.Din * C, lb.gh_out, (long long)p.Dout * C, NL, p.Dout * C, s));
+        } else if (p.has_res) {
           CKL(launch_gather_rows(lb.gh_out, b.species_perm, lb.gout_s, NL, p.Dout * C, s));
           std::vector<SpeciesSpec> sp2;
           for (int l : p.out_ls)

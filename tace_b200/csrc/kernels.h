@@ -136,6 +136,9 @@ template <typename T> cudaError_t launch_fill_zero(T* p, long long n, cudaStream
 template <typename T> cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);
 template <typename T> cudaError_t launch_scatter_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);
 template <typename T> cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s);
+// dst[i, :width] += src[i, :width], rows dst_stride / src_stride elements apart
+template <typename T> cudaError_t launch_add_rows(T* dst, long long dst_stride, const T* src, long long src_stride, long long n, int width,
+                                                 cudaStream_t s);
 
 // ---- per-edge kernels (edge_kernels.cu) -------------------------------------------------------
 template <typename T>

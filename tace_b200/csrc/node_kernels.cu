@@ -355,6 +355,23 @@ cudaError_t launch_readout_linear_bwd(T* gh, long long hs, const T* factor, cons
   return cudaGetLastError();
 }
 
+// dst[i, :width] += src[i, :width] with independent row strides (the identity skip connection)
+template <typename T>
+__global__ void add_rows_kernel(T* __restrict__ dst, long long dst_stride, const T* __restrict__ src, long long src_stride, long long n,
+                                int width) {
+  const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (k >= n * width) return;
+  const long long i = k / width;
+  const long long c = k - i * width;
+  dst[i * dst_stride + c] += src[i * src_stride + c];
+}
+template <typename T>
+cudaError_t launch_add_rows(T* dst, long long dst_stride, const T* src, long long src_stride, long long n, int width, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  add_rows_kernel<T><<<(unsigned)((n * width + 255) / 256), 256, 0, s>>>(dst, dst_stride, src, src_stride, n, width);
+  return cudaGetLastError();
+}
+
 // ---- rows scaled by the learned edge density ----------------------------------------------------
 template <typename T>
 __global__ void scale_rows_kernel(T* __restrict__ x, const T* __restrict__ scale, long long n, int width, long long stride) {
@@ -444,6 +461,7 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
   template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
   template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \
+  template cudaError_t launch_add_rows<T>(T*, long long, const T*, long long, long long, int, cudaStream_t);  \
   template cudaError_t launch_scale_rows<T>(T*, const T*, long long, int, long long, cudaStream_t);           \
   template cudaError_t launch_density_node_bwd<T>(T*, const T*, const T*, T*, long long, int, long long, cudaStream_t); \
   template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, const int*, int, T*, int, cudaStream_t);

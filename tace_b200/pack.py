@@ -61,7 +61,7 @@ class ModelPlan:
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
                  apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0,
-                 density: int = 0):
+                 density: int = 0, resnet_type: str = "aware", product_agnostic: bool = False):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
@@ -70,6 +70,9 @@ class ModelPlan:
         self.n_fid, self.zbl = int(num_fidelities), int(zbl)
         # atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density (learned edge density)
         self.density = int(density)
+        # resnet.linear_type: aware (per-species linear), agnostic (one linear), identity (copy); product_basis.agnostic:
+        # one coefficient matrix for all species instead of one per species
+        self.resnet_type, self.product_agnostic = resnet_type, bool(product_agnostic)
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
         self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
@@ -119,18 +122,20 @@ class ModelPlan:
             out[pre + "linear_down.bias"] = (n0,)
             out[pre + "linear_nonlinearity.weight"] = ((L + 1) * C * C,)
             out[pre + "linear_nonlinearity.bias"] = (C,)
-            if lp.has_res:
-                out[pre + "resnetBB.weight"] = (n_el, len(lp.out_ls) * C * C)
-                out[pre + "resnetBB.bias"] = (n_el, C)
+            res_lead = (n_el,) if self.resnet_type == "aware" else ()
+            if lp.has_res and self.resnet_type != "identity":
+                out[pre + "resnetBB.weight"] = res_lead + (len(lp.out_ls) * C * C,)
+                out[pre + "resnetBB.bias"] = res_lead + (C,)
             pp = f"representation.products.{lp.t}."
-            out[pp + "coefs.0.weight"] = (n_el, len(lp.out_ls) * C * C)
-            out[pp + "coefs.0.bias"] = (n_el, C)
+            co_lead = () if self.product_agnostic else (n_el,)
+            out[pp + "coefs.0.weight"] = co_lead + (len(lp.out_ls) * C * C,)
+            out[pp + "coefs.0.bias"] = co_lead + (C,)
             if self.correlation >= 2:
-                out[pp + "coefs.1.weight"] = (n_el, sum(kp * C * C for kp in lp.kp))
-                out[pp + "coefs.1.bias"] = (n_el, C)
+                out[pp + "coefs.1.weight"] = co_lead + (sum(kp * C * C for kp in lp.kp),)
+                out[pp + "coefs.1.bias"] = co_lead + (C,)
             if self.correlation >= 3:
-                out[pp + "coefs.2.weight"] = (n_el, sum(kp * C * C for kp in lp.kp3))
-                out[pp + "coefs.2.bias"] = (n_el, C)
+                out[pp + "coefs.2.weight"] = co_lead + (sum(kp * C * C for kp in lp.kp3),)
+                out[pp + "coefs.2.bias"] = co_lead + (C,)
             out[pp + "linear.weight"] = (len(lp.out_ls) * C * C,)
             out[pp + "linear.bias"] = (C,)
         # tace/models/_e3nn/readout.py:192-221: with use_alllayer every layer has a read-out (a single linear on
@@ -229,6 +234,11 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         if transposed_name:
             out[transposed_name] = np.ascontiguousarray(np.swapaxes(mat, -1, -2))
 
+    def per_species(key: str, shared: bool) -> np.ndarray:
+        """A per-species parameter; one shared (species-agnostic) array is repeated for every species."""
+        arr = g(key)
+        return np.broadcast_to(arr[None], (n_el,) + arr.shape).copy() if shared else arr
+
     for lp in plan.layers:
         t = lp.t
         pre = f"representation.interactions.{t}."
@@ -278,25 +288,26 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         for l, m in enumerate(split(g(pre + "linear_nonlinearity.weight"), [(C, C)] * (L + 1))):
             put(tp + f"nl.l{l}", m / math.sqrt(C), tp + f"nlT.l{l}")
         out[tp + "nl.b"] = g(pre + "linear_nonlinearity.bias")
-        for l, m in zip(lp.out_ls, split(g(pp + "coefs.0.weight"), [(C, C)] * len(lp.out_ls))):
+        for l, m in zip(lp.out_ls, split(per_species(pp + "coefs.0.weight", plan.product_agnostic), [(C, C)] * len(lp.out_ls))):
             put(tp + f"c0.l{l}", m / math.sqrt(C), tp + f"c0T.l{l}")
-        bias = g(pp + "coefs.0.bias").copy()
+        bias = per_species(pp + "coefs.0.bias", plan.product_agnostic).copy()
         if plan.correlation >= 2:
-            for l, kp, m in zip(lp.out_ls, lp.kp, split(g(pp + "coefs.1.weight"), [(kp * C, C) for kp in lp.kp])):
+            for l, kp, m in zip(lp.out_ls, lp.kp, split(per_species(pp + "coefs.1.weight", plan.product_agnostic), [(kp * C, C) for kp in lp.kp])):
                 put(tp + f"c1.l{l}", m / math.sqrt(kp * C), tp + f"c1T.l{l}")
-            bias = bias + g(pp + "coefs.1.bias")
+            bias = bias + per_species(pp + "coefs.1.bias", plan.product_agnostic)
         if plan.correlation >= 3:
-            for l, kp, m in zip(lp.out_ls, lp.kp3, split(g(pp + "coefs.2.weight"), [(kp * C, C) for kp in lp.kp3])):
+            for l, kp, m in zip(lp.out_ls, lp.kp3, split(per_species(pp + "coefs.2.weight", plan.product_agnostic), [(kp * C, C) for kp in lp.kp3])):
                 put(tp + f"c2.l{l}", m / math.sqrt(kp * C), tp + f"c2T.l{l}")
-            bias = bias + g(pp + "coefs.2.bias")
+            bias = bias + per_species(pp + "coefs.2.bias", plan.product_agnostic)
         out[tp + "c.b"] = bias
         for l, m in zip(lp.out_ls, split(g(pp + "linear.weight"), [(C, C)] * len(lp.out_ls))):
             put(tp + f"lin.l{l}", m / math.sqrt(C), tp + f"linT.l{l}")
         out[tp + "lin.b"] = g(pp + "linear.bias")
-        if lp.has_res:
-            for l, m in zip(lp.out_ls, split(g(pre + "resnetBB.weight"), [(C, C)] * len(lp.out_ls))):
+        if lp.has_res and plan.resnet_type != "identity":
+            shared = plan.resnet_type == "agnostic"
+            for l, m in zip(lp.out_ls, split(per_species(pre + "resnetBB.weight", shared), [(C, C)] * len(lp.out_ls))):
                 put(tp + f"res.l{l}", m / math.sqrt(C), tp + f"resT.l{l}")
-            out[tp + "res.b"] = g(pre + "resnetBB.bias")
+            out[tp + "res.b"] = per_species(pre + "resnetBB.bias", shared)
     ro = plan.num_layers - 1 if plan.use_alllayer else 0
     # multi-head read-out (tace/models/_e3nn/readout.py:18-33,72-84): the hidden layer is [head][H] wide, the mask keeps
     # the block of the atom's head and the head's output column is taken, so head f only ever uses W1[:, f, :] and

@@ -384,3 +384,14 @@ def test_learned_edge_density_normalisation(scatter_norm, radial):
     structs = synth.random_crystals(3, seed=27, nmin=4, nmax=10, zmax=3)
     for dtype in (torch.float64, torch.float32):
         run_case(structs, 2, 32, [1, 2, 3], 4.5, dtype, scatter_norm=scatter_norm, radial=radial)
+
+
+@pytest.mark.parametrize("resnet_linear_type,product_agnostic", [("identity", False), ("agnostic", True), ("identity", True)])
+def test_skip_connection_types_and_species_agnostic_product(resnet_linear_type, product_agnostic):
+    """resnet.linear_type = identity (ranks copied over, none for the last layer but the scalars) / agnostic (one linear for
+    every species) and product_basis.agnostic (one coefficient matrix for every species); three layers so that a middle
+    layer (equal ranks in and out) and the last layer (scalars only) are both covered, node rank below edge rank."""
+    structs = synth.random_crystals(3, seed=29, nmin=4, nmax=10, zmax=3)
+    for dtype in (torch.float64, torch.float32):
+        run_case(structs, 3, 32, [1, 2, 3], 4.5, dtype, num_layers=3, Lmax=2, resnet_linear_type=resnet_linear_type,
+                 product_agnostic=product_agnostic)
