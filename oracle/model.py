@@ -384,11 +384,13 @@ class Interaction(torch.nn.Module):
 
     def __init__(self, layer, num_layers, num_elements, avg_num_neighbors, Lmax, lmax, correlation,
                  num_channel, num_radial_basis, radial_mlp, irreps_in, target_irreps, gate_m0=True, mlp_bias=False, mlp_layer_norm=False,
-                 scatter_norm="avg_num_neighbors", resnet_linear_type="aware"):
+                 scatter_norm="avg_num_neighbors", resnet_linear_type="aware", radial_dim=8):
         super().__init__()
         self.layer, self.avg_num_neighbors = layer, avg_num_neighbors
         self.scatter_norm = scatter_norm
         C = num_channel
+        self.num_channel, self.gate_m0, self.num_radial_basis = C, gate_m0, radial_dim
+        self.mlp_bias, self.mlp_layer_norm = mlp_bias, mlp_layer_norm
         self.irreps_in = Irreps(irreps_in)
         self.irreps_sh = Irreps.spherical_harmonics(lmax)
         tp_out = possible_tp_irreps(self.irreps_in, self.irreps_sh, Lmax if correlation == 1 else lmax)
@@ -407,8 +409,8 @@ class Interaction(torch.nn.Module):
         self.linear_down = Linear(tp_irreps_out.simplify(), self.nonlinearity.irreps_in, bias=True)
         # tace/models/_e3nn/base.py:183-185: edge features wider than the radial basis (an element-dependent edge
         # update) switch LayerNorm on inside the radial MLP
-        self.edge_info = MLP([num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel], bias=mlp_bias,
-                             layer_norm=mlp_layer_norm)
+        self.edge_info_dims = [num_radial_basis] + list(radial_mlp) + [self.rejector.weight_numel]
+        self.edge_info = MLP(self.edge_info_dims, bias=mlp_bias, layer_norm=mlp_layer_norm)
         if scatter_norm in ("density", "no_cutoff_density"):  # inter.py:102-110 (the edge density of MACE)
             self.edge_density = MLP([num_radial_basis, 64, 1], bias=mlp_bias, layer_norm=mlp_layer_norm)
             self.alpha = torch.nn.Parameter(torch.tensor(float(avg_num_neighbors)))
@@ -420,27 +422,35 @@ class Interaction(torch.nn.Module):
                 self.resnetBB = Linear(self.irreps_in, self.irreps_sc, bias=True,
                                        num_elements=num_elements if resnet_linear_type == "aware" else None)
 
-    def forward(self, node_feats, node_attrs, edge_feats, edge_attrs, edge_index, edge_cutoff=None):
-        sc = self.resnetBB(node_feats, node_attrs) if hasattr(self, "resnetBB") else None
-        x = self.linear_up(node_feats)
+    def messages(self, x, edge_feats, edge_attrs, edge_index, edge_cutoff, edge_vector, radial_basis):
+        """inter.py:166-183: per-edge weights from the radial MLP, weighted tensor product with the angular basis, sum
+        over the edges into every atom."""
         w = self.edge_info(edge_feats)
         if edge_cutoff is not None:  # inter.py:174-183
             w = w * edge_cutoff
         msg = self.rejector(x[edge_index[0]], edge_attrs, w)  # tace/models/_e3nn/fused.py:269-271
-        m = scatter_sum(msg, edge_index[1], x.shape[0])
+        return scatter_sum(msg, edge_index[1], x.shape[0])
+
+    def forward(self, node_feats, node_attrs, edge_feats, edge_attrs, edge_index, edge_cutoff=None, edge_vector=None,
+                radial_basis=None):
+        sc = self.resnetBB(node_feats, node_attrs) if hasattr(self, "resnetBB") else None
+        x = self.linear_up(node_feats)
+        m = self.messages(x, edge_feats, edge_attrs, edge_index, edge_cutoff, edge_vector, radial_basis)
         m = self.linear_down(m)
+        m = self.normalise(m, edge_feats, edge_index, edge_cutoff)
+        m = self.linear_nonlinearity(self.nonlinearity(m))
+        return m, sc
+
+    def normalise(self, m, edge_feats, edge_index, edge_cutoff):
         if hasattr(self, "edge_density"):  # inter.py:249-260, base.py:240-249
             density = torch.tanh(self.edge_density(edge_feats) ** 2)
             if edge_cutoff is not None and self.scatter_norm == "density":
                 density = density * edge_cutoff
-            density = scatter_sum(density, edge_index[1], x.shape[0])
+            density = scatter_sum(density, edge_index[1], m.shape[0])
             density = density * self.beta + self.alpha
             density = density.masked_fill(density == 0, 1e-9)
-            m = m / density
-        else:
-            m = m / self.avg_num_neighbors  # base.py:240-249
-        m = self.linear_nonlinearity(self.nonlinearity(m))
-        return m, sc
+            return m / density
+        return m / self.avg_num_neighbors  # base.py:240-249
 
 
 class Product(torch.nn.Module):
@@ -519,13 +529,26 @@ class Representation(torch.nn.Module):
         self.products = torch.nn.ModuleList()
         for layer in range(cfg["num_layers"]):
             irreps_in = self.node_embedding.irreps_out if layer == 0 else self.products[layer - 1].irreps_out
+            ab = cfg.get("atomic_basis", {})
+            kinds = ab.get("type", "cgtp")
+            kind = kinds[layer] if isinstance(kinds, (list, tuple)) else kinds
+            cls, extra = Interaction, {}
+            if kind == "uv_so2":  # the TECE edge block (tace/models/_e3nn/inter.py:440-519,779)
+                from .tece import build_tece_interaction
+
+                cls = build_tece_interaction(Interaction)
+                edge_nl = ab.get("edge_nonlinear", "so2_sigmoid_gate")
+                edge_nl = edge_nl[layer] if isinstance(edge_nl, (list, tuple)) else edge_nl
+                extra = dict(mmax=cfg.get("mmax", 2), num_head=ab.get("num_head") or 1, edge_ace_hidden=ab.get("edge_ace_hidden"),
+                             edge_wise_hidden=ab.get("edge_wise_hidden"), edge_act=edge_nl.split("_")[1])
             self.interactions.append(
-                Interaction(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
-                            cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
-                            irreps_in, [(1, 0)], gate_m0=cfg.get("atomic_basis", {}).get("gate_m0", True),
-                            mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2,
-                            scatter_norm=cfg.get("atomic_basis", {}).get("scatter_norm", "avg_num_neighbors"),
-                            resnet_linear_type=cfg.get("resnet", {}).get("linear_type", "aware"))
+                cls(layer, cfg["num_layers"], n_el, cfg["avg_num_neighbors"], L, l,
+                    cfg["product_basis"]["correlation"][layer], C, edge_dim, rb["hidden"],
+                    irreps_in, [(1, 0)], gate_m0=ab.get("gate_m0", True),
+                    mlp_bias=rb.get("bias", False), mlp_layer_norm=self.element2,
+                    scatter_norm=ab.get("scatter_norm", "avg_num_neighbors"),
+                    resnet_linear_type=cfg.get("resnet", {}).get("linear_type", "aware"),
+                    radial_dim=rb["num_radial_basis"], **extra)
             )
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],
@@ -540,7 +563,7 @@ class Representation(torch.nn.Module):
         descriptors = []
         for inter, prod in zip(self.interactions, self.products):
             ef = self.edge_updates[len(descriptors)](node_attrs, edge_feats, edge_index) if self.element2 else edge_feats
-            h, sc = inter(h, node_attrs, ef, edge_attrs, edge_index, edge_cutoff)
+            h, sc = inter(h, node_attrs, ef, edge_attrs, edge_index, edge_cutoff, edge_vector, edge_feats)
             h = prod(h, node_attrs, sc)
             descriptors.append(h)
         return descriptors
