@@ -87,6 +87,11 @@ typedef struct {
                          above the first copies the ranks the layer output keeps instead of a per-species linear; no
                          "t<i>.res.*" weights.  (linear_type = agnostic needs no flag: the host repeats the one matrix for
                          every species, as it does for product_basis.agnostic) */
+  int product_bilinear; /* product_basis.nonlinear = silu_bilineargate (tace/models/_e3nn/prod.py:58,87-155,183-247; correlation
+                         2 only): the product's linear_up maps A to two factors x, y and to one SiLU gate per (path, channel);
+                         the second-order basis is gate * (x (x) [y, 1]) with separate factors (no symmetry) and the
+                         first-order coefficients act on x.  Weights "t<i>.pu.l<l>" [C][2C], "t<i>.pg" [C][paths*C], biases
+                         "t<i>.pu.b" [2C], "t<i>.pg.b" [paths*C] */
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -125,7 +125,10 @@ class TensorProduct(torch.nn.Module):
     def __init__(self, in1: Irreps, in2: Irreps, out: Irreps, paths):
         super().__init__()
         self.in1, self.in2, self.out, self.paths = Irreps(in1), Irreps(in2), Irreps(out), paths
-        self.weight_numel = sum(self.in1[i][0] * self.in2[j][0] for i, j, _, mode in paths if mode == "uvu")
+        # "uvu": one weight per (u, v); "uuuw": the channel-wise product with one weight per channel (trainable = True in
+        # tace/models/_e3nn/paths.py:66-69)
+        self.weight_numel = sum(self.in1[i][0] * (self.in2[j][0] if mode == "uvu" else 1) for i, j, _, mode in paths
+                                if mode in ("uvu", "uuuw"))
 
     def forward(self, x1: torch.Tensor, x2: torch.Tensor, w: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x1.shape[0]
@@ -140,6 +143,10 @@ class TensorProduct(torch.nn.Module):
                 wk = w[:, woff : woff + m1 * m2].reshape(n, m1, m2)
                 woff += m1 * m2
                 o = torch.einsum("zuv,ijk,zui,zvj->zuk", wk, c, a, b)
+            elif mode == "uuuw":
+                wk = w[:, woff : woff + m1]
+                woff += m1
+                o = torch.einsum("zu,ijk,zui,zuj->zuk", wk, c, a, b)
             else:  # uuu, no weights
                 o = torch.einsum("ijk,zui,zuj->zuk", c, a, b)
             outs.append(o.reshape(n, -1))
@@ -458,10 +465,11 @@ class Product(torch.nn.Module):
     irreps from tace/models/_e3nn/base.py:252-360."""
 
     def __init__(self, layer, num_layers, num_elements, Lmax, lmax, num_channel, correlation, irreps_in,
-                 target_irreps, agnostic=False):
+                 target_irreps, agnostic=False, bilinear=False):
         super().__init__()
         C = num_channel
         self.correlation = correlation
+        self.bilinear = bilinear
         if agnostic:  # prod.py:49-50: one coefficient linear for every species
             num_elements = None
         last = layer == num_layers - 1
@@ -487,19 +495,46 @@ class Product(torch.nn.Module):
         self.coefs = torch.nn.ModuleList([Linear(hidden.simplify(), coefs_out, bias=True, num_elements=num_elements)])
         self.aces = torch.nn.ModuleList()
         in1 = hidden
+        base = hidden
+        if bilinear:  # prod.py:87-92: the second factor gets a block of ones, so the product also carries the factor itself
+            assert correlation == 2
+            base = Irreps(list(hidden) + [(C, 0)])
         for nu in range(2, correlation + 1):
-            paths, out = generate_paths(tp_out_list[nu - 2], in1, hidden, "uuu", identical_inputs=(nu == 2))
-            self.aces.append(TensorProduct(in1, hidden, out, paths))
+            if bilinear:
+                paths, out = generate_paths(tp_out_list[nu - 2], in1, base, "uuuw")
+            else:
+                paths, out = generate_paths(tp_out_list[nu - 2], in1, hidden, "uuu", identical_inputs=(nu == 2))
+            self.aces.append(TensorProduct(in1, base, out, paths))
             self.coefs.append(
                 Linear(Irreps([(C, l) for _, l in out]).simplify(), coefs_out, bias=True, num_elements=num_elements)
             )
             in1 = out
         self.linear = Linear(Irreps([(C, l) for _, l in coefs_out]), self.irreps_out, bias=True)
+        if bilinear:  # prod.py:128-155: gate scalars for every product path and both factors from one linear
+            self.num_gates = self.aces[0].weight_numel
+            self.hidden = hidden
+            self.linear_up = Linear(self.irreps_in, Irreps([(self.num_gates, 0)] + [(2 * C, l) for _, l in hidden]), bias=True)
 
     def forward(self, node_feats, node_attrs, sc):
+        base_feats, gates = node_feats, None
+        if self.bilinear:  # prod.py:183-221
+            x = self.linear_up(node_feats)
+            gates = torch.nn.functional.silu(x[:, :self.num_gates])
+            n, off, first, second = x.shape[0], self.num_gates, [], []
+            for mul, l in self.hidden:
+                field = x[:, off:off + 2 * mul * (2 * l + 1)].reshape(n, 2 * mul, 2 * l + 1)
+                off += 2 * mul * (2 * l + 1)
+                first.append(field[:, :mul].reshape(n, -1))
+                second.append(field[:, mul:].reshape(n, -1))
+            node_feats = torch.cat(first, dim=-1)
+            base_feats = torch.cat(second + [x.new_ones(n, self.hidden[0][0])], dim=-1)
         corr = {1: node_feats}
         outs = self.coefs[0](corr[1], node_attrs)
         for nu in range(2, self.correlation + 1):
+            if self.bilinear:
+                corr[nu] = self.aces[nu - 2](corr[nu - 1], base_feats, gates)
+                outs = outs + self.coefs[nu - 1](corr[nu], node_attrs)
+                continue
             corr[nu] = self.aces[nu - 2](corr[nu - 1], node_feats)
             outs = outs + self.coefs[nu - 1](corr[nu], node_attrs)
         outs = self.linear(outs)
@@ -553,7 +588,8 @@ class Representation(torch.nn.Module):
             self.products.append(
                 Product(layer, cfg["num_layers"], n_el, L, l, C, cfg["product_basis"]["correlation"][layer],
                         self.interactions[layer].irreps_out, [(1, 0)],
-                        agnostic=cfg["product_basis"].get("agnostic", False))
+                        agnostic=cfg["product_basis"].get("agnostic", False),
+                        bilinear=cfg["product_basis"].get("nonlinear") == "silu_bilineargate")
             )
 
     def forward(self, node_attrs, edge_index, edge_vector, edge_length):

@@ -58,6 +58,22 @@ bool pb_meta(int L, int Lout, PBMeta& m) {
   return false;
 }
 
+// gated bilinear product (two different factors, the second extended by a block of ones)
+bool pbl_meta(int L, int Lout, PBMeta& m) {
+#define PBM(TAG) { m = {PBL_##TAG::NP, PBL_##TAG::NB, pbl_##TAG##_k, pbl_##TAG##_base}; return true; }
+  if (L == 1 && Lout < 0) PBM(L1_T)
+  if (L == 1 && Lout == 1) PBM(L1_A)
+  if (L == 2 && Lout < 0) PBM(L2_T)
+  if (L == 2 && Lout == 1) PBM(L2_N1)
+  if (L == 2 && Lout == 2) PBM(L2_A)
+  if (L == 3 && Lout < 0) PBM(L3_T)
+  if (L == 3 && Lout == 1) PBM(L3_N1)
+  if (L == 3 && Lout == 2) PBM(L3_N2)
+  if (L == 3 && Lout == 3) PBM(L3_A)
+#undef PBM
+  return false;
+}
+
 // third-order basis (correlation 3): L = rank of A, Lout as above
 bool pb3_meta(int L, int Lout, PBMeta& m) {
 #define PBM(TAG) { m = {PB3_##TAG::NP, PB3_##TAG::NB, pb3_##TAG##_k, pb3_##TAG##_base}; return true; }
@@ -316,6 +332,7 @@ struct Model : ModelBase {
   int zbl = 0;                // 0 off, 1 ZBL repulsion inside the species scale, 2 outside it
   int density = 0;            // atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density
   bool res_identity = false;  // resnet.linear_type = identity: the skip connection copies the matching ranks, no weights
+  bool bilinear = false;      // product_basis.nonlinear = silu_bilineargate: gated product of two linear images of A
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -358,6 +375,8 @@ struct Model : ModelBase {
     zbl = c.zbl;
     density = c.scatter_norm_density;
     res_identity = c.resnet_identity != 0;
+    bilinear = c.product_bilinear != 0;
+    if (bilinear && c.correlation != 2) return TACE_ERR_UNSUPPORTED_CONFIG;
     if (zbl < 0 || zbl > 2 || density < 0 || density > 2 || (density && element2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
     if (Ln > L || (Ln < L && c.correlation < 2)) return TACE_ERR_UNSUPPORTED_CONFIG;
@@ -371,7 +390,8 @@ struct Model : ModelBase {
       const int lout = p.last ? -1 : Ln;
       p.pb_lout = (c.correlation == 3) ? L : lout;  // with a third order the second keeps every rank (prod.py:216-266)
       p.pb3 = PBMeta{0, 0, nullptr, nullptr};
-      if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !pb_meta(L, p.pb_lout, p.pb)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !(bilinear ? pbl_meta(L, p.pb_lout, p.pb) : pb_meta(L, p.pb_lout, p.pb)))
+        return TACE_ERR_UNSUPPORTED_CONFIG;
       if (c.correlation == 3 && !pb3_meta(L, lout, p.pb3)) return TACE_ERR_UNSUPPORTED_CONFIG;
       p.Din = p.scalar_src ? 1 : Dn;
       p.Dout = p.last ? 1 : Dn;
@@ -445,6 +465,16 @@ struct Model : ModelBase {
           add_linear_weight(pre + "resT.l" + ls, (long long)n_el * C * C);
         }
       }
+      if (bilinear) {  // linear_up of the product: every rank to both factors, the scalars also to the gates
+        for (int l = 0; l <= L; ++l) {
+          add_linear_weight(pre + "pu.l" + std::to_string(l), (long long)C * 2 * C);
+          add_linear_weight(pre + "puT.l" + std::to_string(l), (long long)C * 2 * C);
+        }
+        add_linear_weight(pre + "pg", (long long)C * p.pb.NP * C);
+        add_linear_weight(pre + "pgT", (long long)C * p.pb.NP * C);
+        add_weight(pre + "pu.b", 2 * C);
+        add_weight(pre + "pg.b", (long long)p.pb.NP * C);
+      }
       add_weight(pre + "c.b", (long long)n_el * C);
       add_weight(pre + "lin.b", C);
       if (p.has_res && !res_identity) add_weight(pre + "res.b", (long long)n_el * C);
@@ -494,6 +524,7 @@ struct Model : ModelBase {
     T *As, *gAs, *gout_s, *hs;  // species-sorted copies used by the per-species linears
     T *B3, *gB2;                // third-order basis (reused for its gradient) and the gradient of the second-order one
     T *inv_density, *gdens;     // learned edge density: 1 / density_i and dE / d density_i
+    T *XY, *gXY, *Zg, *gZg;     // gated bilinear product: both factors per (atom, component), gate pre-activations, gradients
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
@@ -553,6 +584,11 @@ struct Model : ModelBase {
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.inv_density = density ? ar.take<T>(NL) : nullptr; lb.gdens = density ? ar.take<T>(NL) : nullptr;
+      lb.XY = lb.gXY = lb.Zg = lb.gZg = nullptr;
+      if (bilinear) {
+        lb.XY = ar.take<T>((size_t)NL * D * 2 * C); lb.gXY = ar.take<T>((size_t)NL * D * 2 * C);
+        lb.Zg = ar.take<T>((size_t)NL * p.pb.NP * C); lb.gZg = ar.take<T>((size_t)NL * p.pb.NP * C);
+      }
       lb.a = ar.take<T>((size_t)NL * D * C);
       lb.ga = ar.take<T>((size_t)NL * D * C);
       lb.A = ar.take<T>((size_t)NL * D * C);
@@ -605,6 +641,7 @@ struct Model : ModelBase {
     const T* A; long long a_s1, a_s2; int q, K;
     std::string wname, wname_t; int N;
     T* Cm; long long c_s1, c_s2; const T* bias;
+    int accumulate;  // Cm += instead of Cm =
   };
   // Plain (not per-species) linears: tcgen05 for fp32 models when every shape fits, CUDA cores otherwise.
   cudaError_t run_linear(const std::vector<LinSpec>& specs, long long n_atoms, cudaStream_t s) {
@@ -617,12 +654,13 @@ struct Model : ModelBase {
         probs[i] = {reinterpret_cast<const float*>(sp.A), sp.a_s1, sp.a_s2, sp.q, n_atoms, sp.K, sp.N,
                     reinterpret_cast<const float*>(w(sp.wname_t + "_hi")), reinterpret_cast<const float*>(w(sp.wname_t + "_lo")),
                     reinterpret_cast<float*>(sp.Cm), sp.c_s1, sp.c_s2, reinterpret_cast<const float*>(sp.bias)};
+        probs[i].accumulate = sp.accumulate;
       }
       return launch_tc_linear(probs, (int)specs.size(), dev_error, s);
     }
     GemmBatch<T> gb = plain_batch(n_atoms);
     for (const auto& sp : specs)
-      add_problem(gb, sp.A, sp.a_s1, sp.a_s2, sp.q, sp.K, w(sp.wname), sp.N, sp.Cm, sp.c_s1, sp.c_s2, sp.bias, 0);
+      add_problem(gb, sp.A, sp.a_s1, sp.a_s2, sp.q, sp.K, w(sp.wname), sp.N, sp.Cm, sp.c_s1, sp.c_s2, sp.bias, sp.accumulate);
     return launch_gemm(gb, n_atoms, s);
   }
 
@@ -973,12 +1011,27 @@ struct Model : ModelBase {
       debug.push_back({"A" + ts, lb.A, NL * D * C});
       // per-species part in species-sorted space: gather A, product basis, coefficient linears scatter into `out`
       CKL(launch_gather_rows(lb.A, b.species_perm, lb.As, NL, D * C, s));
-      if (cfg.correlation >= 2) CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.pb_lout, C, s));
+      if (bilinear) {
+        std::vector<LinSpec> sp;
+        for (int l = 0; l <= L; ++l)
+          sp.push_back({lb.As + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, pre + "pu.l" + std::to_string(l),
+                        pre + "puT.l" + std::to_string(l), 2 * C, lb.XY + (long long)l * l * 2 * C, (long long)D * 2 * C, 2 * C,
+                        l == 0 ? w(pre + "pu.b") : nullptr});
+        CKL(run_linear(sp, NL, s));
+        sp.clear();
+        sp.push_back({lb.As, (long long)D * C, C, 1, C, pre + "pg", pre + "pgT", p.pb.NP * C, lb.Zg, (long long)p.pb.NP * C, 0,
+                      w(pre + "pg.b")});
+        CKL(run_linear(sp, NL, s));
+        CKL(launch_pbl_fwd(lb.XY, lb.Zg, lb.B2, (int)NL, L, p.pb_lout, C, s));
+      } else if (cfg.correlation >= 2) {
+        CKL(launch_pb_fwd(lb.As, lb.B2, (int)NL, L, p.pb_lout, C, s));
+      }
       if (cfg.correlation >= 3) CKL(launch_pb3_fwd(lb.As, lb.B2, lb.B3, (int)NL, L, p.last ? -1 : Ln, C, s));
       {
         std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
-          sp.push_back({lb.As + (long long)l * l * C, (long long)D * C, C, 2 * l + 1, C, pre + "c0.l" + std::to_string(l),
+          sp.push_back({bilinear ? lb.XY + (long long)l * l * 2 * C : lb.As + (long long)l * l * C, (long long)D * C * (bilinear ? 2 : 1),
+                        (long long)C * (bilinear ? 2 : 1), 2 * l + 1, C, pre + "c0.l" + std::to_string(l),
                         pre + "c0T.l" + std::to_string(l), C, lb.out + (long long)l * l * C, (long long)p.Dout * C, C,
                         l == 0 ? w(pre + "c.b") : nullptr, true, 0});
         CKL(run_species_linear(sp, b, NL, s));
@@ -1076,12 +1129,14 @@ struct Model : ModelBase {
       }
       // through the per-species coefficients and the product basis, in species-sorted space
       CKL(launch_gather_rows(lb.gout, b.species_perm, lb.gout_s, NL, p.Dout * C, s));
-      if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gAs, NL * D * C, s));
+      if (bilinear) CKL(launch_fill_zero(lb.gXY, NL * D * 2 * C, s));
+      else if ((int)p.out_ls.size() != L + 1) CKL(launch_fill_zero(lb.gAs, NL * D * C, s));
       {
         std::vector<SpeciesSpec> sp;
         for (int l : p.out_ls)
           sp.push_back({lb.gout_s + (long long)l * l * C, (long long)p.Dout * C, C, 2 * l + 1, C, pre + "c0T.l" + std::to_string(l),
-                        pre + "c0.l" + std::to_string(l), C, lb.gAs + (long long)l * l * C, (long long)D * C, C, nullptr, false, 0});
+                        pre + "c0.l" + std::to_string(l), C, bilinear ? lb.gXY + (long long)l * l * 2 * C : lb.gAs + (long long)l * l * C,
+                        (long long)D * C * (bilinear ? 2 : 1), (long long)C * (bilinear ? 2 : 1), nullptr, false, 0});
         CKL(run_species_linear(sp, b, NL, s));
         if (cfg.correlation >= 2) {
           // gradient of the second-order basis: written over B2 itself, or into gB2 when the third order still needs B2
@@ -1111,7 +1166,20 @@ struct Model : ModelBase {
             CKL(launch_pb3_bwd(lb.As, lb.B2, lb.B3, lb.gB2, lb.gAs, (int)NL, L, p.last ? -1 : Ln, C, s));
             ++launches;
           }
-          CKL(launch_pb_bwd(lb.As, g2, lb.gAs, (int)NL, L, p.pb_lout, C, s));
+          if (bilinear) {  // back through the gated product, then through the product's own linear_up
+            CKL(launch_pbl_bwd(lb.XY, lb.Zg, g2, lb.gXY, lb.gZg, (int)NL, L, p.pb_lout, C, s));
+            std::vector<LinSpec> lp;
+            for (int l = 0; l <= L; ++l)
+              lp.push_back({lb.gXY + (long long)l * l * 2 * C, (long long)D * 2 * C, 2 * C, 2 * l + 1, 2 * C, pre + "puT.l" + std::to_string(l),
+                            pre + "pu.l" + std::to_string(l), C, lb.gAs + (long long)l * l * C, (long long)D * C, C, nullptr});
+            CKL(run_linear(lp, NL, s));
+            lp.clear();
+            lp.push_back({lb.gZg, (long long)p.pb.NP * C, 0, 1, p.pb.NP * C, pre + "pgT", pre + "pg", C, lb.gAs, (long long)D * C, 0,
+                          nullptr, 1});
+            CKL(run_linear(lp, NL, s));
+          } else {
+            CKL(launch_pb_bwd(lb.As, g2, lb.gAs, (int)NL, L, p.pb_lout, C, s));
+          }
         }
       }
       CKL(launch_scatter_rows(lb.gAs, b.species_perm, lb.gA, NL, D * C, s));

@@ -312,6 +312,86 @@ def gen_product(L, Lout, out):
     return dict(tag=tag, P=P, nb=lay.nm, nnz=nnz)
 
 
+def bilinear_paths(L, outs):
+    """Paths of the gated bilinear product (tace/models/_e3nn/prod.py:87-111, paths.py:30-71): first factor ranks 0..L,
+    second factor ranks 0..L followed by a block of ones (rank 0, written l2 = -1 here), output-rank major."""
+    paths = []
+    for l3 in outs:
+        for l1 in range(L + 1):
+            for l2 in range(L + 1):
+                if abs(l1 - l2) <= l3 <= l1 + l2 and (l1 + l2 + l3) % 2 == 0:
+                    paths.append((l1, l2, l3))
+            if l1 == l3:
+                paths.append((l1, -1, l3))
+    return paths
+
+
+def gen_product_bilinear(L, Lout, out):
+    """b[p, m3] = w[p] * sum K x[l1, m1] y[l2, m2] for two different factors and one weight per path; the paths whose
+    second factor is the block of ones reduce to w[p] * x[l3, m3].  Backward: dx, dy (accumulated) and dw."""
+    last = Lout < 0
+    tag = f"L{L}_" + ("T" if last else "A" if Lout == L else f"N{Lout}")
+    outs = [0] if last else list(range(Lout + 1))
+    paths = bilinear_paths(L, outs)
+    lay = Layout(paths, outs)
+    D = (L + 1) ** 2
+    P = len(paths)
+    o = out.append
+    o(f"// ---- gated bilinear product (x (x) [y, 1]), L={L}, {'scalar outputs' if last else f'output ranks <= {Lout}'}: {P} paths, "
+      f"{lay.nm} components")
+    o(f"struct PBL_{tag} {{ static constexpr int L = {L}, NP = {P}, NB = {lay.nm}, D = {D}; }};")
+    o(f"static const int pbl_{tag}_k[{len(outs)}] = {{{', '.join(str(lay.k[l]) for l in outs)}}};")
+    o(f"static const int pbl_{tag}_base[{len(outs)}] = {{{', '.join(str(lay.base[l]) for l in outs)}}};")
+
+    def coupling(l1, l2, l3):
+        return w3j(l1, l2, l3) * math.sqrt(2 * l3 + 1)
+
+    o(f"struct PBLX_{tag} : PBL_{tag} {{")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd(const T (&x)[{D}], const T (&y)[{D}], const T (&w)[{P}], T (&b)[{lay.nm}]) {{")
+    for p, (l1, l2, l3) in enumerate(paths):
+        for m3 in range(2 * l3 + 1):
+            if l2 < 0:
+                o(f"    b[{lay.idx(p, m3)}] = w[{p}] * x[{l1 * l1 + m3}];")
+                continue
+            K = coupling(l1, l2, l3)
+            terms = [f"{lit(float(K[m1, m2, m3]))} * x[{l1 * l1 + m1}] * y[{l2 * l2 + m2}]"
+                     for m1 in range(2 * l1 + 1) for m2 in range(2 * l2 + 1) if K[m1, m2, m3] != 0.0]
+            o(f"    b[{lay.idx(p, m3)}] = w[{p}] * ({' + '.join(terms) if terms else 'T(0)'});")
+    o("  }")
+    o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd(const T (&x)[{D}], const T (&y)[{D}], const T (&w)[{P}], "
+      f"const T (&db)[{lay.nm}], T (&dx)[{D}], T (&dy)[{D}], T (&dw)[{P}]) {{")
+    for p, (l1, l2, l3) in enumerate(paths):
+        if l2 < 0:
+            terms = [f"x[{l1 * l1 + m}] * db[{lay.idx(p, m)}]" for m in range(2 * l3 + 1)]
+            o(f"    dw[{p}] = {' + '.join(terms)};")
+            for m in range(2 * l3 + 1):
+                o(f"    dx[{l1 * l1 + m}] += w[{p}] * db[{lay.idx(p, m)}];")
+            continue
+        K = coupling(l1, l2, l3)
+        o("    {")
+        o(f"      T s = T(0), t;")
+        for m3 in range(2 * l3 + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * x[{l1 * l1 + m1}] * y[{l2 * l2 + m2}]"
+                     for m1 in range(2 * l1 + 1) for m2 in range(2 * l2 + 1) if K[m1, m2, m3] != 0.0]
+            if terms:
+                o(f"      s += db[{lay.idx(p, m3)}] * ({' + '.join(terms)});")
+        o(f"      dw[{p}] = s;")
+        for m1 in range(2 * l1 + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * y[{l2 * l2 + m2}] * db[{lay.idx(p, m3)}]"
+                     for m2 in range(2 * l2 + 1) for m3 in range(2 * l3 + 1) if K[m1, m2, m3] != 0.0]
+            if terms:
+                o(f"      t = {' + '.join(terms)}; dx[{l1 * l1 + m1}] += w[{p}] * t;")
+        for m2 in range(2 * l2 + 1):
+            terms = [f"{lit(float(K[m1, m2, m3]))} * x[{l1 * l1 + m1}] * db[{lay.idx(p, m3)}]"
+                     for m1 in range(2 * l1 + 1) for m3 in range(2 * l3 + 1) if K[m1, m2, m3] != 0.0]
+            if terms:
+                o(f"      t = {' + '.join(terms)}; dy[{l2 * l2 + m2}] += w[{p}] * t;")
+        o("    }")
+    o("  }")
+    o("};")
+    return dict(tag="bilinear " + tag, P=P, nb=lay.nm)
+
+
 def gen_product3(L, Lout, out):
     """Third-order product basis B3 = (A x A) x A (correlation 3, tace/models/_e3nn/prod.py:216-266): the first factor
     is the full second-order basis (every path of ranks <= L keeps its own slot, layout of PB_L{L}_A), the second is A,
@@ -395,6 +475,8 @@ def main():
             summary.append(gen_product(L, Lout, out))
         for Lout in [-1] + list(range(1, L + 1)):
             summary.append(gen_product3(L, Lout, out))
+        for Lout in [-1] + list(range(1, L + 1)):
+            summary.append(gen_product_bilinear(L, Lout, out))
     out.append("}  // namespace tace")
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "tp_gen.cuh"), "w") as fh:

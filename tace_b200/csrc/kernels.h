@@ -65,6 +65,12 @@ template <typename T> cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* g
 // L: rank of A; Lout: highest output rank, or < 0 for scalar outputs only (the last layer)
 template <typename T> cudaError_t launch_pb_fwd(const T* A, T* B2, int n, int L, int Lout, int C, cudaStream_t s);
 template <typename T> cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int Lout, int C, cudaStream_t s);
+// gated bilinear product (product_basis.nonlinear = silu_bilineargate): XY [n][D][2C] holds both factors (channels [0, C) /
+// [C, 2C)), Zg [n][NP][C] the gate pre-activations; B2 = silu(Zg) * (x (x) [y, 1]).  bwd: gXY[.., :C] += , gXY[.., C:] = ,
+// gZg = (gradients of the pre-activations)
+template <typename T> cudaError_t launch_pbl_fwd(const T* XY, const T* Zg, T* B2, int n, int L, int Lout, int C, cudaStream_t s);
+template <typename T> cudaError_t launch_pbl_bwd(const T* XY, const T* Zg, const T* gB2, T* gXY, T* gZg, int n, int L, int Lout, int C,
+                                                cudaStream_t s);
 // read-out C -> H -> 1 with scaled SiLU, per-species scale, isolated-atom masking, atomic energies
 // (tace/models/_e3nn/readout.py:72-84, tace/models/blocks.py:250-273,332-379, _e3nn/tace.py:361-417).
 template <typename T>

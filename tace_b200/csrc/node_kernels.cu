@@ -213,6 +213,75 @@ cudaError_t launch_pb_bwd(const T* A, const T* gB2, T* gA, int n, int L, int Lou
   TACE_PB_DISPATCH(pb_bwd_kernel, A, gB2, gA, n, C)
 }
 
+// ---- gated bilinear product (product_basis.nonlinear = silu_bilineargate, tace/models/_e3nn/prod.py:183-247) ------
+// XY holds both factors per (atom, component): channels [0, C) the first, [C, 2C) the second; Zg [n][NP][C] the gate
+// pre-activations, one per (path, channel); B2 [n][NB][C] = silu(Zg) * (x (x) [y, 1]) per path.
+template <typename T, typename PB>
+__global__ void __launch_bounds__(128) pbl_fwd_kernel(const T* __restrict__ XY, const T* __restrict__ Zg, T* __restrict__ B2, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  T x[PB::D], y[PB::D], w[PB::NP], b[PB::NB];
+  const T* Xi = XY + (long long)i * PB::D * 2 * C;
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) { x[k] = Xi[k * 2 * C + c]; y[k] = Xi[k * 2 * C + C + c]; }
+  const T* Zi = Zg + (long long)i * PB::NP * C;
+#pragma unroll
+  for (int p = 0; p < PB::NP; ++p) w[p] = silu_(Zi[p * C + c]);
+  PB::template fwd<T>(x, y, w, b);
+  T* Bi = B2 + (long long)i * PB::NB * C;
+#pragma unroll
+  for (int k = 0; k < PB::NB; ++k) Bi[k * C + c] = b[k];
+}
+// gXY[.., :C] += dB2/dx^T gB2 (it already holds the gradient that reached x through the first-order coefficients),
+// gXY[.., C:] = dB2/dy^T gB2, gZg = silu'(Zg) * dB2/dw^T gB2
+template <typename T, typename PB>
+__global__ void __launch_bounds__(128) pbl_bwd_kernel(const T* __restrict__ XY, const T* __restrict__ Zg, const T* __restrict__ gB2,
+                                                      T* __restrict__ gXY, T* __restrict__ gZg, int n, int C) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * C) return;
+  const int i = idx / C, c = idx - (long long)i * C;
+  T x[PB::D], y[PB::D], w[PB::NP], db[PB::NB], dx[PB::D], dy[PB::D], dw[PB::NP];
+  const T* Xi = XY + (long long)i * PB::D * 2 * C;
+  T* gXi = gXY + (long long)i * PB::D * 2 * C;
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) { x[k] = Xi[k * 2 * C + c]; y[k] = Xi[k * 2 * C + C + c]; dx[k] = gXi[k * 2 * C + c]; dy[k] = T(0); }
+  const T* Zi = Zg + (long long)i * PB::NP * C;
+#pragma unroll
+  for (int p = 0; p < PB::NP; ++p) w[p] = silu_(Zi[p * C + c]);
+  const T* Gi = gB2 + (long long)i * PB::NB * C;
+#pragma unroll
+  for (int k = 0; k < PB::NB; ++k) db[k] = Gi[k * C + c];
+  PB::template bwd<T>(x, y, w, db, dx, dy, dw);
+#pragma unroll
+  for (int k = 0; k < PB::D; ++k) { gXi[k * 2 * C + c] = dx[k]; gXi[k * 2 * C + C + c] = dy[k]; }
+  T* gZi = gZg + (long long)i * PB::NP * C;
+#pragma unroll
+  for (int p = 0; p < PB::NP; ++p) gZi[p * C + c] = dw[p] * silu_grad_(Zi[p * C + c]);
+}
+#define TACE_PBL_DISPATCH(KERNEL, ...)                                                     \
+  if (n <= 0) return cudaSuccess;                                                          \
+  const unsigned grid = (unsigned)(((long long)n * C + 127) / 128);                        \
+  if (L == 1 && Lout < 0) KERNEL<T, PBLX_L1_T><<<grid, 128, 0, s>>>(__VA_ARGS__);           \
+  else if (L == 1 && Lout == 1) KERNEL<T, PBLX_L1_A><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else if (L == 2 && Lout < 0) KERNEL<T, PBLX_L2_T><<<grid, 128, 0, s>>>(__VA_ARGS__);      \
+  else if (L == 2 && Lout == 1) KERNEL<T, PBLX_L2_N1><<<grid, 128, 0, s>>>(__VA_ARGS__);    \
+  else if (L == 2 && Lout == 2) KERNEL<T, PBLX_L2_A><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else if (L == 3 && Lout < 0) KERNEL<T, PBLX_L3_T><<<grid, 128, 0, s>>>(__VA_ARGS__);      \
+  else if (L == 3 && Lout == 1) KERNEL<T, PBLX_L3_N1><<<grid, 128, 0, s>>>(__VA_ARGS__);    \
+  else if (L == 3 && Lout == 2) KERNEL<T, PBLX_L3_N2><<<grid, 128, 0, s>>>(__VA_ARGS__);    \
+  else if (L == 3 && Lout == 3) KERNEL<T, PBLX_L3_A><<<grid, 128, 0, s>>>(__VA_ARGS__);     \
+  else return cudaErrorInvalidValue;                                                       \
+  return cudaGetLastError();
+template <typename T>
+cudaError_t launch_pbl_fwd(const T* XY, const T* Zg, T* B2, int n, int L, int Lout, int C, cudaStream_t s) {
+  TACE_PBL_DISPATCH(pbl_fwd_kernel, XY, Zg, B2, n, C)
+}
+template <typename T>
+cudaError_t launch_pbl_bwd(const T* XY, const T* Zg, const T* gB2, T* gXY, T* gZg, int n, int L, int Lout, int C, cudaStream_t s) {
+  TACE_PBL_DISPATCH(pbl_bwd_kernel, XY, Zg, gB2, gXY, gZg, n, C)
+}
+
 // ---- third-order product basis (correlation 3) ---------------------------------------------------
 // B3 = (A x A) x A per (atom, channel); B2 is the full second-order basis.  B3 is written / read through the
 // channel-strided column of the thread, so only A and B2 live in registers.
@@ -459,6 +528,8 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_gate_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                    \
   template cudaError_t launch_gate_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);          \
   template cudaError_t launch_pb_fwd<T>(const T*, T*, int, int, int, int, cudaStream_t);                      \
+  template cudaError_t launch_pbl_fwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);           \
+  template cudaError_t launch_pbl_bwd<T>(const T*, const T*, const T*, T*, T*, int, int, int, int, cudaStream_t); \
   template cudaError_t launch_pb_bwd<T>(const T*, const T*, T*, int, int, int, int, cudaStream_t);            \
   template cudaError_t launch_readout<T>(const ReadoutArgs<T>&, cudaStream_t);                                \
   template cudaError_t launch_add_rows<T>(T*, long long, const T*, long long, long long, int, cudaStream_t);  \

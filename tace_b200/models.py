@@ -103,7 +103,7 @@ def check_model_config(cfg: Dict) -> Dict:
         ("resnet", "type", {"BB"}), ("resnet", "linear_type", {"aware", "agnostic", "identity"}), ("resnet", "use_first_resnet", {False}),
         ("layer_norm", "pre_norm_type", {None}), ("layer_norm", "final_norm_type", {None}),
         ("product_basis", "l1l2", {None}), ("product_basis", "return_components", {None}),
-        ("product_basis", "num_expert", {None, 1}), ("product_basis", "nonlinear", {None}),
+        ("product_basis", "num_expert", {None, 1}), ("product_basis", "nonlinear", {None, "silu_bilineargate"}),
         ("product_basis", "agnostic", {False, True}), ("product_basis", "use_shared_expert", {False}),
         ("readout_emlp", "bias", {False}), ("readout_emlp", "use_alllayer", {False, True}), ("readout_emlp", "use_uie", {False}),
         ("scale_shift", "enable", {True}), ("scale_shift", "all_atoms", {False}), ("scale_shift", "shift_type", {None}),
@@ -210,6 +210,7 @@ class e3nnTACE(torch.nn.Module):
                               mlp_layers=len(cfg["radial_basis"]["hidden"]), mlp_bias=cfg["radial_basis"]["bias"],
                               apply_cutoff=cfg["radial_basis"]["apply_cutoff"],
                               element2=cfg["edge_update"]["type"] == "element2", num_fidelities=self.num_fidelities,
+                              product_bilinear=cfg["product_basis"]["nonlinear"] == "silu_bilineargate",
                               resnet_type=cfg["resnet"]["linear_type"], product_agnostic=cfg["product_basis"]["agnostic"],
                               density={"avg_num_neighbors": 0, "density": 1, "no_cutoff_density": 2}[cfg["atomic_basis"]["scatter_norm"]],
                               zbl=0 if not cfg["short_range"]["zbl"]["enable"] else (1 if cfg["scale_shift"]["scale_zbl"] else 2))
@@ -352,7 +353,7 @@ class TensorModel(torch.nn.Module):
             use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,
             mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2),
             num_fidelities=plan.n_fid, zbl=plan.zbl, scatter_norm_density=plan.density,
-            resnet_identity=int(plan.resnet_type == "identity"))
+            resnet_identity=int(plan.resnet_type == "identity"), product_bilinear=int(plan.bilinear))
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

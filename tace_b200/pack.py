@@ -33,7 +33,7 @@ class LayerPlan:
     """``L``: rank of the angular features and of the atomic basis A (the reference's ``lmax``); ``Lnode``: rank of
     the node features between layers (``Lmax``), tace/models/_e3nn/base.py:113-360."""
 
-    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None, correlation: int = 2):
+    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None, correlation: int = 2, bilinear: bool = False):
         Lnode = L if Lnode is None else Lnode
         self.t = t
         self.scalar_src = t == 0 or Lnode == 0
@@ -48,6 +48,12 @@ class LayerPlan:
         # second-order product basis: with a third order behind it every rank <= L keeps its paths (each path is a
         # slot of the next product), otherwise only the output ranks (tace/models/_e3nn/prod.py:216-266)
         self.pb_paths = tp_paths(all_ls, all_ls, all_ls if correlation >= 3 else self.out_ls)
+        if bilinear:
+            # gated bilinear product (tace/models/_e3nn/prod.py:87-111): the second factor carries an extra block of ones
+            # (l2 = -1 here), which adds the path l1 = l3; no symmetry between the factors
+            self.pb_paths = [q for l3 in self.out_ls for l1 in all_ls
+                             for q in ([(l1, l2, l3) for l2 in all_ls if abs(l1 - l2) <= l3 <= l1 + l2 and (l1 + l2 + l3) % 2 == 0]
+                                       + ([(l1, -1, l3)] if l1 == l3 else []))]
         self.kp = [sum(1 for p in self.pb_paths if p[2] == l) for l in self.out_ls]
         self.pb3_paths = []
         if correlation >= 3:
@@ -61,7 +67,7 @@ class ModelPlan:
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
                  apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0,
-                 density: int = 0, resnet_type: str = "aware", product_agnostic: bool = False):
+                 density: int = 0, resnet_type: str = "aware", product_agnostic: bool = False, product_bilinear: bool = False):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
@@ -73,11 +79,14 @@ class ModelPlan:
         # resnet.linear_type: aware (per-species linear), agnostic (one linear), identity (copy); product_basis.agnostic:
         # one coefficient matrix for all species instead of one per species
         self.resnet_type, self.product_agnostic = resnet_type, bool(product_agnostic)
+        self.bilinear = bool(product_bilinear)  # product_basis.nonlinear = silu_bilineargate
+        if self.bilinear and (correlation != 2 or self.Cp != self.C):
+            raise NotImplementedError("tace_b200: silu_bilineargate needs correlation 2 and a channel count that is a multiple of 32")
         self.gate_m0 = bool(gate_m0)  # False: scalars are not gated, so linear_down emits one scalar block less
         # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
         self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
-        self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation) for t in range(num_layers)]
+        self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation, self.bilinear) for t in range(num_layers)]
 
     @property
     def mlp_layer_norm(self) -> bool:
@@ -128,6 +137,9 @@ class ModelPlan:
                 out[pre + "resnetBB.bias"] = res_lead + (C,)
             pp = f"representation.products.{lp.t}."
             co_lead = () if self.product_agnostic else (n_el,)
+            if self.bilinear:  # prod.py:128-141: gates for every product path, then both factors per rank
+                out[pp + "linear_up.weight"] = (C * len(lp.pb_paths) * C + (L + 1) * C * 2 * C,)
+                out[pp + "linear_up.bias"] = (len(lp.pb_paths) * C + 2 * C,)
             out[pp + "coefs.0.weight"] = co_lead + (len(lp.out_ls) * C * C,)
             out[pp + "coefs.0.bias"] = co_lead + (C,)
             if self.correlation >= 2:
@@ -288,6 +300,15 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         for l, m in enumerate(split(g(pre + "linear_nonlinearity.weight"), [(C, C)] * (L + 1))):
             put(tp + f"nl.l{l}", m / math.sqrt(C), tp + f"nlT.l{l}")
         out[tp + "nl.b"] = g(pre + "linear_nonlinearity.bias")
+        if plan.bilinear:
+            # e3nn Linear order: input block major; the scalars feed the gates and the rank-0 factors, rank l its factors
+            npth = len(lp.pb_paths)
+            mats = split(g(pp + "linear_up.weight"), [(C, npth * C)] + [(C, 2 * C)] * (L + 1))
+            put(tp + "pg", mats[0] / math.sqrt(C), tp + "pgT")
+            for l in range(L + 1):
+                put(tp + f"pu.l{l}", mats[1 + l] / math.sqrt(C), tp + f"puT.l{l}")
+            bias = g(pp + "linear_up.bias")
+            out[tp + "pg.b"], out[tp + "pu.b"] = bias[:npth * C], bias[npth * C:]
         for l, m in zip(lp.out_ls, split(per_species(pp + "coefs.0.weight", plan.product_agnostic), [(C, C)] * len(lp.out_ls))):
             put(tp + f"c0.l{l}", m / math.sqrt(C), tp + f"c0T.l{l}")
         bias = per_species(pp + "coefs.0.bias", plan.product_agnostic).copy()
@@ -324,9 +345,9 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
     # TF32 high part / residual of every plain channel-mixing matrix (tensor-core path of fp32 models)
     for name in list(out):
         stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
-        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT")
+        if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT", "pu", "puT")
                 and name.split(".")[-1].startswith("l")) \
-                or stem in ("A1", "A1t", "A2", "A2t", "W3", "W3t"):
+                or stem in ("A1", "A1t", "A2", "A2t", "W3", "W3t") or name.split(".")[-1] in ("pg", "pgT"):
             hi, lo = split_tf32(out[name])
             if stem in ("c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT"):
                 # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,

@@ -11,14 +11,15 @@ from tace_b200 import synth
 def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
                 targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True, radial=None, edge_update="identity",
                 num_fidelities=1, zbl=None, scale_zbl=True, scatter_norm="avg_num_neighbors",
-                resnet_linear_type="aware", product_agnostic=False):
+                resnet_linear_type="aware", product_agnostic=False, product_nonlinear=None):
     """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
     from oracle.model import build_oracle
 
     cfg = synth.model_config(L, C, cutoff, elements, avg, num_layers=num_layers, correlation=correlation,
                              target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0, radial=radial, edge_update=edge_update,
                              num_fidelities=num_fidelities, zbl=zbl, scale_zbl=scale_zbl, scatter_norm=scatter_norm,
-                             resnet_linear_type=resnet_linear_type, product_agnostic=product_agnostic)
+                             resnet_linear_type=resnet_linear_type, product_agnostic=product_agnostic,
+                             product_nonlinear=product_nonlinear)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:

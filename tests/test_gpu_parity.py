@@ -395,3 +395,14 @@ def test_skip_connection_types_and_species_agnostic_product(resnet_linear_type, 
     for dtype in (torch.float64, torch.float32):
         run_case(structs, 3, 32, [1, 2, 3], 4.5, dtype, num_layers=3, Lmax=2, resnet_linear_type=resnet_linear_type,
                  product_agnostic=product_agnostic)
+
+
+@pytest.mark.parametrize("L,Lmax,num_layers", [(2, None, 2), (3, 2, 3)])
+def test_gated_bilinear_product(L, Lmax, num_layers):
+    """product_basis.nonlinear = silu_bilineargate: the product's own linear_up makes two factors and one SiLU gate per
+    (path, channel); second-order basis = gate * (x (x) [y, 1]), first-order coefficients on x."""
+    structs = synth.random_crystals(3, seed=31, nmin=4, nmax=10, zmax=3)
+    for dtype in (torch.float64, torch.float32):
+        run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, num_layers=num_layers, product_nonlinear="silu_bilineargate")
+    run_case(structs, 2, 64, [1, 2, 3], 4.5, torch.float32, product_nonlinear="silu_bilineargate", product_agnostic=True,
+             resnet_linear_type="identity")
