@@ -92,6 +92,15 @@ typedef struct {
                          the second-order basis is gate * (x (x) [y, 1]) with separate factors (no symmetry) and the
                          first-order coefficients act on x.  Weights "t<i>.pu.l<l>" [C][2C], "t<i>.pg" [C][paths*C], biases
                          "t<i>.pu.b" [2C], "t<i>.pg.b" [paths*C] */
+  /* TECE edge block, atomic_basis.type = uv_so2 (tace/models/_e3nn/inter.py:440-519, _e3nn/archive/oam_2026_07_05.py:547-823):
+     bit t of tece_layers makes interaction t (not the first; Lnode == L; whole-batch evaluation only) rotate the features of
+     both ends of every edge into the edge frame, mix the orders |m| <= mmax (<= 2) with SO(2) linears, a gate and an edge
+     cluster expansion of width edge_ace_hidden (0: num_channel), and weight the messages with num_head attention heads
+     normalised over the incoming edges.  edge_act: 0 so2_sigmoid_gate, 1 so2_silu_gate.  Weights "t<i>.so2.<key|query|up|
+     glu|coefs|down>.m<m>" ([K][N], transposed copies "...T.m<m>"), biases "t<i>.so2.<name>.b", "t<i>.att.temp" [heads]
+     (attention scale * temperature), "t<i>.att.rw" [8][2 heads], "t<i>.att.rb" [2 heads]; the radial MLP of such a layer
+     emits [rows per order][2 num_channel] weights */
+  int tece_layers, mmax, num_head, edge_ace_hidden, edge_act;
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtace_b200.so")
 SOURCES = ["engine.cu", "tp_kernels.cu", "node_kernels.cu", "edge_kernels.cu", "graph_kernels.cu", "nl_kernels.cu", "tc_gemm.cu",
-           "md_kernels.cu"]
+           "md_kernels.cu", "tece_kernels.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 

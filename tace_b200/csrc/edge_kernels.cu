@@ -357,6 +357,7 @@ __global__ void __launch_bounds__(128) edge_bwd_kernel(const EdgeArgs<T> a) {
   for (int k = 0; k < D; ++k) dY[k] = a.dY[e * D + k];
   sh_grad<T, L>(v[0] * inv, v[1] * inv, v[2] * inv, dY, dn);
   edge_vector_grad<T>(v, d0, d, dd, dn, g);
+  if (a.gvec_extra) { g[0] += a.gvec_extra[3 * e]; g[1] += a.gvec_extra[3 * e + 1]; g[2] += a.gvec_extra[3 * e + 2]; }
   a.g[3 * e + 0] = g[0]; a.g[3 * e + 1] = g[1]; a.g[3 * e + 2] = g[2];
   if (a.edge_forces) {
     const long long eo = a.e_orig[e];

@@ -99,6 +99,7 @@ struct WeightEntry {
 
 struct LayerPlan {
   bool scalar_src, last, has_res;
+  bool tece = false;        // the interaction is the TECE edge block (atomic_basis.type = uv_so2) instead of the tensor product
   TPMeta tp;
   PBMeta pb;                // second-order product basis (all ranks <= L when a third order follows)
   PBMeta pb3;               // third-order product basis (correlation 3)
@@ -333,6 +334,12 @@ struct Model : ModelBase {
   int density = 0;            // atomic_basis.scatter_norm: 0 avg_num_neighbors, 1 density, 2 no_cutoff_density
   bool res_identity = false;  // resnet.linear_type = identity: the skip connection copies the matching ranks, no weights
   bool bilinear = false;      // product_basis.nonlinear = silu_bilineargate: gated product of two linear images of A
+  // TECE edge block: layers (bit t), orders kept, heads, width of the cluster expansion, activation (0 sigmoid, 1 SiLU)
+  int tece_mask = 0, mmax = 2, heads = 1, Ca = 0, edge_act = 0;
+  int t_NR = 0, t_NC = 0, t_NF = 0, t_G = 0, t_np = 0, t_WN = 0;  // rows (order-major / per weight / full), gates, paths, coefficients
+  int t_k[4] = {1, 1, 1, 1}, t_base[4] = {0, 1, 4, 9};            // message layout of a TECE layer: one block of C per rank
+  int t_row_l[16], t_row_m[16], t_row_comp[16]; double t_row_scale[16];
+  int t_p_m1[12], t_p_m2[12], t_p_m3[12], t_p_sum[12]; double t_p_scale[12];
   int m0 = 1;  // 1: every rank gated (gate_m0 = True); 0: e3nn Gate, scalars through SiLU (gate_m0 = False)
   std::vector<LayerPlan> layers;
   std::vector<WeightEntry> weights;
@@ -376,6 +383,40 @@ struct Model : ModelBase {
     density = c.scatter_norm_density;
     res_identity = c.resnet_identity != 0;
     bilinear = c.product_bilinear != 0;
+    tece_mask = c.tece_layers; mmax = c.mmax; heads = c.num_head > 0 ? c.num_head : 1;
+    Ca = c.edge_ace_hidden > 0 ? c.edge_ace_hidden : c.num_channel; edge_act = c.edge_act;
+    if (tece_mask) {
+      // the block needs ranks above 0 on its input (not the first layer), node rank = edge rank, orders <= 2
+      if ((tece_mask & 1) || (c.Lnode > 0 && c.Lnode != c.L) || mmax < 0 || mmax > 2 || mmax > c.L || heads > 16 || C % heads ||
+          Ca % 4 || density || (edge_act != 0 && edge_act != 1))
+        return TACE_ERR_UNSUPPORTED_CONFIG;
+      const int n = L + 1;
+      t_NR = 0; t_NC = 0;
+      for (int m = 0; m <= mmax; ++m) {
+        for (int sign = 1; sign >= (m ? -1 : 1); sign -= 2)
+          for (int l = m; l <= L; ++l) {
+            t_row_l[t_NR] = l; t_row_m[t_NR] = sign * m; t_row_comp[t_NR] = t_NC + (l - m);
+            t_row_scale[t_NR] = l > mmax ? std::sqrt((2.0 * l + 1.0) / (2.0 * mmax + 1.0)) : 1.0;
+            ++t_NR;
+          }
+        t_NC += L + 1 - m;
+      }
+      t_NF = n + 2 * n * mmax;
+      t_G = n * (mmax + 1 - (m0 ? 0 : 1));
+      // cluster-expansion paths, output order major (oam_2026_07_05.py:331-369 with m1 >= m2)
+      t_np = 0;
+      for (int m3 = 0; m3 <= mmax; ++m3) {
+        const int first = t_np;
+        for (int m1 = 0; m1 <= mmax; ++m1)
+          for (int m2 = 0; m2 <= m1; ++m2) {
+            const bool sum = (m1 + m2 == m3), diff = !sum && (m1 - m2 == m3);
+            if (!sum && !diff) continue;
+            t_p_m1[t_np] = m1; t_p_m2[t_np] = m2; t_p_m3[t_np] = m3; t_p_sum[t_np] = sum ? 1 : 0; ++t_np;
+          }
+        for (int q = first; q < t_np; ++q) t_p_scale[q] = 1.0 / std::sqrt((double)(t_np - first));
+      }
+      t_WN = t_np * n * Ca;
+    }
     if (bilinear && c.correlation != 2) return TACE_ERR_UNSUPPORTED_CONFIG;
     if (zbl < 0 || zbl > 2 || density < 0 || density > 2 || (density && element2)) return TACE_ERR_UNSUPPORTED_CONFIG;
     Ln = (c.Lnode > 0) ? c.Lnode : L;  // node features between layers carry ranks 0..Ln; A, Y and the messages 0..L
@@ -393,6 +434,8 @@ struct Model : ModelBase {
       if (!tp_meta(L, p.scalar_src ? -1 : Ln, p.tp) || !(bilinear ? pbl_meta(L, p.pb_lout, p.pb) : pb_meta(L, p.pb_lout, p.pb)))
         return TACE_ERR_UNSUPPORTED_CONFIG;
       if (c.correlation == 3 && !pb3_meta(L, lout, p.pb3)) return TACE_ERR_UNSUPPORTED_CONFIG;
+      p.tece = (tece_mask >> t) & 1;
+      if (p.tece) p.tp = TPMeta{2 * t_NC, D, D, 0, t_k, t_base};  // radial weights [NC][2C]; messages one C-block per rank
       p.Din = p.scalar_src ? 1 : Dn;
       p.Dout = p.last ? 1 : Dn;
       p.in_ls.clear(); p.out_ls.clear();
@@ -415,6 +458,18 @@ struct Model : ModelBase {
         if (nh >= 2) add_weight(pre + "b1", kHidden);
         if (nh >= 3) add_weight(pre + "b2", kHidden);
         add_weight(pre + "b3", (long long)p.tp.NP * C);
+      }
+      if (p.tece) {
+        for (int i = 0; i < 6; ++i) {
+          const So2Shape sh = so2_shape(i);
+          for (int m = 0; m <= sh.mm; ++m) {
+            const long long numel = (long long)sh.n_in[m] * sh.c_in * sh.n_out[m] * sh.c_out;
+            add_linear_weight(pre + "so2." + sh.name + ".m" + std::to_string(m), numel);
+            add_linear_weight(pre + "so2." + sh.name + "T.m" + std::to_string(m), numel);
+          }
+          add_weight(pre + "so2." + sh.name + ".b", (long long)sh.n_out[0] * sh.c_out);
+        }
+        add_weight(pre + "att.temp", heads); add_weight(pre + "att.rw", (long long)kNumBessel * 2 * heads); add_weight(pre + "att.rb", 2 * heads);
       }
       if (density) {  // edge-density MLP 8 -> 64 -> 1 and the affine parameters {alpha, beta}
         add_weight(pre + "dA0", (long long)kNumBessel * kHidden); add_weight(pre + "dw1", kHidden); add_weight(pre + "dab", 2);
@@ -525,6 +580,9 @@ struct Model : ModelBase {
     T *B3, *gB2;                // third-order basis (reused for its gradient) and the gradient of the second-order one
     T *inv_density, *gdens;     // learned edge density: 1 / density_i and dE / d density_i
     T *XY, *gXY, *Zg, *gZg;     // gated bilinear product: both factors per (atom, component), gate pre-activations, gradients
+    // TECE edge block (layouts at the top of tece_kernels.cu); gradients that may overwrite their forward buffer do
+    T *tKs, *tQt, *tMw, *tKp, *tQp, *tlogit, *talpha, *tup, *tglu, *tcoef, *tU, *tdown;
+    T *tgdown, *tgalpha, *tglogit, *tgcut, *tgproj, *tgQp, *tgKp, *tgKs, *tgQt, *tdxt, *tddlen;
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
@@ -532,6 +590,7 @@ struct Model : ModelBase {
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
     T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor, *env, *denv, *zbl_node;
+    T *tWg, *tgWg, *tgvec;  // TECE: Wigner rows of every edge (shared by the layers), their gradient, dE/d(edge vector) through them
     std::vector<LayerBufs> lay;
   };
 
@@ -544,6 +603,8 @@ struct Model : ModelBase {
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL); b.zbl_node = zbl ? ar.take<T>(NL) : nullptr;
+    b.tWg = b.tgWg = b.tgvec = nullptr;
+    if (tece_mask) { b.tWg = ar.take<T>((size_t)E * t_NR * D); b.tgWg = ar.take<T>((size_t)E * t_NR * D); b.tgvec = ar.take<T>(3 * (size_t)E); }
     b.dlen = ar.take<T>(E); b.ddlen = ar.take<T>(E);
     b.env = env_after ? ar.take<T>(E) : nullptr; b.denv = env_after ? ar.take<T>(E) : nullptr;
     const bool chunked = E > max_chunk_edges;
@@ -585,6 +646,19 @@ struct Model : ModelBase {
       lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.inv_density = density ? ar.take<T>(NL) : nullptr; lb.gdens = density ? ar.take<T>(NL) : nullptr;
       lb.XY = lb.gXY = lb.Zg = lb.gZg = nullptr;
+      if (p.tece) {
+        const size_t Es = (size_t)E;
+        lb.tKs = ar.take<T>(Es * t_NR * C); lb.tQt = ar.take<T>(Es * t_NR * C); lb.tMw = ar.take<T>(Es * t_NR * 2 * C);
+        lb.tKp = ar.take<T>(Es * t_NR * C); lb.tQp = ar.take<T>(Es * t_NR * C);
+        lb.tlogit = ar.take<T>(Es * heads); lb.talpha = ar.take<T>(Es * heads);
+        lb.tup = ar.take<T>(Es * (t_G + t_NF) * Ca); lb.tglu = ar.take<T>(Es * t_NF * Ca); lb.tcoef = ar.take<T>(Es * t_WN);
+        lb.tU = ar.take<T>(Es * t_NF * Ca); lb.tdown = ar.take<T>(Es * t_NR * C);
+        lb.tgdown = ar.take<T>(Es * t_NR * C); lb.tgalpha = ar.take<T>(Es * heads); lb.tglogit = ar.take<T>(Es * heads);
+        lb.tgcut = ar.take<T>(Es * heads); lb.tgproj = ar.take<T>(Es * 2 * heads);
+        lb.tgQp = ar.take<T>(Es * t_NR * C); lb.tgKp = ar.take<T>(Es * t_NR * C);
+        lb.tgKs = ar.take<T>(Es * t_NR * C); lb.tgQt = ar.take<T>(Es * t_NR * C);
+        lb.tdxt = ar.take<T>(Es * D * C); lb.tddlen = ar.take<T>(Es);
+      }
       if (bilinear) {
         lb.XY = ar.take<T>((size_t)NL * D * 2 * C); lb.gXY = ar.take<T>((size_t)NL * D * 2 * C);
         lb.Zg = ar.take<T>((size_t)NL * p.pb.NP * C); lb.gZg = ar.take<T>((size_t)NL * p.pb.NP * C);
@@ -732,6 +806,121 @@ struct Model : ModelBase {
     }
     return r;
   }
+  // ---- TECE edge block --------------------------------------------------------------------------------------
+  // the six SO(2) linears of the block (oam_2026_07_05.py:612-676): channel counts and rows per order on both sides
+  struct So2Shape { const char* name; int mm, c_in, c_out, n_in[3], n_out[3]; };
+  So2Shape so2_shape(int i) const {
+    const int n = L + 1;
+    So2Shape s{};
+    const int red[3] = {n, n - 1, n - 2}, full[3] = {n, n, n};
+    auto set = [&](const char* nm, int mm, int ci, int co, const int* in, const int* out) {
+      s.name = nm; s.mm = mm; s.c_in = ci; s.c_out = co;
+      for (int m = 0; m < 3; ++m) { s.n_in[m] = in[m]; s.n_out[m] = out[m]; }
+    };
+    const int up_out[3] = {t_G + n, n, n}, coef_out[3] = {t_np * n * Ca, 0, 0};
+    switch (i) {
+      case 0: set("key", mmax, C, C, red, red); break;
+      case 1: set("query", mmax, C, C, red, red); break;
+      case 2: set("up", mmax, 2 * C, Ca, red, up_out); break;
+      case 3: set("glu", mmax, 2 * C, Ca, red, full); break;
+      case 4: set("coefs", 0, 2 * C, 1, red, coef_out); break;
+      default: set("down", mmax, Ca, C, full, red); break;
+    }
+    return s;
+  }
+  // GEMM problems of one SO(2) linear over the E edges: `in` [E][in_rows][c_in] -> `out` [E][out_rows][c_out] (forward), or the
+  // gradient of the output back to the gradient of the input (backward; `out` is then the input gradient)
+  void so2_specs(std::vector<LinSpec>& sp, const std::string& pre, int which, const T* in, int in_rows, T* out, int out_rows, bool backward,
+                 int accumulate) const {
+    const So2Shape sh = so2_shape(which);
+    int off_in = 0, off_out = 0;
+    for (int m = 0; m <= sh.mm; ++m) {
+      const int K = sh.n_in[m] * sh.c_in, Nn = sh.n_out[m] * sh.c_out;
+      const std::string nm = pre + "so2." + sh.name + ".m" + std::to_string(m), nmT = pre + "so2." + sh.name + "T.m" + std::to_string(m);
+      if (!backward)
+        sp.push_back({in + (long long)off_in * sh.c_in, (long long)in_rows * sh.c_in, K, m ? 2 : 1, K, nm, nmT, Nn,
+                      out + (long long)off_out * sh.c_out, (long long)out_rows * sh.c_out, Nn, m == 0 ? w(pre + "so2." + sh.name + ".b") : nullptr, 0});
+      else  // `in` holds the gradient of the forward output, `out` receives the gradient of the forward input
+        sp.push_back({in + (long long)off_out * sh.c_out, (long long)out_rows * sh.c_out, Nn, m ? 2 : 1, Nn, nmT, nm, K,
+                      out + (long long)off_in * sh.c_in, (long long)in_rows * sh.c_in, K, nullptr, accumulate});
+      // the order-0 block of the input always spans L + 1 rows (oam_2026_07_05.py:211)
+      off_in += (m == 0) ? (L + 1) : 2 * sh.n_in[m];
+      off_out += (m == 0) ? sh.n_out[0] : 2 * sh.n_out[m];
+    }
+  }
+  TeceArgs<T> tece_args(const EdgeArgs<T>& ea, const Bufs& b, const LayerBufs& lb, const std::string& pre, const T* x_src, long long NL,
+                        long long E) const {
+    TeceArgs<T> a;
+    memset(&a, 0, sizeof(a));
+    a.E = E; a.n_local = (int)NL; a.C = C; a.Ca = Ca; a.L = L; a.mmax = mmax; a.H = heads; a.NR = t_NR; a.NC = t_NC; a.G = t_G;
+    a.n_paths = t_np; a.gate_m0 = m0; a.act = edge_act;
+    for (int r = 0; r < t_NR; ++r) { a.row_l[r] = t_row_l[r]; a.row_m[r] = t_row_m[r]; a.row_comp[r] = t_row_comp[r]; a.row_scale[r] = T(t_row_scale[r]); }
+    for (int q = 0; q < t_np; ++q) { a.p_m1[q] = t_p_m1[q]; a.p_m2[q] = t_p_m2[q]; a.p_m3[q] = t_p_m3[q]; a.p_sum[q] = t_p_sum[q]; a.p_scale[q] = T(t_p_scale[q]); }
+    a.rp = ea.rp; a.vec = b.vec; a.dlen = b.dlen; a.env = env_after ? b.env : nullptr;
+    a.e_src = b.e_src; a.e_dst = b.e_dst; a.rowptr = b.rowptr_dst;
+    a.x = x_src; a.W = lb.W; a.Wg = b.tWg; a.Ks = lb.tKs; a.Qt = lb.tQt; a.Mw = lb.tMw; a.Kp = lb.tKp; a.Qp = lb.tQp;
+    a.logit = lb.tlogit; a.alpha = lb.talpha; a.temp = w(pre + "att.temp"); a.rproj_w = w(pre + "att.rw"); a.rproj_b = w(pre + "att.rb");
+    a.up = lb.tup; a.glu = lb.tglu; a.coefZ = lb.tcoef; a.U = lb.tU; a.down = lb.tdown; a.M = lb.M;
+    a.gM = lb.M; a.gdown = lb.tgdown; a.galpha = lb.tgalpha; a.glogit = lb.tglogit; a.gcut = lb.tgcut; a.gproj = lb.tgproj;
+    a.gQp = lb.tgQp; a.gKp = lb.tgKp; a.gKs = lb.tgKs; a.gQt = lb.tgQt; a.gMw = lb.tMw;
+    a.gU = lb.tU; a.gup = lb.tup; a.gglu = lb.tglu; a.gcoefZ = lb.tcoef; a.gWg = b.tgWg; a.gvec = b.tgvec;
+    a.dxe = b.dxe; a.dxt = lb.tdxt; a.gx = lb.gx; a.ddlen_extra = lb.tddlen;
+    return a;
+  }
+  // forward of the block for one layer: lb.W holds the radial weights, the result lands in lb.M
+  int tece_forward(const TeceArgs<T>& ta, const LayerBufs& lb, const std::string& pre, long long E, cudaStream_t s) {
+    std::vector<LinSpec> sp;
+    CKL(launch_tece(ta, TECE_ROTATE_IN, s));
+    so2_specs(sp, pre, 0, lb.tKs, t_NR, lb.tKp, t_NR, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 1, lb.tQt, t_NR, lb.tQp, t_NR, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    CKL(launch_tece(ta, TECE_LOGIT, s));
+    CKL(launch_tece(ta, TECE_SOFTMAX, s));
+    so2_specs(sp, pre, 2, lb.tMw, t_NR, lb.tup, t_G + t_NF, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 3, lb.tMw, t_NR, lb.tglu, t_NF, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 4, lb.tMw, t_NR, lb.tcoef, t_WN, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    CKL(launch_tece(ta, TECE_MIX, s));
+    so2_specs(sp, pre, 5, lb.tU, t_NF, lb.tdown, t_NR, false, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    CKL(launch_tece(ta, TECE_ROTATE_OUT, s));
+    return TACE_OK;
+  }
+  // backward: lb.M holds dE/d(messages); leaves dE/d(radial weights) in lb.W, the per-edge source rows in dxe, the target part
+  // added to lb.gx by the caller's order (source sum first), and this layer's share of dE/d(edge vector) in tgvec / tddlen
+  int tece_backward(TeceArgs<T> ta, const Bufs& b, const LayerBufs& lb, const std::string& pre, long long N, long long E, bool first_tece,
+                    cudaStream_t s) {
+    std::vector<LinSpec> sp;
+    CKL(launch_tece(ta, TECE_ROTATE_OUT_BWD, s));
+    CKL(launch_tece(ta, TECE_ALPHA_BWD, s));
+    CKL(launch_tece(ta, TECE_SOFTMAX_BWD, s));
+    CKL(launch_tece(ta, TECE_LOGIT_BWD, s));
+    CKL(launch_tece(ta, TECE_EDGE_SCALAR_BWD, s));
+    so2_specs(sp, pre, 5, lb.tgdown, t_NF, lb.tU, t_NR, true, 0);   // gU over U
+    CKL(run_linear(sp, E, s)); sp.clear();
+    CKL(launch_tece(ta, TECE_MIX_BWD, s));                           // gup / gglu / gcoef over their forward buffers
+    so2_specs(sp, pre, 2, lb.tup, t_NR, lb.tMw, t_G + t_NF, true, 0);  // gMw over Mw
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 3, lb.tglu, t_NR, lb.tMw, t_NF, true, 1);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 4, lb.tcoef, t_NR, lb.tMw, t_WN, true, 1);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 0, lb.tgKp, t_NR, lb.tgKs, t_NR, true, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    so2_specs(sp, pre, 1, lb.tgQp, t_NR, lb.tgQt, t_NR, true, 0);
+    CKL(run_linear(sp, E, s)); sp.clear();
+    CKL(launch_tece(ta, TECE_ROTATE_IN_BWD, s));
+    CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, D * C, s));
+    CKL(launch_tece(ta, TECE_TARGET_SUM, s));
+    CKL(launch_tece(ta, TECE_WIGNER_GRAD, s));
+    ta.accumulate_gvec = first_tece ? 0 : 1;
+    CKL(launch_tece(ta, TECE_WIGNER_BWD, s));
+    return TACE_OK;
+  }
+
   DensityArgs<T> density_args(const EdgeArgs<T>& ea, const Bufs& b, const LayerBufs& lb, const std::string& pre, long long NL,
                               long long E) const {
     DensityArgs<T> da;
@@ -936,6 +1125,7 @@ struct Model : ModelBase {
     debug.push_back({"vec", b.vec, 3 * E});
 
     // ---- layers, forward
+    bool wigner_done = false, tece_seen = false;
     PH("embed");
     CKL(launch_species_gather(w("emb"), bt->species, b.lay[0].h_in, (int)N, C, s));
     for (int t = 0; t < NL_; ++t) {
@@ -972,6 +1162,13 @@ struct Model : ModelBase {
         PH(("t" + ts + ".fwd.radial_gemm").c_str());
         CKS(radial_last(p, lb, pre, Ec, false, s));
         PH(("t" + ts + ".fwd.tp").c_str());
+        if (p.tece) {  // the edge block instead of the tensor product (whole batch only)
+          if (chunked) return TACE_ERR_CAPACITY;
+          const TeceArgs<T> tc = tece_args(ea, b, lb, pre, x_src, NL, E);
+          if (!wigner_done) { CKL(launch_tece(tc, TECE_WIGNER, s)); wigner_done = true; }
+          CKS(tece_forward(tc, lb, pre, E, s));
+          continue;
+        }
         TPArgs<T> ta;
         memset(&ta, 0, sizeof(ta));
         ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
@@ -1217,6 +1414,18 @@ struct Model : ModelBase {
           CKS(radial_last(p, lb, pre, Ec, false, s));
         }
         PH(("t" + ts + ".bwd.tp").c_str());
+        if (p.tece) {
+          if (t == NL_ - 1) {  // no tensor product above to initialise the accumulators of the layers below
+            CKL(launch_fill_zero(b.dY, E * D, s));
+            if (b.denv) CKL(launch_fill_zero(b.denv, E, s));
+          }
+          const TeceArgs<T> tc = tece_args(ea, b, lb, pre, lb.xx ? lb.xx : lb.x, NL, E);
+          CKS(tece_backward(tc, b, lb, pre, N, E, !tece_seen, s));
+          tece_seen = true;
+          PH(("t" + ts + ".bwd.radial_gemm").c_str());
+          CKS(radial_last(p, lb, pre, Ec, true, s));
+          continue;
+        }
         TPArgs<T> ta;
         memset(&ta, 0, sizeof(ta));
         ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.e_src = b.e_src; ta.Y = b.Y;
@@ -1265,6 +1474,9 @@ struct Model : ModelBase {
     // ---- back to the edge vectors, then forces and virials
     PH("radial_mlp_bwd");
     if (!chunked) CKS(radial_backward(ea, b, all_layers, 0, E, 0, s));  // lay[t].H3 holds dE/dh3 of each layer's radial MLP
+    for (int t = 0; t < NL_; ++t)  // the edge blocks' own dependence on the edge lengths (radial projection, cutoff in the softmax)
+      if (layers[t].tece) CKL(launch_add_inplace(b.ddlen, b.lay[t].tddlen, E, s));
+    if (tece_mask) ea.gvec_extra = b.tgvec;  // and on the edge vectors through the frames
     if (density) {  // the densities' dependence on the edge lengths
       for (int t = 0; t < NL_; ++t) {
         DensityArgs<T> da = density_args(ea, b, b.lay[t], "t" + std::to_string(t) + ".", NL, E);

@@ -477,6 +477,12 @@ def main():
             summary.append(gen_product3(L, Lout, out))
         for Lout in [-1] + list(range(1, L + 1)):
             summary.append(gen_product_bilinear(L, Lout, out))
+    # coupling tables of the Wigner-matrix recursion D^l = (2l+1) C^T (D^1 (x) D^(l-1)) C (tace/models/o2/wigner.py:316-357)
+    for l in (2, 3):
+        c = w3j(1, l - 1, l)
+        vals = ", ".join(repr(float(v)) for v in c.reshape(-1))
+        out.append(f"// wigner_3j(1, {l - 1}, {l}), [3][{2 * l - 1}][{2 * l + 1}]")
+        out.append(f"TACE_CONST double w3j_1_{l - 1}_{l}[{c.size}] = {{{vals}}};")
     out.append("}  // namespace tace")
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "tp_gen.cuh"), "w") as fh:

@@ -179,6 +179,7 @@ struct EdgeArgs {
   T* env;                // [E] envelope values, written by launch_edge_fwd when the cutoff is applied after the MLP
   const T* denv;         // [E] dE/d(envelope) from the tensor-product backward passes (same case), or nullptr
   int add_denv;          // this launch_edge_mlp_out call adds the envelope term to ddlen
+  const T* gvec_extra;   // [E][3] added to dE/d(edge vector) by launch_edge_bwd (gradient through the TECE edge frames), or nullptr
   int dz1_given;         // dH1 holds dE/d(first pre-activation) already (LayerNorm models): launch_edge_mlp_out applies no silu'
   // backward
   const T* dY;           // [E][D]
@@ -244,6 +245,29 @@ namespace tace {
 // bounded wait inside the kernel expired.
 // Batched form for the per-rank linears: up to four problems per launch, rows = (atom, component) pairs
 // addressed as base + atom * atom_stride + component * comp_stride (elements), K and N contiguous.
+// ---- TECE edge block (tece_kernels.cu; tace/models/_e3nn/archive/oam_2026_07_05.py:547-823) --------------------
+enum TeceStage {
+  TECE_WIGNER, TECE_ROTATE_IN, TECE_LOGIT, TECE_SOFTMAX, TECE_MIX, TECE_ROTATE_OUT,
+  TECE_ROTATE_OUT_BWD, TECE_ALPHA_BWD, TECE_SOFTMAX_BWD, TECE_LOGIT_BWD, TECE_EDGE_SCALAR_BWD, TECE_MIX_BWD,
+  TECE_ROTATE_IN_BWD, TECE_TARGET_SUM, TECE_WIGNER_GRAD, TECE_WIGNER_BWD
+};
+// One argument block for every kernel of the edge block (layouts are described at the top of tece_kernels.cu).
+template <typename T>
+struct TeceArgs {
+  long long E; int n_local, C, Ca, L, mmax, H, NR, NC, G, n_paths, gate_m0, act, accumulate_gvec;
+  int row_l[16], row_m[16], row_comp[16]; T row_scale[16];          // order-major rows: rank, signed order, weight component, inverse rescale
+  int p_m1[12], p_m2[12], p_m3[12], p_sum[12]; T p_scale[12];        // cluster-expansion paths
+  RadialParams<T> rp;
+  const T* vec; const T* dlen; const T* env;                         // env == nullptr: no cutoff factor (apply_cutoff = True)
+  const int* e_src; const int* e_dst; const int* rowptr;
+  const T* x; T* W; T* Wg; T* Ks; T* Qt; T* Mw; T* Kp; T* Qp; T* logit; T* alpha;
+  const T* temp; const T* rproj_w; const T* rproj_b;                 // per-head scale * temperature; radial projection [8][2H], [2H]
+  T* up; T* glu; T* coefZ; T* U; T* down; T* M;
+  const T* gM; T* gdown; T* galpha; T* glogit; T* gcut; T* gproj; T* gQp; T* gKp; T* gKs; T* gQt; T* gMw;
+  const T* gU; T* gup; T* gglu; T* gcoefZ; T* gWg; T* gvec; T* dxe; T* dxt; T* gx; T* ddlen_extra;
+};
+template <typename T> cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s);
+
 struct TcLinearProblem {
   const float* A; long long a_atom_stride, a_comp_stride;
   int q;                 // components per atom (2l+1), <= 128

@@ -31,7 +31,8 @@ class TaceConfig(ctypes.Structure):
         ("correlation", c_int), ("num_bessel", c_int), ("mlp_hidden", c_int), ("envelope_p", c_int),
         ("readout_hidden", c_int), ("cutoff", c_double), ("avg_num_neighbors", c_double), ("Lnode", c_int),
         ("use_alllayer", c_int), ("gate_m0_off", c_int), ("mlp_layers", c_int), ("mlp_bias", c_int), ("env_after_mlp", c_int),
-        ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int), ("scatter_norm_density", c_int), ("resnet_identity", c_int), ("product_bilinear", c_int),
+        ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int), ("scatter_norm_density", c_int), ("resnet_identity", c_int), ("product_bilinear", c_int), ("tece_layers", c_int), ("mmax", c_int),
+        ("num_head", c_int), ("edge_ace_hidden", c_int), ("edge_act", c_int),
     ]
 
 

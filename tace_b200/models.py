@@ -34,7 +34,8 @@ _DEFAULTS: Dict[str, Any] = {
                      "cutoff_fn": "c2poly", "polynomial_cutoff": 5, "trainable": False, "apply_cutoff": True,
                      "hidden": [64, 64, 64], "use_dydynamic_cutoff": False},
     "atomic_basis": {"type": "cgtp", "l1l2": None, "scatter_norm": "avg_num_neighbors", "nonlinear": "sigmoid_gate",
-                     "gate_m0": True, "scalar_act": None, "tensor_act": None, "node_wise_hidden": None},
+                     "edge_nonlinear": "so2_sigmoid_gate", "gate_m0": True, "scalar_act": None, "tensor_act": None,
+                     "node_wise_hidden": None, "edge_wise_hidden": None, "edge_ace_hidden": None, "num_head": None},
     "resnet": {"type": "BB", "linear_type": "aware", "use_first_resnet": False},
     "layer_norm": {"pre_norm_type": None, "final_norm_type": None, "use_first_pre_norm": False},
     "product_basis": {"type": "cgtp", "l1l2": None, "correlation": 2, "return_components": None, "num_expert": None,
@@ -125,7 +126,16 @@ def check_model_config(cfg: Dict) -> Dict:
     for section, key in [("atomic_basis", "type"), ("product_basis", "type"), ("atomic_basis", "nonlinear"),
                          ("product_basis", "correlation")]:
         cfg[section][key] = to_list(cfg[section][key])
-    _require(all(t == "cgtp" for t in cfg["atomic_basis"]["type"]), "atomic_basis.type == cgtp")
+    _require(all(t in ("cgtp", "uv_so2") for t in cfg["atomic_basis"]["type"]), "atomic_basis.type in {cgtp, uv_so2}")
+    if "uv_so2" in cfg["atomic_basis"]["type"]:  # the TECE edge block (tace/models/_e3nn/inter.py:440-519)
+        ab = cfg["atomic_basis"]
+        _require(cfg["atomic_basis"]["type"][0] == "cgtp", "atomic_basis.type: uv_so2 needs input ranks above 0, so not on the first layer")
+        _require(cfg["Lmax"] == cfg["lmax"], "Lmax == lmax with uv_so2 interactions")
+        _require(0 <= cfg["mmax"] <= min(2, cfg["lmax"]), "mmax <= 2 with uv_so2 interactions")
+        _require(ab["edge_wise_hidden"] in (None, cfg["num_channel"]), "atomic_basis.edge_wise_hidden == num_channel")
+        _require(ab["edge_nonlinear"] in ("so2_sigmoid_gate", "so2_silu_gate"), "atomic_basis.edge_nonlinear in {so2_sigmoid_gate, so2_silu_gate}")
+        _require(cfg["num_channel"] % (ab["num_head"] or 1) == 0, "num_head divides num_channel")
+        _require(ab["scatter_norm"] == "avg_num_neighbors", "scatter_norm = avg_num_neighbors next to uv_so2 interactions")
     _require(all(t in ("cgtp", "spatial", "coupled") for t in cfg["product_basis"]["type"]), "product_basis.type == cgtp")
     _require(all(n == "sigmoid_gate" for n in cfg["atomic_basis"]["nonlinear"]), "atomic_basis.nonlinear == sigmoid_gate")
     corr = cfg["product_basis"]["correlation"]
@@ -211,6 +221,9 @@ class e3nnTACE(torch.nn.Module):
                               apply_cutoff=cfg["radial_basis"]["apply_cutoff"],
                               element2=cfg["edge_update"]["type"] == "element2", num_fidelities=self.num_fidelities,
                               product_bilinear=cfg["product_basis"]["nonlinear"] == "silu_bilineargate",
+                              tece_layers=[t for t, k in enumerate(cfg["atomic_basis"]["type"]) if k == "uv_so2"], mmax=cfg["mmax"],
+                              num_head=cfg["atomic_basis"]["num_head"], edge_ace_hidden=cfg["atomic_basis"]["edge_ace_hidden"],
+                              edge_act=cfg["atomic_basis"]["edge_nonlinear"].split("_")[1],
                               resnet_type=cfg["resnet"]["linear_type"], product_agnostic=cfg["product_basis"]["agnostic"],
                               density={"avg_num_neighbors": 0, "density": 1, "no_cutoff_density": 2}[cfg["atomic_basis"]["scatter_norm"]],
                               zbl=0 if not cfg["short_range"]["zbl"]["enable"] else (1 if cfg["scale_shift"]["scale_zbl"] else 2))
@@ -221,6 +234,10 @@ class e3nnTACE(torch.nn.Module):
                 value = torch.zeros(shape, dtype=dt)
             elif ".edge_updates." in name:  # tace/models/_e3nn/edge.py:216-221
                 value = torch.empty(shape, dtype=dt).uniform_(-0.001, 0.001)
+            elif name.endswith("rejector.temperature_logit"):  # oam_2026_07_05.py:687-697: temperature 1
+                value = torch.full(shape, math.log((1.0 - 0.25) / (4.0 - 1.0)), dtype=dt)
+            elif "rejector.radial_proj" in name:  # zero-initialised (oam_2026_07_05.py:681-682)
+                value = torch.zeros(shape, dtype=dt)
             elif name.endswith(".alpha"):  # tace/models/_e3nn/inter.py:109-110
                 value = torch.tensor(float(cfg["avg_num_neighbors"]), dtype=dt)
             elif name.endswith(".beta"):
@@ -353,7 +370,9 @@ class TensorModel(torch.nn.Module):
             use_alllayer=int(plan.use_alllayer), gate_m0_off=int(not plan.gate_m0), mlp_layers=plan.mlp_layers,
             mlp_bias=int(plan.mlp_bias), env_after_mlp=int(not plan.apply_cutoff), edge_update_element2=int(plan.element2),
             num_fidelities=plan.n_fid, zbl=plan.zbl, scatter_norm_density=plan.density,
-            resnet_identity=int(plan.resnet_type == "identity"), product_bilinear=int(plan.bilinear))
+            resnet_identity=int(plan.resnet_type == "identity"), product_bilinear=int(plan.bilinear),
+            tece_layers=sum(1 << t for t in plan.tece_layers), mmax=plan.mmax, num_head=plan.num_head,
+            edge_ace_hidden=plan.edge_ace_hidden, edge_act=0 if plan.edge_act == "sigmoid" else 1)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")

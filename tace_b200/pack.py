@@ -33,8 +33,10 @@ class LayerPlan:
     """``L``: rank of the angular features and of the atomic basis A (the reference's ``lmax``); ``Lnode``: rank of
     the node features between layers (``Lmax``), tace/models/_e3nn/base.py:113-360."""
 
-    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None, correlation: int = 2, bilinear: bool = False):
+    def __init__(self, t: int, num_layers: int, L: int, Lnode: int = None, correlation: int = 2, bilinear: bool = False,
+                 tece: bool = False, mmax: int = 2):
         Lnode = L if Lnode is None else Lnode
+        self.tece = bool(tece)  # the interaction is the TECE edge block (atomic_basis.type = uv_so2)
         self.t = t
         self.scalar_src = t == 0 or Lnode == 0
         self.last = t == num_layers - 1
@@ -45,6 +47,12 @@ class LayerPlan:
         self.out_ls = [0] if self.last else node_ls
         self.tp_paths = tp_paths(self.in_ls, all_ls, all_ls)
         self.k = [sum(1 for p in self.tp_paths if p[2] == l) for l in all_ls]
+        self.radial_out = len(self.tp_paths)  # radial-MLP outputs per channel
+        if self.tece:
+            # messages arrive as one block of channels per rank; the radial MLP weights every (order, rank >= order) row of the
+            # source | target features (tace/models/_e3nn/archive/oam_2026_07_05.py:586-588)
+            self.k = [1] * (L + 1)
+            self.radial_out = 2 * sum(L + 1 - m for m in range(mmax + 1))
         # second-order product basis: with a third order behind it every rank <= L keeps its paths (each path is a
         # slot of the next product), otherwise only the output ranks (tace/models/_e3nn/prod.py:216-266)
         self.pb_paths = tp_paths(all_ls, all_ls, all_ls if correlation >= 3 else self.out_ls)
@@ -67,7 +75,8 @@ class ModelPlan:
                  readout_hidden: int = 16, num_bessel: int = 8, mlp_hidden: int = 64, Lnode: int = None,
                  use_alllayer: bool = False, gate_m0: bool = True, mlp_layers: int = 3, mlp_bias: bool = False,
                  apply_cutoff: bool = True, element2: bool = False, num_fidelities: int = 1, zbl: int = 0,
-                 density: int = 0, resnet_type: str = "aware", product_agnostic: bool = False, product_bilinear: bool = False):
+                 density: int = 0, resnet_type: str = "aware", product_agnostic: bool = False, product_bilinear: bool = False,
+                 tece_layers=(), mmax: int = 2, num_head: int = 1, edge_ace_hidden: int = None, edge_act: str = "sigmoid"):
         self.L, self.num_layers, self.C, self.n_el = L, num_layers, num_channel, num_elements
         self.Cp = 32 * ((num_channel + 31) // 32)  # channel count the kernels run with (zero-padded, see pad_channels)
         self.Lnode = L if Lnode is None else Lnode
@@ -86,7 +95,15 @@ class ModelPlan:
         # radial MLP: hidden layers (all mlp_hidden wide), biases, envelope before (True) or after the MLP; edge update
         self.mlp_layers, self.mlp_bias, self.apply_cutoff, self.element2 = int(mlp_layers), bool(mlp_bias), bool(apply_cutoff), bool(element2)
         self.correlation, self.H, self.num_bessel, self.mlp_hidden = correlation, readout_hidden, num_bessel, mlp_hidden
-        self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation, self.bilinear) for t in range(num_layers)]
+        # TECE edge block: which interactions use it, orders kept, heads, width of the edge cluster expansion, activation
+        self.tece_layers, self.mmax, self.num_head = tuple(sorted(tece_layers)), int(mmax), int(num_head or 1)
+        self.edge_ace_hidden, self.edge_act = int(edge_ace_hidden or num_channel), edge_act
+        if self.tece_layers and (self.Cp != self.C or self.Lnode != L or 0 in self.tece_layers or not 0 <= self.mmax <= min(2, L)
+                                 or self.C % self.num_head or self.edge_ace_hidden % 4):
+            raise NotImplementedError("tace_b200: uv_so2 interactions need Lmax == lmax, mmax <= 2, a channel count that is a multiple "
+                                      "of 32 and of num_head, and cannot be the first layer")
+        self.layers = [LayerPlan(t, num_layers, L, self.Lnode, correlation, self.bilinear, t in self.tece_layers, self.mmax)
+                       for t in range(num_layers)]
 
     @property
     def mlp_layer_norm(self) -> bool:
@@ -98,6 +115,29 @@ class ModelPlan:
         """Position of the i-th linear inside the radial MLP's ``Sequential`` (linear, [LayerNorm], SiLU, ...)."""
         return (3 if self.mlp_layer_norm else 2) * i
 
+    def so2_linears(self):
+        """The six SO(2) linears of the edge block (oam_2026_07_05.py:612-676): reference name, packed name, channels in / out,
+        rows per order in / out."""
+        n, mm, C, Ca = self.L + 1, self.mmax, self.C, self.edge_ace_hidden
+        red, full = [n - m for m in range(mm + 1)], [n] * (mm + 1)
+        gates = n * (mm + 1 - (0 if self.gate_m0 else 1))
+        n_paths = sum(1 for m3 in range(mm + 1) for m1 in range(mm + 1) for m2 in range(m1 + 1) if m1 + m2 == m3 or m1 - m2 == m3)
+        return [("key_proj", "key", C, C, red, red), ("query_proj", "query", C, C, red, red),
+                ("linear_up", "up", 2 * C, Ca, red, [gates + n] + full[1:]), ("linear_glu", "glu", 2 * C, Ca, red, full),
+                ("linear_coefs", "coefs", 2 * C, 1, red[:1], [n_paths * n * Ca]), ("linear_down", "down", Ca, C, full, red)]
+
+    def tece_shapes(self) -> Dict[str, tuple]:
+        out = {}
+        for ref, _, ci, co, n_in, n_out in self.so2_linears():
+            out[f"rejector.{ref}.m0_rlinear.weight"] = (n_out[0] * co, n_in[0] * ci)
+            out[f"rejector.{ref}.m0_rlinear.bias"] = (n_out[0] * co,)
+            for m in range(1, len(n_in)):
+                out[f"rejector.{ref}.ms_clinear.{m - 1}.fc.weight"] = (n_out[m] * co, n_in[m] * ci)
+        out["rejector.radial_proj.weight"] = (2 * self.num_head, self.num_bessel)
+        out["rejector.radial_proj.bias"] = (2 * self.num_head,)
+        out["rejector.temperature_logit"] = (self.num_head,)
+        return out
+
     def parameter_shapes(self) -> Dict[str, tuple]:
         """Reference parameter names (without the ``readout_fn.`` prefix) and shapes."""
         C, n_el, L = self.C, self.n_el, self.L
@@ -107,7 +147,7 @@ class ModelPlan:
             out[pre + "linear_up.weight"] = (len(lp.in_ls) * C * C,)
             out[pre + "linear_up.bias"] = (C,)
             edge_dim = self.num_bessel + (2 * C if self.element2 else 0)
-            dims = [edge_dim] + [self.mlp_hidden] * self.mlp_layers + [len(lp.tp_paths) * C]
+            dims = [edge_dim] + [self.mlp_hidden] * self.mlp_layers + [lp.radial_out * C]
             for i, (a, b) in enumerate(zip(dims, dims[1:])):
                 out[pre + f"edge_info.mlp.{self.mlp_index(i)}.weight"] = (a, b)
                 if self.mlp_bias:
@@ -115,6 +155,8 @@ class ModelPlan:
                 if self.mlp_layer_norm and i < self.mlp_layers:
                     out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.weight"] = (b,)
                     out[pre + f"edge_info.mlp.{self.mlp_index(i) + 1}.bias"] = (b,)
+            if lp.tece:
+                out.update({pre + k: v for k, v in self.tece_shapes().items()})
             if self.density:  # tace/models/_e3nn/inter.py:102-110
                 out[pre + "edge_density.mlp.0.weight"] = (self.num_bessel, self.mlp_hidden)
                 out[pre + "edge_density.mlp.2.weight"] = (self.mlp_hidden, 1)
@@ -286,7 +328,23 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
                 out[tp + f"ln{j}b"] = g(pre + f"edge_info.mlp.{mi(j) + 1}.bias")
         down_shapes = [(lp.k[l] * C, ((L + 2) * C if plan.gate_m0 else (L + 1) * C) if l == 0 else C) for l in range(L + 1)]
         # the constant message normalisation is folded into linear_down; a learned density divides at run time instead
-        norm = 1.0 if plan.density else avg_num_neighbors
+        norm = 1.0 if (plan.density or lp.tece) else avg_num_neighbors  # the edge block is not normalised (inter.py:466)
+        if lp.tece:  # torch-style linears [out, in] with 1 / sqrt(fan_in) (tace/models/linear.py:210-244) -> [K][N]
+            for ref, name, ci, co, n_in, n_out in plan.so2_linears():
+                w0 = g(pre + f"rejector.{ref}.m0_rlinear.weight")
+                put(tp + f"so2.{name}.m0", w0.T / math.sqrt(w0.shape[1]), tp + f"so2.{name}T.m0")
+                out[tp + f"so2.{name}.b"] = g(pre + f"rejector.{ref}.m0_rlinear.bias")
+                for m in range(1, len(n_in)):
+                    wm = g(pre + f"rejector.{ref}.ms_clinear.{m - 1}.fc.weight")
+                    put(tp + f"so2.{name}.m{m}", wm.T / math.sqrt(wm.shape[1]), tp + f"so2.{name}T.m{m}")
+            n, H = plan.L + 1, plan.num_head
+            rows = n + 2 * n * plan.mmax  # oam_2026_07_05.py:597-600,683-685
+            scale = 1.0 / math.sqrt((plan.C // H) * rows)
+            logit = g(pre + "rejector.temperature_logit").reshape(H)
+            out[tp + "att.temp"] = scale * (0.25 + (4.0 - 0.25) / (1.0 + np.exp(-logit)))
+            rw = g(pre + "rejector.radial_proj.weight")
+            out[tp + "att.rw"] = rw.T / math.sqrt(rw.shape[1])
+            out[tp + "att.rb"] = g(pre + "rejector.radial_proj.bias")
         for l, m in enumerate(split(g(pre + "linear_down.weight"), down_shapes)):
             put(tp + f"down.l{l}", m / math.sqrt(lp.k[l] * C) / norm, tp + f"downT.l{l}")
         out[tp + "down.b"] = g(pre + "linear_down.bias") / norm
@@ -347,7 +405,8 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         stem = name.split(".")[1] if name.startswith("t") and "." in name else ""
         if (stem in ("up", "upT", "down", "downT", "nl", "nlT", "lin", "linT", "c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT", "pu", "puT")
                 and name.split(".")[-1].startswith("l")) \
-                or stem in ("A1", "A1t", "A2", "A2t", "W3", "W3t") or name.split(".")[-1] in ("pg", "pgT"):
+                or stem in ("A1", "A1t", "A2", "A2t", "W3", "W3t") or name.split(".")[-1] in ("pg", "pgT") \
+                or (stem == "so2" and name.split(".")[-1].startswith("m")):
             hi, lo = split_tf32(out[name])
             if stem in ("c0", "c0T", "c1", "c1T", "c2", "c2T", "res", "resT"):
                 # per-species matrices [species][N][K] are read once per pass: store them K-tile-major,

@@ -150,17 +150,24 @@ def model_config(L: int, channels: int, cutoff: float, elements: Sequence[int], 
                  Lmax: int = None, use_alllayer: bool = False, gate_m0: bool = True, radial: Dict = None,
                  edge_update: str = "identity", num_fidelities: int = 1, zbl: Dict = None, scale_zbl: bool = True,
                  scatter_norm: str = "avg_num_neighbors", resnet_linear_type: str = "aware",
-                 product_agnostic: bool = False, product_nonlinear: str = None) -> Dict:
+                 product_agnostic: bool = False, product_nonlinear: str = None, tece: Dict = None) -> Dict:
     """Keyword arguments for ``tace_b200.models.e3nnTACE`` (cgtp interaction, cgtp product).  ``L`` is the edge
     rank ``lmax``; the node rank ``Lmax`` defaults to it."""
+    atomic_basis = {"gate_m0": bool(gate_m0), "scatter_norm": scatter_norm}
+    extra = {}
+    if tece:  # every interaction above the first is the TECE edge block: {"num_head", "edge_ace_hidden", "mmax", "edge_nonlinear"}
+        atomic_basis.update(type=["cgtp"] + ["uv_so2"] * (num_layers - 1), num_head=tece.get("num_head", 1),
+                            edge_ace_hidden=tece.get("edge_ace_hidden"), edge_nonlinear=tece.get("edge_nonlinear", "so2_sigmoid_gate"))
+        extra["mmax"] = tece.get("mmax", 2)
     return {
+        **extra,
         "Lmax": L if Lmax is None else Lmax, "lmax": L, "num_layers": num_layers, "num_channel": channels, "cutoff": float(cutoff),
         "statistics": statistics(elements, avg_num_neighbors, num_fidelities),
         "target_property": list(target_property), "max_neighbors": None,
         "product_basis": {"correlation": correlation, "agnostic": bool(product_agnostic), "nonlinear": product_nonlinear},
         "resnet": {"linear_type": resnet_linear_type},
         "readout_emlp": {"use_alllayer": bool(use_alllayer)},
-        "atomic_basis": {"gate_m0": bool(gate_m0), "scatter_norm": scatter_norm},
+        "atomic_basis": atomic_basis,
         "radial_basis": dict(radial or {}),
         "edge_update": {"type": edge_update},
         "short_range": {"zbl": dict(zbl or {"enable": False})},

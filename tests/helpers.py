@@ -11,7 +11,7 @@ from tace_b200 import synth
 def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correlation=2,
                 targets=("energy", "forces", "stress"), Lmax=None, use_alllayer=False, gate_m0=True, radial=None, edge_update="identity",
                 num_fidelities=1, zbl=None, scale_zbl=True, scatter_norm="avg_num_neighbors",
-                resnet_linear_type="aware", product_agnostic=False, product_nonlinear=None):
+                resnet_linear_type="aware", product_agnostic=False, product_nonlinear=None, tece=None):
     """The CUDA-backed TensorModel and the CPU oracle sharing one seeded state_dict."""
     from oracle.model import build_oracle
 
@@ -19,7 +19,7 @@ def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correl
                              target_property=targets, Lmax=Lmax, use_alllayer=use_alllayer, gate_m0=gate_m0, radial=radial, edge_update=edge_update,
                              num_fidelities=num_fidelities, zbl=zbl, scale_zbl=scale_zbl, scatter_norm=scatter_norm,
                              resnet_linear_type=resnet_linear_type, product_agnostic=product_agnostic,
-                             product_nonlinear=product_nonlinear)
+                             product_nonlinear=product_nonlinear, tece=tece)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
@@ -33,6 +33,8 @@ def make_models(L, C, elements, cutoff, avg, dtype, seed=0, num_layers=2, correl
                 v.copy_(0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
             if ".edge_info.mlp." in k and k.endswith(".weight") and v.dim() == 1:  # LayerNorm scale: away from 1
                 v.copy_(1.0 + 0.3 * torch.randn(v.shape, generator=g, dtype=v.dtype))
+            if "radial_proj.weight" in k:  # zero in the reference's initialisation: make the radial bias and phase matter
+                v.copy_(torch.randn(v.shape, generator=g, dtype=v.dtype))
             if k.endswith(".beta"):  # zero in the reference's initialisation: switch the learned density on
                 v.copy_(torch.tensor(0.8, dtype=v.dtype))
             if k.endswith(".alpha"):

@@ -406,3 +406,17 @@ def test_gated_bilinear_product(L, Lmax, num_layers):
         run_case(structs, L, 32, [1, 2, 3], 4.5, dtype, Lmax=Lmax, num_layers=num_layers, product_nonlinear="silu_bilineargate")
     run_case(structs, 2, 64, [1, 2, 3], 4.5, torch.float32, product_nonlinear="silu_bilineargate", product_agnostic=True,
              resnet_linear_type="identity")
+
+
+@pytest.mark.parametrize("L,mmax,gate_m0,radial,num_layers", [
+    (2, 2, True, {"apply_cutoff": False}, 2),
+    (3, 2, False, {"apply_cutoff": False, "bias": True, "hidden": [64, 64]}, 2),
+    (2, 1, True, {}, 3),
+])
+def test_tece_edge_block(L, mmax, gate_m0, radial, num_layers):
+    """atomic_basis.type = [cgtp, uv_so2, ...]: edge-frame rotation with recursive Wigner matrices, SO(2) linears, gate, edge
+    cluster expansion, rotary attention normalised over the incoming edges; gradients through the frames in forward mode."""
+    structs = synth.random_crystals(2, seed=33, nmin=4, nmax=8, zmax=3)
+    tece = {"num_head": 4, "edge_ace_hidden": 8, "mmax": mmax}
+    for dtype in (torch.float64, torch.float32):
+        run_case(structs, L, 32, [1, 2, 3], 4.0, dtype, gate_m0=gate_m0, radial=radial, num_layers=num_layers, tece=tece)
