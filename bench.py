@@ -138,7 +138,7 @@ def sum_over_ranks(x: float, world: int, device) -> float:
 def build_model(wl: dict, dtype):
     import tace_b200
     from tace_b200 import synth
-    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"])
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"], **wl.get("model", {}))
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
@@ -174,7 +174,7 @@ def cpu_sample(structures, wl, dtype, state_dict, budget_s: float, evals: int):
     from tace_b200 import synth
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"])
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"], **wl.get("model", {}))
     oracle = build_oracle(cfg, state_dict, dtype)
     order = sorted(range(len(structures)), key=lambda i: len(structures[i]["positions"]))
     probe = [structures[order[0]]]

@@ -420,3 +420,22 @@ def test_tece_edge_block(L, mmax, gate_m0, radial, num_layers):
     tece = {"num_head": 4, "edge_ace_hidden": 8, "mmax": mmax}
     for dtype in (torch.float64, torch.float32):
         run_case(structs, L, 32, [1, 2, 3], 4.0, dtype, gate_m0=gate_m0, radial=radial, num_layers=num_layers, tece=tece)
+
+
+def test_tece_example_configuration_small():
+    """The model of BASELINE configuration 4 (the reference's example TECE file: cgtp then uv_so2, element-dependent edge
+    update with LayerNorm, envelope after a biased two-layer radial MLP, e3nn gate, identity skip, species-agnostic gated
+    bilinear product) at 32 channels on a small five-component BCC cell, fp64 and fp32; repeated calls replay a CUDA graph."""
+    s = synth.bcc_supercell(2, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))
+    kw = dict(synth.WORKLOADS["tece8192_fp32"]["model"])
+    kw["tece"] = {"num_head": 4, "edge_ace_hidden": 8, "mmax": 2}
+    for dtype in (torch.float64, torch.float32):
+        run_case([s], 3, 32, [23, 24, 26, 27, 28], 4.0, dtype, **kw)
+    model, oracle, _ = make_models(3, 32, [23, 24, 26, 27, 28], 4.0, 20.0, torch.float64, **kw)
+    data = oracle_batch([s], [23, 24, 26, 27, 28], 4.0, torch.float64)
+    dev_data = to_device(data, torch.device("cuda:0"))
+    first = model(dev_data)
+    for _ in range(3):
+        again = model(dev_data)
+    assert model.graph_replays() >= 2
+    assert torch.equal(first["forces"], again["forces"]) and torch.equal(first["energy"], again["energy"])
