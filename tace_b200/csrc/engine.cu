@@ -582,7 +582,7 @@ struct Model : ModelBase {
     T *XY, *gXY, *Zg, *gZg;     // gated bilinear product: both factors per (atom, component), gate pre-activations, gradients
     // TECE edge block (layouts at the top of tece_kernels.cu); gradients that may overwrite their forward buffer do
     T *tKs, *tQt, *tMw, *tKp, *tQp, *tlogit, *talpha, *tup, *tglu, *tcoef, *tU, *tdown;
-    T *tgdown, *tgalpha, *tglogit, *tgcut, *tgproj, *tgQp, *tgKp, *tgKs, *tgQt, *tdxt, *tddlen;
+    T *tgdown, *tgalpha, *tglogit, *tgcut, *tgproj, *tproj, *tgQp, *tgKp, *tgKs, *tgQt, *tdxt, *tddlen;
   };
   struct Bufs {
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
@@ -654,7 +654,7 @@ struct Model : ModelBase {
         lb.tup = ar.take<T>(Es * (t_G + t_NF) * Ca); lb.tglu = ar.take<T>(Es * t_NF * Ca); lb.tcoef = ar.take<T>(Es * t_WN);
         lb.tU = ar.take<T>(Es * t_NF * Ca); lb.tdown = ar.take<T>(Es * t_NR * C);
         lb.tgdown = ar.take<T>(Es * t_NR * C); lb.tgalpha = ar.take<T>(Es * heads); lb.tglogit = ar.take<T>(Es * heads);
-        lb.tgcut = ar.take<T>(Es * heads); lb.tgproj = ar.take<T>(Es * 2 * heads);
+        lb.tgcut = ar.take<T>(Es * heads); lb.tgproj = ar.take<T>(Es * 2 * heads); lb.tproj = ar.take<T>(Es * 2 * heads);
         lb.tgQp = ar.take<T>(Es * t_NR * C); lb.tgKp = ar.take<T>(Es * t_NR * C);
         lb.tgKs = ar.take<T>(Es * t_NR * C); lb.tgQt = ar.take<T>(Es * t_NR * C);
         lb.tdxt = ar.take<T>(Es * D * C); lb.tddlen = ar.take<T>(Es);
@@ -861,7 +861,7 @@ struct Model : ModelBase {
     a.x = x_src; a.W = lb.W; a.Wg = b.tWg; a.Ks = lb.tKs; a.Qt = lb.tQt; a.Mw = lb.tMw; a.Kp = lb.tKp; a.Qp = lb.tQp;
     a.logit = lb.tlogit; a.alpha = lb.talpha; a.temp = w(pre + "att.temp"); a.rproj_w = w(pre + "att.rw"); a.rproj_b = w(pre + "att.rb");
     a.up = lb.tup; a.glu = lb.tglu; a.coefZ = lb.tcoef; a.U = lb.tU; a.down = lb.tdown; a.M = lb.M;
-    a.gM = lb.M; a.gdown = lb.tgdown; a.galpha = lb.tgalpha; a.glogit = lb.tglogit; a.gcut = lb.tgcut; a.gproj = lb.tgproj;
+    a.gM = lb.M; a.gdown = lb.tgdown; a.galpha = lb.tgalpha; a.glogit = lb.tglogit; a.gcut = lb.tgcut; a.gproj = lb.tgproj; a.proj = lb.tproj;
     a.gQp = lb.tgQp; a.gKp = lb.tgKp; a.gKs = lb.tgKs; a.gQt = lb.tgQt; a.gMw = lb.tMw;
     a.gU = lb.tU; a.gup = lb.tup; a.gglu = lb.tglu; a.gcoefZ = lb.tcoef; a.gWg = b.tgWg; a.gvec = b.tgvec;
     a.dxe = b.dxe; a.dxt = lb.tdxt; a.gx = lb.gx; a.ddlen_extra = lb.tddlen;

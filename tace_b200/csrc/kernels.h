@@ -263,7 +263,7 @@ struct TeceArgs {
   const T* x; T* W; T* Wg; T* Ks; T* Qt; T* Mw; T* Kp; T* Qp; T* logit; T* alpha;
   const T* temp; const T* rproj_w; const T* rproj_b;                 // per-head scale * temperature; radial projection [8][2H], [2H]
   T* up; T* glu; T* coefZ; T* U; T* down; T* M;
-  const T* gM; T* gdown; T* galpha; T* glogit; T* gcut; T* gproj; T* gQp; T* gKp; T* gKs; T* gQt; T* gMw;
+  const T* gM; T* gdown; T* galpha; T* glogit; T* gcut; T* gproj; T* proj; T* gQp; T* gKp; T* gKs; T* gQt; T* gMw;
   const T* gU; T* gup; T* gglu; T* gcoefZ; T* gWg; T* gvec; T* dxe; T* dxt; T* gx; T* ddlen_extra;
 };
 template <typename T> cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s);

@@ -334,6 +334,62 @@ __global__ void tece_logit_bwd_kernel(const TeceArgs<T> a) {
   a.gproj[e * 2 * a.H + h] = gl;
   a.gproj[e * 2 * a.H + a.H + h] = gphase * T(3.141592653589793) * (T(1) - th * th);
 }
+// Lane-per-channel forms of the two kernels above, for head widths that are a power of two <= 32: thread (e, c) handles the
+// channel's share of the dot products (contiguous loads), the head's lanes reduce with shuffles, the radial projection is
+// read from proj [E][2H] (tece_proj_kernel).
+template <typename T>
+__global__ void tece_proj_kernel(const TeceArgs<T> a) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= a.E) return;
+  T proj[32];
+  radial_projection(a, a.dlen[e], proj, (T*)nullptr);
+  for (int j = 0; j < 2 * a.H; ++j) a.proj[e * 2 * a.H + j] = proj[j];
+}
+template <typename T, bool BWD>
+__global__ void tece_logit_lane_kernel(const TeceArgs<T> a) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= a.E * a.C) return;
+  const long long e = idx / a.C;
+  const int c = (int)(idx - e * a.C), C = a.C, Ch = C / a.H, h = c / Ch, n0 = a.L + 1;
+  const T th = tanh(a.proj[e * 2 * a.H + a.H + h]);
+  const T phase = T(3.141592653589793) * th;
+  const T* q = a.Qp + e * a.NR * C + c;
+  const T* k = a.Kp + e * a.NR * C + c;
+  T gs = T(0);
+  T* gq = nullptr; T* gk = nullptr;
+  if (BWD) { gs = a.glogit[e * a.H + h] * a.temp[h]; gq = a.gQp + e * a.NR * C + c; gk = a.gKp + e * a.NR * C + c; }
+  T part = T(0);  // forward: the channel's share of the score; backward: of d score / d phase
+  for (int r = 0; r < n0; ++r) {
+    if (!BWD) part += q[r * C] * k[r * C];
+    else { gq[r * C] = gs * k[r * C]; gk[r * C] = gs * q[r * C]; }
+  }
+  int off = n0;
+  for (int m = 1; m <= a.mmax; ++m) {
+    const int n = a.L + 1 - m;
+    const T cs = cos(T(m) * phase), sn = sin(T(m) * phase);
+    for (int r = 0; r < n; ++r) {
+      const int ir = (off + r) * C, ii = (off + n + r) * C;
+      const T kr = k[ir], ki = k[ii], qr = q[ir], qi = q[ii];
+      if (!BWD) part += qr * (cs * kr - sn * ki) + qi * (sn * kr + cs * ki);
+      else {
+        gq[ir] = gs * (cs * kr - sn * ki);
+        gq[ii] = gs * (sn * kr + cs * ki);
+        gk[ir] = gs * (cs * qr + sn * qi);
+        gk[ii] = gs * (-sn * qr + cs * qi);
+        part += gs * T(m) * (qr * (-sn * kr - cs * ki) + qi * (cs * kr - sn * ki));
+      }
+    }
+    off += 2 * n;
+  }
+  for (int o = Ch >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (c % Ch == 0) {
+    if (!BWD) a.logit[e * a.H + h] = part * a.temp[h] + a.proj[e * 2 * a.H + h];
+    else {
+      a.gproj[e * 2 * a.H + h] = a.glogit[e * a.H + h];
+      a.gproj[e * 2 * a.H + a.H + h] = part * T(3.141592653589793) * (T(1) - th * th);
+    }
+  }
+}
 // ddlen_extra[e] = sum_j gproj[e][j] d proj_j / d d + gcut[e] d envelope / d d
 template <typename T>
 __global__ void tece_edge_scalar_bwd_kernel(const TeceArgs<T> a) {
@@ -509,8 +565,10 @@ __global__ void tece_rotate_out_kernel(const TeceArgs<T> a) {
   }
   for (int j = 0; j < D; ++j) a.M[(i * D + j) * C + c] = acc[j];
 }
-// gdown[e][r][c] = alpha scale_r sum_j Wg[e][r][j] gM[target][j][c]
-template <typename T>
+// gdown[e][r][c] = alpha scale_r sum_j Wg[e][r][j] gM[target][j][c].  FUSE (channels per head a power of two <= 32, so one
+// head is a group of neighbouring lanes): also galpha[e][h] = sum over the head's channels and the rows of down * scale_r * t,
+// reduced with shuffles, which saves the separate pass of tece_alpha_bwd_kernel over the same data.
+template <typename T, bool FUSE>
 __global__ void tece_rotate_out_bwd_kernel(const TeceArgs<T> a) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= a.E * a.C) return;
@@ -519,11 +577,19 @@ __global__ void tece_rotate_out_bwd_kernel(const TeceArgs<T> a) {
   const T al = a.alpha[e * a.H + h];
   const T* Wg = a.Wg + e * a.NR * D;
   const T* gM = a.gM + (long long)a.e_dst[e] * D * C + c;
+  T part = T(0);
   for (int r = 0; r < a.NR; ++r) {
     const int l = a.row_l[r], dl = 2 * l + 1;
     T t = T(0);
     for (int j = 0; j < dl; ++j) t += Wg[r * D + l * l + j] * gM[(long long)(l * l + j) * C];
-    a.gdown[(e * a.NR + r) * C + c] = al * a.row_scale[r] * t;
+    t *= a.row_scale[r];
+    a.gdown[(e * a.NR + r) * C + c] = al * t;
+    if (FUSE) part += a.down[(e * a.NR + r) * C + c] * t;
+  }
+  if (FUSE) {
+    const int Ch = C / a.H;
+    for (int o = Ch >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (c % Ch == 0) a.galpha[e * a.H + h] = part;
   }
 }
 // galpha[e][h] = sum_{c in head} sum_r down[e][r][c] scale_r sum_j Wg[e][r][j] gM[target][j][c]
@@ -548,24 +614,44 @@ __global__ void tece_alpha_bwd_kernel(const TeceArgs<T> a) {
   a.galpha[idx] = acc;
 }
 // gWg[e][r][j] = sum_c ( gKs_total x[source][j] + gQt_total x[target][j] + alpha scale_r gM[target][j] down[e][r] )
+// One warp per edge: lane k owns the channels k, k + 32, ...; every lane accumulates all block entries of the edge (at most
+// 70 for L = 3, mmax = 2), then the warp reduces them.  All loads are contiguous in the channel index.
 template <typename T>
-__global__ void tece_wigner_grad_kernel(const TeceArgs<T> a) {
-  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  const int D = (a.L + 1) * (a.L + 1);
-  if (idx >= a.E * a.NR * D) return;
-  const long long e = idx / (a.NR * D);
-  const int rj = (int)(idx - e * a.NR * D), r = rj / D, j = rj - r * D, l = a.row_l[r], C = a.C, Ch = C / a.H;
-  if (j < l * l || j >= (l + 1) * (l + 1)) { a.gWg[idx] = T(0); return; }
-  const T* xs = a.x + ((long long)a.e_src[e] * D + j) * C;
-  const T* xt = a.x + ((long long)a.e_dst[e] * D + j) * C;
-  const T* gM = a.gM + ((long long)a.e_dst[e] * D + j) * C;
-  const T* gks = a.gKs + (e * a.NR + r) * C;
-  const T* gqt = a.gQt + (e * a.NR + r) * C;
-  const T* dn = a.down + (e * a.NR + r) * C;
-  T acc = T(0);
-  for (int c = 0; c < C; ++c)
-    acc += gks[c] * xs[c] + gqt[c] * xt[c] + a.alpha[e * a.H + c / Ch] * a.row_scale[r] * gM[c] * dn[c];
-  a.gWg[idx] = acc;
+__global__ void __launch_bounds__(128) tece_wigner_grad_kernel(const TeceArgs<T> a) {
+  const int lane = threadIdx.x & 31;
+  const long long e = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= a.E) return;
+  const int D = (a.L + 1) * (a.L + 1), C = a.C, Ch = C / a.H;
+  constexpr int MAXE = 70;
+  T acc[MAXE];
+#pragma unroll
+  for (int k = 0; k < MAXE; ++k) acc[k] = T(0);
+  const T* xs = a.x + (long long)a.e_src[e] * D * C;
+  const T* xt = a.x + (long long)a.e_dst[e] * D * C;
+  const T* gM = a.gM + (long long)a.e_dst[e] * D * C;
+  for (int c = lane; c < C; c += 32) {
+    const T al = a.alpha[e * a.H + c / Ch];
+    T vs[16], vt[16], vg[16];
+    for (int j = 0; j < D; ++j) { vs[j] = xs[(long long)j * C + c]; vt[j] = xt[(long long)j * C + c]; vg[j] = al * gM[(long long)j * C + c]; }
+    int k = 0;
+    for (int r = 0; r < a.NR; ++r) {
+      const int l = a.row_l[r], dl = 2 * l + 1;
+      const long long at = (e * a.NR + r) * C + c;
+      const T gk = a.gKs[at], gq = a.gQt[at], dn = a.row_scale[r] * a.down[at];
+      for (int j = 0; j < dl; ++j, ++k) acc[k] += gk * vs[l * l + j] + gq * vt[l * l + j] + dn * vg[l * l + j];
+    }
+  }
+  T* out = a.gWg + e * a.NR * D;
+  int k = 0;
+  for (int r = 0; r < a.NR; ++r) {
+    const int l = a.row_l[r], dl = 2 * l + 1;
+    for (int j = 0; j < dl; ++j, ++k) {
+      T v = acc[k];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) out[r * D + l * l + j] = v;
+    }
+  }
 }
 
 }  // namespace
@@ -583,22 +669,39 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
   if (a.L > 3 || a.mmax > 2 || a.NR > 16 || a.NC > 9 || a.H > 16 || a.G > 12 || a.n_paths * (a.L + 1) > 28 || a.C % a.H != 0)
     return cudaErrorInvalidValue;
   cudaError_t err = cudaSuccess;
+  const int ch = a.C / a.H;
+  const bool fuse_alpha = a.C % 32 == 0 && ch <= 32 && (ch & (ch - 1)) == 0;
   switch (stage) {
     case TECE_WIGNER: tece_wigner_kernel<T><<<(unsigned)((a.E + 63) / 64), 64, 0, s>>>(a); break;
     case TECE_ROTATE_IN: tece_rotate_in_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_LOGIT: tece_logit_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_LOGIT:
+      if (fuse_alpha) {
+        tece_proj_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a);
+        tece_logit_lane_kernel<T, false><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      } else {
+        tece_logit_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a);
+      }
+      break;
     case TECE_SOFTMAX: tece_softmax_kernel<T><<<(unsigned)(((long long)a.n_local * a.H + 127) / 128), 128, 0, s>>>(a); break;
     case TECE_MIX: tece_mix_kernel<T, false><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a); break;
     case TECE_ROTATE_OUT: tece_rotate_out_kernel<T><<<(unsigned)(((long long)a.n_local * a.C + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_ROTATE_OUT_BWD: tece_rotate_out_bwd_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_ALPHA_BWD: tece_alpha_bwd_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_ROTATE_OUT_BWD:
+      if (fuse_alpha) tece_rotate_out_bwd_kernel<T, true><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      else tece_rotate_out_bwd_kernel<T, false><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      break;
+    case TECE_ALPHA_BWD:  // already done by the fused kernel above when the head width allows it
+      if (!fuse_alpha) tece_alpha_bwd_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a);
+      break;
     case TECE_SOFTMAX_BWD: tece_softmax_bwd_kernel<T><<<(unsigned)(((long long)a.n_local * a.H + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_LOGIT_BWD: tece_logit_bwd_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_LOGIT_BWD:
+      if (fuse_alpha) tece_logit_lane_kernel<T, true><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      else tece_logit_bwd_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a);
+      break;
     case TECE_EDGE_SCALAR_BWD: tece_edge_scalar_bwd_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a); break;
     case TECE_MIX_BWD: tece_mix_kernel<T, true><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a); break;
     case TECE_ROTATE_IN_BWD: tece_rotate_in_bwd_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a); break;
     case TECE_TARGET_SUM: tece_target_sum_kernel<T><<<(unsigned)(((long long)a.n_local * D * a.C + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_WIGNER_GRAD: tece_wigner_grad_kernel<T><<<(unsigned)((a.E * a.NR * D + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_WIGNER_GRAD: tece_wigner_grad_kernel<T><<<(unsigned)((a.E + 3) / 4), 128, 0, s>>>(a); break;
     case TECE_WIGNER_BWD: tece_wigner_bwd_kernel<T><<<(unsigned)((a.E + 63) / 64), 64, 0, s>>>(a, a.accumulate_gvec); break;
     default: err = cudaErrorInvalidValue;
   }

@@ -439,3 +439,9 @@ def test_tece_example_configuration_small():
         again = model(dev_data)
     assert model.graph_replays() >= 2
     assert torch.equal(first["forces"], again["forces"]) and torch.equal(first["energy"], again["energy"])
+
+
+def test_tece_edge_block_wide_head():
+    """One head over 64 channels: wider than a warp, so the attention kernels take their per-(edge, head) form."""
+    structs = synth.random_crystals(2, seed=35, nmin=4, nmax=8, zmax=3)
+    run_case(structs, 2, 64, [1, 2, 3], 4.0, torch.float64, radial={"apply_cutoff": False}, tece={"num_head": 1, "edge_ace_hidden": 8, "mmax": 2})
