@@ -256,6 +256,116 @@ __global__ void tece_target_sum_kernel(const TeceArgs<T> a) {
   a.gx[idx] += acc;
 }
 
+// ---- the rotation kernels with rank and order limits known at compile time -------------------------------------
+// for_rows visits the order-major rows with constant (row, rank, weight component) after unrolling, so the per-thread
+// arrays of the kernels below are indexed statically and stay in registers.
+template <int L, int MM, typename F>
+TACE_D TACE_INLINE void for_rows(F&& f) {
+  int r = 0, comp0 = 0;
+#pragma unroll
+  for (int m = 0; m <= MM; ++m) {
+#pragma unroll
+    for (int part = 0; part < (m ? 2 : 1); ++part)
+#pragma unroll
+      for (int l = m; l <= L; ++l) { f(r, l, comp0 + l - m); ++r; }
+    comp0 += L + 1 - m;
+  }
+}
+template <int L, int MM> struct RowCount { static constexpr int NR = (L + 1) + (MM >= 1 ? 2 * L : 0) + (MM >= 2 ? 2 * (L - 1) : 0); };
+
+template <typename T, int L, int MM>
+__global__ void __launch_bounds__(128) tece_rotate_in_t_kernel(const TeceArgs<T> a) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= a.E * a.C) return;
+  const long long e = idx / a.C;
+  constexpr int D = (L + 1) * (L + 1), NR = RowCount<L, MM>::NR;
+  const int c = (int)(idx - e * a.C), C = a.C;
+  const T* xs = a.x + (long long)a.e_src[e] * D * C + c;
+  const T* xt = a.x + (long long)a.e_dst[e] * D * C + c;
+  const T* Wg = a.Wg + e * NR * D;
+  const T* W = a.W + e * a.NC * 2 * C;
+  T vs[D], vt[D];
+#pragma unroll
+  for (int j = 0; j < D; ++j) { vs[j] = xs[(long long)j * C]; vt[j] = xt[(long long)j * C]; }
+  for_rows<L, MM>([&](int r, int l, int comp) {
+    T ks = T(0), qt = T(0);
+#pragma unroll
+    for (int j = 0; j < 2 * l + 1; ++j) {
+      const T wv = Wg[r * D + l * l + j];
+      ks += wv * vs[l * l + j];
+      qt += wv * vt[l * l + j];
+    }
+    a.Ks[(e * NR + r) * C + c] = ks;
+    a.Qt[(e * NR + r) * C + c] = qt;
+    a.Mw[(e * NR + r) * 2 * C + c] = W[comp * 2 * C + c] * ks;
+    a.Mw[(e * NR + r) * 2 * C + C + c] = W[comp * 2 * C + C + c] * qt;
+  });
+}
+template <typename T, int L, int MM>
+__global__ void __launch_bounds__(128) tece_rotate_in_bwd_t_kernel(const TeceArgs<T> a) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= a.E * a.C) return;
+  const long long e = idx / a.C;
+  constexpr int D = (L + 1) * (L + 1), NR = RowCount<L, MM>::NR, NC = (L + 1) + (MM >= 1 ? L : 0) + (MM >= 2 ? L - 1 : 0);
+  const int c = (int)(idx - e * a.C), C = a.C;
+  const T* Wg = a.Wg + e * NR * D;
+  T* W = a.W + e * NC * 2 * C;
+  T gs[D], gt[D], dws[NC], dwt[NC], ws[NC], wt[NC];
+#pragma unroll
+  for (int j = 0; j < D; ++j) { gs[j] = T(0); gt[j] = T(0); }
+#pragma unroll
+  for (int k = 0; k < NC; ++k) { dws[k] = T(0); dwt[k] = T(0); ws[k] = W[k * 2 * C + c]; wt[k] = W[k * 2 * C + C + c]; }
+  for_rows<L, MM>([&](int r, int l, int comp) {
+    const long long at = (e * NR + r);
+    const T gms = a.gMw[at * 2 * C + c], gmt = a.gMw[at * 2 * C + C + c];
+    dws[comp] += gms * a.Ks[at * C + c];
+    dwt[comp] += gmt * a.Qt[at * C + c];
+    const T gks = a.gKs[at * C + c] + ws[comp] * gms;
+    const T gqt = a.gQt[at * C + c] + wt[comp] * gmt;
+    a.gKs[at * C + c] = gks;
+    a.gQt[at * C + c] = gqt;
+#pragma unroll
+    for (int j = 0; j < 2 * l + 1; ++j) {
+      const T wv = Wg[r * D + l * l + j];
+      gs[l * l + j] += wv * gks;
+      gt[l * l + j] += wv * gqt;
+    }
+  });
+#pragma unroll
+  for (int k = 0; k < NC; ++k) { W[k * 2 * C + c] = dws[k]; W[k * 2 * C + C + c] = dwt[k]; }
+#pragma unroll
+  for (int j = 0; j < D; ++j) { a.dxe[(e * D + j) * C + c] = gs[j]; a.dxt[(e * D + j) * C + c] = gt[j]; }
+}
+template <typename T, int L, int MM>
+__global__ void __launch_bounds__(128) tece_rotate_out_t_kernel(const TeceArgs<T> a) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)a.n_local * a.C) return;
+  const long long i = idx / a.C;
+  constexpr int D = (L + 1) * (L + 1), NR = RowCount<L, MM>::NR;
+  const int c = (int)(idx - i * a.C), C = a.C, h = c / (C / a.H);
+  T acc[D];
+#pragma unroll
+  for (int j = 0; j < D; ++j) acc[j] = T(0);
+  for (int e = a.rowptr[i]; e < a.rowptr[i + 1]; ++e) {
+    const T al = a.alpha[(long long)e * a.H + h];
+    const T* Wg = a.Wg + (long long)e * NR * D;
+    const T* dn = a.down + (long long)e * NR * C + c;
+    for_rows<L, MM>([&](int r, int l, int) {
+      const T v = al * a.row_scale[r] * dn[(long long)r * C];
+#pragma unroll
+      for (int j = 0; j < 2 * l + 1; ++j) acc[l * l + j] += Wg[r * D + l * l + j] * v;
+    });
+  }
+#pragma unroll
+  for (int j = 0; j < D; ++j) a.M[(i * D + j) * C + c] = acc[j];
+}
+#define TECE_LM_DISPATCH(KERNEL, GRID, BLOCK)                                              \
+  (a.L == 2 && a.mmax == 1   ? (KERNEL<T, 2, 1><<<GRID, BLOCK, 0, s>>>(a), true)          \
+   : a.L == 2 && a.mmax == 2 ? (KERNEL<T, 2, 2><<<GRID, BLOCK, 0, s>>>(a), true)          \
+   : a.L == 3 && a.mmax == 1 ? (KERNEL<T, 3, 1><<<GRID, BLOCK, 0, s>>>(a), true)          \
+   : a.L == 3 && a.mmax == 2 ? (KERNEL<T, 3, 2><<<GRID, BLOCK, 0, s>>>(a), true)          \
+                             : false)
+
 // ---- K3: attention logits ---------------------------------------------------------------------------
 template <typename T>
 TACE_D void radial_projection(const TeceArgs<T>& a, T d, T* proj, T* dproj) {  // proj[2H], dproj = d proj / d d (or nullptr)
@@ -545,6 +655,131 @@ __global__ void tece_mix_kernel(const TeceArgs<T> a) {
   }
 }
 
+// The same kernel with rows per order, orders and gate layout known at compile time: every array index below is a constant
+// after unrolling, so the ~150 per-thread values live in registers instead of local memory.
+TACE_HD constexpr int mix_path_id(int mm, int m3, int m1, int m2) {  // position of path (m1, m2) -> m3 in the output-order-major list
+  int p = 0;
+  for (int q3 = 0; q3 <= mm; ++q3)
+    for (int q1 = 0; q1 <= mm; ++q1)
+      for (int q2 = 0; q2 <= q1; ++q2) {
+        if (!(q1 + q2 == q3 || q1 - q2 == q3)) continue;
+        if (q3 == m3 && q1 == m1 && q2 == m2) return p;
+        ++p;
+      }
+  return -1;
+}
+template <typename T, int N, int MM, bool GATE_M0, bool BWD>
+__global__ void __launch_bounds__(64) tece_mix_t_kernel(const TeceArgs<T> a) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= a.E * a.Ca) return;
+  const long long e = idx / a.Ca;
+  const int ca = (int)(idx - e * a.Ca), Ca = a.Ca;
+  constexpr int NF = N + 2 * N * MM, G = N * (MM + (GATE_M0 ? 1 : 0));
+  constexpr int START = GATE_M0 ? 0 : 1;
+  T x[NF], y[NF], gz[G > 0 ? G : 1], out[NF];
+  const T* up = a.up + e * (long long)(G + NF) * Ca + ca;
+  const T* glu = a.glu + e * (long long)NF * Ca + ca;
+  const T* cf = a.coefZ + e * (long long)a.n_paths * N * Ca + ca;
+#pragma unroll
+  for (int r = 0; r < G; ++r) gz[r] = up[(long long)r * Ca];
+#pragma unroll
+  for (int r = 0; r < NF; ++r) { x[r] = up[(long long)(G + r) * Ca]; y[r] = glu[(long long)r * Ca]; out[r] = x[r]; }
+  T gx[NF], gy[NF], gg[G > 0 ? G : 1], go[NF];
+  T* gcf = nullptr;
+  if (BWD) {
+    const T* gU = a.gU + e * (long long)NF * Ca + ca;
+#pragma unroll
+    for (int r = 0; r < NF; ++r) { go[r] = gU[(long long)r * Ca]; gx[r] = go[r]; gy[r] = T(0); }
+#pragma unroll
+    for (int r = 0; r < G; ++r) gg[r] = T(0);
+    gcf = a.gcoefZ + e * (long long)a.n_paths * N * Ca + ca;
+  }
+#pragma unroll
+  for (int m = 0; m <= MM; ++m) {
+#pragma unroll
+    for (int part = 0; part < (m == 0 ? 1 : 2); ++part)
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const int r = (m == 0 ? 0 : N + (m - 1) * 2 * N) + part * N + i;
+        if (m == 0 && !GATE_M0) {
+          out[r] += act_eval<T>(a.act, x[r]);
+          if (BWD) gx[r] += go[r] * act_grad<T>(a.act, x[r]);
+        } else {
+          const int g = (m - START) * N + i;
+          const T ag = act_eval<T>(a.act, gz[g]);
+          out[r] += ag * x[r];
+          if (BWD) { gx[r] += go[r] * ag; gg[g] += go[r] * x[r] * act_grad<T>(a.act, gz[g]); }
+        }
+      }
+  }
+#pragma unroll
+  for (int m3 = 0; m3 <= MM; ++m3)
+#pragma unroll
+    for (int m1 = 0; m1 <= MM; ++m1)
+#pragma unroll
+      for (int m2 = 0; m2 <= m1; ++m2) {
+        const bool sum_mode = (m1 + m2 == m3);
+        if (!(sum_mode || m1 - m2 == m3)) continue;
+        const int p = mix_path_id(MM, m3, m1, m2);
+        const T sc = a.p_scale[p];
+        const int x_re = (m1 == 0 ? 0 : N + (m1 - 1) * 2 * N), y_re = (m2 == 0 ? 0 : N + (m2 - 1) * 2 * N),
+                  o_re = (m3 == 0 ? 0 : N + (m3 - 1) * 2 * N);
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const T cz = cf[(long long)(p * N + i) * Ca];
+          const T w = act_eval<T>(a.act, cz) * sc;
+          const T xr = x[x_re + i], xi = m1 ? x[x_re + (m1 ? N : 0) + i] : T(0);
+          const T yr = y[y_re + i], yi = m2 ? y[y_re + (m2 ? N : 0) + i] : T(0);
+          T zr, zi;
+          if (sum_mode) { zr = xr * yr - xi * yi; zi = xr * yi + xi * yr; }
+          else { zr = xr * yr + xi * yi; zi = xi * yr - xr * yi; }
+          out[o_re + i] += w * zr;
+          if (m3) out[o_re + (m3 ? N : 0) + i] += w * zi;
+          if (BWD) {
+            const T gr = go[o_re + i], gi = m3 ? go[o_re + (m3 ? N : 0) + i] : T(0);
+            gcf[(long long)(p * N + i) * Ca] = (gr * zr + gi * zi) * sc * act_grad<T>(a.act, cz);
+            const T ar = w * gr, ai = w * gi;
+            if (sum_mode) {
+              gx[x_re + i] += ar * yr + ai * yi;
+              if (m1) gx[x_re + (m1 ? N : 0) + i] += -ar * yi + ai * yr;
+              gy[y_re + i] += ar * xr + ai * xi;
+              if (m2) gy[y_re + (m2 ? N : 0) + i] += -ar * xi + ai * xr;
+            } else {
+              gx[x_re + i] += ar * yr - ai * yi;
+              if (m1) gx[x_re + (m1 ? N : 0) + i] += ar * yi + ai * yr;
+              gy[y_re + i] += ar * xr + ai * xi;
+              if (m2) gy[y_re + (m2 ? N : 0) + i] += ar * xi - ai * xr;
+            }
+          }
+        }
+      }
+  if (!BWD) {
+    T* U = a.U + e * (long long)NF * Ca + ca;
+#pragma unroll
+    for (int r = 0; r < NF; ++r) U[(long long)r * Ca] = out[r];
+  } else {
+    T* gup = a.gup + e * (long long)(G + NF) * Ca + ca;
+    T* gglu = a.gglu + e * (long long)NF * Ca + ca;
+#pragma unroll
+    for (int r = 0; r < G; ++r) gup[(long long)r * Ca] = gg[r];
+#pragma unroll
+    for (int r = 0; r < NF; ++r) { gup[(long long)(G + r) * Ca] = gx[r]; gglu[(long long)r * Ca] = gy[r]; }
+  }
+}
+template <typename T, bool BWD>
+bool launch_mix_static(const TeceArgs<T>& a, cudaStream_t s) {
+  const unsigned grid = (unsigned)((a.E * a.Ca + 63) / 64);
+#define MIXCASE(N_, MM_)                                                                                        \
+  if (a.L + 1 == N_ && a.mmax == MM_) {                                                                         \
+    if (a.gate_m0) tece_mix_t_kernel<T, N_, MM_, true, BWD><<<grid, 64, 0, s>>>(a);                              \
+    else tece_mix_t_kernel<T, N_, MM_, false, BWD><<<grid, 64, 0, s>>>(a);                                       \
+    return true;                                                                                                \
+  }
+  MIXCASE(3, 1) MIXCASE(3, 2) MIXCASE(4, 1) MIXCASE(4, 2)
+#undef MIXCASE
+  return false;
+}
+
 // ---- K6: attention-weighted inverse rotation and sum per target atom --------------------------------------
 template <typename T>
 __global__ void tece_rotate_out_kernel(const TeceArgs<T> a) {
@@ -673,7 +908,10 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
   const bool fuse_alpha = a.C % 32 == 0 && ch <= 32 && (ch & (ch - 1)) == 0;
   switch (stage) {
     case TECE_WIGNER: tece_wigner_kernel<T><<<(unsigned)((a.E + 63) / 64), 64, 0, s>>>(a); break;
-    case TECE_ROTATE_IN: tece_rotate_in_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_ROTATE_IN:
+      if (!TECE_LM_DISPATCH(tece_rotate_in_t_kernel, (unsigned)((a.E * a.C + 127) / 128), 128))
+        tece_rotate_in_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      break;
     case TECE_LOGIT:
       if (fuse_alpha) {
         tece_proj_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a);
@@ -683,8 +921,13 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
       }
       break;
     case TECE_SOFTMAX: tece_softmax_kernel<T><<<(unsigned)(((long long)a.n_local * a.H + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_MIX: tece_mix_kernel<T, false><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a); break;
-    case TECE_ROTATE_OUT: tece_rotate_out_kernel<T><<<(unsigned)(((long long)a.n_local * a.C + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_MIX:
+      if (!launch_mix_static<T, false>(a, s)) tece_mix_kernel<T, false><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a);
+      break;
+    case TECE_ROTATE_OUT:
+      if (!TECE_LM_DISPATCH(tece_rotate_out_t_kernel, (unsigned)(((long long)a.n_local * a.C + 127) / 128), 128))
+        tece_rotate_out_kernel<T><<<(unsigned)(((long long)a.n_local * a.C + 127) / 128), 128, 0, s>>>(a);
+      break;
     case TECE_ROTATE_OUT_BWD:
       if (fuse_alpha) tece_rotate_out_bwd_kernel<T, true><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
       else tece_rotate_out_bwd_kernel<T, false><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
@@ -698,8 +941,13 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
       else tece_logit_bwd_kernel<T><<<(unsigned)((a.E * a.H + 127) / 128), 128, 0, s>>>(a);
       break;
     case TECE_EDGE_SCALAR_BWD: tece_edge_scalar_bwd_kernel<T><<<(unsigned)((a.E + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_MIX_BWD: tece_mix_kernel<T, true><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a); break;
-    case TECE_ROTATE_IN_BWD: tece_rotate_in_bwd_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a); break;
+    case TECE_MIX_BWD:
+      if (!launch_mix_static<T, true>(a, s)) tece_mix_kernel<T, true><<<(unsigned)((a.E * a.Ca + 63) / 64), 64, 0, s>>>(a);
+      break;
+    case TECE_ROTATE_IN_BWD:
+      if (!TECE_LM_DISPATCH(tece_rotate_in_bwd_t_kernel, (unsigned)((a.E * a.C + 127) / 128), 128))
+        tece_rotate_in_bwd_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
+      break;
     case TECE_TARGET_SUM: tece_target_sum_kernel<T><<<(unsigned)(((long long)a.n_local * D * a.C + 127) / 128), 128, 0, s>>>(a); break;
     case TECE_WIGNER_GRAD: tece_wigner_grad_kernel<T><<<(unsigned)((a.E + 3) / 4), 128, 0, s>>>(a); break;
     case TECE_WIGNER_BWD: tece_wigner_bwd_kernel<T><<<(unsigned)((a.E + 63) / 64), 64, 0, s>>>(a, a.accumulate_gvec); break;
