@@ -359,6 +359,46 @@ __global__ void __launch_bounds__(128) tece_rotate_out_t_kernel(const TeceArgs<T
 #pragma unroll
   for (int j = 0; j < D; ++j) a.M[(i * D + j) * C + c] = acc[j];
 }
+// Wigner-row gradient, one warp per edge (see tece_wigner_grad_kernel below), with static shapes
+template <typename T, int L, int MM>
+__global__ void __launch_bounds__(128) tece_wigner_grad_t_kernel(const TeceArgs<T> a) {
+  const int lane = threadIdx.x & 31;
+  const long long e = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= a.E) return;
+  constexpr int D = (L + 1) * (L + 1), NR = RowCount<L, MM>::NR;
+  constexpr int NE = D + (MM >= 1 ? 2 * (D - 1) : 0) + (MM >= 2 ? 2 * (D - 4) : 0);  // block entries of all rows
+  const int C = a.C, Ch = C / a.H;
+  T acc[NE];
+#pragma unroll
+  for (int k = 0; k < NE; ++k) acc[k] = T(0);
+  const T* xs = a.x + (long long)a.e_src[e] * D * C;
+  const T* xt = a.x + (long long)a.e_dst[e] * D * C;
+  const T* gM = a.gM + (long long)a.e_dst[e] * D * C;
+  for (int c = lane; c < C; c += 32) {
+    const T al = a.alpha[e * a.H + c / Ch];
+    T vs[D], vt[D], vg[D];
+#pragma unroll
+    for (int j = 0; j < D; ++j) { vs[j] = xs[(long long)j * C + c]; vt[j] = xt[(long long)j * C + c]; vg[j] = al * gM[(long long)j * C + c]; }
+    int k = 0;
+    for_rows<L, MM>([&](int r, int l, int) {
+      const long long at = (e * NR + r) * C + c;
+      const T gk = a.gKs[at], gq = a.gQt[at], dn = a.row_scale[r] * a.down[at];
+#pragma unroll
+      for (int j = 0; j < 2 * l + 1; ++j, ++k) acc[k] += gk * vs[l * l + j] + gq * vt[l * l + j] + dn * vg[l * l + j];
+    });
+  }
+  T* out = a.gWg + e * NR * D;
+  int k = 0;
+  for_rows<L, MM>([&](int r, int l, int) {
+#pragma unroll
+    for (int j = 0; j < 2 * l + 1; ++j, ++k) {
+      T v = acc[k];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) out[r * D + l * l + j] = v;
+    }
+  });
+}
 #define TECE_LM_DISPATCH(KERNEL, GRID, BLOCK)                                              \
   (a.L == 2 && a.mmax == 1   ? (KERNEL<T, 2, 1><<<GRID, BLOCK, 0, s>>>(a), true)          \
    : a.L == 2 && a.mmax == 2 ? (KERNEL<T, 2, 2><<<GRID, BLOCK, 0, s>>>(a), true)          \
@@ -949,7 +989,10 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
         tece_rotate_in_bwd_kernel<T><<<(unsigned)((a.E * a.C + 127) / 128), 128, 0, s>>>(a);
       break;
     case TECE_TARGET_SUM: tece_target_sum_kernel<T><<<(unsigned)(((long long)a.n_local * D * a.C + 127) / 128), 128, 0, s>>>(a); break;
-    case TECE_WIGNER_GRAD: tece_wigner_grad_kernel<T><<<(unsigned)((a.E + 3) / 4), 128, 0, s>>>(a); break;
+    case TECE_WIGNER_GRAD:
+      if (!TECE_LM_DISPATCH(tece_wigner_grad_t_kernel, (unsigned)((a.E + 3) / 4), 128))
+        tece_wigner_grad_kernel<T><<<(unsigned)((a.E + 3) / 4), 128, 0, s>>>(a);
+      break;
     case TECE_WIGNER_BWD: tece_wigner_bwd_kernel<T><<<(unsigned)((a.E + 63) / 64), 64, 0, s>>>(a, a.accumulate_gvec); break;
     default: err = cudaErrorInvalidValue;
   }
