@@ -63,3 +63,29 @@ def test_unsupported_options_are_refused_loudly(override, needle):
     with pytest.raises(NotImplementedError) as err:
         check_model_config({k: v for k, v in cfg.items()})
     assert needle in str(err.value)
+
+
+def test_tece_configuration_builds_with_reference_parameter_names():
+    """atomic_basis.type = [cgtp, uv_so2]: accepted, parameters of the edge block named and shaped like the reference's
+    (tace/models/_e3nn/archive/oam_2026_07_05.py:612-697), and the matching oracle loads the same state_dict."""
+    from oracle.model import build_oracle
+
+    cfg = synth.model_config(3, 32, 5.0, [1, 8], 20.0, gate_m0=False, radial={"apply_cutoff": False},
+                             tece={"num_head": 4, "edge_ace_hidden": 8, "mmax": 2})
+    torch.manual_seed(0)
+    model = create_model(cfg)
+    sd = model.state_dict()
+    pre = "readout_fn.representation.interactions.1."
+    n, C, Ca = 4, 32, 8
+    assert sd[pre + "rejector.linear_up.m0_rlinear.weight"].shape == ((2 * n + n) * Ca, n * 2 * C)  # gates for m = 1, 2 + features
+    assert sd[pre + "rejector.linear_up.ms_clinear.1.fc.weight"].shape == (n * Ca, (n - 2) * 2 * C)
+    assert sd[pre + "rejector.linear_coefs.m0_rlinear.weight"].shape == (7 * n * Ca, n * 2 * C)       # 7 cluster paths for mmax = 2
+    assert sd[pre + "rejector.linear_down.ms_clinear.0.fc.weight"].shape == ((n - 1) * C, n * Ca)
+    assert sd[pre + "rejector.key_proj.m0_rlinear.bias"].shape == (n * C,)
+    assert sd[pre + "rejector.radial_proj.weight"].shape == (8, 8) and sd[pre + "rejector.temperature_logit"].shape == (4,)
+    assert sd[pre + "edge_info.mlp.6.weight"].shape == (64, (4 + 3 + 2) * 2 * C)                      # one weight per (row, source | target channel)
+    assert sd[pre + "linear_down.weight"].numel() == (3 + 1) * C * C + 3 * C * C                      # one C-block per rank in
+    build_oracle(cfg, sd, torch.float64)  # raises on any missing or mis-shaped name
+    for bad in ({"Lmax": 2}, {"mmax": 3}):
+        with pytest.raises(NotImplementedError):
+            check_model_config({**cfg, **bad})

@@ -158,3 +158,24 @@ def test_torchsim_model_matches_oracle_and_reuses_cached_setup():
     state.atomic_numbers[0] = 7
     with pytest.raises(ValueError):
         calc(state)
+
+
+def test_lammps_mliap_with_the_tece_edge_block():
+    """Edge-vector mode with ghost atoms for a model whose second interaction is the TECE edge block: ghost features arrive
+    through the forward exchange, the gradients of ghost sources go back through the reverse exchange, and the gradient
+    through the edge frames is part of the pair forces."""
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=6, species=(13, 29), fractions=(0.5, 0.5))
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, radial={"apply_cutoff": False},
+                                     tece={"num_head": 4, "edge_ace_hidden": 8, "mmax": 2})
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64), compute_stress=False)
+    dev = torch.device("cuda:0")
+    data = FakeLammpsData(s, 4.0, [13, 29], dev)
+    calc = TACELammpsCalc(model)
+    calc.compute_forces(data)
+    n = data.nlocal
+    assert abs(data.energy - ref["energy"].item()) < 1e-8 * n
+    f = torch.zeros(data.ntotal, 3, dtype=torch.float64, device=dev)
+    f.index_add_(0, data.pair_i.long(), -data.pair_forces)
+    f.index_add_(0, data.pair_j.long(), data.pair_forces)
+    f[:n].index_add_(0, data.owner, f[n:])
+    assert (f[:n].cpu() - ref["forces"]).abs().max().item() < 1e-7
