@@ -308,18 +308,22 @@ __global__ void __launch_bounds__(128) tece_rotate_in_bwd_t_kernel(const TeceArg
   const long long e = idx / a.C;
   constexpr int D = (L + 1) * (L + 1), NR = RowCount<L, MM>::NR, NC = (L + 1) + (MM >= 1 ? L : 0) + (MM >= 2 ? L - 1 : 0);
   const int c = (int)(idx - e * a.C), C = a.C;
-  const T* Wg = a.Wg + e * NR * D;
+  const T* __restrict__ Wg = a.Wg + e * NR * D;
   T* W = a.W + e * NC * 2 * C;
   T gs[D], gt[D], dws[NC], dwt[NC], ws[NC], wt[NC];
 #pragma unroll
   for (int j = 0; j < D; ++j) { gs[j] = T(0); gt[j] = T(0); }
 #pragma unroll
   for (int k = 0; k < NC; ++k) { dws[k] = T(0); dwt[k] = T(0); ws[k] = W[k * 2 * C + c]; wt[k] = W[k * 2 * C + C + c]; }
+  // read-only inputs through restrict pointers: the stores of the totals below must not hold back the next rows' loads
+  const T* __restrict__ gMw = a.gMw;
+  const T* __restrict__ Ksp = a.Ks;
+  const T* __restrict__ Qtp = a.Qt;
   for_rows<L, MM>([&](int r, int l, int comp) {
     const long long at = (e * NR + r);
-    const T gms = a.gMw[at * 2 * C + c], gmt = a.gMw[at * 2 * C + C + c];
-    dws[comp] += gms * a.Ks[at * C + c];
-    dwt[comp] += gmt * a.Qt[at * C + c];
+    const T gms = gMw[at * 2 * C + c], gmt = gMw[at * 2 * C + C + c];
+    dws[comp] += gms * Ksp[at * C + c];
+    dwt[comp] += gmt * Qtp[at * C + c];
     const T gks = a.gKs[at * C + c] + ws[comp] * gms;
     const T gqt = a.gQt[at * C + c] + wt[comp] * gmt;
     a.gKs[at * C + c] = gks;
@@ -708,6 +712,14 @@ TACE_HD constexpr int mix_path_id(int mm, int m3, int m1, int m2) {  // position
       }
   return -1;
 }
+TACE_HD constexpr int mix_path_count(int mm) {
+  int p = 0;
+  for (int q3 = 0; q3 <= mm; ++q3)
+    for (int q1 = 0; q1 <= mm; ++q1)
+      for (int q2 = 0; q2 <= q1; ++q2)
+        if (q1 + q2 == q3 || q1 - q2 == q3) ++p;
+  return p;
+}
 template <typename T, int N, int MM, bool GATE_M0, bool BWD>
 __global__ void __launch_bounds__(64) tece_mix_t_kernel(const TeceArgs<T> a) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -724,6 +736,12 @@ __global__ void __launch_bounds__(64) tece_mix_t_kernel(const TeceArgs<T> a) {
   for (int r = 0; r < G; ++r) gz[r] = up[(long long)r * Ca];
 #pragma unroll
   for (int r = 0; r < NF; ++r) { x[r] = up[(long long)(G + r) * Ca]; y[r] = glu[(long long)r * Ca]; out[r] = x[r]; }
+  // every input is in registers before the first store: the gradients overwrite their forward buffers, so a load issued
+  // after a store would have to wait for it
+  constexpr int NW = mix_path_count(MM) * N;
+  T cz[NW];
+#pragma unroll
+  for (int k = 0; k < NW; ++k) cz[k] = cf[(long long)k * Ca];
   T gx[NF], gy[NF], gg[G > 0 ? G : 1], go[NF];
   T* gcf = nullptr;
   if (BWD) {
@@ -766,8 +784,8 @@ __global__ void __launch_bounds__(64) tece_mix_t_kernel(const TeceArgs<T> a) {
                   o_re = (m3 == 0 ? 0 : N + (m3 - 1) * 2 * N);
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-          const T cz = cf[(long long)(p * N + i) * Ca];
-          const T w = act_eval<T>(a.act, cz) * sc;
+          const T czv = cz[p * N + i];
+          const T w = act_eval<T>(a.act, czv) * sc;
           const T xr = x[x_re + i], xi = m1 ? x[x_re + (m1 ? N : 0) + i] : T(0);
           const T yr = y[y_re + i], yi = m2 ? y[y_re + (m2 ? N : 0) + i] : T(0);
           T zr, zi;
@@ -777,7 +795,7 @@ __global__ void __launch_bounds__(64) tece_mix_t_kernel(const TeceArgs<T> a) {
           if (m3) out[o_re + (m3 ? N : 0) + i] += w * zi;
           if (BWD) {
             const T gr = go[o_re + i], gi = m3 ? go[o_re + (m3 ? N : 0) + i] : T(0);
-            gcf[(long long)(p * N + i) * Ca] = (gr * zr + gi * zi) * sc * act_grad<T>(a.act, cz);
+            gcf[(long long)(p * N + i) * Ca] = (gr * zr + gi * zi) * sc * act_grad<T>(a.act, czv);
             const T ar = w * gr, ai = w * gi;
             if (sum_mode) {
               gx[x_re + i] += ar * yr + ai * yi;
