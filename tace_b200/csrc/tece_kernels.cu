@@ -282,8 +282,8 @@ __global__ void __launch_bounds__(128) tece_rotate_in_t_kernel(const TeceArgs<T>
   const int c = (int)(idx - e * a.C), C = a.C;
   const T* xs = a.x + (long long)a.e_src[e] * D * C + c;
   const T* xt = a.x + (long long)a.e_dst[e] * D * C + c;
-  const T* Wg = a.Wg + e * NR * D;
-  const T* W = a.W + e * a.NC * 2 * C;
+  const T* __restrict__ Wg = a.Wg + e * NR * D;
+  const T* __restrict__ W = a.W + e * a.NC * 2 * C;
   T vs[D], vt[D];
 #pragma unroll
   for (int j = 0; j < D; ++j) { vs[j] = xs[(long long)j * C]; vt[j] = xt[(long long)j * C]; }
@@ -507,8 +507,8 @@ __global__ void tece_logit_lane_kernel(const TeceArgs<T> a) {
   const int c = (int)(idx - e * a.C), C = a.C, Ch = C / a.H, h = c / Ch, n0 = a.L + 1;
   const T th = tanh(a.proj[e * 2 * a.H + a.H + h]);
   const T phase = T(3.141592653589793) * th;
-  const T* q = a.Qp + e * a.NR * C + c;
-  const T* k = a.Kp + e * a.NR * C + c;
+  const T* __restrict__ q = a.Qp + e * a.NR * C + c;
+  const T* __restrict__ k = a.Kp + e * a.NR * C + c;
   T gs = T(0);
   T* gq = nullptr; T* gk = nullptr;
   if (BWD) { gs = a.glogit[e * a.H + h] * a.temp[h]; gq = a.gQp + e * a.NR * C + c; gk = a.gKp + e * a.NR * C + c; }
@@ -868,8 +868,9 @@ __global__ void tece_rotate_out_bwd_kernel(const TeceArgs<T> a) {
   const long long e = idx / a.C;
   const int c = (int)(idx - e * a.C), C = a.C, D = (a.L + 1) * (a.L + 1), h = c / (C / a.H);
   const T al = a.alpha[e * a.H + h];
-  const T* Wg = a.Wg + e * a.NR * D;
-  const T* gM = a.gM + (long long)a.e_dst[e] * D * C + c;
+  const T* __restrict__ Wg = a.Wg + e * a.NR * D;
+  const T* __restrict__ gM = a.gM + (long long)a.e_dst[e] * D * C + c;
+  const T* __restrict__ down = a.down;
   T part = T(0);
   for (int r = 0; r < a.NR; ++r) {
     const int l = a.row_l[r], dl = 2 * l + 1;
@@ -877,7 +878,7 @@ __global__ void tece_rotate_out_bwd_kernel(const TeceArgs<T> a) {
     for (int j = 0; j < dl; ++j) t += Wg[r * D + l * l + j] * gM[(long long)(l * l + j) * C];
     t *= a.row_scale[r];
     a.gdown[(e * a.NR + r) * C + c] = al * t;
-    if (FUSE) part += a.down[(e * a.NR + r) * C + c] * t;
+    if (FUSE) part += down[(e * a.NR + r) * C + c] * t;
   }
   if (FUSE) {
     const int Ch = C / a.H;
