@@ -176,6 +176,8 @@ def cpu_sample(structures, wl, dtype, state_dict, budget_s: float, evals: int):
     torch.set_num_threads(cores)
     cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"], **wl.get("model", {}))
     oracle = build_oracle(cfg, state_dict, dtype)
+    if wl.get("cpu_sample"):  # one large structure: the CPU leg takes a smaller cell of the same material
+        structures = synth.workload_structures(wl["cpu_sample"])
     order = sorted(range(len(structures)), key=lambda i: len(structures[i]["positions"]))
     probe = [structures[order[0]]]
     data = oracle_batch(probe, wl["elements"], wl["cutoff"], dtype)
@@ -211,7 +213,8 @@ def run_reference(args, rank, world):
         oracle(data)
     dt = time.perf_counter() - t0
     value = n_atoms * args.steps / dt
-    sample = f"{n_struct} smallest crystals of the batch ({n_atoms} atoms, {data['edge_index'].shape[1]} edges) per step"
+    what = f"a smaller cell of the same material ({wl['cpu_sample']})" if wl.get("cpu_sample") else f"{n_struct} smallest crystals of the batch"
+    sample = f"{what} ({n_atoms} atoms, {data['edge_index'].shape[1]} edges) per step"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -461,7 +464,20 @@ def main():
         with open(tpath) as fh:
             traffic = json.load(fh).get(f"{args.workload}:{top}")
     ab = algorithmic_bytes(top, dims)
-    if ab is not None:
+    layer = int(top[1]) if top[1].isdigit() else 0
+    if ".tp" in top and layer in plan.tece_layers:
+        # the TECE edge block is bound by its SO(2) linears: 2 * rows * K * N per order block and edge, the same count
+        # again for the input gradients of the backward pass; fp32 models run them as three TF32 products each
+        fl = 0.0
+        for _ref, _name, ci, co, n_in, n_out in plan.so2_linears():
+            fl += sum(2.0 * (1 if m == 0 else 2) * n_in[m] * ci * n_out[m] * co for m in range(len(n_in)))
+        fl *= n_edges
+        achieved = fl / (phases[top] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": top + " (edge block: SO(2) GEMMs and their element-wise kernels)", "achieved": achieved,
+                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops"], "traffic": None,
+                    "peak_source": pk["source"], "flops_per_launch": fl, "ms_per_launch": phases[top],
+                    "note": "useful FP32 FLOPs of the SO(2) linears over the whole phase; every one costs three TF32 tensor-core FLOPs"}
+    elif ab is not None:
         achieved = ab / (phases[top] * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "peak_source": pk["source"],
@@ -482,7 +498,8 @@ def main():
             oracle(cdata)
         dt = (time.perf_counter() - t0) / 2
         cpu = {"value": c_atoms / dt, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": f"{c_struct} smallest crystals of the batch ({c_atoms} atoms, {cdata['edge_index'].shape[1]} edges), "
+               "sample": (f"a smaller cell of the same material ({wl['cpu_sample']})" if wl.get("cpu_sample")
+                          else f"{c_struct} smallest crystals of the batch") + f" ({c_atoms} atoms, {cdata['edge_index'].shape[1]} edges), "
                          f"2 timed evaluations of the PyTorch CPU restatement with autograd forces"}
 
     print(json.dumps({

@@ -188,6 +188,7 @@ WORKLOADS = {
     "cual1m_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
     # BASELINE config 4: the TECE model of the reference's example/train/tece.yaml at L = 3, C = 128 on a five-component BCC alloy
     "tece8192_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[23, 24, 26, 27, 28], avg_num_neighbors=64.0, dtype="float32",
+                          cpu_sample="tece1024_fp32",
                           model=dict(gate_m0=False, edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},
                                      resnet_linear_type="identity", product_agnostic=True, product_nonlinear="silu_bilineargate",
                                      tece={"num_head": 8, "edge_ace_hidden": 32, "mmax": 2})),
@@ -213,6 +214,8 @@ def workload_structures(name: str) -> List[Structure]:
         return [water_box()]
     if name == "tece8192_fp32":
         return [bcc_supercell(16, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))]
+    if name == "tece1024_fp32":  # 8 x 8 x 8 cells: the CPU baseline's sample of configuration 4
+        return [bcc_supercell(8, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))]
     if name == "tece128_fp32":
         return [bcc_supercell(4, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))]
     if name in MD_WORKLOADS:
