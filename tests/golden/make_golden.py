@@ -23,7 +23,35 @@ from oracle.neighbour_list import neighbour_list  # noqa: E402
 from tace_b200 import synth  # noqa: E402
 
 
+def store_case(name, structure, elements, cutoff, dtype_weights=np.float32, **model_kw):
+    """One model case with its weights (rounded to fp32) and the oracle's fp64 outputs for those weights; the model
+    configuration travels as JSON so that the loader needs no per-case code."""
+    import json
+
+    from oracle.model import build_oracle
+    model, _, cfg = make_models(model_kw.pop("L"), model_kw.pop("C"), elements, cutoff, 20.0, torch.float64, seed=0, **model_kw)
+    data = oracle_batch([structure], elements, cutoff, torch.float64)
+    sd = {k: v.numpy().astype(dtype_weights if v.is_floating_point() else np.int64) for k, v in model.state_dict().items()}
+    sd64 = {k: torch.from_numpy(v.astype(np.float64) if v.dtype == dtype_weights else v) for k, v in sd.items()}
+    ref = build_oracle(cfg, sd64, torch.float64)(data)
+    np.savez_compressed(os.path.join(HERE, name), positions=structure["positions"], cell=structure["cell"],
+                        atomic_numbers=structure["atomic_numbers"], cutoff=cutoff, avg_num_neighbors=20.0,
+                        elements=np.asarray(elements), cfg_json=np.array(json.dumps(cfg)),
+                        energy=ref["energy"].numpy(), forces=ref["forces"].numpy(), stress=ref["stress"].numpy(),
+                        node_energy=ref["node_energy"].numpy(), **{"sd:" + k: v for k, v in sd.items()})
+
+
+def tece_case():
+    # --- model case B: cgtp layer + TECE edge block (two species, BCC 2 x 2 x 2), weights stored
+    s = synth.bcc_supercell(2, 2.87, 0.08, seed=3, species=(26, 28))
+    store_case("case_bcc16_tece_L2_C32.npz", s, [26, 28], 4.0, L=2, C=32, radial={"apply_cutoff": False},
+               tece={"num_head": 4, "edge_ace_hidden": 8, "mmax": 2})
+
+
 def main():
+    if "--tece-only" in sys.argv:
+        tece_case()
+        return
     # --- conventions: Wigner 3j, spherical harmonics, activation constants
     tables = {"activation_constants_reference": np.array([1.6791767923989418, 1.8467055342154763, 1.5937334472592695])}
     for l1 in range(4):
@@ -62,6 +90,7 @@ def main():
     ei, es = neighbour_list(t["positions"], t["cell"], t["pbc"], 6.0)
     np.savez_compressed(os.path.join(HERE, "neighbour_list_triclinic5.npz"), positions=t["positions"], cell=t["cell"],
                         cutoff=6.0, edge_index=ei, edge_shifts=es)
+    tece_case()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 

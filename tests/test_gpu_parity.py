@@ -103,11 +103,13 @@ def test_edge_vector_mode_matches_graph_mode():
     assert (out["forces"].cpu() - ref["forces"]).abs().max().item() < 1e-7
 
 
-def test_golden_model_case():
-    """The committed golden vectors (tests/golden/case_fcc32_L2_C32.npz), fp64 and fp32."""
+@pytest.mark.parametrize("case", ["case_fcc32_L2_C32.npz", "case_bcc16_tece_L2_C32.npz"])
+def test_golden_model_case(case):
+    """The committed golden vectors (tests/golden/): the cgtp model and the one with the TECE edge block, fp64 and fp32."""
     import tace_b200
     from golden_util import load_case
-    blob, sd, cfg, s = load_case()
+    blob, sd, cfg, s = load_case(case)
+    elements = [int(z) for z in blob["elements"]] if "elements" in blob else [29]
     for dtype in (torch.float64, torch.float32):
         prev = torch.get_default_dtype()
         torch.set_default_dtype(dtype)
@@ -117,7 +119,7 @@ def test_golden_model_case():
             torch.set_default_dtype(prev)
         own = model.state_dict()
         model.load_state_dict({k: sd[k].to(own[k].dtype) for k in own})
-        data = to_device(oracle_batch([s], [29], float(blob["cutoff"]), dtype), torch.device("cuda:0"))
+        data = to_device(oracle_batch([s], elements, float(blob["cutoff"]), dtype), torch.device("cuda:0"))
         out = model(data)
         etol, ftol = TOL[dtype]
         n = len(s["positions"])

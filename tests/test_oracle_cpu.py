@@ -64,6 +64,16 @@ def test_oracle_reproduces_golden_model_case():
     np.testing.assert_allclose(ref["stress"].numpy(), blob["stress"], rtol=0, atol=1e-10)
 
 
+def test_oracle_reproduces_golden_tece_case():
+    """The stored case with the TECE edge block (tests/golden/case_bcc16_tece_L2_C32.npz)."""
+    blob, sd, cfg, s = load_case("case_bcc16_tece_L2_C32.npz")
+    oracle = build_oracle(cfg, sd, torch.float64)
+    ref = oracle(oracle_batch([s], [int(z) for z in blob["elements"]], float(blob["cutoff"]), torch.float64))
+    np.testing.assert_allclose(ref["energy"].numpy(), blob["energy"], rtol=0, atol=1e-9)
+    np.testing.assert_allclose(ref["forces"].numpy(), blob["forces"], rtol=0, atol=1e-10)
+    np.testing.assert_allclose(ref["stress"].numpy(), blob["stress"], rtol=0, atol=1e-10)
+
+
 def test_oracle_neighbour_list_golden():
     g = np.load(os.path.join(GOLDEN, "neighbour_list_triclinic5.npz"))
     ei, es = neighbour_list(g["positions"], g["cell"], (True, True, True), float(g["cutoff"]))
