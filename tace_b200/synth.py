@@ -186,7 +186,7 @@ WORKLOADS = {
                             dtype="float32"),
     "water32400_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32"),
     "cual1m_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
-    # BASELINE config 4: the TECE model of the reference's example/train/tece.yaml at L = 3, C = 128 on a five-component BCC alloy
+    # benchmark configuration 4: the TECE model of the reference's example/train/tece.yaml at L = 3, C = 128 on a five-component BCC alloy
     "tece8192_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[23, 24, 26, 27, 28], avg_num_neighbors=64.0, dtype="float32",
                           cpu_sample="tece1024_fp32",
                           model=dict(gate_m0=False, edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},

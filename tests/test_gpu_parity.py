@@ -425,7 +425,7 @@ def test_tece_edge_block(L, mmax, gate_m0, radial, num_layers):
 
 
 def test_tece_example_configuration_small():
-    """The model of BASELINE configuration 4 (the reference's example TECE file: cgtp then uv_so2, element-dependent edge
+    """The model of benchmark configuration 4 (the reference's example TECE file: cgtp then uv_so2, element-dependent edge
     update with LayerNorm, envelope after a biased two-layer radial MLP, e3nn gate, identity skip, species-agnostic gated
     bilinear product) at 32 channels on a small five-component BCC cell, fp64 and fp32; repeated calls replay a CUDA graph."""
     s = synth.bcc_supercell(2, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))
