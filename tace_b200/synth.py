@@ -192,7 +192,12 @@ WORKLOADS = {
                           model=dict(gate_m0=False, edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},
                                      resnet_linear_type="identity", product_agnostic=True, product_nonlinear="silu_bilineargate",
                                      tece={"num_head": 8, "edge_ace_hidden": 32, "mmax": 2})),
-    # the same model on 4 x 4 x 4 cells, for profiler captures and quick checks
+    # the same model on 8 x 8 x 8 cells (1 024 atoms, 65 770 edges, about 8 GB on the device): profiler captures, CPU baseline
+    "tece1024_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[23, 24, 26, 27, 28], avg_num_neighbors=64.0, dtype="float32",
+                          model=dict(gate_m0=False, edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},
+                                     resnet_linear_type="identity", product_agnostic=True, product_nonlinear="silu_bilineargate",
+                                     tece={"num_head": 8, "edge_ace_hidden": 32, "mmax": 2})),
+    # the same model on 4 x 4 x 4 cells, for quick checks
     "tece128_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[23, 24, 26, 27, 28], avg_num_neighbors=64.0, dtype="float32",
                          model=dict(gate_m0=False, edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]},
                                     resnet_linear_type="identity", product_agnostic=True, product_nonlinear="silu_bilineargate",
