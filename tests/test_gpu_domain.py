@@ -37,6 +37,21 @@ def test_single_rank_domain_matches_oracle(num_layers):
     assert model.device_error() == 0
 
 
+def test_single_rank_domain_with_the_tece_edge_block():
+    """The same check for a model whose second interaction is the TECE edge block: ghost features through the exchange,
+    gradients of ghost sources back through it, the edge-frame gradient inside the forces."""
+    s = _system(seed=8)
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"),
+                                     radial={"apply_cutoff": False}, tece={"num_head": 4, "edge_ace_hidden": 8, "mmax": 2})
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64))
+    md = DomainMD(model.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], skin=0.4, device=DEV)
+    assert md.domain.n_ghost > 0
+    got = md.gather()
+    assert abs(md.potential() - float(ref["energy"][0])) / len(s["positions"]) < 1e-8
+    assert np.abs(got["forces"] - ref["forces"].detach().numpy()).max() < 1e-7
+    assert model.device_error() == 0
+
+
 def test_md_support_kernels_match_torch():
     lib = _lib.load()
     g = torch.Generator(device="cpu").manual_seed(0)

@@ -447,3 +447,40 @@ def test_tece_edge_block_wide_head():
     """One head over 64 channels: wider than a warp, so the attention kernels take their per-(edge, head) form."""
     structs = synth.random_crystals(2, seed=35, nmin=4, nmax=8, zmax=3)
     run_case(structs, 2, 64, [1, 2, 3], 4.0, torch.float64, radial={"apply_cutoff": False}, tece={"num_head": 1, "edge_ace_hidden": 8, "mmax": 2})
+
+
+def test_full_size_properties_config4():
+    """Benchmark configuration 4 at full size (TECE model, 8 192 atoms, 526 k edges, L = 3, 128 channels, fp32): properties
+    that need no oracle - net force ~ 0, run-to-run bit reproducibility (graph replay included), energy and forces unchanged
+    by a rigid shift of all atoms and by a permutation of the edge list."""
+    import tace_b200
+    from tace_b200.graph import build_batch
+    wl = synth.WORKLOADS["tece8192_fp32"]
+    structs = synth.workload_structures("tece8192_fp32")
+    cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"], **wl["model"])
+    torch.manual_seed(0)
+    model = tace_b200.TensorModel(tace_b200.e3nnTACE(**cfg))
+    dev = torch.device("cuda:0")
+    data = build_batch(synth.collate(structs), wl["elements"], wl["cutoff"], torch.float32, dev)
+    a = model(data)
+    b = model(data)
+    c = model(data)
+    assert model.device_error() == 0
+    for other in (b, c):
+        assert torch.equal(a["energy"], other["energy"]) and torch.equal(a["forces"], other["forces"])
+    n = a["forces"].shape[0]
+    fscale = a["forces"].abs().max().item()
+    assert torch.isfinite(a["forces"]).all() and fscale > 0
+    assert a["forces"].sum(0).abs().max().item() <= 1e-5 * n * max(1.0, fscale)
+    shifted = dict(data, positions=data["positions"] + torch.tensor([0.31, -0.27, 0.19], device=dev, dtype=data["positions"].dtype))
+    d = model(shifted)
+    assert abs(d["energy"].item() - a["energy"].item()) / n <= 1e-5 * max(1.0, abs(a["energy"].item()) / n)
+    assert (d["forces"] - a["forces"]).abs().max().item() <= 1e-4 * max(1.0, fscale)
+    perm = torch.randperm(data["edge_index"].shape[1], device=dev)
+    shuffled = dict(data, edge_index=data["edge_index"][:, perm].contiguous(), edge_shifts=data["edge_shifts"][perm].contiguous())
+    e = model(shuffled)
+    assert abs(e["energy"].item() - a["energy"].item()) / n <= 1e-5 * max(1.0, abs(a["energy"].item()) / n)
+    assert (e["forces"] - a["forces"]).abs().max().item() <= 1e-4 * max(1.0, fscale)
+    model.release()
+    del model
+    torch.cuda.empty_cache()
