@@ -149,7 +149,7 @@ class TensorProduct(torch.nn.Module):
                 o = torch.einsum("zu,ijk,zui,zuj->zuk", wk, c, a, b)
             else:  # uuu, no weights
                 o = torch.einsum("ijk,zui,zuj->zuk", c, a, b)
-            outs.append(o.reshape(n, -1))
+            outs.append(o.reshape(n, m1 * (2 * l3 + 1)))  # explicit width: n may be 0 (a batch without edges)
         return torch.cat(outs, dim=-1)
 
 

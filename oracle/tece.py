@@ -358,6 +358,8 @@ class EdgeConvolution(torch.nn.Module):
 
     def forward(self, x, w, edge_index, cutoff, wigner, wigner_inv, radial_basis):
         N, E = x.shape[0], w.shape[0]
+        if E == 0:  # no edge, no message (the sums below are empty)
+            return x.new_zeros(N, x.shape[1], self.hidden)
         m_ij = torch.cat((x[edge_index[0]], x[edge_index[1]]), dim=-1)  # source | target channels
         m_ij = torch.bmm(wigner, m_ij)
         key = self.key_proj(m_ij[:, :, :self.C])

@@ -963,6 +963,10 @@ cudaError_t launch_tece(const TeceArgs<T>& a, int stage, cudaStream_t s) {
   if (a.L > 3 || a.mmax > 2 || a.NR > 16 || a.NC > 9 || a.H > 16 || a.G > 12 || a.n_paths * (a.L + 1) > 28 || a.C % a.H != 0)
     return cudaErrorInvalidValue;
   cudaError_t err = cudaSuccess;
+  // nothing to launch: stages over atoms need local atoms, every other stage needs edges (an atom without edges still gets
+  // its zero message from TECE_ROTATE_OUT)
+  const bool per_atom = stage == TECE_SOFTMAX || stage == TECE_ROTATE_OUT || stage == TECE_SOFTMAX_BWD || stage == TECE_TARGET_SUM;
+  if (per_atom ? a.n_local <= 0 : a.E <= 0) return cudaSuccess;
   const int ch = a.C / a.H;
   const bool fuse_alpha = a.C % 32 == 0 && ch <= 32 && (ch & (ch - 1)) == 0;
   switch (stage) {

@@ -79,6 +79,19 @@ def test_isolated_atom_and_empty_graph_edges():
     assert out["forces"][0].abs().max().item() == 0.0
 
 
+def test_isolated_atom_with_the_tece_edge_block():
+    """The same batch through a model with the TECE edge block, and a batch that holds nothing but the lone atom (no edge
+    at all: every per-edge stage has nothing to launch)."""
+    lone = synth.Structure(positions=np.zeros((1, 3)), atomic_numbers=np.array([29]), cell=np.eye(3) * 30.0,
+                           pbc=(True, True, True))
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=0)
+    kw = dict(radial={"apply_cutoff": False}, tece={"num_head": 4, "edge_ace_hidden": 8, "mmax": 2})
+    out, ref = run_case([lone, s], 2, 32, [29], 4.0, torch.float64, **kw)
+    assert out["forces"][0].abs().max().item() == 0.0
+    out, ref = run_case([lone], 2, 32, [29], 4.0, torch.float64, **kw)
+    assert out["forces"].abs().max().item() == 0.0
+
+
 def test_input_not_mutated_and_repeatable():
     s = synth.fcc_supercell(2, 3.61, 0.05, seed=0)
     model, oracle, cfg = make_models(2, 32, [29], 4.0, 20.0, torch.float32)
