@@ -129,3 +129,20 @@ def test_model_with_the_edge_block_is_invariant_and_smooth():
             p[atom, axis] += sign * h
             e.append(float(oracle(oracle_batch([dict(s, positions=p)], [13, 29], 4.0, torch.float64))["energy"][0]))
         assert abs(-(e[0] - e[1]) / (2 * h) - float(ref["forces"][atom, axis])) < 1e-6
+
+
+def test_full_order_wigner_rows_invert_exactly():
+    """With every order kept (mmax == lmax) the inverse map undoes the rotation, as the reference's own round-trip test
+    requires of WignerD(2, 2) (tests/test_o2.py:62-100); with mmax < lmax the product is the projector on the kept orders
+    up to the sqrt((2l+1) / (2 mmax+1)) rescale of the higher ranks."""
+    g = torch.Generator().manual_seed(11)
+    v = torch.randn(7, 3, generator=g, dtype=torch.float64)
+    wig, wig_inv = tece.WignerD(2, 2).get_wigner(v)
+    assert wig.shape == (7, 9, 9)
+    assert torch.allclose(torch.bmm(wig_inv, wig), torch.eye(9, dtype=torch.float64).expand(7, 9, 9), atol=1e-6)
+    x = torch.randn(7, 9, generator=g, dtype=torch.float64)
+    assert torch.allclose(torch.einsum("eij,ej->ei", wig_inv, torch.einsum("eij,ej->ei", wig, x)), x, atol=1e-6)
+    wig, wig_inv = tece.WignerD(2, 3).get_wigner(v)
+    prod = torch.bmm(wig, wig_inv)  # [14, 14]: rows of an orthogonal matrix times their rescaled transpose
+    scale = torch.where(tece.m_layout(3, 2)[1] > 2, (7.0 / 5.0) ** 0.5, 1.0).to(torch.float64)
+    assert torch.allclose(prod, torch.diag(scale).expand(7, 14, 14), atol=1e-6)
