@@ -513,12 +513,16 @@ class TensorModel(torch.nn.Module):
                 # 80 % of the memory this model may use, otherwise halve the chunk size until it does
                 free, _total = torch.cuda.mem_get_info(device)
                 budget = 0.8 * (free + (self._workspace.numel() if self._workspace is not None else 0))
-                for limit in (max(E, 1 << 21), 1 << 22, 1 << 21, 1 << 20, 1 << 19, 1 << 18):
+                whole_only = bool(self.readout_fn.plan.tece_layers)  # the TECE edge block is evaluated on the whole batch only
+                for limit in ((max(E, 1 << 21),) if whole_only else (max(E, 1 << 21), 1 << 22, 1 << 21, 1 << 20, 1 << 19, 1 << 18)):
                     if limit != self._auto_chunk:
                         _lib.check(lib.tace_set_chunk_edges(handle, int(limit)), "tace_set_chunk_edges")
                         self._auto_chunk = limit
                     if needed() <= budget or limit == 1 << 18:
                         break
+                    if whole_only:
+                        raise _lib.TaceError(f"tace_b200: this batch needs {needed() / 2**30:.1f} GiB of workspace with the TECE edge block "
+                                             f"(all per-edge tensors resident), {budget / 2**30:.1f} GiB are available; use smaller batches")
             needed()
             ws = self._get_workspace(nbytes.value, device)
             ws_ptr = (ws.data_ptr() + 255) & ~255
