@@ -179,3 +179,29 @@ def test_lammps_mliap_with_the_tece_edge_block():
     f.index_add_(0, data.pair_j.long(), data.pair_forces)
     f[:n].index_add_(0, data.owner, f[n:])
     assert (f[:n].cpu() - ref["forces"]).abs().max().item() < 1e-7
+
+
+@pytest.mark.parametrize("kw", [
+    dict(zbl={"enable": True, "covalent_radii": {13: 1.5, 29: 1.6}}, scatter_norm="density"),
+    dict(edge_update="element2", radial={"apply_cutoff": False, "bias": True, "hidden": [64, 64]}, gate_m0=False, use_alllayer=True),
+    dict(product_nonlinear="silu_bilineargate", product_agnostic=True, resnet_linear_type="identity", correlation=2),
+])
+def test_lammps_mliap_with_model_options(kw):
+    """Edge-vector mode with ghost atoms for the model options beyond the default: pair repulsion and learned edge density
+    (sums over the edges into local atoms, species of ghost sources), element-dependent edge update with LayerNorm, gated
+    bilinear product with identity skip."""
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=10, species=(13, 29), fractions=(0.5, 0.5))
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, **kw)
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64), compute_stress=False)
+    dev = torch.device("cuda:0")
+    data = FakeLammpsData(s, 4.0, [13, 29], dev)
+    calc = TACELammpsCalc(model)
+    calc.compute_forces(data)
+    n = data.nlocal
+    assert abs(data.energy - ref["energy"].item()) < 1e-8 * n
+    assert (data.eatoms.cpu() - ref["node_energy"]).abs().max().item() < 1e-8
+    f = torch.zeros(data.ntotal, 3, dtype=torch.float64, device=dev)
+    f.index_add_(0, data.pair_i.long(), -data.pair_forces)
+    f.index_add_(0, data.pair_j.long(), data.pair_forces)
+    f[:n].index_add_(0, data.owner, f[n:])
+    assert (f[:n].cpu() - ref["forces"]).abs().max().item() < 1e-7
