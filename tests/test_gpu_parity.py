@@ -208,15 +208,21 @@ def test_graph_replay_is_bit_identical_and_follows_new_inputs(dtype):
     assert model.device_error() == 0
 
 
-@pytest.mark.parametrize("dtype,num_layers", [(torch.float64, 2), (torch.float64, 3), (torch.float32, 2)])
-def test_edge_chunked_pass_matches_the_whole_pass(dtype, num_layers):
+@pytest.mark.parametrize("dtype,num_layers,kw", [
+    (torch.float64, 2, {}), (torch.float64, 3, {}), (torch.float32, 2, {}),
+    (torch.float64, 2, dict(zbl={"enable": True, "covalent_radii": {13: 1.5, 29: 1.6}}, scatter_norm="density", num_fidelities=2)),
+    (torch.float64, 3, dict(product_nonlinear="silu_bilineargate", resnet_linear_type="identity", edge_update="element2")),
+])
+def test_edge_chunked_pass_matches_the_whole_pass(dtype, num_layers, kw):
     """Chunks of target atoms with recomputed per-edge tensors (the mode used when a system's per-edge tensors
     do not fit) must give the whole-batch results up to the order of the per-source sums."""
     structs = [synth.fcc_supercell(4, 3.61, 0.05, seed=2, species=(13, 29), fractions=(0.4, 0.6)),
                synth.fcc_supercell(3, 3.61, 0.05, seed=3, species=(13, 29), fractions=(0.5, 0.5))]
-    model, oracle, cfg = make_models(2, 32, [13, 29], 5.0, 40.0, dtype, num_layers=num_layers)
+    model, oracle, cfg = make_models(2, 32, [13, 29], 5.0, 40.0, dtype, num_layers=num_layers, **kw)
     dev = torch.device("cuda:0")
     data = to_device(oracle_batch(structs, [13, 29], 5.0, dtype), dev)
+    if kw.get("num_fidelities"):
+        data["fidelity_idx"] = torch.tensor([1, 0], device=dev)
     n_edges = data["edge_index"].shape[1]
     whole = {k: v.clone() for k, v in model(data).items() if v is not None}
     model.set_chunk_edges(2048)
