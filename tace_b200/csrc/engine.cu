@@ -1057,6 +1057,33 @@ struct Model : ModelBase {
     const bool need_grad = o->forces || o->virials || o->stress || o->edge_forces;
 
     phase_used = 0;
+    if (NL == 0) {
+      // A rank that owns no atom (a block of vacuum in a domain decomposition): nothing to evaluate, results are
+      // zero, but the exchange callback still runs once per exchanged layer and direction, with zero rows, so that
+      // the point-to-point pattern of the other ranks stays matched.
+      if (o->energy) CKL(launch_fill_zero(static_cast<T*>(o->energy), (long long)B, s));
+      if (o->forces) CKL(launch_fill_zero(static_cast<T*>(o->forces), 3 * N, s));
+      if (o->virials) CKL(launch_fill_zero(static_cast<T*>(o->virials), 9LL * B, s));
+      if (o->stress) CKL(launch_fill_zero(static_cast<T*>(o->stress), 9LL * B, s));
+      if (o->edge_forces) CKL(launch_fill_zero(static_cast<T*>(o->edge_forces), 3 * E, s));
+      for (int pass = 0; pass < (need_grad ? 2 : 1); ++pass)
+        for (int k = 0; k < NL_; ++k) {
+          const int t = pass == 0 ? k : NL_ - 1 - k;
+          LayerBufs& lb = b.lay[t];
+          const long long row = (long long)layers[t].tp.NX * C;
+          if (pass == 0 && lb.xx) {
+            CKL(launch_fill_zero(lb.x, N * row, s));
+            if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+            if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
+          }
+          if (pass == 1 && lb.gxx) {
+            CKL(launch_fill_zero(lb.gx, N * row, s));
+            if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+            if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
+          }
+        }
+      return TACE_OK;
+    }
     PH("graph_prep");
     // ---- graph preparation
     GraphPrepArgs gp;

@@ -117,7 +117,7 @@ cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
   while ((1LL << bits) < (long long)a.n_atoms + 1 && bits < 31) ++bits;
   cudaError_t err;
 
-  atom_graph_kernel<<<(a.n_atoms + 255) / 256, 256, 0, s>>>(a.graph_ptr, a.n_graphs, a.atom_graph, a.n_atoms);
+  if (a.n_atoms > 0) atom_graph_kernel<<<(a.n_atoms + 255) / 256, 256, 0, s>>>(a.graph_ptr, a.n_graphs, a.atom_graph, a.n_atoms);
 
   if (a.E > 0) {
     const unsigned eb = (unsigned)((a.E + 255) / 256);
@@ -134,12 +134,14 @@ cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
   lower_bound_kernel<<<(a.n_local + 256) / 256, 256, 0, s>>>(a.e_dst, a.E, a.rowptr_dst, a.n_local);
   lower_bound_kernel<<<(a.n_atoms + 256) / 256, 256, 0, s>>>(keys_out, a.E, a.rowptr_src, a.n_atoms);
 
-  // species-sorted permutation of the local atoms
+  // species-sorted permutation of the local atoms (none on a rank that owns no atom: the row pointers below are all 0)
   int sbits = 1;
   while ((1 << sbits) < a.n_elements + 1 && sbits < 31) ++sbits;
-  iota_and_key32_kernel<<<(a.n_local + 255) / 256, 256, 0, s>>>(a.species, keys_in, vals_in, a.n_local);
-  err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.species_perm, a.n_local, 0, sbits, s);
-  if (err != cudaSuccess) return err;
+  if (a.n_local > 0) {
+    iota_and_key32_kernel<<<(a.n_local + 255) / 256, 256, 0, s>>>(a.species, keys_in, vals_in, a.n_local);
+    err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.species_perm, a.n_local, 0, sbits, s);
+    if (err != cudaSuccess) return err;
+  }
   lower_bound_kernel<<<(a.n_elements + 256) / 256, 256, 0, s>>>(keys_out, a.n_local, a.species_ptr, a.n_elements);
   tile_ptr_kernel<<<1, 32, 0, s>>>(a.species_ptr, a.n_elements, a.tile_ptr, a.tc_tile_ptr);
   return cudaGetLastError();

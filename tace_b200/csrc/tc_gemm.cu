@@ -525,13 +525,16 @@ bool make_map_c(CUtensorMap* map, float* ptr, long long rows, long long N, long 
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Function attributes and the SM count belong to a device, not to the process: one slot per device ordinal.
+constexpr int kMaxDevices = 64;
+
 template <int BN, bool ONE_CHUNK>
-cudaError_t launch_tc(const TcBatch& b, int sms, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+cudaError_t launch_tc(const TcBatch& b, int dev, int sms, cudaStream_t s) {
+  static bool configured[kMaxDevices] = {};
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, ONE_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   const int tiles = b.tile_start[b.n_problems];  // upper bound for per-species problems
   const int grid = tiles < sms ? tiles : sms;
@@ -546,12 +549,12 @@ bool tc_linear_supported(int N, int K) { return N % 64 == 0 && K % kBK == 0; }
 cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s) {
   if (n_problems <= 0) return cudaSuccess;
   if (n_problems > kTcMaxProblems || !error_flag) return cudaErrorInvalidValue;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      return cudaErrorInvalidValue;
-  }
+  static int sms_of[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidValue;
+  if (!sms_of[dev] && cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return cudaErrorInvalidValue;
+  const int sms = sms_of[dev];
   bool all128 = true, one = true;
   for (int i = 0; i < n_problems; ++i) {
     const TcLinearProblem& h = probs[i];
@@ -596,8 +599,8 @@ cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* 
   }
   for (int i = b.n_problems; i <= kTcMaxProblems; ++i) b.tile_start[i] = tiles;
   if (tiles == 0) return cudaSuccess;
-  if (bn == 128) return one ? launch_tc<128, true>(b, sms, s) : launch_tc<128, false>(b, sms, s);
-  return one ? launch_tc<64, true>(b, sms, s) : launch_tc<64, false>(b, sms, s);
+  if (bn == 128) return one ? launch_tc<128, true>(b, dev, sms, s) : launch_tc<128, false>(b, dev, sms, s);
+  return one ? launch_tc<64, true>(b, dev, sms, s) : launch_tc<64, false>(b, dev, sms, s);
 }
 
 cudaError_t launch_tc_gemm(const float* A, long long lda, const float* Bhi, const float* Blo, float* C, long long ldc, int M,

@@ -214,12 +214,14 @@ template <typename T, typename TP>
 cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
   const size_t smem = sizeof(T) * ((size_t)TP::NM * a.C + kEdgeBatch * TP::NG + kEdgeBatch * 8 * TP::D);
   if (a.env && !a.denv) return cudaErrorInvalidValue;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  static size_t configured[64] = {};  // the attribute belongs to a device: one slot per device ordinal
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024 && smem > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = smem;
+    configured[dev] = smem;
   }
   if (a.env) tp_bwd_kernel<T, TP, true><<<a.n_seg, a.C, smem, s>>>(a);
   else tp_bwd_kernel<T, TP, false><<<a.n_seg, a.C, smem, s>>>(a);

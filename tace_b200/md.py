@@ -140,7 +140,10 @@ class DomainMD:
         lattice = torch.eye(3, dtype=torch.float64, device=self.device)[None]
         pbc = torch.zeros(1, 3, dtype=torch.uint8, device=self.device)
         ptr = torch.tensor([0, n + g], dtype=torch.int32, device=self.device)
-        edge_index, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff, n_targets=n)
+        if n > 0:
+            edge_index, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff, n_targets=n)
+        else:  # a block of vacuum: no target atom, no edge (the evaluation still answers its peers' exchanges)
+            edge_index = torch.empty(2, 0, dtype=torch.int64, device=self.device)
         E = int(edge_index.shape[1])
         vec = torch.empty(E, 3, dtype=self.dtype, device=self.device)
         with torch.cuda.device(self.device):
@@ -166,18 +169,20 @@ class DomainMD:
         fcode = _lib.dtype_code(self.dtype)
         for _ in range(n_steps):
             n = self.domain.n_owned
-            with torch.cuda.device(self.device):
-                _lib.check(self.lib.tace_md_kick_drift(self.positions.data_ptr(), self.velocities.data_ptr(), self.forces.data_ptr(),
-                                                       fcode, self.inv_mass.data_ptr(), n, kick, self.dt, self._stream()),
-                           "tace_md_kick_drift")
+            if n > 0:
+                with torch.cuda.device(self.device):
+                    _lib.check(self.lib.tace_md_kick_drift(self.positions.data_ptr(), self.velocities.data_ptr(), self.forces.data_ptr(),
+                                                           fcode, self.inv_mass.data_ptr(), n, kick, self.dt, self._stream()),
+                               "tace_md_kick_drift")
             if self.domain.needs_partition(self.positions):
                 self._repartition(self._state())
             self._evaluate()
             n = self.domain.n_owned
             with torch.cuda.device(self.device):
-                _lib.check(self.lib.tace_md_kick_drift(None, self.velocities.data_ptr(), self.forces.data_ptr(), fcode,
-                                                       self.inv_mass.data_ptr(), n, kick, 0.0, self._stream()), "tace_md_kick_drift")
-                if self.friction > 0.0:
+                if n > 0:
+                    _lib.check(self.lib.tace_md_kick_drift(None, self.velocities.data_ptr(), self.forces.data_ptr(), fcode,
+                                                           self.inv_mass.data_ptr(), n, kick, 0.0, self._stream()), "tace_md_kick_drift")
+                if self.friction > 0.0 and n > 0:
                     _lib.check(self.lib.tace_md_langevin(self.velocities.data_ptr(), self.inv_mass.data_ptr(), self.ids.data_ptr(), n,
                                                          float(np.exp(-self.friction * self.dt)), KB * self.target_temperature * ACCEL,
                                                          self.seed, self.step_count, self._stream()), "tace_md_langevin")
@@ -196,6 +201,8 @@ class DomainMD:
 
     def kinetic_energy(self) -> float:
         out = self._ke_scratch[1024:1025]
+        if self.domain.n_owned == 0:
+            return self._all_sum(torch.zeros((), dtype=torch.float64, device=self.device)) / ACCEL
         with torch.cuda.device(self.device):
             _lib.check(self.lib.tace_md_kinetic_energy(self.velocities.data_ptr(), self.mass.data_ptr(), self.domain.n_owned,
                                                        self._ke_scratch.data_ptr(), out.data_ptr(), self._stream()),

@@ -459,7 +459,13 @@ class TensorModel(torch.nn.Module):
             nlocal, nghost = int(data["natoms"][0]), int(data["natoms"][1])
             n_atoms, n_local, n_graphs = nlocal + nghost, nlocal, 1
             graph_ptr = torch.tensor([0, nlocal], dtype=torch.int32, device=device)
-            batch.edge_vector = real(data["edge_vector"]).data_ptr()
+            if n_atoms == 0:  # a rank of a domain decomposition that neither owns nor sees any atom
+                zeros = lambda *shape: torch.zeros(*shape, dtype=dtype, device=device)
+                return {"energy": zeros(1), "node_energy": zeros(0), "forces": zeros(0, 3) if flags.compute_forces else None,
+                        "virials": None, "stress": None, "edge_forces": zeros(0, 3)}
+            # an empty edge list (a rank that owns no atom) still has to say "edge-vector mode": never a NULL pointer
+            vec = data["edge_vector"] if E > 0 else torch.zeros(1, 3, dtype=dtype, device=device)
+            batch.edge_vector = real(vec).data_ptr()
         else:
             n_atoms = n_local = int(species.shape[0])
             graph_ptr = data["ptr"].to(torch.int32).contiguous()
@@ -527,10 +533,18 @@ class TensorModel(torch.nn.Module):
             ws = self._get_workspace(nbytes.value, device)
             ws_ptr = (ws.data_ptr() + 255) & ~255
             stream = torch.cuda.current_stream(device).cuda_stream
-            _lib.check(lib.tace_forward(handle, ctypes.byref(batch), ctypes.byref(out), ws_ptr,
-                                        ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
-        if exchange_cb is not None:
-            _lib.check(lib.tace_set_exchange(handle, _lib.EXCHANGE_FN(0), None), "tace_set_exchange")
+            self._exchange_error = None
+            try:
+                _lib.check(lib.tace_forward(handle, ctypes.byref(batch), ctypes.byref(out), ws_ptr,
+                                            ws.numel() - (ws_ptr - ws.data_ptr()), stream), "tace_forward")
+            except _lib.TaceError as exc:
+                if self._exchange_error is not None:  # the callback failed: show its exception, not the bare status
+                    raise self._exchange_error from exc
+                raise
+            finally:
+                # the handle must never keep a pointer to a callback object that dies with this frame
+                if exchange_cb is not None:
+                    lib.tace_set_exchange(handle, _lib.EXCHANGE_FN(0), None)
         return res
 
     def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device):

@@ -87,3 +87,35 @@ def feats_to_oracle_layout(x: torch.Tensor, ls, C: int) -> torch.Tensor:
         out.append(blk.permute(0, 2, 1).reshape(n, -1))
         off += 2 * l + 1
     return torch.cat(out, dim=1)
+
+
+# The task's tolerances, absolute: fp64 energy 1e-8 eV/atom, forces 1e-7 eV/A; fp32 1e-5 eV/atom, 1e-4 eV/A.
+PARITY_TOL = {torch.float64: (1e-8, 1e-7), torch.float32: (1e-5, 1e-4)}
+
+
+def check_parity(out, ref, ptr, dtype, label=""):
+    """Asserts the absolute tolerances and prints the worst deviations (shown by ``pytest -s`` / on failure).
+
+    Energy per atom and forces carry the stated absolute bounds.  Per-atom energies get ten times the energy bound,
+    stress the force bound (eV/A^3).  Virials are extensive (a sum of r x F over all edges of a graph), so their bound
+    is the force bound times max(1, largest reference entry).  Returns the deviations."""
+    etol, ftol = PARITY_TOL[dtype]
+    n_per_graph = (ptr[1:] - ptr[:-1]).to(torch.float64).cpu()
+    cpu = lambda t: t.detach().cpu().to(torch.float64)
+    dev = {"dE_per_atom": ((cpu(out["energy"]) - cpu(ref["energy"])).abs() / n_per_graph).max().item(),
+           "dF": (cpu(out["forces"]) - cpu(ref["forces"])).abs().max().item() if ref.get("forces") is not None else 0.0}
+    if ref.get("node_energy") is not None and out.get("node_energy") is not None:
+        dev["dE_node"] = (cpu(out["node_energy"]) - cpu(ref["node_energy"])).abs().max().item()
+    if ref.get("stress") is not None and out.get("stress") is not None:
+        dev["dStress"] = (cpu(out["stress"]) - cpu(ref["stress"])).abs().max().item()
+        dev["dVirial"] = (cpu(out["virials"]) - cpu(ref["virials"])).abs().max().item()
+    print(f"parity {label} {str(dtype).replace('torch.', '')}: " + ", ".join(f"{k} = {v:.3e}" for k, v in dev.items()))
+    assert dev["dE_per_atom"] <= etol, f"{label}: |dE|/atom = {dev['dE_per_atom']:.3e} eV > {etol}"
+    assert dev["dF"] <= ftol, f"{label}: max |dF| = {dev['dF']:.3e} eV/A > {ftol}"
+    if "dE_node" in dev:
+        assert dev["dE_node"] <= 10 * etol, f"{label}: per-atom energy deviates by {dev['dE_node']:.3e} eV"
+    if "dStress" in dev:
+        assert dev["dStress"] <= ftol, f"{label}: stress deviates by {dev['dStress']:.3e} eV/A^3"
+        vmax = max(1.0, cpu(ref["virials"]).abs().max().item())
+        assert dev["dVirial"] <= ftol * vmax, f"{label}: virial deviates by {dev['dVirial']:.3e} eV (largest entry {vmax:.3e})"
+    return dev

@@ -53,8 +53,23 @@ def _local_edges(pos_local, n_owned, cutoff):
 @pytest.mark.parametrize("grid", [(1, 1, 1), (2, 1, 1), (2, 2, 1), (1, 2, 2), (2, 2, 2), (3, 1, 2)])
 def test_plans_reproduce_the_periodic_edge_set(grid):
     s = synth.fcc_supercell(4, 3.61, 0.05, seed=3)
-    cutoff, skin = 4.0, 0.4
-    pos, cell = s["positions"], s["cell"]
+    _check_plans(s["positions"], s["cell"], grid, 4.0, 0.4)
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 1), (4, 1, 1), (2, 2, 1)])
+def test_plans_with_blocks_of_vacuum(grid):
+    """A slab in a long box: some blocks own no atom (and may or may not see ghosts).  Their plans must still pair up
+    with their neighbours' and the union of the local edge lists must stay the periodic neighbour list."""
+    s = synth.fcc_supercell(3, 3.61, 0.05, seed=3)
+    cell = s["cell"].copy()
+    cell[0, 0] *= 3.0  # the atoms fill about a third of the box along x, away from the cell boundary
+    pos = s["positions"] + np.array([1.0, 0.0, 0.0])
+    plans = _check_plans(pos, cell, grid, 4.0, 0.4)
+    assert any(p.n_owned == 0 for p in plans)
+    assert any(p.n_owned == 0 and p.n_ghost > 0 for p in plans) or grid[0] > 2
+
+
+def _check_plans(pos, cell, grid, cutoff, skin):
     dg = DomainGrid(grid)
     W = dg.world_size
     inv = np.linalg.inv(cell)
@@ -88,6 +103,7 @@ def test_plans_reproduce_the_periodic_edge_set(grid):
         keys += _edge_keys(gid[t], gid[srcs], d)
     ei, vec = _global_edges({"positions": wrapped, "cell": cell}, cutoff)
     assert sorted(keys) == _edge_keys(ei[1], ei[0], vec)
+    return plans
 
 
 def _worker(rank, world, port, ret):

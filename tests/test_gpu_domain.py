@@ -237,3 +237,53 @@ def test_langevin_dynamics_reaches_the_target_temperature():
     # 256 atoms: the instantaneous temperature fluctuates by about 5 %; the mean of the last samples is near the target
     assert 240.0 < sum(temps) / len(temps) < 360.0, temps
     assert model.device_error() == 0
+
+
+def test_rank_without_owned_atoms_answers_its_exchanges():
+    """A block of vacuum in a decomposition (a slab in a long box): the rank owns nothing but holds ghost rows.  Its
+    evaluation must return zeros and still call the exchange once per exchanged layer and direction - its neighbours'
+    point-to-point messages have to meet a partner."""
+    model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, num_layers=3, targets=("energy", "forces"))
+    model = model.to(DEV)
+    model._set_lammps_mliap(True)
+    calls = []
+
+    class Exchange:
+        def forward_exchange(self, src, dst, vec_len):
+            calls.append(("forward", tuple(src.shape)))
+            dst.copy_(src)
+
+        def reverse_exchange(self, src, dst, vec_len):
+            calls.append(("reverse", tuple(src.shape)))
+            dst.copy_(src)
+
+    g = 7
+    out = model({"species": torch.zeros(g, dtype=torch.int32, device=DEV), "edge_index": torch.empty(2, 0, dtype=torch.int64, device=DEV),
+                 "edge_vector": torch.empty(0, 3, dtype=torch.float64, device=DEV), "natoms": (0, g), "lmp_data": Exchange()})
+    torch.cuda.synchronize()
+    assert [c[0] for c in calls] == ["forward", "forward", "reverse", "reverse"]  # layers 1 and 2 read exchanged features
+    assert all(c[1][0] == g for c in calls)
+    assert out["forces"].shape == (g, 3) and float(out["forces"].abs().max()) == 0.0
+    assert out["node_energy"].numel() == 0 and float(out["energy"].abs().max()) == 0.0
+    assert model.device_error() == 0
+    # the next ordinary evaluation on the same handle is unaffected
+    s = _system()
+    model2, oracle, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, num_layers=3, targets=("energy", "forces"))
+    md = DomainMD(model2.to(DEV), s["cell"], s["positions"], s["atomic_numbers"], skin=0.4, device=DEV)
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, torch.float64))
+    assert abs(md.potential() - float(ref["energy"][0])) / len(s["positions"]) < 1e-8
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_one_process_two_devices(dtype):
+    """Models on cuda:0 and then cuda:1 in one process: kernel attributes (opt-in shared memory) are set per device."""
+    from helpers import check_parity, to_device
+
+    s = synth.fcc_supercell(2, 3.61, 0.05, seed=0)
+    for dev in (torch.device("cuda:0"), torch.device("cuda:1")):
+        model, oracle, _ = make_models(3, 128, [29], 4.0, 20.0, dtype)
+        data = oracle_batch([s], [29], 4.0, dtype)
+        out = model(to_device(data, dev))
+        check_parity(out, oracle(data), data["ptr"], dtype, f"L3 C128 on {dev}")
+        assert model.device_error() == 0
