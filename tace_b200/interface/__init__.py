@@ -3,5 +3,5 @@
 in the reference)."""
 
 from .ase_calculator import TACEAseCalc  # noqa: F401
-from .lammps_mliap import EdgeForcesWrapper, TACELammpsCalc  # noqa: F401
+from .lammps_mliap import TACELammpsCalc  # noqa: F401
 from .torchsim import TACETorchSimCalc, tace_b200_nl  # noqa: F401

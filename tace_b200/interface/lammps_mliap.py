@@ -1,15 +1,24 @@
-"""LAMMPS ML-IAP (unified, Kokkos CUDA) entry point with the reference's contract
-(``tace/interface/lammps/mliap.py:25-151``): ``compute_forces(data)`` reads
-``data.{nlocal, ntotal, npairs, elems, rij, pair_i, pair_j, eatoms}``, writes ``data.eatoms`` and
-``data.energy`` and calls ``data.update_pair_forces`` with fp64 pair forces.  Ghost-atom features
-are refreshed between interaction layers through ``data.forward_exchange`` and their gradients are
-returned through ``data.reverse_exchange`` (``tace/models/lammps.py:82-129``).
+"""LAMMPS ML-IAP "unified" plug-in backed by the CUDA evaluation path.
+
+Same contract as the reference's plug-in (``tace/interface/lammps/mliap.py:55-151``), so ``pair_style mliap unified``
+can load an object of this class in its place:
+
+* attributes LAMMPS reads: ``element_types`` (chemical symbols in the model's element order), ``rcutfac`` (half the
+  cutoff), ``nparams`` = ``ndescriptors`` = 1;
+* ``compute_forces(data)`` takes the pair list of one rank (``data.rij`` = neighbour minus centre, ``data.pair_i`` the
+  centre, ``data.pair_j`` the neighbour, owned atoms first, then ghosts), writes per-atom energies into
+  ``data.eatoms``, their sum into ``data.energy`` and hands fp64 dE/d(rij) to ``data.update_pair_forces``;
+* between interaction layers the features of ghost atoms come from their owners through ``data.forward_exchange``
+  and the gradients go back through ``data.reverse_exchange`` (``tace/models/lammps.py:82-142``): that is wired
+  inside ``TensorModel.forward`` (``tace_set_exchange``), this file only passes ``data`` along;
+* the object is pickled on the host and binds to the device of ``data.elems`` at its first call.
+
+The evaluation is one ``tace_forward`` call in edge-vector mode; nothing here touches autograd.
 """
 
 from __future__ import annotations
 
-import logging
-from typing import Dict, Tuple
+from typing import List, Optional
 
 import torch
 
@@ -19,10 +28,10 @@ try:
     from lammps.mliap.mliap_unified_abc import MLIAPUnified
 
     LAMMPS_ML_IAP_AVAILABLE = True
-except ImportError:  # the class stays importable (and testable with a stand-in `data`) without LAMMPS
+except ImportError:  # without LAMMPS the class can still be built, pickled and driven by a stand-in `data` object
     LAMMPS_ML_IAP_AVAILABLE = False
 
-    class MLIAPUnified:  # minimal stand-in for lammps.mliap.mliap_unified_abc.MLIAPUnified
+    class MLIAPUnified:  # the constructor signature of lammps.mliap.mliap_unified_abc.MLIAPUnified
         def __init__(self, interface=None, element_types=None, ndescriptors=None, nparams=None, rcutfac=None):
             self.interface, self.element_types = interface, element_types
             self.ndescriptors, self.nparams, self.rcutfac = ndescriptors, nparams, rcutfac
@@ -33,96 +42,69 @@ _SYMBOLS = ("X H He Li Be B C N O F Ne Na Mg Al Si P S Cl Ar K Ca Sc Ti V Cr Mn 
             "Au Hg Tl Pb Bi Po At Rn Fr Ra Ac Th Pa U Np Pu Am Cm Bk Cf Es Fm Md No Lr").split()
 
 
-class EdgeForcesWrapper(torch.nn.Module):
-    """tace/interface/lammps/mliap.py:25-52: switches the model to edge-vector input and pair-force output."""
-
-    def __init__(self, model: TensorModel, **kwargs):
-        super().__init__()
-        model._set_lammps_mliap(True)
-        model.flags.compute_forces = False
-        model.flags.compute_stress = False
-        model.flags.compute_virials = False
-        model.flags.compute_edge_forces = True
-        self.model = model
-        self.register_buffer("cutoff", model.readout_fn.cutoff)
-        self.register_buffer("atomic_numbers", model.readout_fn.atomic_numbers)
-
-    def forward(self, data: Dict[str, torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        outs = self.model(data)
-        pair_forces = outs["edge_forces"]
-        if pair_forces is None:
-            pair_forces = torch.zeros_like(data["edge_vector"])
-        return outs["energy"][0], outs["node_energy"], pair_forces
+def _pair_force_mode(model: TensorModel) -> TensorModel:
+    """Edge vectors in, dE/d(edge vector) out; no per-atom forces, no strain derivative."""
+    model._set_lammps_mliap(True)
+    flags = model.flags
+    flags.compute_forces = flags.compute_stress = flags.compute_virials = False
+    flags.compute_edge_forces = True
+    return model
 
 
 class TACELammpsCalc(MLIAPUnified):
     def __init__(self, model: TensorModel, **kwargs):
         super().__init__()
-        self.model = EdgeForcesWrapper(model, **kwargs)
-        self.element_types = [_SYMBOLS[int(z)] for z in model.readout_fn.atomic_numbers]
+        head = model.readout_fn
+        self.model = _pair_force_mode(model)
+        self.element_types: List[str] = [_SYMBOLS[int(z)] for z in head.atomic_numbers]
         self.num_species = len(self.element_types)
-        self.rcutfac = 0.5 * float(model.readout_fn.cutoff)
-        self.nparams = 1
-        self.ndescriptors = 1
-        self.dtype = model.readout_fn.cutoff.dtype
-        self.device = torch.device("cpu")
-        self.initialized = False
+        self.rcutfac = float(head.cutoff) / 2.0
+        self.nparams = self.ndescriptors = 1
+        self.dtype = head.cutoff.dtype
+        self.device: Optional[torch.device] = None  # bound at the first compute_forces call
 
-    def _initialize_device(self, data):
+    # -- device binding ----------------------------------------------------------------------------------------------
+    def _bind(self, data) -> torch.device:
+        """The rank's GPU is the one LAMMPS put ``data.elems`` on.  Ghost features travel through LAMMPS' own
+        device-side exchange, which only the KOKKOS build of ML-IAP offers."""
+        missing = [name for name in ("forward_exchange", "reverse_exchange") if not callable(getattr(data, name, None))]
+        if missing:
+            raise RuntimeError(f"the ML-IAP data object has no {' / '.join(missing)}: this model needs the KOKKOS ML-IAP "
+                               "interface (start LAMMPS with '-k on g <gpus per node> -sf kk')")
         device = torch.as_tensor(data.elems).device
-        self._validate_lammps_data(data, device)
-        self.device = device
-        self.model = self.model.to(device)
-        logging.info(f"TACE model initialized on device: {device}")
-        self.initialized = True
-
-    @staticmethod
-    def _validate_lammps_data(data, device):
-        if not all(hasattr(data, m) for m in ("forward_exchange", "reverse_exchange")):
-            raise RuntimeError("TACE requires the KOKKOS ML-IAP interface for ghost exchange. "
-                               "Run LAMMPS with '-k on g <Ng> -sf kk'.")
         if device.type != "cuda":
-            raise RuntimeError("TACE LAMMPS ML-IAP currently requires a CUDA KOKKOS backend. "
-                               "LAMMPS host-side ML-IAP ghost exchange is not supported.")
+            raise RuntimeError(f"ML-IAP data lives on '{device}': tace_b200 evaluates on CUDA devices only, run the KOKKOS "
+                               "CUDA back end")
+        self.model = self.model.to(device)
+        self.device = device
+        return device
 
+    # -- one evaluation ----------------------------------------------------------------------------------------------
     def compute_forces(self, data):
-        nlocal, ntotal, npairs = data.nlocal, data.ntotal, data.npairs
-        nghosts = ntotal - nlocal
-        species = torch.as_tensor(data.elems, dtype=torch.int64)
-        if not self.initialized:
-            self._initialize_device(data)
-        if nlocal == 0 or npairs <= 1:
+        device = self.device if self.device is not None else self._bind(data)
+        n_owned, n_pairs = int(data.nlocal), int(data.npairs)
+        if n_owned == 0 or n_pairs <= 1:  # nothing to evaluate on this rank (the reference returns here as well)
             return
-        batch = self._prepare_batch(data, nlocal, nghosts, species)
-        _, node_energy, pair_forces = self.model(batch)
-        torch.cuda.synchronize(self.device)
-        self._update_lammps_data(data, node_energy, pair_forces, nlocal)
-
-    def _prepare_batch(self, data, nlocal, nghosts, species):
-        species = species.to(self.device)
-        return {
-            "edge_vector": torch.as_tensor(data.rij).to(self.dtype).to(self.device),
-            "node_attrs": torch.nn.functional.one_hot(species, num_classes=self.num_species).to(self.dtype),
-            "species": species.to(torch.int32),
-            "edge_index": torch.stack([torch.as_tensor(data.pair_j, dtype=torch.int64).to(self.device),
-                                       torch.as_tensor(data.pair_i, dtype=torch.int64).to(self.device)], dim=0),
-            "batch": torch.zeros(nlocal, dtype=torch.int64, device=self.device),
-            "ptr": torch.tensor([0, nlocal], dtype=torch.int64, device=self.device),
+        n_ghost = int(data.ntotal) - n_owned
+        species = torch.as_tensor(data.elems).to(device=device, dtype=torch.int32)
+        centre = torch.as_tensor(data.pair_i).to(device=device, dtype=torch.int64)
+        neighbour = torch.as_tensor(data.pair_j).to(device=device, dtype=torch.int64)
+        result = self.model({
+            "species": species,
+            "edge_index": torch.stack((neighbour, centre)),  # messages flow neighbour -> centre
+            "edge_vector": torch.as_tensor(data.rij).to(device=device, dtype=self.dtype),
+            "natoms": (n_owned, n_ghost),
             "lmp_data": data,
-            "natoms": (nlocal, nghosts),
-        }
+        })
+        torch.cuda.synchronize(device)  # LAMMPS reads the results on its own stream
+        per_atom = result["node_energy"][:n_owned].to(torch.float64)
+        torch.as_tensor(data.eatoms).copy_(per_atom)
+        data.energy = float(per_atom.sum())
+        data.update_pair_forces(result["edge_forces"].to(torch.float64).contiguous())
 
-    @staticmethod
-    def _update_lammps_data(data, node_energy, pair_forces, nlocal):
-        pair_forces = pair_forces.to(dtype=torch.float64).contiguous()
-        node_energy = node_energy.to(dtype=torch.float64).contiguous()
-        eatoms = torch.as_tensor(data.eatoms)
-        eatoms.copy_(node_energy[:nlocal])
-        data.energy = node_energy[:nlocal].sum().item()
-        data.update_pair_forces(pair_forces)
-
+    # descriptors and their gradients are not a separate stage of this model
     def compute_descriptors(self, data):
-        pass
+        return None
 
     def compute_gradients(self, data):
-        pass
+        return None

@@ -261,6 +261,70 @@ def pad_channels(out: Dict[str, np.ndarray], C: int, Cp: int) -> None:
                 out[name] = _pad_axis(arr, -1, C, Cp)
 
 
+def _silu(z):
+    return z / (1.0 + np.exp(-z))
+
+
+def _silu_grad(z):
+    sg = 1.0 / (1.0 + np.exp(-z))
+    return sg * (1.0 + z * (1.0 - sg))
+
+
+def radial_table(out: Dict[str, np.ndarray], layer: int, plan: "ModelPlan", cutoff: float, envelope_p: int, intervals: int) -> np.ndarray:
+    """Path weights of interaction ``layer`` as a function of the edge length, tabulated for cubic Hermite interpolation.
+
+    With the identity edge update the radial MLP sees nothing but the radial basis of the edge length
+    (tace/models/_e3nn/edge.py:15-35,169-189, inter.py:166-183), so its output W(d) [paths * channels] is a smooth
+    function of one variable.  Returns [intervals + 1][paths * channels][2] (fp64): W at the knots d_k = k * cutoff /
+    intervals and h * dW/dd there (h = knot spacing), both from an fp64 forward-mode pass through the packed layers of
+    ``out`` (normalisation factors already folded in).  With ``apply_cutoff`` the envelope is part of the features;
+    otherwise the table holds the bare MLP output and the kernels multiply by the envelope as before."""
+    tp = f"t{layer}."
+    K = int(intervals)
+    h = cutoff / K
+    d = np.arange(K + 1, dtype=np.float64) * h
+    d[0] = 1e-3 * h  # sin(w d) / d and its derivative are finite at 0; evaluate just beside it
+    w = out["bessel"].reshape(1, -1)
+    pref = float(out["bessel_pref"].reshape(-1)[0])
+    s, c = np.sin(w * d[:, None]), np.cos(w * d[:, None])
+    f = pref * s / d[:, None]
+    df = pref * (w * c * d[:, None] - s) / d[:, None] ** 2
+    if plan.apply_cutoff:
+        x = d / cutoff
+        pp = float(envelope_p)
+        u = 1.0 - (pp + 1) * (pp + 2) / 2 * x**pp + pp * (pp + 2) * x ** (pp + 1) - pp * (pp + 1) / 2 * x ** (pp + 2)
+        du = -(pp * (pp + 1) * (pp + 2) / 2) * x ** (pp - 1) * (1 - x) ** 2 / cutoff
+        inside = d < cutoff
+        u, du = np.where(inside, u, 0.0), np.where(inside, du, 0.0)
+        f, df = f * u[:, None], df * u[:, None] + f * du[:, None]
+    nh = plan.mlp_layers
+    z = f @ out[tp + "A0"] + (out[tp + "b0"] if plan.mlp_bias else 0.0)
+    dz = df @ out[tp + "A0"]
+    a, da = _silu(z), _silu_grad(z) * dz
+    for j, name in ((1, "A1"), (2, "A2")):
+        if nh > j:
+            z = a @ out[tp + name] + (out[tp + f"b{j}"] if plan.mlp_bias else 0.0)
+            dz = da @ out[tp + name]
+            a, da = _silu(z), _silu_grad(z) * dz
+    val = a @ out[tp + "W3"] + (out[tp + "b3"] if plan.mlp_bias else 0.0)
+    slope = da @ out[tp + "W3"]
+    return np.stack([val, slope * h], axis=-1)
+
+
+def hermite_weights(table: np.ndarray, d: np.ndarray, cutoff: float):
+    """Host restatement of the kernels' interpolation: (W(d), dW/dd) from a table of ``radial_table``."""
+    K = table.shape[0] - 1
+    h = cutoff / K
+    u = np.asarray(d, dtype=np.float64) / h
+    k = np.clip(np.floor(u).astype(np.int64), 0, K - 1)
+    t = (u - k)[:, None]
+    v0, m0, v1, m1 = table[k, :, 0], table[k, :, 1], table[k + 1, :, 0], table[k + 1, :, 1]
+    t2, t3 = t * t, t * t * t
+    val = (2 * t3 - 3 * t2 + 1) * v0 + (t3 - 2 * t2 + t) * m0 + (-2 * t3 + 3 * t2) * v1 + (t3 - t2) * m1
+    der = ((6 * t2 - 6 * t) * v0 + (3 * t2 - 4 * t + 1) * m0 + (-6 * t2 + 6 * t) * v1 + (3 * t2 - 2 * t) * m1) / h
+    return val, der
+
+
 def _np(t) -> np.ndarray:
     return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
 
