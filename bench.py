@@ -3,10 +3,14 @@
 
 One "step" = one evaluation of energy, conservative forces and stress for the whole batch of the
 workload (the headline configuration: 64 random periodic crystals, fp32, L = 3, 128 channels, 89 elements).
-With N GPUs every rank evaluates its own batch of 64 crystals (weak scaling, no collective on the
-data path).  `value` is timed with the batch and its neighbour list resident in HBM; `e2e` goes
-through the public API from pinned host buffers (upload, GPU neighbour list, evaluation,
-download of energy / forces / stress).
+With N GPUs a pool of 64 N crystals is split over the ranks with the longest-processing-time rule on
+estimated edge counts (``tace_b200.shard``); every rank evaluates its share with replicated weights (weak
+scaling, no collective on the data path) and the per-structure energies and stresses are gathered with one
+all_gather in the end-to-end loop.  `value` is timed with the batch and its neighbour list resident in HBM;
+`e2e` goes through the public API from pinned host buffers (upload, GPU neighbour list, evaluation,
+download of energy / forces / stress).  Unless --no-domain-md is given, the line also carries `domain_md`:
+a short velocity-Verlet run of the 1 048 576-atom Cu-Al system of configuration 5, domain-decomposed
+over the same N GPUs (strong scaling, halo exchange per interaction layer).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload NAME]
 """
@@ -95,6 +99,16 @@ def dist_setup(n_gpus: int):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
+        # every rank reports the same CPU affinity on these hosts: give each its own slice of the cores so that the
+        # host sides of the ranks (Python, pinned staging, launches) do not migrate onto each other
+        try:
+            cores = sorted(os.sched_getaffinity(0))
+            per = max(1, len(cores) // world)
+            mine = cores[local * per:(local + 1) * per] or cores
+            os.sched_setaffinity(0, mine)
+            torch.set_num_threads(max(1, min(len(mine), 8)))
+        except (AttributeError, OSError):
+            pass
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return rank, world, local
 
@@ -166,38 +180,40 @@ def gemm_flops(phase: str, dims: dict):
     return 2.0 * dims["E"] * 64 * dims["NP"][layer] * dims["C"]
 
 
-def cpu_sample(structures, wl, dtype, state_dict, budget_s: float, evals: int):
-    """Times the CPU oracle (PyTorch, autograd forces, all host threads) on as many crystals of the
-    workload as fit the time budget.  Returns (atom-steps/s, description, cores)."""
+def cpu_sample_structures(structures, wl):
+    """The fixed sample both CPU legs time: for a batch of crystals, the four crystals at the octile midpoints of the
+    size-sorted batch (12.5 %, 37.5 %, 62.5 %, 87.5 %; about 140 atoms for configuration 2), chosen by index; for a
+    single large structure, a smaller cell of the same material named by the workload."""
+    from tace_b200 import synth
+    if wl.get("cpu_sample"):
+        return synth.workload_structures(wl["cpu_sample"]), f"a smaller cell of the same material ({wl['cpu_sample']})"
+    if len(structures) < 8:
+        return list(structures), "the whole workload"
+    order = sorted(range(len(structures)), key=lambda i: (len(structures[i]["positions"]), i))
+    picks = sorted(order[int(q * len(order))] for q in (0.125, 0.375, 0.625, 0.875))
+    return [structures[i] for i in picks], f"crystals {picks} of the batch (size octile midpoints)"
+
+
+def cpu_sample(structures, wl, dtype, state_dict):
+    """The CPU oracle (PyTorch, autograd forces, all host threads) on the fixed sample."""
     from helpers import oracle_batch
     from oracle.model import build_oracle
     from tace_b200 import synth
-    cores = os.cpu_count() or 1
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     torch.set_num_threads(cores)
     cfg = synth.model_config(wl["L"], wl["channels"], wl["cutoff"], wl["elements"], wl["avg_num_neighbors"], **wl.get("model", {}))
     oracle = build_oracle(cfg, state_dict, dtype)
-    if wl.get("cpu_sample"):  # one large structure: the CPU leg takes a smaller cell of the same material
-        structures = synth.workload_structures(wl["cpu_sample"])
-    order = sorted(range(len(structures)), key=lambda i: len(structures[i]["positions"]))
-    probe = [structures[order[0]]]
-    data = oracle_batch(probe, wl["elements"], wl["cutoff"], dtype)
-    t0 = time.perf_counter(); oracle(data); t1 = time.perf_counter()
-    per_edge = (t1 - t0) / max(1, data["edge_index"].shape[1])
-    # choose crystals (smallest first) so that `evals` evaluations fit the budget
-    chosen, edges = [], 0
-    for i in order:
-        est = len(structures[i]["positions"]) * wl["avg_num_neighbors"]
-        if chosen and (edges + est) * per_edge * evals > budget_s:
-            break
-        chosen.append(structures[i]); edges += est
+    chosen, what = cpu_sample_structures(structures, wl)
     data = oracle_batch(chosen, wl["elements"], wl["cutoff"], dtype)
     n_atoms = data["positions"].shape[0]
-    return oracle, data, n_atoms, len(chosen), cores
+    sample = f"{what}: {len(chosen)} structure(s), {n_atoms} atoms, {data['edge_index'].shape[1]} edges"
+    return oracle, data, n_atoms, sample, cores, chosen
 
 
 def run_reference(args, rank, world):
     """--impl reference: the CPU restatement of the reference path (the reference itself needs e3nn /
-    matscipy / ase, which cannot be installed offline), all host threads, bounded sample per step."""
+    matscipy / ase, which cannot be installed offline), all host threads, the same fixed sample per step as the
+    `cpu_baseline` leg of the native arm."""
     if rank != 0:
         return
     from tace_b200 import synth
@@ -205,35 +221,38 @@ def run_reference(args, rank, world):
     dtype = torch.float64 if wl["dtype"] == "float64" else torch.float32
     structures = synth.workload_structures(args.workload)
     model, cfg = build_model(wl, dtype)
-    oracle, data, n_atoms, n_struct, cores = cpu_sample(structures, wl, dtype, model.state_dict(), 90.0, args.steps + args.warmup)
+    oracle, data, n_atoms, sample, cores, _ = cpu_sample(structures, wl, dtype, model.state_dict())
     for _ in range(args.warmup):
         oracle(data)
-    t0 = time.perf_counter()
+    times = []
     for _ in range(args.steps):
+        t0 = time.perf_counter()
         oracle(data)
-    dt = time.perf_counter() - t0
+        times.append(time.perf_counter() - t0)
+    dt = sum(times)
     value = n_atoms * args.steps / dt
-    what = f"a smaller cell of the same material ({wl['cpu_sample']})" if wl.get("cpu_sample") else f"{n_struct} smallest crystals of the batch"
-    sample = f"{what} ({n_atoms} atoms, {data['edge_index'].shape[1]} edges) per step"
+    plan = model.readout_fn.plan
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
-        "config": {"workload": args.workload, "L": wl["L"], "channels": wl["channels"], "cutoff": wl["cutoff"],
-                   "elements": len(wl["elements"]), "parallelism": "cpu"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": args.workload, "L": plan.L, "channels": plan.C, "cutoff": wl["cutoff"],
+                   "elements": len(wl["elements"]), "parallelism": f"cpu, {cores} threads", "sample": sample + " per step"},
+        "step_ms": {"min": 1e3 * min(times), "median": 1e3 * statistics.median(times), "max": 1e3 * max(times)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample + " per step"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def run_md(args, wl, dtype, rank, world, device):
+def md_measure(workload, wl, dtype, rank, world, device, steps, warmup):
     """Molecular-dynamics workloads: ONE periodic Cu/Al system, velocity Verlet, dt = 1 fs,
-    Maxwell-Boltzmann start at 300 K.  A step = half kick + drift, ghost positions, neighbour list, energy and
-    forces with halo exchanges between layers, ghost forces returned, half kick.  With N GPUs the box is cut
-    into N blocks (strong scaling: the system is the same at every N)."""
+    Maxwell-Boltzmann start at 300 K.  A step = half kick + drift, ghost positions, neighbour list (reused while no
+    atom has moved more than half the skin), energy and forces with halo exchanges between layers, ghost forces
+    returned, half kick.  With N GPUs the box is cut into N blocks (strong scaling: the system is the same at every
+    N).  Collective: every rank calls it; rank 0 gets the result dictionary, the others None."""
     from tace_b200 import synth
     from tace_b200.md import DomainMD, masses_for, maxwell_boltzmann
-    s = synth.workload_structures(args.workload)[0]
+    s = synth.workload_structures(workload)[0]
     model, cfg = build_model(wl, dtype)
     masses = masses_for(s["atomic_numbers"])
     vel = maxwell_boltzmann(masses, 300.0, seed=5)
@@ -244,10 +263,13 @@ def run_md(args, wl, dtype, rank, world, device):
     torch.cuda.synchronize()
     t_setup = time.perf_counter() - t_setup
     e_start = md.potential() + md.kinetic_energy()
-    md.step(args.warmup)
+    md.step(warmup)
     torch.cuda.synchronize()
     launches0 = model.launch_count()
     md.timings.clear()
+    md.domain.set_time_exchanges(True)
+    md.domain.halo_stats(reset=True)
+    rebuilds0 = getattr(md, "n_list_builds", 0)
     sampler = ClockSampler(device.index or 0)
     if rank == 0:
         sampler.start()
@@ -255,7 +277,7 @@ def run_md(args, wl, dtype, rank, world, device):
     barrier(world)
     t0 = time.perf_counter()
     start.record()
-    md.step(args.steps)
+    md.step(steps)
     stop.record()
     torch.cuda.synchronize()
     wall = max_over_ranks(time.perf_counter() - t0, world, device)
@@ -263,65 +285,86 @@ def run_md(args, wl, dtype, rank, world, device):
     total_ms = max_over_ranks(start.elapsed_time(stop), world, device)
     clocks = sampler.stop() if rank == 0 else None
     launches = model.launch_count() - launches0
+    halo_ms, halo_bytes = md.domain.halo_stats()
+    md.domain.set_time_exchanges(False)
+    halo_ms = max_over_ranks(halo_ms, world, device)
+    halo_bytes = sum_over_ranks(float(halo_bytes), world, device)
     e_end = md.potential() + md.kinetic_energy()
     temperature = md.temperature()
-    host_split = {k: round(1e3 * v / args.steps, 3) for k, v in md.timings.items()}
+    host_split = {k: round(1e3 * v / steps, 3) for k, v in md.timings.items()}
     edges = sum_over_ranks(float(md.n_edges), world, device)
     ghosts = sum_over_ranks(float(md.domain.n_ghost), world, device)
-    halo_bytes = sum_over_ranks(float(md.domain.exchange.bytes_sent), world, device)
+    per_rank = gather_floats([float(md.domain.n_owned), float(md.domain.n_ghost), float(md.n_edges)], world, device)
     # per-phase device times of one more evaluation
     model.enable_profile(True)
     md._evaluate()
     phases = model.read_profile()
     model.enable_profile(False)
+    result = None
+    if rank == 0:
+        pk = peaks()
+        plan = model.readout_fn.plan
+        L, C = plan.L, plan.C
+        dims = {"s": 4 if dtype == torch.float32 else 8, "E": int(md.n_edges), "N": md.domain.n_owned + md.domain.n_ghost, "C": C,
+                "D": (L + 1) ** 2, "NM": [sum((2 * l + 1) * lp.k[l] for l in range(L + 1)) for lp in plan.layers],
+                "NP": [len(lp.tp_paths) for lp in plan.layers]}
+        kernel_phases = {k: v for k, v in phases.items() if ".tp" in k}
+        top = max(kernel_phases, key=kernel_phases.get)
+        ab = algorithmic_bytes(top, dims)
+        achieved = ab / (phases[top] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": ab, "ms_per_launch": phases[top],
+                    "note": "all chunk launches of the phase on rank 0 taken together"}
+        value = n_atoms * steps / (total_ms * 1e-3)
+        result = {
+            "metric": "atom-steps/s (MD step)", "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
+            "config": {"workload": workload, "L": L, "channels": C, "cutoff": wl["cutoff"], "elements": len(wl["elements"]),
+                       "atoms": n_atoms, "edges": int(edges), "ghost_atoms": int(ghosts), "grid": list(md.domain.grid.grid),
+                       "parallelism": f"spatial domain decomposition over {world} GPU(s), halo exchange per interaction layer",
+                       "l2": "per-step working set (> 1 GB) exceeds L2", "partitions": md.domain.n_partitions,
+                       "neighbour_list_builds": getattr(md, "n_list_builds", 0) - rebuilds0, "setup_s": round(t_setup, 2),
+                       "radial_table": bool(model.uses_radial_table)},
+            "e2e": {"value": n_atoms * steps / wall, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8,
+                    "note": "state lives on the device; wall clock of the same steps including host-side scheduling"},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
+            "md": {"energy_start_eV": e_start, "energy_end_eV": e_end, "temperature_K": temperature,
+                   "host_ms_per_step": host_split, "exchange_ms_per_step": round(halo_ms / steps, 3),
+                   "halo_bytes_per_step": int(halo_bytes / steps),
+                   "ranks": [{"owned": int(r[0]), "ghosts": int(r[1]), "edges": int(r[2])} for r in per_rank]},
+            "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
+        }
+    model.release()
+    del md, model
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_md(args, wl, dtype, rank, world, device):
+    result = md_measure(args.workload, wl, dtype, rank, world, device, args.steps, args.warmup)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
-    if rank != 0:
-        return
-    pk = peaks()
-    plan = model.readout_fn.plan
-    L, C = plan.L, plan.C
-    dims = {"s": 4 if dtype == torch.float32 else 8, "E": int(md.n_edges), "N": md.domain.n_owned + md.domain.n_ghost, "C": C,
-            "D": (L + 1) ** 2, "NM": [sum((2 * l + 1) * lp.k[l] for l in range(L + 1)) for lp in plan.layers],
-            "NP": [len(lp.tp_paths) for lp in plan.layers]}
-    kernel_phases = {k: v for k, v in phases.items() if ".tp" in k}
-    top = max(kernel_phases, key=kernel_phases.get)
-    ab = algorithmic_bytes(top, dims)
-    achieved = ab / (phases[top] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                "algorithmic_bytes_per_launch": ab, "ms_per_launch": phases[top],
-                "note": "all chunk launches of the phase on rank 0 taken together"}
-    value = n_atoms * args.steps / (total_ms * 1e-3)
-    print(json.dumps({
-        "metric": "atom-steps/s (MD step)", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
-        "config": {"workload": args.workload, "L": L, "channels": C, "cutoff": wl["cutoff"], "elements": len(wl["elements"]),
-                   "atoms": n_atoms, "edges": int(edges), "ghost_atoms": int(ghosts), "grid": list(md.domain.grid.grid),
-                   "parallelism": f"spatial domain decomposition over {world} GPU(s), halo exchange per interaction layer",
-                   "l2": "per-step working set (> 1 GB) exceeds L2", "partitions": md.domain.n_partitions,
-                   "setup_s": round(t_setup, 2)},
-        "e2e": {"value": n_atoms * args.steps / wall, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8,
-                "note": "state lives on the device; wall clock of the same steps including host-side scheduling"},
-        "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
-        "md": {"energy_start_eV": e_start, "energy_end_eV": e_end, "temperature_K": temperature,
-               "host_ms_per_step": host_split, "halo_bytes_sent_total": int(halo_bytes)},
-        "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
-    }))
+    if rank == 0:
+        print(json.dumps(result))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 300 native, 10 reference)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="crystals64_fp32")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-domain-md", action="store_true", help="skip the domain-decomposed MD measurement added to the default line")
+    ap.add_argument("--md-steps", type=int, default=5)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.steps is None:  # a timed region of a second or two for the GPU arm; a few minutes at most for the CPU arm
+        args.steps = 300 if args.impl == "native" else 10
 
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
@@ -333,15 +376,19 @@ def main():
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
 
-    from tace_b200 import synth
+    from tace_b200 import shard, synth
     from tace_b200.graph import build_batch, z_to_index
     wl = synth.WORKLOADS[args.workload]
     dtype = torch.float64 if wl["dtype"] == "float64" else torch.float32
     if args.workload in synth.MD_WORKLOADS:
         run_md(args, wl, dtype, rank, world, device)
         return
+    pool = None
     if args.workload == "crystals64_fp32":
-        structures = synth.random_crystals(64, seed=1 + rank)  # every rank its own batch (weak scaling)
+        # one pool of 64 crystals per GPU (the first 64 are the single-GPU batch), split by estimated edge count
+        pool = synth.random_crystals(64 * world, seed=1)
+        parts = shard.partition_lpt([shard.estimate_edges(c, wl["cutoff"]) for c in pool], world)
+        structures = [pool[i] for i in parts[rank]]
     else:
         structures = synth.workload_structures(args.workload)
     model, cfg = build_model(wl, dtype)
@@ -380,7 +427,8 @@ def main():
     barrier(world)
     step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
     total_ms = max_over_ranks(sum(step_ms), world, device)
-    per_rank = gather_floats([sum(step_ms) / args.steps, 1e3 * host_s / args.steps, float(n_atoms), float(n_edges)], world, device)
+    per_rank = gather_floats([sum(step_ms) / args.steps, 1e3 * host_s / args.steps, float(n_atoms), float(n_edges),
+                              min(step_ms), statistics.median(step_ms), max(step_ms)], world, device)
     clocks = sampler.stop() if rank == 0 else None
     launches = model.launch_count() - launches0
     total_atoms = sum_over_ranks(float(n_atoms), world, device)
@@ -400,9 +448,16 @@ def main():
     # end to end through the public API: pinned host buffers -> upload -> neighbour list -> evaluation -> download
     # The loop is software-pipelined the way a throughput-oriented caller would write it: upload + neighbour list of
     # step k+1 run on a second stream while step k is evaluated; every step still uploads its own inputs from pinned
-    # memory and downloads its own results inside the timed region.
-    e2e_split = {"upload_and_neighbour_list": 0.0, "evaluation_call": 0.0, "download": 0.0}
+    # memory and downloads its own results inside the timed region.  With several GPUs every step ends with one
+    # all_gather of the per-structure energies and stresses of all ranks (shares padded to the largest share).
+    e2e_split = {"upload_and_neighbour_list": 0.0, "evaluation_call": 0.0, "download": 0.0, "gather": 0.0}
     side = torch.cuda.Stream(device)
+    n_graphs = len(structures)
+    share_max = int(max_over_ranks(float(n_graphs), world, device))
+    gather_in = torch.zeros(share_max, 10, dtype=dtype, device=device)
+    gather_out = torch.zeros(world * share_max, 10, dtype=dtype, device=device)
+    host_out = {"energy": torch.empty(n_graphs, dtype=dtype).pin_memory(), "forces": torch.empty(n_atoms, 3, dtype=dtype).pin_memory(),
+                "stress": torch.empty(n_graphs, 3, 3, dtype=dtype).pin_memory()}
 
     def prepare():
         t_a = time.perf_counter()
@@ -414,7 +469,6 @@ def main():
         return d, ready
 
     def e2e_loop(n):
-        res = None
         nxt = prepare()
         for k in range(n):
             d, ready = nxt
@@ -425,23 +479,66 @@ def main():
             if k + 1 < n:
                 nxt = prepare()  # overlaps the evaluation of step k
             t_d = time.perf_counter()
-            res = o["energy"].cpu(), o["forces"].cpu(), o["stress"].cpu()
+            if world > 1:
+                import torch.distributed as dist
+                gather_in[:n_graphs, 0] = o["energy"]
+                gather_in[:n_graphs, 1:] = o["stress"].reshape(n_graphs, 9)
+                dist.all_gather_into_tensor(gather_out, gather_in)
+            t_e = time.perf_counter()
+            for key in host_out:  # one asynchronous copy per result into pinned memory, one synchronisation
+                host_out[key].copy_(o[key], non_blocking=True)
+            torch.cuda.current_stream(device).synchronize()
             e2e_split["evaluation_call"] += t_c - t_b
-            e2e_split["download"] += time.perf_counter() - t_d
-        return res
+            e2e_split["gather"] += t_e - t_d
+            e2e_split["download"] += time.perf_counter() - t_e
+        return host_out
 
+    e2e_steps = min(args.steps, 100)
     e2e_loop(args.warmup)
     barrier(world)
     for key in e2e_split:
         e2e_split[key] = 0.0
     t0 = time.perf_counter()
-    res = e2e_loop(args.steps)
+    res = e2e_loop(e2e_steps)
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
     barrier(world)
     h2d = sum(int(pinned[k].numel() * pinned[k].element_size()) for k in ("positions", "lattice", "pbc", "ptr", "species", "batch"))
-    d2h = sum(int(t.numel() * t.element_size()) for t in res)
-    e2e_value = total_atoms * args.steps / e2e_s
+    d2h = sum(int(t.numel() * t.element_size()) for t in res.values())
+    e2e_value = total_atoms * e2e_steps / e2e_s
+
+    # CPU leg on rank 0 (N = 1 only): the oracle on the fixed sample, timed, and compared with the GPU result for the
+    # very same crystals (the sample's crystals evaluated by the GPU as a batch of their own)
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        oracle, cdata, c_atoms, sample, cores, chosen = cpu_sample(structures, wl, dtype, model.state_dict())
+        ref = oracle(cdata)
+        t0 = time.perf_counter()
+        for _ in range(2):
+            oracle(cdata)
+        dt = (time.perf_counter() - t0) / 2
+        gpu = model({k: v.to(device) for k, v in cdata.items()})
+        n_per = (cdata["ptr"][1:] - cdata["ptr"][:-1]).to(torch.float64)
+        cpu = {"value": c_atoms / dt, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": sample + ", 2 timed evaluations of the PyTorch CPU restatement with autograd forces",
+               "max_abs_dE_per_atom": float(((gpu["energy"].cpu().double() - ref["energy"].double()).abs() / n_per).max()),
+               "max_abs_dF": float((gpu["forces"].cpu().double() - ref["forces"].double()).abs().max())}
+
+    plan = model.readout_fn.plan
+    L, C = plan.L, plan.C
+    uses_table = bool(model.uses_radial_table)
+    graph_replays = model.graph_replays()
+    # the domain-decomposed MD measurement of configuration 5 on the same GPUs (strong scaling)
+    domain_md = None
+    if args.workload == "crystals64_fp32" and not args.no_domain_md:
+        del out, data
+        model.release()
+        torch.cuda.empty_cache()
+        md_wl = synth.WORKLOADS["cual1m_fp32"]
+        domain_md = md_measure("cual1m_fp32", md_wl, torch.float32, rank, world, device, args.md_steps, 3)
+        if domain_md is not None:
+            for key in ("roofline", "cpu_baseline", "higher_is_better", "vs_baseline", "data", "unit"):
+                domain_md.pop(key, None)
 
     if world > 1:
         import torch.distributed as dist
@@ -450,8 +547,6 @@ def main():
         return
 
     pk = peaks()
-    plan = model.readout_fn.plan
-    L, C = plan.L, plan.C
     dims = {"s": 4 if dtype == torch.float32 else 8, "E": n_edges, "N": n_atoms, "C": C, "D": (L + 1) ** 2,
             "NM": [sum((2 * l + 1) * lp.k[l] for l in range(L + 1)) for lp in plan.layers],
             "NP": [len(lp.tp_paths) for lp in plan.layers]}
@@ -462,7 +557,7 @@ def main():
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as fh:
-            traffic = json.load(fh).get(f"{args.workload}:{top}")
+            traffic = json.load(fh).get(f"{args.workload}:{top}" + (":table" if uses_table else ""))
     ab = algorithmic_bytes(top, dims)
     layer = int(top[1]) if top[1].isdigit() else 0
     if ".tp" in top and layer in plan.tece_layers:
@@ -489,35 +584,28 @@ def main():
                     "frac": achieved / pk["bf16_tflops"], "traffic": traffic, "peak_source": pk["source"],
                     "flops_per_launch": fl, "ms_per_launch": phases[top]}
 
-    cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        oracle, cdata, c_atoms, c_struct, cores = cpu_sample(structures, wl, dtype, model.state_dict(), 20.0, 3)
-        oracle(cdata)
-        t0 = time.perf_counter()
-        for _ in range(2):
-            oracle(cdata)
-        dt = (time.perf_counter() - t0) / 2
-        cpu = {"value": c_atoms / dt, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": (f"a smaller cell of the same material ({wl['cpu_sample']})" if wl.get("cpu_sample")
-                          else f"{c_struct} smallest crystals of the batch") + f" ({c_atoms} atoms, {cdata['edge_index'].shape[1]} edges), "
-                         f"2 timed evaluations of the PyTorch CPU restatement with autograd forces"}
-
+    sharding = (f"dp{world}: one pool of {64 * world} crystals split by estimated edge count (longest-processing-time rule), "
+                "replicated weights, no data-path collective; per-structure results gathered with one all_gather per step in e2e"
+                if pool is not None else f"dp{world}")
     print(json.dumps({
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
         "config": {"workload": args.workload, "L": L, "channels": C, "cutoff": wl["cutoff"], "elements": len(wl["elements"]),
                    "atoms_per_gpu": n_atoms, "edges_per_gpu": n_edges, "graphs_per_gpu": len(structures),
-                   "parallelism": f"dp{world} (independent batches, no data-path collective)",
+                   "atoms_total": int(total_atoms), "parallelism": sharding,
+                   "radial_weights": "tabulated (cubic Hermite, 512 intervals)" if uses_table else "radial MLP per edge",
                    "l2": "flushed between timed steps (256 MiB write outside the per-step CUDA-event pair)"},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        "step_ms": {"min": min(r[4] for r in per_rank), "median": statistics.median(step_ms), "max": max(r[6] for r in per_rank)},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "pipelining": "upload + neighbour list of step k+1 on a second stream during the evaluation of step k"},
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
-        "ranks": [{"device_ms_per_step": round(r[0], 3), "host_ms_per_call": round(r[1], 3), "atoms": int(r[2]), "edges": int(r[3])}
-                  for r in per_rank],
-        "graph_replays": model.graph_replays(),
-        "e2e_host_ms_per_step": {k: round(1e3 * v / args.steps, 3) for k, v in e2e_split.items()},
+        "ranks": [{"device_ms_per_step": round(r[0], 3), "host_ms_per_call": round(r[1], 3), "atoms": int(r[2]), "edges": int(r[3]),
+                   "step_ms_min": round(r[4], 3), "step_ms_median": round(r[5], 3), "step_ms_max": round(r[6], 3)} for r in per_rank],
+        "graph_replays": graph_replays,
+        "e2e_host_ms_per_step": {k: round(1e3 * v / e2e_steps, 3) for k, v in e2e_split.items()},
+        "domain_md": domain_md,
     }))
 
 

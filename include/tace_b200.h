@@ -101,6 +101,14 @@ typedef struct {
      (attention scale * temperature), "t<i>.att.rw" [8][2 heads], "t<i>.att.rb" [2 heads]; the radial MLP of such a layer
      emits [rows per order][2 num_channel] weights */
   int tece_layers, mmax, num_head, edge_ace_hidden, edge_act;
+  /* Tabulated radial weights (no reference counterpart; the reference evaluates the radial MLP for every edge,
+     tace/models/_e3nn/inter.py:166-183).  With the identity edge update the MLP's output is a function of the edge
+     length alone, so it can be read from a table: radial_table = K > 0 makes tace_forward interpolate the path weights
+     of every interaction from "t<i>.rtab" [K][paths * num_channel][4] = (W, h dW/dd) at d = k h and at d = (k + 1) h,
+     h = cutoff / K (cubic Hermite on interval k), inside the tensor-product kernels; no per-edge weight or hidden activation is
+     stored and the radial MLP is never launched.  TACE_F32 models only, not with edge_update_element2 or tece_layers.
+     0: the radial MLP runs per edge. */
+  int radial_table;
 } TaceConfig;
 
 /* One batch of structures on the device.  Stands behind the `data` dictionary consumed by
@@ -290,6 +298,10 @@ int tace_nl_build_noalloc(const double* positions, const double* lattice, const 
  * tace_edge_vectors: out[e] = positions[target_e] - positions[source_e] evaluated in fp64 and rounded to
  *   `dtype` (edge_index int64 [2,n_edges], row 0 = source); the edge-vector input of tace_forward
  *   (tace/models/adapter.py:341-352 computes the same difference in the model dtype).
+ * tace_edges_within: keep[e] = 1 where |positions[target_e] - positions[source_e]|^2 < cutoff^2, in fp64 with the
+ *   neighbour-list kernel's operation order: filters a list built with cutoff + skin down to the edges a fresh list
+ *   with `cutoff` would hold (LAMMPS keeps such a skin list, `neighbor 2.0 bin`, docs/source/guide/lammps.rst:125;
+ *   the reference's ASE calculator rebuilds its list on every call, tace/interface/ase/calculator.py:132-152).
  * tace_rows_gather: dst[r,:] = src[index[r],:] for r < n_rows (packs a halo message; elem_bytes 4 or 8).
  * tace_rows_scatter_add: dst[index[r],:] += src[r,:]; the indices of one call must be distinct (unpacks
  *   gradients returned by a neighbouring domain, tace/models/lammps.py:105-129); float / double rows. */
@@ -300,6 +312,8 @@ int tace_md_langevin(double* velocities, const double* inv_mass, const int64_t* 
 int tace_md_kinetic_energy(const double* velocities, const double* mass, int64_t n_atoms, double* scratch, double* out,
                            tace_stream_t stream);
 int tace_edge_vectors(const double* positions, const int64_t* edge_index, int64_t n_edges, void* out, int32_t dtype,
+                      tace_stream_t stream);
+int tace_edges_within(const double* positions, const int64_t* edge_index, int64_t n_edges, double cutoff, uint8_t* keep,
                       tace_stream_t stream);
 int tace_rows_gather(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,
                      tace_stream_t stream);

@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/tace_b200.h"
@@ -336,6 +337,7 @@ struct Model : ModelBase {
   bool bilinear = false;      // product_basis.nonlinear = silu_bilineargate: gated product of two linear images of A
   // TECE edge block: layers (bit t), orders kept, heads, width of the cluster expansion, activation (0 sigmoid, 1 SiLU)
   int tece_mask = 0, mmax = 2, heads = 1, Ca = 0, edge_act = 0;
+  int rt_K = 0;               // > 0: path weights interpolated from per-layer tables with rt_K intervals (TaceConfig.radial_table)
   int t_NR = 0, t_NC = 0, t_NF = 0, t_G = 0, t_np = 0, t_WN = 0;  // rows (order-major / per weight / full), gates, paths, coefficients
   int t_k[4] = {1, 1, 1, 1}, t_base[4] = {0, 1, 4, 9};            // message layout of a TECE layer: one block of C per rank
   int t_row_l[16], t_row_m[16], t_row_comp[16]; double t_row_scale[16];
@@ -384,6 +386,9 @@ struct Model : ModelBase {
     res_identity = c.resnet_identity != 0;
     bilinear = c.product_bilinear != 0;
     tece_mask = c.tece_layers; mmax = c.mmax; heads = c.num_head > 0 ? c.num_head : 1;
+    rt_K = c.radial_table;
+    if (rt_K < 0 || (rt_K > 0 && (!std::is_same<T, float>::value || element2 || tece_mask || rt_K > (1 << 16))))
+      return TACE_ERR_UNSUPPORTED_CONFIG;
     Ca = c.edge_ace_hidden > 0 ? c.edge_ace_hidden : c.num_channel; edge_act = c.edge_act;
     if (tece_mask) {
       // the block needs ranks above 0 on its input (not the first layer), node rank = edge rank, orders <= 2
@@ -450,6 +455,7 @@ struct Model : ModelBase {
       const std::string pre = "t" + std::to_string(t) + ".";
       for (int l : p.in_ls) { add_linear_weight(pre + "up.l" + std::to_string(l), (long long)C * C); add_linear_weight(pre + "upT.l" + std::to_string(l), (long long)C * C); }
       add_weight(pre + "up.b", C);
+      if (rt_K) add_weight(pre + "rtab", (long long)rt_K * p.tp.NP * C * 4);
       add_weight(pre + "A0", kNumBessel * kHidden);
       if (nh >= 2) { add_linear_weight(pre + "A1", kHidden * kHidden); add_linear_weight(pre + "A1t", kHidden * kHidden); }
       if (nh >= 3) { add_linear_weight(pre + "A2", kHidden * kHidden); add_linear_weight(pre + "A2t", kHidden * kHidden); }
@@ -616,7 +622,7 @@ struct Model : ModelBase {
     b.dxe = NL_ > 1 ? ar.take<T>((size_t)Ec * D * C) : nullptr;  // per-edge gradient rows of the source features
     T* shared_edge[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     T* shared_W = nullptr;
-    if (chunked) {  // one set of chunk-sized per-edge buffers serves every layer
+    if (chunked && !rt_K) {  // one set of chunk-sized per-edge buffers serves every layer
       for (int k = 0; k < 5; ++k) shared_edge[k] = ar.take<T>((size_t)Ec * kHidden);
       int np_max = 0;
       for (const auto& p : layers) np_max = p.tp.NP > np_max ? p.tp.NP : np_max;
@@ -635,12 +641,16 @@ struct Model : ModelBase {
       const bool ghosts = (N != NL) && !p.scalar_src;  // exchanged copies of x and of its gradient
       lb.xx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
       lb.gxx = ghosts ? ar.take<T>((size_t)N * p.tp.NX * C) : nullptr;
-      lb.H3 = chunked ? shared_edge[0] : ar.take<T>((size_t)E * kHidden);
-      lb.Z1 = chunked ? shared_edge[1] : ar.take<T>((size_t)E * kHidden);
-      lb.Z2 = chunked ? shared_edge[2] : ar.take<T>((size_t)E * kHidden);
-      lb.Z3 = chunked ? shared_edge[3] : ar.take<T>((size_t)E * kHidden);
-      lb.Hact = chunked ? shared_edge[4] : ar.take<T>((size_t)E * kHidden);
-      lb.W = chunked ? shared_W : ar.take<T>((size_t)E * p.tp.NP * C);
+      if (rt_K) {  // tabulated radial weights: no per-edge activation or weight exists
+        lb.H3 = lb.Z1 = lb.Z2 = lb.Z3 = lb.Hact = lb.W = nullptr;
+      } else {
+        lb.H3 = chunked ? shared_edge[0] : ar.take<T>((size_t)E * kHidden);
+        lb.Z1 = chunked ? shared_edge[1] : ar.take<T>((size_t)E * kHidden);
+        lb.Z2 = chunked ? shared_edge[2] : ar.take<T>((size_t)E * kHidden);
+        lb.Z3 = chunked ? shared_edge[3] : ar.take<T>((size_t)E * kHidden);
+        lb.Hact = chunked ? shared_edge[4] : ar.take<T>((size_t)E * kHidden);
+        lb.W = chunked ? shared_W : ar.take<T>((size_t)E * p.tp.NP * C);
+      }
       lb.M = ar.take<T>((size_t)NL * p.tp.NM * C);
       lb.Gt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
       lb.gGt = ar.take<T>((size_t)NL * (L + 1 + D) * C);
@@ -937,7 +947,7 @@ struct Model : ModelBase {
   // radial MLP hidden layers 8 -> 64 -> 64 -> 64 (tace/models/mlp.py:136-191): the first layer per edge, the
   // two 64 x 64 layers as GEMMs over the edges (all layers of `ts` in one launch), SiLU in between
   int radial_forward(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec, cudaStream_t s) {
-    if (Ec <= 0) return TACE_OK;
+    if (Ec <= 0 || rt_K) return TACE_OK;  // tabulated weights: the radial MLP never runs
     const EdgeArgs<T> er = edge_range(ea, b, ts, e0, Ec);
     CKL(launch_edge_mlp_in(er, s));
     const long long n64 = Ec * kHidden;
@@ -973,6 +983,16 @@ struct Model : ModelBase {
   int radial_backward(const EdgeArgs<T>& ea, const Bufs& b, const std::vector<int>& ts, long long e0, long long Ec, int accumulate,
                       cudaStream_t s) {
     if (Ec <= 0) return TACE_OK;
+    if (rt_K) {
+      // Tabulated weights: the tensor-product backward passes added their dE/d(edge length) to ddlen already; what is
+      // left of this stage is the envelope's own derivative (apply_cutoff = False), once, with the last layer processed.
+      const bool last_call = ts.size() > 1 || NL_ == 1 || ts[0] == 0;
+      if (!last_call || !ea.denv) return TACE_OK;
+      EdgeArgs<T> er = edge_range(ea, b, std::vector<int>{}, e0, Ec);
+      er.accumulate_ddlen = 1; er.add_denv = 1;
+      CKL(launch_edge_mlp_out(er, s));
+      return TACE_OK;
+    }
     const long long n64 = Ec * kHidden;
     // gradient buffer chain: H3 -> Hact -> Z3 (three hidden layers), H3 -> Hact (two), H3 (one); the first layer's
     // activation derivative is applied by launch_edge_mlp_out
@@ -1015,7 +1035,7 @@ struct Model : ModelBase {
   }
   // last radial-MLP layer for edges [e0, e0 + Ec): W[e, :] = H3[e, :] @ W3 (forward) or dH3[e, :] = dW[e, :] @ W3^T
   int radial_last(const LayerPlan& p, const LayerBufs& lb, const std::string& pre, long long Ec, bool backward, cudaStream_t s) {
-    if (Ec <= 0) return TACE_OK;
+    if (Ec <= 0 || rt_K) return TACE_OK;  // tabulated weights: the radial MLP never runs
     const int NW = p.tp.NP * C;
     if (kTensorCore && NW % 64 == 0) {
       if (!backward)
@@ -1201,6 +1221,7 @@ struct Model : ModelBase {
         ta.L = L; ta.scalar_src = p.scalar_src; ta.Lin = Ln; ta.C = C; ta.n_seg = na; ta.rowptr = b.rowptr_dst + a0;
         ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M + (long long)a0 * p.tp.NM * C; ta.e_base = e0;
         ta.env = b.env;
+        if (rt_K) { ta.rtab = w(pre + "rtab"); ta.rt_K = rt_K; ta.rt_inv_h = T(rt_K) / T(cfg.cutoff); ta.dlen = b.dlen; }
         CKL(launch_tp_fwd(ta, s));
       }
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
@@ -1460,6 +1481,10 @@ struct Model : ModelBase {
         ta.rowptr = b.rowptr_dst + a0; ta.dW = lb.W; ta.dY = b.dY; ta.e_base = e0;
         ta.accumulate_dY = (t != NL_ - 1); ta.dxe = p.scalar_src ? nullptr : b.dxe;
         ta.env = b.env; ta.denv = b.denv; ta.accumulate_denv = (t != NL_ - 1);
+        if (rt_K) {
+          ta.rtab = w(pre + "rtab"); ta.rt_K = rt_K; ta.rt_inv_h = T(rt_K) / T(cfg.cutoff); ta.dlen = b.dlen;
+          ta.dW = nullptr; ta.ddlen = b.ddlen; ta.accumulate_ddlen = (t != NL_ - 1);
+        }
         CKL(launch_tp_bwd(ta, s));
         if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
           PH(("t" + ts + ".bwd.src_sum").c_str());

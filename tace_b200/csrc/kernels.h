@@ -37,6 +37,15 @@ struct TPArgs {
   T* denv;            // [E] or nullptr
   int accumulate_denv;
   long long e_base;   // W, dW and dxe hold the rows of edges [e_base, ...) only (edge-chunked passes); Y, dY, e_src are whole
+  // Tabulated path weights (models with the identity edge update, where the radial MLP's output is a function of the
+  // edge length alone): rtab [rt_K][NP*C][4] = (W, h dW/dd) at both ends of the interval [k h, (k + 1) h], read with cubic
+  // Hermite interpolation instead of W; the backward pass then writes no dW and adds sum_{p,c} dW * dW/dd into ddlen.
+  const T* rtab;      // nullptr: per-edge weights W / dW as above
+  int rt_K;           // number of intervals
+  T rt_inv_h;         // 1 / knot spacing
+  const T* dlen;      // [E] edge lengths
+  T* ddlen;           // [E] dE/d(edge length), backward
+  int accumulate_ddlen;
 };
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_tp_bwd(const TPArgs<T>& a, cudaStream_t s);

@@ -166,6 +166,30 @@ extern "C" int tace_edge_vectors(const double* positions, const int64_t* edge_in
   return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }
 
+// keep[e] = 1 where |r_target - r_source|^2 < cutoff^2, evaluated in fp64 with the neighbour-list kernel's own
+// operation order (separately rounded products and sums), so a filtered skin list holds exactly the edges a fresh
+// list with this cutoff would hold.
+__global__ void edges_within_kernel(const double* __restrict__ pos, const long long* __restrict__ edge_index, long long n_edges,
+                                    double cutoff, unsigned char* __restrict__ keep) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= n_edges) return;
+  const long long s = edge_index[e], t = edge_index[n_edges + e];
+  const double dx = __dadd_rn(pos[3 * t], -pos[3 * s]);
+  const double dy = __dadd_rn(pos[3 * t + 1], -pos[3 * s + 1]);
+  const double dz = __dadd_rn(pos[3 * t + 2], -pos[3 * s + 2]);
+  const double dsq = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+  keep[e] = dsq < __dmul_rn(cutoff, cutoff) ? 1 : 0;
+}
+
+extern "C" int tace_edges_within(const double* positions, const int64_t* edge_index, int64_t n_edges, double cutoff,
+                                 uint8_t* keep, tace_stream_t stream) {
+  if (n_edges < 0 || !(cutoff > 0.0) || (n_edges > 0 && (!positions || !edge_index || !keep))) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_edges == 0) return TACE_OK;
+  edges_within_kernel<<<(unsigned)((n_edges + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      positions, reinterpret_cast<const long long*>(edge_index), n_edges, cutoff, keep);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
 namespace {
 template <bool GATHER>
 int rows_dispatch(const void* src, const int64_t* idx, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,

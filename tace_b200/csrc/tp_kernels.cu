@@ -37,13 +37,52 @@ __device__ __forceinline__ void build_G_rows(const T* __restrict__ Y, int e0, in
 
 // ENV: the path weights are multiplied by the per-edge envelope (radial_basis.apply_cutoff = False); a separate
 // instantiation so the default kernels carry none of its registers.
-template <typename T, typename TP, int GRP, bool ENV>
+// Cubic Hermite interpolation of the tabulated path weights: knot index and the four basis values of one edge
+// (and, for the backward pass, the basis derivatives with respect to the edge length).
+template <typename T>
+struct RtEdge {
+  int k;
+  T b[4];
+  T d[4];
+};
+template <typename T, bool DERIV>
+__device__ __forceinline__ void rt_prepare(const TPArgs<T>& a, T d, RtEdge<T>& r) {
+  const T u = d * a.rt_inv_h;
+  int k = (int)u;
+  k = k < 0 ? 0 : (k > a.rt_K - 1 ? a.rt_K - 1 : k);
+  const T t = u - T(k), t2 = t * t, t3 = t2 * t;
+  r.k = k;
+  r.b[0] = T(2) * t3 - T(3) * t2 + T(1);
+  r.b[1] = t3 - T(2) * t2 + t;
+  r.b[2] = T(3) * t2 - T(2) * t3;
+  r.b[3] = t3 - t2;
+  if (DERIV) {
+    r.d[0] = (T(6) * t2 - T(6) * t) * a.rt_inv_h;
+    r.d[1] = (T(3) * t2 - T(4) * t + T(1)) * a.rt_inv_h;
+    r.d[2] = (T(6) * t - T(6) * t2) * a.rt_inv_h;
+    r.d[3] = (T(3) * t2 - T(2) * t) * a.rt_inv_h;
+  }
+}
+// One table entry = (W_k, h W'_k, W_{k+1}, h W'_{k+1}) of a (path, channel) pair for the interval [d_k, d_{k+1}]: the
+// four numbers the interpolation needs, in one 16-byte load.
+template <typename T>
+__device__ __forceinline__ void rt_load(const T* p, T& v0, T& m0, T& v1, T& m1) { v0 = p[0]; m0 = p[1]; v1 = p[2]; m1 = p[3]; }
+template <>
+__device__ __forceinline__ void rt_load<float>(const float* p, float& v0, float& m0, float& v1, float& m1) {
+  const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+  v0 = q.x; m0 = q.y; v1 = q.z; m1 = q.w;
+}
+
+// RT: path weights interpolated from the table a.rtab instead of read from a.W.
+template <typename T, typename TP, int GRP, bool ENV, bool RT>
 __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
   constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
   constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   __shared__ __align__(16) T Gs[kEdgeBatch * TP::NG];
   __shared__ int esrc[kEdgeBatch];
+  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
+  const int rt_first = blockDim.x > 32 ? 32 : 0;  // the second warp (when there is one) prepares the interpolation
   T acc[NMG];
 #pragma unroll
   for (int k = 0; k < NMG; ++k) acc[k] = T(0);
@@ -52,6 +91,8 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
     if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
+    if (RT && (int)threadIdx.x >= rt_first && (int)threadIdx.x < rt_first + nb)
+      rt_prepare<T, false>(a, a.dlen[e0 + threadIdx.x - rt_first], rts[threadIdx.x - rt_first]);
     build_G_rows<T, TP>(a.Y, e0, nb, 2 * GRP, 2, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
@@ -59,9 +100,20 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
       T xv[TP::NX], wv[NPG];
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) xv[k] = a.x[(s * TP::NX + k) * C + c];
-      const T* We = a.W + ((long long)(e0 + e - a.e_base) * TP::NP + P0) * C;
+      if constexpr (RT) {
+        const T* r0 = a.rtab + ((long long)rts[e].k * TP::NP * C + (long long)P0 * C + c) * 4;
+        const T b0 = rts[e].b[0], b1 = rts[e].b[1], b2 = rts[e].b[2], b3 = rts[e].b[3];
 #pragma unroll
-      for (int p = 0; p < NPG; ++p) wv[p] = We[p * C + c];
+        for (int p = 0; p < NPG; ++p) {
+          T v0, m0, v1, m1;
+          rt_load<T>(r0 + (long long)p * C * 4, v0, m0, v1, m1);
+          wv[p] = b0 * v0 + b1 * m0 + b2 * v1 + b3 * m1;
+        }
+      } else {
+        const T* We = a.W + ((long long)(e0 + e - a.e_base) * TP::NP + P0) * C;
+#pragma unroll
+        for (int p = 0; p < NPG; ++p) wv[p] = We[p * C + c];
+      }
       if constexpr (ENV) {
         const T u = a.env[e0 + e];
 #pragma unroll
@@ -77,8 +129,8 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
 }
 
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
-template <typename T, typename TP, bool ENV>
-__global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
+template <typename T, typename TP, bool ENV, bool RT>
+__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,7 +138,10 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
   T* Gs = gMs + TP::NM * C;                          // [kEdgeBatch][NG]
   T* red = Gs + kEdgeBatch * TP::NG;                 // [kEdgeBatch][8 warps][D]
   __shared__ T red_u[kEdgeBatch * 8];                // envelope-gradient partial sums
+  __shared__ T red_r[RT ? kEdgeBatch * 8 : 1];       // edge-length-gradient partial sums (tabulated weights)
+  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
   __shared__ int esrc[kEdgeBatch];
+  const int rt_first = blockDim.x > 32 ? 32 : 0;  // the second warp (when there is one) prepares the interpolation
   const T* gMi = a.gM + (long long)i * TP::NM * C;
   for (int k = 0; k < TP::NM; ++k) gMs[k * C + c] = gMi[k * C + c];  // each thread later reads only its own column
   const int beg = a.rowptr[i], end = a.rowptr[i + 1];
@@ -94,6 +149,8 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
     if (threadIdx.x < nb) esrc[threadIdx.x] = a.e_src[e0 + threadIdx.x];
+    if (RT && (int)threadIdx.x >= rt_first && (int)threadIdx.x < rt_first + nb)
+      rt_prepare<T, true>(a, a.dlen[e0 + threadIdx.x - rt_first], rts[threadIdx.x - rt_first]);
     build_G_rows<T, TP>(a.Y, e0, nb, 0, TP::NPART, Gs);
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
@@ -102,8 +159,19 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) { xv[k] = a.x[(s * TP::NX + k) * C + c]; dx[k] = T(0); }
       const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C;
+      const T* rt0 = RT ? a.rtab + ((long long)rts[e].k * TP::NP * C + c) * 4 : nullptr;
+      if constexpr (RT) {
+        const T b0 = rts[e].b[0], b1 = rts[e].b[1], b2 = rts[e].b[2], b3 = rts[e].b[3];
 #pragma unroll
-      for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
+        for (int p = 0; p < TP::NP; ++p) {
+          T v0, m0, v1, m1;
+          rt_load<T>(rt0 + (long long)p * C * 4, v0, m0, v1, m1);
+          wv[p] = b0 * v0 + b1 * m0 + b2 * v1 + b3 * m1;
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
+      }
 #pragma unroll
       for (int k = 0; k < TP::D; ++k) dYp[k] = T(0);
       T u = T(1);
@@ -119,8 +187,19 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
         for (int p = 0; p < TP::NP; ++p) { du_part += dw[p] * wv[p]; dw[p] *= u; }
         du_part = u > T(0) ? du_part / u : T(0);
       }
+      T dr_part = T(0);  // sum_p dW[p] * dW[p]/dd of this channel
+      if constexpr (RT) {  // the table rows were read a moment ago (L1); reading them again costs fewer registers than keeping them
+        const T d0 = rts[e].d[0], d1 = rts[e].d[1], d2 = rts[e].d[2], d3 = rts[e].d[3];
 #pragma unroll
-      for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
+        for (int p = 0; p < TP::NP; ++p) {
+          T v0, m0, v1, m1;
+          rt_load<T>(rt0 + (long long)p * C * 4, v0, m0, v1, m1);
+          dr_part += dw[p] * (d0 * v0 + d1 * m0 + d2 * v1 + d3 * m1);
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
+      }
       if (a.dxe) {
         T* out = a.dxe + (long long)(e0 + e - a.e_base) * TP::NX * C;
 #pragma unroll
@@ -139,6 +218,12 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         if (lane == 0) red_u[e * 8 + warp] = v;
       }
+      if constexpr (RT) {  // and for the edge-length gradient through the tabulated weights
+        T v = dr_part;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) red_r[e * 8 + warp] = v;
+      }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nb * TP::D; idx += blockDim.x) {
@@ -153,6 +238,13 @@ __global__ void __maxnreg__(152) tp_bwd_kernel(const TPArgs<T> a) {
       for (int w = 0; w < nwarp; ++w) v += red_u[threadIdx.x * 8 + w];
       T* dst = a.denv + (e0 + threadIdx.x);
       *dst = a.accumulate_denv ? (*dst + v) : v;
+    }
+    if (RT && (int)threadIdx.x >= rt_first && (int)threadIdx.x < rt_first + nb) {
+      const int e = threadIdx.x - rt_first;
+      T v = T(0);
+      for (int w = 0; w < nwarp; ++w) v += red_r[e * 8 + w];
+      T* dst = a.ddlen + (e0 + e);
+      *dst = a.accumulate_ddlen ? (*dst + v) : v;
     }
   }
 }
@@ -199,33 +291,44 @@ cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const int* keys, const int*
   return cudaGetLastError();
 }
 
+template <typename T, typename TP, bool ENV, bool RT>
+cudaError_t launch_fwd_v(const TPArgs<T>& a, cudaStream_t s) {
+  tp_fwd_kernel<T, TP, 0, ENV, RT><<<a.n_seg, a.C, 0, s>>>(a);
+  if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, ENV, RT><<<a.n_seg, a.C, 0, s>>>(a);
+  return cudaGetLastError();
+}
 template <typename T, typename TP>
 cudaError_t launch_fwd_t(const TPArgs<T>& a, cudaStream_t s) {
-  if (a.env) {
-    tp_fwd_kernel<T, TP, 0, true><<<a.n_seg, a.C, 0, s>>>(a);
-    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, true><<<a.n_seg, a.C, 0, s>>>(a);
-  } else {
-    tp_fwd_kernel<T, TP, 0, false><<<a.n_seg, a.C, 0, s>>>(a);
-    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, false><<<a.n_seg, a.C, 0, s>>>(a);
+  if (a.rtab) {
+    if (!a.dlen || a.rt_K < 1) return cudaErrorInvalidValue;
+    return a.env ? launch_fwd_v<T, TP, true, true>(a, s) : launch_fwd_v<T, TP, false, true>(a, s);
   }
+  return a.env ? launch_fwd_v<T, TP, true, false>(a, s) : launch_fwd_v<T, TP, false, false>(a, s);
+}
+template <typename T, typename TP, bool RT>
+cudaError_t launch_bwd_v(const TPArgs<T>& a, size_t smem, cudaStream_t s) {
+  static size_t configured[64] = {};  // the attribute belongs to a device: one slot per device ordinal
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024 && smem > configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = smem;
+  }
+  if (a.env) tp_bwd_kernel<T, TP, true, RT><<<a.n_seg, a.C, smem, s>>>(a);
+  else tp_bwd_kernel<T, TP, false, RT><<<a.n_seg, a.C, smem, s>>>(a);
   return cudaGetLastError();
 }
 template <typename T, typename TP>
 cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
   const size_t smem = sizeof(T) * ((size_t)TP::NM * a.C + kEdgeBatch * TP::NG + kEdgeBatch * 8 * TP::D);
   if (a.env && !a.denv) return cudaErrorInvalidValue;
-  static size_t configured[64] = {};  // the attribute belongs to a device: one slot per device ordinal
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidValue;
-  if (smem > 48 * 1024 && smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured[dev] = smem;
+  if (a.rtab) {
+    if (!a.dlen || !a.ddlen || a.rt_K < 1) return cudaErrorInvalidValue;
+    return launch_bwd_v<T, TP, true>(a, smem, s);
   }
-  if (a.env) tp_bwd_kernel<T, TP, true><<<a.n_seg, a.C, smem, s>>>(a);
-  else tp_bwd_kernel<T, TP, false><<<a.n_seg, a.C, smem, s>>>(a);
-  return cudaGetLastError();
+  return launch_bwd_v<T, TP, false>(a, smem, s);
 }
 
 #define TACE_TP_DISPATCH(FN)                                              \

@@ -208,6 +208,25 @@ class HaloExchange:
         self.group = group
         self.calls = 0
         self.bytes_sent = 0
+        self.timed = False      # record a CUDA event pair around every exchange (read with exchange_ms)
+        self._events = []
+
+    def _mark(self, tensor: torch.Tensor):
+        if not (self.timed and tensor.is_cuda):
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(tensor.device))
+        return ev
+
+    def exchange_ms(self, reset: bool = True) -> float:
+        """Device time spent between the start and the end of every exchange since the last reset (synchronises)."""
+        total = 0.0
+        for a, b in self._events:
+            b.synchronize()
+            total += a.elapsed_time(b)
+        if reset:
+            self._events = []
+        return total
 
     # -- helpers -----------------------------------------------------------------------------------
     @staticmethod
@@ -258,6 +277,7 @@ class HaloExchange:
     def forward_exchange(self, src: torch.Tensor, dst: torch.Tensor, vec_len: int = 0) -> None:
         p = self.plan
         n = p.n_owned
+        t_start = self._mark(src)
         src2, dst2 = src.reshape(src.shape[0], -1), dst.reshape(dst.shape[0], -1)
         if dst2.data_ptr() != src2.data_ptr():
             dst2[:n].copy_(src2[:n])
@@ -275,10 +295,13 @@ class HaloExchange:
                 recvs.append((dst2[n + off:n + off + cnt], q))
         self._p2p(sends, recvs)
         self.calls += 1
+        if t_start is not None:
+            self._events.append((t_start, self._mark(src)))
 
     def reverse_exchange(self, src: torch.Tensor, dst: torch.Tensor, vec_len: int = 0) -> None:
         p = self.plan
         n = p.n_owned
+        t_start = self._mark(src)
         src2, dst2 = src.reshape(src.shape[0], -1), dst.reshape(dst.shape[0], -1)
         if dst2.data_ptr() != src2.data_ptr():
             dst2.copy_(src2)
@@ -301,6 +324,8 @@ class HaloExchange:
             if q in landed:
                 self._add_rows(dst2, q, landed[q])
         self.calls += 1
+        if t_start is not None:
+            self._events.append((t_start, self._mark(src)))
 
 
 class Domain:
@@ -330,6 +355,8 @@ class Domain:
         self.exchange: Optional[HaloExchange] = None
         self.reference_positions: Optional[torch.Tensor] = None
         self.n_partitions = 0
+        self.time_exchanges = False  # CUDA-event timing of every exchange (halo_stats)
+        self._halo_ms, self._halo_bytes = 0.0, 0
 
     def _all_gather_rows(self, x: torch.Tensor) -> List[torch.Tensor]:
         """Every rank's rows of ``x`` ([n_r, ...], n_r differs per rank)."""
@@ -369,11 +396,31 @@ class Domain:
         new_state = {k: v[mine].clone() for k, v in gathered.items()}
         new_state["positions"] = (frac[mine] @ self.cell).contiguous()
         self.plan = build_halo_plan(self.grid, self.rank, frac_by_rank, self.ghost_width)
+        if self.exchange is not None:  # keep the totals of the exchange object this partition retires
+            self._halo_ms += self.exchange.exchange_ms()
+            self._halo_bytes += self.exchange.bytes_sent
         self.exchange = HaloExchange(self.plan, self.group)
+        self.exchange.timed = self.time_exchanges
         self.ghost_offset = (self.plan.ghost_shift.to(torch.float64) @ self.cell).contiguous()
         self.reference_positions = new_state["positions"].clone()
         self.n_partitions += 1
         return new_state
+
+    def halo_stats(self, reset: bool = False):
+        """(device milliseconds inside exchanges, bytes sent) since construction or the last reset; the time is only
+        collected while ``time_exchanges`` is set."""
+        ms = self._halo_ms + (self.exchange.exchange_ms(reset=reset) if self.exchange is not None else 0.0)
+        nbytes = self._halo_bytes + (self.exchange.bytes_sent if self.exchange is not None else 0)
+        if reset:
+            self._halo_ms, self._halo_bytes = 0.0, 0
+            if self.exchange is not None:
+                self.exchange.bytes_sent = 0
+        return ms, nbytes
+
+    def set_time_exchanges(self, enable: bool) -> None:
+        self.time_exchanges = bool(enable)
+        if self.exchange is not None:
+            self.exchange.timed = self.time_exchanges
 
     @property
     def n_owned(self) -> int:
@@ -399,6 +446,20 @@ class Domain:
         full[:n] = owned
         self.exchange.forward_exchange(full, full, 0)
         return full
+
+    def displacement(self, owned_positions: torch.Tensor, velocities: torch.Tensor):
+        """(largest distance any atom of any rank has moved since the last partition, largest speed of any atom), read
+        back with one collective and one host synchronisation."""
+        d2 = ((owned_positions - self.reference_positions) ** 2).sum(dim=1)
+        v2 = (velocities ** 2).sum(dim=1)
+        zero = torch.zeros((), dtype=torch.float64, device=owned_positions.device)
+        both = torch.stack([d2.max() if d2.numel() else zero, v2.max() if v2.numel() else zero])
+        if self.world_size > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(both, op=dist.ReduceOp.MAX, group=self.group)
+        moved2, fastest2 = both.tolist()
+        return moved2 ** 0.5, fastest2 ** 0.5
 
     def needs_partition(self, owned_positions: torch.Tensor) -> bool:
         """True on every rank as soon as an atom of any rank moved more than half the skin since the

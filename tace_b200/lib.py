@@ -20,7 +20,7 @@ EXPORTS = [
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill",
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
     "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
-    "tace_edge_vectors", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays",
+    "tace_edge_vectors", "tace_edges_within", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays",
     "tace_set_chunk_edges", "tace_md_langevin",
 ]
 
@@ -32,7 +32,7 @@ class TaceConfig(ctypes.Structure):
         ("readout_hidden", c_int), ("cutoff", c_double), ("avg_num_neighbors", c_double), ("Lnode", c_int),
         ("use_alllayer", c_int), ("gate_m0_off", c_int), ("mlp_layers", c_int), ("mlp_bias", c_int), ("env_after_mlp", c_int),
         ("edge_update_element2", c_int), ("num_fidelities", c_int), ("zbl", c_int), ("scatter_norm_density", c_int), ("resnet_identity", c_int), ("product_bilinear", c_int), ("tece_layers", c_int), ("mmax", c_int),
-        ("num_head", c_int), ("edge_ace_hidden", c_int), ("edge_act", c_int),
+        ("num_head", c_int), ("edge_ace_hidden", c_int), ("edge_act", c_int), ("radial_table", c_int),
     ]
 
 
@@ -109,6 +109,7 @@ def load() -> ctypes.CDLL:
                                      c_void_p]
     lib.tace_md_kinetic_energy.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.tace_edge_vectors.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_void_p]
+    lib.tace_edges_within.argtypes = [c_void_p, c_void_p, c_int64, ctypes.c_double, c_void_p, c_void_p]
     lib.tace_rows_gather.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
     lib.tace_rows_scatter_add.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
     _lib = lib

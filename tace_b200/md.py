@@ -105,6 +105,10 @@ class DomainMD:
         self.n_global = n
         self.step_count = 0
         self.timings: Dict[str, float] = {}
+        self.skin = float(skin)
+        self._skin_edges: Optional[torch.Tensor] = None  # neighbour list within cutoff + skin, built once per partition
+        self.n_list_builds = 0
+        self._next_check = 0                              # step at which the displacement is looked at again
         self._repartition(state)
         self.forces = None
         self.potential_energy = None
@@ -121,6 +125,7 @@ class DomainMD:
         self.inv_mass = (1.0 / self.mass).contiguous()
         self.local_species = self.domain.local_rows(self.species).to(torch.int32).contiguous()
         self._ke_scratch = torch.empty(1025, dtype=torch.float64, device=self.device)
+        self._skin_edges = None  # ownership and ghosts changed: the list is rebuilt at the next evaluation
 
     def _state(self) -> Dict[str, torch.Tensor]:
         return {"positions": self.positions, "velocities": self.velocities, "species": self.species, "mass": self.mass,
@@ -140,10 +145,23 @@ class DomainMD:
         lattice = torch.eye(3, dtype=torch.float64, device=self.device)[None]
         pbc = torch.zeros(1, 3, dtype=torch.uint8, device=self.device)
         ptr = torch.tensor([0, n + g], dtype=torch.int32, device=self.device)
-        if n > 0:
-            edge_index, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff, n_targets=n)
-        else:  # a block of vacuum: no target atom, no edge (the evaluation still answers its peers' exchanges)
+        if n == 0:  # a block of vacuum: no target atom, no edge (the evaluation still answers its peers' exchanges)
             edge_index = torch.empty(2, 0, dtype=torch.int64, device=self.device)
+        else:
+            # Verlet list: all pairs within cutoff + skin, built once per partition.  Ownership, ghost lists and this
+            # list stay valid until an atom has moved more than half the skin; every step only filters the list down
+            # to the pairs that are inside the cutoff now (the same fp64 test a fresh list would apply).
+            if self._skin_edges is None:
+                self._skin_edges, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff + self.skin, n_targets=n)
+                self._skin_edges = self._skin_edges.contiguous()
+                self.n_list_builds += 1
+            wide = self._skin_edges
+            Ew = int(wide.shape[1])
+            keep = torch.empty(Ew, dtype=torch.uint8, device=self.device)
+            with torch.cuda.device(self.device):
+                _lib.check(self.lib.tace_edges_within(local_pos.data_ptr(), wide.data_ptr(), Ew, self.cutoff, keep.data_ptr(),
+                                                      self._stream()), "tace_edges_within")
+            edge_index = wide[:, keep.view(torch.bool)].contiguous()
         E = int(edge_index.shape[1])
         vec = torch.empty(E, 3, dtype=self.dtype, device=self.device)
         with torch.cuda.device(self.device):
@@ -174,8 +192,16 @@ class DomainMD:
                     _lib.check(self.lib.tace_md_kick_drift(self.positions.data_ptr(), self.velocities.data_ptr(), self.forces.data_ptr(),
                                                            fcode, self.inv_mass.data_ptr(), n, kick, self.dt, self._stream()),
                                "tace_md_kick_drift")
-            if self.domain.needs_partition(self.positions):
-                self._repartition(self._state())
+            if self.step_count >= self._next_check:
+                moved, fastest = self.domain.displacement(self.positions, self.velocities)
+                if moved > 0.5 * self.skin:
+                    self._repartition(self._state())
+                    moved = 0.0
+                # no atom can cross half the skin before it has travelled the remaining margin: look again after half
+                # the steps the fastest atom would need at twice its present speed (at most 16 steps)
+                margin = 0.5 * self.skin - moved
+                safe = int(margin / max(2.0 * fastest * self.dt, 1e-12) / 2.0)
+                self._next_check = self.step_count + max(1, min(16, safe))
             self._evaluate()
             n = self.domain.n_owned
             with torch.cuda.device(self.device):

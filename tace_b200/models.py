@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 from . import lib as _lib
-from .pack import ModelPlan, pack_weights
+from .pack import RADIAL_TABLE_INTERVALS, ModelPlan, pack_weights
 
 # Options of the reference constructor that this path implements; anything else raises.
 _DEFAULTS: Dict[str, Any] = {
@@ -303,6 +303,8 @@ class TensorModel(torch.nn.Module):
         self._handle_key = None
         self._workspace = None
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
+        self._radial_table = True   # see set_radial_table
+        self.uses_radial_table = False
         # TACE_B200_CHUNK_EDGES=<n>: fixed edge-chunk size for every model instead of the automatic choice
         self._chunk_edges = int(os.environ["TACE_B200_CHUNK_EDGES"]) if os.environ.get("TACE_B200_CHUNK_EDGES") else None
         self._auto_chunk = None
@@ -373,10 +375,19 @@ class TensorModel(torch.nn.Module):
             resnet_identity=int(plan.resnet_type == "identity"), product_bilinear=int(plan.bilinear),
             tece_layers=sum(1 << t for t in plan.tece_layers), mmax=plan.mmax, num_head=plan.num_head,
             edge_ace_hidden=plan.edge_ace_hidden, edge_act=0 if plan.edge_act == "sigmoid" else 1)
+        # With the identity edge update the radial MLP's output depends on the edge length only: fp32 models read it
+        # from a table (TaceConfig.radial_table) instead of evaluating the MLP per edge.  TACE_B200_RADIAL_TABLE=0
+        # keeps the per-edge MLP.
+        table = (dtype == torch.float32 and not plan.element2 and not plan.tece_layers
+                 and os.environ.get("TACE_B200_RADIAL_TABLE", "1") != "0" and self._radial_table)
+        env_p = int(rf.cfg["radial_basis"]["polynomial_cutoff"])
+        cfg.radial_table = RADIAL_TABLE_INTERVALS if table else 0
+        self.uses_radial_table = bool(table)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.tace_create(ctypes.byref(cfg), ctypes.byref(handle)), "tace_create")
-            packed = pack_weights(plan, rf.state_dict(), float(rf.cfg["avg_num_neighbors"]))
+            packed = pack_weights(plan, rf.state_dict(), float(rf.cfg["avg_num_neighbors"]),
+                                  radial_table_spec=(self.get_cutoff(), env_p, RADIAL_TABLE_INTERVALS) if table else None)
             npdt = np.float64 if dtype == torch.float64 else np.float32
             name, numel = ctypes.c_char_p(), ctypes.c_int64()
             for i in range(lib.tace_weight_count(handle)):
@@ -397,6 +408,14 @@ class TensorModel(torch.nn.Module):
         self._graph_mode = bool(enable)
         if self._handle is not None:
             _lib.check(_lib.load().tace_set_graph_mode(self._handle, int(self._graph_mode)), "tace_set_graph_mode")
+
+    def set_radial_table(self, enable: bool = True) -> None:
+        """fp32 models with the identity edge update read the radial path weights from a per-(path, channel) table of
+        the edge length (cubic Hermite, 512 intervals) instead of evaluating the radial MLP for every edge; ``False``
+        goes back to the per-edge MLP.  Takes effect when the native model is (re)built."""
+        if bool(enable) != self._radial_table:
+            self._radial_table = bool(enable)
+            self.release()
 
     def set_chunk_edges(self, max_edges: Optional[int]) -> None:
         """Batches with more edges than this are evaluated chunk by chunk of target atoms with the per-edge tensors

@@ -308,7 +308,14 @@ def radial_table(out: Dict[str, np.ndarray], layer: int, plan: "ModelPlan", cuto
             a, da = _silu(z), _silu_grad(z) * dz
     val = a @ out[tp + "W3"] + (out[tp + "b3"] if plan.mlp_bias else 0.0)
     slope = da @ out[tp + "W3"]
-    return np.stack([val, slope * h], axis=-1)
+    knots = np.stack([val, slope * h], axis=-1)  # [K + 1][paths * channels][2]
+    return knots
+
+
+def radial_table_intervals(knots: np.ndarray) -> np.ndarray:
+    """The device layout of ``radial_table``'s result: [K][paths * channels][4] = the (value, h * slope) pairs of both
+    ends of interval k, so that one 16-byte load feeds the interpolation of one (path, channel) weight."""
+    return np.ascontiguousarray(np.concatenate([knots[:-1], knots[1:]], axis=-1))
 
 
 def hermite_weights(table: np.ndarray, d: np.ndarray, cutoff: float):
@@ -329,8 +336,13 @@ def _np(t) -> np.ndarray:
     return t.detach().cpu().double().numpy() if hasattr(t, "detach") else np.asarray(t, dtype=np.float64)
 
 
-def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: float, prefix: str = "") -> Dict[str, np.ndarray]:
-    """fp64 arrays keyed by the names ``tace_weight_info`` reports."""
+RADIAL_TABLE_INTERVALS = 512  # knot spacing cutoff / 512: interpolation error below fp32 round-off of the table itself
+
+
+def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: float, prefix: str = "", radial_table_spec=None
+                 ) -> Dict[str, np.ndarray]:
+    """fp64 arrays keyed by the names ``tace_weight_info`` reports.  ``radial_table_spec`` = (cutoff, envelope power,
+    intervals) adds the tabulated radial weights "t<i>.rtab" of every interaction (``radial_table``)."""
     C, n_el, L = plan.C, plan.n_el, plan.L
     g = lambda k: _np(sd[prefix + k])
     out: Dict[str, np.ndarray] = {}
@@ -484,6 +496,10 @@ def pack_weights(plan: ModelPlan, sd: Dict[str, "object"], avg_num_neighbors: fl
         out["zbl.z"] = zs.astype(np.float64)
         out["zbl.rcov"] = g("zbl.covalent_radii").reshape(-1)[zs]
         out["zbl.par"] = np.array([0.529 * float(g("zbl.a_prefactor")), float(g("zbl.a_exp"))])
+    if radial_table_spec is not None:
+        rc, env_p, intervals = radial_table_spec
+        for lp in plan.layers:
+            out[f"t{lp.t}.rtab"] = radial_table_intervals(radial_table(out, lp.t, plan, float(rc), int(env_p), int(intervals)))
     shift = g("scale_shift.shift")
     if np.any(shift != 0.0):
         raise NotImplementedError("a non-zero energy shift (scale_shift.shift_type) is not supported")

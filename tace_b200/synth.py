@@ -184,7 +184,10 @@ WORKLOADS = {
     # a quarter of the batch above, used for profiler captures
     "crystals16_fp32": dict(L=3, channels=128, cutoff=6.0, elements=list(range(1, 90)), avg_num_neighbors=63.3,
                             dtype="float32"),
-    "water32400_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32"),
+    "water32400_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32",
+                            cpu_sample="water192_fp32"),
+    # 64 molecules at the same density, built by the same rules: the CPU baseline's sample of configuration 3
+    "water192_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[1, 8], avg_num_neighbors=90.0, dtype="float32"),
     "cual1m_fp32": dict(L=2, channels=64, cutoff=5.0, elements=[13, 29], avg_num_neighbors=42.1, dtype="float32"),
     # benchmark configuration 4: the TECE model of the reference's example/train/tece.yaml at L = 3, C = 128 on a five-component BCC alloy
     "tece8192_fp32": dict(L=3, channels=128, cutoff=6.0, elements=[23, 24, 26, 27, 28], avg_num_neighbors=64.0, dtype="float32",
@@ -217,6 +220,8 @@ def workload_structures(name: str) -> List[Structure]:
         return random_crystals(16, seed=1)
     if name == "water32400_fp32":
         return [water_box()]
+    if name == "water192_fp32":
+        return [water_box(n_side=4, box=68.6 * (64 / 10800) ** (1.0 / 3.0), n_mol=64)]
     if name == "tece8192_fp32":
         return [bcc_supercell(16, 2.87, 0.08, seed=3, species=(23, 24, 26, 27, 28))]
     if name == "tece1024_fp32":  # 8 x 8 x 8 cells: the CPU baseline's sample of configuration 4

@@ -491,3 +491,34 @@ def test_full_size_properties_config4():
     model.release()
     del model
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("L,C,radial", [(3, 64, {}), (2, 64, {"apply_cutoff": False, "bias": True, "hidden": [64, 64]}), (2, 32, {"hidden": [64]})])
+def test_tabulated_radial_weights_match_the_per_edge_mlp(L, C, radial):
+    """fp32 models with the identity edge update read the path weights from a table of the edge length (cubic Hermite)
+    instead of running the radial MLP per edge.  Both routes must agree far inside the fp32 tolerances, whole and
+    chunked, and both must match the oracle."""
+    structs = [synth.fcc_supercell(3, 3.61, 0.05, seed=61, species=(1, 2, 3), fractions=(0.3, 0.3, 0.4)),
+               synth.random_crystals(1, seed=61, nmin=10, nmax=14, zmax=3)[0]]
+    model, oracle, cfg = make_models(L, C, [1, 2, 3], 5.0, 20.0, torch.float32, radial=radial)
+    data = oracle_batch(structs, [1, 2, 3], 5.0, torch.float32)
+    dev_data = to_device(data, torch.device("cuda:0"))
+    ref = oracle(data)
+    tab = {k: v.clone() for k, v in model(dev_data).items() if v is not None}
+    assert model.uses_radial_table
+    check_parity(tab, ref, data["ptr"], torch.float32, f"table L{L} C{C}")
+    model.set_chunk_edges(1024)
+    assert data["edge_index"].shape[1] > 2 * 1024
+    chunked = {k: v.clone() for k, v in model(dev_data).items() if v is not None}
+    model.set_chunk_edges(1 << 21)
+    model.set_radial_table(False)
+    mlp = model(dev_data)
+    assert not model.uses_radial_table
+    check_parity(mlp, ref, data["ptr"], torch.float32, f"per-edge MLP L{L} C{C}")
+    n_per = (data["ptr"][1:] - data["ptr"][:-1]).float()
+    for other, what in ((chunked, "chunked table"), (mlp, "per-edge MLP")):
+        de = ((tab["energy"] - other["energy"]).abs().cpu() / n_per).max().item()
+        df = (tab["forces"] - other["forces"]).abs().max().item()
+        print(f"table vs {what}: dE/atom = {de:.3e}, dF = {df:.3e}")
+        assert de <= 2e-6 and df <= 2e-5, what
+    assert model.device_error() == 0
