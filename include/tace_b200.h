@@ -206,6 +206,11 @@ int64_t tace_graph_replays(const TaceModel* model);
  * Return 0 on success. */
 typedef int (*tace_exchange_fn)(void* user, int reverse, const void* in, void* out, int64_t n_rows, int32_t vec_len);
 int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user);
+/* host_sync = 1 (default): tace_forward synchronises its stream before every callback, as a caller whose exchange runs on
+ * another stream or on the host needs (LAMMPS' ML-IAP exchange, tace/models/lammps.py:82-102).  host_sync = 0: the callback
+ * enqueues all of its device work on the stream of tace_forward (packing kernels, NCCL send / receive ordered on that
+ * stream); tace_forward then calls it without synchronising and the host runs ahead of the GPU. */
+int tace_set_exchange_sync(TaceModel* model, int host_sync);
 
 /* Instrumentation (no counterpart in the reference, which has no tracing on this path):
  * tace_launch_count returns the number of this library's kernels enqueued by tace_forward so far

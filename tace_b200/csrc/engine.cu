@@ -145,6 +145,7 @@ struct ModelBase {
   long long max_chunk_edges = 1LL << 21;
   tace_exchange_fn exchange_fn = nullptr;  // ghost-row exchange between layers (edge-vector mode)
   void* exchange_user = nullptr;
+  bool exchange_sync = true;                // synchronise the stream before every exchange callback (tace_set_exchange_sync)
   int* dev_error = nullptr;  // device word written by kernels whose bounded waits expire
   bool profile = false;
   std::vector<std::string> phase_names;
@@ -1093,12 +1094,12 @@ struct Model : ModelBase {
           const long long row = (long long)layers[t].tp.NX * C;
           if (pass == 0 && lb.xx) {
             CKL(launch_fill_zero(lb.x, N * row, s));
-            if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+            if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
             if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
           }
           if (pass == 1 && lb.gxx) {
             CKL(launch_fill_zero(lb.gx, N * row, s));
-            if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+            if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
             if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
           }
         }
@@ -1195,7 +1196,7 @@ struct Model : ModelBase {
         // Ghost rows of x are copies of rows owned elsewhere: zero them, let the caller's exchange fill
         // them (lmp_data.forward_exchange in the reference, tace/models/lammps.py:82-129).
         CKL(launch_fill_zero(lb.x + NL * p.tp.NX * C, (N - NL) * p.tp.NX * C, s));
-        if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+        if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
         if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
         x_src = lb.xx;
       }
@@ -1499,7 +1500,7 @@ struct Model : ModelBase {
         }
       }
       if (lb.gxx) {  // gradients that landed on ghost rows go back to their owners (reverse_exchange)
-        if (cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
+        if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
         if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
       }
       if (!p.scalar_src) {
@@ -1660,6 +1661,12 @@ int tace_set_chunk_edges(TaceModel* model, int64_t max_edges) {
   return TACE_OK;
 }
 int64_t tace_graph_replays(const TaceModel* model) { return model ? model->impl->graph_replays : TACE_ERR_INVALID_ARGUMENT; }
+int tace_set_exchange_sync(TaceModel* model, int host_sync) {
+  if (!model || !model->impl) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->exchange_sync = host_sync != 0;
+  return TACE_OK;
+}
+
 int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user) {
   if (!model) return TACE_ERR_INVALID_ARGUMENT;
   model->impl->exchange_fn = fn;

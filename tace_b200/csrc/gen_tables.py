@@ -244,18 +244,25 @@ def gen_interaction(L, Lin, out):
             o(line)
         for m3 in range(n3):
             o(f"    const T g{m3} = gs[{lay.idx(p, m3)} * gstride];")
-        for m1, m3 in pairs:
+        # u[m1] = sum_m3 G[m1][m3] g[m3] serves both the weight gradient (dw = sum_m1 x[m1] u[m1]) and the source
+        # gradient (dx[m1] += w u[m1]); the outer products q = x (x) g are only needed for the angular gradient
+        us = []
+        for m1 in range(2 * l1 + 1):
+            ts = [f"G_{gi[(p, m1, m3)]} * g{m3}" for m3 in range(n3) if (p, m1, m3) in gi]
+            if ts:
+                o(f"    const T u{m1} = {' + '.join(ts)};")
+                us.append(m1)
+        o(f"    dw[{p}] = {' + '.join(f'x[{xoff[l1] + m1}] * u{m1}' for m1 in us)};")
+        if not scalar_src:
+            for m1 in us:
+                o(f"    dx[{xoff[l1] + m1}] += w[{p}] * u{m1};")
+        used = sorted({(m1, m3) for m1, m3 in pairs if any(K[m1, m2, m3] != 0.0 for m2 in range(2 * l2 + 1))})
+        for m1, m3 in used:
             o(f"    const T q{m1}_{m3} = x[{xoff[l1] + m1}] * g{m3};")
-        o(f"    dw[{p}] = {' + '.join(f'G_{gi[(p, m1, m3)]} * q{m1}_{m3}' for m1, m3 in pairs)};")
         for m2 in range(2 * l2 + 1):
             ts = [f"{lit(float(K[m1, m2, m3]))} * q{m1}_{m3}" for m1, m3 in pairs if K[m1, m2, m3] != 0.0]
             if ts:
                 o(f"    dY[{l2 * l2 + m2}] += w[{p}] * ({' + '.join(ts)});")
-        if not scalar_src:
-            for m1 in range(2 * l1 + 1):
-                ts = [f"G_{gi[(p, m1, m3)]} * g{m3}" for m3 in range(n3) if (p, m1, m3) in gi]
-                if ts:
-                    o(f"    dx[{xoff[l1] + m1}] += w[{p}] * ({' + '.join(ts)});")
         o("  }")
     o("  }")
     o("};")

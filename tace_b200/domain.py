@@ -203,6 +203,10 @@ class HaloExchange:
     process group; sums into owner rows are applied peer by peer in ascending rank order.
     """
 
+    # every operation below is enqueued on the current CUDA stream (NCCL send / receive are ordered against it by
+    # torch.distributed), so a caller on that stream needs no host synchronisation around an exchange
+    stream_ordered = True
+
     def __init__(self, plan: HaloPlan, group=None):
         self.plan = plan
         self.group = group

@@ -524,8 +524,12 @@ class TensorModel(torch.nn.Module):
 
         exchange_cb = None
         if self.lmp and n_atoms != n_local and self.readout_fn.num_layers > 1:
-            exchange_cb = self._make_exchange(data["lmp_data"], dtype, device)
+            # an exchange object that enqueues everything on the current stream (tace_b200.domain.HaloExchange) says so
+            # with `stream_ordered`; LAMMPS' own exchange does not, and gets a synchronised stream on both sides
+            ordered = bool(getattr(data["lmp_data"], "stream_ordered", False))
+            exchange_cb = self._make_exchange(data["lmp_data"], dtype, device, sync=not ordered)
             _lib.check(lib.tace_set_exchange(handle, exchange_cb, None), "tace_set_exchange")
+            _lib.check(lib.tace_set_exchange_sync(handle, 0 if ordered else 1), "tace_set_exchange_sync")
         with torch.cuda.device(device):
             nbytes = ctypes.c_size_t()
 
@@ -566,7 +570,7 @@ class TensorModel(torch.nn.Module):
                     lib.tace_set_exchange(handle, _lib.EXCHANGE_FN(0), None)
         return res
 
-    def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device):
+    def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device, sync: bool = True):
         """ctypes callback handing the workspace rows to ``lmp_data.forward_exchange`` /
         ``reverse_exchange`` as torch views (tace/models/lammps.py:82-102)."""
         itemsize = torch.empty((), dtype=dtype).element_size()
@@ -583,7 +587,8 @@ class TensorModel(torch.nn.Module):
                     lmp_data.reverse_exchange(src, dst, vec_len)
                 else:
                     lmp_data.forward_exchange(src, dst, vec_len)
-                torch.cuda.synchronize(device)
+                if sync:
+                    torch.cuda.synchronize(device)
                 return 0
             except Exception as exc:  # an exception must not cross the C boundary
                 self._exchange_error = exc
