@@ -451,7 +451,9 @@ def main():
     # memory and downloads its own results inside the timed region.  With several GPUs every step ends with one
     # all_gather of the per-structure energies and stresses of all ranks (shares padded to the largest share).
     e2e_split = {"upload_and_neighbour_list": 0.0, "evaluation_call": 0.0, "download": 0.0, "gather": 0.0}
-    side = torch.cuda.Stream(device)
+    # high priority: the neighbour-list kernels of step k+1 are short and the host waits for their edge count, so they
+    # must not queue behind the long evaluation kernels of step k
+    side = torch.cuda.Stream(device, priority=-1)
     n_graphs = len(structures)
     share_max = int(max_over_ranks(float(n_graphs), world, device))
     gather_in = torch.zeros(share_max, 10, dtype=dtype, device=device)

@@ -245,24 +245,29 @@ int64_t tace_debug_read(TaceModel* model, const char* name, void* dst, int64_t n
  * get_neighborhood (tace/dataset/neighbour_list.py:195-298, matscipy "ijS" semantics): full
  * list, D = r_j - r_i + S @ cell, strict |D| < cutoff evaluated in fp64, self pairs kept
  * unless S = 0, no shifts along non-periodic axes.  Edges come out grouped by target atom.
- * Two calls: tace_nl_count fills `counts[n_atoms]` (neighbours per target atom) and the
- * total; the caller sizes the outputs; tace_nl_fill writes edge_index [2,n_edges]
- * (row 0 = source, row 1 = target) and integer shifts [n_edges,3].
+ * Two calls: tace_nl_count fills `counts[n_atoms]` (neighbours per target atom); the caller
+ * sizes the outputs; tace_nl_fill writes edge_index [2,n_edges] (row 0 = source, row 1 =
+ * target) and integer shifts [n_edges,3].
  * positions/lattice are fp64, pbc is [n_graphs,3] bytes. `row_ptr` is int64 [n_atoms+1]
- * (exclusive prefix sum of counts, computed by the caller). */
+ * (exclusive prefix sum of counts, computed by the caller).  Both calls take their temporaries
+ * (bins, sort keys, cell starts, sort scratch) from `workspace`, device memory of the caller of at
+ * least tace_nl_workspace_bytes(n_atoms, n_graphs) bytes; they allocate nothing and do not
+ * synchronise. */
+int tace_nl_workspace_bytes(int64_t n_atoms, int32_t n_graphs, size_t* bytes);
 int tace_nl_count(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
-                  int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, tace_stream_t stream);
+                  int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, void* workspace, size_t workspace_bytes,
+                  tace_stream_t stream);
 int tace_nl_fill(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
                  int32_t n_graphs, int64_t n_atoms, double cutoff, const int64_t* row_ptr, int64_t n_edges,
-                 int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream);
+                 int64_t* edge_index, int32_t* edge_shifts, void* workspace, size_t workspace_bytes, tace_stream_t stream);
 
 /* Neighbour list in one call that allocates nothing.  No counterpart in the reference.
  *
  * For hosts that must not allocate device memory while they run: an MD engine that has handed all of
  * the GPU's memory to its own pool (LAMMPS/Kokkos style) so a cudaMalloc inside a plugin can fail or
  * fragment it, or a latency-sensitive loop that cannot afford the device-wide synchronisation a
- * cudaMalloc/cudaFree pair implies.  tace_nl_count / tace_nl_fill take their temporary buffers from the
- * stream-ordered allocator and need a host round trip for the edge count; this variant keeps its
+ * cudaMalloc/cudaFree pair implies.  tace_nl_count / tace_nl_fill need a workspace sized by the caller and a
+ * host round trip for the edge count (the caller allocates the outputs between the two calls); this variant keeps its
  * temporaries (bins, sort keys, cell starts, sort workspace) in a fixed 2 MiB device array built into
  * the library (every GPU that loads the library holds those 2 MiB until the process exits), computes
  * the row pointers on the device and fills the caller's edge arrays directly.  It calls no cudaMalloc,

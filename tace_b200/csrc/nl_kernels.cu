@@ -227,22 +227,33 @@ __global__ void __launch_bounds__(128) nl_search_kernel(const double* __restrict
   if (!FILL && lane == 0) counts[i] = count;
 }
 
+size_t nl_workspace_bytes(int n_atoms, int n_graphs) {
+  auto al = [](size_t x) { return (x + 255) & ~size_t(255); };
+  const int max_cells = 2 * n_atoms + n_graphs + 1;
+  size_t cub_bytes = 0;
+  if (n_atoms > 0)
+    cub::DeviceRadixSort::SortPairs(nullptr, cub_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr, (int*)nullptr, n_atoms);
+  return al(sizeof(GraphBins) * n_graphs) + al(sizeof(int)) + 4 * al(sizeof(int) * (size_t)n_atoms) +
+         al(sizeof(int) * 3 * (size_t)n_atoms) + al(sizeof(int) * (size_t)(max_cells + 1)) + al(cub_bytes) + 256;
+}
+
 int nl_run(bool fill, const double* pos, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr, int32_t n_graphs,
            int64_t n_atoms64, double cutoff, int32_t* counts, const int64_t* row_ptr, int64_t n_edges, int64_t* edge_index,
-           int32_t* shifts, cudaStream_t s) {
+           int32_t* shifts, void* workspace, size_t workspace_bytes, cudaStream_t s) {
   if (!pos || !lattice || !pbc || !graph_ptr || n_graphs <= 0 || n_atoms64 < 0 || !(cutoff > 0.0)) return TACE_ERR_INVALID_ARGUMENT;
   if (n_atoms64 >= (1LL << 30)) return TACE_ERR_CAPACITY;
   if (fill ? (!row_ptr || (n_edges > 0 && (!edge_index || !shifts))) : !counts) return TACE_ERR_INVALID_ARGUMENT;
   const int n_atoms = (int)n_atoms64;
   if (n_atoms == 0) return TACE_OK;
+  if (!workspace) return TACE_ERR_INVALID_ARGUMENT;
   const int max_cells = 2 * n_atoms + n_graphs + 1;
   size_t cub_bytes = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, cub_bytes, (const int*)nullptr, (int*)nullptr, (const int*)nullptr, (int*)nullptr, n_atoms);
   auto al = [](size_t x) { return (x + 255) & ~size_t(255); };
-  const size_t bytes = al(sizeof(GraphBins) * n_graphs) + al(sizeof(int)) + 4 * al(sizeof(int) * (size_t)n_atoms) +
-                       al(sizeof(int) * 3 * (size_t)n_atoms) + al(sizeof(int) * (size_t)(max_cells + 1)) + al(cub_bytes);
-  unsigned char* base = nullptr;
-  if (cudaMallocAsync(&base, bytes, s) != cudaSuccess) return TACE_ERR_CUDA;
+  // the caller's scratch, cut up from its first 256-byte boundary
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  const size_t lead = (size_t)(base - static_cast<unsigned char*>(workspace));
+  if (workspace_bytes < lead || workspace_bytes - lead + 256 < nl_workspace_bytes(n_atoms, n_graphs)) return TACE_ERR_CAPACITY;
   unsigned char* p = base;
   GraphBins* bins = reinterpret_cast<GraphBins*>(p); p += al(sizeof(GraphBins) * n_graphs);
   int* total = reinterpret_cast<int*>(p); p += al(sizeof(int));
@@ -270,7 +281,6 @@ int nl_run(bool fill, const double* pos, const double* lattice, const uint8_t* p
                                                  counts, nullptr, 0, nullptr, nullptr);
     err = cudaGetLastError();
   }
-  cudaFreeAsync(base, s);
   return err == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }
 
@@ -376,17 +386,25 @@ int tace_nl_build_noalloc(const double* positions, const double* lattice, const 
                                 edge_shifts, static_cast<cudaStream_t>(stream));
 }
 
+int tace_nl_workspace_bytes(int64_t n_atoms, int32_t n_graphs, size_t* bytes) {
+  if (!bytes || n_atoms < 0 || n_graphs <= 0) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_atoms >= (1LL << 30)) return TACE_ERR_CAPACITY;
+  *bytes = tace::nl_workspace_bytes((int)n_atoms, n_graphs);
+  return TACE_OK;
+}
+
 int tace_nl_count(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
-                  int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, tace_stream_t stream) {
+                  int32_t n_graphs, int64_t n_atoms, double cutoff, int32_t* counts, void* workspace, size_t workspace_bytes,
+                  tace_stream_t stream) {
   return tace::nl_run(false, positions, lattice, pbc, graph_ptr, n_graphs, n_atoms, cutoff, counts, nullptr, 0, nullptr, nullptr,
-                      static_cast<cudaStream_t>(stream));
+                      workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int tace_nl_fill(const double* positions, const double* lattice, const uint8_t* pbc, const int32_t* graph_ptr,
                  int32_t n_graphs, int64_t n_atoms, double cutoff, const int64_t* row_ptr, int64_t n_edges,
-                 int64_t* edge_index, int32_t* edge_shifts, tace_stream_t stream) {
+                 int64_t* edge_index, int32_t* edge_shifts, void* workspace, size_t workspace_bytes, tace_stream_t stream) {
   return tace::nl_run(true, positions, lattice, pbc, graph_ptr, n_graphs, n_atoms, cutoff, nullptr, row_ptr, n_edges, edge_index,
-                      edge_shifts, static_cast<cudaStream_t>(stream));
+                      edge_shifts, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

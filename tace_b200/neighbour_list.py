@@ -7,6 +7,7 @@ structures); ``get_neighborhood`` keeps the reference signature and numpy return
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Tuple, Union
 
 import numpy as np
@@ -59,10 +60,13 @@ def neighbor_list_batch(positions: torch.Tensor, lattice: torch.Tensor, pbc: tor
     graph_ptr = graph_ptr.to(torch.int32).contiguous()
     n, b = positions.shape[0], lattice.shape[0]
     counts = torch.zeros(n, dtype=torch.int32, device=dev)
+    need = ctypes.c_size_t()
+    _lib.check(lib.tace_nl_workspace_bytes(n, b, ctypes.byref(need)), "tace_nl_workspace_bytes")
+    work = torch.empty(int(need.value), dtype=torch.uint8, device=dev)  # torch's caching allocator: no cudaMalloc once warm
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(lib.tace_nl_count(positions.data_ptr(), lattice.data_ptr(), pbc.data_ptr(), graph_ptr.data_ptr(), b, n,
-                                     float(cutoff), counts.data_ptr(), stream), "tace_nl_count")
+                                     float(cutoff), counts.data_ptr(), work.data_ptr(), work.numel(), stream), "tace_nl_count")
         if n_targets is not None and n_targets < n:
             counts[n_targets:] = 0  # rows without edges start at the end of the list and write nothing
         row_ptr = torch.zeros(n + 1, dtype=torch.int64, device=dev)
@@ -72,7 +76,7 @@ def neighbor_list_batch(positions: torch.Tensor, lattice: torch.Tensor, pbc: tor
         shifts = torch.empty(n_edges, 3, dtype=torch.int32, device=dev)
         _lib.check(lib.tace_nl_fill(positions.data_ptr(), lattice.data_ptr(), pbc.data_ptr(), graph_ptr.data_ptr(), b, n,
                                     float(cutoff), row_ptr.data_ptr(), n_edges, edge_index.data_ptr(), shifts.data_ptr(),
-                                    stream), "tace_nl_fill")
+                                    work.data_ptr(), work.numel(), stream), "tace_nl_fill")
     return edge_index, shifts
 
 
