@@ -249,6 +249,125 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
   }
 }
 
+// Backward pass of the first interaction (scalar source): the paths are (0, l, l), so the coupling is the identity,
+// M[i, (l, m), c] = sum_e w[e, l, c] x[src_e, c] Y_e[l, m], and nothing flows back to the source features.  What costs
+// here is not arithmetic but the sum over channels behind every dY_e[l, m].  Instead of D warp-shuffle reductions per
+// edge the block works in two phases per batch of edges: (1) thread = channel writes z[e][l][c] = w x (and the
+// per-channel terms of dE/d(length) and dE/d(envelope)) to shared memory and the weight gradient to global memory;
+// (2) thread = (edge, component) walks over the channels, dY_e[l, m] = sum_c z[e][l][c] gM[i, (l, m), c], starting at a
+// rotated channel so that the threads of a warp hit different banks.  Sums run in a fixed order: bit-reproducible.
+template <typename T, typename TP, bool ENV, bool RT>
+__global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
+  constexpr int D = TP::D, NP = TP::NP, EB = kEdgeBatch;
+  static_assert(TP::NX == 1 && TP::NM == TP::D, "scalar source: one path per rank");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int i = blockIdx.x, c = threadIdx.x, C = a.C;
+  T* gMs = reinterpret_cast<T*>(smem_raw);  // [D][C]
+  T* zs = gMs + D * C;                      // [EB][NP][C]
+  T* rs = zs + EB * NP * C;                 // [EB][2][C]: per-channel dE/d(length) and dE/d(envelope) terms
+  __shared__ T Ys[EB * D];
+  __shared__ int esrc[EB];
+  __shared__ T env_s[EB];
+  __shared__ RtEdge<T> rts[RT ? EB : 1];
+  const T* gMi = a.gM + (long long)i * D * C;
+  for (int k = 0; k < D; ++k) gMs[k * C + c] = gMi[k * C + c];
+  const int beg = a.rowptr[i], end = a.rowptr[i + 1];
+  for (int e0 = beg; e0 < end; e0 += EB) {
+    const int nb = min(EB, end - e0);
+    __syncthreads();
+    if (c < nb) {
+      esrc[c] = a.e_src[e0 + c];
+      if (ENV) env_s[c] = a.env[e0 + c];
+      if (RT) rt_prepare<T, true>(a, a.dlen[e0 + c], rts[c]);
+    }
+    for (int idx = c; idx < nb * D; idx += blockDim.x) Ys[idx] = a.Y[(long long)e0 * D + idx];
+    __syncthreads();
+    // phase 1: thread = channel.  Four edges at a time: first every global load of the group (source feature, table
+    // entries or weights) goes out, then the arithmetic runs, so the loads of four edges overlap instead of one.
+    constexpr int SUB = 4;
+    for (int eb = 0; eb < nb; eb += SUB) {
+      T xs_[SUB], w_[SUB][NP], wd_[SUB][NP];
+#pragma unroll
+      for (int j = 0; j < SUB; ++j) {
+        const int e = min(eb + j, nb - 1);  // lanes past the end repeat the last edge and are dropped below
+        xs_[j] = a.x[(long long)esrc[e] * C + c];
+        const long long wbase = (long long)(e0 + e - a.e_base) * NP * C;
+#pragma unroll
+        for (int l = 0; l < NP; ++l) {
+          if constexpr (RT) {
+            T v0, m0, v1, m1;
+            rt_load<T>(a.rtab + ((long long)rts[e].k * NP * C + (long long)l * C + c) * 4, v0, m0, v1, m1);
+            w_[j][l] = rts[e].b[0] * v0 + rts[e].b[1] * m0 + rts[e].b[2] * v1 + rts[e].b[3] * m1;
+            wd_[j][l] = rts[e].d[0] * v0 + rts[e].d[1] * m0 + rts[e].d[2] * v1 + rts[e].d[3] * m1;
+          } else {
+            w_[j][l] = a.W[wbase + l * C + c];
+            wd_[j][l] = T(0);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < SUB; ++j) {
+        const int e = eb + j;
+        if (e >= nb) break;
+        const T xs = xs_[j];
+        const T u = ENV ? env_s[e] : T(1);
+        const long long wbase = (long long)(e0 + e - a.e_base) * NP * C;
+        T dr_part = T(0), du_part = T(0);
+        int lm = 0;
+#pragma unroll
+        for (int l = 0; l < NP; ++l) {
+          T t = T(0);  // sum_m Y[l, m] gM[(l, m), c]
+#pragma unroll
+          for (int m = 0; m < 2 * l + 1; ++m, ++lm) t += Ys[e * D + lm] * gMs[lm * C + c];
+          const T dw_eff = xs * t;  // gradient with respect to the (envelope-scaled) weight
+          zs[(e * NP + l) * C + c] = u * w_[j][l] * xs;
+          du_part += dw_eff * w_[j][l];
+          if constexpr (RT) dr_part += u * dw_eff * wd_[j][l];
+          else a.dW[wbase + l * C + c] = u * dw_eff;
+        }
+        rs[(e * 2 + 0) * C + c] = dr_part;
+        rs[(e * 2 + 1) * C + c] = du_part;
+      }
+    }
+    __syncthreads();
+    // phase 2: thread = (edge, component) for dY, then one thread per edge for the two scalar sums
+    for (int r = c; r < nb * D; r += blockDim.x) {
+      const int e = r / D, lm = r - e * D;
+      const int l = lm < 1 ? 0 : lm < 4 ? 1 : lm < 9 ? 2 : 3;
+      const T* zr = zs + (e * NP + l) * C;
+      const T* gr = gMs + lm * C;
+      int k = r % C;  // rotated start: consecutive (edge, component) pairs of a warp start in consecutive banks
+      T acc = T(0);
+      for (int n = 0; n < C; ++n) {
+        acc += zr[k] * gr[k];
+        k = k + 1 == C ? 0 : k + 1;
+      }
+      T* dst = a.dY + (long long)(e0 + e) * D + lm;
+      *dst = a.accumulate_dY ? (*dst + acc) : acc;
+    }
+    const int first = blockDim.x > 32 ? 32 : 0;  // a second warp, when there is one, takes the scalar sums
+    if ((RT || ENV) && c >= first && c < first + 2 * nb) {
+      const int e = (c - first) >> 1, which = (c - first) & 1;
+      if ((which == 0 && RT) || (which == 1 && ENV)) {
+        const T* rr = rs + (e * 2 + which) * C;
+        int k = (8 * e + 4 * which) % C;
+        T acc = T(0);
+        for (int n = 0; n < C; ++n) {
+          acc += rr[k];
+          k = k + 1 == C ? 0 : k + 1;
+        }
+        if (which == 0) {
+          T* dst = a.ddlen + (e0 + e);
+          *dst = a.accumulate_ddlen ? (*dst + acc) : acc;
+        } else {
+          T* dst = a.denv + (e0 + e);
+          *dst = a.accumulate_denv ? (*dst + acc) : acc;
+        }
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void segment_sum_rows_kernel(const T* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
                                         T* __restrict__ gx, int row_len) {
@@ -320,10 +439,29 @@ cudaError_t launch_bwd_v(const TPArgs<T>& a, size_t smem, cudaStream_t s) {
   else tp_bwd_kernel<T, TP, false, RT><<<a.n_seg, a.C, smem, s>>>(a);
   return cudaGetLastError();
 }
+template <typename T, typename TP, bool ENV, bool RT>
+cudaError_t launch_bwd_scalar(const TPArgs<T>& a, cudaStream_t s) {
+  const size_t smem = sizeof(T) * ((size_t)TP::D * a.C + (size_t)kEdgeBatch * (TP::NP + 2) * a.C);
+  static size_t configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024 && smem > configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tp_bwd_scalar_kernel<T, TP, ENV, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = smem;
+  }
+  tp_bwd_scalar_kernel<T, TP, ENV, RT><<<a.n_seg, a.C, smem, s>>>(a);
+  return cudaGetLastError();
+}
 template <typename T, typename TP>
 cudaError_t launch_bwd_t(const TPArgs<T>& a, cudaStream_t s) {
   const size_t smem = sizeof(T) * ((size_t)TP::NM * a.C + kEdgeBatch * TP::NG + kEdgeBatch * 8 * TP::D);
   if (a.env && !a.denv) return cudaErrorInvalidValue;
+  if constexpr (TP::NX == 1 && TP::NM == TP::D) {  // scalar source (first interaction): the two-phase kernel
+    if (a.rtab && (!a.dlen || !a.ddlen || a.rt_K < 1)) return cudaErrorInvalidValue;
+    if (a.rtab) return a.env ? launch_bwd_scalar<T, TP, true, true>(a, s) : launch_bwd_scalar<T, TP, false, true>(a, s);
+    return a.env ? launch_bwd_scalar<T, TP, true, false>(a, s) : launch_bwd_scalar<T, TP, false, false>(a, s);
+  }
   if (a.rtab) {
     if (!a.dlen || !a.ddlen || a.rt_K < 1) return cudaErrorInvalidValue;
     return launch_bwd_v<T, TP, true>(a, smem, s);

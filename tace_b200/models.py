@@ -303,6 +303,7 @@ class TensorModel(torch.nn.Module):
         self._handle_key = None
         self._workspace = None
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
+        self._sized_for, self._sized_bytes = None, 0  # batch shape the workspace size was last computed for
         self._radial_table = True   # see set_radial_table
         self.uses_radial_table = False
         # TACE_B200_CHUNK_EDGES=<n>: fixed edge-chunk size for every model instead of the automatic choice
@@ -362,6 +363,7 @@ class TensorModel(torch.nn.Module):
             return self._handle
         self.release()
         self._auto_chunk = None
+        self._sized_for = None
         lib = _lib.load()
         plan = rf.plan
         cfg = _lib.TaceConfig(
@@ -421,6 +423,7 @@ class TensorModel(torch.nn.Module):
         """Batches with more edges than this are evaluated chunk by chunk of target atoms with the per-edge tensors
         recomputed in the backward pass (library default 2**21 edges)."""
         self._chunk_edges = None if max_edges is None else int(max_edges)
+        self._sized_for = None
         if self._handle is not None and max_edges is not None:
             _lib.check(_lib.load().tace_set_chunk_edges(self._handle, int(max_edges)), "tace_set_chunk_edges")
 
@@ -537,9 +540,11 @@ class TensorModel(torch.nn.Module):
                 _lib.check(lib.tace_workspace_bytes(handle, n_atoms, n_local, E, n_graphs, ctypes.byref(nbytes)), "tace_workspace_bytes")
                 return int(nbytes.value)
 
-            if self._chunk_edges is None:
+            shape_key = (n_atoms, n_local, E, n_graphs, device.index)
+            if self._chunk_edges is None and shape_key != self._sized_for:
                 # automatic edge chunking: keep every per-edge tensor resident when the workspace fits in
-                # 80 % of the memory this model may use, otherwise halve the chunk size until it does
+                # 80 % of the memory this model may use, otherwise halve the chunk size until it does.  Decided once
+                # per batch shape: the memory query is a driver call that can take longer than the evaluation itself.
                 free, _total = torch.cuda.mem_get_info(device)
                 budget = 0.8 * (free + (self._workspace.numel() if self._workspace is not None else 0))
                 whole_only = bool(self.readout_fn.plan.tece_layers)  # the TECE edge block is evaluated on the whole batch only
@@ -552,8 +557,11 @@ class TensorModel(torch.nn.Module):
                     if whole_only:
                         raise _lib.TaceError(f"tace_b200: this batch needs {needed() / 2**30:.1f} GiB of workspace with the TECE edge block "
                                              f"(all per-edge tensors resident), {budget / 2**30:.1f} GiB are available; use smaller batches")
-            needed()
-            ws = self._get_workspace(nbytes.value, device)
+            if shape_key != self._sized_for or self._workspace is None:
+                needed()
+                self._sized_bytes = int(nbytes.value)
+                self._sized_for = shape_key
+            ws = self._get_workspace(self._sized_bytes, device)
             ws_ptr = (ws.data_ptr() + 255) & ~255
             stream = torch.cuda.current_stream(device).cuda_stream
             self._exchange_error = None
