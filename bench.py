@@ -470,9 +470,12 @@ def main():
         e2e_split["upload_and_neighbour_list"] += time.perf_counter() - t_a
         return d, ready
 
+    e2e_step_s = []
+
     def e2e_loop(n):
         nxt = prepare()
         for k in range(n):
+            t_step = time.perf_counter()
             d, ready = nxt
             torch.cuda.current_stream(device).wait_event(ready)
             t_b = time.perf_counter()
@@ -493,6 +496,7 @@ def main():
             e2e_split["evaluation_call"] += t_c - t_b
             e2e_split["gather"] += t_e - t_d
             e2e_split["download"] += time.perf_counter() - t_e
+            e2e_step_s.append(time.perf_counter() - t_step)
         return host_out
 
     e2e_steps = min(args.steps, 100)
@@ -500,6 +504,7 @@ def main():
     barrier(world)
     for key in e2e_split:
         e2e_split[key] = 0.0
+    e2e_step_s.clear()
     t0 = time.perf_counter()
     res = e2e_loop(e2e_steps)
     torch.cuda.synchronize()
@@ -600,6 +605,8 @@ def main():
                    "l2": "flushed between timed steps (256 MiB write outside the per-step CUDA-event pair)"},
         "step_ms": {"min": min(r[4] for r in per_rank), "median": statistics.median(step_ms), "max": max(r[6] for r in per_rank)},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "step_ms": {"min": round(1e3 * min(e2e_step_s), 3), "median": round(1e3 * statistics.median(e2e_step_s), 3),
+                            "max": round(1e3 * max(e2e_step_s), 3)},
                 "pipelining": "upload + neighbour list of step k+1 on a second stream during the evaluation of step k"},
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
