@@ -89,3 +89,34 @@ def test_tece_configuration_builds_with_reference_parameter_names():
     for bad in ({"Lmax": 2}, {"mmax": 3}):
         with pytest.raises(NotImplementedError):
             check_model_config({**cfg, **bad})
+
+
+def test_checkpoint_written_from_the_reference_models_own_state_dict_loads(tmp_path):
+    """A ``.pt`` dictionary in the reference's export format (tace/lightning/lit_model.py:664-677) whose state_dict is the
+    reference model's own (``tests/golden/ref_model_tece_L2_C32.npz`` was written by running the reference's source files:
+    it carries the reference's parameter names and the persistent Wigner buffers this implementation has no use for)."""
+    import json
+    import os
+
+    import numpy as np
+
+    from tace_b200.interface.ase_calculator import load_tace
+
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_model_tece_L2_C32.npz"))
+    cfg = json.loads(str(z["cfg_json"]))
+    for s in cfg["statistics"]:
+        for k, v in list(s.items()):
+            if isinstance(v, dict):
+                s[k] = {int(a): b for a, b in v.items()}
+    sd = {k[3:]: torch.from_numpy(z[k]) for k in z.files if k.startswith("sd:")}
+    extra = [k for k in sd if "so2_angular_basis" in k]
+    assert extra, "the reference's state_dict holds persistent Wigner buffers"
+    statistics = cfg.pop("statistics")
+    target = cfg.pop("target_property")
+    path = str(tmp_path / "reference_export.pt")
+    torch.save({"state_dict": sd, "cfg": cfg, "target_property": target, "embedding_property": [], "statistics": statistics}, path)
+    model = load_tace(path, "cpu", dtype="float64")
+    own = model.state_dict()
+    assert set(own) == set(sd) - set(extra)
+    for k, v in own.items():
+        assert torch.equal(v, sd[k].to(v.dtype)), k
