@@ -211,6 +211,16 @@ int tace_set_exchange(TaceModel* model, tace_exchange_fn fn, void* user);
  * enqueues all of its device work on the stream of tace_forward (packing kernels, NCCL send / receive ordered on that
  * stream); tace_forward then calls it without synchronising and the host runs ahead of the GPU. */
 int tace_set_exchange_sync(TaceModel* model, int host_sync);
+/* Overlap of the exchange with the evaluation (needs host_sync = 0).  `stream` is a second stream of the same device on
+ * which the callback enqueues all of its work (NULL, the default: none).  tace_forward makes that stream wait for the
+ * rows the callback reads, calls the callback, and meanwhile goes on with the part of the layer that needs no ghost row:
+ * the messages of the atoms none of whose neighbours is a ghost (forward), and, in the backward pass, the atoms with ghost
+ * neighbours first, so that the gradient rows of the ghosts travel while the other atoms are processed.  It waits for the
+ * exchange stream only where the exchanged rows are first read.  The reference has no counterpart: it calls
+ * lmp_data.forward_exchange / reverse_exchange synchronously between two layers (tace/models/lammps.py:82-129).  Every
+ * message sum keeps its order, so energies are bit-identical to those without a stream; gradient rows of atoms with several
+ * ghost copies add the arrivals before the caller's own sum, so forces agree to rounding. */
+int tace_set_exchange_stream(TaceModel* model, tace_stream_t stream);
 
 /* Instrumentation (no counterpart in the reference, which has no tracing on this path):
  * tace_launch_count returns the number of this library's kernels enqueued by tace_forward so far

@@ -129,7 +129,33 @@ struct Arena {
 
 struct ModelBase {
   TaceConfig cfg;
-  virtual ~ModelBase() {}
+  virtual ~ModelBase() {
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+  }
+  // Runs the exchange callback.  Without an exchange stream: on the stream of the pass (after a host synchronisation when
+  // the callback asks for one).  With one: everything enqueued on `s` so far happens before the callback's work, which
+  // runs on the exchange stream; the pass goes on with `s` and calls exchange_join before it touches the callback's output.
+  bool exchange_on_side() const { return exchange_stream != nullptr && !exchange_sync; }
+  int exchange_begin(int reverse, const void* in, void* out, long long n_rows, int row, cudaStream_t s) {
+    const bool side = exchange_on_side();
+    if (side) {
+      if (!ev_fork && (cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+                       cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming) != cudaSuccess))
+        return TACE_ERR_CUDA;
+      if (cudaEventRecord(ev_fork, s) != cudaSuccess || cudaStreamWaitEvent(exchange_stream, ev_fork, 0) != cudaSuccess)
+        return TACE_ERR_CUDA;
+    } else if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) {
+      return TACE_ERR_CUDA;
+    }
+    if (exchange_fn(exchange_user, reverse, in, out, n_rows, row) != 0) return TACE_ERR_INVALID_ARGUMENT;
+    if (side && cudaEventRecord(ev_join, exchange_stream) != cudaSuccess) return TACE_ERR_CUDA;
+    return TACE_OK;
+  }
+  int exchange_join(cudaStream_t s) {
+    if (exchange_on_side() && cudaStreamWaitEvent(s, ev_join, 0) != cudaSuccess) return TACE_ERR_CUDA;
+    return TACE_OK;
+  }
   virtual int weight_count() const = 0;
   virtual int weight_info(int i, const char** name, int64_t* numel) const = 0;
   virtual int set_weight(const char* name, const void* host, int64_t numel) = 0;
@@ -146,6 +172,10 @@ struct ModelBase {
   tace_exchange_fn exchange_fn = nullptr;  // ghost-row exchange between layers (edge-vector mode)
   void* exchange_user = nullptr;
   bool exchange_sync = true;                // synchronise the stream before every exchange callback (tace_set_exchange_sync)
+  // Stream on which the exchange callback enqueues its work (tace_set_exchange_stream).  The pass then orders the callback
+  // against its own stream with events and keeps computing what does not need the ghost rows while they travel.
+  cudaStream_t exchange_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   int* dev_error = nullptr;  // device word written by kernels whose bounded waits expire
   bool profile = false;
   std::vector<std::string> phase_names;
@@ -592,6 +622,7 @@ struct Model : ModelBase {
     T *tgdown, *tgalpha, *tglogit, *tgcut, *tgproj, *tproj, *tgQp, *tgKp, *tgKs, *tgQt, *tdxt, *tddlen;
   };
   struct Bufs {
+    int *row_ids, *row_split;  // owned targets without / with a ghost source (passes split around the exchange)
     int *e_src, *e_dst, *e_orig, *perm_src, *rowptr_dst, *rowptr_src, *atom_graph, *species_perm, *species_ptr, *tile_ptr, *tc_tile_ptr;
     int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
@@ -604,6 +635,7 @@ struct Model : ModelBase {
   size_t layout(Arena& ar, Bufs& b, long long N, long long NL, long long E, int B) {
     b.e_src = ar.take<int>(E); b.e_dst = ar.take<int>(E); b.e_orig = ar.take<int>(E); b.perm_src = ar.take<int>(E);
     b.rowptr_dst = ar.take<int>(NL + 1); b.rowptr_src = ar.take<int>(N + 1); b.atom_graph = ar.take<int>(N);
+    b.row_ids = ar.take<int>(NL); b.row_split = ar.take<int>(2);
     b.species_perm = ar.take<int>(NL); b.species_ptr = ar.take<int>(n_el + 1); b.tile_ptr = ar.take<int>(4 * (n_el + 1));
     b.tc_tile_ptr = ar.take<int>(4 * (n_el + 1));
     b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
@@ -924,7 +956,7 @@ struct Model : ModelBase {
     so2_specs(sp, pre, 1, lb.tgQp, t_NR, lb.tgQt, t_NR, true, 0);
     CKL(run_linear(sp, E, s)); sp.clear();
     CKL(launch_tece(ta, TECE_ROTATE_IN_BWD, s));
-    CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, D * C, s));
+    CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, 0, (int)N, D * C, s));
     CKL(launch_tece(ta, TECE_TARGET_SUM, s));
     CKL(launch_tece(ta, TECE_WIGNER_GRAD, s));
     ta.accumulate_gvec = first_tece ? 0 : 1;
@@ -1094,13 +1126,13 @@ struct Model : ModelBase {
           const long long row = (long long)layers[t].tp.NX * C;
           if (pass == 0 && lb.xx) {
             CKL(launch_fill_zero(lb.x, N * row, s));
-            if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
-            if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
+            CKS(exchange_begin(0, lb.x, lb.xx, N, (int)row, s));
+            CKS(exchange_join(s));
           }
           if (pass == 1 && lb.gxx) {
             CKL(launch_fill_zero(lb.gx, N * row, s));
-            if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
-            if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, (int)row) != 0) return TACE_ERR_INVALID_ARGUMENT;
+            CKS(exchange_begin(1, lb.gx, lb.gxx, N, (int)row, s));
+            CKS(exchange_join(s));
           }
         }
       return TACE_OK;
@@ -1114,10 +1146,15 @@ struct Model : ModelBase {
     gp.perm_src = b.perm_src; gp.rowptr_src = b.rowptr_src; gp.atom_graph = b.atom_graph;
     gp.species_perm = b.species_perm; gp.species_ptr = b.species_ptr; gp.tile_ptr = b.tile_ptr; gp.tc_tile_ptr = b.tc_tile_ptr;
     gp.temp = b.prep_temp; gp.temp_bytes = b.prep_temp_bytes;
-    CKL(launch_graph_prep(gp, s));
-    launches += 8;  // launch_graph_prep runs nine kernels of its own besides the radix sorts
     // edge chunks: one chunk (all atoms) unless the batch exceeds max_chunk_edges
     const bool chunked = E > max_chunk_edges;
+    // With an exchange stream the tensor-product passes of the exchanged layers run in two parts: the target atoms none
+    // of whose sources is a ghost while the ghost rows travel, the others afterwards (forward), and the other way round
+    // for the gradients.  Every target is still summed in one piece, so the numbers do not depend on the schedule.
+    const bool overlap = exchange_on_side() && !chunked && NL != N && NL_ > 1;
+    gp.split_rows = overlap ? 1 : 0; gp.row_ids = b.row_ids; gp.row_split = b.row_split;
+    CKL(launch_graph_prep(gp, s));
+    launches += 8 + (overlap ? 2 : 0);  // launch_graph_prep runs nine kernels of its own (eleven) besides the radix sorts
     std::vector<int> chunk_atom{0, (int)NL}, chunk_edge{0, (int)E};
     if (chunked) {
       const int nc = b.n_chunks;
@@ -1192,12 +1229,13 @@ struct Model : ModelBase {
         CKL(run_linear(sp, n_up, s));
       }
       const T* x_src = lb.x;
+      const bool split = overlap && lb.xx && !p.tece;
       if (lb.xx) {
         // Ghost rows of x are copies of rows owned elsewhere: zero them, let the caller's exchange fill
         // them (lmp_data.forward_exchange in the reference, tace/models/lammps.py:82-129).
         CKL(launch_fill_zero(lb.x + NL * p.tp.NX * C, (N - NL) * p.tp.NX * C, s));
-        if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
-        if (exchange_fn(exchange_user, 0, lb.x, lb.xx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
+        CKS(exchange_begin(0, lb.x, lb.xx, N, p.tp.NX * C, s));
+        if (!split) CKS(exchange_join(s));
         x_src = lb.xx;
       }
       for (int c = 0; c < n_chunks; ++c) {
@@ -1223,6 +1261,12 @@ struct Model : ModelBase {
         ta.e_src = b.e_src; ta.Y = b.Y; ta.W = lb.W; ta.x = x_src; ta.M = lb.M + (long long)a0 * p.tp.NM * C; ta.e_base = e0;
         ta.env = b.env;
         if (rt_K) { ta.rtab = w(pre + "rtab"); ta.rt_K = rt_K; ta.rt_inv_h = T(rt_K) / T(cfg.cutoff); ta.dlen = b.dlen; }
+        if (split) {  // targets that read owned rows only (final in x itself); the others once the ghost rows have arrived
+          ta.x = lb.x; ta.row_ids = b.row_ids; ta.row_split = b.row_split + 1; ta.row_part = 0;
+          CKL(launch_tp_fwd(ta, s));
+          CKS(exchange_join(s));
+          ta.x = lb.xx; ta.row_part = 1;
+        }
         CKL(launch_tp_fwd(ta, s));
       }
       debug.push_back({"x" + ts, lb.x, N * p.tp.NX * C});
@@ -1486,11 +1530,30 @@ struct Model : ModelBase {
           ta.rtab = w(pre + "rtab"); ta.rt_K = rt_K; ta.rt_inv_h = T(rt_K) / T(cfg.cutoff); ta.dlen = b.dlen;
           ta.dW = nullptr; ta.ddlen = b.ddlen; ta.accumulate_ddlen = (t != NL_ - 1);
         }
-        CKL(launch_tp_bwd(ta, s));
-        if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
+        if (overlap && lb.gxx) {
+          // Targets with ghost sources first: the per-source sums of the ghost rows are what the owners of those atoms
+          // wait for.  While they travel the other targets follow; the sums over owned sources land in the owned rows of
+          // xx (x itself still holds those rows, and nothing reads xx any more), to be added to the arrivals after the join.
+          const int row = p.tp.NX * C;
+          TPArgs<T> tb = ta;
+          tb.row_ids = b.row_ids; tb.row_split = b.row_split + 1; tb.row_part = 1;
+          CKL(launch_tp_bwd(tb, s));
           PH(("t" + ts + ".bwd.src_sum").c_str());
-          if (chunked) CKL(launch_chunk_src_sum(b.dxe, b.keys_cs, b.perm_cs, e0, e0 + Ec, (long long)c * N, lb.gx, p.tp.NX * C, s));
-          else CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)N, p.tp.NX * C, s));
+          CKL(launch_fill_zero(lb.gx, NL * row, s));
+          CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, (int)NL, (int)(N - NL), row, s));
+          CKS(exchange_begin(1, lb.gx, lb.gxx, N, row, s));
+          PH(("t" + ts + ".bwd.tp").c_str());
+          ta.x = lb.x; ta.row_ids = b.row_ids; ta.row_split = b.row_split + 1; ta.row_part = 0;
+          CKL(launch_tp_bwd(ta, s));
+          PH(("t" + ts + ".bwd.src_sum").c_str());
+          CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.xx, 0, (int)NL, row, s));
+        } else {
+          CKL(launch_tp_bwd(ta, s));
+          if (!p.scalar_src) {  // sum the per-edge rows over the edges leaving each source atom
+            PH(("t" + ts + ".bwd.src_sum").c_str());
+            if (chunked) CKL(launch_chunk_src_sum(b.dxe, b.keys_cs, b.perm_cs, e0, e0 + Ec, (long long)c * N, lb.gx, p.tp.NX * C, s));
+            else CKL(launch_segment_sum_rows(b.dxe, b.rowptr_src, b.perm_src, lb.gx, 0, (int)N, p.tp.NX * C, s));
+          }
         }
         PH(("t" + ts + ".bwd.radial_gemm").c_str());
         CKS(radial_last(p, lb, pre, Ec, true, s));  // back through the last radial-MLP layer: H3 <- dE/dh3
@@ -1500,8 +1563,13 @@ struct Model : ModelBase {
         }
       }
       if (lb.gxx) {  // gradients that landed on ghost rows go back to their owners (reverse_exchange)
-        if (exchange_sync && cudaStreamSynchronize(s) != cudaSuccess) return TACE_ERR_CUDA;
-        if (exchange_fn(exchange_user, 1, lb.gx, lb.gxx, N, p.tp.NX * C) != 0) return TACE_ERR_INVALID_ARGUMENT;
+        if (overlap && !p.tece) {  // already on its way: owned rows of gxx = arrivals + this rank's own sums
+          CKS(exchange_join(s));
+          CKL(launch_add_inplace(lb.gxx, lb.xx, NL * p.tp.NX * C, s));
+        } else {
+          CKS(exchange_begin(1, lb.gx, lb.gxx, N, p.tp.NX * C, s));
+          CKS(exchange_join(s));
+        }
       }
       if (!p.scalar_src) {
         PH(("t" + ts + ".bwd.linear_up").c_str());
@@ -1664,6 +1732,12 @@ int64_t tace_graph_replays(const TaceModel* model) { return model ? model->impl-
 int tace_set_exchange_sync(TaceModel* model, int host_sync) {
   if (!model || !model->impl) return TACE_ERR_INVALID_ARGUMENT;
   model->impl->exchange_sync = host_sync != 0;
+  return TACE_OK;
+}
+
+int tace_set_exchange_stream(TaceModel* model, tace_stream_t stream) {
+  if (!model || !model->impl) return TACE_ERR_INVALID_ARGUMENT;
+  model->impl->exchange_stream = static_cast<cudaStream_t>(stream);
   return TACE_OK;
 }
 

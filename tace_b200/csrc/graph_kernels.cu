@@ -26,6 +26,15 @@ __global__ void gather_src_kernel(const int64_t* __restrict__ src_row, const int
   if (i >= n) return;
   e_src[i] = (int)src_row[e_orig[i]];
 }
+// keys[i] = 1 if any edge into target i comes from a ghost atom (index >= n_local), else 0; vals[i] = i
+__global__ void ghost_row_key_kernel(const int* __restrict__ rowptr, const int* __restrict__ e_src, int n_local, int* keys, int* vals) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_local) return;
+  int flag = 0;
+  for (int e = rowptr[i]; e < rowptr[i + 1]; ++e) flag |= (e_src[e] >= n_local) ? 1 : 0;
+  keys[i] = flag;
+  vals[i] = i;
+}
 // rowptr[i] = number of sorted keys < i, i = 0..n_rows
 __global__ void lower_bound_kernel(const int* __restrict__ sorted_keys, long long n_keys, int* rowptr, int n_rows) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -133,6 +142,13 @@ cudaError_t launch_graph_prep(const GraphPrepArgs& a, cudaStream_t s) {
   }
   lower_bound_kernel<<<(a.n_local + 256) / 256, 256, 0, s>>>(a.e_dst, a.E, a.rowptr_dst, a.n_local);
   lower_bound_kernel<<<(a.n_atoms + 256) / 256, 256, 0, s>>>(keys_out, a.E, a.rowptr_src, a.n_atoms);
+
+  if (a.split_rows && a.n_local > 0) {  // stable one-bit sort: targets without a ghost source first
+    ghost_row_key_kernel<<<(a.n_local + 255) / 256, 256, 0, s>>>(a.rowptr_dst, a.e_src, a.n_local, keys_in, vals_in);
+    err = cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, keys_in, keys_out, vals_in, a.row_ids, a.n_local, 0, 1, s);
+    if (err != cudaSuccess) return err;
+    lower_bound_kernel<<<1, 32, 0, s>>>(keys_out, a.n_local, a.row_split, 1);
+  }
 
   // species-sorted permutation of the local atoms (none on a rank that owns no atom: the row pointers below are all 0)
   int sbits = 1;

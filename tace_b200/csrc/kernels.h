@@ -21,6 +21,12 @@ struct TPArgs {
   int Lin;               // rank of the source features when !scalar_src (1..L)
   int n_seg;          // number of target atoms = thread blocks (per output group)
   const int* rowptr;  // [n_seg+1] CSR over the edges of each target (edges are target-sorted)
+  // Partial passes (target atoms that see no ghost source while the ghost rows of x are still in flight, the others
+  // afterwards): with row_ids the thread blocks of part 0 work on the targets row_ids[0 .. *row_split), those of part 1 on
+  // row_ids[*row_split .. n_seg); both are launched with n_seg blocks, the surplus blocks return at once
+  const int* row_ids;    // [n_seg] or nullptr (then block i works on target i)
+  const int* row_split;  // device word
+  int row_part;
   const int* e_src;   // [E] source atom of each edge
   const T* Y;         // [E][D] spherical harmonics of each edge
   const T* W;         // [E][NP*C] per-edge path weights
@@ -50,8 +56,9 @@ struct TPArgs {
 template <typename T> cudaError_t launch_tp_fwd(const TPArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_tp_bwd(const TPArgs<T>& a, cudaStream_t s);
 // gx[b] = sum of dxe over the edges whose source is b (edges listed by perm within rowptr_src segments)
+// for the source atoms [first_atom, first_atom + n_atoms)
 template <typename T> cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx,
-                                                          int n_atoms, int row_len, cudaStream_t s);
+                                                          int first_atom, int n_atoms, int row_len, cudaStream_t s);
 // Edge-chunked variant: positions [k0, k1) of the (chunk, source)-sorted edge list belong to one chunk whose dxe rows start
 // at edge k0; every run of equal keys is summed in list order and ADDED to gx[key - key_base] (runs of one chunk have
 // distinct sources, chunks are processed one after another, so the sum order is fixed).
@@ -229,6 +236,11 @@ struct GraphPrepArgs {
   // outputs
   int* e_src; int* e_dst; int* e_orig;  // target-sorted
   int* rowptr_dst;            // [n_local+1]
+  // split_rows: row_ids lists the owned targets none of whose sources is a ghost, then the others (each part in
+  // ascending order); row_split[1] is the length of the first part
+  int split_rows;
+  int* row_ids;               // [n_local] or nullptr
+  int* row_split;             // [2]
   int* perm_src; int* rowptr_src;       // [E], [n_atoms+1]
   int* atom_graph;            // [n_atoms]
   int* species_perm; int* species_ptr;  // [n_local], [n_elements+1]

@@ -35,6 +35,20 @@ __device__ __forceinline__ void build_G_rows(const T* __restrict__ Y, int e0, in
   }
 }
 
+// Partial passes.  Entry `it` of the part of the row list this launch works on (first part: entries [0, *row_split);
+// second part: entries [*row_split, n_seg)), or -1 past its end.  The host does not know where the list is split, so every
+// launch covers the whole list with blocks of kListRows entries each; blocks beyond the part return at once.  (One entry per
+// block would make those idle blocks the majority and their launch cost visible; a fixed number of long-lived blocks would
+// keep the exchange's own kernels, which run beside this one, waiting for a free slot.)
+constexpr int kListRows = 8;
+template <typename T>
+__device__ __forceinline__ int tp_row(const TPArgs<T>& a, int it) {
+  const int n0 = *a.row_split;
+  if (a.row_part == 0) { if (it >= n0) return -1; }
+  else { it += n0; if (it >= a.n_seg) return -1; }
+  return a.row_ids[it];
+}
+
 // ENV: the path weights are multiplied by the per-edge envelope (radial_basis.apply_cutoff = False); a separate
 // instantiation so the default kernels carry none of its registers.
 // Cubic Hermite interpolation of the tabulated path weights: knot index and the four basis values of one edge
@@ -74,14 +88,12 @@ __device__ __forceinline__ void rt_load<float>(const float* p, float& v0, float&
 }
 
 // RT: path weights interpolated from the table a.rtab instead of read from a.W.
+// Messages of target atom i (output group GRP); Gs, esrc, rts: shared memory of the block.
 template <typename T, typename TP, int GRP, bool ENV, bool RT>
-__global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
+__device__ __forceinline__ void tp_fwd_row(const TPArgs<T>& a, int i, T* Gs, int* esrc, RtEdge<T>* rts) {
   constexpr int NMG = GRP == 0 ? TP::NMG0 : TP::NMG1, NPG = GRP == 0 ? TP::NPG0 : TP::NPG1;
   constexpr int P0 = GRP == 0 ? TP::P00 : TP::P01, M0 = GRP == 0 ? TP::M00 : TP::M01;
-  const int i = blockIdx.x, c = threadIdx.x, C = a.C;
-  __shared__ __align__(16) T Gs[kEdgeBatch * TP::NG];
-  __shared__ int esrc[kEdgeBatch];
-  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
+  const int c = threadIdx.x, C = a.C;
   const int rt_first = blockDim.x > 32 ? 32 : 0;  // the second warp (when there is one) prepares the interpolation
   T acc[NMG];
 #pragma unroll
@@ -127,24 +139,37 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
 #pragma unroll
   for (int k = 0; k < NMG; ++k) Mi[k * C + c] = acc[k];
 }
+// LIST: block b works on kListRows entries of the row list of a partial pass (tp_row); otherwise block i = target i.
+template <typename T, typename TP, int GRP, bool ENV, bool RT, bool LIST>
+__global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
+  __shared__ __align__(16) T Gs[kEdgeBatch * TP::NG];
+  __shared__ int esrc[kEdgeBatch];
+  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
+  if constexpr (LIST) {
+    for (int it = blockIdx.x * kListRows; it < (blockIdx.x + 1) * kListRows; ++it) {
+      const int i = tp_row(a, it);
+      if (i < 0) break;
+      tp_fwd_row<T, TP, GRP, ENV, RT>(a, i, Gs, esrc, rts);
+    }
+  } else {
+    tp_fwd_row<T, TP, GRP, ENV, RT>(a, blockIdx.x, Gs, esrc, rts);
+  }
+}
 
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
 template <typename T, typename TP, bool ENV, bool RT>
-__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int i = blockIdx.x, c = threadIdx.x, C = a.C;
+__device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned char* smem_raw, T* red_u, T* red_r, RtEdge<T>* rts,
+                                           int* esrc) {
+  const int c = threadIdx.x, C = a.C;
   const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   T* gMs = reinterpret_cast<T*>(smem_raw);          // [NM][C]
   T* Gs = gMs + TP::NM * C;                          // [kEdgeBatch][NG]
   T* red = Gs + kEdgeBatch * TP::NG;                 // [kEdgeBatch][8 warps][D]
-  __shared__ T red_u[kEdgeBatch * 8];                // envelope-gradient partial sums
-  __shared__ T red_r[RT ? kEdgeBatch * 8 : 1];       // edge-length-gradient partial sums (tabulated weights)
-  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
-  __shared__ int esrc[kEdgeBatch];
   const int rt_first = blockDim.x > 32 ? 32 : 0;  // the second warp (when there is one) prepares the interpolation
-  const T* gMi = a.gM + (long long)i * TP::NM * C;
-  for (int k = 0; k < TP::NM; ++k) gMs[k * C + c] = gMi[k * C + c];  // each thread later reads only its own column
   const int beg = a.rowptr[i], end = a.rowptr[i + 1];
+  const T* gMi = a.gM + (long long)i * TP::NM * C;
+  if (beg < end)
+    for (int k = 0; k < TP::NM; ++k) gMs[k * C + c] = gMi[k * C + c];  // each thread reads and writes only its own column
   for (int e0 = beg; e0 < end; e0 += kEdgeBatch) {
     const int nb = min(kEdgeBatch, end - e0);
     __syncthreads();
@@ -246,6 +271,23 @@ __global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
       T* dst = a.ddlen + (e0 + e);
       *dst = a.accumulate_ddlen ? (*dst + v) : v;
     }
+  }
+}
+template <typename T, typename TP, bool ENV, bool RT, bool LIST>
+__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ T red_u[kEdgeBatch * 8];                // envelope-gradient partial sums
+  __shared__ T red_r[RT ? kEdgeBatch * 8 : 1];       // edge-length-gradient partial sums (tabulated weights)
+  __shared__ RtEdge<T> rts[RT ? kEdgeBatch : 1];
+  __shared__ int esrc[kEdgeBatch];
+  if constexpr (LIST) {
+    for (int it = blockIdx.x * kListRows; it < (blockIdx.x + 1) * kListRows; ++it) {
+      const int i = tp_row(a, it);
+      if (i < 0) break;
+      tp_bwd_row<T, TP, ENV, RT>(a, i, smem_raw, red_u, red_r, rts, esrc);
+    }
+  } else {
+    tp_bwd_row<T, TP, ENV, RT>(a, blockIdx.x, smem_raw, red_u, red_r, rts, esrc);
   }
 }
 
@@ -370,8 +412,8 @@ __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
 
 template <typename T>
 __global__ void segment_sum_rows_kernel(const T* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
-                                        T* __restrict__ gx, int row_len) {
-  const int b = blockIdx.x;
+                                        T* __restrict__ gx, int first, int row_len) {
+  const int b = first + blockIdx.x;
   const int beg = rowptr[b], end = rowptr[b + 1];
   for (int k = threadIdx.x; k < row_len; k += blockDim.x) {
     T acc = T(0);
@@ -380,10 +422,10 @@ __global__ void segment_sum_rows_kernel(const T* __restrict__ dxe, const int* __
   }
 }
 template <typename T>
-cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx, int n_atoms, int row_len,
-                                    cudaStream_t s) {
+cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx, int first_atom, int n_atoms,
+                                    int row_len, cudaStream_t s) {
   if (n_atoms <= 0) return cudaSuccess;
-  segment_sum_rows_kernel<T><<<n_atoms, 256, 0, s>>>(dxe, rowptr_src, perm_src, gx, row_len);
+  segment_sum_rows_kernel<T><<<n_atoms, 256, 0, s>>>(dxe, rowptr_src, perm_src, gx, first_atom, row_len);
   return cudaGetLastError();
 }
 
@@ -412,8 +454,13 @@ cudaError_t launch_chunk_src_sum(const T* dxe_chunk, const int* keys, const int*
 
 template <typename T, typename TP, bool ENV, bool RT>
 cudaError_t launch_fwd_v(const TPArgs<T>& a, cudaStream_t s) {
-  tp_fwd_kernel<T, TP, 0, ENV, RT><<<a.n_seg, a.C, 0, s>>>(a);
-  if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, ENV, RT><<<a.n_seg, a.C, 0, s>>>(a);
+  if (a.row_ids) {
+    tp_fwd_kernel<T, TP, 0, ENV, RT, true><<<(a.n_seg + kListRows - 1) / kListRows, a.C, 0, s>>>(a);
+    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, ENV, RT, true><<<(a.n_seg + kListRows - 1) / kListRows, a.C, 0, s>>>(a);
+  } else {
+    tp_fwd_kernel<T, TP, 0, ENV, RT, false><<<a.n_seg, a.C, 0, s>>>(a);
+    if (TP::NGRP > 1) tp_fwd_kernel<T, TP, 1, ENV, RT, false><<<a.n_seg, a.C, 0, s>>>(a);
+  }
   return cudaGetLastError();
 }
 template <typename T, typename TP>
@@ -430,13 +477,20 @@ cudaError_t launch_bwd_v(const TPArgs<T>& a, size_t smem, cudaStream_t s) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidValue;
   if (smem > 48 * 1024 && smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false, RT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true, RT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, false, RT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tp_bwd_kernel<T, TP, true, RT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     configured[dev] = smem;
   }
-  if (a.env) tp_bwd_kernel<T, TP, true, RT><<<a.n_seg, a.C, smem, s>>>(a);
-  else tp_bwd_kernel<T, TP, false, RT><<<a.n_seg, a.C, smem, s>>>(a);
+  if (a.row_ids) {
+    if (a.env) tp_bwd_kernel<T, TP, true, RT, true><<<(a.n_seg + kListRows - 1) / kListRows, a.C, smem, s>>>(a);
+    else tp_bwd_kernel<T, TP, false, RT, true><<<(a.n_seg + kListRows - 1) / kListRows, a.C, smem, s>>>(a);
+  } else {
+    if (a.env) tp_bwd_kernel<T, TP, true, RT, false><<<a.n_seg, a.C, smem, s>>>(a);
+    else tp_bwd_kernel<T, TP, false, RT, false><<<a.n_seg, a.C, smem, s>>>(a);
+  }
   return cudaGetLastError();
 }
 template <typename T, typename TP, bool ENV, bool RT>
@@ -490,8 +544,8 @@ template cudaError_t launch_tp_fwd<float>(const TPArgs<float>&, cudaStream_t);
 template cudaError_t launch_tp_fwd<double>(const TPArgs<double>&, cudaStream_t);
 template cudaError_t launch_tp_bwd<float>(const TPArgs<float>&, cudaStream_t);
 template cudaError_t launch_tp_bwd<double>(const TPArgs<double>&, cudaStream_t);
-template cudaError_t launch_segment_sum_rows<float>(const float*, const int*, const int*, float*, int, int, cudaStream_t);
-template cudaError_t launch_segment_sum_rows<double>(const double*, const int*, const int*, double*, int, int, cudaStream_t);
+template cudaError_t launch_segment_sum_rows<float>(const float*, const int*, const int*, float*, int, int, int, cudaStream_t);
+template cudaError_t launch_segment_sum_rows<double>(const double*, const int*, const int*, double*, int, int, int, cudaStream_t);
 template cudaError_t launch_chunk_src_sum<float>(const float*, const int*, const int*, long long, long long, long long, float*, int, cudaStream_t);
 template cudaError_t launch_chunk_src_sum<double>(const double*, const int*, const int*, long long, long long, long long, double*, int, cudaStream_t);
 

@@ -344,11 +344,22 @@ class Domain:
     """
 
     def __init__(self, cell: np.ndarray, cutoff: float, skin: float, rank: int, world_size: int, device: torch.device,
-                 grid: Optional[Tuple[int, int, int]] = None, group=None):
+                 grid: Optional[Tuple[int, int, int]] = None, group=None, high_priority_halo: bool = False):
         self.cell_np = np.asarray(cell, dtype=np.float64).reshape(3, 3)
         self.heights = cell_heights(self.cell_np)
         self.cutoff, self.skin = float(cutoff), float(skin)
         self.rank, self.world_size, self.device, self.group = rank, world_size, torch.device(device), group
+        # high_priority_halo: halo messages travel on a group of their own whose NCCL streams have high priority, so that an
+        # exchange that runs beside the evaluation (TensorModel.set_exchange_overlap) does not queue behind the
+        # evaluation's thread blocks.
+        self.halo_group = group
+        if high_priority_halo and world_size > 1 and self.device.type == "cuda":
+            import torch.distributed as dist
+
+            if dist.get_backend(group) == "nccl":
+                ranks = None if group is None else dist.get_process_group_ranks(group)
+                options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+                self.halo_group = dist.new_group(ranks=ranks, backend="nccl", pg_options=options)  # collective: every rank builds its Domain
         self.grid = DomainGrid(tuple(grid) if grid is not None else choose_grid(world_size, self.heights))
         if self.grid.world_size != world_size:
             raise ValueError(f"grid {self.grid.grid} does not match world size {world_size}")
@@ -403,7 +414,7 @@ class Domain:
         if self.exchange is not None:  # keep the totals of the exchange object this partition retires
             self._halo_ms += self.exchange.exchange_ms()
             self._halo_bytes += self.exchange.bytes_sent
-        self.exchange = HaloExchange(self.plan, self.group)
+        self.exchange = HaloExchange(self.plan, self.halo_group)
         self.exchange.timed = self.time_exchanges
         self.ghost_offset = (self.plan.ghost_shift.to(torch.float64) @ self.cell).contiguous()
         self.reference_positions = new_state["positions"].clone()

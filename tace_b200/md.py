@@ -81,7 +81,8 @@ class DomainMD:
         self.lib = _lib.load()
         model._set_lammps_mliap(True)
         model.reset_target_property(["energy", "forces"])
-        self.domain = Domain(cell, self.cutoff, skin, rank, world_size, self.device, grid=grid, group=group)
+        self.domain = Domain(cell, self.cutoff, skin, rank, world_size, self.device, grid=grid, group=group,
+                             high_priority_halo=bool(getattr(model, "_exchange_overlap", False)))
 
         positions = np.asarray(positions, dtype=np.float64)
         n = positions.shape[0]

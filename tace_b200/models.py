@@ -305,6 +305,8 @@ class TensorModel(torch.nn.Module):
         self._graph_mode = os.environ.get("TACE_B200_GRAPHS", "1") != "0"
         self._sized_for, self._sized_bytes = None, 0  # batch shape the workspace size was last computed for
         self._radial_table = True   # see set_radial_table
+        self._exchange_overlap = os.environ.get("TACE_B200_EXCHANGE_OVERLAP", "0") == "1"  # see set_exchange_overlap
+        self._exchange_stream = None
         self.uses_radial_table = False
         # TACE_B200_CHUNK_EDGES=<n>: fixed edge-chunk size for every model instead of the automatic choice
         self._chunk_edges = int(os.environ["TACE_B200_CHUNK_EDGES"]) if os.environ.get("TACE_B200_CHUNK_EDGES") else None
@@ -419,6 +421,14 @@ class TensorModel(torch.nn.Module):
             self._radial_table = bool(enable)
             self.release()
 
+    def set_exchange_overlap(self, enable: bool = True) -> None:
+        """Run stream-ordered ghost exchanges (``tace_b200.domain.HaloExchange``) on a stream of their own while the layer
+        works on the atoms without ghost neighbours (``tace_set_exchange_stream``).  Off by default (the environment
+        variable TACE_B200_EXCHANGE_OVERLAP=1 turns it on for every model): over NVLink the exchange inside an evaluation
+        is about 1 % of a step of the 1 M-atom benchmark, less than what splitting the tensor-product passes costs; it
+        is meant for interconnects where the exchange is slow."""
+        self._exchange_overlap = bool(enable)
+
     def set_chunk_edges(self, max_edges: Optional[int]) -> None:
         """Batches with more edges than this are evaluated chunk by chunk of target atoms with the per-edge tensors
         recomputed in the backward pass (library default 2**21 edges)."""
@@ -444,6 +454,7 @@ class TensorModel(torch.nn.Module):
     def __getstate__(self):
         state = self.__dict__.copy()
         state["_handle"], state["_handle_key"], state["_workspace"] = None, None, None
+        state["_exchange_stream"] = None
         return state
 
     def _get_workspace(self, nbytes: int, device: torch.device) -> torch.Tensor:
@@ -530,9 +541,16 @@ class TensorModel(torch.nn.Module):
             # an exchange object that enqueues everything on the current stream (tace_b200.domain.HaloExchange) says so
             # with `stream_ordered`; LAMMPS' own exchange does not, and gets a synchronised stream on both sides
             ordered = bool(getattr(data["lmp_data"], "stream_ordered", False))
-            exchange_cb = self._make_exchange(data["lmp_data"], dtype, device, sync=not ordered)
+            # such an exchange can also run on a stream of its own while the layer works on the edges between owned atoms
+            side = None
+            if ordered and self._exchange_overlap:
+                if self._exchange_stream is None or self._exchange_stream.device != device:
+                    self._exchange_stream = torch.cuda.Stream(device, priority=-1)
+                side = self._exchange_stream
+            exchange_cb = self._make_exchange(data["lmp_data"], dtype, device, sync=not ordered, stream=side)
             _lib.check(lib.tace_set_exchange(handle, exchange_cb, None), "tace_set_exchange")
             _lib.check(lib.tace_set_exchange_sync(handle, 0 if ordered else 1), "tace_set_exchange_sync")
+            _lib.check(lib.tace_set_exchange_stream(handle, side.cuda_stream if side is not None else None), "tace_set_exchange_stream")
         with torch.cuda.device(device):
             nbytes = ctypes.c_size_t()
 
@@ -541,22 +559,35 @@ class TensorModel(torch.nn.Module):
                 return int(nbytes.value)
 
             shape_key = (n_atoms, n_local, E, n_graphs, device.index)
+
+            def set_limit(limit: int) -> None:
+                if limit != self._auto_chunk:
+                    _lib.check(lib.tace_set_chunk_edges(handle, int(limit)), "tace_set_chunk_edges")
+                    self._auto_chunk = limit
+
             if self._chunk_edges is None and shape_key != self._sized_for:
                 # automatic edge chunking: keep every per-edge tensor resident when the workspace fits in
                 # 80 % of the memory this model may use, otherwise halve the chunk size until it does.  Decided once
-                # per batch shape: the memory query is a driver call that can take longer than the evaluation itself.
-                free, _total = torch.cuda.mem_get_info(device)
-                budget = 0.8 * (free + (self._workspace.numel() if self._workspace is not None else 0))
-                whole_only = bool(self.readout_fn.plan.tece_layers)  # the TECE edge block is evaluated on the whole batch only
-                for limit in ((max(E, 1 << 21),) if whole_only else (max(E, 1 << 21), 1 << 22, 1 << 21, 1 << 20, 1 << 19, 1 << 18)):
-                    if limit != self._auto_chunk:
-                        _lib.check(lib.tace_set_chunk_edges(handle, int(limit)), "tace_set_chunk_edges")
-                        self._auto_chunk = limit
-                    if needed() <= budget or limit == 1 << 18:
-                        break
-                    if whole_only:
-                        raise _lib.TaceError(f"tace_b200: this batch needs {needed() / 2**30:.1f} GiB of workspace with the TECE edge block "
-                                             f"(all per-edge tensors resident), {budget / 2**30:.1f} GiB are available; use smaller batches")
+                # per batch shape, and without asking the driver when the whole batch fits into the workspace this
+                # model already holds: the memory query can take longer than the evaluation itself (up to ~20 ms seen).
+                whole = max(E, 1 << 21)
+                held = self._workspace.numel() - 512 if self._workspace is not None and self._workspace.device == device else -1
+                fits = False
+                for limit in (whole, self._auto_chunk):  # the whole batch, else the chunk size chosen last time
+                    if limit is not None and limit <= whole and not fits:
+                        set_limit(limit)
+                        fits = needed() <= held
+                if not fits:
+                    free, _total = torch.cuda.mem_get_info(device)
+                    budget = 0.8 * (free + (self._workspace.numel() if self._workspace is not None else 0))
+                    whole_only = bool(self.readout_fn.plan.tece_layers)  # the TECE edge block is evaluated on the whole batch only
+                    for limit in ((whole,) if whole_only else (whole, 1 << 22, 1 << 21, 1 << 20, 1 << 19, 1 << 18)):
+                        set_limit(limit)
+                        if needed() <= budget or limit == 1 << 18:
+                            break
+                        if whole_only:
+                            raise _lib.TaceError(f"tace_b200: this batch needs {needed() / 2**30:.1f} GiB of workspace with the TECE edge block "
+                                                 f"(all per-edge tensors resident), {budget / 2**30:.1f} GiB are available; use smaller batches")
             if shape_key != self._sized_for or self._workspace is None:
                 needed()
                 self._sized_bytes = int(nbytes.value)
@@ -578,9 +609,11 @@ class TensorModel(torch.nn.Module):
                     lib.tace_set_exchange(handle, _lib.EXCHANGE_FN(0), None)
         return res
 
-    def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device, sync: bool = True):
+    def _make_exchange(self, lmp_data, dtype: torch.dtype, device: torch.device, sync: bool = True, stream=None):
         """ctypes callback handing the workspace rows to ``lmp_data.forward_exchange`` /
-        ``reverse_exchange`` as torch views (tace/models/lammps.py:82-102)."""
+        ``reverse_exchange`` as torch views (tace/models/lammps.py:82-102).  With ``stream`` the exchange's own work is
+        enqueued on that stream (the library orders it against the evaluation, tace_set_exchange_stream)."""
+        import contextlib
         itemsize = torch.empty((), dtype=dtype).element_size()
 
         def view(ptr: int, rows: int, cols: int) -> torch.Tensor:
@@ -591,10 +624,11 @@ class TensorModel(torch.nn.Module):
         def callback(_user, reverse, in_ptr, out_ptr, n_rows, vec_len):
             try:
                 src, dst = view(in_ptr, n_rows, vec_len), view(out_ptr, n_rows, vec_len)
-                if reverse:
-                    lmp_data.reverse_exchange(src, dst, vec_len)
-                else:
-                    lmp_data.forward_exchange(src, dst, vec_len)
+                with (torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext()):
+                    if reverse:
+                        lmp_data.reverse_exchange(src, dst, vec_len)
+                    else:
+                        lmp_data.forward_exchange(src, dst, vec_len)
                 if sync:
                     torch.cuda.synchronize(device)
                 return 0

@@ -37,6 +37,36 @@ def test_single_rank_domain_matches_oracle(num_layers):
     assert model.device_error() == 0
 
 
+@pytest.mark.parametrize("dtype,num_layers", [(torch.float64, 2), (torch.float64, 3), (torch.float32, 2)])
+def test_exchange_on_its_own_stream_gives_the_serial_result(dtype, num_layers):
+    """The ghost exchange may run on a second stream while the layer works on the atoms without ghost neighbours
+    (tace_set_exchange_stream).  Every atom's message sum keeps its order, so both schedules must give the same energy
+    bit for bit; the gradient rows of an atom with several ghost copies add the arrivals before the rank's own sum
+    instead of after it, so forces agree to rounding.  Both must give the oracle's numbers."""
+    s = synth.fcc_supercell(4, 3.61, 0.05, seed=21, species=(13, 29), fractions=(0.4, 0.6))
+    model, oracle, cfg = make_models(2, 32, [13, 29], 4.0, 20.0, dtype, num_layers=num_layers, targets=("energy", "forces"))
+    ref = oracle(oracle_batch([s], [13, 29], 4.0, dtype))
+    model = model.to(DEV)
+    got, launches = {}, {}
+    for overlap in (False, True):
+        model.set_exchange_overlap(overlap)
+        before = model.launch_count()
+        md = DomainMD(model, s["cell"], s["positions"], s["atomic_numbers"], skin=0.4, device=DEV)
+        assert md.domain.n_ghost > 0
+        got[overlap] = (md.potential(), md.gather()["forces"])
+        launches[overlap] = model.launch_count() - before
+        assert model.device_error() == 0
+    # the split passes are extra launches: a schedule that silently fell back to the serial exchange would not add any
+    assert launches[True] > launches[False]
+    tol_e, tol_f = (1e-8, 1e-7) if dtype == torch.float64 else (1e-5, 1e-4)
+    n = len(s["positions"])
+    for overlap in (False, True):
+        assert abs(got[overlap][0] - float(ref["energy"][0])) / n < tol_e
+        assert np.abs(got[overlap][1] - ref["forces"].detach().double().numpy()).max() < tol_f
+    assert got[True][0] == got[False][0]
+    assert np.abs(got[True][1] - got[False][1]).max() < (1e-12 if dtype == torch.float64 else 1e-5)
+
+
 def test_single_rank_domain_with_the_tece_edge_block():
     """The same check for a model whose second interaction is the TECE edge block: ghost features through the exchange,
     gradients of ghost sources back through it, the edge-frame gradient inside the forces."""
@@ -140,7 +170,7 @@ def test_repartition_keeps_the_trajectory():
     assert np.abs(a["forces"] - b["forces"]).max() < 1e-8
 
 
-def _two_rank_worker(rank, world, port, ret):
+def _two_rank_worker(rank, world, port, ret, overlap=False):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -151,6 +181,7 @@ def _two_rank_worker(rank, world, port, ret):
     try:
         s = _system(seed=13)
         model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
+        model.set_exchange_overlap(overlap)  # exchange on its own stream, NCCL messages on a high-priority group
         masses = masses_for(s["atomic_numbers"])
         vel = maxwell_boltzmann(masses, 300.0, seed=3)
         md = DomainMD(model.to(dev), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, skin=0.4, rank=rank,
@@ -165,7 +196,8 @@ def _two_rank_worker(rank, world, port, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_match_one():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_two_ranks_match_one(overlap):
     import torch.multiprocessing as mp
 
     with socket.socket() as sk:
@@ -173,7 +205,7 @@ def test_two_ranks_match_one():
         port = sk.getsockname()[1]
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
-    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, ret, overlap)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
