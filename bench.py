@@ -447,10 +447,12 @@ def main():
 
     # end to end through the public API: pinned host buffers -> upload -> neighbour list -> evaluation -> download
     # The loop is software-pipelined the way a throughput-oriented caller would write it: upload + neighbour list of
-    # step k+1 run on a second stream while step k is evaluated; every step still uploads its own inputs from pinned
-    # memory and downloads its own results inside the timed region.  With several GPUs every step ends with one
-    # all_gather of the per-structure energies and stresses of all ranks (shares padded to the largest share).
-    e2e_split = {"upload_and_neighbour_list": 0.0, "evaluation_call": 0.0, "download": 0.0, "gather": 0.0}
+    # step k+1 run on a second stream while step k is evaluated, and the host waits for the downloaded results of step
+    # k only after it has enqueued step k+1 (two sets of pinned result buffers), so the GPU never waits for the host.
+    # Every step still uploads its own inputs from pinned memory and downloads its own results inside the timed
+    # region.  With several GPUs every step ends with one all_gather of the per-structure energies and stresses of all
+    # ranks (shares padded to the largest share).
+    e2e_split = {"upload_and_neighbour_list": 0.0, "evaluation_call": 0.0, "download_enqueue": 0.0, "gather": 0.0, "wait_previous": 0.0}
     # high priority: the neighbour-list kernels of step k+1 are short and the host waits for their edge count, so they
     # must not queue behind the long evaluation kernels of step k
     side = torch.cuda.Stream(device, priority=-1)
@@ -458,8 +460,8 @@ def main():
     share_max = int(max_over_ranks(float(n_graphs), world, device))
     gather_in = torch.zeros(share_max, 10, dtype=dtype, device=device)
     gather_out = torch.zeros(world * share_max, 10, dtype=dtype, device=device)
-    host_out = {"energy": torch.empty(n_graphs, dtype=dtype).pin_memory(), "forces": torch.empty(n_atoms, 3, dtype=dtype).pin_memory(),
-                "stress": torch.empty(n_graphs, 3, 3, dtype=dtype).pin_memory()}
+    host_out = [{"energy": torch.empty(n_graphs, dtype=dtype).pin_memory(), "forces": torch.empty(n_atoms, 3, dtype=dtype).pin_memory(),
+                 "stress": torch.empty(n_graphs, 3, 3, dtype=dtype).pin_memory()} for _ in range(2)]
 
     def prepare():
         t_a = time.perf_counter()
@@ -474,30 +476,40 @@ def main():
 
     def e2e_loop(n):
         nxt = prepare()
+        pending = None  # (event, inputs, outputs) of the step whose results are still on their way to the host
+        t_prev = time.perf_counter()
         for k in range(n):
-            t_step = time.perf_counter()
             d, ready = nxt
             torch.cuda.current_stream(device).wait_event(ready)
             t_b = time.perf_counter()
             o = model(d)
             t_c = time.perf_counter()
-            if k + 1 < n:
-                nxt = prepare()  # overlaps the evaluation of step k
-            t_d = time.perf_counter()
             if world > 1:
                 import torch.distributed as dist
                 gather_in[:n_graphs, 0] = o["energy"]
                 gather_in[:n_graphs, 1:] = o["stress"].reshape(n_graphs, 9)
                 dist.all_gather_into_tensor(gather_out, gather_in)
+            t_d = time.perf_counter()
+            for key, buf in host_out[k % 2].items():  # one asynchronous copy per result into pinned memory
+                buf.copy_(o[key], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
             t_e = time.perf_counter()
-            for key in host_out:  # one asynchronous copy per result into pinned memory, one synchronisation
-                host_out[key].copy_(o[key], non_blocking=True)
-            torch.cuda.current_stream(device).synchronize()
+            if k + 1 < n:
+                nxt = prepare()  # overlaps the evaluation of step k
+            t_f = time.perf_counter()
+            if pending is not None:  # the results of step k-1 are in host memory after this
+                pending[0].synchronize()
+                e2e_step_s.append(time.perf_counter() - t_prev)
+                t_prev = time.perf_counter()
+            pending = (done, d, o)  # inputs and outputs stay referenced until their step has finished on the device
             e2e_split["evaluation_call"] += t_c - t_b
-            e2e_split["gather"] += t_e - t_d
-            e2e_split["download"] += time.perf_counter() - t_e
-            e2e_step_s.append(time.perf_counter() - t_step)
-        return host_out
+            e2e_split["gather"] += t_d - t_c
+            e2e_split["download_enqueue"] += t_e - t_d
+            e2e_split["wait_previous"] += time.perf_counter() - t_f
+        pending[0].synchronize()
+        e2e_step_s.append(time.perf_counter() - t_prev)
+        return host_out[(n - 1) % 2]
 
     e2e_steps = min(args.steps, 100)
     e2e_loop(args.warmup)
@@ -607,7 +619,8 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "step_ms": {"min": round(1e3 * min(e2e_step_s), 3), "median": round(1e3 * statistics.median(e2e_step_s), 3),
                             "max": round(1e3 * max(e2e_step_s), 3)},
-                "pipelining": "upload + neighbour list of step k+1 on a second stream during the evaluation of step k"},
+                "pipelining": "upload + neighbour list of step k+1 on a second stream during the evaluation of step k; the host "
+                              "reads the downloaded results of step k after enqueueing step k+1"},
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "phases_ms": {k: round(v, 4) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
         "ranks": [{"device_ms_per_step": round(r[0], 3), "host_ms_per_call": round(r[1], 3), "atoms": int(r[2]), "edges": int(r[3]),

@@ -58,10 +58,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is hit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
-  if (*abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return !*abort_flag;  // the common case costs one probe
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return !*abort_flag;
+    if ((it & 1023u) == 0u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(error, 0, code);
@@ -288,12 +288,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      int step = 0, chunk = 0;
+      int chunk = 0;
       bool ok = true;
+      // This one thread issues every tensor-core instruction of the SM, and its own instruction stream is part of what
+      // the ring waits for: descriptors are built once (only their 14-bit start-address field, in 16-byte units, changes
+      // from stage to stage and from one 8-wide K slice to the next, so the later ones are sums), and the stage index and
+      // phase are counted instead of divided.
+      const uint64_t dA0 = umma_desc(stage_a(0)), dAl0 = umma_desc(stage_alo(0));
+      const uint64_t dB0 = umma_desc(stage_bhi(0)), dBl0 = umma_desc(stage_blo(0));
+      int s = 0, ph = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
-        for (int ks = 0; ks < t.num_k; ++ks, ++step) {
-          const int s = step % kStages, ph = (step / kStages) & 1;
+        for (int ks = 0; ks < t.num_k; ++ks, ph ^= (s == kStages - 1), s = (s == kStages - 1) ? 0 : s + 1) {
           const int a = chunk & 1;
           const bool chunk_begin = (ks % kChunk) == 0;
           const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == t.num_k - 1;
@@ -301,10 +307,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           if (!mbar_wait(ready_bar(s), ph, abort_flag, batch.error, 2)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t d = tmem_base + a * BN;
+          const uint64_t stage_off = (uint64_t)((uint32_t)(s * S::kStageBytes) >> 4);
 #pragma unroll
           for (int k8 = 0; k8 < kBK / 8; ++k8) {
-            const uint64_t da = umma_desc(stage_a(s) + k8 * 32), dal = umma_desc(stage_alo(s) + k8 * 32);
-            const uint64_t db = umma_desc(stage_bhi(s) + k8 * 32), dbl = umma_desc(stage_blo(s) + k8 * 32);
+            const uint64_t off = stage_off + (uint64_t)(k8 * 2);  // 8 fp32 = 32 bytes along K inside the swizzled row
+            const uint64_t da = dA0 + off, dal = dAl0 + off, db = dB0 + off, dbl = dBl0 + off;
             umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
             umma_tf32(d, da, dbl, idesc, 1u);
             umma_tf32(d, dal, db, idesc, 1u);
@@ -326,15 +333,21 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
         if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3)) { ok = false; break; }
         float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
         float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
+        // every load of the tile before its first store: the stores go to the buffer the loads come from, so the compiler
+        // must keep their order, and sixteen dependent load -> store rounds would put their latencies end to end on the
+        // critical path of the operand ring
+        constexpr int kPer = kTileABytes / 16 / kSplitThreads;
+        float4 v[kPer];
 #pragma unroll
-        for (int j = 0; j < kTileABytes / 16 / kSplitThreads; ++j) {
+        for (int j = 0; j < kPer; ++j) v[j] = a[t64 + j * kSplitThreads];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
           const int idx = t64 + j * kSplitThreads;
-          const float4 v = a[idx];
           float4 h, l;
-          h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
-          h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
-          h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
-          h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+          h.x = __uint_as_float(__float_as_uint(v[j].x) & 0xFFFFE000u); l.x = v[j].x - h.x;
+          h.y = __uint_as_float(__float_as_uint(v[j].y) & 0xFFFFE000u); l.y = v[j].y - h.y;
+          h.z = __uint_as_float(__float_as_uint(v[j].z) & 0xFFFFE000u); l.z = v[j].z - h.z;
+          h.w = __uint_as_float(__float_as_uint(v[j].w) & 0xFFFFE000u); l.w = v[j].w - h.w;
           a[idx] = h;
           alo[idx] = l;
         }

@@ -153,9 +153,11 @@ class DomainMD:
             # list stay valid until an atom has moved more than half the skin; every step only filters the list down
             # to the pairs that are inside the cutoff now (the same fp64 test a fresh list would apply).
             if self._skin_edges is None:
+                t_l = time.perf_counter()
                 self._skin_edges, _ = neighbor_list_batch(local_pos, lattice, pbc, ptr, self.cutoff + self.skin, n_targets=n)
                 self._skin_edges = self._skin_edges.contiguous()
                 self.n_list_builds += 1
+                self.timings["list_build"] = self.timings.get("list_build", 0.0) + time.perf_counter() - t_l
             wide = self._skin_edges
             Ew = int(wide.shape[1])
             keep = torch.empty(Ew, dtype=torch.uint8, device=self.device)
@@ -196,7 +198,9 @@ class DomainMD:
             if self.step_count >= self._next_check:
                 moved, fastest = self.domain.displacement(self.positions, self.velocities)
                 if moved > 0.5 * self.skin:
+                    t_r = time.perf_counter()
                     self._repartition(self._state())
+                    self.timings["repartition"] = self.timings.get("repartition", 0.0) + time.perf_counter() - t_r
                     moved = 0.0
                 # no atom can cross half the skin before it has travelled the remaining margin: look again after half
                 # the steps the fastest atom would need at twice its present speed (at most 16 steps)
