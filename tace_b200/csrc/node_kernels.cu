@@ -358,51 +358,86 @@ cudaError_t launch_pb3_bwd(const T* A, const T* B2, const T* gB3, T* gB2, T* gA,
 }
 
 // ---- read-out ------------------------------------------------------------------------------------
+// One warp per atom.  Lane j holds the hidden unit r_j (and r_{j+32}): the atom's scalar channels are staged in shared
+// memory and broadcast, the weights of head 0 sit in shared memory as [C][H] (r_j: consecutive lanes, consecutive
+// words) and, when there is room (with_t), also transposed as [H][C] for the gradient d e / d h_c = sum_j (d e / d r_j)
+// W1[c][j], where lanes run over c.  Sums over lanes use a fixed butterfly, so results do not depend on the launch.
 template <typename T>
-__global__ void readout_kernel(const ReadoutArgs<T> a) {
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+template <typename T>
+__global__ void readout_kernel(const ReadoutArgs<T> a, int with_t) {
   extern __shared__ unsigned char smem_raw[];
-  T* W1s = reinterpret_cast<T*>(smem_raw);  // [C][H]: head 0; other heads are read from global memory
-  for (int k = threadIdx.x; k < a.C * a.H; k += blockDim.x) W1s[k] = a.W1[k];
+  const int C = a.C, H = a.H, nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  T* W1s = reinterpret_cast<T*>(smem_raw);       // [C][H], head 0
+  T* W1t = W1s + C * H;                           // [H][C], head 0 (with_t)
+  T* hrow = W1t + (with_t ? C * H : 0) + warp * C;                        // [C] scalar channels of this warp's atom
+  T* dr = W1t + (with_t ? C * H : 0) + nw * C + warp * 64;                // [64] d e / d r_j
+  for (int k = threadIdx.x; k < C * H; k += blockDim.x) {
+    const T v = a.W1[k];
+    W1s[k] = v;
+    if (with_t) W1t[(k % H) * C + k / H] = v;
+  }
   __syncthreads();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= a.n) return;
-  const int g = a.atom_graph[i];
-  const int f = a.fidelity ? a.fidelity[g] : 0;
-  const T* W1 = f == 0 ? W1s : a.W1 + (long long)f * a.C * a.H;
-  const T* W2 = a.W2 + f * a.H;
-  const T* h = a.h + (long long)i * a.hs;
-  T r[64];
-  for (int j = 0; j < a.H; ++j) r[j] = T(0);
-  for (int c = 0; c < a.C; ++c) {
-    const T hc = h[c];
-    for (int j = 0; j < a.H; ++j) r[j] += hc * W1[c * a.H + j];
-  }
-  T e = T(0);
-  for (int j = 0; j < a.H; ++j) {
-    e += T(kSiluCst) * silu_(r[j]) * W2[j];
-    r[j] = T(kSiluCst) * silu_grad_(r[j]) * W2[j];  // d e / d r_j
-  }
-  for (int t = 0; t < a.n_extra; ++t) {
-    const T* ht = a.extra_h[t] + (long long)i * a.extra_hs[t];
-    T acc = T(0);
-    for (int c = 0; c < a.C; ++c) acc += ht[c] * a.extra_w[t][f * a.C + c];
-    e += acc;
-  }
-  if (a.zbl && !a.zbl_after) e += a.zbl[i];
-  const int z = f * a.n_el + a.species[i];
-  const int n_nodes = a.graph_ptr[g + 1] - a.graph_ptr[g];
-  const int n_edges = a.rowptr_dst[a.graph_ptr[g + 1]] - a.rowptr_dst[a.graph_ptr[g]];
-  const T sc = (n_nodes == 1 && n_edges == 0) ? T(0) : a.scale[z];
-  const T es = (a.zbl && a.zbl_after) ? e * sc + a.zbl[i] : e * sc;
-  a.e_scaled[i] = es;
-  if (a.factor) a.factor[i] = sc;
-  if (a.node_energy) a.node_energy[i] = a.e0[z] + es;
-  if (a.gh) {
-    T* gh = a.gh + (long long)i * a.C;
-    for (int c = 0; c < a.C; ++c) {
-      T v = T(0);
-      for (int j = 0; j < a.H; ++j) v += r[j] * W1[c * a.H + j];
-      gh[c] = v * sc;
+  for (int i = blockIdx.x * nw + warp; i < a.n; i += gridDim.x * nw) {
+    const int g = a.atom_graph[i];
+    const int f = a.fidelity ? a.fidelity[g] : 0;
+    const T* W1 = a.W1 + (long long)f * C * H;  // other heads are read from global memory
+    const T* W2 = a.W2 + f * H;
+    const T* h = a.h + (long long)i * a.hs;
+    __syncwarp();
+    for (int c = lane; c < C; c += 32) hrow[c] = h[c];
+    __syncwarp();
+    T r0 = T(0), r1 = T(0);
+    if (f == 0) {
+      for (int c = 0; c < C; ++c) {
+        const T hc = hrow[c];
+        if (lane < H) r0 += hc * W1s[c * H + lane];
+        if (lane + 32 < H) r1 += hc * W1s[c * H + lane + 32];
+      }
+    } else {
+      for (int c = 0; c < C; ++c) {
+        const T hc = hrow[c];
+        if (lane < H) r0 += hc * W1[c * H + lane];
+        if (lane + 32 < H) r1 += hc * W1[c * H + lane + 32];
+      }
+    }
+    T e = T(0);
+    if (lane < H) { e += T(kSiluCst) * silu_(r0) * W2[lane]; dr[lane] = T(kSiluCst) * silu_grad_(r0) * W2[lane]; }
+    if (lane + 32 < H) { e += T(kSiluCst) * silu_(r1) * W2[lane + 32]; dr[lane + 32] = T(kSiluCst) * silu_grad_(r1) * W2[lane + 32]; }
+    e = warp_sum(e);
+    for (int t = 0; t < a.n_extra; ++t) {
+      const T* ht = a.extra_h[t] + (long long)i * a.extra_hs[t];
+      T acc = T(0);
+      for (int c = lane; c < C; c += 32) acc += ht[c] * a.extra_w[t][f * C + c];
+      e += warp_sum(acc);
+    }
+    if (a.zbl && !a.zbl_after) e += a.zbl[i];
+    const int z = f * a.n_el + a.species[i];
+    const int n_nodes = a.graph_ptr[g + 1] - a.graph_ptr[g];
+    const int n_edges = a.rowptr_dst[a.graph_ptr[g + 1]] - a.rowptr_dst[a.graph_ptr[g]];
+    const T sc = (n_nodes == 1 && n_edges == 0) ? T(0) : a.scale[z];
+    const T es = (a.zbl && a.zbl_after) ? e * sc + a.zbl[i] : e * sc;
+    if (lane == 0) {
+      a.e_scaled[i] = es;
+      if (a.factor) a.factor[i] = sc;
+      if (a.node_energy) a.node_energy[i] = a.e0[z] + es;
+    }
+    if (a.gh) {
+      __syncwarp();  // dr is complete
+      T* gh = a.gh + (long long)i * C;
+      for (int c = lane; c < C; c += 32) {
+        T v = T(0);
+        if (f == 0 && with_t) {
+          for (int j = 0; j < H; ++j) v += dr[j] * W1t[j * C + c];
+        } else {
+          for (int j = 0; j < H; ++j) v += dr[j] * W1[c * H + j];
+        }
+        gh[c] = v * sc;
+      }
     }
   }
 }
@@ -487,8 +522,15 @@ template <typename T>
 cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
   if (a.n <= 0) return cudaSuccess;
   if (a.H > 64) return cudaErrorInvalidValue;
-  const size_t smem = sizeof(T) * a.C * a.H;
-  readout_kernel<T><<<(a.n + 63) / 64, 64, smem, s>>>(a);
+  const size_t w1 = sizeof(T) * (size_t)a.C * a.H;
+  int warps = 8;  // fewer warps per block when the weights leave little of the default 48 KB
+  while (warps > 1 && w1 + sizeof(T) * (size_t)warps * (a.C + 64) > 48 * 1024) warps >>= 1;
+  const size_t per_warp = sizeof(T) * (size_t)warps * (a.C + 64);
+  const int with_t = (2 * w1 + per_warp <= 48 * 1024) ? 1 : 0;  // the transposed copy only where it fits as well
+  const size_t smem = (with_t ? 2 : 1) * w1 + per_warp;
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  const int blocks = (a.n + warps - 1) / warps;
+  readout_kernel<T><<<blocks < 1184 ? blocks : 1184, warps * 32, smem, s>>>(a, with_t);
   return cudaGetLastError();
 }
 
