@@ -1,6 +1,7 @@
 // Per-atom element-wise kernels: species gather, gate, product basis, read-out, graph sums.
 // Feature layout everywhere: [atom][component (l, m)][channel], channel fastest, so a warp
 // always touches 32 consecutive channels of one component.
+#include <cstdint>
 #include "kernels.h"
 #include "tp_gen.cuh"
 
@@ -33,8 +34,9 @@ cudaError_t launch_add_inplace(T* dst, const T* src, long long n, cudaStream_t s
   return cudaGetLastError();
 }
 
-template <typename T, bool SCATTER>
-__global__ void permute_rows_kernel(const T* __restrict__ src, const int* __restrict__ perm, T* __restrict__ dst, long long n, int row_len) {
+// V: the row is moved in 16-byte pieces (uint4) when its length and both base addresses allow, else element by element.
+template <typename V, bool SCATTER>
+__global__ void permute_rows_kernel(const V* __restrict__ src, const int* __restrict__ perm, V* __restrict__ dst, long long n, int row_len) {
   const long long total = n * row_len;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     const long long i = idx / row_len, k = idx - i * row_len;
@@ -42,19 +44,27 @@ __global__ void permute_rows_kernel(const T* __restrict__ src, const int* __rest
     if (SCATTER) dst[j * row_len + k] = src[idx]; else dst[idx] = src[j * row_len + k];
   }
 }
-template <typename T>
-cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
+template <typename T, bool SCATTER>
+cudaError_t launch_permute_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  const long long blocks = (n * row_len + 255) / 256;
-  permute_rows_kernel<T, false><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(src, perm, dst, n, row_len);
+  constexpr int per = 16 / sizeof(T);
+  const bool wide = row_len % per == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  const int len = wide ? row_len / per : row_len;
+  const long long blocks = (n * len + 255) / 256;
+  const unsigned grid = (unsigned)(blocks < 148 * 32 ? blocks : 148 * 32);
+  if (wide)
+    permute_rows_kernel<uint4, SCATTER><<<grid, 256, 0, s>>>(reinterpret_cast<const uint4*>(src), perm, reinterpret_cast<uint4*>(dst), n, len);
+  else
+    permute_rows_kernel<T, SCATTER><<<grid, 256, 0, s>>>(src, perm, dst, n, len);
   return cudaGetLastError();
 }
 template <typename T>
+cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
+  return launch_permute_rows<T, false>(src, perm, dst, n, row_len, s);
+}
+template <typename T>
 cudaError_t launch_scatter_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s) {
-  if (n <= 0) return cudaSuccess;
-  const long long blocks = (n * row_len + 255) / 256;
-  permute_rows_kernel<T, true><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(src, perm, dst, n, row_len);
-  return cudaGetLastError();
+  return launch_permute_rows<T, true>(src, perm, dst, n, row_len, s);
 }
 
 template <typename T>
