@@ -241,6 +241,12 @@ int tace_profile_read(TaceModel* model, int index, const char** name, float* ms)
  * non-zero code if a bounded wait inside the kernel expired (results are then undefined). */
 int tace_tc_gemm_f32(const float* A, int64_t lda, const float* B_hi, const float* B_lo, float* C, int64_t ldc, int32_t M,
                      int32_t N, int32_t K, int32_t* error_flag, tace_stream_t stream);
+/* Test mode of that kernel's bounded waits: every wait gives up after `spin_limit` polls (0: the normal 2^22), and every
+ * load barrier expects `extra_expected_bytes` more than its loads deliver (0: normal), so that with a non-zero value it
+ * never completes.  With both set, the next tace_tc_gemm_f32 records the code of the wait that ran out in `error_flag`
+ * (1 ring slot free, 2 operands ready, 3 load landed, 4 accumulator free, 5 accumulator full), waits for the loads it has
+ * issued, frees its tensor memory and returns without a result; no fault is involved.  Process-wide; reset with (0, 0). */
+int tace_tc_gemm_set_test_mode(uint32_t spin_limit, uint32_t extra_expected_bytes);
 
 /* Reads (and clears) the model's device-side error word: 0 = none; non-zero = a bounded wait in a
  * kernel launched by tace_forward expired.  Synchronises the device. */

@@ -57,9 +57,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is hit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code,
+                                          uint32_t limit) {
   if (mbar_try_wait(bar, parity)) return !*abort_flag;  // the common case costs one probe
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return !*abort_flag;
     if ((it & 1023u) == 0u && *abort_flag) return false;
   }
@@ -125,6 +126,8 @@ struct TcBatch {
   int n_problems;
   int tile_start[kTcMaxProblems + 1];  // prefix sum of the problems' tile counts
   int* error;
+  uint32_t spin_limit;   // polls per wait before a role gives up (kSpinLimit; smaller in the test mode)
+  uint32_t extra_tx;     // test mode: bytes added to what the first load barrier expects, so that it never completes
 };
 
 // Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = operand
@@ -217,7 +220,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   auto empty_bar = [&](int s) { return bars + 8u * (2 * kStages + s); };
   auto acc_full = [&](int a) { return bars + 8u * (3 * kStages + a); };
   auto acc_empty = [&](int a) { return bars + 8u * (3 * kStages + 2 + a); };
-  unsigned char* misc = base_ptr + kStages * S::kStageBytes + S::kStoreBytes + 8 * (3 * kStages + 4);
+  const uint32_t drain_bar = bars + 8u * (3 * kStages + 4);  // abort path only: issued tensor-core work has retired
+  unsigned char* misc = base_ptr + kStages * S::kStageBytes + S::kStoreBytes + 8 * (3 * kStages + 5);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
   int* tile_start = reinterpret_cast<int*>(misc + 16);  // [n_problems + 1]
@@ -226,6 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), kSplitThreads); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
+    mbar_init(drain_bar, 1);
     *abort_flag = 0;
     int acc = 0;
     for (int i = 0; i < batch.n_problems; ++i) {
@@ -265,8 +270,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
         const uint32_t a_bytes = (uint32_t)P.R * P.q * kBK * 4;
         for (int ks = 0; ks < t.num_k; ++ks, ++step) {
           const int s = step % kStages, ph = (step / kStages) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, batch.error, 1)) { ok = false; break; }
-          mbar_expect_tx(raw_bar(s), a_bytes + 2 * S::kTileBBytes);
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, batch.error, 1, batch.spin_limit)) { ok = false; break; }
+          mbar_expect_tx(raw_bar(s), a_bytes + 2 * S::kTileBBytes + batch.extra_tx);
           tma_load_3d(stage_a(s), &P.tmA, raw_bar(s), ks * kBK, 0, t.atom0);
           if (P.b_tiled) {  // weights stored K-tile-major: one contiguous block per (k-step, n-tile)
             tma_load_4d(stage_bhi(s), &P.tmBhi, raw_bar(s), 0, t.n0, ks, t.group);
@@ -280,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       if (*abort_flag) {  // loads already issued must land before the CTA exits
         for (int j = step > kStages ? step - kStages : 0; j < step; ++j) {
           const int s = j % kStages, ph = (j / kStages) & 1;
-          for (uint32_t it = 0; it < kSpinLimit; ++it)
+          for (uint32_t it = 0; it < batch.spin_limit; ++it)
             if (mbar_try_wait(raw_bar(s), ph)) break;
         }
       }
@@ -303,8 +308,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           const int a = chunk & 1;
           const bool chunk_begin = (ks % kChunk) == 0;
           const bool chunk_end = (ks % kChunk) == kChunk - 1 || ks == t.num_k - 1;
-          if (chunk_begin && !mbar_wait(acc_empty(a), ((chunk >> 1) & 1) ^ 1, abort_flag, batch.error, 4)) { ok = false; break; }
-          if (!mbar_wait(ready_bar(s), ph, abort_flag, batch.error, 2)) { ok = false; break; }
+          if (chunk_begin && !mbar_wait(acc_empty(a), ((chunk >> 1) & 1) ^ 1, abort_flag, batch.error, 4, batch.spin_limit)) { ok = false; break; }
+          if (!mbar_wait(ready_bar(s), ph, abort_flag, batch.error, 2, batch.spin_limit)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t d = tmem_base + a * BN;
           const uint64_t stage_off = (uint64_t)((uint32_t)(s * S::kStageBytes) >> 4);
@@ -320,6 +325,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           if (chunk_end) { umma_commit(acc_full(a)); ++chunk; }  // partial sum of this chunk complete
         }
       }
+      if (*abort_flag) {  // tensor-core work already issued must retire before the tensor memory is given back
+        umma_commit(drain_bar);
+        for (uint32_t it = 0; it < batch.spin_limit; ++it)
+          if (mbar_try_wait(drain_bar, 0)) break;
+      }
     }
   } else if (warp < 4) {
     // ---- operand splitters: A = hi + lo with hi exact in TF32, element-wise and in place
@@ -330,7 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       const TileInfo t = decode_tile<BN>(batch, tile_start, tile);
       for (int ks = 0; ks < t.num_k; ++ks, ++step) {
         const int s = step % kStages, ph = (step / kStages) & 1;
-        if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3)) { ok = false; break; }
+        if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3, batch.spin_limit)) { ok = false; break; }
         float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
         float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
         // every load of the tile before its first store: the stores go to the buffer the loads come from, so the compiler
@@ -375,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       const int n_chunks = (t.num_k + kChunk - 1) / kChunk;
       for (int cin = 0; cin < n_chunks; ++cin, ++chunk) {
         const int a = chunk & 1;
-        if (!mbar_wait(acc_full(a), (chunk >> 1) & 1, abort_flag, batch.error, 5)) { ok = false; break; }
+        if (!mbar_wait(acc_full(a), (chunk >> 1) & 1, abort_flag, batch.error, 5, batch.spin_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
@@ -557,6 +567,11 @@ cudaError_t launch_tc(const TcBatch& b, int dev, int sms, cudaStream_t s) {
 
 }  // namespace
 
+// Test mode of the bounded waits (tace_tc_gemm_set_test_mode): a short poll limit, and a byte count added to what the
+// load barriers expect so that they never complete; both 0 in normal operation.
+static uint32_t g_test_spin_limit = 0, g_test_extra_tx = 0;
+void tc_gemm_set_test_mode(uint32_t spin_limit, uint32_t extra_tx) { g_test_spin_limit = spin_limit; g_test_extra_tx = extra_tx; }
+
 bool tc_linear_supported(int N, int K) { return N % 64 == 0 && K % kBK == 0; }
 
 cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* error_flag, cudaStream_t s) {
@@ -582,6 +597,8 @@ cudaError_t launch_tc_linear(const TcLinearProblem* probs, int n_problems, int* 
   memset(&b, 0, sizeof(b));
   b.n_problems = 0;
   b.error = error_flag;
+  b.spin_limit = g_test_spin_limit ? g_test_spin_limit : kSpinLimit;
+  b.extra_tx = g_test_extra_tx;
   int tiles = 0;
   for (int i = 0; i < n_problems; ++i) {
     const TcLinearProblem& h = probs[i];
@@ -634,4 +651,9 @@ extern "C" int tace_tc_gemm_f32(const float* A, int64_t lda, const float* B_hi, 
   cudaError_t e = tace::launch_tc_gemm(A, lda, B_hi, B_lo, C, ldc, M, N, K, error_flag, static_cast<cudaStream_t>(stream), nullptr);
   if (e == cudaErrorInvalidValue) return TACE_ERR_INVALID_ARGUMENT;
   return e == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+extern "C" int tace_tc_gemm_set_test_mode(uint32_t spin_limit, uint32_t extra_expected_bytes) {
+  tace::tc_gemm_set_test_mode(spin_limit, extra_expected_bytes);
+  return TACE_OK;
 }

@@ -18,7 +18,7 @@ TACE_F32, TACE_F64 = 0, 1
 EXPORTS = [
     "tace_status_string", "tace_create", "tace_destroy", "tace_weight_count", "tace_weight_info", "tace_set_weight",
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill", "tace_nl_workspace_bytes",
-    "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32",
+    "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32", "tace_tc_gemm_set_test_mode",
     "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
     "tace_edge_vectors", "tace_edges_within", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays", "tace_set_exchange_sync", "tace_set_exchange_stream",
     "tace_set_chunk_edges", "tace_md_langevin",
@@ -99,6 +99,7 @@ def load() -> ctypes.CDLL:
     lib.tace_set_exchange.argtypes = [c_void_p, EXCHANGE_FN, c_void_p]
     lib.tace_set_exchange_sync.argtypes = [c_void_p, c_int]
     lib.tace_set_exchange_stream.argtypes = [c_void_p, c_void_p]
+    lib.tace_tc_gemm_set_test_mode.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
     lib.tace_nl_workspace_bytes.argtypes = [c_int64, c_int32, POINTER(ctypes.c_size_t)]
     lib.tace_nl_count.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_double, c_void_p, c_void_p,
                                   ctypes.c_size_t, c_void_p]
