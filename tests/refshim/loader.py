@@ -23,7 +23,9 @@ import torch
 
 from . import mini_e3nn
 
-REFERENCE_ROOT = os.environ.get("TACE_REFERENCE_ROOT", "/root/reference")
+# The reference's source tree: TACE_REFERENCE_ROOT, or a directory named "reference" beside this repository.
+_REPO_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REFERENCE_ROOT = os.environ.get("TACE_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO_ROOT), "reference"))
 _PLACEHOLDER_ROOTS = ("matscipy", "lightning", "pytorch_lightning", "hydra", "omegaconf", "torch_scatter",
                       "h5py", "lmdb", "vesin", "torch_ema", "torchmetrics", "wandb", "opt_einsum", "cuequivariance",
                       "cuequivariance_torch", "openequivariance", "equitorch", "ase", "torch_geometric", "nvalchemiops",
