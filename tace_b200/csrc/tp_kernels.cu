@@ -11,6 +11,7 @@
 // (in place over W), of the angular features (reduced over channels with warp shuffles) and of
 // the source features (one row per edge, summed per source atom by launch_segment_sum_rows).
 // Edge lists are sorted, so every sum is a segmented reduction: no atomics, bit-reproducible.
+#include <cstdint>
 #include "kernels.h"
 #include "tp_gen.cuh"
 
@@ -410,14 +411,24 @@ __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
   }
 }
 
-template <typename T>
-__global__ void segment_sum_rows_kernel(const T* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
-                                        T* __restrict__ gx, int first, int row_len) {
+// V = T, or a 16-byte vector of T when the row length and the base addresses allow: every element is still summed over the
+// edges in list order, so the result does not depend on the vector width.
+template <typename T, int W>
+struct alignas(sizeof(T) * W) RowVec { T v[W]; };
+template <typename T, int W>
+__global__ void segment_sum_rows_kernel(const RowVec<T, W>* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
+                                        RowVec<T, W>* __restrict__ gx, int first, int row_len) {
   const int b = first + blockIdx.x;
   const int beg = rowptr[b], end = rowptr[b + 1];
   for (int k = threadIdx.x; k < row_len; k += blockDim.x) {
-    T acc = T(0);
-    for (int j = beg; j < end; ++j) acc += dxe[(long long)perm[j] * row_len + k];
+    RowVec<T, W> acc;
+#pragma unroll
+    for (int i = 0; i < W; ++i) acc.v[i] = T(0);
+    for (int j = beg; j < end; ++j) {
+      const RowVec<T, W> x = dxe[(long long)perm[j] * row_len + k];
+#pragma unroll
+      for (int i = 0; i < W; ++i) acc.v[i] += x.v[i];
+    }
     gx[(long long)b * row_len + k] = acc;
   }
 }
@@ -425,7 +436,14 @@ template <typename T>
 cudaError_t launch_segment_sum_rows(const T* dxe, const int* rowptr_src, const int* perm_src, T* gx, int first_atom, int n_atoms,
                                     int row_len, cudaStream_t s) {
   if (n_atoms <= 0) return cudaSuccess;
-  segment_sum_rows_kernel<T><<<n_atoms, 256, 0, s>>>(dxe, rowptr_src, perm_src, gx, first_atom, row_len);
+  constexpr int W = 16 / sizeof(T);
+  auto threads_for = [](int items) { const int t = (items + 31) / 32 * 32; return t < 32 ? 32 : (t > 256 ? 256 : t); };
+  if (row_len % W == 0 && ((reinterpret_cast<uintptr_t>(dxe) | reinterpret_cast<uintptr_t>(gx)) & 15) == 0)
+    segment_sum_rows_kernel<T, W><<<n_atoms, threads_for(row_len / W), 0, s>>>(reinterpret_cast<const RowVec<T, W>*>(dxe), rowptr_src, perm_src,
+                                                            reinterpret_cast<RowVec<T, W>*>(gx), first_atom, row_len / W);
+  else
+    segment_sum_rows_kernel<T, 1><<<n_atoms, threads_for(row_len), 0, s>>>(reinterpret_cast<const RowVec<T, 1>*>(dxe), rowptr_src, perm_src,
+                                                            reinterpret_cast<RowVec<T, 1>*>(gx), first_atom, row_len);
   return cudaGetLastError();
 }
 
