@@ -461,7 +461,10 @@ class TensorModel(torch.nn.Module):
         ws = self._workspace
         if ws is None or ws.numel() < nbytes or ws.device != device:
             self._workspace = None
-            ws = torch.empty(int(nbytes * (1.1 if nbytes < (8 << 30) else 1.02)) + 4096, dtype=torch.uint8, device=device)
+            # head room for batches that grow a little (an MD run re-partitions every few dozen steps and its edge count
+            # drifts by a per cent or so): growing means a second allocation of the full size beside the cached old one
+            # and tens of milliseconds in the allocator
+            ws = torch.empty(int(nbytes + min(0.1 * nbytes, 4 << 30)) + 4096, dtype=torch.uint8, device=device)
             self._workspace = ws
         return ws
 
