@@ -19,6 +19,10 @@ namespace tace {
 
 constexpr int kEdgeBatch = 8;
 
+// W consecutive values of T moved as one piece (16 bytes for W = 16 / sizeof(T)).
+template <typename T, int W>
+struct alignas(sizeof(T) * W) RowVec { T v[W]; };
+
 // Build the coupling rows G_e = K . Y_e of edges [e0, e0 + nb) in shared memory: the generated row
 // builder comes in TP::NPART parts (two per output group); parts [part0, part0 + nparts) are built, one
 // thread per (edge, part).
@@ -303,7 +307,7 @@ template <typename T, typename TP, bool ENV, bool RT>
 __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
   constexpr int D = TP::D, NP = TP::NP, EB = kEdgeBatch;
   static_assert(TP::NX == 1 && TP::NM == TP::D, "scalar source: one path per rank");
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(32) unsigned char smem_raw[];
   const int i = blockIdx.x, c = threadIdx.x, C = a.C;
   T* gMs = reinterpret_cast<T*>(smem_raw);  // [D][C]
   T* zs = gMs + D * C;                      // [EB][NP][C]
@@ -377,14 +381,18 @@ __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
     for (int r = c; r < nb * D; r += blockDim.x) {
       const int e = r / D, lm = r - e * D;
       const int l = lm < 1 ? 0 : lm < 4 ? 1 : lm < 9 ? 2 : 3;
-      const T* zr = zs + (e * NP + l) * C;
-      const T* gr = gMs + lm * C;
-      int k = r % C;  // rotated start: consecutive (edge, component) pairs of a warp start in consecutive banks
-      T acc = T(0);
-      for (int n = 0; n < C; ++n) {
-        acc += zr[k] * gr[k];
-        k = k + 1 == C ? 0 : k + 1;
+      // four channels per step (C is a multiple of 32), four partial sums, combined in a fixed order
+      const RowVec<T, 4>* zr = reinterpret_cast<const RowVec<T, 4>*>(zs + (e * NP + l) * C);
+      const RowVec<T, 4>* gr = reinterpret_cast<const RowVec<T, 4>*>(gMs + lm * C);
+      const int C4 = C >> 2;
+      int k = r % C4;  // rotated start: consecutive (edge, component) pairs of a warp start in different banks
+      T p0 = T(0), p1 = T(0), p2 = T(0), p3 = T(0);
+      for (int n = 0; n < C4; ++n) {
+        const RowVec<T, 4> z = zr[k], g = gr[k];
+        p0 += z.v[0] * g.v[0]; p1 += z.v[1] * g.v[1]; p2 += z.v[2] * g.v[2]; p3 += z.v[3] * g.v[3];
+        k = k + 1 == C4 ? 0 : k + 1;
       }
+      const T acc = (p0 + p1) + (p2 + p3);
       T* dst = a.dY + (long long)(e0 + e) * D + lm;
       *dst = a.accumulate_dY ? (*dst + acc) : acc;
     }
@@ -392,13 +400,16 @@ __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
     if ((RT || ENV) && c >= first && c < first + 2 * nb) {
       const int e = (c - first) >> 1, which = (c - first) & 1;
       if ((which == 0 && RT) || (which == 1 && ENV)) {
-        const T* rr = rs + (e * 2 + which) * C;
-        int k = (8 * e + 4 * which) % C;
-        T acc = T(0);
-        for (int n = 0; n < C; ++n) {
-          acc += rr[k];
-          k = k + 1 == C ? 0 : k + 1;
+        const RowVec<T, 4>* rr = reinterpret_cast<const RowVec<T, 4>*>(rs + (e * 2 + which) * C);
+        const int C4 = C >> 2;
+        int k = (2 * e + which) % C4;
+        T p0 = T(0), p1 = T(0), p2 = T(0), p3 = T(0);
+        for (int n = 0; n < C4; ++n) {
+          const RowVec<T, 4> x = rr[k];
+          p0 += x.v[0]; p1 += x.v[1]; p2 += x.v[2]; p3 += x.v[3];
+          k = k + 1 == C4 ? 0 : k + 1;
         }
+        const T acc = (p0 + p1) + (p2 + p3);
         if (which == 0) {
           T* dst = a.ddlen + (e0 + e);
           *dst = a.accumulate_ddlen ? (*dst + acc) : acc;
@@ -413,8 +424,6 @@ __global__ void tp_bwd_scalar_kernel(const TPArgs<T> a) {
 
 // V = T, or a 16-byte vector of T when the row length and the base addresses allow: every element is still summed over the
 // edges in list order, so the result does not depend on the vector width.
-template <typename T, int W>
-struct alignas(sizeof(T) * W) RowVec { T v[W]; };
 template <typename T, int W>
 __global__ void segment_sum_rows_kernel(const RowVec<T, W>* __restrict__ dxe, const int* __restrict__ rowptr, const int* __restrict__ perm,
                                         RowVec<T, W>* __restrict__ gx, int first, int row_len) {
