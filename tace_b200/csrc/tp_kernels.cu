@@ -279,7 +279,8 @@ __device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned c
   }
 }
 template <typename T, typename TP, bool ENV, bool RT, bool LIST>
-__global__ void __maxnreg__(168) tp_bwd_kernel(const TPArgs<T> a) {
+// register cap: rank 3 needs 168 to stay (nearly) free of spills; up to rank 2 fits 128, which lets two more blocks share an SM
+__global__ void __maxnreg__(TP::L <= 2 ? 128 : 168) tp_bwd_kernel(const TPArgs<T> a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ T red_u[kEdgeBatch * 8];                // envelope-gradient partial sums
   __shared__ T red_r[RT ? kEdgeBatch * 8 : 1];       // edge-length-gradient partial sums (tabulated weights)
