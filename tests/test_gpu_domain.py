@@ -80,6 +80,12 @@ def test_single_rank_domain_with_the_tece_edge_block():
     assert abs(md.potential() - float(ref["energy"][0])) / len(s["positions"]) < 1e-8
     assert np.abs(got["forces"] - ref["forces"].detach().numpy()).max() < 1e-7
     assert model.device_error() == 0
+    # with an exchange stream the edge block still waits for its ghost rows before it starts: same numbers
+    model.set_exchange_overlap(True)
+    md2 = DomainMD(model, s["cell"], s["positions"], s["atomic_numbers"], skin=0.4, device=DEV)
+    assert md2.potential() == md.potential()
+    assert np.abs(md2.gather()["forces"] - got["forces"]).max() < 1e-12
+    assert model.device_error() == 0
 
 
 def test_md_support_kernels_match_torch():
