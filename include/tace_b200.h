@@ -328,6 +328,12 @@ int tace_nl_build_noalloc(const double* positions, const double* lattice, const 
  *   neighbour-list kernel's operation order: filters a list built with cutoff + skin down to the edges a fresh list
  *   with `cutoff` would hold (LAMMPS keeps such a skin list, `neighbor 2.0 bin`, docs/source/guide/lammps.rst:125;
  *   the reference's ASE calculator rebuilds its list on every call, tace/interface/ase/calculator.py:132-152).
+ * tace_edges_scan / tace_edges_compact: the filtered list itself.  tace_edges_scan writes, for every edge of the list,
+ *   the number of kept edges before it (`position`, exclusive sum of `keep`; fewer than 2^31 edges) and the number kept
+ *   (`total`, one device int64 the caller reads to size the outputs); scratch from the caller
+ *   (tace_edges_scan_workspace_bytes).  tace_edges_compact then writes the kept edges in list order (out_index int64
+ *   [2,n_kept], so a list sorted by target stays sorted) and their vectors (out_vec [n_kept,3] in `dtype`, the same
+ *   fp64 difference as tace_edge_vectors).
  * tace_rows_gather: dst[r,:] = src[index[r],:] for r < n_rows (packs a halo message; elem_bytes 4 or 8).
  * tace_rows_scatter_add: dst[index[r],:] += src[r,:]; the indices of one call must be distinct (unpacks
  *   gradients returned by a neighbouring domain, tace/models/lammps.py:105-129); float / double rows. */
@@ -341,6 +347,12 @@ int tace_edge_vectors(const double* positions, const int64_t* edge_index, int64_
                       tace_stream_t stream);
 int tace_edges_within(const double* positions, const int64_t* edge_index, int64_t n_edges, double cutoff, uint8_t* keep,
                       tace_stream_t stream);
+int tace_edges_scan_workspace_bytes(int64_t n_edges, size_t* bytes);
+int tace_edges_scan(const uint8_t* keep, int64_t n_edges, int32_t* position, int64_t* total, void* workspace,
+                    size_t workspace_bytes, tace_stream_t stream);
+int tace_edges_compact(const double* positions, const int64_t* edge_index, int64_t n_edges, const uint8_t* keep,
+                       const int32_t* position, int64_t n_kept, int64_t* out_index, void* out_vec, int32_t dtype,
+                       tace_stream_t stream);
 int tace_rows_gather(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,
                      tace_stream_t stream);
 int tace_rows_scatter_add(const void* src, const int64_t* index, int64_t n_rows, int32_t row_len, int32_t elem_bytes, void* dst,

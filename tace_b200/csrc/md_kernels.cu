@@ -6,6 +6,7 @@
 // The reference has no integrator of its own: its MD runs go through LAMMPS (`fix nve`) or ASE; these
 // entry points stand in for that host so a whole MD step stays on the device.
 #include <cuda_runtime.h>
+#include <cub/cub.cuh>
 #include <cstdint>
 #include <type_traits>
 
@@ -187,6 +188,73 @@ extern "C" int tace_edges_within(const double* positions, const int64_t* edge_in
   if (n_edges == 0) return TACE_OK;
   edges_within_kernel<<<(unsigned)((n_edges + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       positions, reinterpret_cast<const long long*>(edge_index), n_edges, cutoff, keep);
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+namespace tace {
+// (a named namespace: the type is a template argument of a CUB kernel)
+struct KeepToInt {
+  __host__ __device__ int operator()(unsigned char k) const { return k ? 1 : 0; }
+};
+using KeepIterator = cub::TransformInputIterator<int, KeepToInt, const unsigned char*>;
+namespace {
+__global__ void edges_total_kernel(const unsigned char* __restrict__ keep, const int* __restrict__ position, long long n_edges,
+                                   long long* total) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *total = (long long)position[n_edges - 1] + (keep[n_edges - 1] ? 1 : 0);
+}
+// the kept edges of a list, in list order, with their vectors r_target - r_source (fp64 difference, rounded once)
+template <typename T>
+__global__ void edges_compact_kernel(const double* __restrict__ pos, const long long* __restrict__ edge_index, long long n_edges,
+                                     const unsigned char* __restrict__ keep, const int* __restrict__ position, long long n_kept,
+                                     long long* __restrict__ out_index, T* __restrict__ out_vec) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= n_edges || !keep[e]) return;
+  const long long k = position[e];
+  if (k >= n_kept) return;
+  const long long s = edge_index[e], t = edge_index[n_edges + e];
+  out_index[k] = s;
+  out_index[n_kept + k] = t;
+#pragma unroll
+  for (int d = 0; d < 3; ++d) out_vec[3 * k + d] = (T)(pos[3 * t + d] - pos[3 * s + d]);
+}
+}  // namespace
+}  // namespace tace
+
+extern "C" int tace_edges_scan_workspace_bytes(int64_t n_edges, size_t* bytes) {
+  if (!bytes || n_edges < 0 || n_edges >= (1LL << 31)) return TACE_ERR_INVALID_ARGUMENT;
+  size_t temp = 0;
+  KeepIterator in(nullptr, tace::KeepToInt());
+  if (cub::DeviceScan::ExclusiveSum(nullptr, temp, in, static_cast<int*>(nullptr), (int)n_edges) != cudaSuccess) return TACE_ERR_CUDA;
+  *bytes = temp + 256;
+  return TACE_OK;
+}
+
+extern "C" int tace_edges_scan(const uint8_t* keep, int64_t n_edges, int32_t* position, int64_t* total, void* workspace,
+                               size_t workspace_bytes, tace_stream_t stream) {
+  if (n_edges < 0 || n_edges >= (1LL << 31) || !total || (n_edges > 0 && (!keep || !position || !workspace))) return TACE_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_edges == 0) return cudaMemsetAsync(total, 0, sizeof(int64_t), s) == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+  size_t need = 0;
+  KeepIterator in(keep, tace::KeepToInt());
+  if (cub::DeviceScan::ExclusiveSum(nullptr, need, in, position, (int)n_edges, s) != cudaSuccess) return TACE_ERR_CUDA;
+  if (need > workspace_bytes) return TACE_ERR_CAPACITY;
+  if (cub::DeviceScan::ExclusiveSum(workspace, need, in, position, (int)n_edges, s) != cudaSuccess) return TACE_ERR_CUDA;
+  edges_total_kernel<<<1, 32, 0, s>>>(keep, position, n_edges, reinterpret_cast<long long*>(total));
+  return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
+}
+
+extern "C" int tace_edges_compact(const double* positions, const int64_t* edge_index, int64_t n_edges, const uint8_t* keep,
+                                  const int32_t* position, int64_t n_kept, int64_t* out_index, void* out_vec, int32_t dtype,
+                                  tace_stream_t stream) {
+  if (n_edges < 0 || n_kept < 0 || n_kept > n_edges || (dtype != TACE_F32 && dtype != TACE_F64)) return TACE_ERR_INVALID_ARGUMENT;
+  if (n_kept == 0) return TACE_OK;
+  if (!positions || !edge_index || !keep || !position || !out_index || !out_vec) return TACE_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)((n_edges + 255) / 256);
+  const long long* ei = reinterpret_cast<const long long*>(edge_index);
+  long long* oi = reinterpret_cast<long long*>(out_index);
+  if (dtype == TACE_F32) edges_compact_kernel<float><<<blocks, 256, 0, s>>>(positions, ei, n_edges, keep, position, n_kept, oi, static_cast<float*>(out_vec));
+  else edges_compact_kernel<double><<<blocks, 256, 0, s>>>(positions, ei, n_edges, keep, position, n_kept, oi, static_cast<double*>(out_vec));
   return cudaGetLastError() == cudaSuccess ? TACE_OK : TACE_ERR_CUDA;
 }
 

@@ -20,7 +20,7 @@ EXPORTS = [
     "tace_workspace_bytes", "tace_forward", "tace_debug_read", "tace_nl_count", "tace_nl_fill", "tace_nl_workspace_bytes",
     "tace_launch_count", "tace_profile_enable", "tace_profile_count", "tace_profile_read", "tace_tc_gemm_f32", "tace_tc_gemm_set_test_mode",
     "tace_device_error", "tace_set_exchange", "tace_nl_build_noalloc", "tace_md_kick_drift", "tace_md_kinetic_energy",
-    "tace_edge_vectors", "tace_edges_within", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays", "tace_set_exchange_sync", "tace_set_exchange_stream",
+    "tace_edge_vectors", "tace_edges_within", "tace_edges_scan_workspace_bytes", "tace_edges_scan", "tace_edges_compact", "tace_rows_gather", "tace_rows_scatter_add", "tace_set_graph_mode", "tace_graph_replays", "tace_set_exchange_sync", "tace_set_exchange_stream",
     "tace_set_chunk_edges", "tace_md_langevin",
 ]
 
@@ -115,6 +115,9 @@ def load() -> ctypes.CDLL:
     lib.tace_md_kinetic_energy.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.tace_edge_vectors.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_void_p]
     lib.tace_edges_within.argtypes = [c_void_p, c_void_p, c_int64, ctypes.c_double, c_void_p, c_void_p]
+    lib.tace_edges_scan_workspace_bytes.argtypes = [c_int64, POINTER(c_size_t)]
+    lib.tace_edges_scan.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.tace_edges_compact.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_void_p]
     lib.tace_rows_gather.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
     lib.tace_rows_scatter_add.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]
     _lib = lib

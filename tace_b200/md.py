@@ -161,15 +161,26 @@ class DomainMD:
             wide = self._skin_edges
             Ew = int(wide.shape[1])
             keep = torch.empty(Ew, dtype=torch.uint8, device=self.device)
+            position = torch.empty(Ew, dtype=torch.int32, device=self.device)
+            total = torch.empty(1, dtype=torch.int64, device=self.device)
+            nbytes = ctypes.c_size_t()
+            _lib.check(self.lib.tace_edges_scan_workspace_bytes(Ew, ctypes.byref(nbytes)), "tace_edges_scan_workspace_bytes")
+            scratch = torch.empty(int(nbytes.value), dtype=torch.uint8, device=self.device)
             with torch.cuda.device(self.device):
                 _lib.check(self.lib.tace_edges_within(local_pos.data_ptr(), wide.data_ptr(), Ew, self.cutoff, keep.data_ptr(),
                                                       self._stream()), "tace_edges_within")
-            edge_index = wide[:, keep.view(torch.bool)].contiguous()
-        E = int(edge_index.shape[1])
-        vec = torch.empty(E, 3, dtype=self.dtype, device=self.device)
-        with torch.cuda.device(self.device):
-            _lib.check(self.lib.tace_edge_vectors(local_pos.data_ptr(), edge_index.data_ptr(), E, vec.data_ptr(),
-                                                  _lib.dtype_code(self.dtype), self._stream()), "tace_edge_vectors")
+                _lib.check(self.lib.tace_edges_scan(keep.data_ptr(), Ew, position.data_ptr(), total.data_ptr(), scratch.data_ptr(),
+                                                    scratch.numel(), self._stream()), "tace_edges_scan")
+            E = int(total.item())  # the one host read of the step: sizes of the edge arrays
+            edge_index = torch.empty(2, E, dtype=torch.int64, device=self.device)
+            vec = torch.empty(E, 3, dtype=self.dtype, device=self.device)
+            with torch.cuda.device(self.device):
+                _lib.check(self.lib.tace_edges_compact(local_pos.data_ptr(), wide.data_ptr(), Ew, keep.data_ptr(), position.data_ptr(), E,
+                                                       edge_index.data_ptr(), vec.data_ptr(), _lib.dtype_code(self.dtype), self._stream()),
+                           "tace_edges_compact")
+        if n == 0:
+            E = 0
+            vec = torch.empty(0, 3, dtype=self.dtype, device=self.device)
         t2 = time.perf_counter()
         out = self.model({"species": self.local_species, "edge_index": edge_index, "edge_vector": vec, "natoms": (n, g),
                           "lmp_data": dom.exchange})

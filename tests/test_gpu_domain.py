@@ -136,6 +136,43 @@ def test_md_support_kernels_match_torch():
             assert torch.equal(acc, ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_filtered_edge_list_matches_a_boolean_mask(dtype):
+    """tace_edges_within + tace_edges_scan + tace_edges_compact against torch: the kept edges in list order and their
+    vectors (the fp64 difference rounded once), bit for bit."""
+    import ctypes
+
+    lib = _lib.load()
+    g = torch.Generator(device="cpu").manual_seed(5)
+    n, E = 500, 20000
+    pos = (torch.rand(n, 3, generator=g, dtype=torch.float64) * 12.0).to(DEV)
+    ei = torch.randint(0, n, (2, E), generator=g, dtype=torch.int64).to(DEV)
+    cutoff = 5.0
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    keep = torch.empty(E, dtype=torch.uint8, device=DEV)
+    position = torch.empty(E, dtype=torch.int32, device=DEV)
+    total = torch.empty(1, dtype=torch.int64, device=DEV)
+    nbytes = ctypes.c_size_t()
+    _lib.check(lib.tace_edges_scan_workspace_bytes(E, ctypes.byref(nbytes)), "ws")
+    scratch = torch.empty(int(nbytes.value), dtype=torch.uint8, device=DEV)
+    _lib.check(lib.tace_edges_within(pos.data_ptr(), ei.data_ptr(), E, cutoff, keep.data_ptr(), stream), "within")
+    _lib.check(lib.tace_edges_scan(keep.data_ptr(), E, position.data_ptr(), total.data_ptr(), scratch.data_ptr(), scratch.numel(), stream),
+               "scan")
+    n_kept = int(total.item())
+    mask = keep.view(torch.bool)
+    assert 0 < n_kept < E and n_kept == int(mask.sum())
+    out_index = torch.empty(2, n_kept, dtype=torch.int64, device=DEV)
+    out_vec = torch.empty(n_kept, 3, dtype=dtype, device=DEV)
+    _lib.check(lib.tace_edges_compact(pos.data_ptr(), ei.data_ptr(), E, keep.data_ptr(), position.data_ptr(), n_kept,
+                                      out_index.data_ptr(), out_vec.data_ptr(), _lib.dtype_code(dtype), stream), "compact")
+    ref_index = ei[:, mask]
+    assert torch.equal(out_index, ref_index)
+    assert torch.equal(out_vec, (pos[ref_index[1]] - pos[ref_index[0]]).to(dtype))
+    # an empty list is legal
+    _lib.check(lib.tace_edges_scan(None, 0, None, total.data_ptr(), None, 0, stream), "scan of nothing")
+    assert int(total.item()) == 0
+
+
 def test_nve_conserves_energy_and_momentum():
     s = _system(seed=9)
     model, _, _ = make_models(2, 32, [13, 29], 4.0, 20.0, torch.float64, targets=("energy", "forces"))
