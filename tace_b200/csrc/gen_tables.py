@@ -137,7 +137,7 @@ def gen_interaction(L, Lin, out):
     Ks = [w3j(*p) * math.sqrt(2 * p[2] + 1) for p in paths]
     nnz_l3 = {l: sum(int(np.count_nonzero(K)) for K, p in zip(Ks, paths) if p[2] == l) for l in outs}
     # output-rank groups: one group for small cases, otherwise split at the rank that balances the work
-    if scalar_src or L < 2:
+    if scalar_src or L < 3:  # up to rank 2 one thread holds every message component of a channel (35 accumulators)
         groups = [outs]
     else:
         best = min(range(1, L + 1), key=lambda c: abs(sum(nnz_l3[l] for l in outs[:c]) - sum(nnz_l3[l] for l in outs[c:])))
