@@ -87,67 +87,87 @@ cudaError_t launch_species_gather(const T* table, const int* species, T* out, in
 // scalars | all D components], every rank scaled by its gate.  m0 == 0 (gate_m0 = False, the e3nn Gate,
 // nonlinear.py:43-70): [scalars | L gate scalars | components of ranks >= 1 | unused]; the scalars go through the
 // normalised SiLU, rank l >= 1 is scaled by gate l.
-template <typename T>
-__global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int n, int L, int C, int m0) {
+// L is a template parameter so that the loops over ranks and components unroll and every load of a thread is in flight
+// before its first store.
+template <typename T, int L>
+__global__ void gate_fwd_kernel(const T* __restrict__ Gt, T* __restrict__ a, int n, int C, int m0) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)n * C) return;
   const int i = idx / C, c = idx - (long long)i * C;
-  const int D = (L + 1) * (L + 1);
+  constexpr int D = (L + 1) * (L + 1);
   const T* row = Gt + (long long)i * (L + 1 + D) * C;
   T* out = a + (long long)i * D * C;
+  T gs[L + 1], v[D];
   if (!m0) {
-    out[c] = T(kSiluCst) * silu_(row[c]);
+#pragma unroll
+    for (int l = 0; l <= L; ++l) gs[l] = row[l * C + c];
+#pragma unroll
+    for (int k = 1; k < D; ++k) v[k] = row[(L + k) * C + c];
+    out[c] = T(kSiluCst) * silu_(gs[0]);
+#pragma unroll
     for (int l = 1; l <= L; ++l) {
-      const T gate = T(kSigmoidCst) * sigmoid_(row[l * C + c]);
-      for (int m = 0; m < 2 * l + 1; ++m) {
-        const int k = l * l + m;
-        out[k * C + c] = row[(L + k) * C + c] * gate;
-      }
+      const T gate = T(kSigmoidCst) * sigmoid_(gs[l]);
+#pragma unroll
+      for (int m = 0; m < 2 * l + 1; ++m) out[(l * l + m) * C + c] = v[l * l + m] * gate;
     }
     return;
   }
+#pragma unroll
+  for (int l = 0; l <= L; ++l) gs[l] = row[l * C + c];
+#pragma unroll
+  for (int k = 0; k < D; ++k) v[k] = row[(L + 1 + k) * C + c];
+#pragma unroll
   for (int l = 0; l <= L; ++l) {
-    const T gate = T(kSigmoidCst) * sigmoid_(row[l * C + c]);
-    for (int m = 0; m < 2 * l + 1; ++m) {
-      const int k = l * l + m;
-      out[k * C + c] = row[(L + 1 + k) * C + c] * gate;
-    }
+    const T gate = T(kSigmoidCst) * sigmoid_(gs[l]);
+#pragma unroll
+    for (int m = 0; m < 2 * l + 1; ++m) out[(l * l + m) * C + c] = v[l * l + m] * gate;
   }
 }
-template <typename T>
-__global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ ga, T* __restrict__ gGt, int n, int L, int C, int m0) {
+template <typename T, int L>
+__global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ ga, T* __restrict__ gGt, int n, int C, int m0) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)n * C) return;
   const int i = idx / C, c = idx - (long long)i * C;
-  const int D = (L + 1) * (L + 1);
+  constexpr int D = (L + 1) * (L + 1);
   const T* row = Gt + (long long)i * (L + 1 + D) * C;
   const T* g = ga + (long long)i * D * C;
   T* out = gGt + (long long)i * (L + 1 + D) * C;
+  T gs[L + 1], v[D], gk[D];
+#pragma unroll
+  for (int l = 0; l <= L; ++l) gs[l] = row[l * C + c];
+#pragma unroll
+  for (int k = 0; k < D; ++k) gk[k] = g[k * C + c];
   if (!m0) {
-    out[c] = g[c] * T(kSiluCst) * silu_grad_(row[c]);
+#pragma unroll
+    for (int k = 1; k < D; ++k) v[k] = row[(L + k) * C + c];
+    out[c] = gk[0] * T(kSiluCst) * silu_grad_(gs[0]);
+#pragma unroll
     for (int l = 1; l <= L; ++l) {
-      const T sg = sigmoid_(row[l * C + c]);
+      const T sg = sigmoid_(gs[l]);
       const T gate = T(kSigmoidCst) * sg;
       T acc = T(0);
+#pragma unroll
       for (int m = 0; m < 2 * l + 1; ++m) {
         const int k = l * l + m;
-        const T gk = g[k * C + c];
-        acc += gk * row[(L + k) * C + c];
-        out[(L + k) * C + c] = gk * gate;
+        acc += gk[k] * v[k];
+        out[(L + k) * C + c] = gk[k] * gate;
       }
       out[l * C + c] = acc * T(kSigmoidCst) * sg * (T(1) - sg);
     }
     return;
   }
+#pragma unroll
+  for (int k = 0; k < D; ++k) v[k] = row[(L + 1 + k) * C + c];
+#pragma unroll
   for (int l = 0; l <= L; ++l) {
-    const T sg = sigmoid_(row[l * C + c]);
+    const T sg = sigmoid_(gs[l]);
     const T gate = T(kSigmoidCst) * sg;
     T acc = T(0);
+#pragma unroll
     for (int m = 0; m < 2 * l + 1; ++m) {
       const int k = l * l + m;
-      const T gk = g[k * C + c];
-      acc += gk * row[(L + 1 + k) * C + c];
-      out[(L + 1 + k) * C + c] = gk * gate;
+      acc += gk[k] * v[k];
+      out[(L + 1 + k) * C + c] = gk[k] * gate;
     }
     out[l * C + c] = acc * T(kSigmoidCst) * sg * (T(1) - sg);
   }
@@ -155,13 +175,21 @@ __global__ void gate_bwd_kernel(const T* __restrict__ Gt, const T* __restrict__ 
 template <typename T>
 cudaError_t launch_gate_fwd(const T* Gt, T* a, int n, int L, int C, int m0, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  gate_fwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, a, n, L, C, m0);
+  const unsigned blocks = (unsigned)(((long long)n * C + 127) / 128);
+  if (L == 1) gate_fwd_kernel<T, 1><<<blocks, 128, 0, s>>>(Gt, a, n, C, m0);
+  else if (L == 2) gate_fwd_kernel<T, 2><<<blocks, 128, 0, s>>>(Gt, a, n, C, m0);
+  else if (L == 3) gate_fwd_kernel<T, 3><<<blocks, 128, 0, s>>>(Gt, a, n, C, m0);
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 template <typename T>
 cudaError_t launch_gate_bwd(const T* Gt, const T* ga, T* gGt, int n, int L, int C, int m0, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  gate_bwd_kernel<T><<<(unsigned)(((long long)n * C + 127) / 128), 128, 0, s>>>(Gt, ga, gGt, n, L, C, m0);
+  const unsigned blocks = (unsigned)(((long long)n * C + 127) / 128);
+  if (L == 1) gate_bwd_kernel<T, 1><<<blocks, 128, 0, s>>>(Gt, ga, gGt, n, C, m0);
+  else if (L == 2) gate_bwd_kernel<T, 2><<<blocks, 128, 0, s>>>(Gt, ga, gGt, n, C, m0);
+  else if (L == 3) gate_bwd_kernel<T, 3><<<blocks, 128, 0, s>>>(Gt, ga, gGt, n, C, m0);
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 
