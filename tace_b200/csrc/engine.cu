@@ -627,6 +627,7 @@ struct Model : ModelBase {
     int *chunk_atom_ptr, *chunk_edge_ptr, *keys_cs, *perm_cs;  // edge chunks; (chunk, source)-sorted edge list
     int n_chunks; long long chunk_rows;                        // rows held by the per-edge chunk buffers
     void* prep_temp; size_t prep_temp_bytes;
+    T *energy_partial;  // slice sums of the per-graph energies (graph_energy_slices)
     T *vec, *Y, *dY, *g, *e_scaled, *atom_virial, *dxe, *dlen, *ddlen, *ro_factor, *env, *denv, *zbl_node;
     T *tWg, *tgWg, *tgvec;  // TECE: Wigner rows of every edge (shared by the layers), their gradient, dE/d(edge vector) through them
     std::vector<LayerBufs> lay;
@@ -641,6 +642,7 @@ struct Model : ModelBase {
     b.prep_temp_bytes = graph_prep_temp_bytes(E, (int)N);
     b.prep_temp = ar.take<unsigned char>(b.prep_temp_bytes);
     b.vec = ar.take<T>(3 * E); b.Y = ar.take<T>((size_t)D * E); b.dY = ar.take<T>((size_t)D * E); b.g = ar.take<T>(3 * E);
+    b.energy_partial = ar.take<T>((size_t)B * graph_energy_slices(NL, B));
     b.e_scaled = ar.take<T>(NL); b.atom_virial = ar.take<T>(9 * NL); b.ro_factor = ar.take<T>(NL); b.zbl_node = zbl ? ar.take<T>(NL) : nullptr;
     b.tWg = b.tgWg = b.tgvec = nullptr;
     if (tece_mask) { b.tWg = ar.take<T>((size_t)E * t_NR * D); b.tgWg = ar.take<T>((size_t)E * t_NR * D); b.tgvec = ar.take<T>(3 * (size_t)E); }
@@ -1396,8 +1398,11 @@ struct Model : ModelBase {
       ra.factor = b.ro_factor;
     }
     CKL(launch_readout(ra, s));
-    if (o->energy)
-      CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, bt->fidelity, n_el, static_cast<T*>(o->energy), B, s));
+    if (o->energy) {
+      CKL(launch_graph_energy(b.e_scaled, w("e0"), bt->species, bt->graph_ptr, bt->fidelity, n_el, static_cast<T*>(o->energy), B, NL,
+                              b.energy_partial, s));
+      if (graph_energy_slices(NL, B) > 1) ++launches;  // the slice sums are added by a second kernel
+    }
     if (!need_grad) { PH("end"); return TACE_OK; }
 
     // ---- layers, backward

@@ -151,8 +151,16 @@ template <typename T> cudaError_t launch_zbl_fwd(const ZblArgs<T>& a, cudaStream
 template <typename T> cudaError_t launch_zbl_bwd(const ZblArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);
 // energy[g] = sum_{i in g} (e0[species_i] + e_scaled[i])
+// slices per graph of the per-graph energy sum: 1 for batches of small graphs, up to 64 when graphs average more than 8 192
+// atoms; `partial` holds n_graphs * slices values (needed when slices > 1)
+inline int graph_energy_slices(long long n_atoms, int n_graphs) {
+  if (n_graphs <= 0) return 1;
+  const long long per = n_atoms / n_graphs / 8192;
+  return per < 1 ? 1 : (per > 64 ? 64 : (int)per);
+}
 template <typename T> cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr,
-                                                     const int* fidelity, int n_el, T* energy, int n_graphs, cudaStream_t s);
+                                                      const int* fidelity, int n_el, T* energy, int n_graphs, long long n_atoms,
+                                                      T* partial, cudaStream_t s);
 template <typename T> cudaError_t launch_fill_zero(T* p, long long n, cudaStream_t s);
 // dst[i] = src[perm[i]] (gather) / dst[perm[i]] = src[i] (scatter), rows of row_len elements
 template <typename T> cudaError_t launch_gather_rows(const T* src, const int* perm, T* dst, long long n, int row_len, cudaStream_t s);

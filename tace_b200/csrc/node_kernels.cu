@@ -572,27 +572,47 @@ cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+// Energy of every graph: E0 + scaled read-out summed over its atoms.  Graph g is cut into `slices` equal ranges of atoms;
+// block (g, j) sums range j in a fixed order (strided partial sums, then a tree), and with more than one slice a second
+// launch adds the slice sums in order.  A batch of many small graphs uses one slice; one large system (an MD block) many.
 template <typename T>
 __global__ void graph_energy_kernel(const T* __restrict__ e_scaled, const T* __restrict__ e0, const int* __restrict__ species,
-                                    const int* __restrict__ graph_ptr, const int* __restrict__ fidelity, int n_el, T* energy) {
+                                    const int* __restrict__ graph_ptr, const int* __restrict__ fidelity, int n_el, int slices,
+                                    T* __restrict__ out) {
   __shared__ T red[256];
-  const int g = blockIdx.x;
+  const int g = blockIdx.x, j = blockIdx.y;
   const T* e0f = e0 + (fidelity ? fidelity[g] : 0) * n_el;
+  const long long beg = graph_ptr[g], len = graph_ptr[g + 1] - beg;
+  const long long lo = beg + len * j / slices, hi = beg + len * (j + 1) / slices;
   T acc = T(0);
-  for (int i = graph_ptr[g] + threadIdx.x; i < graph_ptr[g + 1]; i += blockDim.x) acc += e0f[species[i]] + e_scaled[i];
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) acc += e0f[species[i]] + e_scaled[i];
   red[threadIdx.x] = acc;
   __syncthreads();
   for (int off = 128; off > 0; off >>= 1) {
     if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
     __syncthreads();
   }
-  if (threadIdx.x == 0) energy[g] = red[0];
+  if (threadIdx.x == 0) out[(long long)g * slices + j] = red[0];
+}
+template <typename T>
+__global__ void graph_energy_finish_kernel(const T* __restrict__ partial, int slices, T* __restrict__ energy, int n_graphs) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_graphs) return;
+  T acc = T(0);
+  for (int j = 0; j < slices; ++j) acc += partial[(long long)g * slices + j];
+  energy[g] = acc;
 }
 template <typename T>
 cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* species, const int* graph_ptr, const int* fidelity,
-                                int n_el, T* energy, int n_graphs, cudaStream_t s) {
+                                int n_el, T* energy, int n_graphs, long long n_atoms, T* partial, cudaStream_t s) {
   if (n_graphs <= 0) return cudaSuccess;
-  graph_energy_kernel<T><<<n_graphs, 256, 0, s>>>(e_scaled, e0, species, graph_ptr, fidelity, n_el, energy);
+  const int slices = graph_energy_slices(n_atoms, n_graphs);
+  if (slices == 1 || !partial) {
+    graph_energy_kernel<T><<<dim3(n_graphs, 1), 256, 0, s>>>(e_scaled, e0, species, graph_ptr, fidelity, n_el, 1, energy);
+    return cudaGetLastError();
+  }
+  graph_energy_kernel<T><<<dim3(n_graphs, slices), 256, 0, s>>>(e_scaled, e0, species, graph_ptr, fidelity, n_el, slices, partial);
+  graph_energy_finish_kernel<T><<<(n_graphs + 127) / 128, 128, 0, s>>>(partial, slices, energy, n_graphs);
   return cudaGetLastError();
 }
 
@@ -615,7 +635,7 @@ cudaError_t launch_graph_energy(const T* e_scaled, const T* e0, const int* speci
   template cudaError_t launch_add_rows<T>(T*, long long, const T*, long long, long long, int, cudaStream_t);  \
   template cudaError_t launch_scale_rows<T>(T*, const T*, long long, int, long long, cudaStream_t);           \
   template cudaError_t launch_density_node_bwd<T>(T*, const T*, const T*, T*, long long, int, long long, cudaStream_t); \
-  template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, const int*, int, T*, int, cudaStream_t);
+  template cudaError_t launch_graph_energy<T>(const T*, const T*, const int*, const int*, const int*, int, T*, int, long long, T*, cudaStream_t);
 INST(float)
 INST(double)
 template cudaError_t launch_fill_zero<int>(int*, long long, cudaStream_t);
