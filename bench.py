@@ -247,7 +247,7 @@ def run_reference(args, rank, world):
 def md_measure(workload, wl, dtype, rank, world, device, steps, warmup):
     """Molecular-dynamics workloads: ONE periodic Cu/Al system, velocity Verlet, dt = 1 fs,
     Maxwell-Boltzmann start at 300 K.  A step = half kick + drift, ghost positions, neighbour list (reused while no
-    atom has moved more than half the skin), energy and forces with halo exchanges between layers, ghost forces
+    atom has moved more than half the 1.0 A skin), energy and forces with halo exchanges between layers, ghost forces
     returned, half kick.  With N GPUs the box is cut into N blocks (strong scaling: the system is the same at every
     N).  Collective: every rank calls it; rank 0 gets the result dictionary, the others None."""
     from tace_b200 import synth
@@ -258,7 +258,7 @@ def md_measure(workload, wl, dtype, rank, world, device, steps, warmup):
     vel = maxwell_boltzmann(masses, 300.0, seed=5)
     n_atoms = len(masses)
     t_setup = time.perf_counter()
-    md = DomainMD(model.to(device), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, masses=masses, dt=1.0, skin=0.5,
+    md = DomainMD(model.to(device), s["cell"], s["positions"], s["atomic_numbers"], velocities=vel, masses=masses, dt=1.0, skin=1.0,
                   rank=rank, world_size=world, device=device)
     torch.cuda.synchronize()
     t_setup = time.perf_counter() - t_setup
