@@ -8,14 +8,16 @@
 // Plain TF32 (10-bit mantissa) is too coarse for the 1e-5 eV/atom parity target, so every
 // operand is split into a TF32-exact high part and a residual, x = hi + lo, and the product is
 // accumulated as hi*hi + hi*lo + lo*hi in the FP32 TMEM accumulator (the dropped lo*lo term is
-// ~2^-22 relative).  The weight operand B is split once on the host; the activation operand A
-// is split in shared memory right after its TMA load, element-wise and in place, which keeps
-// the 128-byte-swizzled layout the TMA engine wrote.
+// ~2^-22 relative).  The weight operand B is split once on the host.  The activation operand A is split by the kernel
+// right after its TMA load: one thread per row reads the row's 128 bytes (in the swizzled order the TMA engine wrote)
+// and stores the high parts and the residuals to tensor memory, from where the tensor core takes its A operand
+// (`tcgen05.mma` with A in TMEM, B from shared memory); a variant that keeps A in shared memory (split in place, residual
+// in a second tile) remains selectable.
 //
 // One persistent CTA per SM walks its share of 128 x BN output tiles with specialised warps: a TMA
-// producer fills a 3- or 4-stage ring of {A, A_lo, B_hi, B_lo} per 32-wide K step, four warps split A,
-// one thread issues the tcgen05.mma instructions into one of two TMEM accumulators, and four
-// epilogue warps drain the other accumulator (tcgen05.ld of their 32 lanes, 128-bit stores), so
+// producer fills a ring of {A, B_hi, B_lo} per 32-wide K step (four stages at BN = 128, six at BN = 64; three / four
+// with A_lo in shared memory), four warps split A, one thread issues the tcgen05.mma instructions into one of two TMEM
+// accumulators, and four epilogue warps drain the other accumulator (tcgen05.ld of their 32 lanes, 128-bit stores), so
 // loads, splitting, tensor-core work and stores overlap.  The tensor core adds into its accumulator with truncation, an error that
 // grows linearly with the number of accumulated instructions; long K loops are therefore cut
 // into chunks of kChunk steps whose partial sums are drained from TMEM and added in FP32
@@ -25,6 +27,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstring>
+#include <cstdlib>
 
 #include "../../include/tace_b200.h"
 #include "kernels.h"
@@ -87,6 +90,23 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -132,14 +152,22 @@ struct TcBatch {
 
 // Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-3 = operand
 // splitters, warps 4-7 = epilogue (warp w owns the TMEM lanes 32 * (w % 4) .. + 31).
-constexpr int kThreads = 256;
-constexpr int kSplitThreads = 64;
+constexpr int kSplitThreads = 64;  // without TS: warps 2 and 3
 
-template <int BN>
+// TS: the activation operand of the tensor-core instructions lives in tensor memory.  The splitters read the tile the TMA
+// unit wrote and store its high part and residual to TMEM (one thread per row = TMEM lane), so a stage needs no room for
+// them in shared memory: 48 KB instead of 64 KB at BN = 128, i.e. four K-steps in flight instead of three (six instead
+// of four at BN = 64), and the tensor core reads only the weight operand from shared memory.  The ring's round trip, not any
+// unit, is what bounds this kernel, so the number of stages in flight is its throughput.
+template <int BN, bool TS>
 struct TcSmem {
-  static constexpr int kStages = BN == 128 ? 3 : 4;
+  static constexpr int kStages = TS ? (BN == 128 ? 4 : 6) : (BN == 128 ? 3 : 4);
   static constexpr int kTileBBytes = BN * kBK * 4;
-  static constexpr int kStageBytes = 2 * kTileABytes + 2 * kTileBBytes;
+  static constexpr int kStageBytes = (TS ? 1 : 2) * kTileABytes + 2 * kTileBBytes;
+  static constexpr int kThreads = TS ? 320 : 256;        // TS: four splitter warps (2, 3, 8, 9), one per TMEM lane quarter
+  static constexpr int kSplit = TS ? 128 : 64;           // splitter threads = arrivals on a `ready` barrier
+  static constexpr int kTmemCols = TS ? 512 : 2 * BN;    // accumulators [0, 2 BN) | TS: per stage 32 columns high part, 32 residual
+  static constexpr int kTmemA = 2 * BN;                  // first activation column (TS)
   static constexpr int kBarrierBytes = 256;
   // result staging for TMA stores: per epilogue warp two slabs of 32 rows x 32 columns (128-byte swizzled rows)
   static constexpr int kStoreBytes = 4 * 2 * 32 * 128;
@@ -204,9 +232,9 @@ __device__ __forceinline__ TileInfo decode_tile(const TcBatch& b, const int* til
 
 // ONE_CHUNK: every K loop of the launch fits one TMEM accumulation chunk, so the epilogue stores
 // straight from the drained registers and needs no running sums.
-template <int BN, bool ONE_CHUNK>
-__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_constant__ TcBatch batch) {
-  using S = TcSmem<BN>;
+template <int BN, bool ONE_CHUNK, bool TS>
+__global__ void __launch_bounds__(TcSmem<BN, TS>::kThreads, 1) tc_gemm_kernel(const __grid_constant__ TcBatch batch) {
+  using S = TcSmem<BN, TS>;
   constexpr int kStages = S::kStages;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -227,8 +255,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   int* tile_start = reinterpret_cast<int*>(misc + 16);  // [n_problems + 1]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), kSplitThreads); mbar_init(empty_bar(s), 1); }
+  if (tid == 0) {  // `ready` takes one arrival per splitter warp
+    for (int s = 0; s < kStages; ++s) { mbar_init(raw_bar(s), 1); mbar_init(ready_bar(s), S::kSplit / 32); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -243,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // two accumulators of BN fp32 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(S::kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -255,9 +283,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   auto stage_a = [&](int s) { return base + s * S::kStageBytes; };
-  auto stage_alo = [&](int s) { return base + s * S::kStageBytes + kTileABytes; };
-  auto stage_bhi = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes; };
-  auto stage_blo = [&](int s) { return base + s * S::kStageBytes + 2 * kTileABytes + S::kTileBBytes; };
+  constexpr int kBOff = (TS ? 1 : 2) * kTileABytes;  // weights follow the activation tile (and, without TS, its residual)
+  auto stage_alo = [&](int s) { return base + s * S::kStageBytes + kTileABytes; };  // not TS
+  auto stage_bhi = [&](int s) { return base + s * S::kStageBytes + kBOff; };
+  auto stage_blo = [&](int s) { return base + s * S::kStageBytes + kBOff + S::kTileBBytes; };
 
   if (warp == 0) {
     // ---- TMA producer
@@ -316,10 +345,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
 #pragma unroll
           for (int k8 = 0; k8 < kBK / 8; ++k8) {
             const uint64_t off = stage_off + (uint64_t)(k8 * 2);  // 8 fp32 = 32 bytes along K inside the swizzled row
-            const uint64_t da = dA0 + off, dal = dAl0 + off, db = dB0 + off, dbl = dBl0 + off;
-            umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
-            umma_tf32(d, da, dbl, idesc, 1u);
-            umma_tf32(d, dal, db, idesc, 1u);
+            const uint64_t db = dB0 + off, dbl = dBl0 + off;
+            if constexpr (TS) {  // activations: 8 TMEM columns per slice, high part at +0, residual at +32 of the stage
+              const uint32_t ta = tmem_base + (uint32_t)(S::kTmemA + s * 64 + k8 * 8);
+              umma_tf32_ts(d, ta, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
+              umma_tf32_ts(d, ta, dbl, idesc, 1u);
+              umma_tf32_ts(d, ta + 32, db, idesc, 1u);
+            } else {
+              const uint64_t da = dA0 + off, dal = dAl0 + off;
+              umma_tf32(d, da, db, idesc, (!chunk_begin || k8 > 0) ? 1u : 0u);
+              umma_tf32(d, da, dbl, idesc, 1u);
+              umma_tf32(d, dal, db, idesc, 1u);
+            }
           }
           umma_commit(empty_bar(s));  // ring slot reusable once these MMAs have read it
           if (chunk_end) { umma_commit(acc_full(a)); ++chunk; }  // partial sum of this chunk complete
@@ -331,8 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           if (mbar_try_wait(drain_bar, 0)) break;
       }
     }
-  } else if (warp < 4) {
-    // ---- operand splitters: A = hi + lo with hi exact in TF32, element-wise and in place
+  } else if (warp < 4 || (TS && warp >= 8)) {
+    // ---- operand splitters: A = hi + lo with hi exact in TF32
     const int t64 = tid - 64;
     int step = 0;
     bool ok = true;
@@ -341,6 +378,32 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
       for (int ks = 0; ks < t.num_k; ++ks, ++step) {
         const int s = step % kStages, ph = (step / kStages) & 1;
         if (!mbar_wait(raw_bar(s), ph, abort_flag, batch.error, 3, batch.spin_limit)) { ok = false; break; }
+        if constexpr (TS) {
+          // one thread per row (= TMEM lane): the row's eight 16-byte pieces sit at positions j ^ (row & 7) of its 128 bytes
+          // (the swizzle the TMA unit wrote); high parts go to 32 TMEM columns of the stage, residuals to the next 32
+          const int row = (warp & 3) * 32 + lane;
+          const float4* arow = reinterpret_cast<const float4*>(base_ptr + s * S::kStageBytes + row * 128);
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = arow[j ^ (row & 7)];
+            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t h = __float_as_uint(x[q]) & 0xFFFFE000u;
+              hi[4 * j + q] = h;
+              lo[4 * j + q] = __float_as_uint(x[q] - __uint_as_float(h));
+            }
+          }
+          const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(S::kTmemA + s * 64);
+          tmem_st32(ta, hi);
+          tmem_st32(ta + 32, lo);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ready_bar(s));
+          continue;
+        }
         float4* a = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes);
         float4* alo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + kTileABytes);
         // every load of the tile before its first store: the stores go to the buffer the loads come from, so the compiler
@@ -362,7 +425,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
           alo[idx] = l;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-        mbar_arrive(ready_bar(s));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar(s));
       }
     }
   } else {
@@ -477,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const __grid_const
   if (warp >= 4 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // TMA stores of this warp are complete
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::kTmemCols));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -551,18 +615,25 @@ bool make_map_c(CUtensorMap* map, float* ptr, long long rows, long long N, long 
 // Function attributes and the SM count belong to a device, not to the process: one slot per device ordinal.
 constexpr int kMaxDevices = 64;
 
-template <int BN, bool ONE_CHUNK>
-cudaError_t launch_tc(const TcBatch& b, int dev, int sms, cudaStream_t s) {
+template <int BN, bool ONE_CHUNK, bool TS>
+cudaError_t launch_tc_v(const TcBatch& b, int dev, int sms, cudaStream_t s) {
   static bool configured[kMaxDevices] = {};
+  using S = TcSmem<BN, TS>;
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, ONE_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, ONE_CHUNK, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int tiles = b.tile_start[b.n_problems];  // upper bound for per-species problems
   const int grid = tiles < sms ? tiles : sms;
-  tc_gemm_kernel<BN, ONE_CHUNK><<<grid, kThreads, TcSmem<BN>::kTotal, s>>>(b);
+  tc_gemm_kernel<BN, ONE_CHUNK, TS><<<grid, S::kThreads, S::kTotal, s>>>(b);
   return cudaGetLastError();
+}
+template <int BN, bool ONE_CHUNK>
+cudaError_t launch_tc(const TcBatch& b, int dev, int sms, cudaStream_t s) {
+  // TACE_B200_GEMM_TMEM_OPERAND=0 selects the variant with both operands in shared memory (three / four stages)
+  static const bool ts = [] { const char* e = getenv("TACE_B200_GEMM_TMEM_OPERAND"); return !(e && e[0] == '0'); }();
+  return ts ? launch_tc_v<BN, ONE_CHUNK, true>(b, dev, sms, s) : launch_tc_v<BN, ONE_CHUNK, false>(b, dev, sms, s);
 }
 
 }  // namespace
