@@ -157,6 +157,24 @@ def test_full_size_properties_config2():
     assert (c["forces"] - a["forces"]).abs().max().item() <= 1e-4
 
 
+def test_energy_of_large_graphs_is_the_sum_of_their_node_energies():
+    """Graphs that average more than 16 384 atoms are summed in slices by several thread blocks and a second launch; two such graphs
+    in one batch, each checked against the sum of its own node energies (fp64, a small model)."""
+    from tace_b200.graph import build_batch
+    structs = [synth.fcc_supercell(17, 3.61, 0.05, seed=31, species=(13, 29), fractions=(0.5, 0.5)),
+               synth.fcc_supercell(16, 3.65, 0.05, seed=32, species=(13, 29), fractions=(0.2, 0.8))]
+    model, _, _ = make_models(1, 32, [13, 29], 3.0, 12.0, torch.float64, num_layers=1, targets=("energy",))
+    dev = torch.device("cuda:0")
+    data = build_batch(synth.collate(structs), [13, 29], 3.0, torch.float64, dev)
+    ptr = data["ptr"].tolist()
+    assert (ptr[2] // 2) // 8192 >= 2  # two slices per graph at least
+    out = model(data)
+    assert model.device_error() == 0
+    for g in range(2):
+        total = out["node_energy"][ptr[g]:ptr[g + 1]].sum().item()
+        assert abs(out["energy"][g].item() - total) <= 1e-9 * max(1.0, abs(total))
+
+
 @pytest.mark.parametrize("L,C", [(2, 64), (3, 128)])
 def test_fp32_tensor_core_channel_widths(L, C):
     """Channel counts for which fp32 models run the radial GEMMs and the per-rank linears on tcgen05."""
