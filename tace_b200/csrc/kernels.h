@@ -151,8 +151,8 @@ template <typename T> cudaError_t launch_zbl_fwd(const ZblArgs<T>& a, cudaStream
 template <typename T> cudaError_t launch_zbl_bwd(const ZblArgs<T>& a, cudaStream_t s);
 template <typename T> cudaError_t launch_readout(const ReadoutArgs<T>& a, cudaStream_t s);
 // energy[g] = sum_{i in g} (e0[species_i] + e_scaled[i])
-// slices per graph of the per-graph energy sum: 1 for batches of small graphs, up to 64 when graphs average 16 384 atoms or more (one slice per 8 192)
-// atoms; `partial` holds n_graphs * slices values (needed when slices > 1)
+// slices per graph of the per-graph energy sum: one per 8 192 atoms of the average graph (1 for batches of small graphs,
+// 64 at most); `partial` holds n_graphs * slices values (needed when slices > 1)
 inline int graph_energy_slices(long long n_atoms, int n_graphs) {
   if (n_graphs <= 0) return 1;
   const long long per = n_atoms / n_graphs / 8192;
