@@ -231,15 +231,24 @@ def gen_interaction(L, Lin, out):
         o(f"  template <typename T> static TACE_HD TACE_INLINE void fwd1(const T (&x)[{nx}], const T* __restrict__ G, "
           f"const T (&w)[{grp_np[0]}], T (&acc)[{grp_nm[0]}]) {{ fwd0<T>(x, G, w, acc); }}")
 
-    # backward of one (edge, channel): g is read from gs[k * gstride] (the target's message gradient, channel c)
+    # backward of one (edge, channel): g is read from gs[k * gstride] (the target's message gradient, channel c).  The
+    # path weights come from, and their gradients go to, an accessor: wf.get<p>() is called once when the block of path p
+    # starts (paths in ascending order) and wf.put<p>(dE/dw_p) once when it ends, so a caller may produce a weight just
+    # before it is needed and consume its gradient at once instead of holding all of them in registers.
     o(f"  template <typename T> static TACE_HD TACE_INLINE void bwd(const T (&x)[{nx}], const T* __restrict__ gs, int gstride, "
       f"const T* __restrict__ G, const T (&w)[{P}], T (&dw)[{P}], T (&dY)[{D}], T (&dx)[{nx}]) {{")
+    o(f"    TpArrayWeights<T> wf{{w, dw}};")
+    o(f"    bwd_w<T>(x, gs, gstride, G, wf, dY, dx);")
+    o("  }")
+    o(f"  template <typename T, typename WF> static TACE_HD TACE_INLINE void bwd_w(const T (&x)[{nx}], const T* __restrict__ gs, "
+      f"int gstride, const T* __restrict__ G, WF& wf, T (&dY)[{D}], T (&dx)[{nx}]) {{")
     for p, (l1, l2, l3) in enumerate(paths):
         K = Ks[p]
         n3 = 2 * l3 + 1
         pairs = [(m1, m3) for m3 in range(n3) for m1 in range(2 * l1 + 1) if (p, m1, m3) in gi]
         ids = [gi[(p, m1, m3)] for m1, m3 in pairs]
         o("  {")
+        o(f"    const T w{p} = wf.template get<{p}>();")
         for line in load_G(min(ids), max(ids) + 1, set()):
             o(line)
         for m3 in range(n3):
@@ -252,17 +261,17 @@ def gen_interaction(L, Lin, out):
             if ts:
                 o(f"    const T u{m1} = {' + '.join(ts)};")
                 us.append(m1)
-        o(f"    dw[{p}] = {' + '.join(f'x[{xoff[l1] + m1}] * u{m1}' for m1 in us)};")
+        o(f"    wf.template put<{p}>({' + '.join(f'x[{xoff[l1] + m1}] * u{m1}' for m1 in us)});")
         if not scalar_src:
             for m1 in us:
-                o(f"    dx[{xoff[l1] + m1}] += w[{p}] * u{m1};")
+                o(f"    dx[{xoff[l1] + m1}] += w{p} * u{m1};")
         used = sorted({(m1, m3) for m1, m3 in pairs if any(K[m1, m2, m3] != 0.0 for m2 in range(2 * l2 + 1))})
         for m1, m3 in used:
             o(f"    const T q{m1}_{m3} = x[{xoff[l1] + m1}] * g{m3};")
         for m2 in range(2 * l2 + 1):
             ts = [f"{lit(float(K[m1, m2, m3]))} * q{m1}_{m3}" for m1, m3 in pairs if K[m1, m2, m3] != 0.0]
             if ts:
-                o(f"    dY[{l2 * l2 + m2}] += w[{p}] * ({' + '.join(ts)});")
+                o(f"    dY[{l2 * l2 + m2}] += w{p} * ({' + '.join(ts)});")
         o("  }")
     o("  }")
     o("};")

@@ -39,6 +39,15 @@ template <typename T>
 inline void ld4(const T* p, T& a, T& b, T& c, T& d) { a = p[0]; b = p[1]; c = p[2]; d = p[3]; }
 #endif
 
+// Path weights of a generated backward pass held in arrays: get<p>() reads w[p], put<p>(v) stores dE/dw_p.
+template <typename T>
+struct TpArrayWeights {
+  const T* w;
+  T* dw;
+  template <int P> TACE_HD TACE_INLINE T get() const { return w[P]; }
+  template <int P> TACE_HD TACE_INLINE void put(T v) { dw[P] = v; }
+};
+
 template <typename T>
 TACE_HD TACE_INLINE T sigmoid_(T x) { return T(1) / (T(1) + exp(-x)); }
 template <>

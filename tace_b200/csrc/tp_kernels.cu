@@ -161,6 +161,35 @@ __global__ void __maxnreg__(128) tp_fwd_kernel(const TPArgs<T> a) {
   }
 }
 
+// Path weights of one (edge, channel) in the backward pass, interpolated from the table when their path comes up and
+// forgotten when it is done: get<p>() turns the entry fetched one path ahead into the weight (and keeps dW_p/dd), asks for
+// the entry of path p + 1, and put<p>() folds dE/dW_p into the two per-edge sums that are all the pass keeps of it,
+// dE/d(length) += dE/dW_p dW_p/dd and, with an envelope u on the weights, dE/du += dE/dW_p W_p.  Twenty-three weights
+// and as many gradients never sit in registers together, and every table entry is read once.
+template <typename T, typename TP, bool ENV>
+struct RtBwdWeights {
+  const T* row;       // table entries of this edge's interval, this thread's channel: path p at row + p * stride
+  long long stride;   // 4 * C
+  T b0, b1, b2, b3, d0, d1, d2, d3, u;
+  T v0, m0, v1, m1;   // entry of the next path
+  T w_now, wd_now;    // weight and length derivative of the path in flight
+  T dr, du;
+  __device__ __forceinline__ void start() {
+    dr = T(0); du = T(0);
+    rt_load<T>(row, v0, m0, v1, m1);
+  }
+  template <int P> __device__ __forceinline__ T get() {
+    w_now = b0 * v0 + b1 * m0 + b2 * v1 + b3 * m1;
+    wd_now = d0 * v0 + d1 * m0 + d2 * v1 + d3 * m1;
+    if (P + 1 < TP::NP) rt_load<T>(row + (long long)(P + 1) * stride, v0, m0, v1, m1);
+    return ENV ? w_now * u : w_now;
+  }
+  template <int P> __device__ __forceinline__ void put(T dwv) {
+    if (ENV) { du += dwv * w_now; dr += dwv * u * wd_now; }
+    else dr += dwv * wd_now;
+  }
+};
+
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
 template <typename T, typename TP, bool ENV, bool RT>
 __device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned char* smem_raw, T* red_u, T* red_r, RtEdge<T>* rts,
@@ -185,48 +214,41 @@ __device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned c
     __syncthreads();
     for (int e = 0; e < nb; ++e) {
       const long long s = esrc[e];
-      T xv[TP::NX], wv[TP::NP], dw[TP::NP], dYp[TP::D], dx[TP::NX];
+      T xv[TP::NX], dYp[TP::D], dx[TP::NX];
 #pragma unroll
       for (int k = 0; k < TP::NX; ++k) { xv[k] = a.x[(s * TP::NX + k) * C + c]; dx[k] = T(0); }
-      const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C;
-      const T* rt0 = RT ? a.rtab + ((long long)rts[e].k * TP::NP * C + c) * 4 : nullptr;
-      if constexpr (RT) {
-        const T b0 = rts[e].b[0], b1 = rts[e].b[1], b2 = rts[e].b[2], b3 = rts[e].b[3];
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) {
-          T v0, m0, v1, m1;
-          rt_load<T>(rt0 + (long long)p * C * 4, v0, m0, v1, m1);
-          wv[p] = b0 * v0 + b1 * m0 + b2 * v1 + b3 * m1;
-        }
-      } else {
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
-      }
 #pragma unroll
       for (int k = 0; k < TP::D; ++k) dYp[k] = T(0);
       T u = T(1);
-      if constexpr (ENV) {
-        u = a.env[e0 + e];
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) wv[p] *= u;
-      }
-      TP::template bwd<T>(xv, gMs + c, C, Gs + e * TP::NG, wv, dw, dYp, dx);
-      T du_part = T(0);  // sum_p dw * (unscaled weight) = sum_p dw * wv / u
-      if constexpr (ENV) {
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) { du_part += dw[p] * wv[p]; dw[p] *= u; }
-        du_part = u > T(0) ? du_part / u : T(0);
-      }
-      T dr_part = T(0);  // sum_p dW[p] * dW[p]/dd of this channel
-      if constexpr (RT) {  // the table rows were read a moment ago (L1); reading them again costs fewer registers than keeping them
-        const T d0 = rts[e].d[0], d1 = rts[e].d[1], d2 = rts[e].d[2], d3 = rts[e].d[3];
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) {
-          T v0, m0, v1, m1;
-          rt_load<T>(rt0 + (long long)p * C * 4, v0, m0, v1, m1);
-          dr_part += dw[p] * (d0 * v0 + d1 * m0 + d2 * v1 + d3 * m1);
-        }
+      if constexpr (ENV) u = a.env[e0 + e];
+      T du_part = T(0);  // dE/d(envelope) of this channel: sum_p dE/dW_p W_p
+      T dr_part = T(0);  // dE/d(length) through the tabulated weights: sum_p dE/dW_p dW_p/dd
+      if constexpr (RT) {
+        RtBwdWeights<T, TP, ENV> wf;
+        wf.row = a.rtab + ((long long)rts[e].k * TP::NP * C + c) * 4;
+        wf.stride = (long long)C * 4;
+        wf.b0 = rts[e].b[0]; wf.b1 = rts[e].b[1]; wf.b2 = rts[e].b[2]; wf.b3 = rts[e].b[3];
+        wf.d0 = rts[e].d[0]; wf.d1 = rts[e].d[1]; wf.d2 = rts[e].d[2]; wf.d3 = rts[e].d[3];
+        wf.u = u;
+        wf.start();
+        TP::template bwd_w<T>(xv, gMs + c, C, Gs + e * TP::NG, wf, dYp, dx);
+        dr_part = wf.dr;
+        du_part = wf.du;
       } else {
+        T wv[TP::NP], dw[TP::NP];
+        const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C;
+#pragma unroll
+        for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
+        if constexpr (ENV) {
+#pragma unroll
+          for (int p = 0; p < TP::NP; ++p) wv[p] *= u;
+        }
+        TP::template bwd<T>(xv, gMs + c, C, Gs + e * TP::NG, wv, dw, dYp, dx);
+        if constexpr (ENV) {  // sum_p dw * (unscaled weight) = sum_p dw * wv / u
+#pragma unroll
+          for (int p = 0; p < TP::NP; ++p) { du_part += dw[p] * wv[p]; dw[p] *= u; }
+          du_part = u > T(0) ? du_part / u : T(0);
+        }
 #pragma unroll
         for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
       }
