@@ -190,6 +190,26 @@ struct RtBwdWeights {
   }
 };
 
+// The same for path weights held in memory (W[edge][path][channel]): each weight is loaded one path ahead of its use
+// and its gradient stored as soon as it is known.
+template <typename T, typename TP, bool ENV>
+struct ArrayBwdWeights {
+  const T* W;   // this edge's weights, this thread's channel: path p at W[p * C]
+  T* dW;
+  int C;
+  T u, next, w_now, du;
+  __device__ __forceinline__ void start() { du = T(0); next = W[0]; }
+  template <int P> __device__ __forceinline__ T get() {
+    w_now = next;
+    if (P + 1 < TP::NP) next = W[(P + 1) * C];
+    return ENV ? w_now * u : w_now;
+  }
+  template <int P> __device__ __forceinline__ void put(T dwv) {
+    if (ENV) { du += dwv * w_now; dW[P * C] = dwv * u; }
+    else dW[P * C] = dwv;
+  }
+};
+
 // Dynamic shared memory: [NM][C] message gradient of the target | G rows | dY partial sums.
 template <typename T, typename TP, bool ENV, bool RT>
 __device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned char* smem_raw, T* red_u, T* red_r, RtEdge<T>* rts,
@@ -235,22 +255,15 @@ __device__ __forceinline__ void tp_bwd_row(const TPArgs<T>& a, int i, unsigned c
         dr_part = wf.dr;
         du_part = wf.du;
       } else {
-        T wv[TP::NP], dw[TP::NP];
-        const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C;
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) wv[p] = a.W[wbase + p * C + c];
-        if constexpr (ENV) {
-#pragma unroll
-          for (int p = 0; p < TP::NP; ++p) wv[p] *= u;
-        }
-        TP::template bwd<T>(xv, gMs + c, C, Gs + e * TP::NG, wv, dw, dYp, dx);
-        if constexpr (ENV) {  // sum_p dw * (unscaled weight) = sum_p dw * wv / u
-#pragma unroll
-          for (int p = 0; p < TP::NP; ++p) { du_part += dw[p] * wv[p]; dw[p] *= u; }
-          du_part = u > T(0) ? du_part / u : T(0);
-        }
-#pragma unroll
-        for (int p = 0; p < TP::NP; ++p) a.dW[wbase + p * C + c] = dw[p];
+        ArrayBwdWeights<T, TP, ENV> wf;
+        const long long wbase = (long long)(e0 + e - a.e_base) * TP::NP * C + c;
+        wf.W = a.W + wbase;
+        wf.dW = a.dW + wbase;
+        wf.C = C;
+        wf.u = u;
+        wf.start();
+        TP::template bwd_w<T>(xv, gMs + c, C, Gs + e * TP::NG, wf, dYp, dx);
+        du_part = wf.du;
       }
       if (a.dxe) {
         T* out = a.dxe + (long long)(e0 + e - a.e_base) * TP::NX * C;
