@@ -473,7 +473,8 @@ def gen_product3(L, Lout, out):
     return dict(tag="3:" + tag, P=len(paths), nb=lay3.nm, nnz=nnz)
 
 
-def main():
+def generate():
+    """Text of ``tp_gen.cuh`` and one summary dictionary per generated struct."""
     out = [
         "// GENERATED by tace_b200/csrc/gen_tables.py -- do not edit by hand.",
         "// Path tables and unrolled contraction code for the interaction tensor product and the",
@@ -500,9 +501,14 @@ def main():
         out.append(f"// wigner_3j(1, {l - 1}, {l}), [3][{2 * l - 1}][{2 * l + 1}]")
         out.append(f"TACE_CONST double w3j_1_{l - 1}_{l}[{c.size}] = {{{vals}}};")
     out.append("}  // namespace tace")
+    return "\n".join(out) + "\n", summary
+
+
+def main():
+    text, summary = generate()
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "tp_gen.cuh"), "w") as fh:
-        fh.write("\n".join(out) + "\n")
+        fh.write(text)
     for s in summary:
         print(s)
 

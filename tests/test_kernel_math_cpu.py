@@ -228,3 +228,18 @@ def test_edge_vector_gradient(cpu_harness):
     cpu_harness.h_edge_grad.argtypes = [DP, ctypes.c_double, DP, DP]
     cpu_harness.h_edge_grad(ptr(v.detach().numpy()), float(dd), ptr(dn.numpy()), ptr(g))
     np.testing.assert_allclose(g, g_ref.numpy(), rtol=0, atol=1e-12)
+
+
+def test_generated_header_is_what_its_generator_writes():
+    """``tp_gen.cuh`` is committed so that a build needs no generator run; it must not drift from ``gen_tables.py``."""
+    import importlib.util
+    import os
+
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tace_b200", "csrc")
+    spec = importlib.util.spec_from_file_location("tace_gen_tables", os.path.join(csrc, "gen_tables.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text, summary = gen.generate()
+    with open(os.path.join(csrc, "tp_gen.cuh")) as fh:
+        assert fh.read() == text
+    assert any(s["tag"] == "L3_F" and s["P"] == 23 and s["nm"] == 99 for s in summary)
