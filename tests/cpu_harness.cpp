@@ -32,7 +32,46 @@ using namespace tace;
     return 0;                                                                                     \
   }
 
+// What the kernels' weight accessors rely on: the generated backward code asks for the weight of path p exactly once,
+// hands back its gradient before it asks for the next one, and walks the paths in ascending order.
+struct OrderedWeights {
+  const double* w;
+  double* dw;
+  int next_get = 0, next_put = 0, bad = 0;
+  template <int P> double get() { if (P != next_get || next_put != P) ++bad; ++next_get; return w[P]; }
+  template <int P> void put(double v) { if (P != next_put || next_get != P + 1) ++bad; ++next_put; dw[P] = v; }
+};
+#define TP_ORDER_CASE(TAG)                                                                        \
+  {                                                                                               \
+    using TP = TPX_##TAG;                                                                         \
+    double YY[TP::D], xx[TP::NX], dY[TP::D], dx[TP::NX];                                          \
+    alignas(16) double G[TP::NG];                                                                 \
+    memcpy(YY, Y, sizeof YY); memcpy(xx, x, sizeof xx);                                           \
+    memset(dY, 0, sizeof dY); memset(dx, 0, sizeof dx);                                           \
+    TP::build_G<double>(YY, G);                                                                   \
+    OrderedWeights wf{w, out0};                                                                   \
+    TP::bwd_w<double>(xx, g, 1, G, wf, dY, dx);                                                   \
+    memcpy(out1, dY, sizeof dY); memcpy(out2, dx, sizeof dx);                                     \
+    return wf.bad + (wf.next_get != TP::NP) + (wf.next_put != TP::NP);                            \
+  }
+
 extern "C" {
+
+// The backward pass through an accessor that counts every call out of order (return value; 0 = contract kept):
+// out0 = d/dw, out1 = d/dY, out2 = d/dx as in h_tp mode 1.
+int h_tp_bwd_ordered(int L, int Lin, const double* x, const double* Y, const double* w, const double* g,
+                     double* out0, double* out1, double* out2) {
+  if (L == 1 && Lin < 0) TP_ORDER_CASE(L1_S)
+  if (L == 1 && Lin == 1) TP_ORDER_CASE(L1_F)
+  if (L == 2 && Lin < 0) TP_ORDER_CASE(L2_S)
+  if (L == 2 && Lin == 1) TP_ORDER_CASE(L2_N1)
+  if (L == 2 && Lin == 2) TP_ORDER_CASE(L2_F)
+  if (L == 3 && Lin < 0) TP_ORDER_CASE(L3_S)
+  if (L == 3 && Lin == 1) TP_ORDER_CASE(L3_N1)
+  if (L == 3 && Lin == 2) TP_ORDER_CASE(L3_N2)
+  if (L == 3 && Lin == 3) TP_ORDER_CASE(L3_F)
+  return -1;
+}
 
 // mode 0: forward (out0 = message components); mode 1: out0 = d/dw, out1 = d/dY, out2 = d/dx
 // Lin: rank of the source features, or < 0 for the scalar source of the first layer

@@ -79,6 +79,23 @@ def test_interaction_tp_matches_oracle(cpu_harness, L, Lin):
         np.testing.assert_allclose(dx, dx_ref.numpy(), rtol=0, atol=1e-12)
 
 
+@pytest.mark.parametrize("L,Lin", RANK_PAIRS)
+def test_backward_asks_for_weights_in_path_order(cpu_harness, L, Lin):
+    """The kernels hand the generated backward code an accessor that produces a path's weight when it is asked for and
+    consumes its gradient at once (one table entry in flight): every path must be asked for once, in ascending order,
+    and its gradient handed back before the next weight is asked for.  The results equal those of the array form."""
+    rng = np.random.default_rng(L * 7 + Lin)
+    dims = (ctypes.c_int * 4)()
+    assert cpu_harness.h_tp_dims(L, Lin, dims) == 0
+    NP, NX, NM, D = list(dims)
+    x, Y, w, g = rng.normal(size=NX), rng.normal(size=D), rng.normal(size=NP), rng.normal(size=NM)
+    dw, dY, dx = np.zeros(NP), np.zeros(D), np.zeros(NX)
+    cpu_harness.h_tp(L, Lin, 1, ptr(x), ptr(Y), ptr(w), ptr(g), ptr(dw), ptr(dY), ptr(dx))
+    dw2, dY2, dx2 = np.zeros(NP), np.zeros(D), np.zeros(NX)
+    assert cpu_harness.h_tp_bwd_ordered(L, Lin, ptr(x), ptr(Y), ptr(w), ptr(g), ptr(dw2), ptr(dY2), ptr(dx2)) == 0
+    assert np.array_equal(dw, dw2) and np.array_equal(dY, dY2) and np.array_equal(dx, dx2)
+
+
 @pytest.mark.parametrize("L,Lout", RANK_PAIRS)
 def test_product_basis_matches_oracle(cpu_harness, L, Lout):
     torch.manual_seed(10 + L)
